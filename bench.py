@@ -1,0 +1,365 @@
+"""Benchmark of the identical-mode matrix product on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A STEP is one pass of the product over the FP32 GEMM shape sweep of the
+baseline's second configuration: (M, N, K) in {(4096, 4096, 4096),
+(8192, 8192, 1024), (128, 11008, 4096), (2048, 50304, 768), (1000, 1000, 1000)},
+operands i.i.d. N(0, 1) float32 from seed 0, linear-layer orientation
+C = A . W^T. The metric is whole-job GFLOP/s with 2*M*N*K flops per product.
+
+  value   operands resident in HBM, CUDA-event timed on the launching stream.
+  e2e     the same sweep through the public host-buffer call
+          (mojolearn_b200.linalg.matmul) from pinned host memory, uploads and
+          downloads inside the timed region.
+  roofline        the tiled GEMM kernel against the FP32 fused-multiply-add peak
+                  (an in-run probe; the contract's one-rounding-per-step chain
+                  cannot run on tensor cores).
+  roofline_decode the row-streaming decode kernel (INT8 weights [11008, 4096],
+                  one activation row) against the measured HBM copy bandwidth.
+  cpu_baseline    the reference's CPU algorithm (AVX2 restatement, all host
+                  threads) on a bounded sample of the same sweep.
+
+With --impl reference the CPU algorithm itself is the timed arm. Under torchrun
+(N > 1) every rank runs the sweep on its own shard of a batch N times larger
+(rows of A are independent), there is no data-path collective, and the value
+is the total work over the slowest rank's time.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SWEEP = [(4096, 4096, 4096), (8192, 8192, 1024), (128, 11008, 4096), (2048, 50304, 768), (1000, 1000, 1000)]
+DECODE_N, DECODE_K = 11008, 4096
+
+
+def sweep_flops(shapes):
+    return sum(2.0 * m * n * k for m, n, k in shapes)
+
+
+class ClockSampler(object):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([v.strip() for v in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+                power.append(float(r[3]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [s for s, p in zip(sm, power) if p > 250.0] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_sample_shapes(target_seconds, gflops_guess):
+    """A bounded sample of the sweep for the CPU arm: every shape keeps its n and k
+    (k is what the leaf rule and the fold read) and takes the first rows of A."""
+    budget = target_seconds * gflops_guess * 1e9
+    per_row = sum(2.0 * n * k for _, n, k in SWEEP)
+    rows = max(8, int(budget / per_row))
+    return [(min(m, rows), n, k) for m, n, k in SWEEP]
+
+
+def run_cpu(shapes, steps, warmup, threads):
+    import numpy as np
+    import oracle
+    rng = np.random.default_rng(0)
+    ops = []
+    for m, n, k in shapes:
+        ops.append((rng.standard_normal((m, k), dtype=np.float32), rng.standard_normal((n, k), dtype=np.float32)))
+    for _ in range(warmup):
+        for a, w in ops[2:3]:
+            oracle.gemm_rows(a[:8], w, oracle.OP_NT, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        for a, w in ops:
+            oracle.gemm_rows(a, w, oracle.OP_NT, threads=threads)
+    dt = time.perf_counter() - t0
+    return sweep_flops(shapes) * steps / dt / 1e9, dt
+
+
+def reference_arm(args, rank, world):
+    """The reference's CPU implementation of the path (its AVX2 host product,
+    restated; the reference itself is Mojo and cannot be built here), all host
+    threads, on a bounded sample of the sweep."""
+    if rank != 0:
+        return
+    threads = host_threads()
+    shapes = cpu_sample_shapes(4.0, 12.0 * threads)
+    gflops, dt = run_cpu(shapes, args.steps, min(args.warmup, 1), threads)
+    sample = "first rows of A per sweep shape, n and k exact: " + ", ".join("%dx%dx%d" % s for s in shapes)
+    line = {"impl": "reference", "metric": "identical_fp32_gemm_gflops", "value": gflops, "unit": "GFLOP/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "fp32_gemm_shape_sweep (baseline config 2), CPU arm on a bounded sample", "op": "NT",
+                       "shapes": [list(s) for s in shapes]},
+            "cpu_baseline": {"value": gflops, "unit": "GFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": gflops, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        reference_arm(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from mojolearn_b200 import _native, linalg, torch_ops
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _native.lib()
+    args.warmup = max(args.warmup, 3)
+
+    # ---- operands resident in HBM (1.5 GB per pass: far beyond the 126 MB L2) ----
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    ops = []
+    for m, n, k in SWEEP:
+        a = torch.randn((m, k), generator=gen, device=dev, dtype=torch.float32)
+        w = torch.randn((n, k), generator=gen, device=dev, dtype=torch.float32)
+        c = torch.empty((m, n), device=dev, dtype=torch.float32)
+        ops.append((a, w, c))
+
+    def one_pass():
+        for a, w, c in ops:
+            torch_ops.matmul(a, w, transpose_b=True, out=c)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        one_pass()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.b200i_launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    shape_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(SWEEP) + 1)] for _ in range(args.steps)]
+    barrier()
+    ev[0].record()
+    for s in range(args.steps):
+        shape_ev[s][0].record()
+        for i, (a, w, c) in enumerate(ops):
+            torch_ops.matmul(a, w, transpose_b=True, out=c)
+            shape_ev[s][i + 1].record()
+    ev[1].record()
+    barrier()
+    elapsed_ms = ev[0].elapsed_time(ev[1])
+    launches = lib.b200i_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    per_shape_ms = [statistics.mean(shape_ev[s][i].elapsed_time(shape_ev[s][i + 1]) for s in range(args.steps))
+                    for i in range(len(SWEEP))]
+    t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+    flops_step = sweep_flops(SWEEP) * world
+    value = flops_step * args.steps / (elapsed_ms * 1e-3) / 1e9
+
+    # ---- FP32 peak probe (scalar and packed fused multiply-add) ----
+    scratch = torch.zeros(4, device=dev)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    peaks = {}
+    for packed in (0, 1):
+        blocks, iters = sms * 8, 20000
+        for _ in range(2):
+            _native.call("b200i_ffma_probe", local_rank, None, ctypes.c_void_p(scratch.data_ptr()), blocks, iters, packed)
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(torch.cuda.default_stream(dev))
+        for _ in range(3):
+            _native.call("b200i_ffma_probe", local_rank, None, ctypes.c_void_p(scratch.data_ptr()), blocks, iters, packed)
+        e1.record(torch.cuda.default_stream(dev))
+        torch.cuda.synchronize(dev)
+        fl = 3.0 * blocks * 256 * 16 * iters * 2 * (2 if packed else 1)
+        peaks["packed" if packed else "scalar"] = fl / (e0.elapsed_time(e1) * 1e-3) / 1e12
+    fp32_peak = max(peaks.values())
+
+    # the dominant kernel: the 128x128 tile kernel (shapes 0, 1, 3 of the sweep run nothing else)
+    tile_shapes = [0, 1, 3]
+    tile_flops = sum(2.0 * SWEEP[i][0] * SWEEP[i][1] * SWEEP[i][2] for i in tile_shapes)
+    tile_ms = sum(per_shape_ms[i] for i in tile_shapes)
+    tile_tflops = tile_flops / (tile_ms * 1e-3) / 1e12
+    sm_max = (clocks or {}).get("sm_max_mhz") or 1965.0
+    roofline = {"bound": "fp32_ffma", "kernel": "gemm_tile_kernel<128,128>", "achieved": tile_tflops, "peak": fp32_peak,
+                "unit": "TFLOP/s", "frac": tile_tflops / fp32_peak,
+                "peak_source": "in-run fused-multiply-add probe (max of scalar %.1f and packed f32x2 %.1f TFLOP/s); nominal %d SMs x 128 lanes x 2 x %.0f MHz = %.1f"
+                % (peaks["scalar"], peaks["packed"], sms, sm_max, sms * 128 * 2 * sm_max * 1e6 / 1e12),
+                "launch_ms": {"%dx%dx%d" % SWEEP[i]: per_shape_ms[i] for i in range(len(SWEEP))},
+                "traffic": None}
+
+    # ---- decode kernel against HBM: INT8 weights [11008, 4096], one activation row ----
+    peaks_file = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    hbm_peak, hbm_src = 6650.0, "fallback"
+    if os.path.exists(peaks_file):
+        try:
+            hbm_peak, hbm_src = float(json.load(open(peaks_file))["hbm_gbs"]), "measured"
+        except (ValueError, KeyError):
+            pass
+    nbuf = 6  # 6 x 45 MB of weights rotate through, so no launch finds its weights in the 126 MB L2
+    g2 = torch.Generator(device=dev).manual_seed(100 + rank)
+    wq = [torch.randint(-127, 128, (DECODE_N, DECODE_K), generator=g2, device=dev, dtype=torch.int8) for _ in range(nbuf)]
+    we = torch.randint(-10, -5, (DECODE_N,), generator=g2, device=dev, dtype=torch.int32)
+    decode = {}
+    for mrows in (1, 8):
+        x = torch.randn((mrows, DECODE_K), generator=g2, device=dev)
+        y = torch.empty((mrows, DECODE_N), device=dev)
+        for i in range(nbuf):
+            torch_ops.linear_int8w(x, wq[i], exponents=we, out=y)
+        torch.cuda.synchronize(dev)
+        reps = 5
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for i in range(nbuf):
+                torch_ops.linear_int8w(x, wq[i], exponents=we, out=y)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        us = e0.elapsed_time(e1) * 1e3 / (reps * nbuf)
+        nbytes = mrows * DECODE_K * 4 + DECODE_N * DECODE_K + DECODE_N * 4 + mrows * DECODE_N * 4
+        decode[mrows] = {"us": us, "gbs": nbytes / (us * 1e-6) / 1e9, "bytes": nbytes,
+                         "tflops": 2.0 * mrows * DECODE_N * DECODE_K / (us * 1e-6) / 1e12}
+    roofline_decode = {"bound": "hbm", "kernel": "decode_kernel<int8,1>", "achieved": decode[1]["gbs"], "peak": hbm_peak,
+                       "unit": "GB/s", "frac": decode[1]["gbs"] / hbm_peak, "peak_source": hbm_src + " HBM copy bandwidth",
+                       "us_per_launch": decode[1]["us"], "algorithmic_bytes": decode[1]["bytes"], "traffic": None,
+                       "m8": decode[8], "rows_per_s_m1": 1e6 / decode[1]["us"]}
+    del wq
+
+    # ---- end to end: host buffers through linalg.matmul, pinned memory ----
+    e2e = None
+    if not args.skip_e2e:
+        host = []
+        for (m, n, k), (a, w, c) in zip(SWEEP, ops):
+            ha = torch.empty((m, k), dtype=torch.float32).pin_memory()
+            hw = torch.empty((n, k), dtype=torch.float32).pin_memory()
+            hc = torch.empty((m, n), dtype=torch.float32).pin_memory()
+            ha.copy_(a)
+            hw.copy_(w)
+            host.append((ha.numpy(), hw.numpy(), hc.numpy()))
+        e2e_steps = max(1, min(args.steps, 3))
+        for ha, hw, hc in host:
+            linalg.matmul(ha, hw, transpose_b=True, out=hc)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            for ha, hw, hc in host:
+                linalg.matmul(ha, hw, transpose_b=True, out=hc)
+        torch.cuda.synchronize(dev)
+        dt = time.perf_counter() - t0
+        tt = torch.tensor([dt], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = float(tt.item())
+        e2e = {"value": flops_step * e2e_steps / dt / 1e9, "unit": "GFLOP/s",
+               "h2d_bytes_per_step": int(sum(4 * (m * k + n * k) for m, n, k in SWEEP)),
+               "d2h_bytes_per_step": int(sum(4 * m * n for m, n, k in SWEEP)), "steps": e2e_steps,
+               "api": "mojolearn_b200.linalg.matmul(a, w, transpose_b=True, out=...) on pinned host arrays"}
+        del host
+
+    # ---- CPU baseline on rank 0 at N = 1 ----
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        threads = host_threads()
+        shapes = cpu_sample_shapes(12.0, 12.0 * threads)
+        gflops, dt = run_cpu(shapes, 1, 1, threads)
+        cpu = {"value": gflops, "unit": "GFLOP/s", "cores": threads, "kind": "port", "seconds": dt,
+               "sample": "first rows of A per sweep shape, n and k exact: " + ", ".join("%dx%dx%d" % s for s in shapes)}
+
+    if rank == 0:
+        line = {"metric": "identical_fp32_gemm_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "fp32_gemm_shape_sweep (baseline config 2)", "op": "NT (C = A . W^T)",
+                           "shapes": [list(s) for s in SWEEP], "operands": "N(0,1) float32, torch generator seed = rank",
+                           "l2": "inputs larger than L2: one pass reads 1.5 GB of operands",
+                           "bit_exact": "every product is the oracle's bits (tests/test_gpu_gemm.py)"},
+                "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
+                "roofline_decode": roofline_decode, "cpu_baseline": cpu,
+                "decode": {"metric": "int8w_decode_rows_per_s", "value": 1e6 / decode[1]["us"], "unit": "rows/s",
+                           "weights": "int8 [11008, 4096] + int32 row exponents", "rotating_weight_buffers": nbuf}}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,514 @@
+// The C ABI of libb200i.so: argument checks, plan selection, launches.
+// Declarations and the reference interfaces they replace are in include/b200i.h.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/b200i.h"
+#include "decode.cuh"
+#include "gemm_tile.cuh"
+#include "lowbit.cuh"
+
+using namespace b200i;
+
+namespace {
+
+std::atomic<long long> g_launches{0};
+
+int64_t fail(char *err, int64_t cap, const char *fmt, ...) {
+    if (err && cap > 0) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(err, (size_t)cap, fmt, ap);
+        va_end(ap);
+    }
+    return 1;
+}
+void clear(char *err, int64_t cap) {
+    if (err && cap > 0) err[0] = 0;
+}
+
+#define CUDA_TRY(expr)                                                                                      \
+    do {                                                                                                    \
+        cudaError_t e_ = (expr);                                                                            \
+        if (e_ != cudaSuccess) return fail(err, err_cap, "b200i: %s failed: %s", #expr, cudaGetErrorString(e_)); \
+    } while (0)
+
+struct DeviceInfo {
+    int sms = 148;
+    bool known = false;
+};
+DeviceInfo g_info[64];
+std::mutex g_mu;
+
+int sm_count(int device) {
+    if (device < 0 || device >= 64) return 148;
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!g_info[device].known) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && v > 0) g_info[device].sms = v;
+        g_info[device].known = true;
+    }
+    return g_info[device].sms;
+}
+
+int select_device(int64_t device, char *err, int64_t err_cap, int *out) {
+    int dev = 0;
+    if (device >= 0) {
+        dev = (int)device;
+        CUDA_TRY(cudaSetDevice(dev));
+    } else {
+        CUDA_TRY(cudaGetDevice(&dev));
+    }
+    *out = dev;
+    return 0;
+}
+
+// ---- plans -----------------------------------------------------------------------------
+enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3 };
+
+struct Plan {
+    int kind;
+    int group_leaves; // S
+    int groups;       // G
+};
+
+int pow2_floor(int v) {
+    int p = 1;
+    while (p * 2 <= v) p *= 2;
+    return p;
+}
+
+// Modelled time of a tiled plan in units of one SM-cycle-equivalent of fused
+// multiply-adds: waves of CTAs over the SM slots, each CTA running its share of
+// the leaves, plus the traffic of the group nodes when the leaves are split.
+double tiled_cost(int bm, int bn, double eff, int per_sm, long long m, long long n, int leaf, int leaves, int s, int sms) {
+    const long long tiles = ((m + bm - 1) / bm) * ((n + bn - 1) / bn);
+    const int groups = (leaves + s - 1) / s;
+    const long long ctas = tiles * groups;
+    const long long slots = (long long)sms * per_sm;
+    const long long waves = (ctas + slots - 1) / slots;
+    const double cta = (double)bm * bn * (double)leaf * s * per_sm / (128.0 * eff);
+    double t = (double)waves * cta;
+    if (groups > 1) t += (double)groups * m * n * 8.0 / (6.0e12 / 1.9e9) / 1.0 + 4000.0; // node write+read at HBM rate, second launch
+    return t + 3000.0;
+}
+
+Plan choose_plan(long long m, long long n, long long k, int sms) {
+    const int leaf = (int)leaf_size(k), leaves = (int)leaf_count(k);
+    Plan best{PLAN_T128, leaves > 0 ? leaves : 1, 1};
+    double best_t = 1e300;
+    const int max_s = pow2_floor(leaves > 0 ? leaves : 1) * ((leaves & (leaves - 1)) ? 2 : 1);
+    for (int kind = PLAN_T128; kind <= PLAN_T64; kind++) {
+        const int bm = kind == PLAN_T128 ? 128 : 64;
+        const double eff = kind == PLAN_T128 ? 1.0 : 0.72;
+        const int per_sm = kind == PLAN_T128 ? 2 : 3;
+        for (int s = max_s; s >= 1; s /= 2) {
+            const int groups = (leaves + s - 1) / s;
+            if (groups > MAX_GROUPS) break;
+            const double t = tiled_cost(bm, bm, eff, per_sm, m, n, leaf, leaves, s, sms);
+            if (t < best_t) { best_t = t; best = Plan{kind, s, groups}; }
+        }
+    }
+    if (best.groups <= 1) best.group_leaves = leaves > 0 ? leaves : 1;
+    return best;
+}
+
+bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const void *b, const void *bscale, int wkind,
+                       int64_t m, int64_t n, int64_t k, int op, int plan_kind, int64_t group_leaves, void *ws,
+                       int64_t ws_bytes, char *err, int64_t err_cap) {
+    if (m <= 0 || n <= 0 || k <= 0)
+        return fail(err, err_cap, "identical gemm: m, n and k must be positive (got m=%lld n=%lld k=%lld)", (long long)m,
+                    (long long)n, (long long)k);
+    if (op != OP_NN && op != OP_NT && op != OP_TN) return fail(err, err_cap, "identical gemm: unknown op %d", op);
+    if (wkind < W_F32 || wkind > W_INT8_SCALE) return fail(err, err_cap, "identical gemm: unknown weight kind %d", wkind);
+    if ((wkind == W_INT8_EXP || wkind == W_INT8_SCALE) && op != OP_NT)
+        return fail(err, err_cap, "identical gemm: int8 weight storage is row-scaled and needs op NT");
+    if ((wkind == W_INT8_EXP || wkind == W_INT8_SCALE) && !bscale)
+        return fail(err, err_cap, "identical gemm: int8 weight storage needs its per-row exponents or scales");
+    if (!c || !a || !b) return fail(err, err_cap, "identical gemm: null storage");
+    if (m > 0x7FFFFFFF || n > 0x7FFFFFFF || k > 0x7FFFFFFF || m * n > 0x7FFFFFFFll * 64)
+        return fail(err, err_cap, "identical gemm: extent out of range");
+    if (!aligned(c, 4) || !aligned(a, 4) || (wkind == W_F32 && !aligned(b, 4)) || (wkind == W_BF16 && !aligned(b, 2)))
+        return fail(err, err_cap, "identical gemm: misaligned storage");
+
+    GemmArgs g;
+    g.a = a; g.b = b; g.bscale = bscale; g.c = c; g.ws = static_cast<float *>(ws);
+    g.m = (int)m; g.n = (int)n; g.k = (int)k; g.op = op; g.wkind = wkind;
+    g.leaf = (int)leaf_size(k);
+    g.leaves = (int)leaf_count(k);
+
+    Plan plan;
+    if (plan_kind == PLAN_AUTO) {
+        plan = choose_plan(m, n, k, sm_count(dev));
+        if (decode_plan_fits(m, n, k, op) && aligned(b, 16)) plan = Plan{PLAN_DECODE, g.leaves, 1};
+    } else {
+        plan.kind = plan_kind;
+        int s = group_leaves > 0 ? (int)group_leaves : g.leaves;
+        if (s & (s - 1)) {
+            if (s < g.leaves) return fail(err, err_cap, "identical gemm: a leaf group must be a power of two");
+        }
+        if (s > g.leaves) s = g.leaves;
+        plan.group_leaves = s;
+        plan.groups = (g.leaves + s - 1) / s;
+        if (plan.groups > 1 && (s & (s - 1))) return fail(err, err_cap, "identical gemm: a leaf group must be a power of two");
+        if (plan.groups > MAX_GROUPS) return fail(err, err_cap, "identical gemm: more than %d leaf groups", MAX_GROUPS);
+        if (plan.kind == PLAN_FLAT || plan.kind == PLAN_DECODE) { plan.groups = 1; plan.group_leaves = g.leaves; }
+    }
+    g.group_leaves = plan.group_leaves;
+    g.groups = plan.groups;
+    if (plan.groups > 1) {
+        const int64_t need = (int64_t)plan.groups * m * n * 4;
+        if (!ws || ws_bytes < need)
+            return fail(err, err_cap, "identical gemm: workspace of %lld bytes needed, %lld given", (long long)need,
+                        (long long)ws_bytes);
+    }
+
+    // 128-bit access is legal when the contiguous axis keeps every vector inside a row and aligned
+    const bool a_kc = (op != OP_TN), b_kc = (op == OP_NT);
+    const bool leaf_ok = (g.leaves == 1) || (g.leaf % 4 == 0);
+    g.vec_a = a_kc ? (k % 4 == 0 && leaf_ok && aligned(a, 16)) : (m % 4 == 0 && aligned(a, 16));
+    const size_t balign = wkind == W_F32 ? 16 : (wkind == W_BF16 ? 8 : 4);
+    g.vec_b = b_kc ? (k % 4 == 0 && leaf_ok && aligned(b, balign)) : (n % 4 == 0 && aligned(b, balign));
+    g.vec_c = (n % 4 == 0) && aligned(c, 16) && (plan.groups == 1 || aligned(ws, 16));
+
+    if (plan.kind == PLAN_FLAT) {
+        const long long cells = (long long)m * n;
+        gemm_flat_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(g);
+        g_launches++;
+    } else if (plan.kind == PLAN_DECODE) {
+        if (!decode_plan_fits(m, n, k, op) || !aligned(b, 16))
+            return fail(err, err_cap, "identical gemm: the decode plan needs op NT, m <= %d, k a multiple of 16 and 16-byte aligned weights", DECODE_MAX_M);
+        g_launches += launch_decode(g, sm_count(dev), st);
+    } else if (plan.kind == PLAN_T128) {
+        g.tiles_n = (int)((n + 127) / 128);
+        dim3 grid((unsigned)(((m + 127) / 128) * g.tiles_n), (unsigned)plan.groups);
+        gemm_tile_kernel<128, 128, 2, 2, 2><<<grid, 256, 0, st>>>(g);
+        g_launches++;
+    } else if (plan.kind == PLAN_T64) {
+        g.tiles_n = (int)((n + 63) / 64);
+        dim3 grid((unsigned)(((m + 63) / 64) * g.tiles_n), (unsigned)plan.groups);
+        gemm_tile_kernel<64, 64, 1, 1, 3><<<grid, 256, 0, st>>>(g);
+        g_launches++;
+    } else {
+        return fail(err, err_cap, "identical gemm: unknown plan %d", plan.kind);
+    }
+    if (plan.groups > 1) {
+        const long long cells = (long long)m * n;
+        fold_groups_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(g.ws, c, cells, plan.groups);
+        g_launches++;
+    }
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+// Grow-only per-device scratch for the host-pointer twins.
+struct HostPool {
+    void *buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    size_t cap[5] = {0, 0, 0, 0, 0};
+    cudaStream_t stream = nullptr;
+};
+HostPool g_pool[64];
+std::mutex g_pool_mu;
+
+cudaError_t pool_get(int dev, int slot, size_t bytes, void **out) {
+    HostPool &p = g_pool[dev];
+    if (p.cap[slot] < bytes) {
+        if (p.buf[slot]) cudaFree(p.buf[slot]);
+        p.buf[slot] = nullptr;
+        p.cap[slot] = 0;
+        size_t want = bytes + (bytes >> 3) + 256;
+        cudaError_t e = cudaMalloc(&p.buf[slot], want);
+        if (e != cudaSuccess) return e;
+        p.cap[slot] = want;
+    }
+    *out = p.buf[slot];
+    return cudaSuccess;
+}
+
+size_t wkind_elem_bytes(int wkind) { return wkind == W_F32 ? 4 : (wkind == W_BF16 ? 2 : 1); }
+
+} // namespace
+
+extern "C" {
+
+int64_t b200i_abi(void) { return 1; }
+int64_t b200i_numeric_mode(void) { return 1; }
+int64_t b200i_profile_version(void) { return 1; }
+int64_t b200i_lowbit_profile_version(void) { return 1; }
+const char *b200i_numerical_profile(void) { return "mojolearn.identical.gemm.fp32.v1"; }
+const char *b200i_vendor(void) { return "cuda"; }
+int64_t b200i_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+int64_t b200i_launch_count(void) { return g_launches.load(); }
+
+int64_t b200i_decode_status(int64_t device) {
+    if (device >= 0 && cudaSetDevice((int)device) != cudaSuccess) { cudaGetLastError(); return -1; }
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return -1; }
+    return v;
+}
+
+int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+    if (m <= 0 || n <= 0 || k <= 0) return 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = -1; }
+    if (decode_plan_fits(m, n, k, OP_NT)) {
+        // the decode plan needs none; a tiled plan may still run for another op
+    }
+    Plan p = choose_plan(m, n, k, sm_count(dev));
+    return p.groups > 1 ? (int64_t)p.groups * m * n * 4 : 0;
+}
+
+int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale,
+                          int64_t wkind, int64_t m, int64_t n, int64_t k, int64_t op, int64_t plan, int64_t group_leaves,
+                          void *ws, int64_t ws_bytes, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    return launch_product(dev, static_cast<cudaStream_t>(stream), c, a, b, bscale, (int)wkind, m, n, k, (int)op, (int)plan,
+                          group_leaves, ws, ws_bytes, err, err_cap);
+}
+
+int64_t b200i_gemm_w(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale,
+                     int64_t wkind, int64_t m, int64_t n, int64_t k, int64_t op, void *ws, int64_t ws_bytes, char *err,
+                     int64_t err_cap) {
+    return b200i_gemm_w_plan(device, stream, c, a, b, bscale, wkind, m, n, k, op, PLAN_AUTO, 0, ws, ws_bytes, err, err_cap);
+}
+
+int64_t b200i_gemm_f32(int64_t device, void *stream, float *c, const float *a, const float *b, int64_t m, int64_t n,
+                       int64_t k, int64_t op, void *ws, int64_t ws_bytes, char *err, int64_t err_cap) {
+    return b200i_gemm_w_plan(device, stream, c, a, b, nullptr, W_F32, m, n, k, op, PLAN_AUTO, 0, ws, ws_bytes, err, err_cap);
+}
+
+static unsigned grid_for(long long work_items, int block, int sms) {
+    long long blocks = (work_items + block - 1) / block;
+    const long long cap = (long long)sms * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (unsigned)blocks;
+}
+
+int64_t b200i_to_bf16(int64_t device, void *stream, uint16_t *dst, const float *src, int64_t count, char *err,
+                      int64_t err_cap) {
+    clear(err, err_cap);
+    if (count < 0 || (count > 0 && (!dst || !src))) return fail(err, err_cap, "to_bf16: null storage or negative count");
+    if (count == 0) return 0;
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    to_bf16_kernel<<<grid_for((count + 3) / 4, 256, sm_count(dev)), 256, 0, static_cast<cudaStream_t>(stream)>>>(dst, src, count);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_from_bf16(int64_t device, void *stream, float *dst, const uint16_t *src, int64_t count, char *err,
+                        int64_t err_cap) {
+    clear(err, err_cap);
+    if (count < 0 || (count > 0 && (!dst || !src))) return fail(err, err_cap, "from_bf16: null storage or negative count");
+    if (count == 0) return 0;
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    from_bf16_kernel<<<grid_for((count + 3) / 4, 256, sm_count(dev)), 256, 0, static_cast<cudaStream_t>(stream)>>>(dst, src, count);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_quantize_int8(int64_t device, void *stream, int8_t *codes, int32_t *exponents, const float *x, int64_t rows,
+                            int64_t cols, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    if (rows <= 0 || cols <= 0) return fail(err, err_cap, "quantize_int8: rows and cols must be positive");
+    if (!codes || !exponents || !x) return fail(err, err_cap, "quantize_int8: null storage");
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    quantize_int8_kernel<<<grid_for(rows * 32, 256, sm_count(dev)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<signed char *>(codes), exponents, x, rows, cols);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_dequantize_int8(int64_t device, void *stream, float *y, const int8_t *codes, const int32_t *exponents,
+                              int64_t rows, int64_t cols, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    if (rows <= 0 || cols <= 0) return fail(err, err_cap, "dequantize_int8: rows and cols must be positive");
+    if (!codes || !exponents || !y) return fail(err, err_cap, "dequantize_int8: null storage");
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    dequantize_int8_kernel<<<grid_for(rows * cols, 256, sm_count(dev)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        y, reinterpret_cast<const signed char *>(codes), exponents, rows, cols);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_gemm_int8(int64_t device, void *stream, float *c, const int8_t *qa, const int32_t *ea, const int8_t *qb,
+                        const int32_t *eb, int64_t m, int64_t n, int64_t k, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    if (m <= 0 || n <= 0 || k <= 0) return fail(err, err_cap, "identical int8 gemm: m, n and k must be positive");
+    if (k > 131072) return fail(err, err_cap, "identical int8 gemm: k = %lld exceeds INT8_MAX_K = 131072", (long long)k);
+    if (!c || !qa || !ea || !qb || !eb) return fail(err, err_cap, "identical int8 gemm: null storage");
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    const long long cells = m * n;
+    gemm_int8_flat_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        c, reinterpret_cast<const signed char *>(qa), ea, reinterpret_cast<const signed char *>(qb), eb, (int)m, (int)n, (int)k);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_ffma_probe(int64_t device, void *stream, float *scratch, int64_t blocks, int64_t iters, int64_t packed,
+                         char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    if (!scratch || blocks <= 0 || iters <= 0) return fail(err, err_cap, "ffma_probe: bad arguments");
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    ffma_probe_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(scratch, (int)iters, (int)packed, 1.0f);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+// ---- host-pointer twins -------------------------------------------------------------------
+
+int64_t b200i_host_gemm_w(int64_t device, float *c, const float *a, const void *b, const void *bscale, int64_t wkind,
+                          int64_t m, int64_t n, int64_t k, int64_t op, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    if (m <= 0 || n <= 0 || k <= 0)
+        return fail(err, err_cap, "identical gemm: m, n and k must be positive (got m=%lld n=%lld k=%lld)", (long long)m,
+                    (long long)n, (long long)k);
+    if (wkind < W_F32 || wkind > W_INT8_SCALE) return fail(err, err_cap, "identical gemm: unknown weight kind %lld", (long long)wkind);
+    if (!c || !a || !b) return fail(err, err_cap, "identical gemm: null storage");
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    std::lock_guard<std::mutex> lock(g_pool_mu);
+    HostPool &pool = g_pool[dev];
+    if (!pool.stream) CUDA_TRY(cudaStreamCreateWithFlags(&pool.stream, cudaStreamNonBlocking));
+    const size_t abytes = (size_t)m * k * 4, bbytes = (size_t)n * k * wkind_elem_bytes((int)wkind), cbytes = (size_t)m * n * 4;
+    const size_t sbytes = (wkind >= W_INT8_EXP) ? (size_t)n * 4 : 0;
+    const int64_t wsbytes = b200i_workspace_bytes(m, n, k);
+    void *da, *db, *dc, *ds = nullptr, *dw = nullptr;
+    CUDA_TRY(pool_get(dev, 0, abytes, &da));
+    CUDA_TRY(pool_get(dev, 1, bbytes, &db));
+    CUDA_TRY(pool_get(dev, 2, cbytes, &dc));
+    if (sbytes) CUDA_TRY(pool_get(dev, 3, sbytes, &ds));
+    if (wsbytes) CUDA_TRY(pool_get(dev, 4, (size_t)wsbytes, &dw));
+    CUDA_TRY(cudaMemcpyAsync(da, a, abytes, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(db, b, bbytes, cudaMemcpyHostToDevice, pool.stream));
+    if (sbytes) {
+        if (!bscale) return fail(err, err_cap, "identical gemm: int8 weight storage needs its per-row exponents or scales");
+        CUDA_TRY(cudaMemcpyAsync(ds, bscale, sbytes, cudaMemcpyHostToDevice, pool.stream));
+    }
+    if (launch_product(dev, pool.stream, static_cast<float *>(dc), static_cast<const float *>(da), db, ds, (int)wkind, m, n, k,
+                       (int)op, PLAN_AUTO, 0, dw, wsbytes, err, err_cap))
+        return 1;
+    CUDA_TRY(cudaMemcpyAsync(c, dc, cbytes, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaStreamSynchronize(pool.stream));
+    return 0;
+}
+
+#define HOST_PREP()                                                                  \
+    clear(err, err_cap);                                                             \
+    int dev;                                                                         \
+    if (select_device(device, err, err_cap, &dev)) return 1;                         \
+    std::lock_guard<std::mutex> lock(g_pool_mu);                                     \
+    HostPool &pool = g_pool[dev];                                                    \
+    if (!pool.stream) CUDA_TRY(cudaStreamCreateWithFlags(&pool.stream, cudaStreamNonBlocking))
+
+int64_t b200i_host_to_bf16(int64_t device, uint16_t *dst, const float *src, int64_t count, char *err, int64_t err_cap) {
+    if (count < 0) return fail(err, err_cap, "to_bf16: negative count");
+    if (count == 0) { clear(err, err_cap); return 0; }
+    HOST_PREP();
+    void *ds, *dd;
+    CUDA_TRY(pool_get(dev, 0, (size_t)count * 4, &ds));
+    CUDA_TRY(pool_get(dev, 1, (size_t)count * 2, &dd));
+    CUDA_TRY(cudaMemcpyAsync(ds, src, (size_t)count * 4, cudaMemcpyHostToDevice, pool.stream));
+    if (b200i_to_bf16(dev, pool.stream, static_cast<uint16_t *>(dd), static_cast<const float *>(ds), count, err, err_cap)) return 1;
+    CUDA_TRY(cudaMemcpyAsync(dst, dd, (size_t)count * 2, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaStreamSynchronize(pool.stream));
+    return 0;
+}
+
+int64_t b200i_host_from_bf16(int64_t device, float *dst, const uint16_t *src, int64_t count, char *err, int64_t err_cap) {
+    if (count < 0) return fail(err, err_cap, "from_bf16: negative count");
+    if (count == 0) { clear(err, err_cap); return 0; }
+    HOST_PREP();
+    void *ds, *dd;
+    CUDA_TRY(pool_get(dev, 0, (size_t)count * 2, &ds));
+    CUDA_TRY(pool_get(dev, 1, (size_t)count * 4, &dd));
+    CUDA_TRY(cudaMemcpyAsync(ds, src, (size_t)count * 2, cudaMemcpyHostToDevice, pool.stream));
+    if (b200i_from_bf16(dev, pool.stream, static_cast<float *>(dd), static_cast<const uint16_t *>(ds), count, err, err_cap)) return 1;
+    CUDA_TRY(cudaMemcpyAsync(dst, dd, (size_t)count * 4, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaStreamSynchronize(pool.stream));
+    return 0;
+}
+
+int64_t b200i_host_quantize_int8(int64_t device, int8_t *codes, int32_t *exponents, const float *x, int64_t rows,
+                                 int64_t cols, char *err, int64_t err_cap) {
+    if (rows <= 0 || cols <= 0) return fail(err, err_cap, "quantize_int8: rows and cols must be positive");
+    HOST_PREP();
+    void *dx, *dq, *de;
+    CUDA_TRY(pool_get(dev, 0, (size_t)rows * cols * 4, &dx));
+    CUDA_TRY(pool_get(dev, 1, (size_t)rows * cols, &dq));
+    CUDA_TRY(pool_get(dev, 2, (size_t)rows * 4, &de));
+    CUDA_TRY(cudaMemcpyAsync(dx, x, (size_t)rows * cols * 4, cudaMemcpyHostToDevice, pool.stream));
+    if (b200i_quantize_int8(dev, pool.stream, static_cast<int8_t *>(dq), static_cast<int32_t *>(de), static_cast<const float *>(dx),
+                            rows, cols, err, err_cap))
+        return 1;
+    CUDA_TRY(cudaMemcpyAsync(codes, dq, (size_t)rows * cols, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(exponents, de, (size_t)rows * 4, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaStreamSynchronize(pool.stream));
+    return 0;
+}
+
+int64_t b200i_host_dequantize_int8(int64_t device, float *y, const int8_t *codes, const int32_t *exponents, int64_t rows,
+                                   int64_t cols, char *err, int64_t err_cap) {
+    if (rows <= 0 || cols <= 0) return fail(err, err_cap, "dequantize_int8: rows and cols must be positive");
+    HOST_PREP();
+    void *dy, *dq, *de;
+    CUDA_TRY(pool_get(dev, 0, (size_t)rows * cols * 4, &dy));
+    CUDA_TRY(pool_get(dev, 1, (size_t)rows * cols, &dq));
+    CUDA_TRY(pool_get(dev, 2, (size_t)rows * 4, &de));
+    CUDA_TRY(cudaMemcpyAsync(dq, codes, (size_t)rows * cols, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(de, exponents, (size_t)rows * 4, cudaMemcpyHostToDevice, pool.stream));
+    if (b200i_dequantize_int8(dev, pool.stream, static_cast<float *>(dy), static_cast<const int8_t *>(dq),
+                              static_cast<const int32_t *>(de), rows, cols, err, err_cap))
+        return 1;
+    CUDA_TRY(cudaMemcpyAsync(y, dy, (size_t)rows * cols * 4, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaStreamSynchronize(pool.stream));
+    return 0;
+}
+
+int64_t b200i_host_gemm_int8(int64_t device, float *c, const int8_t *qa, const int32_t *ea, const int8_t *qb,
+                             const int32_t *eb, int64_t m, int64_t n, int64_t k, char *err, int64_t err_cap) {
+    if (m <= 0 || n <= 0 || k <= 0) return fail(err, err_cap, "identical int8 gemm: m, n and k must be positive");
+    if (k > 131072) return fail(err, err_cap, "identical int8 gemm: k = %lld exceeds INT8_MAX_K = 131072", (long long)k);
+    HOST_PREP();
+    void *dqa, *dqb, *dc, *dea, *deb;
+    CUDA_TRY(pool_get(dev, 0, (size_t)m * k, &dqa));
+    CUDA_TRY(pool_get(dev, 1, (size_t)n * k, &dqb));
+    CUDA_TRY(pool_get(dev, 2, (size_t)m * n * 4, &dc));
+    CUDA_TRY(pool_get(dev, 3, (size_t)m * 4, &dea));
+    CUDA_TRY(pool_get(dev, 4, (size_t)n * 4, &deb));
+    CUDA_TRY(cudaMemcpyAsync(dqa, qa, (size_t)m * k, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(dqb, qb, (size_t)n * k, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(dea, ea, (size_t)m * 4, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(deb, eb, (size_t)n * 4, cudaMemcpyHostToDevice, pool.stream));
+    if (b200i_gemm_int8(dev, pool.stream, static_cast<float *>(dc), static_cast<const int8_t *>(dqa), static_cast<const int32_t *>(dea),
+                        static_cast<const int8_t *>(dqb), static_cast<const int32_t *>(deb), m, n, k, err, err_cap))
+        return 1;
+    CUDA_TRY(cudaMemcpyAsync(c, dc, (size_t)m * n * 4, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaStreamSynchronize(pool.stream));
+    return 0;
+}
+
+} // extern "C"

@@ -1,0 +1,43 @@
+"""Compile libb200i.so (the CUDA kernels and their C ABI) for sm_100a, in tree.
+
+    python -m mojolearn_b200.csrc.build [--force] [--verbose]
+
+nvcc cross-compiles without a GPU. The flags are part of the numerical
+contract: no multiply-add contraction by the compiler (-fmad=false), IEEE
+subnormals (-ftz=false), IEEE division and square root, no fast-math. Every
+fused multiply-add in the kernels is an explicit fma.rn.
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB = os.path.join(HERE, "libb200i.so")
+SOURCES = ["b200i.cu"]
+HEADERS = ["seams.cuh", "gemm_tile.cuh", "decode.cuh", "lowbit.cuh", os.path.join("..", "..", "include", "b200i.h")]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-fmad=false", "-ftz=false", "-prec-div=true", "-prec-sqrt=true",
+    "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "-cudart", "shared",
+]
+
+
+def stale():
+    if not os.path.exists(LIB):
+        return True
+    t = os.path.getmtime(LIB)
+    deps = [os.path.join(HERE, s) for s in SOURCES + HEADERS] + [os.path.abspath(__file__)]
+    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+
+
+def build(force=False, verbose=False):
+    if not force and not stale():
+        return LIB
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [os.path.join(HERE, s) for s in SOURCES] + ["-o", LIB]
+    subprocess.run(cmd, check=True)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,425 @@
+// The tiled identical-mode GEMM kernel for sm_100a.
+//
+// NUMERICAL PLAN (fixed by the contract, gemm/IDENTICAL_FP32_CONTRACT.md and
+// gemm/host/gemm_oracle.mojo:146-371 of the reference): k is cut into leaves of
+// leaf_size(k) elements; a cell's leaf partial is ONE accumulator seeded +0.0
+// and advanced p-ascending by acc = ftz(fma_rn(ftz(a), ftz(b), acc)); the
+// partials are folded by the fixed adjacent-pair tree with an odd tail carried.
+//
+// EXECUTION PLAN (free, and chosen here for B200): a CTA owns a BM x BN tile of
+// C and a power-of-two aligned group of leaves. Operands are staged global ->
+// registers -> shared memory in windows of 16 k-steps, double buffered, with
+// 128-bit loads and stores; while a window is staged every thread folds the
+// admission key of the words it touched, and the __syncthreads_and that
+// publishes the window also publishes whether it is admitted. An admitted
+// window runs the bare packed fma (fma.rn.f32x2: two cells per instruction,
+// which leaves issue slots for the shared-memory loads); any other window, and
+// the rest of its leaf, runs fma + flush. A window never crosses a leaf
+// boundary and a ragged k tail is looped, never zero padded (a padded step
+// would turn a -0.0 accumulator into +0.0). At a leaf boundary the partial is
+// pushed on a per-thread binary-counter stack, which merges (2q, 2q+1) pairs
+// as soon as both exist and carries an odd tail at the drain: the contract's
+// tree evaluated in streaming order.
+#pragma once
+#include "seams.cuh"
+
+namespace b200i {
+
+struct GemmArgs {
+    const float *a;     // left operand, float32
+    const void *b;      // right operand, storage per wkind
+    const void *bscale; // int32 exponents or float32 scales, one per right-operand row (int8 kinds)
+    float *c;           // m x n output
+    float *ws;          // group nodes [groups][m][n] when groups > 1
+    int m, n, k, op, wkind;
+    int leaf, leaves;         // L and P
+    int group_leaves, groups; // S (a power of two) and ceil(P / S)
+    int vec_a, vec_b, vec_c;  // operand may be read / written with 128-bit accesses
+    int tiles_n;
+};
+
+constexpr int KS = 16;       // k-steps per staged window
+constexpr int FOLD_LEVELS = 11; // 2^10 = MAX_LEAVES
+
+template <int BM, int BN, int RM, int RN>
+struct TileShape {
+    static constexpr int TX = BN / (4 * RN), TY = BM / (4 * RM), THREADS = TX * TY;
+    static constexpr int TM = 4 * RM, TN = 4 * RN;
+    static constexpr int UNITS = BM + BN; // staging units of 16 words each
+    static constexpr int UPT = (UNITS + THREADS - 1) / THREADS;
+};
+
+// ---- staging -------------------------------------------------------------------
+// A unit is 16 words of one operand's window: either 4 rows x 4 consecutive k
+// of a k-contiguous operand (transposed through registers on the way to shared
+// memory) or 4 k-rows x 4 consecutive cells of a cell-contiguous operand.
+
+__device__ __forceinline__ float4 ld4_f32(const float *p, bool vec, int valid) {
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (valid <= 0) return r;
+    if (vec) return __ldg(reinterpret_cast<const float4 *>(p));
+    r.x = __ldg(p);
+    if (valid > 1) r.y = __ldg(p + 1);
+    if (valid > 2) r.z = __ldg(p + 2);
+    if (valid > 3) r.w = __ldg(p + 3);
+    return r;
+}
+__device__ __forceinline__ float4 ld4_bf16(const unsigned short *p, bool vec, int valid) {
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (valid <= 0) return r;
+    if (vec) {
+        uint2 w = __ldg(reinterpret_cast<const uint2 *>(p));
+        r.x = __uint_as_float(w.x << 16);
+        r.y = __uint_as_float(w.x & 0xFFFF0000u);
+        r.z = __uint_as_float(w.y << 16);
+        r.w = __uint_as_float(w.y & 0xFFFF0000u);
+        return r;
+    }
+    r.x = bf16_bits_to_f32(__ldg(p));
+    if (valid > 1) r.y = bf16_bits_to_f32(__ldg(p + 1));
+    if (valid > 2) r.z = bf16_bits_to_f32(__ldg(p + 2));
+    if (valid > 3) r.w = bf16_bits_to_f32(__ldg(p + 3));
+    return r;
+}
+// int8 codes times one row factor; `pinned` picks the power-of-two spelling
+// (code * 2^e, flushed) or the general scale (code * s, one pinned product, flushed).
+__device__ __forceinline__ float4 ld4_int8(const signed char *p, bool vec, int valid, float factor) {
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (valid <= 0) return r;
+    int c0, c1 = 0, c2 = 0, c3 = 0;
+    if (vec) {
+        int w = __ldg(reinterpret_cast<const int *>(p));
+        c0 = (int)(signed char)(w & 0xFF);
+        c1 = (int)(signed char)((w >> 8) & 0xFF);
+        c2 = (int)(signed char)((w >> 16) & 0xFF);
+        c3 = w >> 24;
+        valid = 4;
+    } else {
+        c0 = __ldg(p);
+        if (valid > 1) c1 = __ldg(p + 1);
+        if (valid > 2) c2 = __ldg(p + 2);
+        if (valid > 3) c3 = __ldg(p + 3);
+    }
+    r.x = dequant_int8_pow2(c0, factor);
+    if (valid > 1) r.y = dequant_int8_pow2(c1, factor);
+    if (valid > 2) r.z = dequant_int8_pow2(c2, factor);
+    if (valid > 3) r.w = dequant_int8_pow2(c3, factor);
+    return r;
+}
+
+__device__ __forceinline__ unsigned key4(float4 v, unsigned k) {
+    k = min(k, admit_key(v.x));
+    k = min(k, admit_key(v.y));
+    k = min(k, admit_key(v.z));
+    k = min(k, admit_key(v.w));
+    return k;
+}
+
+// Loads one unit of the left operand (E = BM, origin e0 = first row of the
+// tile) or of the right operand (E = BN). `kcontig` says the operand's storage
+// is contiguous along k.
+template <int E>
+__device__ __forceinline__ void unit_load(float4 (&r)[4], int u, const void *base, int wkind, const void *scale,
+                                          bool kcontig, bool vec, int e0, int extent, int kdim, int k0) {
+    const int lane_e = u % (E / 4), quad = u / (E / 4);
+    if (kcontig) {
+        const int kk = k0 + 4 * quad;
+        const int kvalid = kdim - kk;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int row = e0 + 4 * lane_e + c;
+            const int valid = (row < extent) ? kvalid : 0;
+            const size_t off = (size_t)row * (size_t)kdim + (size_t)kk;
+            if (wkind == W_F32) r[c] = ld4_f32(static_cast<const float *>(base) + off, vec, valid);
+            else if (wkind == W_BF16) r[c] = ld4_bf16(static_cast<const unsigned short *>(base) + off, vec, valid);
+            else {
+                float factor = 0.f;
+                if (valid > 0)
+                    factor = (wkind == W_INT8_EXP) ? pow2_f32(__ldg(static_cast<const int *>(scale) + row))
+                                                   : __ldg(static_cast<const float *>(scale) + row);
+                r[c] = ld4_int8(static_cast<const signed char *>(base) + off, vec, valid, factor);
+            }
+        }
+    } else {
+        const int col = e0 + 4 * lane_e;
+        const int cvalid = extent - col;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int kk = k0 + 4 * quad + c;
+            const int valid = (kk < kdim) ? cvalid : 0;
+            const size_t off = (size_t)kk * (size_t)extent + (size_t)col;
+            if (wkind == W_BF16) r[c] = ld4_bf16(static_cast<const unsigned short *>(base) + off, vec, valid);
+            else r[c] = ld4_f32(static_cast<const float *>(base) + off, vec, valid);
+        }
+    }
+}
+
+template <int E>
+__device__ __forceinline__ void unit_store(const float4 (&r)[4], int u, float (*dst)[E], bool kcontig) {
+    const int lane_e = u % (E / 4), quad = u / (E / 4);
+    if (kcontig) {
+        *reinterpret_cast<float4 *>(&dst[4 * quad + 0][4 * lane_e]) = make_float4(r[0].x, r[1].x, r[2].x, r[3].x);
+        *reinterpret_cast<float4 *>(&dst[4 * quad + 1][4 * lane_e]) = make_float4(r[0].y, r[1].y, r[2].y, r[3].y);
+        *reinterpret_cast<float4 *>(&dst[4 * quad + 2][4 * lane_e]) = make_float4(r[0].z, r[1].z, r[2].z, r[3].z);
+        *reinterpret_cast<float4 *>(&dst[4 * quad + 3][4 * lane_e]) = make_float4(r[0].w, r[1].w, r[2].w, r[3].w);
+    } else {
+#pragma unroll
+        for (int c = 0; c < 4; c++) *reinterpret_cast<float4 *>(&dst[4 * quad + c][4 * lane_e]) = r[c];
+    }
+}
+
+// ---- the kernel -------------------------------------------------------------------
+
+template <int BM, int BN, int RM, int RN, int MINB>
+__global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) gemm_tile_kernel(const GemmArgs g) {
+    using S = TileShape<BM, BN, RM, RN>;
+    constexpr int TM = S::TM, TN = S::TN, NT = S::THREADS, UPT = S::UPT;
+    __shared__ __align__(16) float As[2][KS][BM];
+    __shared__ __align__(16) float Bs[2][KS][BN];
+
+    const int tid = threadIdx.x;
+    const int tx = tid % S::TX, ty = tid / S::TX;
+    const int bm0 = (blockIdx.x / g.tiles_n) * BM;
+    const int bn0 = (blockIdx.x % g.tiles_n) * BN;
+    const bool a_kcontig = (g.op != OP_TN);
+    const bool b_kcontig = (g.op == OP_NT);
+
+    const int t_first = blockIdx.y * g.group_leaves;
+    const int t_end = min(t_first + g.group_leaves, g.leaves);
+
+    // accumulators: TM rows x TN/2 packed column pairs
+    unsigned long long acc[TM][TN / 2];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN / 2; j++) acc[i][j] = 0ull;
+
+    float stack[FOLD_LEVELS][TM * TN]; // local memory; touched once per leaf
+
+    float4 stage[UPT][4];
+    unsigned stage_key;
+
+    auto load_window = [&](int t, int koff) {
+        const int k0 = t * g.leaf + koff;
+        stage_key = 0xFFFFFFFFu;
+#pragma unroll
+        for (int i = 0; i < UPT; i++) {
+            const int u = tid + i * NT;
+            if (u < BM) unit_load<BM>(stage[i], u, g.a, W_F32, nullptr, a_kcontig, g.vec_a, bm0, g.m, g.k, k0);
+            else if (u < BM + BN)
+                unit_load<BN>(stage[i], u - BM, g.b, g.wkind, g.bscale, b_kcontig, g.vec_b, bn0, g.n, g.k, k0);
+            if (u < BM + BN) {
+#pragma unroll
+                for (int c = 0; c < 4; c++) stage_key = key4(stage[i][c], stage_key);
+            }
+        }
+    };
+    auto store_window = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < UPT; i++) {
+            const int u = tid + i * NT;
+            if (u < BM) unit_store<BM>(stage[i], u, As[buf], a_kcontig);
+            else if (u < BM + BN) unit_store<BN>(stage[i], u - BM, Bs[buf], b_kcontig);
+        }
+    };
+
+    auto read_operands = [&](int buf, int kk, float (&av)[TM], float (&bv)[TN]) {
+#pragma unroll
+        for (int r = 0; r < RM; r++) {
+            const float4 v = *reinterpret_cast<const float4 *>(&As[buf][kk][r * (BM / RM) + ty * 4]);
+            av[4 * r + 0] = v.x; av[4 * r + 1] = v.y; av[4 * r + 2] = v.z; av[4 * r + 3] = v.w;
+        }
+#pragma unroll
+        for (int r = 0; r < RN; r++) {
+            const float4 v = *reinterpret_cast<const float4 *>(&Bs[buf][kk][r * (BN / RN) + tx * 4]);
+            bv[4 * r + 0] = v.x; bv[4 * r + 1] = v.y; bv[4 * r + 2] = v.z; bv[4 * r + 3] = v.w;
+        }
+    };
+    auto step_fast = [&](int buf, int kk) {
+        float av[TM], bv[TN];
+        read_operands(buf, kk, av, bv);
+        unsigned long long b2[TN / 2];
+#pragma unroll
+        for (int j = 0; j < TN / 2; j++) b2[j] = pack2(bv[2 * j], bv[2 * j + 1]);
+#pragma unroll
+        for (int i = 0; i < TM; i++) {
+            const unsigned long long a2 = pack2(av[i], av[i]);
+#pragma unroll
+            for (int j = 0; j < TN / 2; j++) acc[i][j] = fma2_bare(a2, b2[j], acc[i][j]);
+        }
+    };
+    auto step_slow = [&](int buf, int kk) {
+        float av[TM], bv[TN];
+        read_operands(buf, kk, av, bv);
+        unsigned long long b2[TN / 2];
+#pragma unroll
+        for (int j = 0; j < TN / 2; j++) b2[j] = pack2(ftz_bits(bv[2 * j]), ftz_bits(bv[2 * j + 1]));
+#pragma unroll
+        for (int i = 0; i < TM; i++) {
+            const float af = ftz_bits(av[i]);
+            const unsigned long long a2 = pack2(af, af);
+#pragma unroll
+            for (int j = 0; j < TN / 2; j++) acc[i][j] = ftz2_hw(fma2_bare(a2, b2[j], acc[i][j]));
+        }
+    };
+
+    // leaf boundary: push the partial on the binary-counter stack
+    auto push_leaf = [&](int local_leaf) {
+#pragma unroll
+        for (int i = 0; i < TM; i++)
+#pragma unroll
+            for (int j = 0; j < TN / 2; j++) {
+                float v0, v1;
+                unpack2(acc[i][j], v0, v1);
+                v0 = ftz_hw(v0);
+                v1 = ftz_hw(v1);
+                const int c = i * TN + 2 * j;
+                int lvl = 0;
+                for (int bits = local_leaf; bits & 1; bits >>= 1, lvl++) {
+                    v0 = fold_add(stack[lvl][c], v0);
+                    v1 = fold_add(stack[lvl][c + 1], v1);
+                }
+                stack[lvl][c] = v0;
+                stack[lvl][c + 1] = v1;
+                acc[i][j] = 0ull;
+            }
+    };
+
+    if (t_first < t_end) {
+        int t = t_first, koff = 0;
+        load_window(t, koff);
+        store_window(0);
+        bool admitted = __syncthreads_and(stage_key >= ADMIT_MIN);
+        bool leaf_clean = true;
+        int buf = 0;
+        while (true) {
+            const int leaf_len = min(g.leaf, g.k - t * g.leaf);
+            const int len = min(KS, leaf_len - koff);
+            // the window after this one
+            int nt = t, nkoff = koff + KS;
+            if (nkoff >= leaf_len) { nt = t + 1; nkoff = 0; }
+            const bool more = nt < t_end;
+            if (more) load_window(nt, nkoff);
+
+            const bool fast = admitted && leaf_clean && len == KS;
+            if (fast) {
+#pragma unroll
+                for (int kk = 0; kk < KS; kk++) step_fast(buf, kk);
+            } else {
+                leaf_clean = false;
+#pragma unroll 1
+                for (int kk = 0; kk < len; kk++) step_slow(buf, kk);
+            }
+            if (nt != t) { // this window closed its leaf
+                if (g.leaves > 1) push_leaf(t - t_first);
+                leaf_clean = true;
+            }
+            if (!more) break;
+            store_window(buf ^ 1);
+            admitted = __syncthreads_and(stage_key >= ADMIT_MIN);
+            buf ^= 1;
+            t = nt;
+            koff = nkoff;
+        }
+    }
+
+    // drain the stack (lowest occupied level first: the carry rule) and store
+    const int count = t_end - t_first;
+    float *out = g.groups > 1 ? g.ws + (size_t)blockIdx.y * (size_t)g.m * (size_t)g.n : g.c;
+#pragma unroll
+    for (int i = 0; i < TM; i++) {
+        const int row = bm0 + (i / 4) * (BM / RM) + ty * 4 + (i % 4);
+#pragma unroll
+        for (int jr = 0; jr < RN; jr++) {
+            float vals[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int cj = jr * 4 + e;
+                float v;
+                if (g.leaves > 1) {
+                    const int c = i * TN + cj;
+                    bool have = false;
+                    v = 0.f;
+                    for (int lvl = 0; lvl < FOLD_LEVELS; lvl++)
+                        if ((count >> lvl) & 1) {
+                            v = have ? fold_add(stack[lvl][c], v) : stack[lvl][c];
+                            have = true;
+                        }
+                } else {
+                    float v0, v1;
+                    unpack2(acc[i][cj / 2], v0, v1);
+                    v = (cj & 1) ? v1 : v0;
+                }
+                vals[e] = nan_canon(ftz_hw(v));
+            }
+            const int col = bn0 + jr * (BN / RN) + tx * 4;
+            if (row < g.m) {
+                float *dst = out + (size_t)row * (size_t)g.n + col;
+                if (g.vec_c && col + 3 < g.n) *reinterpret_cast<float4 *>(dst) = make_float4(vals[0], vals[1], vals[2], vals[3]);
+                else
+                    for (int e = 0; e < 4; e++)
+                        if (col + e < g.n) dst[e] = vals[e];
+            }
+        }
+    }
+}
+
+// Folds the group nodes of a split product: node g of cell c is ws[g][c]; the
+// nodes are the level-log2(S) row of the contract's tree, so the same
+// adjacent-pair fold with an odd tail carried finishes it.
+constexpr int MAX_GROUPS = 64;
+__global__ void fold_groups_kernel(const float *__restrict__ ws, float *__restrict__ c, long long cells, int groups) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= cells) return;
+    float v[MAX_GROUPS];
+    for (int gi = 0; gi < groups; gi++) v[gi] = ws[(size_t)gi * (size_t)cells + idx];
+    int width = groups;
+    while (width > 1) {
+        const int pairs = width / 2;
+        for (int q = 0; q < pairs; q++) v[q] = fold_add(v[2 * q], v[2 * q + 1]);
+        if (width & 1) v[pairs] = v[width - 1];
+        width = pairs + (width & 1);
+    }
+    c[idx] = nan_canon(ftz_hw(v[0]));
+}
+
+// One thread per cell, whole product serial: the on-device restatement of the
+// oracle, used by the self-check entry point and as the reference every tiled
+// plan is compared with on the device.
+__global__ void gemm_flat_kernel(const GemmArgs g) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)g.m * g.n) return;
+    const int i = (int)(idx / g.n), j = (int)(idx % g.n);
+    float stack[FOLD_LEVELS];
+    for (int t = 0; t < g.leaves; t++) {
+        const int pb = t * g.leaf, pe = min(pb + g.leaf, g.k);
+        float acc = 0.f;
+        for (int p = pb; p < pe; p++) {
+            const float av = (g.op == OP_TN) ? g.a[(size_t)p * g.m + i] : g.a[(size_t)i * g.k + p];
+            const size_t boff = (g.op == OP_NT) ? (size_t)j * g.k + p : (size_t)p * g.n + j;
+            float bv;
+            if (g.wkind == W_F32) bv = static_cast<const float *>(g.b)[boff];
+            else if (g.wkind == W_BF16) bv = bf16_bits_to_f32(static_cast<const unsigned short *>(g.b)[boff]);
+            else {
+                const float f = (g.wkind == W_INT8_EXP) ? pow2_f32(static_cast<const int *>(g.bscale)[j])
+                                                        : static_cast<const float *>(g.bscale)[j];
+                bv = dequant_int8_pow2(static_cast<const signed char *>(g.b)[boff], f);
+            }
+            acc = step_flush(ftz_bits(av), ftz_bits(bv), acc);
+        }
+        float v = ftz_hw(acc);
+        int lvl = 0;
+        for (int bits = t; bits & 1; bits >>= 1, lvl++) v = fold_add(stack[lvl], v);
+        stack[lvl] = v;
+    }
+    float v = 0.f;
+    bool have = false;
+    for (int lvl = 0; lvl < FOLD_LEVELS; lvl++)
+        if ((g.leaves >> lvl) & 1) {
+            v = have ? fold_add(stack[lvl], v) : stack[lvl];
+            have = true;
+        }
+    g.c[idx] = nan_canon(ftz_hw(v));
+}
+
+} // namespace b200i

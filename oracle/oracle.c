@@ -325,6 +325,7 @@ static inline int8_t quantize_int8_value(float x, int e) {
     volatile float prod = ftz(x) * pow2_f32(-(int64_t)e);
     float s = ftz(prod);
     float r = round_half_even(s);
+    if (r != r) return 0; /* 0 * inf when the scale overflows: the code stays zero (tools/identity_break.py:4120-4122) */
     if (r > 127.0f) r = 127.0f;
     if (r < -127.0f) r = -127.0f;
     return (int8_t)(int)r;

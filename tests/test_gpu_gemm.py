@@ -1,0 +1,177 @@
+"""GPU parity for the fp32 product: the CUDA path, through the C ABI, against the
+CPU oracle, bit for bit. Modelled on the reference's device gates
+(gemm/checks/gemm_device_check.mojo: device == oracle :840, launch invariance
+:1016, batch invariance :1464) and its Python-surface gate
+(python/mojolearn/tests/test_linalg_identity.py: shapes chosen by leaf count
+with m, n, k pairwise distinct, :382-412)."""
+import numpy as np
+import pytest
+
+import oracle
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from mojolearn_b200 import _native, linalg, torch_ops  # noqa: E402
+
+OPS = {"NN": oracle.OP_NN, "NT": oracle.OP_NT, "TN": oracle.OP_TN}
+PLANS = [(torch_ops.PLAN_FLAT, 0), (torch_ops.PLAN_T128, 0), (torch_ops.PLAN_T64, 0), (torch_ops.PLAN_T128, 1),
+         (torch_ops.PLAN_T64, 2), (torch_ops.PLAN_T128, 4)]
+
+# (m, n, k): P = 1, 2, 3 (ragged, odd carry), 5 (carries twice), 6, 8 with a short last leaf, tails, k = 1
+SHAPES = [(40, 20, 300), (11, 6, 640), (9, 5, 256), (17, 3, 64), (8, 48, 384), (36, 9, 300), (1, 1, 1), (5, 7, 1),
+          (130, 70, 129), (257, 131, 768), (100, 100, 1000), (64, 192, 128), (3, 515, 136), (129, 257, 2049)]
+
+
+def _operands(m, n, k, op, seed):
+    rng = np.random.default_rng(seed)
+    a = rng.standard_normal((k, m) if op == oracle.OP_TN else (m, k)).astype(np.float32)
+    b = rng.standard_normal((n, k) if op == oracle.OP_NT else (k, n)).astype(np.float32)
+    return a, b
+
+
+def _gpu(a, b, op, plan=torch_ops.PLAN_AUTO, groups=0):
+    c = torch_ops.product(torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(), None, linalg.W_F32, op, plan=plan,
+                          group_leaves=groups)
+    return c.cpu().numpy()
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+@pytest.mark.parametrize("opname", ["NN", "NT", "TN"])
+def test_device_matches_oracle_on_every_plan(m, n, k, opname):
+    op = OPS[opname]
+    a, b = _operands(m, n, k, op, m * 7 + n * 3 + k)
+    want = oracle.nan_canon(oracle.gemm(a, b, op))
+    assert _gpu(a, b, op).tobytes() == want.tobytes()
+    leaves = oracle.leaf_count(k)
+    for plan, groups in PLANS:
+        if groups and groups >= leaves and leaves > 1 and plan != torch_ops.PLAN_FLAT:
+            groups = 1
+        got = _gpu(a, b, op, plan, groups)
+        assert got.tobytes() == want.tobytes(), "plan %d groups %d" % (plan, groups)
+
+
+@pytest.mark.parametrize("opname", ["NN", "NT", "TN"])
+def test_public_call_with_host_buffers(opname):
+    op = OPS[opname]
+    a, b = _operands(70, 90, 640, op, 1)
+    got = linalg.matmul(a, b, transpose_a=(opname == "TN"), transpose_b=(opname == "NT"))
+    assert got.tobytes() == oracle.nan_canon(oracle.gemm(a, b, op)).tobytes()
+    out = np.full((70, 90), -987654.0, np.float32)  # poison: an unwritten cell would survive
+    ret = linalg.matmul(a, b, transpose_a=(opname == "TN"), transpose_b=(opname == "NT"), out=out)
+    assert ret is out and out.tobytes() == got.tobytes()
+
+
+def test_subnormal_forcing_operands_take_the_flushed_path():
+    rng = np.random.default_rng(0)
+    a = (rng.standard_normal((150, 300)) * 2.0 ** -62).astype(np.float32)
+    b = (rng.standard_normal((300, 140)) * 2.0 ** -63).astype(np.float32)
+    a[::3, ::7] = np.float32(1e-41)  # subnormal operands
+    b[::5, ::3] = -0.0
+    want = oracle.gemm(a, b)
+    assert ((want != 0) & (np.abs(want) < 2.0 ** -118)).any()
+    for plan, groups in PLANS:
+        assert _gpu(a, b, oracle.OP_NN, plan, min(groups, 2)).tobytes() == want.tobytes()
+    # the boundary window: exact values in [2^-126 - 2^-150, 2^-126) round up and are kept
+    a2 = np.full((4, 130), np.float32(1.0) - np.float32(2.0 ** -24), np.float32)
+    b2 = np.zeros((130, 4), np.float32)
+    b2[0, :] = np.float32(2.0 ** -126)
+    want2 = oracle.gemm(a2, b2)
+    assert (want2.view(np.uint32) == 0x00800000).all()
+    for plan, groups in PLANS:
+        assert _gpu(a2, b2, oracle.OP_NN, plan, min(groups, 1)).tobytes() == want2.tobytes()
+
+
+def test_signed_zero_nan_and_inf():
+    a = np.zeros((5, 300), np.float32)
+    a[:] = -0.0
+    b = np.ones((300, 6), np.float32)
+    want = oracle.gemm(a, b)
+    assert not np.signbit(want).any()
+    assert _gpu(a, b, oracle.OP_NN).tobytes() == want.tobytes()
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal((33, 260)).astype(np.float32)
+    b = rng.standard_normal((260, 65)).astype(np.float32)
+    a[3, 5] = np.nan
+    a[7, 200] = np.inf
+    b[100, 9] = -np.inf
+    want = oracle.nan_canon(oracle.gemm(a, b))
+    for plan, groups in PLANS:
+        got = _gpu(a, b, oracle.OP_NN, plan, min(groups, 2))
+        assert got.tobytes() == want.tobytes()
+    assert (want.view(np.uint32)[np.isnan(want)] == 0x7FC00000).all()
+
+
+def test_batch_invariance():
+    """One row alone equals that row inside a bigger call; one column likewise (n: 4 vs 4096)."""
+    rng = np.random.default_rng(2)
+    a = rng.standard_normal((300, 1000)).astype(np.float32)
+    b = rng.standard_normal((4096, 1000)).astype(np.float32)
+    full = _gpu(a, b, oracle.OP_NT)
+    for i in (0, 7, 299):
+        assert _gpu(a[i:i + 1].copy(), b, oracle.OP_NT).tobytes() == full[i:i + 1].tobytes()
+    assert _gpu(a, b[:4].copy(), oracle.OP_NT).tobytes() == np.ascontiguousarray(full[:, :4]).tobytes()
+    assert _gpu(a[:8].copy(), b, oracle.OP_NT).tobytes() == full[:8].tobytes()
+
+
+def test_tail_shape_1000_cubed_against_cpu_rows():
+    rng = np.random.default_rng(0)
+    a = rng.standard_normal((1000, 1000)).astype(np.float32)
+    b = rng.standard_normal((1000, 1000)).astype(np.float32)
+    want = oracle.gemm_rows(a, b, oracle.OP_NN)
+    assert _gpu(a, b, oracle.OP_NN).tobytes() == want.tobytes()
+    assert _gpu(a, b, oracle.OP_NT).tobytes() == oracle.gemm_rows(a, b, oracle.OP_NT).tobytes()
+
+
+def test_config1_1024_cubed_uniform_seed0():
+    """BASELINE config 1: M = N = K = 1024, U(-1, 1) from seed 0, bit for bit."""
+    rng = np.random.default_rng(0)
+    a = rng.uniform(-1.0, 1.0, (1024, 1024)).astype(np.float32)
+    b = rng.uniform(-1.0, 1.0, (1024, 1024)).astype(np.float32)
+    want = oracle.gemm_rows(a, b, oracle.OP_NN)
+    got = linalg.matmul(a, b)
+    assert got.tobytes() == want.tobytes()
+    assert oracle.gemm(a[:8], b).tobytes() == want[:8].tobytes()  # the scalar oracle on a sample of rows
+
+
+@pytest.mark.parametrize("m,n,k", [(4096, 4096, 4096), (8192, 8192, 1024), (128, 11008, 4096), (2048, 50304, 768)])
+def test_config2_full_size_rows_sampled_against_the_oracle(m, n, k):
+    """Full BASELINE sizes: the whole product on the GPU; sampled rows against the
+    CPU oracle (a row's bits do not depend on the other rows); plans against
+    each other on the full output (launch invariance is size independent)."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn((m, k), generator=g, device="cuda", dtype=torch.float32)
+    b = torch.randn((n, k), generator=g, device="cuda", dtype=torch.float32)
+    c = torch_ops.matmul(a, b, transpose_b=True)
+    rows = sorted(set([0, 1, m // 2, m - 1] + [int(v) for v in np.random.default_rng(1).integers(0, m, 4)]))
+    bh = b.cpu().numpy()
+    want = oracle.gemm_rows(a[rows].cpu().numpy(), bh, oracle.OP_NT)
+    assert c[rows].cpu().numpy().tobytes() == want.tobytes()
+    other = torch_ops.product(a, b, None, linalg.W_F32, oracle.OP_NT, plan=torch_ops.PLAN_T64,
+                              group_leaves=2 if k >= 256 else 0)
+    assert torch.equal(c.view(torch.int32), other.view(torch.int32))
+    del other
+    if m * n * k <= 128 * 11008 * 4096:
+        bt = b.t().contiguous()
+        nn = torch_ops.matmul(a, bt)
+        assert torch.equal(c.view(torch.int32), nn.view(torch.int32))  # orientations agree
+
+
+def test_c_abi_refusals_on_device():
+    a = torch.zeros((4, 4), device="cuda")
+    with pytest.raises(_native.NativeError):
+        torch_ops.product(a, a, None, linalg.W_F32, 7)
+    with pytest.raises(TypeError):
+        torch_ops.product(a.double(), a)
+    with pytest.raises(ValueError):
+        torch_ops.product(a.t(), a)
+    with pytest.raises(_native.NativeError):
+        torch_ops.product(a, a.to(torch.int8), None, linalg.W_INT8_EXP, oracle.OP_NT)
+
+
+def test_custom_op_registration():
+    a = torch.randn((8, 300), device="cuda")
+    b = torch.randn((300, 5), device="cuda")
+    c = torch.ops.mojolearn_b200.matmul(a, b, 0)
+    want = oracle.gemm(a.cpu().numpy(), b.cpu().numpy())
+    assert c.cpu().numpy().tobytes() == want.tobytes()

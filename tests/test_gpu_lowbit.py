@@ -1,0 +1,138 @@
+"""GPU parity for the weight-storage paths: conversions, the int8 / bf16 weight
+products at decode and prefill row counts (BASELINE config 3 shapes), and the
+launch invariance of the decode plan against the tiled and flat plans."""
+import numpy as np
+import pytest
+
+import oracle
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from mojolearn_b200 import _native, linalg, lowbit, torch_ops  # noqa: E402
+
+
+def test_conversions_match_the_oracle():
+    rng = np.random.default_rng(0)
+    x = (rng.standard_normal((257, 131)) * np.exp2(rng.integers(-140, 120, (257, 1)))).astype(np.float32)
+    x[0, :5] = [np.nan, np.inf, -np.inf, 1e-41, -1e-41]
+    assert linalg.to_bf16(x).tobytes() == oracle.to_bf16(x).tobytes()
+    bits = np.arange(65536, dtype=np.uint16).reshape(256, 256)
+    assert linalg.from_bf16(bits).tobytes() == oracle.from_bf16(bits).tobytes()
+    allf = oracle.from_bf16(bits)
+    assert linalg.to_bf16(allf).tobytes() == oracle.to_bf16(allf).tobytes()
+    q, e = linalg.quantize_int8(x)
+    qo, eo = oracle.quantize_int8(x)
+    assert q.tobytes() == qo.tobytes() and e.tobytes() == eo.tobytes()
+    assert linalg.dequantize_int8(q, e).tobytes() == oracle.dequantize_int8(qo, eo).tobytes()
+    x3 = rng.standard_normal((5, 7, 9)).astype(np.float32)
+    assert linalg.to_bf16(x3).shape == (5, 7, 9)
+    odd = rng.standard_normal(1001).astype(np.float32)[1:]  # misaligned, odd count
+    assert linalg.to_bf16(odd).tobytes() == oracle.to_bf16(odd).tobytes()
+
+
+def test_lowbit_pack_roundtrip():
+    rng = np.random.default_rng(1)
+    w = {"q": (rng.standard_normal((64, 48)) * 0.02).astype(np.float32), "norm": np.ones(48, np.float32)}
+    for fmt in ("bfloat16", "int8", "float32"):
+        packed = lowbit.pack(w, fmt)
+        assert lowbit.format_of(packed) == fmt and packed["norm"] is w["norm"]
+        mat = lowbit.unpack(packed)
+        if fmt == "int8":
+            q, e = oracle.quantize_int8(w["q"])
+            assert mat["q"].tobytes() == oracle.dequantize_int8(q, e).tobytes()
+        elif fmt == "bfloat16":
+            assert mat["q"].tobytes() == oracle.from_bf16(oracle.to_bf16(w["q"])).tobytes()
+
+
+def _weights(n, k, seed):
+    rng = np.random.default_rng(seed)
+    codes = rng.integers(-127, 128, (n, k)).astype(np.int8)
+    scales = rng.uniform(0.001, 0.02, n).astype(np.float32)
+    exps = np.round(np.log2(scales)).astype(np.int32)  # snapped to powers of two: the reference's format
+    wb = oracle.to_bf16((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+    return codes, scales, exps, wb
+
+
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 32, 128])
+def test_config3_reduced_n_against_the_scalar_oracle(m):
+    n, k = 520, 4096
+    codes, scales, exps, wb = _weights(n, k, 3)
+    x = np.random.default_rng(4).standard_normal((m, k)).astype(np.float32)
+    w8 = oracle.dequantize_int8(codes, exps)
+    assert linalg.matmul_int8w(x, codes, exps).tobytes() == oracle.gemm(x, w8, oracle.OP_NT).tobytes()
+    w8s = oracle.dequantize_int8_scaled(codes, scales)  # extension: general float32 scales (parity unpinned)
+    assert linalg.matmul_int8w(x, codes, scales=scales).tobytes() == oracle.gemm(x, w8s, oracle.OP_NT).tobytes()
+    wf = oracle.from_bf16(wb)
+    assert linalg.matmul_bf16(x, wb, transpose_b=True).tobytes() == oracle.gemm(x, wf, oracle.OP_NT).tobytes()
+    assert linalg.matmul(x, wf, transpose_b=True).tobytes() == oracle.gemm(x, wf, oracle.OP_NT).tobytes()
+
+
+@pytest.mark.parametrize("m", [1, 8, 32, 128])
+def test_config3_full_size(m):
+    """W [11008, 4096]: the whole product on the GPU against the threaded CPU
+    oracle (m <= 8), or sampled columns of it (larger m), plus plan invariance."""
+    n, k = 11008, 4096
+    codes, scales, exps, wb = _weights(n, k, 5)
+    x = np.random.default_rng(6).standard_normal((m, k)).astype(np.float32)
+    dx = torch.from_numpy(x).cuda()
+    dcodes, dexps, dscales, dwb = (torch.from_numpy(v).cuda() for v in (codes, exps, scales, wb))
+    got8 = torch_ops.linear_int8w(dx, dcodes, exponents=dexps)
+    gots = torch_ops.linear_int8w(dx, dcodes, scales=dscales)
+    gotb = torch_ops.matmul_bf16(dx, dwb, transpose_b=True)
+    cols = np.arange(n) if m <= 8 else np.sort(np.random.default_rng(7).choice(n, 600, replace=False))
+    w8 = oracle.dequantize_int8(codes[cols], exps[cols])
+    assert got8.cpu().numpy()[:, cols].tobytes() == oracle.gemm_rows(x, w8, oracle.OP_NT).tobytes()
+    w8s = oracle.dequantize_int8_scaled(codes[cols], scales[cols])
+    assert gots.cpu().numpy()[:, cols].tobytes() == oracle.gemm_rows(x, w8s, oracle.OP_NT).tobytes()
+    wf = oracle.from_bf16(wb[cols])
+    assert gotb.cpu().numpy()[:, cols].tobytes() == oracle.gemm_rows(x, wf, oracle.OP_NT).tobytes()
+    # every plan that accepts the shape returns the same words
+    plans = [(torch_ops.PLAN_T128, 0), (torch_ops.PLAN_T64, 4)] + ([(torch_ops.PLAN_DECODE, 0)] if m <= 8 else [])
+    for plan, groups in plans:
+        alt = torch_ops.product(dx, dcodes, dexps, linalg.W_INT8_EXP, oracle.OP_NT, plan=plan, group_leaves=groups)
+        assert torch.equal(alt.view(torch.int32), got8.view(torch.int32)), (plan, groups)
+        altb = torch_ops.product(dx, dwb, None, linalg.W_BF16, oracle.OP_NT, plan=plan, group_leaves=groups)
+        assert torch.equal(altb.view(torch.int32), gotb.view(torch.int32)), (plan, groups)
+    assert _native.lib().b200i_decode_status(-1) == 0
+
+
+def test_decode_plan_edges():
+    """Ragged row counts per CTA, k below one leaf, k with a short last leaf,
+    subnormal-forcing weights and activations, exotic exponents."""
+    rng = np.random.default_rng(8)
+    for (m, n, k) in [(1, 7, 16), (3, 33, 128), (8, 1000, 1040), (2, 4097, 2048), (4, 300, 8192), (1, 50304, 768)]:
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+        dx, dw = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+        want = oracle.gemm_rows(x, w, oracle.OP_NT)
+        got = torch_ops.product(dx, dw, None, linalg.W_F32, oracle.OP_NT, plan=torch_ops.PLAN_DECODE)
+        assert got.cpu().numpy().tobytes() == want.tobytes(), (m, n, k)
+    m, n, k = 4, 200, 512
+    x = (rng.standard_normal((m, k)) * 2.0 ** -62).astype(np.float32)
+    x[0, ::9] = np.float32(3e-42)
+    codes = rng.integers(-127, 128, (n, k)).astype(np.int8)
+    exps = rng.integers(-70, -58, n).astype(np.int32)
+    exps[:4] = [-140, 127, 121, -127]
+    w = oracle.dequantize_int8(codes, exps)
+    want = oracle.nan_canon(oracle.gemm(x, w, oracle.OP_NT))
+    dx, dc, de = torch.from_numpy(x).cuda(), torch.from_numpy(codes).cuda(), torch.from_numpy(exps).cuda()
+    for plan in (torch_ops.PLAN_DECODE, torch_ops.PLAN_T64, torch_ops.PLAN_FLAT, torch_ops.PLAN_AUTO):
+        got = torch_ops.product(dx, dc, de, linalg.W_INT8_EXP, oracle.OP_NT, plan=plan)
+        assert got.cpu().numpy().tobytes() == want.tobytes(), plan
+    wb = oracle.to_bf16((rng.standard_normal((n, k)) * 2.0 ** -64).astype(np.float32))
+    wantb = oracle.gemm(x, oracle.from_bf16(wb), oracle.OP_NT)
+    for plan in (torch_ops.PLAN_DECODE, torch_ops.PLAN_T128):
+        got = torch_ops.product(dx, torch.from_numpy(wb).cuda(), None, linalg.W_BF16, oracle.OP_NT, plan=plan)
+        assert got.cpu().numpy().tobytes() == wantb.tobytes(), plan
+    assert _native.lib().b200i_decode_status(-1) == 0
+
+
+def test_int8_product_profile():
+    rng = np.random.default_rng(9)
+    a = rng.standard_normal((37, 1000)).astype(np.float32)
+    b = rng.standard_normal((41, 1000)).astype(np.float32)
+    qa, ea = oracle.quantize_int8(a)
+    qb, eb = oracle.quantize_int8(b)
+    assert linalg.matmul_int8((qa, ea), (qb, eb)).tobytes() == oracle.gemm_int8(qa, ea, qb, eb).tobytes()
+    assert linalg.matmul_int8(a, b).tobytes() == oracle.gemm_int8(qa, ea, qb, eb).tobytes()
