@@ -83,6 +83,11 @@ int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a
                           int64_t wkind, int64_t m, int64_t n, int64_t k, int64_t op, int64_t plan,
                           int64_t group_leaves, void *ws, int64_t ws_bytes, char *err, int64_t err_cap);
 
+/* 1 when the row-streaming decode plan accepts the shape (op NT, m <= 8, k a
+ * multiple of 16 with 128-element leaves, leaf partials and two ring stages
+ * within shared memory), else 0. */
+int64_t b200i_decode_plan_fits(int64_t m, int64_t n, int64_t k, int64_t op, int64_t wkind);
+
 /* Scratch bytes the product needs for this shape on the current device. */
 int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k);
 
@@ -122,7 +127,8 @@ int64_t b200i_host_gemm_int8(int64_t device, float *c, const int8_t *qa, const i
 
 /* Status word of the decode plan's bounded waits on `device` (synchronises the
  * device): 0 = no wait ever ran out; 1 / 2 = the producer / a consumer gave up
- * waiting on a stage; -1 = the word could not be read. No reference counterpart:
+ * waiting on a stage; -1 = the word could not be read. A nonzero word is cleared
+ * by the read. No reference counterpart:
  * the reference has no device-side wait. */
 int64_t b200i_decode_status(int64_t device);
 

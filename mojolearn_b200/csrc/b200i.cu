@@ -145,7 +145,7 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     Plan plan;
     if (plan_kind == PLAN_AUTO) {
         plan = choose_plan(m, n, k, sm_count(dev));
-        if (decode_plan_fits(m, n, k, op) && aligned(b, 16)) plan = Plan{PLAN_DECODE, g.leaves, 1};
+        if (decode_plan_fits(m, n, k, op, wkind) && aligned(b, 16) && aligned(a, 16)) plan = Plan{PLAN_DECODE, g.leaves, 1};
     } else {
         plan.kind = plan_kind;
         int s = group_leaves > 0 ? (int)group_leaves : g.leaves;
@@ -181,7 +181,7 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
         gemm_flat_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(g);
         g_launches++;
     } else if (plan.kind == PLAN_DECODE) {
-        if (!decode_plan_fits(m, n, k, op) || !aligned(b, 16))
+        if (!decode_plan_fits(m, n, k, op, wkind) || !aligned(b, 16) || !aligned(a, 16))
             return fail(err, err_cap, "identical gemm: the decode plan needs op NT, m <= %d, k a multiple of 16 and 16-byte aligned weights", DECODE_MAX_M);
         g_launches += launch_decode(g, sm_count(dev), st);
     } else if (plan.kind == PLAN_T128) {
@@ -248,11 +248,15 @@ int64_t b200i_device_count(void) {
     return n;
 }
 int64_t b200i_launch_count(void) { return g_launches.load(); }
+int64_t b200i_decode_plan_fits(int64_t m, int64_t n, int64_t k, int64_t op, int64_t wkind) {
+    return decode_plan_fits(m, n, k, (int)op, (int)wkind) ? 1 : 0;
+}
 
 int64_t b200i_decode_status(int64_t device) {
     if (device >= 0 && cudaSetDevice((int)device) != cudaSuccess) { cudaGetLastError(); return -1; }
-    int v = 0;
+    int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (v != 0 && cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return -1; }
     return v;
 }
 
@@ -260,9 +264,6 @@ int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (m <= 0 || n <= 0 || k <= 0) return 0;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = -1; }
-    if (decode_plan_fits(m, n, k, OP_NT)) {
-        // the decode plan needs none; a tiled plan may still run for another op
-    }
     Plan p = choose_plan(m, n, k, sm_count(dev));
     return p.groups > 1 ? (int64_t)p.groups * m * n * 4 : 0;
 }

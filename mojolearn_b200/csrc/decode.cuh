@@ -34,7 +34,6 @@ constexpr int DEC_CONSUMERS = 8;             // consumer warps
 constexpr int DEC_THREADS = 32 * (DEC_CONSUMERS + 1);
 constexpr int DEC_CHUNK_BYTES = 1024;        // bytes of one weight row per stage
 constexpr int DEC_PITCH = DEC_CHUNK_BYTES + 16; // row pitch in a stage: 16-byte skew keeps 128-bit reads conflict free
-constexpr int DEC_STAGE_BYTES = DEC_ROWS * DEC_PITCH;
 constexpr int DEC_SMEM_LIMIT = 220 * 1024;
 constexpr unsigned DEC_SPIN_LIMIT = 1u << 22;
 
@@ -42,34 +41,39 @@ __device__ int g_decode_status = 0; // 0 = ok; nonzero = a bounded wait ran out 
 
 struct DecodeLayout {
     int stages;
-    size_t xs_off, xkey_off, part_off, stage_off, bar_off, total;
+    size_t x_bytes;     // activation bytes per stage: m rows x (leaves per stage x 128) floats
+    size_t stage_bytes; // one ring slot: the weight tile, then the activation tile
+    size_t part_off, stage_off, bar_off, total;
 };
 
 __host__ __device__ inline int dec_esize(int wkind) { return wkind == W_F32 ? 4 : (wkind == W_BF16 ? 2 : 1); }
 
-__host__ __device__ inline DecodeLayout decode_layout(int m, int k, int leaves) {
+__host__ __device__ inline DecodeLayout decode_layout(int m, int k, int leaves, int wkind) {
     DecodeLayout l;
+    const int lps = DEC_CHUNK_BYTES / (K_LEAF_MIN * dec_esize(wkind));
+    l.x_bytes = (size_t)m * lps * K_LEAF_MIN * 4;
+    l.stage_bytes = (size_t)DEC_ROWS * DEC_PITCH + l.x_bytes;
     size_t off = 0;
-    l.xs_off = off;   off += (size_t)m * k * 4;
-    l.xkey_off = off; off += (size_t)((leaves + 3) / 4) * 16;
-    l.part_off = off; off += (size_t)m * leaves * DEC_ROWS * 4;
+    l.part_off = off;
+    off += (size_t)m * leaves * DEC_ROWS * 4;
     off = (off + 127) / 128 * 128;
     l.stage_off = off;
-    int stages = (int)((DEC_SMEM_LIMIT - 256 - (long long)off) / DEC_STAGE_BYTES);
+    long long room = (long long)DEC_SMEM_LIMIT - 256 - (long long)off;
+    int stages = room > 0 ? (int)(room / (long long)l.stage_bytes) : 0;
     if (stages > 4) stages = 4;
     l.stages = stages;
-    off += (size_t)(stages > 0 ? stages : 0) * DEC_STAGE_BYTES;
+    off += (size_t)(stages > 0 ? stages : 0) * l.stage_bytes;
     l.bar_off = off;
     off += 128;
     l.total = off;
     return l;
 }
 
-inline bool decode_plan_fits(long long m, long long n, long long k, int op) {
+inline bool decode_plan_fits(long long m, long long n, long long k, int op, int wkind = W_F32) {
     if (op != OP_NT || m < 1 || m > DECODE_MAX_M || n < 1) return false;
     if (k % 16 != 0 || k > 131072) return false; // 16-byte rows for every storage kind; leaves of 128
     if (k > K_LEAF_MIN && leaf_size(k) != K_LEAF_MIN) return false;
-    DecodeLayout l = decode_layout((int)m, (int)k, (int)leaf_count(k));
+    DecodeLayout l = decode_layout((int)m, (int)k, (int)leaf_count(k), wkind);
     return l.stages >= 2;
 }
 
@@ -152,26 +156,39 @@ __device__ __forceinline__ void leaf_chain(const unsigned char *w, const float *
                 else if (WK == W_F32 || WK == W_BF16) wkey = min(wkey, admit_key(wf));
 #pragma unroll
                 for (int mi = 0; mi < M; mi++)
-                    acc[mi] = FLUSH ? step_flush(xv[mi][s], wf, acc[mi]) : step_bare(xv[mi][s], wf, acc[mi]);
+                    acc[mi] = FLUSH ? step_flush(ftz_bits(xv[mi][s]), wf, acc[mi]) : step_bare(xv[mi][s], wf, acc[mi]);
             }
         }
     }
 }
 
+// Admission key of one leaf of the staged activations: the lanes split the
+// m x len words between them and vote.
+template <int M>
+__device__ __forceinline__ bool leaf_x_admitted(const float *xs, int xstride, int len, int lane) {
+    unsigned key = 0xFFFFFFFFu;
+    const int quads = len / 4;
+    for (int idx = lane; idx < M * quads; idx += 32) {
+        const int mi = idx / quads, q = idx % quads;
+        key = key4(*reinterpret_cast<const float4 *>(xs + (size_t)mi * xstride + 4 * q), key);
+    }
+    return __all_sync(0xFFFFFFFFu, key >= ADMIT_MIN);
+}
+
 template <int WK, int M>
 __global__ void __launch_bounds__(DEC_THREADS, 1) decode_kernel(const GemmArgs g) {
     extern __shared__ __align__(128) unsigned char smem[];
-    const DecodeLayout lay = decode_layout(M, g.k, g.leaves);
-    float *xs = reinterpret_cast<float *>(smem + lay.xs_off);
-    unsigned *xkey = reinterpret_cast<unsigned *>(smem + lay.xkey_off);
+    const DecodeLayout lay = decode_layout(M, g.k, g.leaves, WK);
     float *part = reinterpret_cast<float *>(smem + lay.part_off);
     unsigned char *stage_base = smem + lay.stage_off;
     unsigned long long *full = reinterpret_cast<unsigned long long *>(smem + lay.bar_off);
     unsigned long long *empty = full + 4;
     const int nst = lay.stages;
+    const size_t stage_bytes = lay.stage_bytes;
 
     constexpr int ES = WK == W_F32 ? 4 : (WK == W_BF16 ? 2 : 1);
     constexpr int LPS = DEC_CHUNK_BYTES / (K_LEAF_MIN * ES); // leaves per stage: 8, 4 or 2
+    constexpr int XSTRIDE = LPS * K_LEAF_MIN;                 // floats per activation row in a stage
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int leaves = g.leaves, k = g.k, n = g.n;
     const int chunks = (leaves + LPS - 1) / LPS; // stages per row block
@@ -185,7 +202,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) decode_kernel(const GemmArgs g
     if (tid == 0) {
         for (int s = 0; s < nst; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], LPS);
+            mbar_init(&empty[s], DEC_CONSUMERS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -214,47 +231,33 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) decode_kernel(const GemmArgs g
                 }
                 const size_t koff = (size_t)c * DEC_CHUNK_BYTES;
                 const unsigned bytes = (unsigned)min((size_t)DEC_CHUNK_BYTES, row_bytes - koff);
-                if (lane == 0) mbar_expect_tx(&full[slot], bytes * (unsigned)valid);
+                const unsigned xbytes = bytes / ES * 4; // the same k range of one activation row
+                unsigned char *slot_base = stage_base + (size_t)slot * stage_bytes;
+                if (lane == 0) mbar_expect_tx(&full[slot], bytes * (unsigned)valid + xbytes * (unsigned)M);
                 __syncwarp();
                 if (lane < valid)
-                    bulk_copy_g2s(stage_base + (size_t)slot * DEC_STAGE_BYTES + (size_t)lane * DEC_PITCH,
-                                  wbase + (size_t)(row0 + lane) * row_bytes + koff, bytes, &full[slot]);
+                    bulk_copy_g2s(slot_base + (size_t)lane * DEC_PITCH, wbase + (size_t)(row0 + lane) * row_bytes + koff, bytes,
+                                  &full[slot]);
+                if (lane < M)
+                    bulk_copy_g2s(slot_base + (size_t)DEC_ROWS * DEC_PITCH + (size_t)lane * XSTRIDE * 4,
+                                  g.a + (size_t)lane * k + (size_t)c * XSTRIDE, xbytes, &full[slot]);
             }
         }
         return;
     }
 
     // ---------------- consumers ----------------
-    // activations: flushed once into shared memory, admission key per leaf
-    for (int t = tid; t < leaves; t += 32 * DEC_CONSUMERS) xkey[t] = 0xFFFFFFFFu;
-    consumer_sync();
-    {
-        const int quads = k / 4;
-        for (int idx = tid; idx < M * quads; idx += 32 * DEC_CONSUMERS) {
-            const int mi = idx / quads, q = idx % quads;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (mi < g.m) {
-                if (g.vec_a) v = __ldg(reinterpret_cast<const float4 *>(g.a + (size_t)mi * k) + q);
-                else {
-                    const float *p = g.a + (size_t)mi * k + 4 * q;
-                    v = make_float4(__ldg(p), __ldg(p + 1), __ldg(p + 2), __ldg(p + 3));
-                }
-            }
-            v.x = ftz_bits(v.x); v.y = ftz_bits(v.y); v.z = ftz_bits(v.z); v.w = ftz_bits(v.w);
-            reinterpret_cast<float4 *>(xs + (size_t)mi * k)[q] = v;
-            atomicMin(&xkey[(4 * q) / g.leaf], key4(v, 0xFFFFFFFFu));
-        }
-    }
-    consumer_sync();
-
-    int s_base = 0;
+    // Every consumer warp waits on and releases EVERY stage in order (so no warp is
+    // ever more than the ring ahead of another), and computes the one leaf of the
+    // stage whose index is congruent to the warp modulo the consumer count.
+    int s_index = 0;
     bool alive = true;
-    for (int b = 0; b < blocks; b++, s_base += chunks) {
+    for (int b = 0; b < blocks; b++) {
         const int row0 = r_begin + b * DEC_ROWS;
         const int valid = min(DEC_ROWS, r_end - row0);
         const bool row_ok = lane < valid;
         float factor = 0.f;
-        bool wfast = true; // int8 kinds: the row's factor decides admission and the fused dequantisation
+        bool wfast = true; // int8 kinds: the row's factor decides admission
         if (WK == W_INT8_EXP || WK == W_INT8_SCALE) {
             if (row_ok)
                 factor = (WK == W_INT8_EXP) ? pow2_f32(__ldg(static_cast<const int *>(g.bscale) + row0 + lane))
@@ -262,35 +265,36 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) decode_kernel(const GemmArgs g
             const unsigned fexp = (__float_as_uint(factor) >> 23) & 0xFFu;
             wfast = fexp >= ADMIT_EXP; // |code * factor| >= |factor| for a nonzero code
         }
-        // this warp's leaves of the block: warp, warp + 8, ... (padded to whole stages so every stage gets LPS arrivals)
-        for (int t = warp; t < chunks * LPS && alive; t += DEC_CONSUMERS) {
-            const int s_index = s_base + t / LPS;
+        for (int c = 0; c < chunks && alive; c++, s_index++) {
             const int slot = s_index % nst;
             const unsigned round = (unsigned)(s_index / nst);
-            if (t < leaves) {
-                bool ok = true;
-                if (lane == 0) ok = mbar_wait(&full[slot], round & 1u);
-                ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
-                if (!ok) {
-                    if (lane == 0) atomicExch(&g_decode_status, 2);
-                    alive = false;
-                    break;
-                }
+            // every lane observes the completion itself: it reads what the copy engine wrote
+            const bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&full[slot], round & 1u));
+            if (!ok) {
+                if (lane == 0) atomicExch(&g_decode_status, 2);
+                alive = false;
+                break;
+            }
+            // the leaf of this stage that belongs to this warp, if any
+            const int j = (warp - (c * LPS) % DEC_CONSUMERS + DEC_CONSUMERS) % DEC_CONSUMERS;
+            const int t = c * LPS + j;
+            if (j < LPS && t < leaves) {
                 const int len = min(g.leaf, k - t * g.leaf);
-                const unsigned char *w = stage_base + (size_t)slot * DEC_STAGE_BYTES + (size_t)lane * DEC_PITCH +
-                                         (size_t)(t % LPS) * K_LEAF_MIN * ES;
-                const float *x = xs + (size_t)t * g.leaf;
+                const unsigned char *slot_base = stage_base + (size_t)slot * stage_bytes;
+                const unsigned char *w = slot_base + (size_t)lane * DEC_PITCH + (size_t)j * K_LEAF_MIN * ES;
+                const float *x = reinterpret_cast<const float *>(slot_base + (size_t)DEC_ROWS * DEC_PITCH) + (size_t)j * K_LEAF_MIN;
+                const bool xfast = leaf_x_admitted<M>(x, XSTRIDE, len, lane);
                 float acc[M];
 #pragma unroll
                 for (int mi = 0; mi < M; mi++) acc[mi] = 0.f;
                 unsigned wkey = 0xFFFFFFFFu;
-                leaf_chain<WK, M, false>(w, x, k, len, factor, acc, wkey);
-                bool admitted = (wkey >= ADMIT_MIN) && wfast && (xkey[t] >= ADMIT_MIN);
+                leaf_chain<WK, M, false>(w, x, XSTRIDE, len, factor, acc, wkey);
+                bool admitted = (wkey >= ADMIT_MIN) && wfast && xfast;
                 if (!row_ok) admitted = true;
                 if (!__all_sync(0xFFFFFFFFu, admitted)) {
 #pragma unroll
                     for (int mi = 0; mi < M; mi++) acc[mi] = 0.f;
-                    leaf_chain<WK, M, true>(w, x, k, len, factor, acc, wkey);
+                    leaf_chain<WK, M, true>(w, x, XSTRIDE, len, factor, acc, wkey);
                 }
 #pragma unroll
                 for (int mi = 0; mi < M; mi++) part[((size_t)mi * leaves + t) * DEC_ROWS + lane] = ftz_hw(acc[mi]);
@@ -303,21 +307,18 @@ __global__ void __launch_bounds__(DEC_THREADS, 1) decode_kernel(const GemmArgs g
         // fold: one thread per cell of the block
         for (int cell = tid; cell < M * DEC_ROWS; cell += 32 * DEC_CONSUMERS) {
             const int mi = cell / DEC_ROWS, r = cell % DEC_ROWS;
-            if (mi < g.m && r < valid && alive) {
+            if (r < valid && alive) {
                 float stack[FOLD_LEVELS];
+                float v = 0.f;
                 for (int t = 0; t < leaves; t++) {
-                    float v = part[((size_t)mi * leaves + t) * DEC_ROWS + r];
+                    v = part[((size_t)mi * leaves + t) * DEC_ROWS + r];
+                    if (t + 1 == leaves) break; // the last partial stays in a register for the drain
                     int lvl = 0;
                     for (int bits = t; bits & 1; bits >>= 1, lvl++) v = fold_add(stack[lvl], v);
                     stack[lvl] = v;
                 }
-                float v = 0.f;
-                bool have = false;
-                for (int lvl = 0; lvl < FOLD_LEVELS; lvl++)
-                    if ((leaves >> lvl) & 1) {
-                        v = have ? fold_add(stack[lvl], v) : stack[lvl];
-                        have = true;
-                    }
+                for (int lvl = 0, last = leaves - 1; lvl < FOLD_LEVELS; lvl++)
+                    if ((last >> lvl) & 1) v = fold_add(stack[lvl], v);
                 g.c[(size_t)mi * n + row0 + r] = nan_canon(ftz_hw(v));
             }
         }
@@ -350,7 +351,7 @@ inline int launch_decode_m(const GemmArgs &g, int grid, size_t smem, cudaStream_
 
 // Returns the number of kernels launched.
 inline int launch_decode(const GemmArgs &g, int sms, cudaStream_t st) {
-    const DecodeLayout lay = decode_layout(g.m, g.k, g.leaves);
+    const DecodeLayout lay = decode_layout(g.m, g.k, g.leaves, g.wkind);
     int grid = sms;
     const int max_grid = (g.n + 7) / 8; // no CTA with fewer than ~8 rows
     if (grid > max_grid) grid = max_grid;

@@ -263,26 +263,28 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
         }
     };
 
-    // leaf boundary: push the partial on the binary-counter stack
+    // leaf boundary: push the partial on the binary-counter stack. The merge depth
+    // depends on the leaf index alone, so the walk is level-major: all TM*TN loads
+    // of a level are independent and in flight together.
     auto push_leaf = [&](int local_leaf) {
+        float v[TM * TN];
 #pragma unroll
         for (int i = 0; i < TM; i++)
 #pragma unroll
             for (int j = 0; j < TN / 2; j++) {
                 float v0, v1;
                 unpack2(acc[i][j], v0, v1);
-                v0 = ftz_hw(v0);
-                v1 = ftz_hw(v1);
-                const int c = i * TN + 2 * j;
-                int lvl = 0;
-                for (int bits = local_leaf; bits & 1; bits >>= 1, lvl++) {
-                    v0 = fold_add(stack[lvl][c], v0);
-                    v1 = fold_add(stack[lvl][c + 1], v1);
-                }
-                stack[lvl][c] = v0;
-                stack[lvl][c + 1] = v1;
+                v[i * TN + 2 * j] = ftz_hw(v0);
+                v[i * TN + 2 * j + 1] = ftz_hw(v1);
                 acc[i][j] = 0ull;
             }
+        int lvl = 0;
+        for (int bits = local_leaf; bits & 1; bits >>= 1, lvl++) {
+#pragma unroll
+            for (int c = 0; c < TM * TN; c++) v[c] = fold_add(stack[lvl][c], v[c]);
+        }
+#pragma unroll
+        for (int c = 0; c < TM * TN; c++) stack[lvl][c] = v[c];
     };
 
     if (t_first < t_end) {
@@ -310,8 +312,8 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
 #pragma unroll 1
                 for (int kk = 0; kk < len; kk++) step_slow(buf, kk);
             }
-            if (nt != t) { // this window closed its leaf
-                if (g.leaves > 1) push_leaf(t - t_first);
+            if (nt != t) { // this window closed its leaf; the group's last leaf stays in registers for the drain
+                if (more) push_leaf(t - t_first);
                 leaf_clean = true;
             }
             if (!more) break;
@@ -323,9 +325,31 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
         }
     }
 
-    // drain the stack (lowest occupied level first: the carry rule) and store
+    // Drain and store. The group's last partial is still in registers: pushing it
+    // would merge it with every level whose bit is set in its index below the first
+    // clear bit, and the drain would then add the remaining occupied levels in
+    // ascending order (the carry rule). Together: add stack[l] for every set bit l of
+    // (count - 1), ascending, level-major so the loads of a level fly together.
     const int count = t_end - t_first;
     float *out = g.groups > 1 ? g.ws + (size_t)blockIdx.y * (size_t)g.m * (size_t)g.n : g.c;
+    float v[TM * TN];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN / 2; j++) {
+            float v0, v1;
+            unpack2(acc[i][j], v0, v1);
+            v[i * TN + 2 * j] = ftz_hw(v0);
+            v[i * TN + 2 * j + 1] = ftz_hw(v1);
+        }
+    if (count > 1) {
+        const int last = count - 1;
+        for (int lvl = 0; lvl < FOLD_LEVELS; lvl++)
+            if ((last >> lvl) & 1) {
+#pragma unroll
+                for (int c = 0; c < TM * TN; c++) v[c] = fold_add(stack[lvl][c], v[c]);
+            }
+    }
 #pragma unroll
     for (int i = 0; i < TM; i++) {
         const int row = bm0 + (i / 4) * (BM / RM) + ty * 4 + (i % 4);
@@ -333,25 +357,7 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
         for (int jr = 0; jr < RN; jr++) {
             float vals[4];
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int cj = jr * 4 + e;
-                float v;
-                if (g.leaves > 1) {
-                    const int c = i * TN + cj;
-                    bool have = false;
-                    v = 0.f;
-                    for (int lvl = 0; lvl < FOLD_LEVELS; lvl++)
-                        if ((count >> lvl) & 1) {
-                            v = have ? fold_add(stack[lvl][c], v) : stack[lvl][c];
-                            have = true;
-                        }
-                } else {
-                    float v0, v1;
-                    unpack2(acc[i][cj / 2], v0, v1);
-                    v = (cj & 1) ? v1 : v0;
-                }
-                vals[e] = nan_canon(ftz_hw(v));
-            }
+            for (int e = 0; e < 4; e++) vals[e] = nan_canon(ftz_hw(v[i * TN + jr * 4 + e]));
             const int col = bn0 + jr * (BN / RN) + tx * 4;
             if (row < g.m) {
                 float *dst = out + (size_t)row * (size_t)g.n + col;

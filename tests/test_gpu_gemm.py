@@ -4,6 +4,8 @@ CPU oracle, bit for bit. Modelled on the reference's device gates
 :1016, batch invariance :1464) and its Python-surface gate
 (python/mojolearn/tests/test_linalg_identity.py: shapes chosen by leaf count
 with m, n, k pairwise distinct, :382-412)."""
+import ctypes
+
 import numpy as np
 import pytest
 
@@ -159,8 +161,15 @@ def test_config2_full_size_rows_sampled_against_the_oracle(m, n, k):
 
 def test_c_abi_refusals_on_device():
     a = torch.zeros((4, 4), device="cuda")
-    with pytest.raises(_native.NativeError):
+    with pytest.raises(ValueError):
         torch_ops.product(a, a, None, linalg.W_F32, 7)
+    buf = ctypes.create_string_buffer(256)
+    rc = _native.lib().b200i_gemm_f32(0, None, a.data_ptr(), a.data_ptr(), a.data_ptr(), 4, 4, 4, 7, None, 0,
+                                      ctypes.cast(buf, ctypes.c_void_p), 256)
+    assert rc == 1 and b"unknown op" in buf.value
+    rc = _native.lib().b200i_gemm_f32(0, None, a.data_ptr(), a.data_ptr(), a.data_ptr(), 0, 4, 4, 0, None, 0,
+                                      ctypes.cast(buf, ctypes.c_void_p), 256)
+    assert rc == 1 and b"must be positive" in buf.value
     with pytest.raises(TypeError):
         torch_ops.product(a.double(), a)
     with pytest.raises(ValueError):

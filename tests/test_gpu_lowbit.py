@@ -88,7 +88,9 @@ def test_config3_full_size(m):
     wf = oracle.from_bf16(wb[cols])
     assert gotb.cpu().numpy()[:, cols].tobytes() == oracle.gemm_rows(x, wf, oracle.OP_NT).tobytes()
     # every plan that accepts the shape returns the same words
-    plans = [(torch_ops.PLAN_T128, 0), (torch_ops.PLAN_T64, 4)] + ([(torch_ops.PLAN_DECODE, 0)] if m <= 8 else [])
+    fits = _native.lib().b200i_decode_plan_fits(m, n, k, oracle.OP_NT, linalg.W_INT8_EXP)
+    assert fits == (1 if m <= 8 else 0)
+    plans = [(torch_ops.PLAN_T128, 0), (torch_ops.PLAN_T64, 4)] + ([(torch_ops.PLAN_DECODE, 0)] if fits else [])
     for plan, groups in plans:
         alt = torch_ops.product(dx, dcodes, dexps, linalg.W_INT8_EXP, oracle.OP_NT, plan=plan, group_leaves=groups)
         assert torch.equal(alt.view(torch.int32), got8.view(torch.int32)), (plan, groups)
@@ -101,13 +103,14 @@ def test_decode_plan_edges():
     """Ragged row counts per CTA, k below one leaf, k with a short last leaf,
     subnormal-forcing weights and activations, exotic exponents."""
     rng = np.random.default_rng(8)
-    for (m, n, k) in [(1, 7, 16), (3, 33, 128), (8, 1000, 1040), (2, 4097, 2048), (4, 300, 8192), (1, 50304, 768)]:
+    for (m, n, k) in [(1, 7, 16), (3, 33, 128), (8, 1000, 1040), (2, 4097, 2048), (4, 300, 8192), (8, 70, 8192), (1, 50304, 768), (8, 48, 384)]:
         x = rng.standard_normal((m, k)).astype(np.float32)
         w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
         dx, dw = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
         want = oracle.gemm_rows(x, w, oracle.OP_NT)
         got = torch_ops.product(dx, dw, None, linalg.W_F32, oracle.OP_NT, plan=torch_ops.PLAN_DECODE)
         assert got.cpu().numpy().tobytes() == want.tobytes(), (m, n, k)
+        assert _native.lib().b200i_decode_status(-1) == 0, (m, n, k)
     m, n, k = 4, 200, 512
     x = (rng.standard_normal((m, k)) * 2.0 ** -62).astype(np.float32)
     x[0, ::9] = np.float32(3e-42)
