@@ -75,7 +75,7 @@ int64_t b200i_gemm_w(int64_t device, void *stream, float *c, const float *a, con
 
 /* Same, with the execution plan forced: plan 0 = one thread per cell (the
  * on-device restatement of the oracle), 1 = 128x128 tiles, 2 = 64x64 tiles,
- * 3 = the row-streaming decode plan; `group_leaves` = leaves per group (a
+ * 3 = the row-streaming decode plan, 4 = 32x128 tiles; `group_leaves` = leaves per group (a
  * power of two, 0 = no split). Every plan returns the same bits; the tests
  * hold them to that (the reference's launch-invariance gate,
  * gemm/checks/gemm_device_check.mojo:1016). */

@@ -8,7 +8,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libb200i.so")
+#: MOJOLEARN_B200_LIB overrides the in-tree library (a differently built libb200i.so with the same ABI).
+LIB_PATH = os.environ.get("MOJOLEARN_B200_LIB") or os.path.join(_HERE, "csrc", "libb200i.so")
 ERR_CAP = 512
 
 _lib = None

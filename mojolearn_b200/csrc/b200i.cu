@@ -67,12 +67,22 @@ int select_device(int64_t device, char *err, int64_t err_cap, int *out) {
 }
 
 // ---- plans -----------------------------------------------------------------------------
-enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3 };
+enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4 };
 
 struct Plan {
     int kind;
     int group_leaves; // S
     int groups;       // G
+};
+
+struct TileCfg {
+    int kind, bm, bn, per_sm;
+    double eff; // fraction of the fused-multiply-add peak the kernel sustains on a full tile (measured)
+};
+const TileCfg TILE_CFGS[] = {
+    {PLAN_T128, 128, 128, 2, 0.55},
+    {PLAN_T64, 64, 64, 3, 0.33},
+    {PLAN_T32, 32, 128, 4, 0.40},
 };
 
 int pow2_floor(int v) {
@@ -81,19 +91,19 @@ int pow2_floor(int v) {
     return p;
 }
 
-// Modelled time of a tiled plan in units of one SM-cycle-equivalent of fused
-// multiply-adds: waves of CTAs over the SM slots, each CTA running its share of
-// the leaves, plus the traffic of the group nodes when the leaves are split.
-double tiled_cost(int bm, int bn, double eff, int per_sm, long long m, long long n, int leaf, int leaves, int s, int sms) {
-    const long long tiles = ((m + bm - 1) / bm) * ((n + bn - 1) / bn);
+// Modelled time of a tiled plan in SM cycles: waves of CTAs over the SM slots,
+// each CTA running its share of the leaves, plus the traffic of the group nodes
+// and the second launch when the leaves are split.
+double tiled_cost(const TileCfg &cfg, long long m, long long n, int leaf, int leaves, int s, int sms) {
+    const long long tiles = ((m + cfg.bm - 1) / cfg.bm) * ((n + cfg.bn - 1) / cfg.bn);
     const int groups = (leaves + s - 1) / s;
     const long long ctas = tiles * groups;
-    const long long slots = (long long)sms * per_sm;
+    const long long slots = (long long)sms * cfg.per_sm;
     const long long waves = (ctas + slots - 1) / slots;
-    const double cta = (double)bm * bn * (double)leaf * s * per_sm / (128.0 * eff);
-    double t = (double)waves * cta;
-    if (groups > 1) t += (double)groups * m * n * 8.0 / (6.0e12 / 1.9e9) / 1.0 + 4000.0; // node write+read at HBM rate, second launch
-    return t + 3000.0;
+    const double cta = (double)cfg.bm * cfg.bn * (double)leaf * s * cfg.per_sm / (128.0 * cfg.eff);
+    double t = (double)waves * cta + 4000.0;
+    if (groups > 1) t += (double)groups * m * n * 8.0 / 2500.0 + 6000.0; // node write + read at HBM rate, second launch
+    return t;
 }
 
 Plan choose_plan(long long m, long long n, long long k, int sms) {
@@ -101,19 +111,31 @@ Plan choose_plan(long long m, long long n, long long k, int sms) {
     Plan best{PLAN_T128, leaves > 0 ? leaves : 1, 1};
     double best_t = 1e300;
     const int max_s = pow2_floor(leaves > 0 ? leaves : 1) * ((leaves & (leaves - 1)) ? 2 : 1);
-    for (int kind = PLAN_T128; kind <= PLAN_T64; kind++) {
-        const int bm = kind == PLAN_T128 ? 128 : 64;
-        const double eff = kind == PLAN_T128 ? 1.0 : 0.72;
-        const int per_sm = kind == PLAN_T128 ? 2 : 3;
+    for (const TileCfg &cfg : TILE_CFGS) {
         for (int s = max_s; s >= 1; s /= 2) {
             const int groups = (leaves + s - 1) / s;
             if (groups > MAX_GROUPS) break;
-            const double t = tiled_cost(bm, bm, eff, per_sm, m, n, leaf, leaves, s, sms);
-            if (t < best_t) { best_t = t; best = Plan{kind, s, groups}; }
+            const double t = tiled_cost(cfg, m, n, leaf, leaves, s, sms);
+            if (t < best_t) { best_t = t; best = Plan{cfg.kind, s, groups}; }
         }
     }
     if (best.groups <= 1) best.group_leaves = leaves > 0 ? leaves : 1;
     return best;
+}
+
+template <int BM, int BN, int RM, int RN, int MINB>
+void launch_tile(GemmArgs &g, int groups, cudaStream_t st) {
+    using S = TileShape<BM, BN, RM, RN>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaFuncSetAttribute(gemm_tile_kernel<BM, BN, RM, RN, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
+        configured[dev] = true;
+    }
+    g.tiles_n = (g.n + BN - 1) / BN;
+    dim3 grid((unsigned)(((g.m + BM - 1) / BM) * g.tiles_n), (unsigned)groups);
+    gemm_tile_kernel<BM, BN, RM, RN, MINB><<<grid, S::THREADS, S::SMEM_BYTES, st>>>(g);
 }
 
 bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
@@ -185,14 +207,13 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
             return fail(err, err_cap, "identical gemm: the decode plan needs op NT, m <= %d, k a multiple of 16 and 16-byte aligned weights", DECODE_MAX_M);
         g_launches += launch_decode(g, sm_count(dev), st);
     } else if (plan.kind == PLAN_T128) {
-        g.tiles_n = (int)((n + 127) / 128);
-        dim3 grid((unsigned)(((m + 127) / 128) * g.tiles_n), (unsigned)plan.groups);
-        gemm_tile_kernel<128, 128, 2, 2, 2><<<grid, 256, 0, st>>>(g);
+        launch_tile<128, 128, 2, 2, 2>(g, plan.groups, st);
         g_launches++;
     } else if (plan.kind == PLAN_T64) {
-        g.tiles_n = (int)((n + 63) / 64);
-        dim3 grid((unsigned)(((m + 63) / 64) * g.tiles_n), (unsigned)plan.groups);
-        gemm_tile_kernel<64, 64, 1, 1, 3><<<grid, 256, 0, st>>>(g);
+        launch_tile<64, 64, 1, 1, 3>(g, plan.groups, st);
+        g_launches++;
+    } else if (plan.kind == PLAN_T32) {
+        launch_tile<32, 128, 1, 2, 4>(g, plan.groups, st);
         g_launches++;
     } else {
         return fail(err, err_cap, "identical gemm: unknown plan %d", plan.kind);

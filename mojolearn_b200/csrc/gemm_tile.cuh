@@ -47,6 +47,7 @@ struct TileShape {
     static constexpr int TM = 4 * RM, TN = 4 * RN;
     static constexpr int UNITS = BM + BN; // staging units of 16 words each
     static constexpr int UPT = (UNITS + THREADS - 1) / THREADS;
+    static constexpr int SMEM_BYTES = (2 * 16 * (BM + BN) + TM * TN * THREADS) * 4;
 };
 
 // ---- staging -------------------------------------------------------------------
@@ -54,56 +55,50 @@ struct TileShape {
 // of a k-contiguous operand (transposed through registers on the way to shared
 // memory) or 4 k-rows x 4 consecutive cells of a cell-contiguous operand.
 
-__device__ __forceinline__ float4 ld4_f32(const float *p, bool vec, int valid) {
-    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+// Raw words of one unit as they come out of global memory. Nothing here touches
+// a loaded value, so the loads stay in flight while the previous window computes;
+// widening, dequantisation and the admission key happen at store time.
+struct UnitRaw {
+    uint4 w[4];    // float32: 4 words; bf16: 4 patterns in .x/.y; int8: 4 codes in .x
+    unsigned f[4]; // int8 kinds, k-contiguous: the row's raw exponent or scale word
+};
+
+__device__ __forceinline__ uint4 ld4_words(const float *p, bool vec, int valid) {
+    uint4 r = make_uint4(0u, 0u, 0u, 0u);
     if (valid <= 0) return r;
-    if (vec) return __ldg(reinterpret_cast<const float4 *>(p));
-    r.x = __ldg(p);
-    if (valid > 1) r.y = __ldg(p + 1);
-    if (valid > 2) r.z = __ldg(p + 2);
-    if (valid > 3) r.w = __ldg(p + 3);
+    if (vec) return __ldg(reinterpret_cast<const uint4 *>(p));
+    r.x = __float_as_uint(__ldg(p));
+    if (valid > 1) r.y = __float_as_uint(__ldg(p + 1));
+    if (valid > 2) r.z = __float_as_uint(__ldg(p + 2));
+    if (valid > 3) r.w = __float_as_uint(__ldg(p + 3));
     return r;
 }
-__device__ __forceinline__ float4 ld4_bf16(const unsigned short *p, bool vec, int valid) {
-    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+__device__ __forceinline__ uint4 ld4_halves(const unsigned short *p, bool vec, int valid) {
+    uint4 r = make_uint4(0u, 0u, 0u, 0u);
     if (valid <= 0) return r;
     if (vec) {
-        uint2 w = __ldg(reinterpret_cast<const uint2 *>(p));
-        r.x = __uint_as_float(w.x << 16);
-        r.y = __uint_as_float(w.x & 0xFFFF0000u);
-        r.z = __uint_as_float(w.y << 16);
-        r.w = __uint_as_float(w.y & 0xFFFF0000u);
+        const uint2 w = __ldg(reinterpret_cast<const uint2 *>(p));
+        r.x = w.x;
+        r.y = w.y;
         return r;
     }
-    r.x = bf16_bits_to_f32(__ldg(p));
-    if (valid > 1) r.y = bf16_bits_to_f32(__ldg(p + 1));
-    if (valid > 2) r.z = bf16_bits_to_f32(__ldg(p + 2));
-    if (valid > 3) r.w = bf16_bits_to_f32(__ldg(p + 3));
+    r.x = __ldg(p);
+    if (valid > 1) r.x |= (unsigned)__ldg(p + 1) << 16;
+    if (valid > 2) r.y = __ldg(p + 2);
+    if (valid > 3) r.y |= (unsigned)__ldg(p + 3) << 16;
     return r;
 }
-// int8 codes times one row factor; `pinned` picks the power-of-two spelling
-// (code * 2^e, flushed) or the general scale (code * s, one pinned product, flushed).
-__device__ __forceinline__ float4 ld4_int8(const signed char *p, bool vec, int valid, float factor) {
-    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+__device__ __forceinline__ uint4 ld4_bytes(const signed char *p, bool vec, int valid) {
+    uint4 r = make_uint4(0u, 0u, 0u, 0u);
     if (valid <= 0) return r;
-    int c0, c1 = 0, c2 = 0, c3 = 0;
     if (vec) {
-        int w = __ldg(reinterpret_cast<const int *>(p));
-        c0 = (int)(signed char)(w & 0xFF);
-        c1 = (int)(signed char)((w >> 8) & 0xFF);
-        c2 = (int)(signed char)((w >> 16) & 0xFF);
-        c3 = w >> 24;
-        valid = 4;
-    } else {
-        c0 = __ldg(p);
-        if (valid > 1) c1 = __ldg(p + 1);
-        if (valid > 2) c2 = __ldg(p + 2);
-        if (valid > 3) c3 = __ldg(p + 3);
+        r.x = (unsigned)__ldg(reinterpret_cast<const int *>(p));
+        return r;
     }
-    r.x = dequant_int8_pow2(c0, factor);
-    if (valid > 1) r.y = dequant_int8_pow2(c1, factor);
-    if (valid > 2) r.z = dequant_int8_pow2(c2, factor);
-    if (valid > 3) r.w = dequant_int8_pow2(c3, factor);
+    r.x = (unsigned)(unsigned char)__ldg(p);
+    if (valid > 1) r.x |= (unsigned)(unsigned char)__ldg(p + 1) << 8;
+    if (valid > 2) r.x |= (unsigned)(unsigned char)__ldg(p + 2) << 16;
+    if (valid > 3) r.x |= (unsigned)(unsigned char)__ldg(p + 3) << 24;
     return r;
 }
 
@@ -119,8 +114,8 @@ __device__ __forceinline__ unsigned key4(float4 v, unsigned k) {
 // tile) or of the right operand (E = BN). `kcontig` says the operand's storage
 // is contiguous along k.
 template <int E>
-__device__ __forceinline__ void unit_load(float4 (&r)[4], int u, const void *base, int wkind, const void *scale,
-                                          bool kcontig, bool vec, int e0, int extent, int kdim, int k0) {
+__device__ __forceinline__ void unit_load(UnitRaw &r, int u, const void *base, int wkind, const void *scale, bool kcontig,
+                                          bool vec, int e0, int extent, int kdim, int k0) {
     const int lane_e = u % (E / 4), quad = u / (E / 4);
     if (kcontig) {
         const int kk = k0 + 4 * quad;
@@ -130,14 +125,12 @@ __device__ __forceinline__ void unit_load(float4 (&r)[4], int u, const void *bas
             const int row = e0 + 4 * lane_e + c;
             const int valid = (row < extent) ? kvalid : 0;
             const size_t off = (size_t)row * (size_t)kdim + (size_t)kk;
-            if (wkind == W_F32) r[c] = ld4_f32(static_cast<const float *>(base) + off, vec, valid);
-            else if (wkind == W_BF16) r[c] = ld4_bf16(static_cast<const unsigned short *>(base) + off, vec, valid);
+            r.f[c] = 0u;
+            if (wkind == W_F32) r.w[c] = ld4_words(static_cast<const float *>(base) + off, vec, valid);
+            else if (wkind == W_BF16) r.w[c] = ld4_halves(static_cast<const unsigned short *>(base) + off, vec, valid);
             else {
-                float factor = 0.f;
-                if (valid > 0)
-                    factor = (wkind == W_INT8_EXP) ? pow2_f32(__ldg(static_cast<const int *>(scale) + row))
-                                                   : __ldg(static_cast<const float *>(scale) + row);
-                r[c] = ld4_int8(static_cast<const signed char *>(base) + off, vec, valid, factor);
+                if (valid > 0) r.f[c] = __ldg(static_cast<const unsigned *>(scale) + row);
+                r.w[c] = ld4_bytes(static_cast<const signed char *>(base) + off, vec, valid);
             }
         }
     } else {
@@ -148,8 +141,30 @@ __device__ __forceinline__ void unit_load(float4 (&r)[4], int u, const void *bas
             const int kk = k0 + 4 * quad + c;
             const int valid = (kk < kdim) ? cvalid : 0;
             const size_t off = (size_t)kk * (size_t)extent + (size_t)col;
-            if (wkind == W_BF16) r[c] = ld4_bf16(static_cast<const unsigned short *>(base) + off, vec, valid);
-            else r[c] = ld4_f32(static_cast<const float *>(base) + off, vec, valid);
+            r.f[c] = 0u;
+            if (wkind == W_BF16) r.w[c] = ld4_halves(static_cast<const unsigned short *>(base) + off, vec, valid);
+            else r.w[c] = ld4_words(static_cast<const float *>(base) + off, vec, valid);
+        }
+    }
+}
+
+// The float32 words a unit stands for: exact widening / dequantisation.
+__device__ __forceinline__ void unit_widen(const UnitRaw &r, int wkind, float4 (&v)[4]) {
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const uint4 w = r.w[c];
+        if (wkind == W_F32) {
+            v[c] = make_float4(__uint_as_float(w.x), __uint_as_float(w.y), __uint_as_float(w.z), __uint_as_float(w.w));
+        } else if (wkind == W_BF16) {
+            v[c] = make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xFFFF0000u), __uint_as_float(w.y << 16),
+                               __uint_as_float(w.y & 0xFFFF0000u));
+        } else {
+            const float factor = (wkind == W_INT8_EXP) ? pow2_f32((int)r.f[c]) : __uint_as_float(r.f[c]);
+            const int word = (int)w.x;
+            v[c] = make_float4(dequant_int8_pow2((int)(signed char)(word & 0xFF), factor),
+                               dequant_int8_pow2((int)(signed char)((word >> 8) & 0xFF), factor),
+                               dequant_int8_pow2((int)(signed char)((word >> 16) & 0xFF), factor),
+                               dequant_int8_pow2(word >> 24, factor));
         }
     }
 }
@@ -174,8 +189,11 @@ template <int BM, int BN, int RM, int RN, int MINB>
 __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) gemm_tile_kernel(const GemmArgs g) {
     using S = TileShape<BM, BN, RM, RN>;
     constexpr int TM = S::TM, TN = S::TN, NT = S::THREADS, UPT = S::UPT;
-    __shared__ __align__(16) float As[2][KS][BM];
-    __shared__ __align__(16) float Bs[2][KS][BN];
+    // dynamic shared memory: two pages of each operand window, then level 0 of the fold stack
+    extern __shared__ __align__(16) float tile_smem[];
+    float (*As)[KS][BM] = reinterpret_cast<float (*)[KS][BM]>(tile_smem);
+    float (*Bs)[KS][BN] = reinterpret_cast<float (*)[KS][BN]>(tile_smem + 2 * KS * BM);
+    float (*level0)[NT] = reinterpret_cast<float (*)[NT]>(tile_smem + 2 * KS * (BM + BN)); // [cell][thread]: conflict free
 
     const int tid = threadIdx.x;
     const int tx = tid % S::TX, ty = tid / S::TX;
@@ -194,32 +212,34 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
 #pragma unroll
         for (int j = 0; j < TN / 2; j++) acc[i][j] = 0ull;
 
-    float stack[FOLD_LEVELS][TM * TN]; // local memory; touched once per leaf
+    float stack[FOLD_LEVELS - 1][TM * TN]; // levels 1.. in local memory (level 0 is in shared memory)
 
-    float4 stage[UPT][4];
+    UnitRaw stage[UPT];
     unsigned stage_key;
 
-    auto load_window = [&](int t, int koff) {
+    auto load_window = [&](int t, int koff) { // loads only: nothing waits on them until store_window
         const int k0 = t * g.leaf + koff;
-        stage_key = 0xFFFFFFFFu;
 #pragma unroll
         for (int i = 0; i < UPT; i++) {
             const int u = tid + i * NT;
             if (u < BM) unit_load<BM>(stage[i], u, g.a, W_F32, nullptr, a_kcontig, g.vec_a, bm0, g.m, g.k, k0);
             else if (u < BM + BN)
                 unit_load<BN>(stage[i], u - BM, g.b, g.wkind, g.bscale, b_kcontig, g.vec_b, bn0, g.n, g.k, k0);
-            if (u < BM + BN) {
-#pragma unroll
-                for (int c = 0; c < 4; c++) stage_key = key4(stage[i][c], stage_key);
-            }
         }
     };
-    auto store_window = [&](int buf) {
+    auto store_window = [&](int buf) { // widen, fold the admission key, store
+        stage_key = 0xFFFFFFFFu;
 #pragma unroll
         for (int i = 0; i < UPT; i++) {
             const int u = tid + i * NT;
-            if (u < BM) unit_store<BM>(stage[i], u, As[buf], a_kcontig);
-            else if (u < BM + BN) unit_store<BN>(stage[i], u - BM, Bs[buf], b_kcontig);
+            if (u < BM + BN) {
+                float4 v[4];
+                unit_widen(stage[i], u < BM ? W_F32 : g.wkind, v);
+#pragma unroll
+                for (int c = 0; c < 4; c++) stage_key = key4(v[c], stage_key);
+                if (u < BM) unit_store<BM>(v, u, As[buf], a_kcontig);
+                else unit_store<BN>(v, u - BM, Bs[buf], b_kcontig);
+            }
         }
     };
 
@@ -278,13 +298,20 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
                 v[i * TN + 2 * j + 1] = ftz_hw(v1);
                 acc[i][j] = 0ull;
             }
-        int lvl = 0;
-        for (int bits = local_leaf; bits & 1; bits >>= 1, lvl++) {
+        if ((local_leaf & 1) == 0) { // an even leaf waits at level 0 for its right sibling
 #pragma unroll
-            for (int c = 0; c < TM * TN; c++) v[c] = fold_add(stack[lvl][c], v[c]);
+            for (int c = 0; c < TM * TN; c++) level0[c][tid] = v[c];
+            return;
         }
 #pragma unroll
-        for (int c = 0; c < TM * TN; c++) stack[lvl][c] = v[c];
+        for (int c = 0; c < TM * TN; c++) v[c] = fold_add(level0[c][tid], v[c]);
+        int lvl = 1;
+        for (int bits = local_leaf >> 1; bits & 1; bits >>= 1, lvl++) {
+#pragma unroll
+            for (int c = 0; c < TM * TN; c++) v[c] = fold_add(stack[lvl - 1][c], v[c]);
+        }
+#pragma unroll
+        for (int c = 0; c < TM * TN; c++) stack[lvl - 1][c] = v[c];
     };
 
     if (t_first < t_end) {
@@ -344,10 +371,14 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
         }
     if (count > 1) {
         const int last = count - 1;
-        for (int lvl = 0; lvl < FOLD_LEVELS; lvl++)
+        if (last & 1) {
+#pragma unroll
+            for (int c = 0; c < TM * TN; c++) v[c] = fold_add(level0[c][tid], v[c]);
+        }
+        for (int lvl = 1; lvl < FOLD_LEVELS; lvl++)
             if ((last >> lvl) & 1) {
 #pragma unroll
-                for (int c = 0; c < TM * TN; c++) v[c] = fold_add(stack[lvl][c], v[c]);
+                for (int c = 0; c < TM * TN; c++) v[c] = fold_add(stack[lvl - 1][c], v[c]);
             }
     }
 #pragma unroll

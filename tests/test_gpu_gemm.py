@@ -18,7 +18,7 @@ from mojolearn_b200 import _native, linalg, torch_ops  # noqa: E402
 
 OPS = {"NN": oracle.OP_NN, "NT": oracle.OP_NT, "TN": oracle.OP_TN}
 PLANS = [(torch_ops.PLAN_FLAT, 0), (torch_ops.PLAN_T128, 0), (torch_ops.PLAN_T64, 0), (torch_ops.PLAN_T128, 1),
-         (torch_ops.PLAN_T64, 2), (torch_ops.PLAN_T128, 4)]
+         (torch_ops.PLAN_T64, 2), (torch_ops.PLAN_T128, 4), (torch_ops.PLAN_T32, 0), (torch_ops.PLAN_T32, 2)]
 
 # (m, n, k): P = 1, 2, 3 (ragged, odd carry), 5 (carries twice), 6, 8 with a short last leaf, tails, k = 1
 SHAPES = [(40, 20, 300), (11, 6, 640), (9, 5, 256), (17, 3, 64), (8, 48, 384), (36, 9, 300), (1, 1, 1), (5, 7, 1),
