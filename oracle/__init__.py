@@ -241,3 +241,125 @@ def train_hash(parts):
     (tools/identity_break.py:1374-1380)."""
     text = "|".join("%s=%s" % (k, v) for k, v in sorted(parts.items()))
     return sha16(np.frombuffer(text.encode(), dtype=np.uint8))
+
+
+# ---- decoder seams (decoder_oracle.c) --------------------------------------------------------
+
+NORM_KINDS = {"rmsnorm": 0, "layernorm": 1, "rmsnorm_offset": 2}
+MLP_KINDS = {"swiglu": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "geglu": 4, "geglu_tanh": 5}
+WEIGHT_SLOTS = ["norm1", "norm1_b", "q", "q_b", "k", "k_b", "v", "v_b", "o", "o_b", "norm2", "norm2_b", "gate", "gate_b",
+                "up", "up_b", "down", "down_b"]
+
+
+class BlockCfg(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("d_model", "n_heads", "n_kv_heads", "head_dim", "inter", "norm_kind",
+                                              "norm_bias", "qkv_bias", "o_bias", "mlp_kind", "mlp_bias", "rope", "window")] + \
+               [("norm_eps", ctypes.c_float), ("rope_theta", ctypes.c_float)]
+
+
+def block_cfg(d_model, n_heads, n_kv_heads=None, head_dim=None, inter=None, norm="rmsnorm", norm_eps=1e-6, norm_bias=False,
+              qkv_bias=False, o_bias=False, mlp="swiglu", mlp_bias=False, rope=True, rope_theta=10000.0, window=0):
+    n_kv_heads = n_kv_heads or n_heads
+    head_dim = head_dim or d_model // n_heads
+    return BlockCfg(d_model, n_heads, n_kv_heads, head_dim, inter, NORM_KINDS[norm], int(norm_bias), int(qkv_bias),
+                    int(o_bias), MLP_KINDS[mlp], int(mlp_bias), int(rope), int(window), norm_eps, rope_theta)
+
+
+def _math1(name):
+    fn = getattr(lib(), name)
+    fn.restype = ctypes.c_float
+    fn.argtypes = [ctypes.c_float]
+    return lambda x: np.float32(fn(ctypes.c_float(float(x))))
+
+
+def math(name, *args):
+    """One of the portable scalar functions: expf logf sqrtf rsqrtf cosf sinf siluf tanhf erff gelu_erf gelu_tanh
+    (one argument), powf divf fmaxf (two)."""
+    fn = getattr(lib(), "p_" + name)
+    fn.restype = ctypes.c_float
+    fn.argtypes = [ctypes.c_float] * len(args)
+    return np.float32(fn(*[ctypes.c_float(float(np.float32(a))) for a in args]))
+
+
+def norm(x, w, bias=None, eps=1e-6, kind="rmsnorm"):
+    x = _f32(x)
+    w = _f32(w)
+    m, dm = int(np.prod(x.shape[:-1])), x.shape[-1]
+    out = np.empty_like(x)
+    b = _f32(bias) if bias is not None else None
+    f = lib().dec_norm
+    f.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_int]
+    f(_ptr(out), _ptr(x), _ptr(w), _ptr(b) if b is not None else None, m, dm, ctypes.c_float(eps), NORM_KINDS[kind])
+    return out
+
+
+def rope_table(pos0, l, head_dim, theta=10000.0):
+    cosv = np.empty((l, head_dim // 2), np.float32)
+    sinv = np.empty((l, head_dim // 2), np.float32)
+    f = lib().dec_rope_table
+    f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_float]
+    f(_ptr(cosv), _ptr(sinv), pos0, l, head_dim, ctypes.c_float(theta))
+    return cosv, sinv
+
+
+class KVState(object):
+    """k and v caches [b, n_kv_heads, cap, head_dim] and the positions used."""
+
+    def __init__(self, b, n_kv, cap, head_dim):
+        self.k = np.zeros((b, n_kv, cap, head_dim), np.float32)
+        self.v = np.zeros((b, n_kv, cap, head_dim), np.float32)
+        self.used = 0
+        self.cap = cap
+
+
+def block_forward(cfg, weights, x, state=None, threads=None):
+    """One decoder block. `weights` maps slot names (WEIGHT_SLOTS) to float32 arrays in
+    torch `[out, in]` layout; x is [b, l, d_model]. With no state a fresh cache of l positions is used."""
+    x = _f32(x)
+    b, l, dm = x.shape
+    if state is None:
+        state = KVState(b, cfg.n_kv_heads, l, cfg.head_dim)
+    keep = [_f32(weights[s]) if weights.get(s) is not None else None for s in WEIGHT_SLOTS]
+    arr = (ctypes.c_void_p * len(WEIGHT_SLOTS))(*[(_ptr(a) if a is not None else None) for a in keep])
+    y = np.empty_like(x)
+    f = lib().dec_block_forward
+    f.restype = ctypes.c_int
+    f.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                          ctypes.c_int64, ctypes.c_int]
+    rc = f(ctypes.byref(cfg), arr, _ptr(x), _ptr(y), b, l, _ptr(state.k), _ptr(state.v), state.cap, state.used,
+           int(threads or (os.cpu_count() or 1)))
+    if rc != 0:
+        raise ValueError("decoder oracle refused the call")
+    state.used += l
+    return y
+
+
+def embedding(table, ids):
+    table = _f32(table)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    out = np.empty(ids.shape + (table.shape[1],), np.float32)
+    f = lib().dec_embedding
+    f.restype = ctypes.c_int
+    f.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int64] * 3
+    if f(_ptr(out), _ptr(table), _ptr(ids), ids.size, table.shape[0], table.shape[1]) != 0:
+        raise ValueError("token id outside the embedding table")
+    return out
+
+
+def add_positions(x, pos_table, pos0):
+    x = np.array(_f32(x), copy=True)
+    b, l, width = x.shape
+    f = lib().dec_add_positions
+    f.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int64] * 4
+    f(_ptr(x), _ptr(_f32(pos_table)), b, l, pos0, width)
+    return x
+
+
+def argmax(logits):
+    logits = _f32(logits)
+    rows, vocab = int(np.prod(logits.shape[:-1])), logits.shape[-1]
+    out = np.empty(logits.shape[:-1], np.int32)
+    f = lib().dec_argmax
+    f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64]
+    f(_ptr(out), _ptr(logits), rows, vocab)
+    return out
