@@ -125,6 +125,52 @@ int64_t b200i_host_dequantize_int8(int64_t device, float *y, const int8_t *codes
 int64_t b200i_host_gemm_int8(int64_t device, float *c, const int8_t *qa, const int32_t *ea, const int8_t *qb,
                              const int32_t *eb, int64_t m, int64_t n, int64_t k, char *err, int64_t err_cap);
 
+/* --- decoder-block seams, device pointers, asynchronous on the caller's stream -------------------
+ * The non-GEMM steps of the reference's decoder block, each spelled as the
+ * reference pins it (transformer/IDENTICAL_TRANSFORMER_CONTRACT.md:207-240; host
+ * oracle transformer/checks/transformer_oracle.mojo). They replace the device
+ * block's stages behind transformer_forward / transformer_decode_step
+ * (bindings/_mojolearn_transformer.mojo:1209-1230) and the primitive doors
+ * embedding_forward / rms_norm_forward (bindings/_mojolearn_training.mojo:575-587, :607-619). */
+
+/* kind 0 = RMSNorm (S1-S4), 1 = LayerNorm (bias optional), 2 = RMSNorm with weight 1 + w.
+ * out and x are [rows, width]; transformer_oracle.mojo:1223-1341. */
+int64_t b200i_norm(int64_t device, void *stream, float *out, const float *x, const float *w, const float *bias, int64_t rows,
+                   int64_t width, double eps, int64_t kind, char *err, int64_t err_cap);
+/* cos and sin [l, head_dim/2] for absolute positions pos0 .. pos0+l-1 (S6-S8); positions stay below 8192. */
+int64_t b200i_rope_table(int64_t device, void *stream, float *cosv, float *sinv, int64_t pos0, int64_t l, int64_t head_dim,
+                         double theta, char *err, int64_t err_cap);
+/* out[rows, n_heads*head_dim] = rotate(src) with the table of the call's l positions (S9-S10); not in place. */
+int64_t b200i_rope_apply(int64_t device, void *stream, float *out, const float *src, const float *cosv, const float *sinv,
+                         int64_t rows, int64_t l, int64_t n_heads, int64_t head_dim, char *err, int64_t err_cap);
+/* cache[b, n_kv, cap, head_dim] <- src[b*l, n_kv*head_dim] at positions pos0 .. pos0+l-1 (a copy). */
+int64_t b200i_kv_append(int64_t device, void *stream, float *cache, const float *src, int64_t b, int64_t l, int64_t n_kv,
+                        int64_t head_dim, int64_t cap, int64_t pos0, char *err, int64_t err_cap);
+/* ctx[b*l, n_heads*head_dim] from rotated queries q[b*l, n_heads*head_dim] and caches holding `used`
+ * positions, this call's l included (S11-S19: eager attention, serial key-axis chains). `scores` is
+ * scratch of b*n_heads*l*min(used, window or used) floats. head_dim <= 128. */
+int64_t b200i_attention(int64_t device, void *stream, float *ctx, const float *q, const float *kcache, const float *vcache,
+                        float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
+                        int64_t used, int64_t window, char *err, int64_t err_cap);
+/* kind 0 = silu(gate)*up, 1 = gelu_erf(up), 2 = gelu_tanh(up), 3 = silu(up), 4 / 5 = gelu(gate)*up (S20-S21). */
+int64_t b200i_act_mul(int64_t device, void *stream, float *out, const float *gate, const float *up, int64_t count, int64_t kind,
+                      char *err, int64_t err_cap);
+/* out = ftz(ftz(a) + ftz(b)) (S22, S23); may be in place. */
+int64_t b200i_add(int64_t device, void *stream, float *out, const float *a, const float *b, int64_t count, char *err, int64_t err_cap);
+/* buf[rows, width] += bias[width], one plain add per cell (transformer_oracle.mojo:1344-1372). */
+int64_t b200i_bias_add(int64_t device, void *stream, float *buf, const float *bias, int64_t rows, int64_t width, char *err,
+                       int64_t err_cap);
+/* y[n, width] = ftz(table[ids[n]]); status[0] becomes 1 if an id is outside [0, vocab)
+ * (embedding/checks/embedding_oracle.mojo:369-382). */
+int64_t b200i_embedding(int64_t device, void *stream, float *y, const float *table, const int32_t *ids, int64_t n, int64_t vocab,
+                        int64_t width, int32_t *status, char *err, int64_t err_cap);
+/* x[rows, width] += pos[pos0 + row % l] (learned positions; an extension, the reference's block always rotates). */
+int64_t b200i_add_positions(int64_t device, void *stream, float *x, const float *pos, int64_t rows, int64_t l, int64_t pos0,
+                            int64_t width, char *err, int64_t err_cap);
+/* out[rows] = index of the largest logit, ties to the lowest id (python/mojolearn/models/causal_lm.py:190). */
+int64_t b200i_argmax(int64_t device, void *stream, int32_t *out, const float *logits, int64_t rows, int64_t vocab, char *err,
+                     int64_t err_cap);
+
 /* Status word of the decode plan's bounded waits on `device` (synchronises the
  * device): 0 = no wait ever ran out; 1 / 2 = the producer / a consumer gave up
  * waiting on a stage; -1 = the word could not be read. A nonzero word is cleared

@@ -32,7 +32,7 @@ def lib():
     return _lib
 
 
-I64, VP, CP = ctypes.c_int64, ctypes.c_void_p, ctypes.c_char_p
+I64, VP, CP, F64 = ctypes.c_int64, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_double
 
 #: name -> argument types, as declared in include/b200i.h (all return int64 unless noted)
 SIGNATURES = {
@@ -59,6 +59,17 @@ SIGNATURES = {
     "b200i_host_dequantize_int8": [I64, VP, VP, VP, I64, I64, VP, I64],
     "b200i_host_gemm_int8": [I64, VP, VP, VP, VP, VP, I64, I64, I64, VP, I64],
     "b200i_decode_status": [I64],
+    "b200i_norm": [I64, VP, VP, VP, VP, VP, I64, I64, F64, I64, VP, I64],
+    "b200i_rope_table": [I64, VP, VP, VP, I64, I64, I64, F64, VP, I64],
+    "b200i_rope_apply": [I64, VP, VP, VP, VP, VP, I64, I64, I64, I64, VP, I64],
+    "b200i_kv_append": [I64, VP, VP, VP, I64, I64, I64, I64, I64, I64, VP, I64],
+    "b200i_attention": [I64, VP, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, I64, I64, I64, VP, I64],
+    "b200i_act_mul": [I64, VP, VP, VP, VP, I64, I64, VP, I64],
+    "b200i_add": [I64, VP, VP, VP, VP, I64, VP, I64],
+    "b200i_bias_add": [I64, VP, VP, VP, I64, I64, VP, I64],
+    "b200i_embedding": [I64, VP, VP, VP, VP, I64, I64, I64, VP, VP, I64],
+    "b200i_add_positions": [I64, VP, VP, VP, I64, I64, I64, I64, VP, I64],
+    "b200i_argmax": [I64, VP, VP, VP, I64, I64, VP, I64],
     "b200i_ffma_probe": [I64, VP, VP, I64, I64, I64, VP, I64],
 }
 STRING_FUNCTIONS = ["b200i_numerical_profile", "b200i_vendor"]

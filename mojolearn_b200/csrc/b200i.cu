@@ -8,6 +8,7 @@
 
 #include "../../include/b200i.h"
 #include "decode.cuh"
+#include "decoder.cuh"
 #include "gemm_tile.cuh"
 #include "lowbit.cuh"
 
@@ -255,6 +256,14 @@ size_t wkind_elem_bytes(int wkind) { return wkind == W_F32 ? 4 : (wkind == W_BF1
 
 } // namespace
 
+static unsigned grid_for(long long work_items, int block, int sms) {
+    long long blocks = (work_items + block - 1) / block;
+    const long long cap = (long long)sms * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (unsigned)blocks;
+}
+
 extern "C" {
 
 int64_t b200i_abi(void) { return 1; }
@@ -310,13 +319,6 @@ int64_t b200i_gemm_f32(int64_t device, void *stream, float *c, const float *a, c
     return b200i_gemm_w_plan(device, stream, c, a, b, nullptr, W_F32, m, n, k, op, PLAN_AUTO, 0, ws, ws_bytes, err, err_cap);
 }
 
-static unsigned grid_for(long long work_items, int block, int sms) {
-    long long blocks = (work_items + block - 1) / block;
-    const long long cap = (long long)sms * 16;
-    if (blocks > cap) blocks = cap;
-    if (blocks < 1) blocks = 1;
-    return (unsigned)blocks;
-}
 
 int64_t b200i_to_bf16(int64_t device, void *stream, uint16_t *dst, const float *src, int64_t count, char *err,
                       int64_t err_cap) {
@@ -395,6 +397,154 @@ int64_t b200i_ffma_probe(int64_t device, void *stream, float *scratch, int64_t b
     int dev;
     if (select_device(device, err, err_cap, &dev)) return 1;
     ffma_probe_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(scratch, (int)iters, (int)packed, 1.0f);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+// ---- decoder-block seams (device pointers, asynchronous on the caller's stream) ----------------
+
+#define SEAM_PROLOGUE()                                          \
+    clear(err, err_cap);                                         \
+    int dev;                                                     \
+    if (select_device(device, err, err_cap, &dev)) return 1;     \
+    cudaStream_t st = static_cast<cudaStream_t>(stream)
+
+int64_t b200i_norm(int64_t device, void *stream, float *out, const float *x, const float *w, const float *bias, int64_t rows,
+                   int64_t width, double eps, int64_t kind, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (rows <= 0 || width <= 0 || !out || !x || !w) return fail(err, err_cap, "norm: bad arguments");
+    if (kind < NORM_RMS || kind > NORM_RMS_OFFSET) return fail(err, err_cap, "norm: norm kind %lld is not spelled", (long long)kind);
+    if (bias && kind != NORM_LAYER) return fail(err, err_cap, "norm: an RMSNorm carries no bias (norm_bias needs layernorm)");
+    const long long threads = rows * 32;
+    norm_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(out, x, w, bias, rows, (int)width, (float)eps, (int)kind);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_rope_table(int64_t device, void *stream, float *cosv, float *sinv, int64_t pos0, int64_t l, int64_t head_dim,
+                         double theta, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (l <= 0 || head_dim <= 0 || (head_dim & 1) || !cosv || !sinv) return fail(err, err_cap, "rope_table: bad arguments");
+    if (pos0 < 0 || pos0 + l > 8192)
+        return fail(err, err_cap, "rope_table: absolute position %lld is at or beyond 8192, the domain of the sine and cosine reduction",
+                    (long long)(pos0 + l - 1));
+    const long long n = l * (head_dim / 2);
+    rope_table_kernel<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(cosv, sinv, (int)pos0, (int)l, (int)head_dim, (float)theta);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_rope_apply(int64_t device, void *stream, float *out, const float *src, const float *cosv, const float *sinv,
+                         int64_t rows, int64_t l, int64_t n_heads, int64_t head_dim, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (rows <= 0 || l <= 0 || n_heads <= 0 || head_dim <= 0 || (head_dim & 1) || !out || !src || out == src)
+        return fail(err, err_cap, "rope_apply: bad arguments (the rotation is not in place)");
+    const long long n = rows * n_heads * head_dim;
+    rope_apply_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(out, src, cosv, sinv, rows, (int)l, (int)n_heads, (int)head_dim);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_kv_append(int64_t device, void *stream, float *cache, const float *src, int64_t b, int64_t l, int64_t n_kv,
+                        int64_t head_dim, int64_t cap, int64_t pos0, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (b <= 0 || l <= 0 || n_kv <= 0 || head_dim <= 0 || pos0 < 0 || !cache || !src) return fail(err, err_cap, "kv_append: bad arguments");
+    if (pos0 + l > cap)
+        return fail(err, err_cap, "transformer: this call would use %lld KV slots and the cache holds %lld REFUSED", (long long)(pos0 + l),
+                    (long long)cap);
+    const long long n = b * l * n_kv * head_dim;
+    kv_append_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(cache, src, (int)b, (int)l, (int)n_kv, (int)head_dim, (int)cap, (int)pos0);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_attention(int64_t device, void *stream, float *ctx, const float *q, const float *kcache, const float *vcache,
+                        float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
+                        int64_t used, int64_t window, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (b <= 0 || l <= 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || head_dim <= 0 || !ctx || !q || !kcache || !vcache || !scores)
+        return fail(err, err_cap, "attention: bad arguments");
+    if (head_dim > K_LEAF_MIN || head_dim > CTX_MAX_HD)
+        return fail(err, err_cap, "attention: head_dim %lld above 128 needs the leaf partition of the product, which this kernel does not spell",
+                    (long long)head_dim);
+    if (used < l || used > cap) return fail(err, err_cap, "attention: the cache holds %lld positions, this call's %lld included", (long long)used, (long long)l);
+    if (b * n_heads > 65535) return fail(err, err_cap, "attention: batch x heads above 65535");
+    const int64_t pos0 = used - l;
+    int64_t key_lo = 0;
+    if (window > 0 && pos0 - (window - 1) > 0) key_lo = pos0 - (window - 1);
+    const int s = (int)(used - key_lo), own0 = (int)(pos0 - key_lo);
+    dim3 g1((unsigned)((s + ATT_T - 1) / ATT_T), (unsigned)((l + ATT_T - 1) / ATT_T), (unsigned)(b * n_heads));
+    attn_scores_kernel<<<g1, 256, 0, st>>>(scores, q, kcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, (int)key_lo, s,
+                                             own0, (int)window);
+    dim3 g2((unsigned)((l + CTX_ROWS - 1) / CTX_ROWS), (unsigned)(b * n_heads));
+    attn_context_kernel<<<g2, 32 * CTX_ROWS, (size_t)CTX_KT * head_dim * sizeof(float), st>>>(
+        ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, (int)key_lo, s, own0, (int)window);
+    g_launches += 2;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_act_mul(int64_t device, void *stream, float *out, const float *gate, const float *up, int64_t count, int64_t kind,
+                      char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (count <= 0 || !out || !up || kind < ACT_SWIGLU || kind > ACT_GEGLU_TANH) return fail(err, err_cap, "act_mul: bad arguments");
+    const bool gated = kind == ACT_SWIGLU || kind == ACT_GEGLU_ERF || kind == ACT_GEGLU_TANH;
+    if (gated && !gate) return fail(err, err_cap, "act_mul: a gated MLP needs its gate projection");
+    act_mul_kernel<<<grid_for(count, 256, sm_count(dev)), 256, 0, st>>>(out, gate, up, count, (int)kind);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_add(int64_t device, void *stream, float *out, const float *a, const float *b, int64_t count, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (count <= 0 || !out || !a || !b) return fail(err, err_cap, "add: bad arguments");
+    add_kernel<<<grid_for(count, 256, sm_count(dev)), 256, 0, st>>>(out, a, b, count);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_bias_add(int64_t device, void *stream, float *buf, const float *bias, int64_t rows, int64_t width, char *err,
+                       int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (rows <= 0 || width <= 0 || !buf || !bias) return fail(err, err_cap, "bias_add: bad arguments");
+    bias_add_kernel<<<grid_for(rows * width, 256, sm_count(dev)), 256, 0, st>>>(buf, bias, rows, (int)width);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_embedding(int64_t device, void *stream, float *y, const float *table, const int32_t *ids, int64_t n, int64_t vocab,
+                        int64_t width, int32_t *status, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (n <= 0 || vocab <= 0 || width <= 0 || !y || !table || !ids || !status) return fail(err, err_cap, "embedding: bad arguments");
+    embedding_kernel<<<grid_for(n * width, 256, sm_count(dev)), 256, 0, st>>>(y, table, ids, n, (int)vocab, (int)width, status);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_add_positions(int64_t device, void *stream, float *x, const float *pos, int64_t rows, int64_t l, int64_t pos0,
+                            int64_t width, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (rows <= 0 || l <= 0 || width <= 0 || pos0 < 0 || !x || !pos) return fail(err, err_cap, "add_positions: bad arguments");
+    add_positions_kernel<<<grid_for(rows * width, 256, sm_count(dev)), 256, 0, st>>>(x, pos, rows, (int)l, (int)pos0, (int)width);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_argmax(int64_t device, void *stream, int32_t *out, const float *logits, int64_t rows, int64_t vocab, char *err,
+                     int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (rows <= 0 || vocab <= 0 || !out || !logits) return fail(err, err_cap, "argmax: bad arguments");
+    argmax_kernel<<<(unsigned)rows, 256, 0, st>>>(out, logits, (int)vocab);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;

@@ -1,0 +1,339 @@
+// The decoder-block seams around the matrix product, as CUDA kernels.
+//
+// Each kernel spells exactly the reference's pinned seam (paths relative to the
+// reference project's root; seam numbers from
+// transformer/IDENTICAL_TRANSFORMER_CONTRACT.md:207-240):
+//   norm_kernel          S1-S4 and the LayerNorm / offset variants, transformer/checks/transformer_oracle.mojo:1223-1341
+//   rope_table_kernel    S6-S8, transformer/checks/transformer_oracle.mojo:539-640
+//   rope_apply_kernel    S9-S10 (halves pairing, three roundings), :1375-1500
+//   attn_scores_kernel   S11 (gemm fp32.v1 cells, k = head_dim, one leaf), S12 scale, S13 mask ADD, :2230-2372
+//   attn_context_kernel  S14 row max (order free), S15-S16 exp, S17 serial denominator, S18 one division per
+//                        weight, S19 serial value sum (NOT a GEMM), :2373-2472 and core/host_lanes.mojo:271-330
+//   act_mul_kernel       S20-S21 and the GELU variants, :2580-2620
+//   add_kernel           S22 / S23 residuals; bias_add_kernel :1344-1372
+//   embedding_kernel     Y = ftz(W[id]), embedding/checks/embedding_oracle.mojo:369-382
+//   argmax_kernel        greedy, ties to the lowest id, python/mojolearn/models/causal_lm.py:190
+// Serial chains stay serial: the order of a chain is the contract, so the
+// parallelism is across rows, heads and feature lanes, never inside a chain.
+// These kernels are HBM- or latency-bound byte work around the GEMMs: coalesced
+// 128-byte row segments, one warp per row or one thread per element, grids sized
+// from the row count.
+#pragma once
+#include "seams_math.cuh"
+
+namespace b200i {
+
+constexpr int NORM_RMS = 0, NORM_LAYER = 1, NORM_RMS_OFFSET = 2;
+constexpr int ACT_SWIGLU = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_GEGLU_ERF = 4, ACT_GEGLU_TANH = 5;
+
+// ---- normalisation: one warp per row -------------------------------------------------------
+// The sum of squares (or of deviations) is ONE serial chain over the row. Every
+// lane runs the same chain on values broadcast by shuffle, so the loads are
+// coalesced and the chain costs one dependent fma per element.
+__global__ void norm_kernel(float *__restrict__ out, const float *__restrict__ src, const float *__restrict__ w,
+                            const float *__restrict__ bias, long long rows, int dm, float eps, int kind) {
+    const int lane = threadIdx.x & 31;
+    const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (row >= rows) return;
+    const float *x = src + row * dm;
+    float mean = 0.f;
+    if (kind == NORM_LAYER) {
+        float acc = 0.f;
+        for (int j0 = 0; j0 < dm; j0 += 32) {
+            const float mine = (j0 + lane < dm) ? ftz_bits(x[j0 + lane]) : 0.f;
+            const int cnt = min(32, dm - j0);
+            for (int j = 0; j < cnt; j++) acc = ftz_hw(__fadd_rn(acc, __shfl_sync(0xFFFFFFFFu, mine, j)));
+        }
+        mean = ftz_bits(p_divf(acc, (float)dm));
+    }
+    float acc = 0.f;
+    for (int j0 = 0; j0 < dm; j0 += 32) {
+        float mine = (j0 + lane < dm) ? ftz_bits(x[j0 + lane]) : 0.f;
+        if (kind == NORM_LAYER) mine = ftz_bits(__fsub_rn(mine, mean));
+        const int cnt = min(32, dm - j0);
+        for (int j = 0; j < cnt; j++) {
+            const float v = __shfl_sync(0xFFFFFFFFu, mine, j);
+            acc = step_flush(v, v, acc);
+        }
+    }
+    const float var = ftz_bits(p_divf(acc, (float)dm));
+    const float rstd = ftz_bits(p_rsqrtf(ftz_bits(__fadd_rn(var, eps))));
+    for (int j = lane; j < dm; j += 32) {
+        float v = ftz_bits(x[j]);
+        if (kind == NORM_LAYER) v = ftz_bits(__fsub_rn(v, mean));
+        const float inner = ftz_bits(__fmul_rn(v, rstd));
+        float wj = ftz_bits(w[j]);
+        if (kind == NORM_RMS_OFFSET) wj = ftz_bits(__fadd_rn(1.0f, wj));
+        float y = ftz_bits(__fmul_rn(wj, inner));
+        if (kind == NORM_LAYER && bias) y = ftz_bits(__fadd_rn(y, ftz_bits(bias[j])));
+        out[row * dm + j] = y;
+    }
+}
+
+// ---- rotary table and application -----------------------------------------------------------
+__global__ void rope_table_kernel(float *__restrict__ cosv, float *__restrict__ sinv, int pos0, int l, int head_dim,
+                                  float theta) {
+    const int half = head_dim / 2;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= l * half) return;
+    const int p = idx / half, i = idx % half;
+    const float e = ftz_bits(p_divf((float)(2 * i), (float)head_dim));
+    const float inv = ftz_bits(p_divf(1.0f, p_powf(theta, e)));
+    const float angle = ftz_bits(__fmul_rn((float)(pos0 + p), ftz_bits(inv)));
+    cosv[idx] = ftz_bits(p_cosf(angle));
+    sinv[idx] = ftz_bits(p_sinf(angle));
+}
+
+__global__ void rope_apply_kernel(float *__restrict__ out, const float *__restrict__ src, const float *__restrict__ cosv,
+                                  const float *__restrict__ sinv, long long m, int l, int n_head, int hd) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long width = (long long)n_head * hd;
+    if (idx >= m * width) return;
+    const long long t = idx / width;
+    const int j = (int)(idx % hd), half = hd / 2, li = (int)(t % l);
+    const int ci = j < half ? j : j - half;
+    const float partner = j < half ? -ftz_bits(src[idx + half]) : ftz_bits(src[idx - half]);
+    const float c = ftz_bits(cosv[li * half + ci]), s = ftz_bits(sinv[li * half + ci]);
+    const float pa = ftz_bits(__fmul_rn(ftz_bits(src[idx]), c));
+    const float pb = ftz_bits(__fmul_rn(partner, s));
+    out[idx] = ftz_bits(__fadd_rn(pa, pb));
+}
+
+// KV cache append: a copy, not a seam. cache is [b, n_kv, cap, hd]; src is [b*l, n_kv*hd].
+__global__ void kv_append_kernel(float *__restrict__ cache, const float *__restrict__ src, int b, int l, int n_kv, int hd,
+                                 int cap, int pos0) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)b * l * n_kv * hd;
+    if (idx >= total) return;
+    const int d = (int)(idx % hd);
+    const int kv = (int)((idx / hd) % n_kv);
+    const long long t = idx / ((long long)hd * n_kv);
+    const int bb = (int)(t / l), li = (int)(t % l);
+    cache[(((long long)bb * n_kv + kv) * cap + pos0 + li) * hd + d] = src[idx];
+}
+
+// ---- attention scores -------------------------------------------------------------------------
+// scores[b, h, qi, j] = ftz(ftz(ftz(q . k) * scale) + fill), the dot being one
+// gemm fp32.v1 leaf (k = head_dim <= 128: a single serial chain from +0.0).
+// A CTA owns a 64 x 64 tile of one (batch, head); a thread owns 4 x 4 cells.
+constexpr int ATT_T = 64, ATT_KC = 32;
+__global__ void __launch_bounds__(256) attn_scores_kernel(float *__restrict__ scores, const float *__restrict__ q,
+                                                          const float *__restrict__ kcache, int b, int l, int nh, int nkv, int hd,
+                                                          int cap, int key_lo, int s, int own0, int window) {
+    // the attention scale, ftz(rsqrt(head_dim)) in the portable spelling: a pure function of head_dim
+    const float scale = ftz_bits(p_rsqrtf((float)hd));
+    __shared__ float qs[ATT_KC][ATT_T + 1];
+    __shared__ float ks[ATT_KC][ATT_T + 1];
+    const int bh = blockIdx.z, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
+    const int q0 = blockIdx.y * ATT_T, j0 = blockIdx.x * ATT_T;
+    const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+    const long long qw = (long long)nh * hd;
+    const float *qbase = q + ((long long)bb * l) * qw + (long long)h * hd;
+    const float *kbase = kcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    for (int p0 = 0; p0 < hd; p0 += ATT_KC) {
+        for (int idx = tid; idx < ATT_T * ATT_KC; idx += 256) {
+            const int r = idx / ATT_KC, p = idx % ATT_KC;
+            const bool pk = p0 + p < hd;
+            qs[p][r] = (pk && q0 + r < l) ? ftz_bits(qbase[(long long)(q0 + r) * qw + p0 + p]) : 0.f;
+            ks[p][r] = (pk && j0 + r < s) ? ftz_bits(kbase[(long long)(j0 + r) * hd + p0 + p]) : 0.f;
+        }
+        __syncthreads();
+        const int pn = min(ATT_KC, hd - p0);
+        for (int p = 0; p < pn; p++) {
+            float a[4], c[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { a[i] = qs[p][ty * 4 + i]; c[i] = ks[p][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = step_flush(a[i], c[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    const float mfill = __uint_as_float(0xFF7FFFFFu);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int qi = q0 + ty * 4 + i;
+        if (qi >= l) continue;
+        int jlo = 0, jhi = own0 + qi;
+        if (jhi > s - 1) jhi = s - 1;
+        if (window > 0) { jlo = own0 + qi - window + 1; if (jlo < 0) jlo = 0; }
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) {
+            const int j = j0 + tx * 4 + jj;
+            if (j >= s) continue;
+            const float sc = ftz_bits(__fmul_rn(ftz_hw(acc[i][jj]), scale));
+            const float fill = (j < jlo || j > jhi) ? mfill : 0.0f;
+            scores[((long long)bh * l + qi) * s + j] = ftz_bits(__fadd_rn(sc, fill));
+        }
+    }
+}
+
+// ---- softmax and value sum ----------------------------------------------------------------------
+// One warp per query row; the eight rows of a CTA share one (batch, head) and the
+// value tiles staged in shared memory. The masked scores are overwritten in place
+// by exp(s - max) and then by the weights.
+constexpr int CTX_ROWS = 8, CTX_KT = 32, CTX_MAX_HD = 256;
+__global__ void __launch_bounds__(32 * CTX_ROWS) attn_context_kernel(float *__restrict__ ctx, float *__restrict__ scores,
+                                                                      const float *__restrict__ vcache, int b, int l, int nh,
+                                                                      int nkv, int hd, int cap, int key_lo, int s, int own0,
+                                                                      int window) {
+    extern __shared__ float vtile[]; // [CTX_KT][hd]
+    const int bh = blockIdx.y, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qi = blockIdx.x * CTX_ROWS + warp;
+    const bool active = qi < l;
+    float *row = scores + ((long long)bh * l + (active ? qi : 0)) * s;
+    int jlo = 0, jhi = own0 + qi;
+    if (jhi > s - 1) jhi = s - 1;
+    if (window > 0) { jlo = own0 + qi - window + 1; if (jlo < 0) jlo = 0; }
+    float den = 0.f;
+    if (active) {
+        // S14: the row maximum over the WHOLE row, as a total-order key (fold shape is free)
+        unsigned best = 0u;
+        for (int j = lane; j < s; j += 32) best = max(best, order_key(ftz_bits(row[j])));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, off));
+        const float fm = ftz_bits(order_unkey(best));
+        // S15, S16 in parallel; S17 serial ascending over the visible keys
+        for (int j0 = jlo; j0 <= jhi; j0 += 32) {
+            const int j = j0 + lane;
+            float e = 0.f;
+            if (j <= jhi) {
+                e = ftz_bits(p_expf(ftz_bits(__fsub_rn(ftz_bits(row[j]), fm))));
+                row[j] = e;
+            }
+            const int cnt = min(32, jhi - j0 + 1);
+            for (int t = 0; t < cnt; t++) den = ftz_hw(__fadd_rn(den, __shfl_sync(0xFFFFFFFFu, e, t)));
+        }
+    }
+    // S18 + S19 over value tiles shared by the CTA's rows
+    constexpr int DPL = CTX_MAX_HD / 32;
+    float acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; i++) acc[i] = 0.f;
+    const float *vbase = vcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
+    // keys any row of this CTA can see
+    const int q_first = blockIdx.x * CTX_ROWS, q_last = min(l - 1, q_first + CTX_ROWS - 1);
+    int t_lo = 0, t_hi = min(s - 1, own0 + q_last);
+    if (window > 0) { t_lo = own0 + q_first - window + 1; if (t_lo < 0) t_lo = 0; }
+    for (int j0 = (t_lo / CTX_KT) * CTX_KT; j0 <= t_hi; j0 += CTX_KT) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < CTX_KT * hd; idx += 32 * CTX_ROWS) {
+            const int jj = idx / hd;
+            vtile[idx] = (j0 + jj < s) ? ftz_bits(vbase[(long long)(j0 + jj) * hd + idx % hd]) : 0.f;
+        }
+        __syncthreads();
+        if (!active) continue;
+        const int j = j0 + lane;
+        float wgt = 0.f;
+        if (j >= jlo && j <= jhi) {
+            wgt = ftz_bits(p_divf(ftz_bits(row[j]), den));
+            row[j] = wgt;
+        }
+        const int a = max(jlo, j0), z = min(jhi, j0 + CTX_KT - 1);
+        for (int jk = a; jk <= z; jk++) {
+            const float wv = __shfl_sync(0xFFFFFFFFu, wgt, jk - j0);
+#pragma unroll
+            for (int i = 0; i < DPL; i++) {
+                const int d = lane + 32 * i;
+                if (d < hd) acc[i] = step_flush(wv, vtile[(jk - j0) * hd + d], acc[i]);
+            }
+        }
+    }
+    if (active) {
+        float *o = ctx + ((long long)bb * l + qi) * ((long long)nh * hd) + (long long)h * hd;
+#pragma unroll
+        for (int i = 0; i < DPL; i++) {
+            const int d = lane + 32 * i;
+            if (d < hd) o[d] = acc[i];
+        }
+    }
+}
+
+// ---- elementwise seams --------------------------------------------------------------------------
+__global__ void act_mul_kernel(float *__restrict__ out, const float *__restrict__ gate, const float *__restrict__ up,
+                               long long count, int kind) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const bool gated = kind == ACT_SWIGLU || kind == ACT_GEGLU_ERF || kind == ACT_GEGLU_TANH;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        const float z = ftz_bits(gated ? gate[i] : up[i]);
+        float a;
+        if (kind == ACT_SWIGLU || kind == ACT_SILU) a = ftz_bits(p_siluf(z));
+        else if (kind == ACT_GELU_TANH || kind == ACT_GEGLU_TANH) a = ftz_bits(p_gelu_tanh(z));
+        else a = ftz_bits(p_gelu_erf(z));
+        out[i] = gated ? ftz_bits(__fmul_rn(a, ftz_bits(up[i]))) : a;
+    }
+}
+
+__global__ void add_kernel(float *__restrict__ out, const float *__restrict__ a, const float *__restrict__ b, long long count) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
+        out[i] = ftz_bits(__fadd_rn(ftz_bits(a[i]), ftz_bits(b[i])));
+}
+
+__global__ void bias_add_kernel(float *__restrict__ buf, const float *__restrict__ bias, long long rows, int width) {
+    const long long stride = (long long)gridDim.x * blockDim.x, total = rows * width;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
+        buf[i] = ftz_bits(__fadd_rn(ftz_bits(buf[i]), ftz_bits(bias[i % width])));
+}
+
+// status[0] is set to 1 when a token id falls outside the table (the row is then zero filled)
+__global__ void embedding_kernel(float *__restrict__ y, const float *__restrict__ table, const int *__restrict__ ids,
+                                 long long n, int vocab, int width, int *__restrict__ status) {
+    const long long stride = (long long)gridDim.x * blockDim.x, total = n * width;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long t = i / width;
+        const int id = ids[t];
+        if (id < 0 || id >= vocab) {
+            y[i] = 0.f;
+            if (i % width == 0) atomicExch(status, 1);
+        } else {
+            y[i] = ftz_bits(table[(long long)id * width + i % width]);
+        }
+    }
+}
+
+// learned positions (an extension: the reference's block always rotates): one plain add
+__global__ void add_positions_kernel(float *__restrict__ x, const float *__restrict__ pos, long long rows, int l, int pos0,
+                                     int width) {
+    const long long stride = (long long)gridDim.x * blockDim.x, total = rows * width;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long t = i / width;
+        x[i] = ftz_bits(__fadd_rn(ftz_bits(x[i]), ftz_bits(pos[(long long)(pos0 + t % l) * width + i % width])));
+    }
+}
+
+// greedy argmax, one CTA per row: strictly greater wins, equal keeps the lower index
+__global__ void argmax_kernel(int *__restrict__ out, const float *__restrict__ logits, int vocab) {
+    __shared__ float bv[256];
+    __shared__ int bi[256];
+    const float *p = logits + (long long)blockIdx.x * vocab;
+    float best = 0.f;
+    int idx = -1;
+    for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
+        const float v = p[j];
+        if (v == v && (idx < 0 || v > best)) { best = v; idx = j; } // a NaN is never a candidate, as in the scalar walk
+    }
+    bv[threadIdx.x] = best;
+    bi[threadIdx.x] = idx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // the scalar walk visits indices ascending and replaces on strictly greater;
+        // replay it over each thread's candidate in index order of first occurrence
+        float b0 = p[0];
+        int i0 = 0;
+        for (int t = 0; t < (int)blockDim.x; t++) {
+            if (bi[t] < 0) continue;
+            if (bv[t] > b0 || (bv[t] == b0 && bi[t] < i0)) { b0 = bv[t]; i0 = bi[t]; }
+        }
+        out[blockIdx.x] = i0;
+    }
+}
+
+} // namespace b200i

@@ -1,0 +1,221 @@
+"""`CausalLM`: embedding -> decoder blocks -> final norm -> lm_head, with prefill,
+single-step decoding and greedy generation, device resident.
+
+Mirrors python/mojolearn/models/causal_lm.py of the reference (:121-209:
+`forward(ids, state)`, `step`, `allocate_state`, `generate(ids, max_new_tokens,
+greedy=True)`; ids are `(batch, length)` int32, logits `(B, L, V)` float32;
+greedy ties go to the lowest id, :190). The three non-block steps are the
+reference's primitives: embedding gather `Y = ftz(W[id])`, the final norm, and
+the head as a `gemm.fp32.v1` OP_NT product (bindings/_mojolearn_training.mojo
+:575-587, :607-619, :683-696).
+
+Weights use HuggingFace names (`model.embed_tokens.weight`,
+`model.layers.N.self_attn.q_proj.weight`, ..., `model.norm.weight`,
+`lm_head.weight`); 2-D projection weights may be `lowbit`-packed.
+
+Extensions the reference does not have: learned absolute positions with
+`positions="learned"` (`model.embed_positions.weight`, one plain add, rotary
+off), a LayerNorm final norm, and output-column sharding across one process per
+GPU: with a `torch.distributed` group every projection and the head keep only
+their rows [r*N/g, (r+1)*N/g) and the full activation is rebuilt by an NCCL
+all-gather. A cell reads one weight row and all of k, so the shard moves no bit:
+the logits equal the single-GPU logits word for word.
+"""
+import ctypes
+
+import numpy as np
+import torch
+
+from .. import _native
+from ..parallel import gather_columns, shard_bounds
+from ..transformer import Linear, TransformerBlock, TransformerState, _stream, _vp, add, norm, NORM_KINDS
+
+
+class CausalLMConfig(object):
+    def __init__(self, vocab, d_model, n_layers, n_heads, n_kv_heads=None, head_dim=None, intermediate=None, norm="rmsnorm",
+                 norm_eps=1e-6, norm_bias=False, mlp="swiglu", mlp_bias=False, qkv_bias=False, o_bias=False,
+                 positions="rope", rope_theta=10000.0, max_positions=8192, window=0):
+        self.vocab, self.d_model, self.n_layers, self.n_heads = vocab, d_model, n_layers, n_heads
+        self.n_kv_heads = n_kv_heads or n_heads
+        self.head_dim = head_dim or d_model // n_heads
+        self.intermediate = intermediate or 4 * d_model
+        self.norm, self.norm_eps, self.norm_bias = norm, norm_eps, norm_bias
+        self.mlp, self.mlp_bias, self.qkv_bias, self.o_bias = mlp, mlp_bias, qkv_bias, o_bias
+        if positions not in ("rope", "learned"):
+            raise ValueError("positions must be 'rope' or 'learned'")
+        self.positions, self.rope_theta, self.max_positions, self.window = positions, rope_theta, max_positions, window
+
+
+class CausalLMState(object):
+    """One block state per layer, the batch size, the capacity and the tokens consumed."""
+
+    def __init__(self, layers, batch_size, max_tokens):
+        self.layers, self.batch_size, self.max_tokens = layers, batch_size, max_tokens
+
+    @property
+    def positions(self):
+        return self.layers[0].cached_tokens if self.layers else 0
+
+
+class _ShardedLinear(object):
+    """Rows [r*N/g, (r+1)*N/g) of a layer on this rank; the call all-gathers the output columns."""
+
+    def __init__(self, full, group, rank, world):
+        n = full.out_features
+        lo, hi = shard_bounds(n, rank, world)
+        self.local = full.shard_rows(lo, hi)
+        self.group, self.world, self.out_features, self.in_features = group, world, n, full.in_features
+
+    def __call__(self, x2d):
+        return gather_columns(self.local(x2d), self.group)  # pure data movement: no arithmetic order is introduced
+
+
+class CausalLM(object):
+    def __init__(self, config, weights, *, device=None, group=None):
+        _native.require_device()
+        self.config = cfg = config
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.group, self.rank, self.world = group, 0, 1
+        if group is not None:
+            import torch.distributed as dist
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+
+        def get(name):
+            for key in (name, "model." + name):
+                if key in weights:
+                    return weights[key]
+            raise ValueError("weights lack %r" % name)
+
+        emb = np.ascontiguousarray(np.asarray(get("embed_tokens.weight"), dtype=np.float32))
+        if emb.shape != (cfg.vocab, cfg.d_model):
+            raise ValueError("embed_tokens.weight must be (%d, %d)" % (cfg.vocab, cfg.d_model))
+        self.embed = torch.from_numpy(emb).to(self.device)
+        self.pos_table = None
+        if cfg.positions == "learned":
+            self.pos_table = torch.from_numpy(np.ascontiguousarray(np.asarray(get("embed_positions.weight"), np.float32))).to(self.device)
+        self.blocks = []
+        for i in range(cfg.n_layers):
+            bw = {}
+            for key, val in weights.items():
+                for prefix in ("model.layers.%d." % i, "layers.%d." % i):
+                    if key.startswith(prefix):
+                        bw[key[len(prefix):].replace("self_attn.", "").replace("mlp.", "")] = val
+            blk = TransformerBlock(bw, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim, window=cfg.window,
+                                   rope=cfg.positions == "rope", rope_theta=cfg.rope_theta, qkv_bias=cfg.qkv_bias,
+                                   o_bias=cfg.o_bias, norm=cfg.norm, norm_eps=cfg.norm_eps, norm_bias=cfg.norm_bias, mlp=cfg.mlp,
+                                   mlp_bias=cfg.mlp_bias, device=self.device)
+            if self.world > 1:
+                for slot in ("q", "k", "v", "o", "gate", "up", "down"):
+                    full = getattr(blk, slot)
+                    if full is not None:
+                        setattr(blk, slot, _ShardedLinear(full, group, self.rank, self.world))
+            self.blocks.append(blk)
+        self.final_w = torch.from_numpy(np.ascontiguousarray(np.asarray(get("norm.weight"), np.float32))).to(self.device)
+        self.final_b = None
+        if cfg.norm_bias:
+            self.final_b = torch.from_numpy(np.ascontiguousarray(np.asarray(get("norm.bias"), np.float32))).to(self.device)
+        head = weights.get("lm_head.weight", None)
+        self.head = Linear(head if head is not None else emb, self.device)
+        if self.head.out_features != cfg.vocab:
+            raise ValueError("lm_head.weight must have %d rows" % cfg.vocab)
+        if self.world > 1:
+            self.head = _ShardedLinear(self.head, group, self.rank, self.world)
+        self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def allocate_state(self, batch_size, max_tokens):
+        return CausalLMState([b.allocate_state(batch_size, max_tokens) for b in self.blocks], batch_size, int(max_tokens))
+
+    def _ids(self, ids):
+        if isinstance(ids, torch.Tensor):
+            t = ids.to(self.device, torch.int32)
+        else:
+            a = np.asarray(ids)
+            if a.dtype.kind not in "iu":
+                raise TypeError("token ids must be integers")
+            t = torch.from_numpy(np.ascontiguousarray(a.astype(np.int32))).to(self.device)
+        if t.dim() != 2:
+            raise ValueError("token ids must be (batch, length)")
+        return t.contiguous()
+
+    def hidden_device(self, ids, state):
+        """Final-normed hidden states [B*L, d_model] for the ids, advancing the state."""
+        b, l = ids.shape
+        dev, st, cfg = self.device, _stream(self.device), self.config
+        if state.positions + l > cfg.max_positions:
+            raise ValueError("absolute position %d is at or beyond max_positions %d" % (state.positions + l - 1, cfg.max_positions))
+        x = torch.empty((b * l, cfg.d_model), dtype=torch.float32, device=dev)
+        _native.call("b200i_embedding", dev.index, st, _vp(x), _vp(self.embed), _vp(ids), b * l, cfg.vocab, cfg.d_model,
+                     _vp(self._status))
+        if self.pos_table is not None:
+            if state.positions + l > self.pos_table.shape[0]:
+                raise ValueError("position table of %d rows is too short" % self.pos_table.shape[0])
+            _native.call("b200i_add_positions", dev.index, st, _vp(x), _vp(self.pos_table), b * l, l, state.positions, cfg.d_model)
+        h = x.reshape(b, l, cfg.d_model)
+        for blk, bs in zip(self.blocks, state.layers):
+            h = blk.forward_device(h, bs)
+        return norm(h.reshape(b * l, cfg.d_model), self.final_w, self.final_b, cfg.norm_eps, NORM_KINDS[cfg.norm])
+
+    def check_ids(self):
+        """Raise if any id given since the last check was outside the vocabulary (reads one device word)."""
+        if int(self._status.item()) != 0:
+            self._status.zero_()
+            raise ValueError("a token id is outside the embedding table")
+
+    def forward_device(self, ids, state=None, last_only=False):
+        ids = self._ids(ids)
+        b, l = ids.shape
+        if state is None:
+            state = self.allocate_state(b, l)
+        hn = self.hidden_device(ids, state)
+        if last_only:
+            hn = hn.reshape(b, l, -1)[:, -1, :].contiguous()
+            return self.head(hn)
+        return self.head(hn).reshape(b, l, self.config.vocab)
+
+    def forward(self, ids, state=None):
+        """Logits (B, L, V) for the ids; with a state, appends to its caches."""
+        host = not isinstance(ids, torch.Tensor)
+        out = self.forward_device(ids, state)
+        self.check_ids()
+        return out.cpu().numpy() if host else out
+
+    def step(self, ids, state):
+        """Logits (B, V) for one new token per row."""
+        host = not isinstance(ids, torch.Tensor)
+        t = self._ids(ids if (isinstance(ids, torch.Tensor) and ids.dim() == 2) or np.ndim(ids) == 2 else np.asarray(ids)[:, None])
+        out = self.forward_device(t, state)[:, -1, :]
+        self.check_ids()
+        return out.cpu().numpy() if host else out
+
+    def argmax_device(self, logits2d):
+        out = torch.empty((logits2d.shape[0],), dtype=torch.int32, device=logits2d.device)
+        _native.call("b200i_argmax", logits2d.device.index, _stream(logits2d.device), _vp(out), _vp(logits2d.contiguous()),
+                     logits2d.shape[0], logits2d.shape[1])
+        return out
+
+    def generate(self, ids, max_new_tokens, greedy=True, state=None, return_logits=False):
+        """Prefill on `ids` (B, L), then `max_new_tokens` greedy steps; returns (B, L + new) ids. The whole
+        continuation stays on the device: one host read at the end."""
+        if not greedy:
+            raise ValueError("only greedy decoding is spelled")
+        host = not isinstance(ids, torch.Tensor)
+        t = self._ids(ids)
+        b, l = t.shape
+        if state is None:
+            state = self.allocate_state(b, l + max_new_tokens)
+        logits = self.forward_device(t, state, last_only=True)
+        out, kept = [t], []
+        for step in range(max_new_tokens):
+            nxt = self.argmax_device(logits).reshape(b, 1)
+            out.append(nxt)
+            if return_logits:
+                kept.append(logits)
+            if step + 1 < max_new_tokens:
+                logits = self.forward_device(nxt, state, last_only=True)
+        self.check_ids()
+        seq = torch.cat(out, dim=1)
+        seq = seq.cpu().numpy() if host else seq
+        if return_logits:
+            stack = torch.stack(kept, dim=1)
+            return seq, (stack.cpu().numpy() if host else stack)
+        return seq

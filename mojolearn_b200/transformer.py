@@ -1,0 +1,256 @@
+"""`TransformerBlock`: the reference's decoder block on B200, device resident.
+
+Mirrors python/mojolearn/_transformer_impl.py of the reference (:408-419 the
+constructor and its options, :461-481 `forward`, :527-572 `step` and
+`allocate_state`, :195-216 the state): weights by HuggingFace names in torch
+`[out, in]` layout, either float32 arrays or `lowbit`-packed (bf16 bits, or int8
+codes with per-row power-of-two exponents), which are materialised exactly inside
+the product kernels. Every projection is a `gemm.fp32.v1` OP_NT product; every
+other step is the reference's pinned seam (see csrc/decoder.cuh). A decode step
+is the same entry at L = 1 and equals the prefill bit for bit.
+
+`rope=False` and learned positions are an extension: the reference's block
+always rotates (transformer/block_options.mojo:46-48).
+
+Activations may be numpy arrays (copied to the device and back, like the
+reference's host surface) or CUDA torch tensors (stay on the device).
+"""
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _native, lowbit
+from .linalg import OP_NT, W_BF16, W_F32, W_INT8_EXP, W_INT8_SCALE
+from . import torch_ops
+
+NORM_KINDS = {"rmsnorm": 0, "layernorm": 1, "rmsnorm_offset": 2}
+MLP_KINDS = {"swiglu": 0, "silu_gated": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "geglu": 4, "geglu_tanh": 5}
+GATED = (0, 4, 5)
+MAX_POSITIONS = 8192
+
+
+def _vp(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream(dev):
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+class Linear(object):
+    """One `[out, in]` weight on the device in its storage format, applied as x @ W^T."""
+
+    def __init__(self, w, device, bias=None, rows=None):
+        if isinstance(w, Linear):
+            self.__dict__.update(w.__dict__)
+            return
+        self.scale = None
+        if isinstance(w, lowbit.BF16Weight):
+            self.w, self.kind = torch.from_numpy(np.ascontiguousarray(w.bits)).to(device), W_BF16
+        elif isinstance(w, lowbit.Int8Weight):
+            self.w, self.kind = torch.from_numpy(np.ascontiguousarray(w.codes)).to(device), W_INT8_EXP
+            self.scale = torch.from_numpy(np.ascontiguousarray(w.exponents)).to(device)
+        elif isinstance(w, tuple) and len(w) == 2:  # (int8 codes, float32 scales): the extension format
+            self.w, self.kind = torch.as_tensor(np.ascontiguousarray(w[0])).to(device), W_INT8_SCALE
+            self.scale = torch.as_tensor(np.ascontiguousarray(w[1], dtype=np.float32)).to(device)
+        else:
+            a = w if isinstance(w, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(np.asarray(w)))
+            if a.dtype != torch.float32 or a.dim() != 2:
+                raise TypeError("a projection weight must be 2-D float32 (or a lowbit-packed weight)")
+            self.w, self.kind = a.to(device).contiguous(), W_F32
+        self.bias = None
+        if bias is not None:
+            self.bias = torch.as_tensor(np.ascontiguousarray(np.asarray(bias, dtype=np.float32))).to(device)
+        self.out_features, self.in_features = self.w.shape
+
+    def shard_rows(self, lo, hi):
+        """The same layer restricted to output rows [lo, hi): a bit-neutral shard (a cell reads one weight row)."""
+        part = Linear.__new__(Linear)
+        part.__dict__.update(self.__dict__)
+        part.w = self.w[lo:hi].contiguous()
+        part.scale = self.scale[lo:hi].contiguous() if self.scale is not None else None
+        part.bias = self.bias[lo:hi].contiguous() if self.bias is not None else None
+        part.out_features = hi - lo
+        return part
+
+    def __call__(self, x2d):
+        y = torch_ops.product(x2d, self.w, self.scale, self.kind, OP_NT)
+        if self.bias is not None:
+            dev = y.device
+            _native.call("b200i_bias_add", dev.index, _stream(dev), _vp(y), _vp(self.bias), y.shape[0], y.shape[1])
+        return y
+
+
+class TransformerState(object):
+    """Caller-owned KV caches `[B, n_kv_heads, max_tokens, head_dim]` float32 and the tokens cached."""
+
+    def __init__(self, batch, n_kv_heads, max_tokens, head_dim, device):
+        self.k = torch.zeros((batch, n_kv_heads, max_tokens, head_dim), dtype=torch.float32, device=device)
+        self.v = torch.zeros_like(self.k)
+        self.cached_tokens = 0
+        self.max_tokens = max_tokens
+
+    def clone(self):
+        other = TransformerState.__new__(TransformerState)
+        other.k, other.v = self.k.clone(), self.v.clone()
+        other.cached_tokens, other.max_tokens = self.cached_tokens, self.max_tokens
+        return other
+
+
+def norm(x2d, w, bias, eps, kind):
+    out = torch.empty_like(x2d)
+    dev = x2d.device
+    _native.call("b200i_norm", dev.index, _stream(dev), _vp(out), _vp(x2d), _vp(w), _vp(bias), x2d.shape[0], x2d.shape[1],
+                 float(eps), kind)
+    return out
+
+
+def add(a, b):
+    out = torch.empty_like(a)
+    dev = a.device
+    _native.call("b200i_add", dev.index, _stream(dev), _vp(out), _vp(a), _vp(b), a.numel())
+    return out
+
+
+class TransformerBlock(object):
+    _NAMES = {"norm1": "input_layernorm.weight", "norm1_b": "input_layernorm.bias", "q": "q_proj.weight", "q_b": "q_proj.bias",
+              "k": "k_proj.weight", "k_b": "k_proj.bias", "v": "v_proj.weight", "v_b": "v_proj.bias", "o": "o_proj.weight",
+              "o_b": "o_proj.bias", "norm2": "post_attention_layernorm.weight", "norm2_b": "post_attention_layernorm.bias",
+              "gate": "gate_proj.weight", "gate_b": "gate_proj.bias", "up": "up_proj.weight", "up_b": "up_proj.bias",
+              "down": "down_proj.weight", "down_b": "down_proj.bias"}
+
+    def __init__(self, weights, *, n_heads, n_kv_heads=None, head_dim=None, window=0, rope=True, rope_theta=10000.0,
+                 qkv_bias=False, o_bias=False, norm="rmsnorm", norm_eps=1e-6, norm_bias=False, mlp="swiglu", mlp_bias=False,
+                 device=None, numeric_mode="identical"):
+        if numeric_mode != "identical":
+            raise RuntimeError("mojolearn_b200 has only the identical build")
+        _native.require_device()
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        if norm not in NORM_KINDS or mlp not in MLP_KINDS:
+            raise ValueError("unknown norm %r or mlp %r" % (norm, mlp))
+        if norm_bias and norm != "layernorm":
+            raise ValueError("an RMSNorm carries no bias (norm_bias needs layernorm)")
+        self.n_heads, self.n_kv_heads = int(n_heads), int(n_kv_heads or n_heads)
+        self.window, self.rope, self.rope_theta = int(window or 0), bool(rope), float(rope_theta)
+        self.norm_kind, self.norm_eps, self.norm_bias = NORM_KINDS[norm], float(norm_eps), bool(norm_bias)
+        self.mlp_kind, self.mlp_bias, self.qkv_bias, self.o_bias = MLP_KINDS[mlp], bool(mlp_bias), bool(qkv_bias), bool(o_bias)
+        self.weight_format = lowbit.format_of({k: v for k, v in weights.items() if not isinstance(v, (tuple, Linear))})
+
+        def vec(slot, need=True):
+            name = self._NAMES[slot]
+            if name not in weights:
+                if need:
+                    raise ValueError("weights lack %r" % name)
+                return None
+            a = np.ascontiguousarray(np.asarray(weights[name], dtype=np.float32))
+            if not np.isfinite(a).all():
+                raise ValueError("non-finite values in %s REFUSED" % name)
+            return torch.from_numpy(a).to(self.device)
+
+        def lin(slot, bias_slot, with_bias):
+            name = self._NAMES[slot]
+            if name not in weights:
+                raise ValueError("weights lack %r" % name)
+            bias = None
+            if with_bias:
+                bname = self._NAMES[bias_slot]
+                if bname not in weights:
+                    raise ValueError("weights lack %r" % bname)
+                bias = weights[bname]
+            return Linear(weights[name], self.device, bias)
+
+        self.norm1_w, self.norm2_w = vec("norm1"), vec("norm2")
+        self.norm1_b = vec("norm1_b") if self.norm_bias else None
+        self.norm2_b = vec("norm2_b") if self.norm_bias else None
+        self.q, self.k, self.v = (lin(s, s + "_b", self.qkv_bias) for s in ("q", "k", "v"))
+        self.o = lin("o", "o_b", self.o_bias)
+        self.gated = self.mlp_kind in GATED
+        self.gate = lin("gate", "gate_b", self.mlp_bias) if self.gated else None
+        self.up = lin("up", "up_b", self.mlp_bias)
+        self.down = lin("down", "down_b", self.mlp_bias)
+        self.d_model = self.q.in_features
+        self.head_dim = int(head_dim or self.q.out_features // self.n_heads)
+        if self.q.out_features != self.n_heads * self.head_dim or self.k.out_features != self.n_kv_heads * self.head_dim:
+            raise ValueError("projection widths do not match n_heads * head_dim")
+        if self.n_heads % self.n_kv_heads or self.head_dim % 2:
+            raise ValueError("n_heads must be a multiple of n_kv_heads and head_dim even")
+        self.inter = self.up.out_features
+
+    def allocate_state(self, batch, max_tokens):
+        return TransformerState(batch, self.n_kv_heads, int(max_tokens), self.head_dim, self.device)
+
+    # -- the block on device tensors: x [B, L, d_model] -> [B, L, d_model]; state is advanced by L
+    def forward_device(self, x, state):
+        b, l, dm = x.shape
+        if dm != self.d_model:
+            raise ValueError("x has width %d, the block %d" % (dm, self.d_model))
+        pos0, m = state.cached_tokens, b * l
+        if pos0 + l > state.max_tokens:
+            raise ValueError("transformer: this call would use %d KV slots and the cache holds %d REFUSED" %
+                             (pos0 + l, state.max_tokens))
+        if pos0 + l > MAX_POSITIONS:
+            raise ValueError("transformer: absolute position %d is at or beyond %d" % (pos0 + l - 1, MAX_POSITIONS))
+        dev, st = x.device, _stream(x.device)
+        x2 = x.reshape(m, dm).contiguous()
+        n1 = norm(x2, self.norm1_w, self.norm1_b, self.norm_eps, self.norm_kind)
+        q, k, v = self.q(n1), self.k(n1), self.v(n1)
+        if self.rope:
+            half = self.head_dim // 2
+            cosv = torch.empty((l, half), dtype=torch.float32, device=dev)
+            sinv = torch.empty_like(cosv)
+            _native.call("b200i_rope_table", dev.index, st, _vp(cosv), _vp(sinv), pos0, l, self.head_dim, self.rope_theta)
+            qr, kr = torch.empty_like(q), torch.empty_like(k)
+            _native.call("b200i_rope_apply", dev.index, st, _vp(qr), _vp(q), _vp(cosv), _vp(sinv), m, l, self.n_heads, self.head_dim)
+            _native.call("b200i_rope_apply", dev.index, st, _vp(kr), _vp(k), _vp(cosv), _vp(sinv), m, l, self.n_kv_heads,
+                         self.head_dim)
+        else:
+            qr, kr = q, k
+        cap = state.max_tokens
+        _native.call("b200i_kv_append", dev.index, st, _vp(state.k), _vp(kr), b, l, self.n_kv_heads, self.head_dim, cap, pos0)
+        _native.call("b200i_kv_append", dev.index, st, _vp(state.v), _vp(v), b, l, self.n_kv_heads, self.head_dim, cap, pos0)
+        used = pos0 + l
+        s = used - (max(0, pos0 - (self.window - 1)) if self.window else 0)
+        scores = torch.empty((b * self.n_heads * l * s,), dtype=torch.float32, device=dev)
+        ctx = torch.empty((m, self.n_heads * self.head_dim), dtype=torch.float32, device=dev)
+        _native.call("b200i_attention", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
+                     self.n_heads, self.n_kv_heads, self.head_dim, cap, used, self.window)
+        del scores
+        r1 = add(x2, self.o(ctx))
+        n2 = norm(r1, self.norm2_w, self.norm2_b, self.norm_eps, self.norm_kind)
+        up = self.up(n2)
+        gate = self.gate(n2) if self.gated else None
+        act = torch.empty_like(up)
+        _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(gate), _vp(up), up.numel(), self.mlp_kind)
+        y = add(r1, self.down(act))
+        state.cached_tokens = used
+        return y.reshape(b, l, dm)
+
+    def _run(self, x, state):
+        host = not isinstance(x, torch.Tensor)
+        if host:
+            a = np.asarray(x)
+            if a.dtype != np.float32:
+                raise TypeError("x must be float32, got %s" % a.dtype)
+            if not np.isfinite(a).all():
+                raise ValueError("non-finite values in x REFUSED")
+            xt = torch.from_numpy(np.ascontiguousarray(a)).to(self.device)
+        else:
+            xt = x
+        if xt.dim() != 3:
+            raise ValueError("x must be [B, L, d_model]")
+        if state is None:
+            state = self.allocate_state(xt.shape[0], xt.shape[1])
+        y = self.forward_device(xt, state)
+        return y.cpu().numpy() if host else y
+
+    def forward(self, x, state=None):
+        return self._run(x, state)
+
+    def step(self, x, state):
+        """One decode step: x [B, 1, d_model] (or [B, d_model]) against the cached tokens."""
+        if x.ndim == 2:
+            return self._run(x[:, None, :], state)[:, 0, :]
+        return self._run(x, state)

@@ -1,0 +1,152 @@
+"""The CPU-oracle composition of a decoder LM, used by the tests as the checker
+for mojolearn_b200.models.CausalLM: embedding gather, (learned positions,)
+blocks, final norm, head product, greedy argmax."""
+import hashlib
+
+import numpy as np
+
+import oracle
+
+BLOCK_NAMES = {"norm1": "input_layernorm.weight", "norm1_b": "input_layernorm.bias", "q": "self_attn.q_proj.weight",
+               "q_b": "self_attn.q_proj.bias", "k": "self_attn.k_proj.weight", "k_b": "self_attn.k_proj.bias",
+               "v": "self_attn.v_proj.weight", "v_b": "self_attn.v_proj.bias", "o": "self_attn.o_proj.weight",
+               "o_b": "self_attn.o_proj.bias", "norm2": "post_attention_layernorm.weight",
+               "norm2_b": "post_attention_layernorm.bias", "gate": "mlp.gate_proj.weight", "gate_b": "mlp.gate_proj.bias",
+               "up": "mlp.up_proj.weight", "up_b": "mlp.up_proj.bias", "down": "mlp.down_proj.weight",
+               "down_b": "mlp.down_proj.bias"}
+
+
+def hashed_uniform(n, seed):
+    """The verify harness's counter-mode sha256 stream (tools/identity_break.py:1415-1431 of the reference)."""
+    ctr = np.arange(n, dtype=np.uint64)
+    dig = hashlib.sha256(ctr.tobytes() + str(seed).encode()).digest()
+    chunks, blk, have = [], 0, 0
+    while have < n * 4:
+        h = hashlib.sha256(dig + blk.to_bytes(8, "little")).digest()
+        chunks.append(h)
+        have += len(h)
+        blk += 1
+    u32 = np.frombuffer(b"".join(chunks)[: n * 4], dtype=np.uint32)
+    return (u32.astype(np.float64) / 2 ** 32).astype(np.float32)
+
+
+def hashed_weight(shape, seed, lo, hi):
+    """tools/identity_break.py:3022-3027."""
+    n = int(np.prod(shape))
+    u = hashed_uniform(n, seed)
+    return np.ascontiguousarray((u * np.float32(hi - lo) + np.float32(lo)).astype(np.float32).reshape(shape))
+
+
+def transformer_lane_weights():
+    """The nine weights of the `transformer` lane (tools/identity_break.py:3639-3653)."""
+    dm, nh, nkv, hd, it = 32, 2, 1, 16, 64
+    shapes = {"input_layernorm.weight": (dm,), "post_attention_layernorm.weight": (dm,), "q_proj.weight": (nh * hd, dm),
+              "k_proj.weight": (nkv * hd, dm), "v_proj.weight": (nkv * hd, dm), "o_proj.weight": (dm, nh * hd),
+              "gate_proj.weight": (it, dm), "up_proj.weight": (it, dm), "down_proj.weight": (dm, it)}
+    near_one = ("input_layernorm.weight", "post_attention_layernorm.weight")
+    w = {}
+    for name, shp in shapes.items():
+        if name in near_one:
+            w[name] = (np.float32(1.0) + hashed_weight(shp, "transformer:near_one:" + name, -0.125, 0.125)).astype(np.float32)
+        else:
+            w[name] = hashed_weight(shp, "transformer:" + name, -0.125, 0.125)
+    return w, dict(d_model=dm, n_heads=nh, n_kv_heads=nkv, head_dim=hd, inter=it)
+
+
+def seq(X, b, l, dm, skip=0):
+    flat = np.ascontiguousarray(X).reshape(-1)
+    return np.ascontiguousarray(flat[skip: skip + b * l * dm].reshape(b, l, dm)).astype(np.float32)
+
+
+def block_slots(weights, prefix=""):
+    """HuggingFace-named block weights -> the oracle's slot dict (materialised float32)."""
+    out = {}
+    for slot, name in BLOCK_NAMES.items():
+        for key in (prefix + name, prefix + name.replace("self_attn.", "").replace("mlp.", "")):
+            if key in weights:
+                out[slot] = np.asarray(weights[key], dtype=np.float32)
+    return out
+
+
+def random_lm_weights(cfg, seed, scale=0.02):
+    """HuggingFace-named float32 weights for a CausalLMConfig, N(0, scale), norm weights near one."""
+    rng = np.random.default_rng(seed)
+
+    def mat(*shape):
+        return (rng.standard_normal(shape) * scale).astype(np.float32)
+
+    hd, nh, nkv, dm, it = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_model, cfg.intermediate
+    w = {"model.embed_tokens.weight": mat(cfg.vocab, dm), "model.norm.weight": (1 + mat(dm)).astype(np.float32),
+         "lm_head.weight": mat(cfg.vocab, dm)}
+    if cfg.norm_bias:
+        w["model.norm.bias"] = mat(dm)
+    if cfg.positions == "learned":
+        w["model.embed_positions.weight"] = mat(cfg.max_positions, dm)
+    gated = cfg.mlp in ("swiglu", "geglu", "geglu_tanh")
+    for i in range(cfg.n_layers):
+        p = "model.layers.%d." % i
+        w[p + "input_layernorm.weight"] = (1 + mat(dm)).astype(np.float32)
+        w[p + "post_attention_layernorm.weight"] = (1 + mat(dm)).astype(np.float32)
+        w[p + "self_attn.q_proj.weight"] = mat(nh * hd, dm)
+        w[p + "self_attn.k_proj.weight"] = mat(nkv * hd, dm)
+        w[p + "self_attn.v_proj.weight"] = mat(nkv * hd, dm)
+        w[p + "self_attn.o_proj.weight"] = mat(dm, nh * hd)
+        w[p + "mlp.up_proj.weight"] = mat(it, dm)
+        w[p + "mlp.down_proj.weight"] = mat(dm, it)
+        if gated:
+            w[p + "mlp.gate_proj.weight"] = mat(it, dm)
+        if cfg.norm_bias:
+            w[p + "input_layernorm.bias"] = mat(dm)
+            w[p + "post_attention_layernorm.bias"] = mat(dm)
+        if cfg.qkv_bias:
+            for n_, width in (("q", nh * hd), ("k", nkv * hd), ("v", nkv * hd)):
+                w[p + "self_attn.%s_proj.bias" % n_] = mat(width)
+        if cfg.o_bias:
+            w[p + "self_attn.o_proj.bias"] = mat(dm)
+        if cfg.mlp_bias:
+            w[p + "mlp.up_proj.bias"] = mat(it)
+            w[p + "mlp.down_proj.bias"] = mat(dm)
+            if gated:
+                w[p + "mlp.gate_proj.bias"] = mat(it)
+    return w
+
+
+class OracleLM(object):
+    def __init__(self, cfg, weights):
+        self.cfg, self.w = cfg, weights
+        self.bcfg = oracle.block_cfg(cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.intermediate, norm=cfg.norm,
+                                     norm_eps=cfg.norm_eps, norm_bias=cfg.norm_bias, qkv_bias=cfg.qkv_bias, o_bias=cfg.o_bias,
+                                     mlp=cfg.mlp, mlp_bias=cfg.mlp_bias, rope=cfg.positions == "rope",
+                                     rope_theta=cfg.rope_theta, window=cfg.window)
+        self.slots = [block_slots(weights, "model.layers.%d." % i) for i in range(cfg.n_layers)]
+
+    def allocate_state(self, b, cap):
+        return [oracle.KVState(b, self.cfg.n_kv_heads, cap, self.cfg.head_dim) for _ in range(self.cfg.n_layers)]
+
+    def forward(self, ids, state=None):
+        ids = np.asarray(ids, dtype=np.int32)
+        b, l = ids.shape
+        if state is None:
+            state = self.allocate_state(b, l)
+        x = oracle.embedding(self.w["model.embed_tokens.weight"], ids)
+        if self.cfg.positions == "learned":
+            x = oracle.add_positions(x, self.w["model.embed_positions.weight"], state[0].used)
+        for slots, st in zip(self.slots, state):
+            x = oracle.block_forward(self.bcfg, slots, x, st)
+        hn = oracle.norm(x.reshape(b * l, -1), self.w["model.norm.weight"], self.w.get("model.norm.bias"), self.cfg.norm_eps,
+                         self.cfg.norm)
+        return oracle.gemm_rows(hn, self.w["lm_head.weight"], oracle.OP_NT).reshape(b, l, -1)
+
+    def generate(self, ids, new_tokens):
+        ids = np.asarray(ids, dtype=np.int32)
+        b, l = ids.shape
+        state = self.allocate_state(b, l + new_tokens)
+        logits = self.forward(ids, state)[:, -1, :]
+        out, kept = [ids], []
+        for step in range(new_tokens):
+            nxt = oracle.argmax(logits).reshape(b, 1)
+            out.append(nxt)
+            kept.append(logits)
+            if step + 1 < new_tokens:
+                logits = self.forward(nxt, state)[:, -1, :]
+        return np.concatenate(out, axis=1), np.stack(kept, axis=1)

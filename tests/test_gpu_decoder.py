@@ -1,0 +1,99 @@
+"""GPU parity for the decoder path: the block's seams and the CausalLM against
+the CPU oracle, bit for bit, and against the verify table's transformer cells."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import decoder_ref
+import fixtures
+import oracle
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from mojolearn_b200 import lowbit  # noqa: E402
+from mojolearn_b200.models import CausalLM, CausalLMConfig  # noqa: E402
+from mojolearn_b200.transformer import TransformerBlock  # noqa: E402
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TABLE = json.load(open(os.path.join(GOLDEN, "verify_table_cells.json")))
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+def test_transformer_infer_cell_on_gpu(lane, fmt, kind):
+    w, dims = decoder_ref.transformer_lane_weights()
+    packed = lowbit.pack(w, fmt) if fmt != "float32" else w
+    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"])
+    assert blk.weight_format == fmt
+    x = decoder_ref.seq(fixtures.fixture(kind, seed=1), 2, 16, dims["d_model"])
+    y = blk.forward(x)
+    assert oracle.sha16(y) == TABLE["cells"]["%s/%s" % (lane, kind)]["infer"]
+
+
+OPTION_SETS = [
+    dict(),
+    dict(norm="layernorm", norm_bias=True, mlp="gelu", mlp_bias=True, qkv_bias=True, o_bias=True, positions="learned"),
+    dict(mlp="gelu_tanh", n_kv_heads=4, norm="rmsnorm_offset"),
+    dict(mlp="geglu", window=5),
+]
+
+
+@pytest.mark.parametrize("opts", OPTION_SETS)
+def test_causal_lm_matches_the_oracle_and_decode_equals_prefill(opts):
+    opts = dict(opts)
+    cfg = CausalLMConfig(vocab=97, d_model=48, n_layers=2, n_heads=4, n_kv_heads=opts.pop("n_kv_heads", 2), head_dim=12,
+                         intermediate=300, max_positions=64, **opts)
+    w = decoder_ref.random_lm_weights(cfg, seed=3, scale=0.2)
+    ref = decoder_ref.OracleLM(cfg, w)
+    lm = CausalLM(cfg, w)
+    ids = np.random.default_rng(0).integers(0, cfg.vocab, (3, 9)).astype(np.int32)
+    want = ref.forward(ids)
+    got = lm.forward(ids)
+    assert got.tobytes() == want.tobytes()
+    state = lm.allocate_state(3, 9)
+    first = lm.forward(ids[:, :5], state)
+    rest = [lm.step(ids[:, t], state) for t in range(5, 9)]
+    assert np.concatenate([first] + [r[:, None, :] for r in rest], axis=1).tobytes() == want.tobytes()
+    seq, logits = lm.generate(ids[:, :4], 6, return_logits=True)
+    rseq, rlogits = ref.generate(ids[:, :4], 6)
+    assert seq.tolist() == rseq.tolist() and logits.tobytes() == rlogits.tobytes()
+    with pytest.raises(ValueError):
+        lm.forward(np.full((1, 2), cfg.vocab, np.int32))
+
+
+def test_block_subnormal_forcing_inputs():
+    w, dims = decoder_ref.transformer_lane_weights()
+    blk = TransformerBlock(w, n_heads=2, n_kv_heads=1)
+    cfg = oracle.block_cfg(32, 2, 1, 16, 64)
+    x = decoder_ref.seq(fixtures.fixture("base", seed=1), 2, 16, 32) * np.float32(2.0 ** -70)
+    x[0, 3, :5] = np.float32(1e-41)
+    want = oracle.block_forward(cfg, decoder_ref.block_slots(w), x)
+    assert blk.forward(x).tobytes() == want.tobytes()
+
+
+def test_config4_shape_reduced_length():
+    """BASELINE config 4's architecture (12 layers would only repeat the block: 2 here), d_model 768, 12 heads,
+    MLP 3072 GELU, LayerNorm, learned positions, vocab 50304, batch 8: prompt 24 tokens then 4 greedy steps."""
+    cfg = CausalLMConfig(vocab=50304, d_model=768, n_layers=2, n_heads=12, intermediate=3072, norm="layernorm", norm_bias=True,
+                         mlp="gelu", mlp_bias=True, qkv_bias=True, o_bias=True, positions="learned", max_positions=64)
+    w = decoder_ref.random_lm_weights(cfg, seed=0, scale=0.02)
+    ids = np.random.default_rng(0).integers(0, cfg.vocab, (8, 24)).astype(np.int32)
+    seq, logits = CausalLM(cfg, w).generate(ids, 4, return_logits=True)
+    rseq, rlogits = decoder_ref.OracleLM(cfg, w).generate(ids, 4)
+    assert logits.tobytes() == rlogits.tobytes() and seq.tolist() == rseq.tolist()
+
+
+def test_config5_shape_int8_weights_reduced():
+    """BASELINE config 5's layer shapes (d_model 2048, 16 heads of 128, MLP 8192, vocab 50304, INT8 weights with
+    power-of-two row exponents), 1 layer, batch 4, prompt 20 then 3 steps, against the oracle on the materialised weights."""
+    cfg = CausalLMConfig(vocab=50304, d_model=2048, n_layers=1, n_heads=16, intermediate=8192, max_positions=64)
+    w = decoder_ref.random_lm_weights(cfg, seed=1, scale=0.02)
+    packed = {k: (lowbit.pack_one(v, "int8") if (v.ndim == 2 and "embed" not in k) else v) for k, v in w.items()}
+    mat = {k: lowbit.materialize_one(v) for k, v in packed.items()}
+    ids = np.random.default_rng(2).integers(0, cfg.vocab, (4, 20)).astype(np.int32)
+    seq, logits = CausalLM(cfg, packed).generate(ids, 3, return_logits=True)
+    rseq, rlogits = decoder_ref.OracleLM(cfg, mat).generate(ids, 3)
+    assert logits.tobytes() == rlogits.tobytes() and seq.tolist() == rseq.tolist()

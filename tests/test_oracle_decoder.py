@@ -1,0 +1,89 @@
+"""The decoder-block oracle against the verify table's transformer cells, and
+its own structural properties (decode equals prefill, batch rows independent)."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+
+import decoder_ref
+import fixtures
+import oracle
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TABLE = json.load(open(os.path.join(GOLDEN, "verify_table_cells.json")))
+
+
+def _materialise(w, fmt):
+    out = dict(w)
+    for name, a in w.items():
+        if a.ndim != 2:
+            continue
+        if fmt == "bfloat16":
+            out[name] = oracle.from_bf16(oracle.to_bf16(a))
+        elif fmt == "int8":
+            out[name] = oracle.dequantize_int8(*oracle.quantize_int8(a))
+    return out
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+def test_transformer_infer_cell(lane, fmt, kind):
+    """forward of the held-out (2, 16, 32) slab hashes to the table's `infer` cell (tools/identity_break.py:3639-3653, :3729-3737)."""
+    w, dims = decoder_ref.transformer_lane_weights()
+    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"])
+    x = decoder_ref.seq(fixtures.fixture(kind, seed=1), 2, 16, dims["d_model"])
+    y = oracle.block_forward(cfg, decoder_ref.block_slots(_materialise(w, fmt)), x)
+    assert oracle.sha16(y) == TABLE["cells"]["%s/%s" % (lane, kind)]["infer"]
+
+
+def test_portable_math_is_close_to_libm_and_exact_at_anchors():
+    assert oracle.math("powf", 10000.0, 0.0) == 1.0
+    assert oracle.math("rsqrtf", 16.0) == 0.25 and oracle.math("rsqrtf", 64.0) == 0.125
+    assert oracle.math("sqrtf", 2.0) == np.float32(math.sqrt(2.0))  # correctly rounded
+    rng = np.random.default_rng(0)
+    for x in rng.uniform(-20, 20, 200).astype(np.float32):
+        x = float(x)
+        assert abs(float(oracle.math("expf", x)) - math.exp(x)) <= 1e-6 * math.exp(x)
+        assert abs(float(oracle.math("tanhf", x)) - math.tanh(x)) <= 1e-6
+        y = float(np.float32(x / 5))
+        assert abs(float(oracle.math("erff", y)) - math.erf(y)) <= 1e-6
+    for x in rng.uniform(0, 8000, 200).astype(np.float32):
+        x = float(x)
+        assert abs(float(oracle.math("cosf", x)) - math.cos(x)) <= 1e-6
+        assert abs(float(oracle.math("sinf", x)) - math.sin(x)) <= 1e-6
+    assert oracle.math("fmaxf", -0.0, 0.0).view(np.uint32) == 0 and oracle.math("fmaxf", 0.0, -0.0).view(np.uint32) == 0
+
+
+@pytest.mark.parametrize("opts", [dict(), dict(norm="layernorm", norm_bias=True, mlp="gelu", mlp_bias=True, qkv_bias=True, o_bias=True, rope=False),
+                                  dict(mlp="gelu_tanh", n_kv_heads=4)])
+def test_decode_equals_prefill_and_rows_are_independent(opts):
+    rng = np.random.default_rng(1)
+    dm, nh, hd, it = 48, 4, 12, 300  # k = 300 in the down projection: three leaves, one carry
+    nkv = opts.pop("n_kv_heads", 2)
+    cfg = oracle.block_cfg(dm, nh, nkv, hd, it, **opts)
+    gated = cfg.mlp_kind in (0, 4, 5)
+    w = {"norm1": 1 + rng.standard_normal(dm) * 0.1, "norm2": 1 + rng.standard_normal(dm) * 0.1,
+         "q": rng.standard_normal((nh * hd, dm)) * 0.2, "k": rng.standard_normal((nkv * hd, dm)) * 0.2,
+         "v": rng.standard_normal((nkv * hd, dm)) * 0.2, "o": rng.standard_normal((dm, nh * hd)) * 0.2,
+         "up": rng.standard_normal((it, dm)) * 0.2, "down": rng.standard_normal((dm, it)) * 0.2}
+    if gated:
+        w["gate"] = rng.standard_normal((it, dm)) * 0.2
+    for b_, width in (("norm1_b", dm), ("norm2_b", dm), ("q_b", nh * hd), ("k_b", nkv * hd), ("v_b", nkv * hd), ("o_b", dm),
+                      ("up_b", it), ("down_b", dm), ("gate_b", it)):
+        w[b_] = rng.standard_normal(width) * 0.1
+    w = {k: np.asarray(v, dtype=np.float32) for k, v in w.items()}
+    x = rng.standard_normal((3, 9, dm)).astype(np.float32)
+    whole = oracle.block_forward(cfg, w, x)
+    state = oracle.KVState(3, nkv, 9, hd)
+    first = oracle.block_forward(cfg, w, x[:, :5].copy(), state)
+    rest = [oracle.block_forward(cfg, w, x[:, t:t + 1].copy(), state) for t in range(5, 9)]
+    assert np.concatenate([first] + rest, axis=1).tobytes() == whole.tobytes()
+    alone = oracle.block_forward(cfg, w, x[1:2].copy())
+    assert alone.tobytes() == whole[1:2].tobytes()
+
+
+def test_argmax_ties_go_to_the_lowest_id():
+    logits = np.array([[1.0, 3.0, 3.0, -1.0], [0.0, -0.0, 0.0, 0.0], [np.nan, 2.0, 1.0, 2.0]], dtype=np.float32)
+    assert oracle.argmax(logits).tolist() == [1, 0, 0]
