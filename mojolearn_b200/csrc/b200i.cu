@@ -478,12 +478,23 @@ int64_t b200i_attention(int64_t device, void *stream, float *ctx, const float *q
     int64_t key_lo = 0;
     if (window > 0 && pos0 - (window - 1) > 0) key_lo = pos0 - (window - 1);
     const int s = (int)(used - key_lo), own0 = (int)(pos0 - key_lo);
+    if (l <= ATT_SMALL_Q) {
+        dim3 gs((unsigned)((s + 127) / 128), (unsigned)(b * n_heads));
+        attn_scores_small_kernel<<<gs, 128, 0, st>>>(scores, q, kcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap,
+                                                       (int)key_lo, s, own0, (int)window);
+    } else {
     dim3 g1((unsigned)((s + ATT_T - 1) / ATT_T), (unsigned)((l + ATT_T - 1) / ATT_T), (unsigned)(b * n_heads));
     attn_scores_kernel<<<g1, 256, 0, st>>>(scores, q, kcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, (int)key_lo, s,
                                              own0, (int)window);
-    dim3 g2((unsigned)((l + CTX_ROWS - 1) / CTX_ROWS), (unsigned)(b * n_heads));
-    attn_context_kernel<<<g2, 32 * CTX_ROWS, (size_t)CTX_KT * head_dim * sizeof(float), st>>>(
-        ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, (int)key_lo, s, own0, (int)window);
+    }
+    if (l <= ATT_SMALL_Q && (size_t)s * sizeof(float) <= 40 * 1024) {
+        attn_context_row_kernel<<<(unsigned)(b * n_heads * l), 128, (size_t)s * sizeof(float), st>>>(
+            ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, (int)key_lo, s, own0, (int)window);
+    } else {
+        dim3 g2((unsigned)((l + CTX_ROWS - 1) / CTX_ROWS), (unsigned)(b * n_heads));
+        attn_context_kernel<<<g2, 32 * CTX_ROWS, (size_t)CTX_KT * head_dim * sizeof(float), st>>>(
+            ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, (int)key_lo, s, own0, (int)window);
+    }
     g_launches += 2;
     CUDA_TRY(cudaGetLastError());
     return 0;

@@ -41,19 +41,41 @@ __global__ void norm_kernel(float *__restrict__ out, const float *__restrict__ s
         float acc = 0.f;
         for (int j0 = 0; j0 < dm; j0 += 32) {
             const float mine = (j0 + lane < dm) ? ftz_bits(x[j0 + lane]) : 0.f;
-            const int cnt = min(32, dm - j0);
-            for (int j = 0; j < cnt; j++) acc = ftz_hw(__fadd_rn(acc, __shfl_sync(0xFFFFFFFFu, mine, j)));
+            if (j0 + 32 <= dm) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) acc = add_flushed(acc, __shfl_sync(0xFFFFFFFFu, mine, j));
+            } else {
+                for (int j = 0; j < dm - j0; j++) acc = add_flushed(acc, __shfl_sync(0xFFFFFFFFu, mine, j));
+            }
         }
         mean = ftz_bits(p_divf(acc, (float)dm));
     }
+    // Admission for the sum of squares: with every nonzero term at or above 2^-63 in
+    // magnitude each square is a normal number, the accumulator only grows, and no
+    // step result can be subnormal, so the bare fma is the contract's step.
+    unsigned key = 0xFFFFFFFFu;
+    for (int j = lane; j < dm; j += 32) {
+        float v = ftz_bits(x[j]);
+        if (kind == NORM_LAYER) v = ftz_bits(__fsub_rn(v, mean));
+        key = min(key, admit_key(v));
+    }
+    const bool bare = __all_sync(0xFFFFFFFFu, key >= (64u << 24) - 2u);
     float acc = 0.f;
     for (int j0 = 0; j0 < dm; j0 += 32) {
         float mine = (j0 + lane < dm) ? ftz_bits(x[j0 + lane]) : 0.f;
         if (kind == NORM_LAYER) mine = ftz_bits(__fsub_rn(mine, mean));
-        const int cnt = min(32, dm - j0);
-        for (int j = 0; j < cnt; j++) {
-            const float v = __shfl_sync(0xFFFFFFFFu, mine, j);
-            acc = step_flush(v, v, acc);
+        if (j0 + 32 <= dm && bare) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const float v = __shfl_sync(0xFFFFFFFFu, mine, j);
+                acc = step_bare(v, v, acc);
+            }
+        } else {
+            const int cnt = min(32, dm - j0);
+            for (int j = 0; j < cnt; j++) {
+                const float v = __shfl_sync(0xFFFFFFFFu, mine, j);
+                acc = step_flush(v, v, acc);
+            }
         }
     }
     const float var = ftz_bits(p_divf(acc, (float)dm));
@@ -174,6 +196,58 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(float *__restrict__ sc
     }
 }
 
+// The same scores for a handful of query rows (a decode step): one lane per key, one
+// serial chain per (query, key) over head_dim, keys staged through shared memory so
+// the cache rows are read in 128-byte segments.
+constexpr int ATT_SMALL_Q = 8;
+__global__ void __launch_bounds__(128) attn_scores_small_kernel(float *__restrict__ scores, const float *__restrict__ q,
+                                                                const float *__restrict__ kcache, int b, int l, int nh, int nkv,
+                                                                int hd, int cap, int key_lo, int s, int own0, int window) {
+    const float scale = ftz_bits(p_rsqrtf((float)hd));
+    __shared__ float qs[ATT_SMALL_Q][K_LEAF_MIN];
+    __shared__ float kt[4][32][33];
+    const int bh = blockIdx.y, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j0 = blockIdx.x * 128 + warp * 32;
+    const long long qw = (long long)nh * hd;
+    for (int idx = threadIdx.x; idx < l * hd; idx += 128)
+        qs[idx / hd][idx % hd] = ftz_bits(q[((long long)bb * l + idx / hd) * qw + (long long)h * hd + idx % hd]);
+    __syncthreads();
+    const float *kbase = kcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
+    float acc[ATT_SMALL_Q];
+#pragma unroll
+    for (int i = 0; i < ATT_SMALL_Q; i++) acc[i] = 0.f;
+    for (int p0 = 0; p0 < hd; p0 += 32) {
+        float tmp[32]; // all 32 row segments in flight before any is stored
+#pragma unroll
+        for (int r = 0; r < 32; r++)
+            tmp[r] = (j0 + r < s && p0 + lane < hd) ? kbase[(long long)(j0 + r) * hd + p0 + lane] : 0.f;
+#pragma unroll
+        for (int r = 0; r < 32; r++) kt[warp][r][lane] = ftz_bits(tmp[r]);
+        __syncwarp();
+        const int pn = min(32, hd - p0);
+        for (int p = 0; p < pn; p++) {
+            const float kvv = kt[warp][lane][p];
+#pragma unroll
+            for (int i = 0; i < ATT_SMALL_Q; i++)
+                if (i < l) acc[i] = step_flush(qs[i][p0 + p], kvv, acc[i]);
+        }
+        __syncwarp();
+    }
+    const int j = j0 + lane;
+    if (j >= s) return;
+    const float mfill = __uint_as_float(0xFF7FFFFFu);
+#pragma unroll
+    for (int i = 0; i < ATT_SMALL_Q; i++) {
+        if (i >= l) break;
+        int jlo = 0, jhi = own0 + i;
+        if (jhi > s - 1) jhi = s - 1;
+        if (window > 0) { jlo = own0 + i - window + 1; if (jlo < 0) jlo = 0; }
+        const float sc = ftz_bits(__fmul_rn(ftz_hw(acc[i]), scale));
+        scores[((long long)bh * l + i) * s + j] = ftz_bits(__fadd_rn(sc, (j < jlo || j > jhi) ? mfill : 0.0f));
+    }
+}
+
 // ---- softmax and value sum ----------------------------------------------------------------------
 // One warp per query row; the eight rows of a CTA share one (batch, head) and the
 // value tiles staged in shared memory. The masked scores are overwritten in place
@@ -253,6 +327,70 @@ __global__ void __launch_bounds__(32 * CTX_ROWS) attn_context_kernel(float *__re
             const int d = lane + 32 * i;
             if (d < hd) o[d] = acc[i];
         }
+    }
+}
+
+// The same seams with ONE CTA per query row, for a decode step (few query rows, long
+// key axis): the row's weights are built once in shared memory (the denominator by
+// one warp, shuffle rounds), then thread d walks the value chain of feature d down
+// the keys, reading the cache in coalesced rows with the loads running ahead.
+__global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict__ ctx, float *__restrict__ scores,
+                                                                const float *__restrict__ vcache, int b, int l, int nh, int nkv,
+                                                                int hd, int cap, int key_lo, int s, int own0, int window) {
+    extern __shared__ float wrow[]; // [s] weights of this row
+    __shared__ unsigned red[4];
+    __shared__ float den_s;
+    const int r = blockIdx.x; // (bh, qi)
+    const int bh = r / l, qi = r % l, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float *row = scores + (long long)r * s;
+    int jlo = 0, jhi = own0 + qi;
+    if (jhi > s - 1) jhi = s - 1;
+    if (window > 0) { jlo = own0 + qi - window + 1; if (jlo < 0) jlo = 0; }
+    unsigned best = 0u;
+    for (int j = tid; j < s; j += 128) best = max(best, order_key(ftz_bits(row[j])));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, off));
+    if (lane == 0) red[warp] = best;
+    __syncthreads();
+    best = max(max(red[0], red[1]), max(red[2], red[3]));
+    const float fm = ftz_bits(order_unkey(best));
+    for (int j = jlo + tid; j <= jhi; j += 128) wrow[j] = ftz_bits(p_expf(ftz_bits(__fsub_rn(ftz_bits(row[j]), fm))));
+    __syncthreads();
+    if (warp == 0) { // S17: serial ascending, every value already flushed
+        float den = 0.f;
+        for (int j0 = jlo; j0 <= jhi; j0 += 32) {
+            const float e = (j0 + lane <= jhi) ? wrow[j0 + lane] : 0.f;
+            if (j0 + 31 <= jhi) {
+#pragma unroll
+                for (int t = 0; t < 32; t++) den = add_flushed(den, __shfl_sync(0xFFFFFFFFu, e, t));
+            } else {
+                for (int t = 0; t < jhi - j0 + 1; t++) den = add_flushed(den, __shfl_sync(0xFFFFFFFFu, e, t));
+            }
+        }
+        if (lane == 0) den_s = den;
+    }
+    __syncthreads();
+    const float den = den_s;
+    for (int j = jlo + tid; j <= jhi; j += 128) {
+        const float wgt = ftz_bits(p_divf(wrow[j], den));
+        wrow[j] = wgt;
+        row[j] = wgt;
+    }
+    __syncthreads();
+    const float *vbase = vcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
+    for (int d = tid; d < hd; d += 128) {
+        float acc = 0.f;
+        int j = jlo;
+        for (; j + 7 <= jhi; j += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = ftz_bits(vbase[(long long)(j + u) * hd + d]);
+#pragma unroll
+            for (int u = 0; u < 8; u++) acc = step_flush(wrow[j + u], v[u], acc);
+        }
+        for (; j <= jhi; j++) acc = step_flush(wrow[j], ftz_bits(vbase[(long long)j * hd + d]), acc);
+        ctx[((long long)bb * l + qi) * ((long long)nh * hd) + (long long)h * hd + d] = acc;
     }
 }
 

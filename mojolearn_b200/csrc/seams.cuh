@@ -89,6 +89,16 @@ __device__ __forceinline__ unsigned long long ftz2_hw(unsigned long long x) {
     return d;
 }
 
+// ftz(a + b) for operands that are ALREADY flushed, in one instruction. Two floats
+// that are zero or normal are multiples of 2^-149, so a sum below 2^-126 is exactly
+// representable: nothing is rounded there, and flushing the result is the same as
+// rounding first and flushing after (the window that breaks fma.rn.ftz cannot occur).
+__device__ __forceinline__ float add_flushed(float a, float b) {
+    float r;
+    asm("add.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+
 // fold-node addition: both children are already flushed; add, then flush.
 __device__ __forceinline__ float fold_add(float x, float y) { return ftz_hw(__fadd_rn(x, y)); }
 

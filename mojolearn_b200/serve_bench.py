@@ -1,0 +1,127 @@
+"""Decoder serving benchmark: INT8-weight decode tokens/s (baseline configuration 5).
+
+    python -m mojolearn_b200.serve_bench [--layers 24] [--d-model 2048] [--heads 16] [--mlp 8192] [--vocab 50304]
+                                         [--batch 32] [--prompt 1024] [--decode 256] [--timed-steps 32] [--format int8]
+    torchrun --nproc-per-node N -m mojolearn_b200.serve_bench ...   (output-column sharded, NCCL all-gather)
+
+Random-init weights N(0, 0.02) quantised per row to int8 codes with power-of-two
+exponents, uniform random token ids, prefill on the prompt, then greedy decode
+steps timed with CUDA events (max over ranks). Prints one JSON line on rank 0,
+with a hash of the generated ids and of the last logits so runs at different N
+can be compared word for word.
+"""
+import argparse
+import hashlib
+import json
+import os
+
+import numpy as np
+import torch
+
+from . import _native, lowbit
+from .models import CausalLM, CausalLMConfig
+
+
+def build_weights(cfg, fmt, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+
+    def mat(*shape):
+        return (torch.randn(shape, generator=g, device="cuda") * 0.02).cpu().numpy()
+
+    def proj(*shape):
+        a = mat(*shape)
+        return a if fmt == "float32" else lowbit.pack_one(a, fmt)
+
+    dm, hd, nh, nkv, it = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.intermediate
+    w = {"model.embed_tokens.weight": mat(cfg.vocab, dm), "model.norm.weight": np.ones(dm, np.float32),
+         "lm_head.weight": proj(cfg.vocab, dm)}
+    for i in range(cfg.n_layers):
+        p = "model.layers.%d." % i
+        w[p + "input_layernorm.weight"] = np.ones(dm, np.float32)
+        w[p + "post_attention_layernorm.weight"] = np.ones(dm, np.float32)
+        w[p + "self_attn.q_proj.weight"] = proj(nh * hd, dm)
+        w[p + "self_attn.k_proj.weight"] = proj(nkv * hd, dm)
+        w[p + "self_attn.v_proj.weight"] = proj(nkv * hd, dm)
+        w[p + "self_attn.o_proj.weight"] = proj(dm, nh * hd)
+        w[p + "mlp.gate_proj.weight"] = proj(it, dm)
+        w[p + "mlp.up_proj.weight"] = proj(it, dm)
+        w[p + "mlp.down_proj.weight"] = proj(dm, it)
+    return w
+
+
+def run(args):
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    cfg = CausalLMConfig(vocab=args.vocab, d_model=args.d_model, n_layers=args.layers, n_heads=args.heads,
+                         intermediate=args.mlp, max_positions=8192)
+    lm = CausalLM(cfg, build_weights(cfg, args.format), device=dev, group=group)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    ids = torch.randint(0, cfg.vocab, (args.batch, args.prompt), generator=gen, device=dev, dtype=torch.int32)
+    state = lm.allocate_state(args.batch, args.prompt + args.decode)
+    launches0 = _native.lib().b200i_launch_count()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    torch.cuda.synchronize(dev)
+    e[0].record()
+    logits = lm.forward_device(ids, state, last_only=True)
+    e[1].record()
+    steps, timed, toks = args.decode, min(args.timed_steps, args.decode), []
+    for step in range(steps):
+        if step == steps - timed:
+            if world > 1:
+                torch.distributed.barrier()
+            torch.cuda.synchronize(dev)
+            e[2].record()
+        nxt = lm.argmax_device(logits).reshape(args.batch, 1)
+        toks.append(nxt)
+        logits = lm.forward_device(nxt, state, last_only=True)
+    e[3].record()
+    torch.cuda.synchronize(dev)
+    t = torch.tensor([e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])], device=dev, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    prefill_ms, decode_ms = float(t[0]), float(t[1])
+    lm.check_ids()
+    seq = torch.cat(toks, dim=1).cpu().numpy()
+    out = {"metric": "int8w_decode_tokens_per_s", "value": args.batch * timed / (decode_ms * 1e-3), "unit": "tokens/s",
+           "n_gpus": world, "ms_per_decode_step": decode_ms / timed, "prefill_ms": prefill_ms,
+           "prefill_tokens_per_s": args.batch * args.prompt / (prefill_ms * 1e-3), "timed_steps": timed,
+           "config": {"layers": args.layers, "d_model": args.d_model, "heads": args.heads, "mlp": args.mlp, "vocab": args.vocab,
+                      "batch": args.batch, "prompt": args.prompt, "decode": args.decode, "weights": args.format,
+                      "sharding": "output columns over %d ranks, NCCL all-gather" % world if world > 1 else "none"},
+           "ids_sha256": hashlib.sha256(seq.tobytes()).hexdigest()[:16],
+           "logits_sha256": hashlib.sha256(logits.cpu().numpy().tobytes()).hexdigest()[:16],
+           "gpu_launches": int(_native.lib().b200i_launch_count() - launches0)}
+    return out, rank
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--d-model", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--mlp", type=int, default=8192)
+    ap.add_argument("--vocab", type=int, default=50304)
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--decode", type=int, default=256)
+    ap.add_argument("--timed-steps", type=int, default=32)
+    ap.add_argument("--format", default="int8", choices=["int8", "bfloat16", "float32"])
+    args = ap.parse_args()
+    out, rank = run(args)
+    if rank == 0:
+        print(json.dumps(out))
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
