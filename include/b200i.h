@@ -88,6 +88,23 @@ int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a
  * within shared memory), else 0. */
 int64_t b200i_decode_plan_fits(int64_t m, int64_t n, int64_t k, int64_t op, int64_t wkind);
 
+/* The float32 product for callers that must not allocate: code running inside an
+ * allocator hook or a memory-pool callback, a real-time serving loop with a fixed
+ * device-memory budget, or a host that hands this library raw pointers and forbids
+ * it cudaMalloc. It has no counterpart in the reference. Same arithmetic and same
+ * bits as b200i_gemm_f32; the difference is where the split plan's scratch (the
+ * leaf-group nodes) lives: in a fixed 16 MiB array inside the library image, which
+ * every GPU that loads the library holds until the process exits. The call makes no
+ * cudaMalloc, cudaFree or other allocating call. A shape whose plan needs more than
+ * 16 MiB of scratch is refused with a message naming both sizes (use b200i_gemm_f32
+ * and caller scratch for it). The first call on each device looks up the array's
+ * device address (a synchronous runtime query), so make that first call before any
+ * stream capture begins. All calls on a device share the one array: nothing in it has
+ * to start at zero (every node a launch reads was written by that launch), but two
+ * calls that overlap on the GPU, on different streams or threads, race on it. */
+int64_t b200i_gemm_f32_noalloc(int64_t device, void *stream, float *c, const float *a, const float *b, int64_t m, int64_t n,
+                               int64_t k, int64_t op, char *err, int64_t err_cap);
+
 /* Scratch bytes the product needs for this shape on the current device. */
 int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k);
 

@@ -402,6 +402,39 @@ int64_t b200i_ffma_probe(int64_t device, void *stream, float *scratch, int64_t b
     return 0;
 }
 
+// ---- the product without any allocation ---------------------------------------------------------
+// Scratch for the split plan lives in the library image itself: a fixed device array
+// that every GPU loading the library carries until the process exits.
+constexpr size_t STATIC_SCRATCH_BYTES = 16u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+static void *g_static_scratch_ptr[64]; // per device: the array's DEVICE address (the symbol itself is only a host-side stand-in)
+
+int64_t b200i_gemm_f32_noalloc(int64_t device, void *stream, float *c, const float *a, const float *b, int64_t m, int64_t n,
+                               int64_t k, int64_t op, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    if (dev < 0 || dev >= 64) return fail(err, err_cap, "identical gemm: device %d out of range", dev);
+    if (!g_static_scratch_ptr[dev]) {
+        // once per device, with that device current: ask the runtime where the array lives on it
+        void *p = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        g_static_scratch_ptr[dev] = p;
+    }
+    if (m <= 0 || n <= 0 || k <= 0)
+        return fail(err, err_cap, "identical gemm: m, n and k must be positive (got m=%lld n=%lld k=%lld)", (long long)m,
+                    (long long)n, (long long)k);
+    const Plan plan = choose_plan(m, n, k, sm_count(dev));
+    const int64_t need = plan.groups > 1 ? (int64_t)plan.groups * m * n * 4 : 0;
+    if (need > (int64_t)STATIC_SCRATCH_BYTES)
+        return fail(err, err_cap,
+                    "identical gemm: this shape needs %lld bytes of scratch and the built-in scratch holds %lld; "
+                    "call b200i_gemm_f32 with scratch of b200i_workspace_bytes(m, n, k) bytes instead",
+                    (long long)need, (long long)STATIC_SCRATCH_BYTES);
+    return launch_product(dev, static_cast<cudaStream_t>(stream), c, a, b, nullptr, W_F32, m, n, k, (int)op, plan.kind,
+                          plan.groups > 1 ? plan.group_leaves : 0, g_static_scratch_ptr[dev], (int64_t)STATIC_SCRATCH_BYTES, err, err_cap);
+}
+
 // ---- decoder-block seams (device pointers, asynchronous on the caller's stream) ----------------
 
 #define SEAM_PROLOGUE()                                          \
