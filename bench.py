@@ -139,7 +139,7 @@ def reference_arm(args, rank, world):
     if rank != 0:
         return
     threads = host_threads()
-    shapes = cpu_sample_shapes(4.0, 12.0 * threads)
+    shapes = cpu_sample_shapes(4.0, 25.0 * threads)
     gflops, dt = run_cpu(shapes, args.steps, min(args.warmup, 1), threads)
     sample = "first rows of A per sweep shape, n and k exact: " + ", ".join("%dx%dx%d" % s for s in shapes)
     line = {"impl": "reference", "metric": "identical_fp32_gemm_gflops", "value": gflops, "unit": "GFLOP/s",
@@ -161,6 +161,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-serve", action="store_true")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -267,7 +268,7 @@ def main():
                 "launch_ms": {"%dx%dx%d" % SWEEP[i]: per_shape_ms[i] for i in range(len(SWEEP))},
                 "traffic": None}
 
-    # ---- decode kernel against HBM: INT8 weights [11008, 4096], one activation row ----
+    # ---- decode kernel against HBM: weights [11008, 4096] in three storage kinds, one activation row ----
     peaks_file = os.path.join(ROOT, "MEASURED_PEAKS.json")
     hbm_peak, hbm_src = 6650.0, "fallback"
     if os.path.exists(peaks_file):
@@ -275,34 +276,53 @@ def main():
             hbm_peak, hbm_src = float(json.load(open(peaks_file))["hbm_gbs"]), "measured"
         except (ValueError, KeyError):
             pass
-    nbuf = 6  # 6 x 45 MB of weights rotate through, so no launch finds its weights in the 126 MB L2
+    from mojolearn_b200.linalg import OP_NT, W_BF16, W_F32, W_INT8_EXP
     g2 = torch.Generator(device=dev).manual_seed(100 + rank)
-    wq = [torch.randint(-127, 128, (DECODE_N, DECODE_K), generator=g2, device=dev, dtype=torch.int8) for _ in range(nbuf)]
     we = torch.randint(-10, -5, (DECODE_N,), generator=g2, device=dev, dtype=torch.int32)
     decode = {}
-    for mrows in (1, 8):
-        x = torch.randn((mrows, DECODE_K), generator=g2, device=dev)
-        y = torch.empty((mrows, DECODE_N), device=dev)
-        for i in range(nbuf):
-            torch_ops.linear_int8w(x, wq[i], exponents=we, out=y)
-        torch.cuda.synchronize(dev)
-        reps = 5
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
+    for kind_name, wkind, wbytes, nbuf in (("int8", W_INT8_EXP, 1, 6), ("bf16", W_BF16, 2, 4), ("f32", W_F32, 4, 3)):
+        # nbuf weight buffers rotate through, so no launch finds its weights in the 126 MB L2
+        if wkind == W_INT8_EXP:
+            wq = [torch.randint(-127, 128, (DECODE_N, DECODE_K), generator=g2, device=dev, dtype=torch.int8) for _ in range(nbuf)]
+        elif wkind == W_BF16:
+            wq = [torch_ops.to_bf16(torch.randn((DECODE_N, DECODE_K), generator=g2, device=dev) * 0.02) for _ in range(nbuf)]
+        else:
+            wq = [torch.randn((DECODE_N, DECODE_K), generator=g2, device=dev) * 0.02 for _ in range(nbuf)]
+        scale = we if wkind == W_INT8_EXP else None
+        for mrows in (1, 8):
+            x = torch.randn((mrows, DECODE_K), generator=g2, device=dev)
+            y = torch.empty((mrows, DECODE_N), device=dev)
+            reps = 4
             for i in range(nbuf):
-                torch_ops.linear_int8w(x, wq[i], exponents=we, out=y)
-        e1.record()
-        torch.cuda.synchronize(dev)
-        us = e0.elapsed_time(e1) * 1e3 / (reps * nbuf)
-        nbytes = mrows * DECODE_K * 4 + DECODE_N * DECODE_K + DECODE_N * 4 + mrows * DECODE_N * 4
-        decode[mrows] = {"us": us, "gbs": nbytes / (us * 1e-6) / 1e9, "bytes": nbytes,
-                         "tflops": 2.0 * mrows * DECODE_N * DECODE_K / (us * 1e-6) / 1e12}
-    roofline_decode = {"bound": "hbm", "kernel": "decode_kernel<int8,1>", "achieved": decode[1]["gbs"], "peak": hbm_peak,
-                       "unit": "GB/s", "frac": decode[1]["gbs"] / hbm_peak, "peak_source": hbm_src + " HBM copy bandwidth",
-                       "us_per_launch": decode[1]["us"], "algorithmic_bytes": decode[1]["bytes"], "traffic": None,
-                       "m8": decode[8], "rows_per_s_m1": 1e6 / decode[1]["us"]}
-    del wq
+                torch_ops.product(x, wq[i], scale, wkind, OP_NT, out=y)
+            torch.cuda.synchronize(dev)
+            # the launches are replayed from one CUDA graph, so the host's launch cost is not in the number
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(reps):
+                    for i in range(nbuf):
+                        torch_ops.product(x, wq[i], scale, wkind, OP_NT, out=y)
+            graph.replay()
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            us = e0.elapsed_time(e1) * 1e3 / (reps * nbuf)
+            nbytes = mrows * DECODE_K * 4 + DECODE_N * DECODE_K * wbytes + (DECODE_N * 4 if scale is not None else 0) + mrows * DECODE_N * 4
+            decode[(kind_name, mrows)] = {"us": us, "gbs": nbytes / (us * 1e-6) / 1e9, "bytes": nbytes, "frac_hbm": nbytes / (us * 1e-6) / 1e9 / hbm_peak,
+                                          "tflops": 2.0 * mrows * DECODE_N * DECODE_K / (us * 1e-6) / 1e12}
+            del graph
+        del wq
+    d1 = decode[("int8", 1)]
+    roofline_decode = {"bound": "hbm", "kernel": "decode_kernel<int8,1>", "achieved": d1["gbs"], "peak": hbm_peak, "unit": "GB/s",
+                       "frac": d1["gbs"] / hbm_peak, "peak_source": hbm_src + " HBM copy bandwidth", "us_per_launch": d1["us"],
+                       "algorithmic_bytes": d1["bytes"], "traffic": None, "timing": "CUDA events around one graph replay of 24 launches",
+                       "all": {"%s_m%d" % k: v for k, v in decode.items()}}
+    nbuf = 6
 
     # ---- end to end: host buffers through linalg.matmul, pinned memory ----
     e2e = None
@@ -339,10 +359,24 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         threads = host_threads()
-        shapes = cpu_sample_shapes(12.0, 12.0 * threads)
-        gflops, dt = run_cpu(shapes, 1, 1, threads)
+        shapes = cpu_sample_shapes(4.0, 25.0 * threads)
+        _, probe_dt = run_cpu(shapes, 1, 1, threads)
+        passes = max(1, min(20, int(12.0 / max(probe_dt, 0.05))))  # about 12 s of CPU work
+        gflops, dt = run_cpu(shapes, passes, 0, threads)
         cpu = {"value": gflops, "unit": "GFLOP/s", "cores": threads, "kind": "port", "seconds": dt,
-               "sample": "first rows of A per sweep shape, n and k exact: " + ", ".join("%dx%dx%d" % s for s in shapes)}
+               "sample": "%d passes over the first rows of A per sweep shape, n and k exact: " % passes
+                         + ", ".join("%dx%dx%d" % s for s in shapes)}
+
+    # ---- decoder serving, baseline configuration 5 (INT8 weights), sharded by output columns when N > 1 ----
+    serve = None
+    if not args.skip_serve:
+        import argparse as _ap
+        from mojolearn_b200 import serve_bench
+        sargs = _ap.Namespace(layers=24, d_model=2048, heads=16, mlp=8192, vocab=50304, batch=32, prompt=1024, decode=48,
+                              timed_steps=32, format="int8")
+        del ops
+        torch.cuda.empty_cache()
+        serve, _ = serve_bench.run(sargs)
 
     if rank == 0:
         line = {"metric": "identical_fp32_gemm_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world,
@@ -354,8 +388,9 @@ def main():
                            "bit_exact": "every product is the oracle's bits (tests/test_gpu_gemm.py)"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
                 "roofline_decode": roofline_decode, "cpu_baseline": cpu,
-                "decode": {"metric": "int8w_decode_rows_per_s", "value": 1e6 / decode[1]["us"], "unit": "rows/s",
-                           "weights": "int8 [11008, 4096] + int32 row exponents", "rotating_weight_buffers": nbuf}}
+                "decode": {"metric": "int8w_matvec_rows_per_s", "value": 1e6 / d1["us"], "unit": "rows/s",
+                           "weights": "int8 [11008, 4096] + int32 row exponents", "rotating_weight_buffers": nbuf},
+                "serve": serve}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -68,7 +68,7 @@ int select_device(int64_t device, char *err, int64_t err_cap, int *out) {
 }
 
 // ---- plans -----------------------------------------------------------------------------
-enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4 };
+enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4, PLAN_T128X64 = 5 };
 
 struct Plan {
     int kind;
@@ -208,13 +208,19 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
             return fail(err, err_cap, "identical gemm: the decode plan needs op NT, m <= %d, k a multiple of 16 and 16-byte aligned weights", DECODE_MAX_M);
         g_launches += launch_decode(g, sm_count(dev), st);
     } else if (plan.kind == PLAN_T128) {
-        launch_tile<128, 128, 2, 2, 2>(g, plan.groups, st);
+#ifndef B200I_T128_MINB
+#define B200I_T128_MINB 2
+#endif
+        launch_tile<128, 128, 2, 2, B200I_T128_MINB>(g, plan.groups, st);
         g_launches++;
     } else if (plan.kind == PLAN_T64) {
         launch_tile<64, 64, 1, 1, 3>(g, plan.groups, st);
         g_launches++;
     } else if (plan.kind == PLAN_T32) {
         launch_tile<32, 128, 1, 2, 4>(g, plan.groups, st);
+        g_launches++;
+    } else if (plan.kind == PLAN_T128X64) {
+        launch_tile<128, 64, 2, 1, 3>(g, plan.groups, st);
         g_launches++;
     } else {
         return fail(err, err_cap, "identical gemm: unknown plan %d", plan.kind);

@@ -258,6 +258,16 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
     auto step_fast = [&](int buf, int kk) {
         float av[TM], bv[TN];
         read_operands(buf, kk, av, bv);
+#ifdef B200I_SCALAR_FMA
+#pragma unroll
+        for (int i = 0; i < TM; i++)
+#pragma unroll
+            for (int j = 0; j < TN / 2; j++) {
+                float lo, hi;
+                unpack2(acc[i][j], lo, hi);
+                acc[i][j] = pack2(step_bare(av[i], bv[2 * j], lo), step_bare(av[i], bv[2 * j + 1], hi));
+            }
+#else
         unsigned long long b2[TN / 2];
 #pragma unroll
         for (int j = 0; j < TN / 2; j++) b2[j] = pack2(bv[2 * j], bv[2 * j + 1]);
@@ -267,6 +277,7 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
 #pragma unroll
             for (int j = 0; j < TN / 2; j++) acc[i][j] = fma2_bare(a2, b2[j], acc[i][j]);
         }
+#endif
     };
     auto step_slow = [&](int buf, int kk) {
         float av[TM], bv[TN];

@@ -28,7 +28,7 @@ import torch
 
 from .. import _native
 from ..parallel import gather_columns, shard_bounds
-from ..transformer import Linear, TransformerBlock, TransformerState, _stream, _vp, add, norm, NORM_KINDS
+from ..transformer import Linear, TransformerBlock, TransformerState, _stream, _vector, _vp, add, norm, NORM_KINDS
 
 
 class CausalLMConfig(object):
@@ -86,13 +86,12 @@ class CausalLM(object):
                     return weights[key]
             raise ValueError("weights lack %r" % name)
 
-        emb = np.ascontiguousarray(np.asarray(get("embed_tokens.weight"), dtype=np.float32))
-        if emb.shape != (cfg.vocab, cfg.d_model):
+        self.embed = _vector(get("embed_tokens.weight"), "embed_tokens.weight", self.device)
+        if tuple(self.embed.shape) != (cfg.vocab, cfg.d_model):
             raise ValueError("embed_tokens.weight must be (%d, %d)" % (cfg.vocab, cfg.d_model))
-        self.embed = torch.from_numpy(emb).to(self.device)
         self.pos_table = None
         if cfg.positions == "learned":
-            self.pos_table = torch.from_numpy(np.ascontiguousarray(np.asarray(get("embed_positions.weight"), np.float32))).to(self.device)
+            self.pos_table = _vector(get("embed_positions.weight"), "embed_positions.weight", self.device)
         self.blocks = []
         for i in range(cfg.n_layers):
             bw = {}
@@ -110,12 +109,10 @@ class CausalLM(object):
                     if full is not None:
                         setattr(blk, slot, _ShardedLinear(full, group, self.rank, self.world))
             self.blocks.append(blk)
-        self.final_w = torch.from_numpy(np.ascontiguousarray(np.asarray(get("norm.weight"), np.float32))).to(self.device)
-        self.final_b = None
-        if cfg.norm_bias:
-            self.final_b = torch.from_numpy(np.ascontiguousarray(np.asarray(get("norm.bias"), np.float32))).to(self.device)
+        self.final_w = _vector(get("norm.weight"), "norm.weight", self.device)
+        self.final_b = _vector(get("norm.bias"), "norm.bias", self.device) if cfg.norm_bias else None
         head = weights.get("lm_head.weight", None)
-        self.head = Linear(head if head is not None else emb, self.device)
+        self.head = Linear(head if head is not None else self.embed, self.device)
         if self.head.out_features != cfg.vocab:
             raise ValueError("lm_head.weight must have %d rows" % cfg.vocab)
         if self.world > 1:

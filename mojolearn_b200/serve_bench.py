@@ -18,27 +18,36 @@ import os
 import numpy as np
 import torch
 
-from . import _native, lowbit
+from . import _native
 from .models import CausalLM, CausalLMConfig
 
 
 def build_weights(cfg, fmt, seed=0):
+    """Random-init weights built and quantised on the device (nothing crosses the host)."""
+    from . import torch_ops
+    from .linalg import W_BF16, W_INT8_EXP
+    from .transformer import Linear
     g = torch.Generator(device="cuda").manual_seed(seed)
 
     def mat(*shape):
-        return (torch.randn(shape, generator=g, device="cuda") * 0.02).cpu().numpy()
+        return torch.randn(shape, generator=g, device="cuda") * 0.02
 
     def proj(*shape):
         a = mat(*shape)
-        return a if fmt == "float32" else lowbit.pack_one(a, fmt)
+        if fmt == "int8":
+            codes, exps = torch_ops.quantize_int8(a)
+            return Linear.from_device(codes, exps, W_INT8_EXP)
+        if fmt == "bfloat16":
+            return Linear.from_device(torch_ops.to_bf16(a), None, W_BF16)
+        return Linear.from_device(a)
 
     dm, hd, nh, nkv, it = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.intermediate
-    w = {"model.embed_tokens.weight": mat(cfg.vocab, dm), "model.norm.weight": np.ones(dm, np.float32),
-         "lm_head.weight": proj(cfg.vocab, dm)}
+    ones = torch.ones(dm, device="cuda")
+    w = {"model.embed_tokens.weight": mat(cfg.vocab, dm), "model.norm.weight": ones, "lm_head.weight": proj(cfg.vocab, dm)}
     for i in range(cfg.n_layers):
         p = "model.layers.%d." % i
-        w[p + "input_layernorm.weight"] = np.ones(dm, np.float32)
-        w[p + "post_attention_layernorm.weight"] = np.ones(dm, np.float32)
+        w[p + "input_layernorm.weight"] = ones
+        w[p + "post_attention_layernorm.weight"] = ones
         w[p + "self_attn.q_proj.weight"] = proj(nh * hd, dm)
         w[p + "self_attn.k_proj.weight"] = proj(nkv * hd, dm)
         w[p + "self_attn.v_proj.weight"] = proj(nkv * hd, dm)

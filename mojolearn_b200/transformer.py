@@ -38,6 +38,19 @@ def _stream(dev):
     return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
 
+def _vector(x, name, device):
+    """A float32 tensor on the device from a numpy array or a torch tensor; non-finite values are refused by name."""
+    if isinstance(x, torch.Tensor):
+        t = x.to(device=device, dtype=torch.float32).contiguous()
+        if not bool(torch.isfinite(t).all()):
+            raise ValueError("non-finite values in %s REFUSED" % name)
+        return t
+    a = np.ascontiguousarray(np.asarray(x, dtype=np.float32))
+    if not np.isfinite(a).all():
+        raise ValueError("non-finite values in %s REFUSED" % name)
+    return torch.from_numpy(a).to(device)
+
+
 class Linear(object):
     """One `[out, in]` weight on the device in its storage format, applied as x @ W^T."""
 
@@ -63,6 +76,14 @@ class Linear(object):
         if bias is not None:
             self.bias = torch.as_tensor(np.ascontiguousarray(np.asarray(bias, dtype=np.float32))).to(device)
         self.out_features, self.in_features = self.w.shape
+
+    @classmethod
+    def from_device(cls, w, scale=None, kind=W_F32, bias=None):
+        """A layer over tensors that already live on the device (weights built or quantised there)."""
+        self = cls.__new__(cls)
+        self.w, self.scale, self.kind, self.bias = w.contiguous(), scale, kind, bias
+        self.out_features, self.in_features = self.w.shape
+        return self
 
     def shard_rows(self, lo, hi):
         """The same layer restricted to output rows [lo, hi): a bit-neutral shard (a cell reads one weight row)."""
@@ -137,7 +158,7 @@ class TransformerBlock(object):
         self.window, self.rope, self.rope_theta = int(window or 0), bool(rope), float(rope_theta)
         self.norm_kind, self.norm_eps, self.norm_bias = NORM_KINDS[norm], float(norm_eps), bool(norm_bias)
         self.mlp_kind, self.mlp_bias, self.qkv_bias, self.o_bias = MLP_KINDS[mlp], bool(mlp_bias), bool(qkv_bias), bool(o_bias)
-        self.weight_format = lowbit.format_of({k: v for k, v in weights.items() if not isinstance(v, (tuple, Linear))})
+        self.weight_format = lowbit.format_of({k: v for k, v in weights.items() if lowbit.is_packed(v)})
 
         def vec(slot, need=True):
             name = self._NAMES[slot]
@@ -145,10 +166,7 @@ class TransformerBlock(object):
                 if need:
                     raise ValueError("weights lack %r" % name)
                 return None
-            a = np.ascontiguousarray(np.asarray(weights[name], dtype=np.float32))
-            if not np.isfinite(a).all():
-                raise ValueError("non-finite values in %s REFUSED" % name)
-            return torch.from_numpy(a).to(self.device)
+            return _vector(weights[name], name, self.device)
 
         def lin(slot, bias_slot, with_bias):
             name = self._NAMES[slot]
