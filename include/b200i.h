@@ -75,8 +75,9 @@ int64_t b200i_gemm_w(int64_t device, void *stream, float *c, const float *a, con
 
 /* Same, with the execution plan forced: plan 0 = one thread per cell (the
  * on-device restatement of the oracle), 1 = 128x128 tiles, 2 = 64x64 tiles,
- * 3 = the row-streaming decode plan, 4 = 32x128 tiles; `group_leaves` = leaves per group (a
- * power of two, 0 = no split). Every plan returns the same bits; the tests
+ * 3 = the row-streaming decode plan (up to 8 rows), 4 = 32x128 tiles, 5 = 128x64 tiles,
+ * 6 = the skinny plan (op NT, up to 32 activation rows, k a multiple of 16, 16-byte aligned
+ * operands); `group_leaves` = leaves per group (a power of two, 0 = no split). Every plan returns the same bits; the tests
  * hold them to that (the reference's launch-invariance gate,
  * gemm/checks/gemm_device_check.mojo:1016). */
 int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale,
@@ -184,6 +185,25 @@ int64_t b200i_embedding(int64_t device, void *stream, float *y, const float *tab
 /* x[rows, width] += pos[pos0 + row % l] (learned positions; an extension, the reference's block always rotates). */
 int64_t b200i_add_positions(int64_t device, void *stream, float *x, const float *pos, int64_t rows, int64_t l, int64_t pos0,
                             int64_t width, char *err, int64_t err_cap);
+/* The position-on-device twins, for a decode step captured once as a CUDA graph and replayed:
+ * a replayed launch cannot take the number of cached tokens as an argument, so these read it
+ * from `position`, one device int32 holding the tokens cached BEFORE the call (the pos0 of the
+ * calls above; `used` = *position + l). Same arithmetic, same bits. The launch is sized for the
+ * whole cache, `scores` must hold b*n_heads*l*min(cap, window - 1 + l or cap) floats, and the
+ * caller keeps *position + l within cap and below 8192 (a write past the cache is skipped).
+ * b200i_advance_position adds `delta` to the word on the stream. No reference counterpart: the
+ * reference's resident decode session (python/mojolearn/models/causal_lm.py:197-201) keeps its
+ * position on the host. */
+int64_t b200i_rope_table_at(int64_t device, void *stream, float *cosv, float *sinv, const int32_t *position, int64_t l,
+                            int64_t head_dim, double theta, char *err, int64_t err_cap);
+int64_t b200i_kv_append_at(int64_t device, void *stream, float *cache, const float *src, int64_t b, int64_t l, int64_t n_kv,
+                           int64_t head_dim, int64_t cap, const int32_t *position, char *err, int64_t err_cap);
+int64_t b200i_attention_at(int64_t device, void *stream, float *ctx, const float *q, const float *kcache, const float *vcache,
+                           float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
+                           const int32_t *position, int64_t window, char *err, int64_t err_cap);
+int64_t b200i_add_positions_at(int64_t device, void *stream, float *x, const float *pos, int64_t rows, int64_t l,
+                               const int32_t *position, int64_t width, char *err, int64_t err_cap);
+int64_t b200i_advance_position(int64_t device, void *stream, int32_t *position, int64_t delta, char *err, int64_t err_cap);
 /* out[rows] = index of the largest logit, ties to the lowest id (python/mojolearn/models/causal_lm.py:190). */
 int64_t b200i_argmax(int64_t device, void *stream, int32_t *out, const float *logits, int64_t rows, int64_t vocab, char *err,
                      int64_t err_cap);

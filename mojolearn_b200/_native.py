@@ -71,6 +71,11 @@ SIGNATURES = {
     "b200i_embedding": [I64, VP, VP, VP, VP, I64, I64, I64, VP, VP, I64],
     "b200i_add_positions": [I64, VP, VP, VP, I64, I64, I64, I64, VP, I64],
     "b200i_argmax": [I64, VP, VP, VP, I64, I64, VP, I64],
+    "b200i_rope_table_at": [I64, VP, VP, VP, VP, I64, I64, F64, VP, I64],
+    "b200i_kv_append_at": [I64, VP, VP, VP, I64, I64, I64, I64, I64, VP, VP, I64],
+    "b200i_attention_at": [I64, VP, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, I64, VP, I64, VP, I64],
+    "b200i_add_positions_at": [I64, VP, VP, VP, I64, I64, VP, I64, VP, I64],
+    "b200i_advance_position": [I64, VP, VP, I64, VP, I64],
     "b200i_ffma_probe": [I64, VP, VP, I64, I64, I64, VP, I64],
 }
 STRING_FUNCTIONS = ["b200i_numerical_profile", "b200i_vendor"]

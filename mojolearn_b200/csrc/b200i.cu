@@ -10,6 +10,7 @@
 #include "decode.cuh"
 #include "decoder.cuh"
 #include "gemm_tile.cuh"
+#include "gemm_skinny.cuh"
 #include "lowbit.cuh"
 
 using namespace b200i;
@@ -68,7 +69,9 @@ int select_device(int64_t device, char *err, int64_t err_cap, int *out) {
 }
 
 // ---- plans -----------------------------------------------------------------------------
-enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4, PLAN_T128X64 = 5 };
+enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4, PLAN_T128X64 = 5, PLAN_SKINNY = 6 };
+
+constexpr int DECODE_PREFER_M = 4; // up to this many rows the weight-streaming decode plan wins; above, the skinny plan
 
 struct Plan {
     int kind;
@@ -124,6 +127,26 @@ Plan choose_plan(long long m, long long n, long long k, int sms) {
     return best;
 }
 
+// The skinny plan's leaf split: the largest power-of-two group that still gives
+// every CTA slot of the device a CTA (the kernel is latency-bound, so resident
+// warps matter more than the few extra group nodes), else single leaves.
+Plan choose_skinny(long long m, long long n, long long k, int sms) {
+    const int leaves = (int)leaf_count(k) > 0 ? (int)leaf_count(k) : 1;
+    const long long col_ctas = (n + skinny_bn((int)m) - 1) / skinny_bn((int)m);
+    const long long want = (long long)sms * skinny_per_sm((int)m) * 9 / 10;
+    const int max_s = pow2_floor(leaves) * ((leaves & (leaves - 1)) ? 2 : 1);
+    int min_s = 1;
+    while ((leaves + min_s - 1) / min_s > MAX_GROUPS) min_s *= 2;
+    int best = min_s;
+    for (int s = max_s; s >= min_s; s /= 2)
+        if (col_ctas * ((leaves + s - 1) / s) >= want) { best = s; break; }
+    Plan p{PLAN_SKINNY, best, (leaves + best - 1) / best};
+    if (p.groups <= 1) p.group_leaves = leaves;
+    return p;
+}
+
+bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
 template <int BM, int BN, int RM, int RN, int MINB>
 void launch_tile(GemmArgs &g, int groups, cudaStream_t st) {
     using S = TileShape<BM, BN, RM, RN>;
@@ -138,8 +161,6 @@ void launch_tile(GemmArgs &g, int groups, cudaStream_t st) {
     dim3 grid((unsigned)(((g.m + BM - 1) / BM) * g.tiles_n), (unsigned)groups);
     gemm_tile_kernel<BM, BN, RM, RN, MINB><<<grid, S::THREADS, S::SMEM_BYTES, st>>>(g);
 }
-
-bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const void *b, const void *bscale, int wkind,
                        int64_t m, int64_t n, int64_t k, int op, int plan_kind, int64_t group_leaves, void *ws,
@@ -168,7 +189,11 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     Plan plan;
     if (plan_kind == PLAN_AUTO) {
         plan = choose_plan(m, n, k, sm_count(dev));
-        if (decode_plan_fits(m, n, k, op, wkind) && aligned(b, 16) && aligned(a, 16)) plan = Plan{PLAN_DECODE, g.leaves, 1};
+        const bool al16 = aligned(b, 16) && aligned(a, 16);
+        const bool dec = decode_plan_fits(m, n, k, op, wkind) && al16;
+        if (dec && m <= DECODE_PREFER_M) plan = Plan{PLAN_DECODE, g.leaves, 1};
+        else if (skinny_plan_fits(m, n, k, op) && al16) plan = choose_skinny(m, n, k, sm_count(dev));
+        else if (dec) plan = Plan{PLAN_DECODE, g.leaves, 1};
     } else {
         plan.kind = plan_kind;
         int s = group_leaves > 0 ? (int)group_leaves : g.leaves;
@@ -221,6 +246,11 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
         g_launches++;
     } else if (plan.kind == PLAN_T128X64) {
         launch_tile<128, 64, 2, 1, 3>(g, plan.groups, st);
+        g_launches++;
+    } else if (plan.kind == PLAN_SKINNY) {
+        if (!skinny_plan_fits(m, n, k, op) || !aligned(b, 16) || !aligned(a, 16))
+            return fail(err, err_cap, "identical gemm: the skinny plan needs op NT, m <= 32, k a multiple of 16 and 16-byte aligned operands");
+        launch_skinny(g, plan.groups, st);
         g_launches++;
     } else {
         return fail(err, err_cap, "identical gemm: unknown plan %d", plan.kind);
@@ -301,7 +331,12 @@ int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = -1; }
     Plan p = choose_plan(m, n, k, sm_count(dev));
-    return p.groups > 1 ? (int64_t)p.groups * m * n * 4 : 0;
+    int groups = p.groups;
+    if (skinny_plan_fits(m, n, k, OP_NT)) { // the plan an NT product with aligned operands takes instead
+        const Plan q = choose_skinny(m, n, k, sm_count(dev));
+        if (q.groups > groups) groups = q.groups;
+    }
+    return groups > 1 ? (int64_t)groups * m * n * 4 : 0;
 }
 
 int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale,
@@ -455,8 +490,19 @@ int64_t b200i_norm(int64_t device, void *stream, float *out, const float *x, con
     if (rows <= 0 || width <= 0 || !out || !x || !w) return fail(err, err_cap, "norm: bad arguments");
     if (kind < NORM_RMS || kind > NORM_RMS_OFFSET) return fail(err, err_cap, "norm: norm kind %lld is not spelled", (long long)kind);
     if (bias && kind != NORM_LAYER) return fail(err, err_cap, "norm: an RMSNorm carries no bias (norm_bias needs layernorm)");
-    const long long threads = rows * 32;
-    norm_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(out, x, w, bias, rows, (int)width, (float)eps, (int)kind);
+    const int wpc = rows >= 1024 ? 4 : 1; // warps (rows) per CTA: few rows spread over the SMs
+    const size_t smem = (size_t)wpc * (size_t)((width + 3) & ~3ll) * sizeof(float);
+    if (smem <= 200 * 1024) {
+        static bool configured[64] = {};
+        if (dev >= 0 && dev < 64 && !configured[dev]) {
+            CUDA_TRY(cudaFuncSetAttribute(norm_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            configured[dev] = true;
+        }
+        norm_rows_kernel<<<(unsigned)((rows + wpc - 1) / wpc), 32 * wpc, smem, st>>>(out, x, w, bias, rows, (int)width, (float)eps, (int)kind);
+    } else {
+        const long long threads = rows * 32;
+        norm_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(out, x, w, bias, rows, (int)width, (float)eps, (int)kind);
+    }
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -470,7 +516,18 @@ int64_t b200i_rope_table(int64_t device, void *stream, float *cosv, float *sinv,
         return fail(err, err_cap, "rope_table: absolute position %lld is at or beyond 8192, the domain of the sine and cosine reduction",
                     (long long)(pos0 + l - 1));
     const long long n = l * (head_dim / 2);
-    rope_table_kernel<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(cosv, sinv, (int)pos0, (int)l, (int)head_dim, (float)theta);
+    rope_table_kernel<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(cosv, sinv, (int)pos0, (int)l, (int)head_dim, (float)theta, nullptr);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_rope_table_at(int64_t device, void *stream, float *cosv, float *sinv, const int32_t *position, int64_t l,
+                            int64_t head_dim, double theta, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (l <= 0 || head_dim <= 0 || (head_dim & 1) || !cosv || !sinv || !position) return fail(err, err_cap, "rope_table: bad arguments");
+    const long long n = l * (head_dim / 2);
+    rope_table_kernel<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(cosv, sinv, 0, (int)l, (int)head_dim, (float)theta, position);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -496,9 +553,67 @@ int64_t b200i_kv_append(int64_t device, void *stream, float *cache, const float 
         return fail(err, err_cap, "transformer: this call would use %lld KV slots and the cache holds %lld REFUSED", (long long)(pos0 + l),
                     (long long)cap);
     const long long n = b * l * n_kv * head_dim;
-    kv_append_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(cache, src, (int)b, (int)l, (int)n_kv, (int)head_dim, (int)cap, (int)pos0);
+    kv_append_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(cache, src, (int)b, (int)l, (int)n_kv, (int)head_dim, (int)cap, (int)pos0,
+                                                                  nullptr);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_kv_append_at(int64_t device, void *stream, float *cache, const float *src, int64_t b, int64_t l, int64_t n_kv,
+                           int64_t head_dim, int64_t cap, const int32_t *position, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (b <= 0 || l <= 0 || n_kv <= 0 || head_dim <= 0 || l > cap || !cache || !src || !position)
+        return fail(err, err_cap, "kv_append: bad arguments");
+    const long long n = b * l * n_kv * head_dim;
+    kv_append_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(cache, src, (int)b, (int)l, (int)n_kv, (int)head_dim, (int)cap, 0, position);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+// `s_grid` sizes the launch (the key count, or its upper bound when the position is read on the device)
+static int64_t attention_launch(int dev, cudaStream_t st, float *ctx, const float *q, const float *kcache, const float *vcache,
+                                float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
+                                int key_lo, int s, int own0, int s_grid, int64_t window, const int32_t *position, char *err,
+                                int64_t err_cap) {
+    (void)dev;
+    if (l <= ATT_SMALL_Q) {
+        dim3 gs((unsigned)((s_grid + 127) / 128), (unsigned)(b * n_heads));
+#define SCORES_SMALL(LQ)                                                                                                              \
+    attn_scores_small_kernel<LQ><<<gs, 128, 0, st>>>(scores, q, kcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, \
+                                                     key_lo, s, own0, (int)window, position)
+        if (l == 1) SCORES_SMALL(1);
+        else if (l == 2) SCORES_SMALL(2);
+        else if (l <= 4) SCORES_SMALL(4);
+        else SCORES_SMALL(8);
+#undef SCORES_SMALL
+    } else {
+        dim3 g1((unsigned)((s_grid + ATT_T - 1) / ATT_T), (unsigned)((l + ATT_T - 1) / ATT_T), (unsigned)(b * n_heads));
+        attn_scores_kernel<<<g1, 256, 0, st>>>(scores, q, kcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, key_lo, s,
+                                                 own0, (int)window, position);
+    }
+    if (l <= ATT_SMALL_Q && (size_t)s_grid * sizeof(float) <= 40 * 1024) {
+        attn_context_row_kernel<<<(unsigned)(b * n_heads * l), 128, (size_t)s_grid * sizeof(float), st>>>(
+            ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, key_lo, s, own0, (int)window, position);
+    } else {
+        dim3 g2((unsigned)((l + CTX_ROWS - 1) / CTX_ROWS), (unsigned)(b * n_heads));
+        attn_context_kernel<<<g2, 32 * CTX_ROWS, (size_t)CTX_KT * head_dim * sizeof(float), st>>>(
+            ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, key_lo, s, own0, (int)window, position);
+    }
+    g_launches += 2;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+static int64_t attention_check(int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, const void *ctx, const void *q,
+                               const void *kcache, const void *vcache, const void *scores, char *err, int64_t err_cap) {
+    if (b <= 0 || l <= 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || head_dim <= 0 || !ctx || !q || !kcache || !vcache || !scores)
+        return fail(err, err_cap, "attention: bad arguments");
+    if (head_dim > K_LEAF_MIN || head_dim > CTX_MAX_HD)
+        return fail(err, err_cap, "attention: head_dim %lld above 128 needs the leaf partition of the product, which this kernel does not spell",
+                    (long long)head_dim);
+    if (b * n_heads > 65535) return fail(err, err_cap, "attention: batch x heads above 65535");
     return 0;
 }
 
@@ -506,37 +621,26 @@ int64_t b200i_attention(int64_t device, void *stream, float *ctx, const float *q
                         float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
                         int64_t used, int64_t window, char *err, int64_t err_cap) {
     SEAM_PROLOGUE();
-    if (b <= 0 || l <= 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || head_dim <= 0 || !ctx || !q || !kcache || !vcache || !scores)
-        return fail(err, err_cap, "attention: bad arguments");
-    if (head_dim > K_LEAF_MIN || head_dim > CTX_MAX_HD)
-        return fail(err, err_cap, "attention: head_dim %lld above 128 needs the leaf partition of the product, which this kernel does not spell",
-                    (long long)head_dim);
+    if (attention_check(b, l, n_heads, n_kv, head_dim, ctx, q, kcache, vcache, scores, err, err_cap)) return 1;
     if (used < l || used > cap) return fail(err, err_cap, "attention: the cache holds %lld positions, this call's %lld included", (long long)used, (long long)l);
-    if (b * n_heads > 65535) return fail(err, err_cap, "attention: batch x heads above 65535");
     const int64_t pos0 = used - l;
     int64_t key_lo = 0;
     if (window > 0 && pos0 - (window - 1) > 0) key_lo = pos0 - (window - 1);
     const int s = (int)(used - key_lo), own0 = (int)(pos0 - key_lo);
-    if (l <= ATT_SMALL_Q) {
-        dim3 gs((unsigned)((s + 127) / 128), (unsigned)(b * n_heads));
-        attn_scores_small_kernel<<<gs, 128, 0, st>>>(scores, q, kcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap,
-                                                       (int)key_lo, s, own0, (int)window);
-    } else {
-    dim3 g1((unsigned)((s + ATT_T - 1) / ATT_T), (unsigned)((l + ATT_T - 1) / ATT_T), (unsigned)(b * n_heads));
-    attn_scores_kernel<<<g1, 256, 0, st>>>(scores, q, kcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, (int)key_lo, s,
-                                             own0, (int)window);
-    }
-    if (l <= ATT_SMALL_Q && (size_t)s * sizeof(float) <= 40 * 1024) {
-        attn_context_row_kernel<<<(unsigned)(b * n_heads * l), 128, (size_t)s * sizeof(float), st>>>(
-            ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, (int)key_lo, s, own0, (int)window);
-    } else {
-        dim3 g2((unsigned)((l + CTX_ROWS - 1) / CTX_ROWS), (unsigned)(b * n_heads));
-        attn_context_kernel<<<g2, 32 * CTX_ROWS, (size_t)CTX_KT * head_dim * sizeof(float), st>>>(
-            ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, (int)key_lo, s, own0, (int)window);
-    }
-    g_launches += 2;
-    CUDA_TRY(cudaGetLastError());
-    return 0;
+    return attention_launch(dev, st, ctx, q, kcache, vcache, scores, b, l, n_heads, n_kv, head_dim, cap, (int)key_lo, s, own0, s, window,
+                            nullptr, err, err_cap);
+}
+
+int64_t b200i_attention_at(int64_t device, void *stream, float *ctx, const float *q, const float *kcache, const float *vcache,
+                           float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
+                           const int32_t *position, int64_t window, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (attention_check(b, l, n_heads, n_kv, head_dim, ctx, q, kcache, vcache, scores, err, err_cap)) return 1;
+    if (!position || l > cap) return fail(err, err_cap, "attention: bad arguments");
+    int64_t s_max = cap; // the most keys any position can see
+    if (window > 0 && window - 1 + l < s_max) s_max = window - 1 + l;
+    return attention_launch(dev, st, ctx, q, kcache, vcache, scores, b, l, n_heads, n_kv, head_dim, cap, 0, (int)s_max, 0, (int)s_max, window,
+                            position, err, err_cap);
 }
 
 int64_t b200i_act_mul(int64_t device, void *stream, float *out, const float *gate, const float *up, int64_t count, int64_t kind,
@@ -584,7 +688,26 @@ int64_t b200i_add_positions(int64_t device, void *stream, float *x, const float 
                             int64_t width, char *err, int64_t err_cap) {
     SEAM_PROLOGUE();
     if (rows <= 0 || l <= 0 || width <= 0 || pos0 < 0 || !x || !pos) return fail(err, err_cap, "add_positions: bad arguments");
-    add_positions_kernel<<<grid_for(rows * width, 256, sm_count(dev)), 256, 0, st>>>(x, pos, rows, (int)l, (int)pos0, (int)width);
+    add_positions_kernel<<<grid_for(rows * width, 256, sm_count(dev)), 256, 0, st>>>(x, pos, rows, (int)l, (int)pos0, (int)width, nullptr);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_add_positions_at(int64_t device, void *stream, float *x, const float *pos, int64_t rows, int64_t l,
+                               const int32_t *position, int64_t width, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (rows <= 0 || l <= 0 || width <= 0 || !x || !pos || !position) return fail(err, err_cap, "add_positions: bad arguments");
+    add_positions_kernel<<<grid_for(rows * width, 256, sm_count(dev)), 256, 0, st>>>(x, pos, rows, (int)l, 0, (int)width, position);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_advance_position(int64_t device, void *stream, int32_t *position, int64_t delta, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (!position) return fail(err, err_cap, "advance_position: bad arguments");
+    advance_position_kernel<<<1, 1, 0, st>>>(position, (int)delta);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -594,7 +717,7 @@ int64_t b200i_argmax(int64_t device, void *stream, int32_t *out, const float *lo
                      int64_t err_cap) {
     SEAM_PROLOGUE();
     if (rows <= 0 || vocab <= 0 || !out || !logits) return fail(err, err_cap, "argmax: bad arguments");
-    argmax_kernel<<<(unsigned)rows, 256, 0, st>>>(out, logits, (int)vocab);
+    argmax_kernel<<<(unsigned)rows, ARGMAX_THREADS, 0, st>>>(out, logits, (int)vocab);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;

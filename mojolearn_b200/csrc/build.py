@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libb200i.so")
 SOURCES = ["b200i.cu"]
-HEADERS = ["seams.cuh", "gemm_tile.cuh", "decode.cuh", "lowbit.cuh", os.path.join("..", "..", "include", "b200i.h")]
+HEADERS = sorted(f for f in os.listdir(HERE) if f.endswith(".cuh")) + [os.path.join("..", "..", "include", "b200i.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-fmad=false", "-ftz=false", "-prec-div=true", "-prec-sqrt=true",

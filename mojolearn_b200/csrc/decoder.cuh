@@ -27,9 +27,133 @@ constexpr int NORM_RMS = 0, NORM_LAYER = 1, NORM_RMS_OFFSET = 2;
 constexpr int ACT_SWIGLU = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_GEGLU_ERF = 4, ACT_GEGLU_TANH = 5;
 
 // ---- normalisation: one warp per row -------------------------------------------------------
-// The sum of squares (or of deviations) is ONE serial chain over the row. Every
-// lane runs the same chain on values broadcast by shuffle, so the loads are
-// coalesced and the chain costs one dependent fma per element.
+// The sum of squares (or of deviations) is ONE serial chain over the row.
+//
+// norm_rows_kernel stages the row in shared memory first (every load of the row in
+// flight at once, 128-bit where the row allows), then every lane runs the same
+// chain on 128-bit broadcast reads: one dependent fma per element and nothing else
+// on the critical path. norm_kernel is the same arithmetic for rows too wide for
+// shared memory, the values broadcast by shuffle.
+//
+// Admission for the sum of squares: with every nonzero term at or above 2^-63 in
+// magnitude each square is a normal number, the accumulator only grows, and no
+// step result can be subnormal, so the bare fma is the contract's step.
+constexpr unsigned NORM_ADMIT_MIN = (64u << 24) - 2u;
+__global__ void norm_rows_kernel(float *__restrict__ out, const float *__restrict__ src, const float *__restrict__ w,
+                                 const float *__restrict__ bias, long long rows, int dm, float eps, int kind) {
+    extern __shared__ __align__(16) float norm_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= rows) return; // warps are independent: only warp-level barriers below
+    const int pitch = (dm + 3) & ~3;
+    float *xs = norm_smem + (size_t)warp * pitch;
+    const float *x = src + row * dm;
+    const bool vec = (dm % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    unsigned key = 0xFFFFFFFFu;
+    if (vec) {
+        // eight 128-bit loads per lane in flight: a lone warp has no other warp to hide a load behind
+        for (int j0 = lane * 4; j0 < dm; j0 += 8 * 128) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                v[u] = (j0 + u * 128 < dm) ? *reinterpret_cast<const float4 *>(x + j0 + u * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (j0 + u * 128 >= dm) break;
+                v[u].x = ftz_bits(v[u].x); v[u].y = ftz_bits(v[u].y); v[u].z = ftz_bits(v[u].z); v[u].w = ftz_bits(v[u].w);
+                key = min(min(key, admit_key(v[u].x)), min(admit_key(v[u].y), min(admit_key(v[u].z), admit_key(v[u].w))));
+                *reinterpret_cast<float4 *>(xs + j0 + u * 128) = v[u];
+            }
+        }
+    } else {
+        for (int j = lane; j < dm; j += 32) {
+            const float v = ftz_bits(x[j]);
+            key = min(key, admit_key(v));
+            xs[j] = v;
+        }
+    }
+    for (int j = dm + lane; j < pitch; j += 32) xs[j] = 0.f;
+    __syncwarp();
+    const int dm4 = dm & ~3;
+    if (kind == NORM_LAYER) {
+        float acc = 0.f;
+#pragma unroll 4
+        for (int j = 0; j < dm4; j += 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(xs + j);
+            acc = add_flushed(add_flushed(add_flushed(add_flushed(acc, v.x), v.y), v.z), v.w);
+        }
+        for (int j = dm4; j < dm; j++) acc = add_flushed(acc, xs[j]);
+        const float mean = ftz_bits(p_divf(acc, (float)dm));
+        __syncwarp();
+        key = 0xFFFFFFFFu;
+        for (int j = lane; j < dm; j += 32) {
+            const float v = ftz_bits(__fsub_rn(xs[j], mean));
+            key = min(key, admit_key(v));
+            xs[j] = v;
+        }
+        __syncwarp();
+    }
+    const bool bare = __all_sync(0xFFFFFFFFu, key >= NORM_ADMIT_MIN);
+    float acc = 0.f;
+    if (bare) {
+#pragma unroll 4
+        for (int j = 0; j < dm4; j += 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(xs + j);
+            acc = step_bare(v.x, v.x, acc);
+            acc = step_bare(v.y, v.y, acc);
+            acc = step_bare(v.z, v.z, acc);
+            acc = step_bare(v.w, v.w, acc);
+        }
+        for (int j = dm4; j < dm; j++) acc = step_bare(xs[j], xs[j], acc);
+    } else {
+#pragma unroll 2
+        for (int j = 0; j < dm4; j += 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(xs + j);
+            acc = step_flush(v.x, v.x, acc);
+            acc = step_flush(v.y, v.y, acc);
+            acc = step_flush(v.z, v.z, acc);
+            acc = step_flush(v.w, v.w, acc);
+        }
+        for (int j = dm4; j < dm; j++) acc = step_flush(xs[j], xs[j], acc);
+    }
+    const float var = ftz_bits(p_divf(acc, (float)dm));
+    const float rstd = ftz_bits(p_rsqrtf(ftz_bits(__fadd_rn(var, eps))));
+    auto finish = [&](float xv, float wv, float bv) {
+        const float inner = ftz_bits(__fmul_rn(xv, rstd));
+        float wj = ftz_bits(wv);
+        if (kind == NORM_RMS_OFFSET) wj = ftz_bits(__fadd_rn(1.0f, wj));
+        float y = ftz_bits(__fmul_rn(wj, inner));
+        if (kind == NORM_LAYER && bias) y = ftz_bits(__fadd_rn(y, ftz_bits(bv)));
+        return y;
+    };
+    const bool vec_out = vec && ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+                         (!bias || (reinterpret_cast<uintptr_t>(bias) & 15) == 0);
+    if (vec_out) {
+        const bool has_bias = kind == NORM_LAYER && bias;
+        for (int j0 = lane * 4; j0 < dm; j0 += 4 * 128) {
+            float4 wv[4], bv[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const bool in = j0 + u * 128 < dm;
+                wv[u] = in ? *reinterpret_cast<const float4 *>(w + j0 + u * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
+                bv[u] = (in && has_bias) ? *reinterpret_cast<const float4 *>(bias + j0 + u * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int j = j0 + u * 128;
+                if (j >= dm) break;
+                const float4 xv = *reinterpret_cast<const float4 *>(xs + j);
+                float4 y;
+                y.x = finish(xv.x, wv[u].x, bv[u].x); y.y = finish(xv.y, wv[u].y, bv[u].y);
+                y.z = finish(xv.z, wv[u].z, bv[u].z); y.w = finish(xv.w, wv[u].w, bv[u].w);
+                *reinterpret_cast<float4 *>(out + row * dm + j) = y;
+            }
+        }
+    } else {
+        for (int j = lane; j < dm; j += 32) out[row * dm + j] = finish(xs[j], w[j], (kind == NORM_LAYER && bias) ? bias[j] : 0.f);
+    }
+}
+
 __global__ void norm_kernel(float *__restrict__ out, const float *__restrict__ src, const float *__restrict__ w,
                             const float *__restrict__ bias, long long rows, int dm, float eps, int kind) {
     const int lane = threadIdx.x & 31;
@@ -50,16 +174,13 @@ __global__ void norm_kernel(float *__restrict__ out, const float *__restrict__ s
         }
         mean = ftz_bits(p_divf(acc, (float)dm));
     }
-    // Admission for the sum of squares: with every nonzero term at or above 2^-63 in
-    // magnitude each square is a normal number, the accumulator only grows, and no
-    // step result can be subnormal, so the bare fma is the contract's step.
     unsigned key = 0xFFFFFFFFu;
     for (int j = lane; j < dm; j += 32) {
         float v = ftz_bits(x[j]);
         if (kind == NORM_LAYER) v = ftz_bits(__fsub_rn(v, mean));
         key = min(key, admit_key(v));
     }
-    const bool bare = __all_sync(0xFFFFFFFFu, key >= (64u << 24) - 2u);
+    const bool bare = __all_sync(0xFFFFFFFFu, key >= NORM_ADMIT_MIN);
     float acc = 0.f;
     for (int j0 = 0; j0 < dm; j0 += 32) {
         float mine = (j0 + lane < dm) ? ftz_bits(x[j0 + lane]) : 0.f;
@@ -94,7 +215,8 @@ __global__ void norm_kernel(float *__restrict__ out, const float *__restrict__ s
 
 // ---- rotary table and application -----------------------------------------------------------
 __global__ void rope_table_kernel(float *__restrict__ cosv, float *__restrict__ sinv, int pos0, int l, int head_dim,
-                                  float theta) {
+                                  float theta, const int *__restrict__ pos_dev) {
+    if (pos_dev) pos0 = *pos_dev;
     const int half = head_dim / 2;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= l * half) return;
@@ -123,7 +245,8 @@ __global__ void rope_apply_kernel(float *__restrict__ out, const float *__restri
 
 // KV cache append: a copy, not a seam. cache is [b, n_kv, cap, hd]; src is [b*l, n_kv*hd].
 __global__ void kv_append_kernel(float *__restrict__ cache, const float *__restrict__ src, int b, int l, int n_kv, int hd,
-                                 int cap, int pos0) {
+                                 int cap, int pos0, const int *__restrict__ pos_dev) {
+    if (pos_dev) pos0 = *pos_dev;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long total = (long long)b * l * n_kv * hd;
     if (idx >= total) return;
@@ -131,8 +254,26 @@ __global__ void kv_append_kernel(float *__restrict__ cache, const float *__restr
     const int kv = (int)((idx / hd) % n_kv);
     const long long t = idx / ((long long)hd * n_kv);
     const int bb = (int)(t / l), li = (int)(t % l);
+    if (pos0 + li >= cap) return; // the host refuses such a call; a replayed graph must not write past the cache either
     cache[(((long long)bb * n_kv + kv) * cap + pos0 + li) * hd + d] = src[idx];
 }
+
+// ---- a position read on the device ------------------------------------------------------------
+// A decode step replayed from a captured graph cannot take its position as a launch
+// argument. Every kernel that depends on the number of cached tokens therefore also
+// accepts `pos_dev`, a device word holding it; when it is not null it overrides the
+// by-value arguments, and the key range of the attention kernels is derived from it
+// exactly as the host derives it (pos0 = cached tokens before this call).
+__device__ __forceinline__ void attn_geometry(const int *pos_dev, int l, int cap, int window, int &key_lo, int &s, int &own0) {
+    if (!pos_dev) return;
+    const int pos0 = *pos_dev;
+    int used = pos0 + l;
+    if (used > cap) used = cap;
+    key_lo = (window > 0 && pos0 - (window - 1) > 0) ? pos0 - (window - 1) : 0;
+    s = used - key_lo;
+    own0 = pos0 - key_lo;
+}
+__global__ void advance_position_kernel(int *pos_dev, int delta) { *pos_dev += delta; }
 
 // ---- attention scores -------------------------------------------------------------------------
 // scores[b, h, qi, j] = ftz(ftz(ftz(q . k) * scale) + fill), the dot being one
@@ -141,7 +282,10 @@ __global__ void kv_append_kernel(float *__restrict__ cache, const float *__restr
 constexpr int ATT_T = 64, ATT_KC = 32;
 __global__ void __launch_bounds__(256) attn_scores_kernel(float *__restrict__ scores, const float *__restrict__ q,
                                                           const float *__restrict__ kcache, int b, int l, int nh, int nkv, int hd,
-                                                          int cap, int key_lo, int s, int own0, int window) {
+                                                          int cap, int key_lo, int s, int own0, int window,
+                                                          const int *__restrict__ pos_dev) {
+    attn_geometry(pos_dev, l, cap, window, key_lo, s, own0);
+    if ((int)blockIdx.x * ATT_T >= s) return;
     // the attention scale, ftz(rsqrt(head_dim)) in the portable spelling: a pure function of head_dim
     const float scale = ftz_bits(p_rsqrtf((float)hd));
     __shared__ float qs[ATT_KC][ATT_T + 1];
@@ -198,39 +342,65 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(float *__restrict__ sc
 
 // The same scores for a handful of query rows (a decode step): one lane per key, one
 // serial chain per (query, key) over head_dim, keys staged through shared memory so
-// the cache rows are read in 128-byte segments.
+// the cache rows are read in 128-byte segments. LQ is the query-row count rounded up
+// to a power of two, a template parameter so that absent rows cost no issue slots.
+// While every staged 32-wide window of keys and the query rows pass the product's
+// admission test, the chain runs the bare fma (exactly the flushed step there).
 constexpr int ATT_SMALL_Q = 8;
+template <int LQ>
 __global__ void __launch_bounds__(128) attn_scores_small_kernel(float *__restrict__ scores, const float *__restrict__ q,
                                                                 const float *__restrict__ kcache, int b, int l, int nh, int nkv,
-                                                                int hd, int cap, int key_lo, int s, int own0, int window) {
+                                                                int hd, int cap, int key_lo, int s, int own0, int window,
+                                                                const int *__restrict__ pos_dev) {
+    attn_geometry(pos_dev, l, cap, window, key_lo, s, own0);
+    if ((int)blockIdx.x * 128 >= s) return;
     const float scale = ftz_bits(p_rsqrtf((float)hd));
-    __shared__ float qs[ATT_SMALL_Q][K_LEAF_MIN];
+    __shared__ float qs[LQ][K_LEAF_MIN];
     __shared__ float kt[4][32][33];
     const int bh = blockIdx.y, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int j0 = blockIdx.x * 128 + warp * 32;
     const long long qw = (long long)nh * hd;
-    for (int idx = threadIdx.x; idx < l * hd; idx += 128)
-        qs[idx / hd][idx % hd] = ftz_bits(q[((long long)bb * l + idx / hd) * qw + (long long)h * hd + idx % hd]);
-    __syncthreads();
+    unsigned qkey = 0xFFFFFFFFu;
+    for (int idx = threadIdx.x; idx < LQ * hd; idx += 128) {
+        const int i = idx / hd, p = idx % hd;
+        const float v = i < l ? ftz_bits(q[((long long)bb * l + i) * qw + (long long)h * hd + p]) : 0.f;
+        qkey = min(qkey, admit_key(v));
+        qs[i][p] = v;
+    }
+    bool clean = __syncthreads_and(qkey >= ADMIT_MIN);
     const float *kbase = kcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
-    float acc[ATT_SMALL_Q];
+    float acc[LQ];
 #pragma unroll
-    for (int i = 0; i < ATT_SMALL_Q; i++) acc[i] = 0.f;
+    for (int i = 0; i < LQ; i++) acc[i] = 0.f;
     for (int p0 = 0; p0 < hd; p0 += 32) {
         float tmp[32]; // all 32 row segments in flight before any is stored
 #pragma unroll
         for (int r = 0; r < 32; r++)
             tmp[r] = (j0 + r < s && p0 + lane < hd) ? kbase[(long long)(j0 + r) * hd + p0 + lane] : 0.f;
+        unsigned kkey = 0xFFFFFFFFu;
 #pragma unroll
-        for (int r = 0; r < 32; r++) kt[warp][r][lane] = ftz_bits(tmp[r]);
+        for (int r = 0; r < 32; r++) {
+            const float v = ftz_bits(tmp[r]);
+            kkey = min(kkey, admit_key(v));
+            kt[warp][r][lane] = v;
+        }
         __syncwarp();
         const int pn = min(32, hd - p0);
-        for (int p = 0; p < pn; p++) {
-            const float kvv = kt[warp][lane][p];
+        clean = clean && __all_sync(0xFFFFFFFFu, kkey >= ADMIT_MIN) && pn == 32;
+        if (clean) {
 #pragma unroll
-            for (int i = 0; i < ATT_SMALL_Q; i++)
-                if (i < l) acc[i] = step_flush(qs[i][p0 + p], kvv, acc[i]);
+            for (int p = 0; p < 32; p++) {
+                const float kvv = kt[warp][lane][p];
+#pragma unroll
+                for (int i = 0; i < LQ; i++) acc[i] = step_bare(qs[i][p0 + p], kvv, acc[i]);
+            }
+        } else {
+            for (int p = 0; p < pn; p++) {
+                const float kvv = kt[warp][lane][p];
+#pragma unroll
+                for (int i = 0; i < LQ; i++) acc[i] = step_flush(qs[i][p0 + p], kvv, acc[i]);
+            }
         }
         __syncwarp();
     }
@@ -238,7 +408,7 @@ __global__ void __launch_bounds__(128) attn_scores_small_kernel(float *__restric
     if (j >= s) return;
     const float mfill = __uint_as_float(0xFF7FFFFFu);
 #pragma unroll
-    for (int i = 0; i < ATT_SMALL_Q; i++) {
+    for (int i = 0; i < LQ; i++) {
         if (i >= l) break;
         int jlo = 0, jhi = own0 + i;
         if (jhi > s - 1) jhi = s - 1;
@@ -256,7 +426,8 @@ constexpr int CTX_ROWS = 8, CTX_KT = 32, CTX_MAX_HD = 256;
 __global__ void __launch_bounds__(32 * CTX_ROWS) attn_context_kernel(float *__restrict__ ctx, float *__restrict__ scores,
                                                                       const float *__restrict__ vcache, int b, int l, int nh,
                                                                       int nkv, int hd, int cap, int key_lo, int s, int own0,
-                                                                      int window) {
+                                                                      int window, const int *__restrict__ pos_dev) {
+    attn_geometry(pos_dev, l, cap, window, key_lo, s, own0);
     extern __shared__ float vtile[]; // [CTX_KT][hd]
     const int bh = blockIdx.y, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -333,10 +504,30 @@ __global__ void __launch_bounds__(32 * CTX_ROWS) attn_context_kernel(float *__re
 // The same seams with ONE CTA per query row, for a decode step (few query rows, long
 // key axis): the row's weights are built once in shared memory (the denominator by
 // one warp, shuffle rounds), then thread d walks the value chain of feature d down
-// the keys, reading the cache in coalesced rows with the loads running ahead.
+// the keys. The cache is read in coalesced rows, a batch of CTX_NB keys per thread
+// always in flight ahead of the chain (the first batch is issued before the softmax
+// phases), so the kernel keeps about 16 KB per CTA outstanding to HBM.
+constexpr int CTX_NB = 32;
+__device__ __forceinline__ void ctx_load_batch(float (&buf)[CTX_NB], const float *__restrict__ vbase, int hd, int d, int j0, int jhi) {
+#pragma unroll
+    for (int u = 0; u < CTX_NB; u++) buf[u] = (j0 + u <= jhi) ? vbase[(long long)(j0 + u) * hd + d] : 0.f;
+}
+__device__ __forceinline__ float ctx_walk_batch(const float (&buf)[CTX_NB], const float *wrow, int j0, int jhi, float acc) {
+    if (j0 + CTX_NB - 1 <= jhi) {
+#pragma unroll
+        for (int u = 0; u < CTX_NB; u++) acc = step_flush(wrow[j0 + u], ftz_bits(buf[u]), acc);
+    } else {
+#pragma unroll
+        for (int u = 0; u < CTX_NB; u++)
+            if (j0 + u <= jhi) acc = step_flush(wrow[j0 + u], ftz_bits(buf[u]), acc);
+    }
+    return acc;
+}
 __global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict__ ctx, float *__restrict__ scores,
                                                                 const float *__restrict__ vcache, int b, int l, int nh, int nkv,
-                                                                int hd, int cap, int key_lo, int s, int own0, int window) {
+                                                                int hd, int cap, int key_lo, int s, int own0, int window,
+                                                                const int *__restrict__ pos_dev) {
+    attn_geometry(pos_dev, l, cap, window, key_lo, s, own0);
     extern __shared__ float wrow[]; // [s] weights of this row
     __shared__ unsigned red[4];
     __shared__ float den_s;
@@ -347,6 +538,9 @@ __global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict
     int jlo = 0, jhi = own0 + qi;
     if (jhi > s - 1) jhi = s - 1;
     if (window > 0) { jlo = own0 + qi - window + 1; if (jlo < 0) jlo = 0; }
+    const float *vbase = vcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
+    float cur[CTX_NB], nxt[CTX_NB];
+    if (tid < hd) ctx_load_batch(cur, vbase, hd, tid, jlo, jhi);
     unsigned best = 0u;
     for (int j = tid; j < s; j += 128) best = max(best, order_key(ftz_bits(row[j])));
 #pragma unroll
@@ -378,18 +572,16 @@ __global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict
         row[j] = wgt;
     }
     __syncthreads();
-    const float *vbase = vcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
     for (int d = tid; d < hd; d += 128) {
         float acc = 0.f;
-        int j = jlo;
-        for (; j + 7 <= jhi; j += 8) {
-            float v[8];
-#pragma unroll
-            for (int u = 0; u < 8; u++) v[u] = ftz_bits(vbase[(long long)(j + u) * hd + d]);
-#pragma unroll
-            for (int u = 0; u < 8; u++) acc = step_flush(wrow[j + u], v[u], acc);
+        if (d >= 128) ctx_load_batch(cur, vbase, hd, d, jlo, jhi);
+        for (int j0 = jlo; j0 <= jhi; j0 += 2 * CTX_NB) { // two batches per turn: the buffers swap roles without moves
+            if (j0 + CTX_NB <= jhi) ctx_load_batch(nxt, vbase, hd, d, j0 + CTX_NB, jhi);
+            acc = ctx_walk_batch(cur, wrow, j0, jhi, acc);
+            if (j0 + CTX_NB > jhi) break;
+            if (j0 + 2 * CTX_NB <= jhi) ctx_load_batch(cur, vbase, hd, d, j0 + 2 * CTX_NB, jhi);
+            acc = ctx_walk_batch(nxt, wrow, j0 + CTX_NB, jhi, acc);
         }
-        for (; j <= jhi; j++) acc = step_flush(wrow[j], ftz_bits(vbase[(long long)j * hd + d]), acc);
         ctx[((long long)bb * l + qi) * ((long long)nh * hd) + (long long)h * hd + d] = acc;
     }
 }
@@ -439,7 +631,8 @@ __global__ void embedding_kernel(float *__restrict__ y, const float *__restrict_
 
 // learned positions (an extension: the reference's block always rotates): one plain add
 __global__ void add_positions_kernel(float *__restrict__ x, const float *__restrict__ pos, long long rows, int l, int pos0,
-                                     int width) {
+                                     int width, const int *__restrict__ pos_dev) {
+    if (pos_dev) pos0 = *pos_dev;
     const long long stride = (long long)gridDim.x * blockDim.x, total = rows * width;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const long long t = i / width;
@@ -447,30 +640,51 @@ __global__ void add_positions_kernel(float *__restrict__ x, const float *__restr
     }
 }
 
-// greedy argmax, one CTA per row: strictly greater wins, equal keeps the lower index
-__global__ void argmax_kernel(int *__restrict__ out, const float *__restrict__ logits, int vocab) {
-    __shared__ float bv[256];
-    __shared__ int bi[256];
+// greedy argmax, one CTA per row. The scalar walk starts from element 0, visits the
+// indices ascending and replaces on strictly greater, so its answer is the lowest
+// index among the largest non-NaN values, or 0 when element 0 is a NaN (nothing
+// compares greater than a NaN). "Larger value, then lower index" is associative, so
+// the candidates combine in any order: four loads per thread in flight, shuffles
+// inside a warp, one round through shared memory.
+constexpr int ARGMAX_THREADS = 1024;
+__device__ __forceinline__ void argmax_take(float &best, int &idx, float v, int j) {
+    if (v == v && (idx < 0 || v > best || (v == best && j < idx))) { best = v; idx = j; }
+}
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(int *__restrict__ out, const float *__restrict__ logits, int vocab) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
     const float *p = logits + (long long)blockIdx.x * vocab;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float best = 0.f;
     int idx = -1;
-    for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
-        const float v = p[j];
-        if (v == v && (idx < 0 || v > best)) { best = v; idx = j; } // a NaN is never a candidate, as in the scalar walk
+    for (int j0 = tid; j0 < vocab; j0 += 4 * ARGMAX_THREADS) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) v[u] = (j0 + u * ARGMAX_THREADS < vocab) ? p[j0 + u * ARGMAX_THREADS] : __uint_as_float(0x7FC00000u);
+#pragma unroll
+        for (int u = 0; u < 4; u++) argmax_take(best, idx, v[u], j0 + u * ARGMAX_THREADS);
     }
-    bv[threadIdx.x] = best;
-    bi[threadIdx.x] = idx;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+        const int oi = __shfl_xor_sync(0xFFFFFFFFu, idx, off);
+        if (oi >= 0) argmax_take(best, idx, ov, oi);
+    }
+    if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        // the scalar walk visits indices ascending and replaces on strictly greater;
-        // replay it over each thread's candidate in index order of first occurrence
-        float b0 = p[0];
-        int i0 = 0;
-        for (int t = 0; t < (int)blockDim.x; t++) {
-            if (bi[t] < 0) continue;
-            if (bv[t] > b0 || (bv[t] == b0 && bi[t] < i0)) { b0 = bv[t]; i0 = bi[t]; }
+    if (warp == 0) {
+        best = bv[lane];
+        idx = bi[lane];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, idx, off);
+            if (oi >= 0) argmax_take(best, idx, ov, oi);
         }
-        out[blockIdx.x] = i0;
+        if (lane == 0) {
+            const float first = p[0];
+            out[blockIdx.x] = (first != first || idx < 0) ? 0 : idx;
+        }
     }
 }
 

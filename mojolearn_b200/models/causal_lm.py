@@ -134,8 +134,9 @@ class CausalLM(object):
             raise ValueError("token ids must be (batch, length)")
         return t.contiguous()
 
-    def hidden_device(self, ids, state):
-        """Final-normed hidden states [B*L, d_model] for the ids, advancing the state."""
+    def hidden_device(self, ids, state, position=None):
+        """Final-normed hidden states [B*L, d_model] for the ids, advancing the state. `position`: see
+        TransformerBlock.forward_device."""
         b, l = ids.shape
         dev, st, cfg = self.device, _stream(self.device), self.config
         if state.positions + l > cfg.max_positions:
@@ -146,10 +147,15 @@ class CausalLM(object):
         if self.pos_table is not None:
             if state.positions + l > self.pos_table.shape[0]:
                 raise ValueError("position table of %d rows is too short" % self.pos_table.shape[0])
-            _native.call("b200i_add_positions", dev.index, st, _vp(x), _vp(self.pos_table), b * l, l, state.positions, cfg.d_model)
+            if position is None:
+                _native.call("b200i_add_positions", dev.index, st, _vp(x), _vp(self.pos_table), b * l, l, state.positions,
+                             cfg.d_model)
+            else:
+                _native.call("b200i_add_positions_at", dev.index, st, _vp(x), _vp(self.pos_table), b * l, l, _vp(position),
+                             cfg.d_model)
         h = x.reshape(b, l, cfg.d_model)
         for blk, bs in zip(self.blocks, state.layers):
-            h = blk.forward_device(h, bs)
+            h = blk.forward_device(h, bs, position)
         return norm(h.reshape(b * l, cfg.d_model), self.final_w, self.final_b, cfg.norm_eps, NORM_KINDS[cfg.norm])
 
     def check_ids(self):
@@ -158,12 +164,12 @@ class CausalLM(object):
             self._status.zero_()
             raise ValueError("a token id is outside the embedding table")
 
-    def forward_device(self, ids, state=None, last_only=False):
+    def forward_device(self, ids, state=None, last_only=False, position=None):
         ids = self._ids(ids)
         b, l = ids.shape
         if state is None:
             state = self.allocate_state(b, l)
-        hn = self.hidden_device(ids, state)
+        hn = self.hidden_device(ids, state, position)
         if last_only:
             hn = hn.reshape(b, l, -1)[:, -1, :].contiguous()
             return self.head(hn)
@@ -190,9 +196,14 @@ class CausalLM(object):
                      logits2d.shape[0], logits2d.shape[1])
         return out
 
-    def generate(self, ids, max_new_tokens, greedy=True, state=None, return_logits=False):
+    def decode_session(self, state, logits, graph=True):
+        """A resident greedy decode session over a prefilled state and the logits of its last position."""
+        return DecodeSession(self, state, logits, graph)
+
+    def generate(self, ids, max_new_tokens, greedy=True, state=None, return_logits=False, graph=True):
         """Prefill on `ids` (B, L), then `max_new_tokens` greedy steps; returns (B, L + new) ids. The whole
-        continuation stays on the device: one host read at the end."""
+        continuation stays on the device: one host read at the end. With `graph` the decode step is captured
+        once as a CUDA graph and replayed (same kernels, same bits, no per-launch host cost)."""
         if not greedy:
             raise ValueError("only greedy decoding is spelled")
         host = not isinstance(ids, torch.Tensor)
@@ -202,13 +213,13 @@ class CausalLM(object):
             state = self.allocate_state(b, l + max_new_tokens)
         logits = self.forward_device(t, state, last_only=True)
         out, kept = [t], []
+        session = DecodeSession(self, state, logits, graph)
         for step in range(max_new_tokens):
-            nxt = self.argmax_device(logits).reshape(b, 1)
-            out.append(nxt)
+            out.append(session.next_ids().clone())
             if return_logits:
-                kept.append(logits)
+                kept.append(session.logits.clone())
             if step + 1 < max_new_tokens:
-                logits = self.forward_device(nxt, state, last_only=True)
+                session.step()
         self.check_ids()
         seq = torch.cat(out, dim=1)
         seq = seq.cpu().numpy() if host else seq
@@ -216,3 +227,72 @@ class CausalLM(object):
             stack = torch.stack(kept, dim=1)
             return seq, (stack.cpu().numpy() if host else stack)
         return seq
+
+
+class DecodeSession(object):
+    """Greedy decoding with everything resident on the device (the reference's resident decode session,
+    python/mojolearn/models/causal_lm.py:197-201).
+
+    `next_ids()` is the argmax of the current logits, `step()` feeds it back: embedding, every block, the final
+    norm, the head. The first step runs launch by launch; from the second on the step is captured once as a
+    CUDA graph (the position lives in a device word that the graph itself advances) and replayed, which removes
+    the host cost of its several hundred launches. Kernels and bits are those of `CausalLM.step`."""
+
+    def __init__(self, lm, state, logits, graph=True):
+        self.lm, self.state, self.use_graph = lm, state, bool(graph)
+        self.logits = logits.contiguous()
+        b = self.logits.shape[0]
+        self.ids = torch.empty((b, 1), dtype=torch.int32, device=lm.device)
+        self.position = torch.zeros(1, dtype=torch.int32, device=lm.device)
+        self.graph, self.steps, self._fresh = None, 0, False
+        self.graph_launches, self.replays = 0, 0  # kernels in the captured step; times it was replayed
+
+    def next_ids(self):
+        """(B, 1) int32 on the device: the greedy choice from the current logits."""
+        if not self._fresh:
+            self.ids.copy_(self.lm.argmax_device(self.logits).reshape(-1, 1))
+            self._fresh = True
+        return self.ids
+
+    def _check_room(self):
+        pos, cfg = self.state.positions, self.lm.config
+        if pos + 1 > self.state.max_tokens:
+            raise ValueError("transformer: this call would use %d KV slots and the cache holds %d REFUSED" %
+                             (pos + 1, self.state.max_tokens))
+        if pos + 1 > cfg.max_positions:
+            raise ValueError("absolute position %d is at or beyond max_positions %d" % (pos, cfg.max_positions))
+
+    def _captured_step(self):
+        lm, dev = self.lm, self.lm.device
+        out = lm.forward_device(self.ids, self.state, last_only=True, position=self.position)
+        self.ids.copy_(lm.argmax_device(out).reshape(-1, 1))
+        _native.call("b200i_advance_position", dev.index, _stream(dev), _vp(self.position), 1)
+        return out
+
+    def step(self):
+        """Consume next_ids(); afterwards `logits` are those of the new position."""
+        self.next_ids()
+        self._check_room()
+        if not self.use_graph or self.steps == 0:
+            self.logits = self.lm.forward_device(self.ids, self.state, last_only=True)
+            self._fresh = False
+        else:
+            if self.graph is None:
+                self.position.fill_(self.state.positions)
+                before = [s.cached_tokens for s in self.state.layers]
+                torch.cuda.synchronize(self.lm.device)
+                self.graph = torch.cuda.CUDAGraph()
+                counted = _native.lib().b200i_launch_count()
+                with torch.cuda.graph(self.graph):
+                    self._out = self._captured_step()
+                self.graph_launches = int(_native.lib().b200i_launch_count() - counted)
+                for s, n in zip(self.state.layers, before):  # capturing launched nothing
+                    s.cached_tokens = n
+            self.graph.replay()
+            self.replays += 1
+            for s in self.state.layers:
+                s.cached_tokens += 1
+            self.logits = self._out
+            self._fresh = True  # the graph already wrote the next ids
+        self.steps += 1
+        return self.logits

@@ -83,15 +83,15 @@ def run(args):
     logits = lm.forward_device(ids, state, last_only=True)
     e[1].record()
     steps, timed, toks = args.decode, min(args.timed_steps, args.decode), []
+    session = lm.decode_session(state, logits, graph=not args.no_graph)
     for step in range(steps):
         if step == steps - timed:
             if world > 1:
                 torch.distributed.barrier()
             torch.cuda.synchronize(dev)
             e[2].record()
-        nxt = lm.argmax_device(logits).reshape(args.batch, 1)
-        toks.append(nxt)
-        logits = lm.forward_device(nxt, state, last_only=True)
+        toks.append(session.next_ids().clone())
+        logits = session.step()
     e[3].record()
     torch.cuda.synchronize(dev)
     t = torch.tensor([e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])], device=dev, dtype=torch.float64)
@@ -105,10 +105,13 @@ def run(args):
            "prefill_tokens_per_s": args.batch * args.prompt / (prefill_ms * 1e-3), "timed_steps": timed,
            "config": {"layers": args.layers, "d_model": args.d_model, "heads": args.heads, "mlp": args.mlp, "vocab": args.vocab,
                       "batch": args.batch, "prompt": args.prompt, "decode": args.decode, "weights": args.format,
+                      "decode_step": "launch by launch" if args.no_graph else "CUDA graph replay",
                       "sharding": "output columns over %d ranks, NCCL all-gather" % world if world > 1 else "none"},
            "ids_sha256": hashlib.sha256(seq.tobytes()).hexdigest()[:16],
            "logits_sha256": hashlib.sha256(logits.cpu().numpy().tobytes()).hexdigest()[:16],
-           "gpu_launches": int(_native.lib().b200i_launch_count() - launches0)}
+           # the library counts a captured launch once, at capture, when nothing runs; replays are counted here
+           "gpu_launches": int(_native.lib().b200i_launch_count() - launches0 + (session.replays - 1) * session.graph_launches
+                               if session.replays else _native.lib().b200i_launch_count() - launches0)}
     return out, rank
 
 
@@ -124,6 +127,7 @@ def main():
     ap.add_argument("--decode", type=int, default=256)
     ap.add_argument("--timed-steps", type=int, default=32)
     ap.add_argument("--format", default="int8", choices=["int8", "bfloat16", "float32"])
+    ap.add_argument("--no-graph", action="store_true", help="launch every decode step kernel by kernel")
     args = ap.parse_args()
     out, rank = run(args)
     if rank == 0:

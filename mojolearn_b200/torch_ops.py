@@ -19,7 +19,7 @@ import torch
 from . import _native
 from .linalg import OP_NN, OP_NT, OP_TN, W_BF16, W_F32, W_INT8_EXP, W_INT8_SCALE, leaf_count
 
-PLAN_AUTO, PLAN_FLAT, PLAN_T128, PLAN_T64, PLAN_DECODE, PLAN_T32 = -1, 0, 1, 2, 3, 4
+PLAN_AUTO, PLAN_FLAT, PLAN_T128, PLAN_T64, PLAN_DECODE, PLAN_T32, PLAN_T128X64, PLAN_SKINNY = -1, 0, 1, 2, 3, 4, 5, 6
 
 
 def _check(t, name, dtype):

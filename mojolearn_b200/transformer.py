@@ -201,7 +201,10 @@ class TransformerBlock(object):
         return TransformerState(batch, self.n_kv_heads, int(max_tokens), self.head_dim, self.device)
 
     # -- the block on device tensors: x [B, L, d_model] -> [B, L, d_model]; state is advanced by L
-    def forward_device(self, x, state):
+    def forward_device(self, x, state, position=None):
+        """`position`, when given, is a device int32 word holding the tokens cached before this call: the
+        position-dependent kernels read it instead of taking the host's count as an argument, so the launches
+        can be captured in a CUDA graph and replayed at later positions (the host count still sizes and checks)."""
         b, l, dm = x.shape
         if dm != self.d_model:
             raise ValueError("x has width %d, the block %d" % (dm, self.d_model))
@@ -219,7 +222,11 @@ class TransformerBlock(object):
             half = self.head_dim // 2
             cosv = torch.empty((l, half), dtype=torch.float32, device=dev)
             sinv = torch.empty_like(cosv)
-            _native.call("b200i_rope_table", dev.index, st, _vp(cosv), _vp(sinv), pos0, l, self.head_dim, self.rope_theta)
+            if position is None:
+                _native.call("b200i_rope_table", dev.index, st, _vp(cosv), _vp(sinv), pos0, l, self.head_dim, self.rope_theta)
+            else:
+                _native.call("b200i_rope_table_at", dev.index, st, _vp(cosv), _vp(sinv), _vp(position), l, self.head_dim,
+                             self.rope_theta)
             qr, kr = torch.empty_like(q), torch.empty_like(k)
             _native.call("b200i_rope_apply", dev.index, st, _vp(qr), _vp(q), _vp(cosv), _vp(sinv), m, l, self.n_heads, self.head_dim)
             _native.call("b200i_rope_apply", dev.index, st, _vp(kr), _vp(k), _vp(cosv), _vp(sinv), m, l, self.n_kv_heads,
@@ -227,14 +234,24 @@ class TransformerBlock(object):
         else:
             qr, kr = q, k
         cap = state.max_tokens
-        _native.call("b200i_kv_append", dev.index, st, _vp(state.k), _vp(kr), b, l, self.n_kv_heads, self.head_dim, cap, pos0)
-        _native.call("b200i_kv_append", dev.index, st, _vp(state.v), _vp(v), b, l, self.n_kv_heads, self.head_dim, cap, pos0)
         used = pos0 + l
-        s = used - (max(0, pos0 - (self.window - 1)) if self.window else 0)
-        scores = torch.empty((b * self.n_heads * l * s,), dtype=torch.float32, device=dev)
         ctx = torch.empty((m, self.n_heads * self.head_dim), dtype=torch.float32, device=dev)
-        _native.call("b200i_attention", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
-                     self.n_heads, self.n_kv_heads, self.head_dim, cap, used, self.window)
+        if position is None:
+            _native.call("b200i_kv_append", dev.index, st, _vp(state.k), _vp(kr), b, l, self.n_kv_heads, self.head_dim, cap, pos0)
+            _native.call("b200i_kv_append", dev.index, st, _vp(state.v), _vp(v), b, l, self.n_kv_heads, self.head_dim, cap, pos0)
+            s = used - (max(0, pos0 - (self.window - 1)) if self.window else 0)
+            scores = torch.empty((b * self.n_heads * l * s,), dtype=torch.float32, device=dev)
+            _native.call("b200i_attention", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
+                         self.n_heads, self.n_kv_heads, self.head_dim, cap, used, self.window)
+        else:
+            _native.call("b200i_kv_append_at", dev.index, st, _vp(state.k), _vp(kr), b, l, self.n_kv_heads, self.head_dim, cap,
+                         _vp(position))
+            _native.call("b200i_kv_append_at", dev.index, st, _vp(state.v), _vp(v), b, l, self.n_kv_heads, self.head_dim, cap,
+                         _vp(position))
+            s = min(cap, self.window - 1 + l) if self.window else cap  # the most keys any later position sees
+            scores = torch.empty((b * self.n_heads * l * s,), dtype=torch.float32, device=dev)
+            _native.call("b200i_attention_at", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
+                         self.n_heads, self.n_kv_heads, self.head_dim, cap, _vp(position), self.window)
         del scores
         r1 = add(x2, self.o(ctx))
         n2 = norm(r1, self.norm2_w, self.norm2_b, self.norm_eps, self.norm_kind)

@@ -1,5 +1,6 @@
 """GPU parity for the decoder path: the block's seams and the CausalLM against
 the CPU oracle, bit for bit, and against the verify table's transformer cells."""
+import ctypes
 import json
 import os
 
@@ -13,7 +14,7 @@ import oracle
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
-from mojolearn_b200 import lowbit  # noqa: E402
+from mojolearn_b200 import _native, lowbit  # noqa: E402
 from mojolearn_b200.models import CausalLM, CausalLMConfig  # noqa: E402
 from mojolearn_b200.transformer import TransformerBlock  # noqa: E402
 
@@ -57,9 +58,11 @@ def test_causal_lm_matches_the_oracle_and_decode_equals_prefill(opts):
     first = lm.forward(ids[:, :5], state)
     rest = [lm.step(ids[:, t], state) for t in range(5, 9)]
     assert np.concatenate([first] + [r[:, None, :] for r in rest], axis=1).tobytes() == want.tobytes()
-    seq, logits = lm.generate(ids[:, :4], 6, return_logits=True)
+    seq, logits = lm.generate(ids[:, :4], 6, return_logits=True)  # steps 2.. replay the captured graph
     rseq, rlogits = ref.generate(ids[:, :4], 6)
     assert seq.tolist() == rseq.tolist() and logits.tobytes() == rlogits.tobytes()
+    seq2, logits2 = lm.generate(ids[:, :4], 6, return_logits=True, graph=False)
+    assert seq2.tolist() == rseq.tolist() and logits2.tobytes() == rlogits.tobytes()
     with pytest.raises(ValueError):
         lm.forward(np.full((1, 2), cfg.vocab, np.int32))
 
@@ -97,3 +100,43 @@ def test_config5_shape_int8_weights_reduced():
     seq, logits = CausalLM(cfg, packed).generate(ids, 3, return_logits=True)
     rseq, rlogits = decoder_ref.OracleLM(cfg, mat).generate(ids, 3)
     assert logits.tobytes() == rlogits.tobytes() and seq.tolist() == rseq.tolist()
+
+
+def test_argmax_kernel_ties_nans_and_wide_rows():
+    rng = np.random.default_rng(5)
+    logits = rng.standard_normal((7, 50304)).astype(np.float32)
+    logits[1, 40000] = logits[1, 123] = logits[1].max() + 1.0      # a tie: the lower index wins
+    logits[2, 0] = np.nan                                          # a NaN at element 0 is never displaced
+    logits[3, 5:9000] = np.nan                                     # NaNs elsewhere are never candidates
+    logits[4, :] = 0.0
+    logits[4, 77] = -0.0                                           # signed zeros compare equal
+    logits[5, :] = -np.inf
+    logits[6, -1] = np.inf
+    small = np.array([[1.0, 3.0, 3.0, -1.0], [0.0, -0.0, 0.0, 0.0], [np.nan, 2.0, 1.0, 2.0]], dtype=np.float32)
+    for arr in (logits, small, logits[:, :1], logits[:, :1025]):
+        arr = np.ascontiguousarray(arr)
+        d = torch.from_numpy(arr).cuda()
+        out = torch.empty(arr.shape[0], dtype=torch.int32, device="cuda")
+        _native.call("b200i_argmax", 0, None, ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(d.data_ptr()), arr.shape[0], arr.shape[1])
+        torch.cuda.synchronize()
+        assert out.cpu().numpy().tolist() == oracle.argmax(arr).tolist()
+
+
+def test_norm_kernel_row_widths_and_kinds():
+    """Rows staged in shared memory: vector and scalar widths, one and many rows per launch, the three kinds,
+    rows that fail the admission test of the sum of squares."""
+    from mojolearn_b200 import transformer
+    rng = np.random.default_rng(6)
+    for rows, dm in [(1, 4), (3, 37), (32, 2048), (5, 1000), (1500, 96), (2, 8192)]:
+        x = rng.standard_normal((rows, dm)).astype(np.float32)
+        x[0, :: 5] *= np.float32(2.0 ** -70)  # below the admission threshold: the flushed chain
+        if rows > 1:
+            x[1, 0] = np.float32(1e-41)
+        w = rng.standard_normal(dm).astype(np.float32)
+        bias = rng.standard_normal(dm).astype(np.float32)
+        for name, b in (("rmsnorm", None), ("layernorm", bias), ("layernorm", None), ("rmsnorm_offset", None)):
+            kind = transformer.NORM_KINDS[name]
+            want = oracle.norm(x, w, b, 1e-6, name)
+            got = transformer.norm(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(),
+                                   None if b is None else torch.from_numpy(b).cuda(), 1e-6, kind)
+            assert got.cpu().numpy().tobytes() == want.tobytes(), (rows, dm, kind)

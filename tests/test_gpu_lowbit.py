@@ -91,6 +91,7 @@ def test_config3_full_size(m):
     fits = _native.lib().b200i_decode_plan_fits(m, n, k, oracle.OP_NT, linalg.W_INT8_EXP)
     assert fits == (1 if m <= 8 else 0)
     plans = [(torch_ops.PLAN_T128, 0), (torch_ops.PLAN_T64, 4)] + ([(torch_ops.PLAN_DECODE, 0)] if fits else [])
+    plans += [(torch_ops.PLAN_SKINNY, 0), (torch_ops.PLAN_SKINNY, 2)] if m <= 32 else []
     for plan, groups in plans:
         alt = torch_ops.product(dx, dcodes, dexps, linalg.W_INT8_EXP, oracle.OP_NT, plan=plan, group_leaves=groups)
         assert torch.equal(alt.view(torch.int32), got8.view(torch.int32)), (plan, groups)
@@ -129,6 +130,53 @@ def test_decode_plan_edges():
         got = torch_ops.product(dx, torch.from_numpy(wb).cuda(), None, linalg.W_BF16, oracle.OP_NT, plan=plan)
         assert got.cpu().numpy().tobytes() == wantb.tobytes(), plan
     assert _native.lib().b200i_decode_status(-1) == 0
+
+
+def test_skinny_plan_every_storage_kind():
+    """The skinny plan (up to 32 activation rows): ragged row and column counts,
+    one to many leaves per group, a short last leaf, every storage kind, and
+    operands that force the flushed path."""
+    rng = np.random.default_rng(11)
+    shapes = [(5, 300, 512, 0), (8, 1030, 4096, 8), (9, 520, 2048, 4), (16, 1000, 1024, 0), (17, 700, 4096, 16),
+              (32, 513, 2048, 2), (32, 256, 64, 0), (12, 99, 4096 + 128, 8), (3, 2050, 768, 2), (1, 40, 16, 0)]
+    for (m, n, k, gl) in shapes:
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        codes = rng.integers(-127, 128, (n, k)).astype(np.int8)
+        exps = rng.integers(-9, -5, n).astype(np.int32)
+        scales = rng.uniform(0.001, 0.02, n).astype(np.float32)
+        wb = oracle.to_bf16((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+        wf = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+        dx = torch.from_numpy(x).cuda()
+        cases = [(wf, None, linalg.W_F32, wf), (wb, None, linalg.W_BF16, oracle.from_bf16(wb)),
+                 (codes, exps, linalg.W_INT8_EXP, oracle.dequantize_int8(codes, exps)),
+                 (codes, scales, linalg.W_INT8_SCALE, oracle.dequantize_int8_scaled(codes, scales))]
+        for w, sc, kind, wref in cases:
+            want = oracle.gemm_rows(x, wref, oracle.OP_NT)
+            got = torch_ops.product(dx, torch.from_numpy(w).cuda(), None if sc is None else torch.from_numpy(sc).cuda(), kind,
+                                    oracle.OP_NT, plan=torch_ops.PLAN_SKINNY, group_leaves=gl)
+            assert got.cpu().numpy().tobytes() == want.tobytes(), (m, n, k, gl, kind)
+    m, n, k = 12, 200, 512
+    x = (rng.standard_normal((m, k)) * 2.0 ** -62).astype(np.float32)
+    x[0, ::9] = np.float32(3e-42)
+    codes = rng.integers(-127, 128, (n, k)).astype(np.int8)
+    exps = rng.integers(-70, -58, n).astype(np.int32)
+    exps[:4] = [-140, 127, 121, -127]
+    want = oracle.nan_canon(oracle.gemm(x, oracle.dequantize_int8(codes, exps), oracle.OP_NT))
+    dx = torch.from_numpy(x).cuda()
+    for plan in (torch_ops.PLAN_SKINNY, torch_ops.PLAN_AUTO):
+        got = torch_ops.product(dx, torch.from_numpy(codes).cuda(), torch.from_numpy(exps).cuda(), linalg.W_INT8_EXP, oracle.OP_NT, plan=plan)
+        assert got.cpu().numpy().tobytes() == want.tobytes(), plan
+    wb = oracle.to_bf16((rng.standard_normal((n, k)) * 2.0 ** -64).astype(np.float32))
+    wantb = oracle.gemm(x, oracle.from_bf16(wb), oracle.OP_NT)
+    got = torch_ops.product(dx, torch.from_numpy(wb).cuda(), None, linalg.W_BF16, oracle.OP_NT, plan=torch_ops.PLAN_SKINNY)
+    assert got.cpu().numpy().tobytes() == wantb.tobytes()
+    # refusals: more than 32 rows, k not a multiple of 16, another op
+    with pytest.raises(_native.NativeError):
+        torch_ops.product(torch.zeros(33, 64).cuda(), torch.zeros(8, 64).cuda(), None, linalg.W_F32, oracle.OP_NT, plan=torch_ops.PLAN_SKINNY)
+    with pytest.raises(_native.NativeError):
+        torch_ops.product(torch.zeros(4, 40).cuda(), torch.zeros(8, 40).cuda(), None, linalg.W_F32, oracle.OP_NT, plan=torch_ops.PLAN_SKINNY)
+    with pytest.raises(_native.NativeError):
+        torch_ops.product(torch.zeros(4, 64).cuda(), torch.zeros(64, 8).cuda(), None, linalg.W_F32, oracle.OP_NN, plan=torch_ops.PLAN_SKINNY)
 
 
 def test_int8_product_profile():
