@@ -158,21 +158,25 @@ int64_t b200i_norm(int64_t device, void *stream, float *out, const float *x, con
 /* cos and sin [l, head_dim/2] for absolute positions pos0 .. pos0+l-1 (S6-S8); positions stay below 8192. */
 int64_t b200i_rope_table(int64_t device, void *stream, float *cosv, float *sinv, int64_t pos0, int64_t l, int64_t head_dim,
                          double theta, char *err, int64_t err_cap);
-/* out[rows, n_heads*head_dim] = rotate(src) with the table of the call's l positions (S9-S10); not in place. */
+/* out[rows, n_heads*head_dim] = rotate(src) with the table of the call's l positions (S9-S10); not in place.
+ * `src_ld` is the row pitch of src in floats (0 = contiguous rows): the projection may be a column block of
+ * one fused q|k|v product. */
 int64_t b200i_rope_apply(int64_t device, void *stream, float *out, const float *src, const float *cosv, const float *sinv,
-                         int64_t rows, int64_t l, int64_t n_heads, int64_t head_dim, char *err, int64_t err_cap);
-/* cache[b, n_kv, cap, head_dim] <- src[b*l, n_kv*head_dim] at positions pos0 .. pos0+l-1 (a copy). */
+                         int64_t rows, int64_t l, int64_t n_heads, int64_t head_dim, int64_t src_ld, char *err, int64_t err_cap);
+/* cache[b, n_kv, cap, head_dim] <- src[b*l, n_kv*head_dim] (row pitch src_ld, 0 = contiguous) at positions
+ * pos0 .. pos0+l-1 (a copy). */
 int64_t b200i_kv_append(int64_t device, void *stream, float *cache, const float *src, int64_t b, int64_t l, int64_t n_kv,
-                        int64_t head_dim, int64_t cap, int64_t pos0, char *err, int64_t err_cap);
+                        int64_t head_dim, int64_t cap, int64_t pos0, int64_t src_ld, char *err, int64_t err_cap);
 /* ctx[b*l, n_heads*head_dim] from rotated queries q[b*l, n_heads*head_dim] and caches holding `used`
  * positions, this call's l included (S11-S19: eager attention, serial key-axis chains). `scores` is
  * scratch of b*n_heads*l*min(used, window or used) floats. head_dim <= 128. */
 int64_t b200i_attention(int64_t device, void *stream, float *ctx, const float *q, const float *kcache, const float *vcache,
                         float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
                         int64_t used, int64_t window, char *err, int64_t err_cap);
-/* kind 0 = silu(gate)*up, 1 = gelu_erf(up), 2 = gelu_tanh(up), 3 = silu(up), 4 / 5 = gelu(gate)*up (S20-S21). */
-int64_t b200i_act_mul(int64_t device, void *stream, float *out, const float *gate, const float *up, int64_t count, int64_t kind,
-                      char *err, int64_t err_cap);
+/* kind 0 = silu(gate)*up, 1 = gelu_erf(up), 2 = gelu_tanh(up), 3 = silu(up), 4 / 5 = gelu(gate)*up (S20-S21).
+ * out is [rows, width] contiguous; gate and up are [rows, width] with row pitch in_ld (0 = contiguous). */
+int64_t b200i_act_mul(int64_t device, void *stream, float *out, const float *gate, const float *up, int64_t rows, int64_t width,
+                      int64_t in_ld, int64_t kind, char *err, int64_t err_cap);
 /* out = ftz(ftz(a) + ftz(b)) (S22, S23); may be in place. */
 int64_t b200i_add(int64_t device, void *stream, float *out, const float *a, const float *b, int64_t count, char *err, int64_t err_cap);
 /* buf[rows, width] += bias[width], one plain add per cell (transformer_oracle.mojo:1344-1372). */
@@ -197,7 +201,7 @@ int64_t b200i_add_positions(int64_t device, void *stream, float *x, const float 
 int64_t b200i_rope_table_at(int64_t device, void *stream, float *cosv, float *sinv, const int32_t *position, int64_t l,
                             int64_t head_dim, double theta, char *err, int64_t err_cap);
 int64_t b200i_kv_append_at(int64_t device, void *stream, float *cache, const float *src, int64_t b, int64_t l, int64_t n_kv,
-                           int64_t head_dim, int64_t cap, const int32_t *position, char *err, int64_t err_cap);
+                           int64_t head_dim, int64_t cap, const int32_t *position, int64_t src_ld, char *err, int64_t err_cap);
 int64_t b200i_attention_at(int64_t device, void *stream, float *ctx, const float *q, const float *kcache, const float *vcache,
                            float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
                            const int32_t *position, int64_t window, char *err, int64_t err_cap);

@@ -534,39 +534,45 @@ int64_t b200i_rope_table_at(int64_t device, void *stream, float *cosv, float *si
 }
 
 int64_t b200i_rope_apply(int64_t device, void *stream, float *out, const float *src, const float *cosv, const float *sinv,
-                         int64_t rows, int64_t l, int64_t n_heads, int64_t head_dim, char *err, int64_t err_cap) {
+                         int64_t rows, int64_t l, int64_t n_heads, int64_t head_dim, int64_t src_ld, char *err, int64_t err_cap) {
     SEAM_PROLOGUE();
     if (rows <= 0 || l <= 0 || n_heads <= 0 || head_dim <= 0 || (head_dim & 1) || !out || !src || out == src)
         return fail(err, err_cap, "rope_apply: bad arguments (the rotation is not in place)");
+    if (src_ld == 0) src_ld = n_heads * head_dim;
+    if (src_ld < n_heads * head_dim) return fail(err, err_cap, "rope_apply: the row pitch is below the row width");
     const long long n = rows * n_heads * head_dim;
-    rope_apply_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(out, src, cosv, sinv, rows, (int)l, (int)n_heads, (int)head_dim);
+    rope_apply_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(out, src, cosv, sinv, rows, (int)l, (int)n_heads, (int)head_dim, src_ld);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
 }
 
 int64_t b200i_kv_append(int64_t device, void *stream, float *cache, const float *src, int64_t b, int64_t l, int64_t n_kv,
-                        int64_t head_dim, int64_t cap, int64_t pos0, char *err, int64_t err_cap) {
+                        int64_t head_dim, int64_t cap, int64_t pos0, int64_t src_ld, char *err, int64_t err_cap) {
     SEAM_PROLOGUE();
-    if (b <= 0 || l <= 0 || n_kv <= 0 || head_dim <= 0 || pos0 < 0 || !cache || !src) return fail(err, err_cap, "kv_append: bad arguments");
+    if (src_ld == 0) src_ld = n_kv * head_dim;
+    if (b <= 0 || l <= 0 || n_kv <= 0 || head_dim <= 0 || pos0 < 0 || !cache || !src || src_ld < n_kv * head_dim)
+        return fail(err, err_cap, "kv_append: bad arguments");
     if (pos0 + l > cap)
         return fail(err, err_cap, "transformer: this call would use %lld KV slots and the cache holds %lld REFUSED", (long long)(pos0 + l),
                     (long long)cap);
     const long long n = b * l * n_kv * head_dim;
     kv_append_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(cache, src, (int)b, (int)l, (int)n_kv, (int)head_dim, (int)cap, (int)pos0,
-                                                                  nullptr);
+                                                                  nullptr, src_ld);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
 }
 
 int64_t b200i_kv_append_at(int64_t device, void *stream, float *cache, const float *src, int64_t b, int64_t l, int64_t n_kv,
-                           int64_t head_dim, int64_t cap, const int32_t *position, char *err, int64_t err_cap) {
+                           int64_t head_dim, int64_t cap, const int32_t *position, int64_t src_ld, char *err, int64_t err_cap) {
     SEAM_PROLOGUE();
-    if (b <= 0 || l <= 0 || n_kv <= 0 || head_dim <= 0 || l > cap || !cache || !src || !position)
+    if (src_ld == 0) src_ld = n_kv * head_dim;
+    if (b <= 0 || l <= 0 || n_kv <= 0 || head_dim <= 0 || l > cap || !cache || !src || !position || src_ld < n_kv * head_dim)
         return fail(err, err_cap, "kv_append: bad arguments");
     const long long n = b * l * n_kv * head_dim;
-    kv_append_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(cache, src, (int)b, (int)l, (int)n_kv, (int)head_dim, (int)cap, 0, position);
+    kv_append_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(cache, src, (int)b, (int)l, (int)n_kv, (int)head_dim, (int)cap, 0, position,
+                                                                  src_ld);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -643,13 +649,15 @@ int64_t b200i_attention_at(int64_t device, void *stream, float *ctx, const float
                             position, err, err_cap);
 }
 
-int64_t b200i_act_mul(int64_t device, void *stream, float *out, const float *gate, const float *up, int64_t count, int64_t kind,
-                      char *err, int64_t err_cap) {
+int64_t b200i_act_mul(int64_t device, void *stream, float *out, const float *gate, const float *up, int64_t rows, int64_t width,
+                      int64_t in_ld, int64_t kind, char *err, int64_t err_cap) {
     SEAM_PROLOGUE();
-    if (count <= 0 || !out || !up || kind < ACT_SWIGLU || kind > ACT_GEGLU_TANH) return fail(err, err_cap, "act_mul: bad arguments");
+    if (in_ld == 0) in_ld = width;
+    if (rows <= 0 || width <= 0 || in_ld < width || !out || !up || kind < ACT_SWIGLU || kind > ACT_GEGLU_TANH)
+        return fail(err, err_cap, "act_mul: bad arguments");
     const bool gated = kind == ACT_SWIGLU || kind == ACT_GEGLU_ERF || kind == ACT_GEGLU_TANH;
     if (gated && !gate) return fail(err, err_cap, "act_mul: a gated MLP needs its gate projection");
-    act_mul_kernel<<<grid_for(count, 256, sm_count(dev)), 256, 0, st>>>(out, gate, up, count, (int)kind);
+    act_mul_kernel<<<grid_for(rows * width, 256, sm_count(dev)), 256, 0, st>>>(out, gate, up, rows, width, in_ld, (int)kind);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;

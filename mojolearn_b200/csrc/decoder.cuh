@@ -228,24 +228,25 @@ __global__ void rope_table_kernel(float *__restrict__ cosv, float *__restrict__ 
     sinv[idx] = ftz_bits(p_sinf(angle));
 }
 
+// `ld` is the row pitch of src in floats (the projections may be column blocks of one fused product).
 __global__ void rope_apply_kernel(float *__restrict__ out, const float *__restrict__ src, const float *__restrict__ cosv,
-                                  const float *__restrict__ sinv, long long m, int l, int n_head, int hd) {
+                                  const float *__restrict__ sinv, long long m, int l, int n_head, int hd, long long ld) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long width = (long long)n_head * hd;
     if (idx >= m * width) return;
-    const long long t = idx / width;
+    const long long t = idx / width, si = t * ld + idx % width;
     const int j = (int)(idx % hd), half = hd / 2, li = (int)(t % l);
     const int ci = j < half ? j : j - half;
-    const float partner = j < half ? -ftz_bits(src[idx + half]) : ftz_bits(src[idx - half]);
+    const float partner = j < half ? -ftz_bits(src[si + half]) : ftz_bits(src[si - half]);
     const float c = ftz_bits(cosv[li * half + ci]), s = ftz_bits(sinv[li * half + ci]);
-    const float pa = ftz_bits(__fmul_rn(ftz_bits(src[idx]), c));
+    const float pa = ftz_bits(__fmul_rn(ftz_bits(src[si]), c));
     const float pb = ftz_bits(__fmul_rn(partner, s));
     out[idx] = ftz_bits(__fadd_rn(pa, pb));
 }
 
-// KV cache append: a copy, not a seam. cache is [b, n_kv, cap, hd]; src is [b*l, n_kv*hd].
+// KV cache append: a copy, not a seam. cache is [b, n_kv, cap, hd]; src is [b*l, n_kv*hd] with row pitch ld.
 __global__ void kv_append_kernel(float *__restrict__ cache, const float *__restrict__ src, int b, int l, int n_kv, int hd,
-                                 int cap, int pos0, const int *__restrict__ pos_dev) {
+                                 int cap, int pos0, const int *__restrict__ pos_dev, long long ld) {
     if (pos_dev) pos0 = *pos_dev;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long total = (long long)b * l * n_kv * hd;
@@ -255,7 +256,7 @@ __global__ void kv_append_kernel(float *__restrict__ cache, const float *__restr
     const long long t = idx / ((long long)hd * n_kv);
     const int bb = (int)(t / l), li = (int)(t % l);
     if (pos0 + li >= cap) return; // the host refuses such a call; a replayed graph must not write past the cache either
-    cache[(((long long)bb * n_kv + kv) * cap + pos0 + li) * hd + d] = src[idx];
+    cache[(((long long)bb * n_kv + kv) * cap + pos0 + li) * hd + d] = src[t * ld + (long long)kv * hd + d];
 }
 
 // ---- a position read on the device ------------------------------------------------------------
@@ -587,17 +588,19 @@ __global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict
 }
 
 // ---- elementwise seams --------------------------------------------------------------------------
+// out is [rows, width] contiguous; gate and up have row pitch ld
 __global__ void act_mul_kernel(float *__restrict__ out, const float *__restrict__ gate, const float *__restrict__ up,
-                               long long count, int kind) {
-    const long long stride = (long long)gridDim.x * blockDim.x;
+                               long long rows, long long width, long long ld, int kind) {
+    const long long stride = (long long)gridDim.x * blockDim.x, count = rows * width;
     const bool gated = kind == ACT_SWIGLU || kind == ACT_GEGLU_ERF || kind == ACT_GEGLU_TANH;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+    for (long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x; o < count; o += stride) {
+        const long long i = (o / width) * ld + o % width;
         const float z = ftz_bits(gated ? gate[i] : up[i]);
         float a;
         if (kind == ACT_SWIGLU || kind == ACT_SILU) a = ftz_bits(p_siluf(z));
         else if (kind == ACT_GELU_TANH || kind == ACT_GEGLU_TANH) a = ftz_bits(p_gelu_tanh(z));
         else a = ftz_bits(p_gelu_erf(z));
-        out[i] = gated ? ftz_bits(__fmul_rn(a, ftz_bits(up[i]))) : a;
+        out[o] = gated ? ftz_bits(__fmul_rn(a, ftz_bits(up[i]))) : a;
     }
 }
 

@@ -95,30 +95,36 @@ __device__ __forceinline__ unsigned skinny_widen(const SkinnyRaw<WK> &r, float (
     return key;
 }
 
-template <int BM, int CPT>
+// BM rows per CTA, split over RSPLIT thread groups of SK_THREADS / RSPLIT threads; a
+// thread owns TR = BM / RSPLIT rows of CPT columns.
+template <int BM, int CPT, int RSPLIT>
 struct SkinnyShape {
-    static constexpr int BN = SK_THREADS * CPT;
-    static constexpr int LQ = CPT < 4 ? CPT : 4;  // columns per shared-memory store vector
-    static constexpr int GROUPS = CPT / LQ;       // row groups a thread loads
+    static constexpr int CT = SK_THREADS / RSPLIT; // column threads
+    static constexpr int TR = BM / RSPLIT;         // rows per thread
+    static constexpr int BN = CT * CPT;
+    static constexpr int LQ = CPT < 4 ? CPT : 4;   // columns per shared-memory store vector
+    static constexpr int ROW_GROUPS = BN / LQ;     // groups of LQ weight rows to stage per window
+    static constexpr int GROUPS = (ROW_GROUPS + SK_THREADS - 1) / SK_THREADS; // per thread
     static constexpr int SMEM_BYTES = 2 * KS * (BM + BN) * 4;
 };
 
-template <int WK, int BM, int CPT, int MINB>
+template <int WK, int BM, int CPT, int RSPLIT, int MINB>
 __global__ void __launch_bounds__(SK_THREADS, MINB) gemm_skinny_kernel(const GemmArgs g) {
-    using S = SkinnyShape<BM, CPT>;
-    constexpr int BN = S::BN, LQ = S::LQ, NG = S::GROUPS, CELLS = BM * CPT;
+    using S = SkinnyShape<BM, CPT, RSPLIT>;
+    constexpr int BN = S::BN, LQ = S::LQ, NG = S::GROUPS, TR = S::TR, CT = S::CT, CELLS = TR * CPT;
     extern __shared__ __align__(16) float sk_smem[];
     float (*As)[KS][BM] = reinterpret_cast<float (*)[KS][BM]>(sk_smem);
     float (*Bs)[KS][BN] = reinterpret_cast<float (*)[KS][BN]>(sk_smem + 2 * KS * BM);
 
     const int tid = threadIdx.x;
+    const int ctid = tid % CT, row0 = (tid / CT) * TR; // this thread's column slot and first row
     const int bn0 = blockIdx.x * BN;
     const int t_first = blockIdx.y * g.group_leaves;
     const int t_end = min(t_first + g.group_leaves, g.leaves);
 
-    unsigned long long acc[BM / 2][CPT];
+    unsigned long long acc[TR / 2][CPT];
 #pragma unroll
-    for (int i = 0; i < BM / 2; i++)
+    for (int i = 0; i < TR / 2; i++)
 #pragma unroll
         for (int c = 0; c < CPT; c++) acc[i][c] = 0ull;
     float stack[FOLD_LEVELS][CELLS];
@@ -136,7 +142,8 @@ __global__ void __launch_bounds__(SK_THREADS, MINB) gemm_skinny_kernel(const Gem
         for (int gi = 0; gi < NG; gi++)
 #pragma unroll
             for (int r = 0; r < LQ; r++)
-                skinny_load_row<WK>(braw[gi][r], g.b, g.bscale, (long long)bn0 + (long long)(tid + SK_THREADS * gi) * LQ + r, g.n, g.k, k0);
+                if (tid + SK_THREADS * gi < S::ROW_GROUPS)
+                    skinny_load_row<WK>(braw[gi][r], g.b, g.bscale, (long long)bn0 + (long long)(tid + SK_THREADS * gi) * LQ + r, g.n, g.k, k0);
         araw = make_float4(0.f, 0.f, 0.f, 0.f);
         if (a_owner && a_row < g.m && k0 + 4 * a_kq < g.k)
             araw = __ldg(reinterpret_cast<const float4 *>(g.a + (size_t)a_row * g.k + k0 + 4 * a_kq));
@@ -145,6 +152,7 @@ __global__ void __launch_bounds__(SK_THREADS, MINB) gemm_skinny_kernel(const Gem
         stage_key = 0xFFFFFFFFu;
 #pragma unroll
         for (int gi = 0; gi < NG; gi++) {
+            if (tid + SK_THREADS * gi >= S::ROW_GROUPS) break;
             float v[LQ][16];
 #pragma unroll
             for (int r = 0; r < LQ; r++) {
@@ -168,23 +176,23 @@ __global__ void __launch_bounds__(SK_THREADS, MINB) gemm_skinny_kernel(const Gem
     };
 
     // this thread's columns inside the tile: CPT consecutive columns (two halves when CPT is 8)
-    auto col_of = [&](int c) { return CPT == 8 ? (c / 4) * (BN / 2) + tid * 4 + (c % 4) : tid * CPT + c; };
+    auto col_of = [&](int c) { return CPT == 8 ? (c / 4) * (BN / 2) + ctid * 4 + (c % 4) : ctid * CPT + c; };
 
     auto step = [&](int buf, int kk, bool flush) {
         float bv[CPT];
         if (CPT == 8) {
-            const float4 lo = *reinterpret_cast<const float4 *>(&Bs[buf][kk][tid * 4]);
-            const float4 hi = *reinterpret_cast<const float4 *>(&Bs[buf][kk][BN / 2 + tid * 4]);
+            const float4 lo = *reinterpret_cast<const float4 *>(&Bs[buf][kk][ctid * 4]);
+            const float4 hi = *reinterpret_cast<const float4 *>(&Bs[buf][kk][BN / 2 + ctid * 4]);
             bv[0] = lo.x; bv[1] = lo.y; bv[2] = lo.z; bv[3] = lo.w;
             bv[CPT - 4] = hi.x; bv[CPT - 3] = hi.y; bv[CPT - 2] = hi.z; bv[CPT - 1] = hi.w;
         } else if (CPT == 4) {
-            const float4 v = *reinterpret_cast<const float4 *>(&Bs[buf][kk][tid * 4]);
+            const float4 v = *reinterpret_cast<const float4 *>(&Bs[buf][kk][ctid * 4]);
             bv[0] = v.x; bv[1] = v.y; bv[CPT - 2] = v.z; bv[CPT - 1] = v.w;
         } else if (CPT == 2) {
-            const float2 v = *reinterpret_cast<const float2 *>(&Bs[buf][kk][tid * 2]);
+            const float2 v = *reinterpret_cast<const float2 *>(&Bs[buf][kk][ctid * 2]);
             bv[0] = v.x; bv[CPT - 1] = v.y;
         } else {
-            bv[0] = Bs[buf][kk][tid];
+            bv[0] = Bs[buf][kk][ctid];
         }
         unsigned long long b2[CPT];
 #pragma unroll
@@ -193,9 +201,9 @@ __global__ void __launch_bounds__(SK_THREADS, MINB) gemm_skinny_kernel(const Gem
             b2[c] = pack2(b, b);
         }
 #pragma unroll
-        for (int q = 0; q < BM / 4; q++) {
+        for (int q = 0; q < TR / 4; q++) {
             // four activation rows of this k-step: two packed pairs straight out of one 128-bit read
-            ulonglong2 a4 = *reinterpret_cast<const ulonglong2 *>(&As[buf][kk][4 * q]);
+            ulonglong2 a4 = *reinterpret_cast<const ulonglong2 *>(&As[buf][kk][row0 + 4 * q]);
             if (flush) {
                 float x0, x1, x2, x3;
                 unpack2(a4.x, x0, x1);
@@ -218,7 +226,7 @@ __global__ void __launch_bounds__(SK_THREADS, MINB) gemm_skinny_kernel(const Gem
     // cell index of (row pair i, half h, column c): level-major fold walks all cells
     auto unpack_cells = [&](float (&v)[CELLS], bool clear_acc) {
 #pragma unroll
-        for (int i = 0; i < BM / 2; i++)
+        for (int i = 0; i < TR / 2; i++)
 #pragma unroll
             for (int c = 0; c < CPT; c++) {
                 float v0, v1;
@@ -288,12 +296,12 @@ __global__ void __launch_bounds__(SK_THREADS, MINB) gemm_skinny_kernel(const Gem
             }
     }
 #pragma unroll
-    for (int i = 0; i < BM; i++) {
-        if (i >= g.m) break;
+    for (int i = 0; i < TR; i++) {
+        if (row0 + i >= g.m) break;
 #pragma unroll
         for (int c = 0; c < CPT; c++) {
             const int col = bn0 + col_of(c);
-            if (col < g.n) out[(size_t)i * g.n + col] = nan_canon(ftz_hw(v[i * CPT + c]));
+            if (col < g.n) out[(size_t)(row0 + i) * g.n + col] = nan_canon(ftz_hw(v[i * CPT + c]));
         }
     }
 }
@@ -305,18 +313,18 @@ inline bool skinny_plan_fits(long long m, long long n, long long k, int op) {
     return true;
 }
 
-template <int WK, int BM, int CPT, int MINB>
+template <int WK, int BM, int CPT, int RSPLIT, int MINB>
 inline void launch_skinny_cfg(const GemmArgs &g, int groups, cudaStream_t st) {
-    using S = SkinnyShape<BM, CPT>;
+    using S = SkinnyShape<BM, CPT, RSPLIT>;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaFuncSetAttribute(gemm_skinny_kernel<WK, BM, CPT, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_skinny_kernel<WK, BM, CPT, RSPLIT, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
         configured[dev] = true;
     }
     dim3 grid((unsigned)((g.n + S::BN - 1) / S::BN), (unsigned)groups);
-    gemm_skinny_kernel<WK, BM, CPT, MINB><<<grid, SK_THREADS, S::SMEM_BYTES, st>>>(g);
+    gemm_skinny_kernel<WK, BM, CPT, RSPLIT, MINB><<<grid, SK_THREADS, S::SMEM_BYTES, st>>>(g);
 }
 
 // columns per thread for the row count (8, 16 or 32 rows of accumulators), and CTAs per SM
@@ -329,6 +337,9 @@ inline void launch_skinny_cfg(const GemmArgs &g, int groups, cudaStream_t st) {
 #ifndef B200I_SK_CPT32
 #define B200I_SK_CPT32 2
 #endif
+#ifndef B200I_SK_RSPLIT32
+#define B200I_SK_RSPLIT32 1
+#endif
 #ifndef B200I_SK_MINB8
 #define B200I_SK_MINB8 5
 #endif
@@ -338,14 +349,14 @@ inline void launch_skinny_cfg(const GemmArgs &g, int groups, cudaStream_t st) {
 #ifndef B200I_SK_MINB32
 #define B200I_SK_MINB32 3
 #endif
-inline int skinny_bn(int m) { return SK_THREADS * (m <= 8 ? B200I_SK_CPT8 : (m <= 16 ? B200I_SK_CPT16 : B200I_SK_CPT32)); }
+inline int skinny_bn(int m) { return m <= 8 ? SK_THREADS * B200I_SK_CPT8 : (m <= 16 ? SK_THREADS * B200I_SK_CPT16 : SK_THREADS / B200I_SK_RSPLIT32 * B200I_SK_CPT32); }
 inline int skinny_per_sm(int m) { return m <= 8 ? B200I_SK_MINB8 : (m <= 16 ? B200I_SK_MINB16 : B200I_SK_MINB32); }
 
 template <int WK>
 inline void launch_skinny_wk(const GemmArgs &g, int groups, cudaStream_t st) {
-    if (g.m <= 8) launch_skinny_cfg<WK, 8, B200I_SK_CPT8, B200I_SK_MINB8>(g, groups, st);
-    else if (g.m <= 16) launch_skinny_cfg<WK, 16, B200I_SK_CPT16, B200I_SK_MINB16>(g, groups, st);
-    else launch_skinny_cfg<WK, 32, B200I_SK_CPT32, B200I_SK_MINB32>(g, groups, st);
+    if (g.m <= 8) launch_skinny_cfg<WK, 8, B200I_SK_CPT8, 1, B200I_SK_MINB8>(g, groups, st);
+    else if (g.m <= 16) launch_skinny_cfg<WK, 16, B200I_SK_CPT16, 1, B200I_SK_MINB16>(g, groups, st);
+    else launch_skinny_cfg<WK, 32, B200I_SK_CPT32, B200I_SK_RSPLIT32, B200I_SK_MINB32>(g, groups, st);
 }
 
 inline void launch_skinny(const GemmArgs &g, int groups, cudaStream_t st) {

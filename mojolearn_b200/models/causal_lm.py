@@ -104,7 +104,7 @@ class CausalLM(object):
                                    o_bias=cfg.o_bias, norm=cfg.norm, norm_eps=cfg.norm_eps, norm_bias=cfg.norm_bias, mlp=cfg.mlp,
                                    mlp_bias=cfg.mlp_bias, device=self.device)
             if self.world > 1:
-                for slot in ("q", "k", "v", "o", "gate", "up", "down"):
+                for slot in TransformerBlock.PROJECTIONS:
                     full = getattr(blk, slot)
                     if full is not None:
                         setattr(blk, slot, _ShardedLinear(full, group, self.rank, self.world))

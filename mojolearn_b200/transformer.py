@@ -85,6 +85,22 @@ class Linear(object):
         self.out_features, self.in_features = self.w.shape
         return self
 
+    @classmethod
+    def concat(cls, parts):
+        """One layer whose output columns are those of `parts` side by side (weight rows stacked), or None when
+        the parts differ in storage kind, width or in having a bias. Bit-neutral: a product cell reads one
+        weight row, so which launch computes it does not matter."""
+        first = parts[0]
+        if any(type(p) is not Linear or p.kind != first.kind or p.in_features != first.in_features or
+               (p.bias is None) != (first.bias is None) for p in parts):
+            return None
+        self = cls.__new__(cls)
+        self.w, self.kind = torch.cat([p.w for p in parts], dim=0).contiguous(), first.kind
+        self.scale = torch.cat([p.scale for p in parts]).contiguous() if first.scale is not None else None
+        self.bias = torch.cat([p.bias for p in parts]).contiguous() if first.bias is not None else None
+        self.out_features, self.in_features = self.w.shape
+        return self
+
     def shard_rows(self, lo, hi):
         """The same layer restricted to output rows [lo, hi): a bit-neutral shard (a cell reads one weight row)."""
         part = Linear.__new__(Linear)
@@ -196,6 +212,16 @@ class TransformerBlock(object):
         if self.n_heads % self.n_kv_heads or self.head_dim % 2:
             raise ValueError("n_heads must be a multiple of n_kv_heads and head_dim even")
         self.inter = self.up.out_features
+        # q|k|v and gate|up as one product each: fewer, wider launches, the same cells
+        self.widths = (self.q.out_features, self.k.out_features, self.v.out_features)
+        self.qkv = Linear.concat([self.q, self.k, self.v])
+        if self.qkv is not None:
+            self.q = self.k = self.v = None
+        self.gateup = Linear.concat([self.gate, self.up]) if self.gated else None
+        if self.gateup is not None:
+            self.gate = self.up = None
+
+    PROJECTIONS = ("qkv", "q", "k", "v", "o", "gateup", "gate", "up", "down")
 
     def allocate_state(self, batch, max_tokens):
         return TransformerState(batch, self.n_kv_heads, int(max_tokens), self.head_dim, self.device)
@@ -217,7 +243,12 @@ class TransformerBlock(object):
         dev, st = x.device, _stream(x.device)
         x2 = x.reshape(m, dm).contiguous()
         n1 = norm(x2, self.norm1_w, self.norm1_b, self.norm_eps, self.norm_kind)
-        q, k, v = self.q(n1), self.k(n1), self.v(n1)
+        if self.qkv is not None:
+            fused = self.qkv(n1)
+            wq, wk, wv = self.widths
+            q, k, v, ld = fused[:, :wq], fused[:, wq:wq + wk], fused[:, wq + wk:], fused.shape[1]
+        else:
+            q, k, v, ld = self.q(n1), self.k(n1), self.v(n1), 0
         if self.rope:
             half = self.head_dim // 2
             cosv = torch.empty((l, half), dtype=torch.float32, device=dev)
@@ -227,27 +258,29 @@ class TransformerBlock(object):
             else:
                 _native.call("b200i_rope_table_at", dev.index, st, _vp(cosv), _vp(sinv), _vp(position), l, self.head_dim,
                              self.rope_theta)
-            qr, kr = torch.empty_like(q), torch.empty_like(k)
-            _native.call("b200i_rope_apply", dev.index, st, _vp(qr), _vp(q), _vp(cosv), _vp(sinv), m, l, self.n_heads, self.head_dim)
+            qr = torch.empty(q.shape, dtype=torch.float32, device=dev)
+            kr = torch.empty(k.shape, dtype=torch.float32, device=dev)
+            _native.call("b200i_rope_apply", dev.index, st, _vp(qr), _vp(q), _vp(cosv), _vp(sinv), m, l, self.n_heads, self.head_dim,
+                         ld)
             _native.call("b200i_rope_apply", dev.index, st, _vp(kr), _vp(k), _vp(cosv), _vp(sinv), m, l, self.n_kv_heads,
-                         self.head_dim)
+                         self.head_dim, ld)
         else:
-            qr, kr = q, k
+            qr, kr = q.contiguous(), k.contiguous()
         cap = state.max_tokens
         used = pos0 + l
         ctx = torch.empty((m, self.n_heads * self.head_dim), dtype=torch.float32, device=dev)
         if position is None:
-            _native.call("b200i_kv_append", dev.index, st, _vp(state.k), _vp(kr), b, l, self.n_kv_heads, self.head_dim, cap, pos0)
-            _native.call("b200i_kv_append", dev.index, st, _vp(state.v), _vp(v), b, l, self.n_kv_heads, self.head_dim, cap, pos0)
+            _native.call("b200i_kv_append", dev.index, st, _vp(state.k), _vp(kr), b, l, self.n_kv_heads, self.head_dim, cap, pos0, 0)
+            _native.call("b200i_kv_append", dev.index, st, _vp(state.v), _vp(v), b, l, self.n_kv_heads, self.head_dim, cap, pos0, ld)
             s = used - (max(0, pos0 - (self.window - 1)) if self.window else 0)
             scores = torch.empty((b * self.n_heads * l * s,), dtype=torch.float32, device=dev)
             _native.call("b200i_attention", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
                          self.n_heads, self.n_kv_heads, self.head_dim, cap, used, self.window)
         else:
             _native.call("b200i_kv_append_at", dev.index, st, _vp(state.k), _vp(kr), b, l, self.n_kv_heads, self.head_dim, cap,
-                         _vp(position))
+                         _vp(position), 0)
             _native.call("b200i_kv_append_at", dev.index, st, _vp(state.v), _vp(v), b, l, self.n_kv_heads, self.head_dim, cap,
-                         _vp(position))
+                         _vp(position), ld)
             s = min(cap, self.window - 1 + l) if self.window else cap  # the most keys any later position sees
             scores = torch.empty((b * self.n_heads * l * s,), dtype=torch.float32, device=dev)
             _native.call("b200i_attention_at", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
@@ -255,10 +288,14 @@ class TransformerBlock(object):
         del scores
         r1 = add(x2, self.o(ctx))
         n2 = norm(r1, self.norm2_w, self.norm2_b, self.norm_eps, self.norm_kind)
-        up = self.up(n2)
-        gate = self.gate(n2) if self.gated else None
-        act = torch.empty_like(up)
-        _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(gate), _vp(up), up.numel(), self.mlp_kind)
+        if self.gateup is not None:
+            fused = self.gateup(n2)
+            gate, up, gld = fused[:, :self.inter], fused[:, self.inter:], fused.shape[1]
+        else:
+            up, gld = self.up(n2), 0
+            gate = self.gate(n2) if self.gated else None
+        act = torch.empty((m, self.inter), dtype=torch.float32, device=dev)
+        _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(gate), _vp(up), m, self.inter, gld, self.mlp_kind)
         y = add(r1, self.down(act))
         state.cached_tokens = used
         return y.reshape(b, l, dm)
