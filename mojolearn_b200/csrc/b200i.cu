@@ -583,12 +583,20 @@ static int64_t attention_launch(int dev, cudaStream_t st, float *ctx, const floa
                                 float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
                                 int key_lo, int s, int own0, int s_grid, int64_t window, const int32_t *position, char *err,
                                 int64_t err_cap) {
-    (void)dev;
     if (l <= ATT_SMALL_Q) {
         dim3 gs((unsigned)((s_grid + 127) / 128), (unsigned)(b * n_heads));
-#define SCORES_SMALL(LQ)                                                                                                              \
-    attn_scores_small_kernel<LQ><<<gs, 128, 0, st>>>(scores, q, kcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, \
-                                                     key_lo, s, own0, (int)window, position)
+#define SCORES_SMALL(LQ)                                                                                                          \
+    do {                                                                                                                          \
+        static bool configured[64] = {};                                                                                          \
+        if (dev >= 0 && dev < 64 && !configured[dev]) {                                                                           \
+            CUDA_TRY(cudaFuncSetAttribute(attn_scores_small_kernel<LQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
+                                          attn_scores_small_smem<LQ>()));                                                         \
+            configured[dev] = true;                                                                                               \
+        }                                                                                                                         \
+        attn_scores_small_kernel<LQ><<<gs, 128, attn_scores_small_smem<LQ>(), st>>>(                                              \
+            scores, q, kcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, key_lo, s, own0, (int)window,    \
+            position);                                                                                                            \
+    } while (0)
         if (l == 1) SCORES_SMALL(1);
         else if (l == 2) SCORES_SMALL(2);
         else if (l <= 4) SCORES_SMALL(4);
@@ -600,8 +608,15 @@ static int64_t attention_launch(int dev, cudaStream_t st, float *ctx, const floa
                                                  own0, (int)window, position);
     }
     if (l <= ATT_SMALL_Q && (size_t)s_grid * sizeof(float) <= 40 * 1024) {
-        attn_context_row_kernel<<<(unsigned)(b * n_heads * l), 128, (size_t)s_grid * sizeof(float), st>>>(
-            ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, key_lo, s, own0, (int)window, position);
+        static bool configured[64] = {};
+        if (dev >= 0 && dev < 64 && !configured[dev]) {
+            CUDA_TRY(cudaFuncSetAttribute(attn_context_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)attn_context_row_smem(40 * 1024 / 4, K_LEAF_MIN)));
+            configured[dev] = true;
+        }
+        attn_context_row_kernel<<<(unsigned)(b * n_heads * l), 128, attn_context_row_smem(s_grid, (int)head_dim), st>>>(
+            ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, key_lo, s, own0, (int)window, position,
+            s_grid);
     } else {
         dim3 g2((unsigned)((l + CTX_ROWS - 1) / CTX_ROWS), (unsigned)(b * n_heads));
         attn_context_kernel<<<g2, 32 * CTX_ROWS, (size_t)CTX_KT * head_dim * sizeof(float), st>>>(

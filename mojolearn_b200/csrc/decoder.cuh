@@ -19,6 +19,7 @@
 // 128-byte row segments, one warp per row or one thread per element, grids sized
 // from the row count.
 #pragma once
+#include "decode.cuh" // mbarrier and bulk-copy primitives, the status word of the bounded waits
 #include "seams_math.cuh"
 
 namespace b200i {
@@ -341,13 +342,44 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(float *__restrict__ sc
     }
 }
 
+// ---- asynchronous copies into shared memory (cp.async): no register staging, so the bytes a
+// warp keeps in flight are bounded by shared memory, not by registers.
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void *smem, const void *gmem) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// `count` floats, contiguous on both sides, by the threads t, t + nthreads, ...; head_dim is
+// even, so every row starts on 8 bytes, and on 16 when head_dim is a multiple of 4
+__device__ __forceinline__ void cp_async_floats(float *dst, const float *src, int count, bool vec16, int t, int nthreads) {
+    if (vec16) {
+        for (int c = t * 4; c < count; c += nthreads * 4) cp_async16(dst + c, src + c);
+    } else {
+        for (int c = t * 2; c < count; c += nthreads * 2) cp_async8(dst + c, src + c);
+    }
+}
+__device__ __forceinline__ unsigned key_of4(float4 v) {
+    return min(min(admit_key(v.x), admit_key(v.y)), min(admit_key(v.z), admit_key(v.w)));
+}
+
 // The same scores for a handful of query rows (a decode step): one lane per key, one
-// serial chain per (query, key) over head_dim, keys staged through shared memory so
-// the cache rows are read in 128-byte segments. LQ is the query-row count rounded up
-// to a power of two, a template parameter so that absent rows cost no issue slots.
-// While every staged 32-wide window of keys and the query rows pass the product's
-// admission test, the chain runs the bare fma (exactly the flushed step there).
-constexpr int ATT_SMALL_Q = 8;
+// serial chain per (query, key) over head_dim. A warp copies the cache rows of its 32
+// keys (16 KB at head_dim 128) straight into padded shared memory with cp.async, all
+// of them in flight at once, then lane j walks row j with 128-bit reads (the padding
+// makes them conflict-free). LQ is the query-row count rounded up to a power of two,
+// a template parameter so that absent rows cost no issue slots. The chain first runs
+// the bare fma while folding the admission key of what it reads; a lane whose row (or
+// the query) fails the product's admission test walks its chain again with the
+// flushed step, which is the contract's spelling for any operands.
+constexpr int ATT_SMALL_Q = 8, ATT_KT_PITCH = K_LEAF_MIN + 4;
+template <int LQ>
+constexpr int attn_scores_small_smem() { return (LQ * K_LEAF_MIN + 4 * 32 * ATT_KT_PITCH) * (int)sizeof(float); }
 template <int LQ>
 __global__ void __launch_bounds__(128) attn_scores_small_kernel(float *__restrict__ scores, const float *__restrict__ q,
                                                                 const float *__restrict__ kcache, int b, int l, int nh, int nkv,
@@ -355,12 +387,35 @@ __global__ void __launch_bounds__(128) attn_scores_small_kernel(float *__restric
                                                                 const int *__restrict__ pos_dev) {
     attn_geometry(pos_dev, l, cap, window, key_lo, s, own0);
     if ((int)blockIdx.x * 128 >= s) return;
-    const float scale = ftz_bits(p_rsqrtf((float)hd));
-    __shared__ float qs[LQ][K_LEAF_MIN];
-    __shared__ float kt[4][32][33];
+    extern __shared__ __align__(16) float att_smem[];
+    float (*qs)[K_LEAF_MIN] = reinterpret_cast<float (*)[K_LEAF_MIN]>(att_smem);
     const int bh = blockIdx.y, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float (*kt)[ATT_KT_PITCH] = reinterpret_cast<float (*)[ATT_KT_PITCH]>(att_smem + LQ * K_LEAF_MIN) + warp * 32;
     const int j0 = blockIdx.x * 128 + warp * 32;
+    const bool vec16 = (hd % 4) == 0;
+    const float *kbase = kcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
+    const int rows = min(32, s - j0); // keys of this warp that exist (uniform across the warp; may be <= 0)
+    if (vec16) {
+        // one instruction per cache row: lane t moves the 16 bytes at float 4t of the row
+        const float *src = kbase + (long long)j0 * hd + lane * 4;
+        float *dst = &kt[0][lane * 4];
+        if (lane * 4 < hd) {
+            if (rows == 32) {
+#pragma unroll
+                for (int r = 0; r < 32; r++) cp_async16(dst + r * ATT_KT_PITCH, src + (long long)r * hd);
+            } else {
+                for (int r = 0; r < rows; r++) cp_async16(dst + r * ATT_KT_PITCH, src + (long long)r * hd);
+            }
+        }
+    } else {
+        for (int r = 0; r < rows; r++) cp_async_floats(&kt[r][0], kbase + (long long)(j0 + r) * hd, hd, false, lane, 32);
+    }
+    for (int r = max(rows, 0); r < 32; r++)
+        for (int c = lane; c < hd; c += 32) kt[r][c] = 0.f;
+    cp_async_commit();
+    __shared__ float scale_s;
+    if (threadIdx.x == 0) scale_s = ftz_bits(p_rsqrtf((float)hd)); // a pure function of head_dim: one thread spells it
     const long long qw = (long long)nh * hd;
     unsigned qkey = 0xFFFFFFFFu;
     for (int idx = threadIdx.x; idx < LQ * hd; idx += 128) {
@@ -369,41 +424,40 @@ __global__ void __launch_bounds__(128) attn_scores_small_kernel(float *__restric
         qkey = min(qkey, admit_key(v));
         qs[i][p] = v;
     }
-    bool clean = __syncthreads_and(qkey >= ADMIT_MIN);
-    const float *kbase = kcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
+    const bool q_ok = __syncthreads_and(qkey >= ADMIT_MIN);
+    const float scale = scale_s;
+    cp_async_wait<0>();
+    __syncwarp();
+    const float *krow = &kt[lane][0];
     float acc[LQ];
-#pragma unroll
-    for (int i = 0; i < LQ; i++) acc[i] = 0.f;
-    for (int p0 = 0; p0 < hd; p0 += 32) {
-        float tmp[32]; // all 32 row segments in flight before any is stored
-#pragma unroll
-        for (int r = 0; r < 32; r++)
-            tmp[r] = (j0 + r < s && p0 + lane < hd) ? kbase[(long long)(j0 + r) * hd + p0 + lane] : 0.f;
+    bool exact = false;
+    if (q_ok && vec16) {
         unsigned kkey = 0xFFFFFFFFu;
 #pragma unroll
-        for (int r = 0; r < 32; r++) {
-            const float v = ftz_bits(tmp[r]);
-            kkey = min(kkey, admit_key(v));
-            kt[warp][r][lane] = v;
-        }
-        __syncwarp();
-        const int pn = min(32, hd - p0);
-        clean = clean && __all_sync(0xFFFFFFFFu, kkey >= ADMIT_MIN) && pn == 32;
-        if (clean) {
+        for (int i = 0; i < LQ; i++) acc[i] = 0.f;
+#pragma unroll 8
+        for (int p = 0; p < hd; p += 4) {
+            const float4 kvv = *reinterpret_cast<const float4 *>(krow + p);
+            kkey = min(kkey, key_of4(kvv));
 #pragma unroll
-            for (int p = 0; p < 32; p++) {
-                const float kvv = kt[warp][lane][p];
-#pragma unroll
-                for (int i = 0; i < LQ; i++) acc[i] = step_bare(qs[i][p0 + p], kvv, acc[i]);
-            }
-        } else {
-            for (int p = 0; p < pn; p++) {
-                const float kvv = kt[warp][lane][p];
-#pragma unroll
-                for (int i = 0; i < LQ; i++) acc[i] = step_flush(qs[i][p0 + p], kvv, acc[i]);
+            for (int i = 0; i < LQ; i++) {
+                const float4 qv = *reinterpret_cast<const float4 *>(&qs[i][p]);
+                acc[i] = step_bare(qv.x, kvv.x, acc[i]);
+                acc[i] = step_bare(qv.y, kvv.y, acc[i]);
+                acc[i] = step_bare(qv.z, kvv.z, acc[i]);
+                acc[i] = step_bare(qv.w, kvv.w, acc[i]);
             }
         }
-        __syncwarp();
+        exact = kkey >= ADMIT_MIN;
+    }
+    if (!exact) {
+#pragma unroll
+        for (int i = 0; i < LQ; i++) acc[i] = 0.f;
+        for (int p = 0; p < hd; p++) {
+            const float kvv = ftz_bits(krow[p]);
+#pragma unroll
+            for (int i = 0; i < LQ; i++) acc[i] = step_flush(qs[i][p], kvv, acc[i]);
+        }
     }
     const int j = j0 + lane;
     if (j >= s) return;
@@ -505,33 +559,29 @@ __global__ void __launch_bounds__(32 * CTX_ROWS) attn_context_kernel(float *__re
 // The same seams with ONE CTA per query row, for a decode step (few query rows, long
 // key axis): the row's weights are built once in shared memory (the denominator by
 // one warp, shuffle rounds), then thread d walks the value chain of feature d down
-// the keys. The cache is read in coalesced rows, a batch of CTX_NB keys per thread
-// always in flight ahead of the chain (the first batch is issued before the softmax
-// phases), so the kernel keeps about 16 KB per CTA outstanding to HBM.
-constexpr int CTX_NB = 32;
-__device__ __forceinline__ void ctx_load_batch(float (&buf)[CTX_NB], const float *__restrict__ vbase, int hd, int d, int j0, int jhi) {
-#pragma unroll
-    for (int u = 0; u < CTX_NB; u++) buf[u] = (j0 + u <= jhi) ? vbase[(long long)(j0 + u) * hd + d] : 0.f;
-}
-__device__ __forceinline__ float ctx_walk_batch(const float (&buf)[CTX_NB], const float *wrow, int j0, int jhi, float acc) {
-    if (j0 + CTX_NB - 1 <= jhi) {
-#pragma unroll
-        for (int u = 0; u < CTX_NB; u++) acc = step_flush(wrow[j0 + u], ftz_bits(buf[u]), acc);
-    } else {
-#pragma unroll
-        for (int u = 0; u < CTX_NB; u++)
-            if (j0 + u <= jhi) acc = step_flush(wrow[j0 + u], ftz_bits(buf[u]), acc);
-    }
-    return acc;
+// the keys. The cache rows of 32 keys at a time are one contiguous block (16 KB at
+// head_dim 128): thread 0 moves each block into a ring of CTX_ST stages with one bulk
+// copy (cp.async.bulk, completion on an mbarrier), the first stages issued before the
+// softmax phases, so a CTA keeps up to 32 KB outstanding to HBM while the chain runs.
+// A head_dim that is not a multiple of 4 leaves rows off the 16-byte grid the bulk
+// copy needs; those caches go through per-thread cp.async instead.
+// Every wait on an mbarrier is bounded; one that runs out sets the status word read by
+// b200i_decode_status (value 3) and the kernel carries on to its end.
+constexpr int CTX_NB = 32, CTX_ST = 3; // three stages and a 4K-key weight row fit four CTAs on an SM
+inline size_t attn_context_row_smem(int s_grid, int hd) {
+    return ((size_t)((s_grid + 3) & ~3) + (size_t)CTX_ST * CTX_NB * hd) * sizeof(float);
 }
 __global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict__ ctx, float *__restrict__ scores,
                                                                 const float *__restrict__ vcache, int b, int l, int nh, int nkv,
                                                                 int hd, int cap, int key_lo, int s, int own0, int window,
-                                                                const int *__restrict__ pos_dev) {
+                                                                const int *__restrict__ pos_dev, int s_grid) {
     attn_geometry(pos_dev, l, cap, window, key_lo, s, own0);
-    extern __shared__ float wrow[]; // [s] weights of this row
+    extern __shared__ __align__(16) float ctx_smem[];
+    float *wrow = ctx_smem;                        // [s] weights of this row
+    float *ring = ctx_smem + ((s_grid + 3) & ~3);  // [CTX_ST][CTX_NB * hd]
     __shared__ unsigned red[4];
     __shared__ float den_s;
+    __shared__ __align__(8) unsigned long long full[CTX_ST];
     const int r = blockIdx.x; // (bh, qi)
     const int bh = r / l, qi = r % l, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -540,8 +590,32 @@ __global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict
     if (jhi > s - 1) jhi = s - 1;
     if (window > 0) { jlo = own0 + qi - window + 1; if (jlo < 0) jlo = 0; }
     const float *vbase = vcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
-    float cur[CTX_NB], nxt[CTX_NB];
-    if (tid < hd) ctx_load_batch(cur, vbase, hd, tid, jlo, jhi);
+    const bool bulk = (hd % 4) == 0;
+    const int nstages = (jhi - jlo + CTX_NB) / CTX_NB;
+    if (bulk && tid == 0) {
+#pragma unroll
+        for (int i = 0; i < CTX_ST; i++) mbar_init(&full[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    auto issue = [&](int k) { // stage k: keys jlo + 32k ..., into slot k % CTX_ST
+        if (bulk) {
+            if (tid == 0 && k < nstages) {
+                const int first = jlo + k * CTX_NB, keys = min(CTX_NB, jhi - first + 1);
+                const unsigned bytes = (unsigned)(keys * hd) * 4u;
+                mbar_expect_tx(&full[k % CTX_ST], bytes);
+                bulk_copy_g2s(ring + (size_t)(k % CTX_ST) * CTX_NB * hd, vbase + (long long)first * hd, bytes, &full[k % CTX_ST]);
+            }
+        } else { // always one commit, so that the groups count stages
+            if (k < nstages) {
+                const int first = jlo + k * CTX_NB, keys = min(CTX_NB, jhi - first + 1);
+                cp_async_floats(ring + (size_t)(k % CTX_ST) * CTX_NB * hd, vbase + (long long)first * hd, keys * hd, false, tid, 128);
+            }
+            cp_async_commit();
+        }
+    };
+#pragma unroll
+    for (int k = 0; k < CTX_ST - 1; k++) issue(k);
     unsigned best = 0u;
     for (int j = tid; j < s; j += 128) best = max(best, order_key(ftz_bits(row[j])));
 #pragma unroll
@@ -572,19 +646,28 @@ __global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict
         wrow[j] = wgt;
         row[j] = wgt;
     }
-    __syncthreads();
-    for (int d = tid; d < hd; d += 128) {
-        float acc = 0.f;
-        if (d >= 128) ctx_load_batch(cur, vbase, hd, d, jlo, jhi);
-        for (int j0 = jlo; j0 <= jhi; j0 += 2 * CTX_NB) { // two batches per turn: the buffers swap roles without moves
-            if (j0 + CTX_NB <= jhi) ctx_load_batch(nxt, vbase, hd, d, j0 + CTX_NB, jhi);
-            acc = ctx_walk_batch(cur, wrow, j0, jhi, acc);
-            if (j0 + CTX_NB > jhi) break;
-            if (j0 + 2 * CTX_NB <= jhi) ctx_load_batch(cur, vbase, hd, d, j0 + 2 * CTX_NB, jhi);
-            acc = ctx_walk_batch(nxt, wrow, j0 + CTX_NB, jhi, acc);
+    float acc = 0.f;
+    for (int k = 0; k < nstages; k++) {
+        issue(k + CTX_ST - 1); // refills the slot the previous turn finished with
+        if (bulk) {
+            if (!mbar_wait(&full[k % CTX_ST], (unsigned)(k / CTX_ST) & 1u) && lane == 0) atomicExch(&g_decode_status, 3);
+        } else {
+            cp_async_wait<CTX_ST - 1>(); // this thread's copies of stage k have landed
         }
-        ctx[((long long)bb * l + qi) * ((long long)nh * hd) + (long long)h * hd + d] = acc;
+        __syncthreads(); // everyone's copies are visible (the first turn also orders the weights above)
+        if (tid < hd) {
+            const float *vs = ring + (size_t)(k % CTX_ST) * CTX_NB * hd + tid;
+            const int first = jlo + k * CTX_NB;
+            if (first + CTX_NB - 1 <= jhi) {
+#pragma unroll
+                for (int u = 0; u < CTX_NB; u++) acc = step_flush(wrow[first + u], ftz_bits(vs[u * hd]), acc);
+            } else {
+                for (int u = 0; first + u <= jhi; u++) acc = step_flush(wrow[first + u], ftz_bits(vs[u * hd]), acc);
+            }
+        }
+        __syncthreads(); // the slot is free for the copy the next turn issues
     }
+    if (tid < hd) ctx[((long long)bb * l + qi) * ((long long)nh * hd) + (long long)h * hd + tid] = acc;
 }
 
 // ---- elementwise seams --------------------------------------------------------------------------
