@@ -77,12 +77,18 @@ int64_t b200i_gemm_w(int64_t device, void *stream, float *c, const float *a, con
  * on-device restatement of the oracle), 1 = 128x128 tiles, 2 = 64x64 tiles,
  * 3 = the row-streaming decode plan (up to 8 rows), 4 = 32x128 tiles, 5 = 128x64 tiles,
  * 6 = the skinny plan (op NT, up to 32 activation rows, k a multiple of 16, 16-byte aligned
- * operands); `group_leaves` = leaves per group (a power of two, 0 = no split). Every plan returns the same bits; the tests
+ * operands), 7 = the packed plan (operands repacked into tile-major panels in the workspace,
+ * then 128x128 tiles fed by bulk copies; needs a 256-byte aligned workspace of
+ * b200i_plan_workspace_bytes); `group_leaves` = leaves per group (a power of two, 0 = no split). Every plan returns the same bits; the tests
  * hold them to that (the reference's launch-invariance gate,
  * gemm/checks/gemm_device_check.mojo:1016). */
 int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale,
                           int64_t wkind, int64_t m, int64_t n, int64_t k, int64_t op, int64_t plan,
                           int64_t group_leaves, void *ws, int64_t ws_bytes, char *err, int64_t err_cap);
+
+/* Scratch a forced plan needs for the shape (group nodes, and the packed plan's panels and flags);
+ * plan -1 is b200i_workspace_bytes. */
+int64_t b200i_plan_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t plan, int64_t group_leaves);
 
 /* 1 when the row-streaming decode plan accepts the shape (op NT, m <= 8, k a
  * multiple of 16 with 128-element leaves, leaf partials and two ring stages

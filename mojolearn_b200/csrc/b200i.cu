@@ -11,6 +11,7 @@
 #include "decoder.cuh"
 #include "gemm_tile.cuh"
 #include "gemm_skinny.cuh"
+#include "gemm_packed.cuh"
 #include "lowbit.cuh"
 
 using namespace b200i;
@@ -69,7 +70,7 @@ int select_device(int64_t device, char *err, int64_t err_cap, int *out) {
 }
 
 // ---- plans -----------------------------------------------------------------------------
-enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4, PLAN_T128X64 = 5, PLAN_SKINNY = 6 };
+enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4, PLAN_T128X64 = 5, PLAN_SKINNY = 6, PLAN_PACKED = 7 };
 
 constexpr int DECODE_PREFER_M = 4; // up to this many rows the weight-streaming decode plan wins; above, the skinny plan
 
@@ -147,6 +148,47 @@ Plan choose_skinny(long long m, long long n, long long k, int sms) {
 
 bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// rows below which packing the operands costs more than the bulk-copy pipeline returns
+constexpr long long PACKED_MIN_EXTENT = 256;
+size_t round256(size_t v) { return (v + 255) / 256 * 256; }
+size_t packed_need(long long m, long long n, long long k, int groups) {
+    return round256(groups > 1 ? (size_t)groups * m * n * 4 : 0) + pk_workspace_bytes(m, n, k);
+}
+
+template <int WK>
+void launch_pack(const PackArgs &a, cudaStream_t st) {
+    dim3 grid((unsigned)a.leaves, (unsigned)((a.extent + PK_TILE - 1) / PK_TILE));
+    pack_operand_kernel<WK><<<grid, 256, 0, st>>>(a);
+}
+
+// Packs both operands into `scratch` (panels, then flags) and runs the packed kernel.
+int launch_packed(const GemmArgs &g, int groups, unsigned char *scratch, cudaStream_t st) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaFuncSetAttribute(gemm_packed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PK_SMEM_BYTES);
+        configured[dev] = true;
+    }
+    const int wpl = pk_windows_per_leaf(g.leaf);
+    float *pa = reinterpret_cast<float *>(scratch);
+    float *pb = pa + pk_panel_floats(g.m, g.k);
+    unsigned char *fa = reinterpret_cast<unsigned char *>(pb + pk_panel_floats(g.n, g.k));
+    unsigned char *fb = fa + pk_flag_bytes(g.m, g.k);
+    PackArgs a{pa, fa, g.a, nullptr, g.m, g.k, g.leaf, g.leaves, wpl, g.op != OP_TN};
+    launch_pack<W_F32>(a, st);
+    PackArgs b{pb, fb, g.b, g.bscale, g.n, g.k, g.leaf, g.leaves, wpl, g.op == OP_NT};
+    if (g.wkind == W_F32) launch_pack<W_F32>(b, st);
+    else if (g.wkind == W_BF16) launch_pack<W_BF16>(b, st);
+    else if (g.wkind == W_INT8_EXP) launch_pack<W_INT8_EXP>(b, st);
+    else launch_pack<W_INT8_SCALE>(b, st);
+    PackedGemmArgs p{pa, pb, fa, fb, g.c, g.ws, g.m, g.n, g.k, g.leaf, g.leaves, wpl, g.group_leaves, groups,
+                     (g.n + PK_TILE - 1) / PK_TILE, g.vec_c};
+    dim3 grid((unsigned)(((g.m + PK_TILE - 1) / PK_TILE) * p.tiles_n), (unsigned)groups);
+    gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, st>>>(p);
+    return 3;
+}
+
 template <int BM, int BN, int RM, int RN, int MINB>
 void launch_tile(GemmArgs &g, int groups, cudaStream_t st) {
     using S = TileShape<BM, BN, RM, RN>;
@@ -189,6 +231,9 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     Plan plan;
     if (plan_kind == PLAN_AUTO) {
         plan = choose_plan(m, n, k, sm_count(dev));
+        if (plan.kind == PLAN_T128 && m >= PACKED_MIN_EXTENT && n >= PACKED_MIN_EXTENT && ws && aligned(ws, 256) &&
+            (size_t)ws_bytes >= packed_need(m, n, k, plan.groups))
+            plan.kind = PLAN_PACKED;
         const bool al16 = aligned(b, 16) && aligned(a, 16);
         const bool dec = decode_plan_fits(m, n, k, op, wkind) && al16;
         if (dec && m <= DECODE_PREFER_M) plan = Plan{PLAN_DECODE, g.leaves, 1};
@@ -247,6 +292,12 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     } else if (plan.kind == PLAN_T128X64) {
         launch_tile<128, 64, 2, 1, 3>(g, plan.groups, st);
         g_launches++;
+    } else if (plan.kind == PLAN_PACKED) {
+        const size_t nodes = round256(plan.groups > 1 ? (size_t)plan.groups * m * n * 4 : 0);
+        if (!ws || !aligned(ws, 256) || (size_t)ws_bytes < packed_need(m, n, k, plan.groups))
+            return fail(err, err_cap, "identical gemm: the packed plan needs a 256-byte aligned workspace of %lld bytes, %lld given",
+                        (long long)packed_need(m, n, k, plan.groups), (long long)ws_bytes);
+        g_launches += launch_packed(g, plan.groups, static_cast<unsigned char *>(ws) + nodes, st);
     } else if (plan.kind == PLAN_SKINNY) {
         if (!skinny_plan_fits(m, n, k, op) || !aligned(b, 16) || !aligned(a, 16))
             return fail(err, err_cap, "identical gemm: the skinny plan needs op NT, m <= 32, k a multiple of 16 and 16-byte aligned operands");
@@ -332,11 +383,23 @@ int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = -1; }
     Plan p = choose_plan(m, n, k, sm_count(dev));
     int groups = p.groups;
+    if (p.kind == PLAN_T128 && m >= PACKED_MIN_EXTENT && n >= PACKED_MIN_EXTENT) return (int64_t)packed_need(m, n, k, groups);
     if (skinny_plan_fits(m, n, k, OP_NT)) { // the plan an NT product with aligned operands takes instead
         const Plan q = choose_skinny(m, n, k, sm_count(dev));
         if (q.groups > groups) groups = q.groups;
     }
     return groups > 1 ? (int64_t)groups * m * n * 4 : 0;
+}
+
+int64_t b200i_plan_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t plan, int64_t group_leaves) {
+    if (m <= 0 || n <= 0 || k <= 0) return 0;
+    if (plan == PLAN_AUTO) return b200i_workspace_bytes(m, n, k);
+    const int64_t leaves = leaf_count(k);
+    int64_t s = group_leaves > 0 ? group_leaves : leaves;
+    if (s > leaves) s = leaves;
+    const int64_t groups = (plan == PLAN_FLAT || plan == PLAN_DECODE) ? 1 : (leaves + s - 1) / s;
+    if (plan == PLAN_PACKED) return (int64_t)packed_need(m, n, k, (int)groups);
+    return groups > 1 ? groups * m * n * 4 : 0;
 }
 
 int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale,

@@ -19,7 +19,7 @@ import torch
 from . import _native
 from .linalg import OP_NN, OP_NT, OP_TN, W_BF16, W_F32, W_INT8_EXP, W_INT8_SCALE, leaf_count
 
-PLAN_AUTO, PLAN_FLAT, PLAN_T128, PLAN_T64, PLAN_DECODE, PLAN_T32, PLAN_T128X64, PLAN_SKINNY = -1, 0, 1, 2, 3, 4, 5, 6
+PLAN_AUTO, PLAN_FLAT, PLAN_T128, PLAN_T64, PLAN_DECODE, PLAN_T32, PLAN_T128X64, PLAN_SKINNY, PLAN_PACKED = -1, 0, 1, 2, 3, 4, 5, 6, 7
 
 
 def _check(t, name, dtype):
@@ -78,12 +78,7 @@ def product(a, b, bscale=None, wkind=W_F32, op=OP_NN, out=None, plan=PLAN_AUTO, 
             raise ValueError("out must be (%d, %d)" % (m, n))
     lib = _native.lib()
     with torch.cuda.device(dev):
-        if plan == PLAN_AUTO:
-            ws_bytes = int(lib.b200i_workspace_bytes(m, n, k))
-        elif group_leaves > 0:
-            ws_bytes = (-(-leaf_count(k) // group_leaves)) * m * n * 4
-        else:
-            ws_bytes = 0
+        ws_bytes = int(lib.b200i_plan_workspace_bytes(m, n, k, plan, group_leaves))
         ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=dev) if ws_bytes else None
         _native.call("b200i_gemm_w_plan", dev.index, _stream(dev), _vp(out), _vp(a), _vp(b), _vp(bscale), wkind, m, n, k,
                      op, plan, group_leaves, _vp(ws), ws_bytes)

@@ -18,7 +18,8 @@ from mojolearn_b200 import _native, linalg, torch_ops  # noqa: E402
 
 OPS = {"NN": oracle.OP_NN, "NT": oracle.OP_NT, "TN": oracle.OP_TN}
 PLANS = [(torch_ops.PLAN_FLAT, 0), (torch_ops.PLAN_T128, 0), (torch_ops.PLAN_T64, 0), (torch_ops.PLAN_T128, 1),
-         (torch_ops.PLAN_T64, 2), (torch_ops.PLAN_T128, 4), (torch_ops.PLAN_T32, 0), (torch_ops.PLAN_T32, 2)]
+         (torch_ops.PLAN_T64, 2), (torch_ops.PLAN_T128, 4), (torch_ops.PLAN_T32, 0), (torch_ops.PLAN_T32, 2),
+         (torch_ops.PLAN_PACKED, 0), (torch_ops.PLAN_PACKED, 2)]
 
 # (m, n, k): P = 1, 2, 3 (ragged, odd carry), 5 (carries twice), 6, 8 with a short last leaf, tails, k = 1
 SHAPES = [(40, 20, 300), (11, 6, 640), (9, 5, 256), (17, 3, 64), (8, 48, 384), (36, 9, 300), (1, 1, 1), (5, 7, 1),
@@ -153,6 +154,11 @@ def test_config2_full_size_rows_sampled_against_the_oracle(m, n, k):
                               group_leaves=2 if k >= 256 else 0)
     assert torch.equal(c.view(torch.int32), other.view(torch.int32))
     del other
+    for plan in (torch_ops.PLAN_T128, torch_ops.PLAN_PACKED):  # the automatic choice is one of these; both must agree
+        other = torch_ops.product(a, b, None, linalg.W_F32, oracle.OP_NT, plan=plan)
+        assert torch.equal(c.view(torch.int32), other.view(torch.int32)), plan
+        del other
+    assert _native.lib().b200i_decode_status(-1) == 0
     if m * n * k <= 128 * 11008 * 4096:
         bt = b.t().contiguous()
         nn = torch_ops.matmul(a, bt)
