@@ -213,6 +213,7 @@ def main():
     if rank == 0:
         sampler.start()
     launches0 = lib.b200i_launch_count()
+    lib.b200i_kernel_timing(1)  # event pairs around every product's main kernel, on the launching stream
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     shape_ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(SWEEP) + 1)] for _ in range(args.steps)]
     barrier()
@@ -226,6 +227,9 @@ def main():
     barrier()
     elapsed_ms = ev[0].elapsed_time(ev[1])
     launches = lib.b200i_launch_count() - launches0
+    kernel_ms, kernel_calls = ctypes.c_double(0.0), ctypes.c_int64(0)
+    lib.b200i_kernel_timing_read(ctypes.byref(kernel_ms), ctypes.byref(kernel_calls))
+    lib.b200i_kernel_timing(0)
     clocks = sampler.stop() if rank == 0 else None
     per_shape_ms = [statistics.mean(shape_ev[s][i].elapsed_time(shape_ev[s][i + 1]) for s in range(args.steps))
                     for i in range(len(SWEEP))]
@@ -255,14 +259,16 @@ def main():
         peaks["packed" if packed else "scalar"] = fl / (e0.elapsed_time(e1) * 1e-3) / 1e12
     fp32_peak = max(peaks.values())
 
-    # the dominant kernel: the 128x128 tile kernel (shapes 0, 1, 3 of the sweep run nothing else)
-    tile_shapes = [0, 1, 3]
-    tile_flops = sum(2.0 * SWEEP[i][0] * SWEEP[i][1] * SWEEP[i][2] for i in tile_shapes)
-    tile_ms = sum(per_shape_ms[i] for i in tile_shapes)
-    tile_tflops = tile_flops / (tile_ms * 1e-3) / 1e12
+    # the dominant kernel: each product's main kernel (gemm_packed_kernel on four of the five shapes, the 128x128
+    # tile kernel on 128x11008x4096), timed by the library's own event pairs: operand packing and the group fold
+    # are outside these pairs and inside `value`
+    tile_flops = sweep_flops(SWEEP) * args.steps
+    tile_ms = float(kernel_ms.value)
+    tile_tflops = tile_flops / (tile_ms * 1e-3) / 1e12 if tile_ms > 0 else 0.0
     sm_max = (clocks or {}).get("sm_max_mhz") or 1965.0
-    roofline = {"bound": "fp32_ffma", "kernel": "gemm_tile_kernel<128,128>", "achieved": tile_tflops, "peak": fp32_peak,
-                "unit": "TFLOP/s", "frac": tile_tflops / fp32_peak,
+    roofline = {"bound": "fp32_ffma", "kernel": "gemm_packed_kernel (128x128 tiles, bulk-copy ring)", "achieved": tile_tflops,
+                "peak": fp32_peak, "unit": "TFLOP/s", "frac": tile_tflops / fp32_peak if fp32_peak else None,
+                "kernel_launches_timed": int(kernel_calls.value), "kernel_ms_per_step": tile_ms / max(args.steps, 1),
                 "peak_source": "in-run fused-multiply-add probe (max of scalar %.1f and packed f32x2 %.1f TFLOP/s); nominal %d SMs x 128 lanes x 2 x %.0f MHz = %.1f"
                 % (peaks["scalar"], peaks["packed"], sms, sm_max, sms * 128 * 2 * sm_max * 1e6 / 1e12),
                 "launch_ms": {"%dx%dx%d" % SWEEP[i]: per_shape_ms[i] for i in range(len(SWEEP))},
@@ -373,7 +379,7 @@ def main():
         import argparse as _ap
         from mojolearn_b200 import serve_bench
         sargs = _ap.Namespace(layers=24, d_model=2048, heads=16, mlp=8192, vocab=50304, batch=32, prompt=1024, decode=48,
-                              timed_steps=32, format="int8")
+                              timed_steps=32, format="int8", no_graph=False)
         del ops
         torch.cuda.empty_cache()
         serve, _ = serve_bench.run(sargs)

@@ -86,6 +86,15 @@ int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a
                           int64_t wkind, int64_t m, int64_t n, int64_t k, int64_t op, int64_t plan,
                           int64_t group_leaves, void *ws, int64_t ws_bytes, char *err, int64_t err_cap);
 
+/* Device timing of the product's main kernel, for benchmarks. While enabled (enable = 1 also
+ * clears the record) every product call records a CUDA event pair on its stream around its main
+ * kernel: the tile, packed, skinny or decode kernel, not the packing passes or the group fold.
+ * b200i_kernel_timing_read waits for the recorded events and returns their summed milliseconds
+ * and count (at most 4096 calls are recorded), then clears the record. Not for use while a
+ * stream is being captured. No reference counterpart. */
+int64_t b200i_kernel_timing(int64_t enable);
+int64_t b200i_kernel_timing_read(double *total_ms, int64_t *launches);
+
 /* Scratch a forced plan needs for the shape (group nodes, and the packed plan's panels and flags);
  * plan -1 is b200i_workspace_bytes. */
 int64_t b200i_plan_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t plan, int64_t group_leaves);

@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "../../include/b200i.h"
 #include "decode.cuh"
@@ -148,11 +149,51 @@ Plan choose_skinny(long long m, long long n, long long k, int sms) {
 
 bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// ---- optional device timing of the product's main kernel ------------------------------------
+// While enabled, every product call records a CUDA event pair on its stream around its main
+// kernel (the tile / packed / skinny / decode kernel; not the packing passes, not the group fold).
+struct KernelTiming {
+    bool on = false;
+    int used = 0;
+    std::vector<cudaEvent_t> ev; // pairs
+};
+KernelTiming g_timing;
+std::mutex g_timing_mu;
+constexpr int TIMING_MAX_PAIRS = 4096;
+int timing_begin(cudaStream_t st) {
+    std::lock_guard<std::mutex> lock(g_timing_mu);
+    if (!g_timing.on || g_timing.used >= TIMING_MAX_PAIRS) return -1;
+    const int slot = g_timing.used++;
+    while ((int)g_timing.ev.size() < 2 * (slot + 1)) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); g_timing.used = slot; return -1; }
+        g_timing.ev.push_back(e);
+    }
+    cudaEventRecord(g_timing.ev[2 * slot], st);
+    return slot;
+}
+void timing_end(int slot, cudaStream_t st) {
+    if (slot < 0) return;
+    std::lock_guard<std::mutex> lock(g_timing_mu);
+    cudaEventRecord(g_timing.ev[2 * slot + 1], st);
+}
+
 // rows below which packing the operands costs more than the bulk-copy pipeline returns
 constexpr long long PACKED_MIN_EXTENT = 256;
 size_t round256(size_t v) { return (v + 255) / 256 * 256; }
 size_t packed_need(long long m, long long n, long long k, int groups) {
     return round256(groups > 1 ? (size_t)groups * m * n * 4 : 0) + pk_workspace_bytes(m, n, k);
+}
+
+// The packed plan's leaf split: with at least two CTAs per slot of the device the tiles alone keep every SM busy
+// (a CTA left alone on an SM in the last wave runs at nearly twice the speed, so a partial wave costs little)
+// and a split would only add group nodes; below that, the tile plan's split stands.
+Plan packed_split(const Plan &tile_plan, long long m, long long n, int sms) {
+    const long long tiles = ((m + PK_TILE - 1) / PK_TILE) * ((n + PK_TILE - 1) / PK_TILE);
+    Plan p = tile_plan;
+    p.kind = PLAN_PACKED;
+    if (tiles >= 4ll * sms) { p.groups = 1; p.group_leaves = tile_plan.group_leaves * tile_plan.groups; }
+    return p;
 }
 
 template <int WK>
@@ -185,7 +226,9 @@ int launch_packed(const GemmArgs &g, int groups, unsigned char *scratch, cudaStr
     PackedGemmArgs p{pa, pb, fa, fb, g.c, g.ws, g.m, g.n, g.k, g.leaf, g.leaves, wpl, g.group_leaves, groups,
                      (g.n + PK_TILE - 1) / PK_TILE, g.vec_c};
     dim3 grid((unsigned)(((g.m + PK_TILE - 1) / PK_TILE) * p.tiles_n), (unsigned)groups);
+    const int tslot = timing_begin(st);
     gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, st>>>(p);
+    timing_end(tslot, st);
     return 3;
 }
 
@@ -231,9 +274,10 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     Plan plan;
     if (plan_kind == PLAN_AUTO) {
         plan = choose_plan(m, n, k, sm_count(dev));
-        if (plan.kind == PLAN_T128 && m >= PACKED_MIN_EXTENT && n >= PACKED_MIN_EXTENT && ws && aligned(ws, 256) &&
-            (size_t)ws_bytes >= packed_need(m, n, k, plan.groups))
-            plan.kind = PLAN_PACKED;
+        if (plan.kind == PLAN_T128 && m >= PACKED_MIN_EXTENT && n >= PACKED_MIN_EXTENT) {
+            const Plan packed = packed_split(plan, m, n, sm_count(dev));
+            if (ws && aligned(ws, 256) && (size_t)ws_bytes >= packed_need(m, n, k, packed.groups)) plan = packed;
+        }
         const bool al16 = aligned(b, 16) && aligned(a, 16);
         const bool dec = decode_plan_fits(m, n, k, op, wkind) && al16;
         if (dec && m <= DECODE_PREFER_M) plan = Plan{PLAN_DECODE, g.leaves, 1};
@@ -269,6 +313,8 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     g.vec_b = b_kc ? (k % 4 == 0 && leaf_ok && aligned(b, balign)) : (n % 4 == 0 && aligned(b, balign));
     g.vec_c = (n % 4 == 0) && aligned(c, 16) && (plan.groups == 1 || aligned(ws, 16));
 
+    int tslot = -1;
+    if (plan.kind != PLAN_PACKED) tslot = timing_begin(st);
     if (plan.kind == PLAN_FLAT) {
         const long long cells = (long long)m * n;
         gemm_flat_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(g);
@@ -306,6 +352,7 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     } else {
         return fail(err, err_cap, "identical gemm: unknown plan %d", plan.kind);
     }
+    timing_end(tslot, st);
     if (plan.groups > 1) {
         const long long cells = (long long)m * n;
         fold_groups_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(g.ws, c, cells, plan.groups);
@@ -383,12 +430,38 @@ int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = -1; }
     Plan p = choose_plan(m, n, k, sm_count(dev));
     int groups = p.groups;
-    if (p.kind == PLAN_T128 && m >= PACKED_MIN_EXTENT && n >= PACKED_MIN_EXTENT) return (int64_t)packed_need(m, n, k, groups);
+    if (p.kind == PLAN_T128 && m >= PACKED_MIN_EXTENT && n >= PACKED_MIN_EXTENT)
+        return (int64_t)packed_need(m, n, k, packed_split(p, m, n, sm_count(dev)).groups);
     if (skinny_plan_fits(m, n, k, OP_NT)) { // the plan an NT product with aligned operands takes instead
         const Plan q = choose_skinny(m, n, k, sm_count(dev));
         if (q.groups > groups) groups = q.groups;
     }
     return groups > 1 ? (int64_t)groups * m * n * 4 : 0;
+}
+
+int64_t b200i_kernel_timing(int64_t enable) {
+    std::lock_guard<std::mutex> lock(g_timing_mu);
+    g_timing.on = enable != 0;
+    if (enable) g_timing.used = 0;
+    return 0;
+}
+
+int64_t b200i_kernel_timing_read(double *total_ms, int64_t *launches) {
+    std::lock_guard<std::mutex> lock(g_timing_mu);
+    double sum = 0.0;
+    for (int i = 0; i < g_timing.used; i++) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(g_timing.ev[2 * i + 1]) != cudaSuccess ||
+            cudaEventElapsedTime(&ms, g_timing.ev[2 * i], g_timing.ev[2 * i + 1]) != cudaSuccess) {
+            cudaGetLastError();
+            return 1;
+        }
+        sum += ms;
+    }
+    if (total_ms) *total_ms = sum;
+    if (launches) *launches = g_timing.used;
+    g_timing.used = 0;
+    return 0;
 }
 
 int64_t b200i_plan_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t plan, int64_t group_leaves) {
