@@ -216,9 +216,10 @@ int launch_packed(const GemmArgs &g, int groups, unsigned char *scratch, cudaStr
     float *pb = pa + pk_panel_floats(g.m, g.k);
     unsigned char *fa = reinterpret_cast<unsigned char *>(pb + pk_panel_floats(g.n, g.k));
     unsigned char *fb = fa + pk_flag_bytes(g.m, g.k);
-    PackArgs a{pa, fa, g.a, nullptr, g.m, g.k, g.leaf, g.leaves, wpl, g.op != OP_TN};
+    const bool k8 = (g.k % 8 == 0) && (g.leaves == 1 || g.leaf % 8 == 0);
+    PackArgs a{pa, fa, g.a, nullptr, g.m, g.k, g.leaf, g.leaves, wpl, g.op != OP_TN, g.op != OP_TN && k8 && aligned(g.a, 16)};
     launch_pack<W_F32>(a, st);
-    PackArgs b{pb, fb, g.b, g.bscale, g.n, g.k, g.leaf, g.leaves, wpl, g.op == OP_NT};
+    PackArgs b{pb, fb, g.b, g.bscale, g.n, g.k, g.leaf, g.leaves, wpl, g.op == OP_NT, g.op == OP_NT && k8 && aligned(g.b, 16)};
     if (g.wkind == W_F32) launch_pack<W_F32>(b, st);
     else if (g.wkind == W_BF16) launch_pack<W_BF16>(b, st);
     else if (g.wkind == W_INT8_EXP) launch_pack<W_INT8_EXP>(b, st);

@@ -54,6 +54,7 @@ struct PackArgs {
     const void *scale;
     int extent, k, leaf, leaves, wpl;
     int kcontig; // 1: x is [extent][k]; 0: x is [k][extent]
+    int vec;     // k-contiguous, every 8-step run of a thread starts on a 16-byte (float32) / element-size * 8 boundary
 };
 
 __device__ __forceinline__ float pk_element(const void *x, const void *scale, int wkind, size_t off, int row) {
@@ -77,12 +78,40 @@ __global__ void __launch_bounds__(256) pack_operand_kernel(const PackArgs a) {
         const int len = min(KS, leaf_len - koff);
         unsigned key = 0xFFFFFFFFu;
         float v[8];
+        if (a.vec && live && len == KS) { // this thread's 8 k-steps are contiguous in the operand: 32, 16 or 8 bytes
+            const size_t off = (size_t)row * a.k + kb + koff + half * 8;
+            if (WK == W_F32) {
+                const float4 lo = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(a.x) + off));
+                const float4 hi = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(a.x) + off) + 1);
+                v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
-            const int kk = kb + koff + half * 8 + e;
-            v[e] = 0.f;
-            if (live && half * 8 + e < len)
-                v[e] = pk_element(a.x, a.scale, WK, a.kcontig ? (size_t)row * a.k + kk : (size_t)kk * a.extent + row, row);
+                for (int e = 0; e < 8; e++) v[e] = ftz_bits(v[e]);
+            } else if (WK == W_BF16) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4 *>(static_cast<const unsigned short *>(a.x) + off));
+                const unsigned ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    v[2 * e] = ftz_bits(__uint_as_float(ws[e] << 16));
+                    v[2 * e + 1] = ftz_bits(__uint_as_float(ws[e] & 0xFFFF0000u));
+                }
+            } else {
+                const uint2 w = __ldg(reinterpret_cast<const uint2 *>(static_cast<const signed char *>(a.x) + off));
+                const float f = (WK == W_INT8_EXP) ? pow2_f32(__ldg(static_cast<const int *>(a.scale) + row))
+                                                   : __ldg(static_cast<const float *>(a.scale) + row);
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const unsigned word = e < 4 ? w.x : w.y;
+                    v[e] = dequant_int8_pow2((int)(signed char)((word >> (8 * (e & 3))) & 0xFFu), f);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int kk = kb + koff + half * 8 + e;
+                v[e] = 0.f;
+                if (live && half * 8 + e < len)
+                    v[e] = pk_element(a.x, a.scale, WK, a.kcontig ? (size_t)row * a.k + kk : (size_t)kk * a.extent + row, row);
+            }
         }
 #pragma unroll
         for (int e = 0; e < 8; e++) {

@@ -90,7 +90,8 @@ def test_config3_full_size(m):
     # every plan that accepts the shape returns the same words
     fits = _native.lib().b200i_decode_plan_fits(m, n, k, oracle.OP_NT, linalg.W_INT8_EXP)
     assert fits == (1 if m <= 8 else 0)
-    plans = [(torch_ops.PLAN_T128, 0), (torch_ops.PLAN_T64, 4)] + ([(torch_ops.PLAN_DECODE, 0)] if fits else [])
+    plans = [(torch_ops.PLAN_T128, 0), (torch_ops.PLAN_T64, 4), (torch_ops.PLAN_PACKED, 0), (torch_ops.PLAN_PACKED, 4)]
+    plans += [(torch_ops.PLAN_DECODE, 0)] if fits else []
     plans += [(torch_ops.PLAN_SKINNY, 0), (torch_ops.PLAN_SKINNY, 2)] if m <= 32 else []
     for plan, groups in plans:
         alt = torch_ops.product(dx, dcodes, dexps, linalg.W_INT8_EXP, oracle.OP_NT, plan=plan, group_leaves=groups)
@@ -121,12 +122,12 @@ def test_decode_plan_edges():
     w = oracle.dequantize_int8(codes, exps)
     want = oracle.nan_canon(oracle.gemm(x, w, oracle.OP_NT))
     dx, dc, de = torch.from_numpy(x).cuda(), torch.from_numpy(codes).cuda(), torch.from_numpy(exps).cuda()
-    for plan in (torch_ops.PLAN_DECODE, torch_ops.PLAN_T64, torch_ops.PLAN_FLAT, torch_ops.PLAN_AUTO):
+    for plan in (torch_ops.PLAN_DECODE, torch_ops.PLAN_T64, torch_ops.PLAN_FLAT, torch_ops.PLAN_AUTO, torch_ops.PLAN_PACKED):
         got = torch_ops.product(dx, dc, de, linalg.W_INT8_EXP, oracle.OP_NT, plan=plan)
         assert got.cpu().numpy().tobytes() == want.tobytes(), plan
     wb = oracle.to_bf16((rng.standard_normal((n, k)) * 2.0 ** -64).astype(np.float32))
     wantb = oracle.gemm(x, oracle.from_bf16(wb), oracle.OP_NT)
-    for plan in (torch_ops.PLAN_DECODE, torch_ops.PLAN_T128):
+    for plan in (torch_ops.PLAN_DECODE, torch_ops.PLAN_T128, torch_ops.PLAN_PACKED):
         got = torch_ops.product(dx, torch.from_numpy(wb).cuda(), None, linalg.W_BF16, oracle.OP_NT, plan=plan)
         assert got.cpu().numpy().tobytes() == wantb.tobytes(), plan
     assert _native.lib().b200i_decode_status(-1) == 0
