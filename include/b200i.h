@@ -86,6 +86,24 @@ int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a
                           int64_t wkind, int64_t m, int64_t n, int64_t k, int64_t op, int64_t plan,
                           int64_t group_leaves, void *ws, int64_t ws_bytes, char *err, int64_t err_cap);
 
+/* A static weight laid out once for the decode-step product (up to 32 activation rows).
+ * b200i_pack_weight rewrites W[n, k] (storage kind `wkind`, `scale` as for b200i_gemm_w) into
+ * column-tile-major panels of the same storage type, with per-column factors and per-window
+ * admission flags, in `packed` (256-byte aligned, b200i_packed_weight_bytes(n, k, wkind) bytes;
+ * k a multiple of 16 with 128-step leaves, else 0 bytes and a refusal). b200i_gemm_packed_w is
+ * then C[m, n] = A[m, k] . W^T for m <= 32 with the same bits as b200i_gemm_w: the panels let one
+ * thread feed the CTA with bulk copies instead of staging the weight through registers. `ws` is
+ * per-call scratch of b200i_gemm_packed_w_workspace_bytes(m, n, k) bytes, 256-byte aligned. The
+ * reference packs its weights for the same reason (python/mojolearn/lowbit.py pack / pack_one keep a
+ * layer's storage form; gemm/checks/gemm_lowbit.mojo:369-395 consumes it); the panel layout itself
+ * has no reference counterpart. */
+int64_t b200i_packed_weight_bytes(int64_t n, int64_t k, int64_t wkind);
+int64_t b200i_pack_weight(int64_t device, void *stream, void *packed, const void *w, const void *scale, int64_t wkind, int64_t n,
+                          int64_t k, char *err, int64_t err_cap);
+int64_t b200i_gemm_packed_w_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int64_t b200i_gemm_packed_w(int64_t device, void *stream, float *c, const float *a, const void *packed, int64_t wkind, int64_t m,
+                            int64_t n, int64_t k, void *ws, int64_t ws_bytes, char *err, int64_t err_cap);
+
 /* Device timing of the product's main kernel, for benchmarks. While enabled (enable = 1 also
  * clears the record) every product call records a CUDA event pair on its stream around its main
  * kernel: the tile, packed, skinny or decode kernel, not the packing passes or the group fold.

@@ -44,6 +44,10 @@ SIGNATURES = {
     "b200i_launch_count": [],
     "b200i_workspace_bytes": [I64, I64, I64],
     "b200i_plan_workspace_bytes": [I64, I64, I64, I64, I64],
+    "b200i_packed_weight_bytes": [I64, I64, I64],
+    "b200i_pack_weight": [I64, VP, VP, VP, VP, I64, I64, I64, VP, I64],
+    "b200i_gemm_packed_w_workspace_bytes": [I64, I64, I64],
+    "b200i_gemm_packed_w": [I64, VP, VP, VP, VP, I64, I64, I64, I64, VP, I64, VP, I64],
     "b200i_kernel_timing": [I64],
     "b200i_kernel_timing_read": [VP, VP],
     "b200i_decode_plan_fits": [I64, I64, I64, I64, I64],

@@ -13,6 +13,7 @@
 #include "gemm_tile.cuh"
 #include "gemm_skinny.cuh"
 #include "gemm_packed.cuh"
+#include "gemm_skinny_packed.cuh"
 #include "lowbit.cuh"
 
 using namespace b200i;
@@ -178,9 +179,59 @@ void timing_end(int slot, cudaStream_t st) {
     cudaEventRecord(g_timing.ev[2 * slot + 1], st);
 }
 
+size_t round256(size_t v) { return (v + 255) / 256 * 256; }
+size_t round256_sz(size_t v) { return round256(v); }
+
+// ---- the skinny product against a prepacked weight ------------------------------------------
+Plan choose_skinny_packed(long long n, long long k, int sms) {
+    const int leaves = (int)leaf_count(k) > 0 ? (int)leaf_count(k) : 1;
+    const long long col_ctas = (n + SKP_BN - 1) / SKP_BN;
+    const long long want = (long long)sms * SKP_PER_SM * 9 / 10;
+    const int max_s = pow2_floor(leaves) * ((leaves & (leaves - 1)) ? 2 : 1);
+    int min_s = 1;
+    while ((leaves + min_s - 1) / min_s > MAX_GROUPS) min_s *= 2;
+    int best = min_s;
+    for (int s = max_s; s >= min_s; s /= 2)
+        if (col_ctas * ((leaves + s - 1) / s) >= want) { best = s; break; }
+    Plan p{PLAN_SKINNY, best, (leaves + best - 1) / best};
+    if (p.groups <= 1) p.group_leaves = leaves;
+    return p;
+}
+int skp_bm(long long m) { return m <= 8 ? 8 : (m <= 16 ? 16 : 32); }
+size_t skp_call_bytes(long long m, long long n, long long k, int groups) {
+    return round256_sz((size_t)k * skp_bm(m) * 4) + round256_sz((size_t)(k / KS)) + (groups > 1 ? (size_t)groups * m * n * 4 : 0);
+}
+
+template <int WK, int BM>
+void launch_skinny_packed_cfg(const SkinnyPackedArgs &g, cudaStream_t st) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    constexpr int smem = skp_smem_bytes(WK, BM);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaFuncSetAttribute(gemm_skinny_packed_kernel<WK, BM, SKP_PER_SM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        configured[dev] = true;
+    }
+    dim3 grid((unsigned)((g.n + SKP_BN - 1) / SKP_BN), (unsigned)g.groups);
+    gemm_skinny_packed_kernel<WK, BM, SKP_PER_SM><<<grid, SKP_THREADS, smem, st>>>(g);
+}
+template <int WK>
+void launch_skinny_packed_wk(const SkinnyPackedArgs &g, float *at, unsigned char *aflags, const float *a, cudaStream_t st) {
+    const unsigned windows = (unsigned)(g.k / KS);
+    if (g.m <= 8) {
+        skinny_pack_a_kernel<8><<<windows, 128, 0, st>>>(at, aflags, a, g.m, g.k);
+        launch_skinny_packed_cfg<WK, 8>(g, st);
+    } else if (g.m <= 16) {
+        skinny_pack_a_kernel<16><<<windows, 128, 0, st>>>(at, aflags, a, g.m, g.k);
+        launch_skinny_packed_cfg<WK, 16>(g, st);
+    } else {
+        skinny_pack_a_kernel<32><<<windows, 128, 0, st>>>(at, aflags, a, g.m, g.k);
+        launch_skinny_packed_cfg<WK, 32>(g, st);
+    }
+}
+
 // rows below which packing the operands costs more than the bulk-copy pipeline returns
 constexpr long long PACKED_MIN_EXTENT = 256;
-size_t round256(size_t v) { return (v + 255) / 256 * 256; }
 size_t packed_need(long long m, long long n, long long k, int groups) {
     return round256(groups > 1 ? (size_t)groups * m * n * 4 : 0) + pk_workspace_bytes(m, n, k);
 }
@@ -438,6 +489,78 @@ int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k) {
         if (q.groups > groups) groups = q.groups;
     }
     return groups > 1 ? (int64_t)groups * m * n * 4 : 0;
+}
+
+int64_t b200i_packed_weight_bytes(int64_t n, int64_t k, int64_t wkind) {
+    if (n <= 0 || k <= 0 || k % KS != 0 || wkind < W_F32 || wkind > W_INT8_SCALE) return 0;
+    return (int64_t)skp_weight_layout(n, k, (int)wkind).total;
+}
+
+int64_t b200i_pack_weight(int64_t device, void *stream, void *packed, const void *w, const void *scale, int64_t wkind, int64_t n,
+                          int64_t k, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    if (n <= 0 || k <= 0 || !packed || !w || wkind < W_F32 || wkind > W_INT8_SCALE) return fail(err, err_cap, "pack_weight: bad arguments");
+    if (k % KS != 0 || k > 131072 || (k > K_LEAF_MIN && leaf_size(k) != K_LEAF_MIN))
+        return fail(err, err_cap, "pack_weight: k must be a multiple of 16 with 128-step leaves (got %lld)", (long long)k);
+    if ((wkind == W_INT8_EXP || wkind == W_INT8_SCALE) && !scale)
+        return fail(err, err_cap, "pack_weight: int8 weight storage needs its per-row exponents or scales");
+    if (!aligned(packed, 256)) return fail(err, err_cap, "pack_weight: the packed buffer must be 256-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const SkpWeightLayout l = skp_weight_layout(n, k, (int)wkind);
+    dim3 grid((unsigned)(k / KS), (unsigned)l.tiles);
+    unsigned char *p = static_cast<unsigned char *>(packed);
+    if (wkind == W_F32) skinny_pack_w_kernel<W_F32><<<grid, SKP_BN, 0, st>>>(p, w, scale, (int)n, (int)k, l.factor_off, l.flag_off);
+    else if (wkind == W_BF16) skinny_pack_w_kernel<W_BF16><<<grid, SKP_BN, 0, st>>>(p, w, scale, (int)n, (int)k, l.factor_off, l.flag_off);
+    else if (wkind == W_INT8_EXP) skinny_pack_w_kernel<W_INT8_EXP><<<grid, SKP_BN, 0, st>>>(p, w, scale, (int)n, (int)k, l.factor_off, l.flag_off);
+    else skinny_pack_w_kernel<W_INT8_SCALE><<<grid, SKP_BN, 0, st>>>(p, w, scale, (int)n, (int)k, l.factor_off, l.flag_off);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_gemm_packed_w_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+    if (m <= 0 || n <= 0 || k <= 0 || !skinny_packed_fits(m, n, k)) return 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = -1; }
+    return (int64_t)skp_call_bytes(m, n, k, choose_skinny_packed(n, k, sm_count(dev)).groups);
+}
+
+int64_t b200i_gemm_packed_w(int64_t device, void *stream, float *c, const float *a, const void *packed, int64_t wkind, int64_t m,
+                            int64_t n, int64_t k, void *ws, int64_t ws_bytes, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    if (m <= 0 || n <= 0 || k <= 0) return fail(err, err_cap, "identical gemm: m, n and k must be positive");
+    if (!c || !a || !packed || wkind < W_F32 || wkind > W_INT8_SCALE) return fail(err, err_cap, "identical gemm: bad arguments");
+    if (!skinny_packed_fits(m, n, k) || !aligned(a, 16) || !aligned(packed, 256))
+        return fail(err, err_cap, "identical gemm: the prepacked plan needs m <= 32, k a multiple of 16 with 128-step leaves and aligned operands");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const Plan plan = choose_skinny_packed(n, k, sm_count(dev));
+    const size_t need = skp_call_bytes(m, n, k, plan.groups);
+    if (!ws || !aligned(ws, 256) || (size_t)ws_bytes < need)
+        return fail(err, err_cap, "identical gemm: a 256-byte aligned workspace of %lld bytes is needed, %lld given", (long long)need,
+                    (long long)ws_bytes);
+    unsigned char *w8 = static_cast<unsigned char *>(ws);
+    float *at = reinterpret_cast<float *>(w8);
+    unsigned char *aflags = w8 + round256((size_t)k * skp_bm(m) * 4);
+    float *nodes = reinterpret_cast<float *>(aflags + round256((size_t)(k / KS)));
+    const SkpWeightLayout l = skp_weight_layout(n, k, (int)wkind);
+    SkinnyPackedArgs g{at, aflags, static_cast<const unsigned char *>(packed), l.factor_off, l.flag_off, c, nodes,
+                       (int)m, (int)n, (int)k, (int)leaf_size(k), (int)leaf_count(k), plan.group_leaves, plan.groups};
+    if (wkind == W_F32) launch_skinny_packed_wk<W_F32>(g, at, aflags, a, st);
+    else if (wkind == W_BF16) launch_skinny_packed_wk<W_BF16>(g, at, aflags, a, st);
+    else if (wkind == W_INT8_EXP) launch_skinny_packed_wk<W_INT8_EXP>(g, at, aflags, a, st);
+    else launch_skinny_packed_wk<W_INT8_SCALE>(g, at, aflags, a, st);
+    g_launches += 2;
+    if (plan.groups > 1) {
+        const long long cells = (long long)m * n;
+        fold_groups_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(nodes, c, cells, plan.groups);
+        g_launches++;
+    }
+    CUDA_TRY(cudaGetLastError());
+    return 0;
 }
 
 int64_t b200i_kernel_timing(int64_t enable) {

@@ -85,6 +85,40 @@ def product(a, b, bscale=None, wkind=W_F32, op=OP_NN, out=None, plan=PLAN_AUTO, 
     return out
 
 
+def pack_weight(w, scale=None, wkind=W_F32):
+    """A static weight [n, k] laid out once for the decode-step product: a uint8 tensor holding the panels, the
+    per-column factors and the admission flags. None when the shape is outside the prepacked plan."""
+    wdtype = _W_DTYPES[wkind]
+    if wkind == W_BF16 and w.dtype in (torch.int16, torch.bfloat16):
+        w = w.view(torch.uint16)
+    _check(w, "w", wdtype)
+    n, k = w.shape
+    lib = _native.lib()
+    nbytes = int(lib.b200i_packed_weight_bytes(n, k, wkind))
+    if nbytes == 0:
+        return None
+    dev = w.device
+    packed = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _native.call("b200i_pack_weight", dev.index, _stream(dev), _vp(packed), _vp(w), _vp(scale), wkind, n, k)
+    return packed
+
+
+def product_packed(a, packed, wkind, n, out=None):
+    """a [m, k] (m <= 32) times the prepacked weight [n, k]: the bits of product(a, w, ..., OP_NT)."""
+    _check(a, "a", torch.float32)
+    m, k = a.shape
+    dev = a.device
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=dev)
+    lib = _native.lib()
+    with torch.cuda.device(dev):
+        ws_bytes = int(lib.b200i_gemm_packed_w_workspace_bytes(m, n, k))
+        ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device=dev)
+        _native.call("b200i_gemm_packed_w", dev.index, _stream(dev), _vp(out), _vp(a), _vp(packed), wkind, m, n, k, _vp(ws), ws_bytes)
+    return out
+
+
 def matmul(a, b, *, transpose_a=False, transpose_b=False, out=None):
     if transpose_a and transpose_b:
         raise ValueError("both transposes are not an operation of the profile; compute (b @ a).T instead")
