@@ -346,9 +346,12 @@ def main():
             linalg.matmul(ha, hw, transpose_b=True, out=hc)
         barrier()
         t0 = time.perf_counter()
+        e2e_shape_s = [0.0] * len(host)
         for _ in range(e2e_steps):
-            for ha, hw, hc in host:
-                linalg.matmul(ha, hw, transpose_b=True, out=hc)
+            for i, (ha, hw, hc) in enumerate(host):
+                t1 = time.perf_counter()
+                linalg.matmul(ha, hw, transpose_b=True, out=hc)  # returns with the result in host memory
+                e2e_shape_s[i] += time.perf_counter() - t1
         torch.cuda.synchronize(dev)
         dt = time.perf_counter() - t0
         tt = torch.tensor([dt], device=dev, dtype=torch.float64)
@@ -358,6 +361,7 @@ def main():
         e2e = {"value": flops_step * e2e_steps / dt / 1e9, "unit": "GFLOP/s",
                "h2d_bytes_per_step": int(sum(4 * (m * k + n * k) for m, n, k in SWEEP)),
                "d2h_bytes_per_step": int(sum(4 * m * n for m, n, k in SWEEP)), "steps": e2e_steps,
+               "ms_per_shape": {"%dx%dx%d" % SWEEP[i]: 1e3 * e2e_shape_s[i] / e2e_steps for i in range(len(SWEEP))},
                "api": "mojolearn_b200.linalg.matmul(a, w, transpose_b=True, out=...) on pinned host arrays"}
         del host
 

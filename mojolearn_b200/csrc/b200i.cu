@@ -254,7 +254,7 @@ void launch_pack(const PackArgs &a, cudaStream_t st) {
 }
 
 // Packs both operands into `scratch` (panels, then flags) and runs the packed kernel.
-int launch_packed(const GemmArgs &g, int groups, unsigned char *scratch, cudaStream_t st) {
+void packed_configure() {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -262,6 +262,16 @@ int launch_packed(const GemmArgs &g, int groups, unsigned char *scratch, cudaStr
         cudaFuncSetAttribute(gemm_packed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PK_SMEM_BYTES);
         configured[dev] = true;
     }
+}
+void launch_pack_b(const PackArgs &b, int wkind, cudaStream_t st) {
+    if (wkind == W_F32) launch_pack<W_F32>(b, st);
+    else if (wkind == W_BF16) launch_pack<W_BF16>(b, st);
+    else if (wkind == W_INT8_EXP) launch_pack<W_INT8_EXP>(b, st);
+    else launch_pack<W_INT8_SCALE>(b, st);
+}
+
+int launch_packed(const GemmArgs &g, int groups, unsigned char *scratch, cudaStream_t st) {
+    packed_configure();
     const int wpl = pk_windows_per_leaf(g.leaf);
     float *pa = reinterpret_cast<float *>(scratch);
     float *pb = pa + pk_panel_floats(g.m, g.k);
@@ -271,10 +281,7 @@ int launch_packed(const GemmArgs &g, int groups, unsigned char *scratch, cudaStr
     PackArgs a{pa, fa, g.a, nullptr, g.m, g.k, g.leaf, g.leaves, wpl, g.op != OP_TN, g.op != OP_TN && k8 && aligned(g.a, 16)};
     launch_pack<W_F32>(a, st);
     PackArgs b{pb, fb, g.b, g.bscale, g.n, g.k, g.leaf, g.leaves, wpl, g.op == OP_NT, g.op == OP_NT && k8 && aligned(g.b, 16)};
-    if (g.wkind == W_F32) launch_pack<W_F32>(b, st);
-    else if (g.wkind == W_BF16) launch_pack<W_BF16>(b, st);
-    else if (g.wkind == W_INT8_EXP) launch_pack<W_INT8_EXP>(b, st);
-    else launch_pack<W_INT8_SCALE>(b, st);
+    launch_pack_b(b, g.wkind, st);
     PackedGemmArgs p{pa, pb, fa, fb, g.c, g.ws, g.m, g.n, g.k, g.leaf, g.leaves, wpl, g.group_leaves, groups,
                      (g.n + PK_TILE - 1) / PK_TILE, g.vec_c};
     dim3 grid((unsigned)(((g.m + PK_TILE - 1) / PK_TILE) * p.tiles_n), (unsigned)groups);
@@ -415,10 +422,14 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
 }
 
 // Grow-only per-device scratch for the host-pointer twins.
+constexpr int HOST_CHUNKS = 8; // row chunks of a pipelined host-pointer product
 struct HostPool {
     void *buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     size_t cap[5] = {0, 0, 0, 0, 0};
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;                      // compute (and the only stream of the unpipelined twins)
+    cudaStream_t s_in = nullptr, s_out = nullptr;       // host-to-device and device-to-host copies of the pipelined product
+    cudaEvent_t ev[1 + 2 * HOST_CHUNKS] = {};           // weight landed; chunk landed / chunk computed
+    bool pipe_ready = false;
 };
 HostPool g_pool[64];
 std::mutex g_pool_mu;
@@ -1008,6 +1019,78 @@ int64_t b200i_argmax(int64_t device, void *stream, int32_t *out, const float *lo
 
 // ---- host-pointer twins -------------------------------------------------------------------
 
+// The host-pointer product for a tall left operand, pipelined: the weight crosses once and is packed once; the rows of
+// A cross in chunks on a second stream while earlier chunks are packed and multiplied on the compute stream and their
+// rows of C return on a third (PCIe is full duplex). Each chunk is a product of its own, so the bits are those of the
+// whole product (a cell reads one row of A). Returns 0 done, 1 error, -1 not applicable (the caller runs the plain path).
+static int64_t host_gemm_pipelined(int dev, HostPool &pool, float *c, const float *a, const void *b, const void *bscale, int wkind,
+                                   int64_t m, int64_t n, int64_t k, int op, char *err, int64_t err_cap) {
+    if (op == OP_TN || m < 4 * PACKED_MIN_EXTENT || n < PACKED_MIN_EXTENT) return -1;
+    int64_t rows_per = ((m + 3) / 4 + PK_TILE - 1) / PK_TILE * PK_TILE; // about four chunks, whole tiles
+    const int nch = (int)((m + rows_per - 1) / rows_per);
+    if (nch < 2 || nch > HOST_CHUNKS) return -1;
+    if (!pool.pipe_ready) {
+        CUDA_TRY(cudaStreamCreateWithFlags(&pool.s_in, cudaStreamNonBlocking));
+        CUDA_TRY(cudaStreamCreateWithFlags(&pool.s_out, cudaStreamNonBlocking));
+        for (auto &e : pool.ev) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        pool.pipe_ready = true;
+    }
+    const size_t abytes = (size_t)m * k * 4, bbytes = (size_t)n * k * wkind_elem_bytes(wkind), cbytes = (size_t)m * n * 4;
+    const size_t sbytes = (wkind >= W_INT8_EXP) ? (size_t)n * 4 : 0;
+    const size_t wsbytes = pk_workspace_bytes(m, n, k);
+    void *da, *db, *dc, *ds = nullptr, *dw = nullptr;
+    CUDA_TRY(pool_get(dev, 0, abytes, &da));
+    CUDA_TRY(pool_get(dev, 1, bbytes, &db));
+    CUDA_TRY(pool_get(dev, 2, cbytes, &dc));
+    if (sbytes) CUDA_TRY(pool_get(dev, 3, sbytes, &ds));
+    CUDA_TRY(pool_get(dev, 4, wsbytes, &dw));
+    packed_configure();
+    const int leaf = (int)leaf_size(k), leaves = (int)leaf_count(k), wpl = pk_windows_per_leaf(leaf);
+    float *pa = static_cast<float *>(dw);
+    float *pb = pa + pk_panel_floats(m, k);
+    unsigned char *fa = reinterpret_cast<unsigned char *>(pb + pk_panel_floats(n, k));
+    unsigned char *fb = fa + pk_flag_bytes(m, k);
+    const bool k8 = (k % 8 == 0) && (leaves == 1 || leaf % 8 == 0);
+    // everything queued below waits for whatever the compute stream still holds from an earlier call
+    CUDA_TRY(cudaEventRecord(pool.ev[0], pool.stream));
+    CUDA_TRY(cudaStreamWaitEvent(pool.s_in, pool.ev[0], 0));
+    CUDA_TRY(cudaStreamWaitEvent(pool.s_out, pool.ev[0], 0));
+    CUDA_TRY(cudaMemcpyAsync(db, b, bbytes, cudaMemcpyHostToDevice, pool.s_in));
+    if (sbytes) CUDA_TRY(cudaMemcpyAsync(ds, bscale, sbytes, cudaMemcpyHostToDevice, pool.s_in));
+    CUDA_TRY(cudaEventRecord(pool.ev[0], pool.s_in));
+    CUDA_TRY(cudaStreamWaitEvent(pool.stream, pool.ev[0], 0));
+    PackArgs pbargs{pb, fb, db, ds, (int)n, (int)k, leaf, leaves, wpl, op == OP_NT, op == OP_NT && k8};
+    launch_pack_b(pbargs, wkind, pool.stream);
+    g_launches++;
+    const int tiles_n = (int)((n + PK_TILE - 1) / PK_TILE);
+    for (int i = 0; i < nch; i++) {
+        const int64_t r0 = i * rows_per, rows = (m - r0 < rows_per) ? m - r0 : rows_per;
+        const int64_t tile0 = r0 / PK_TILE;
+        const float *ha = a + (size_t)r0 * k;
+        float *dai = static_cast<float *>(da) + (size_t)r0 * k, *dci = static_cast<float *>(dc) + (size_t)r0 * n;
+        CUDA_TRY(cudaMemcpyAsync(dai, ha, (size_t)rows * k * 4, cudaMemcpyHostToDevice, pool.s_in));
+        CUDA_TRY(cudaEventRecord(pool.ev[1 + 2 * i], pool.s_in));
+        CUDA_TRY(cudaStreamWaitEvent(pool.stream, pool.ev[1 + 2 * i], 0));
+        float *pai = pa + (size_t)tile0 * k * PK_TILE;
+        unsigned char *fai = fa + (size_t)tile0 * leaves * wpl;
+        PackArgs paargs{pai, fai, dai, nullptr, (int)rows, (int)k, leaf, leaves, wpl, 1, k8};
+        launch_pack<W_F32>(paargs, pool.stream);
+        PackedGemmArgs p{pai, pb, fai, fb, dci, nullptr, (int)rows, (int)n, (int)k, leaf, leaves, wpl, leaves, 1, tiles_n, (n % 4 == 0) ? 1 : 0};
+        dim3 grid((unsigned)(((rows + PK_TILE - 1) / PK_TILE) * tiles_n), 1u);
+        gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, pool.stream>>>(p);
+        g_launches += 2;
+        CUDA_TRY(cudaEventRecord(pool.ev[2 + 2 * i], pool.stream));
+        CUDA_TRY(cudaStreamWaitEvent(pool.s_out, pool.ev[2 + 2 * i], 0));
+        CUDA_TRY(cudaMemcpyAsync(c + (size_t)r0 * n, dci, (size_t)rows * n * 4, cudaMemcpyDeviceToHost, pool.s_out));
+    }
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaStreamSynchronize(pool.s_out));
+    CUDA_TRY(cudaStreamSynchronize(pool.stream));
+    CUDA_TRY(cudaStreamSynchronize(pool.s_in));
+    (void)err; (void)err_cap;
+    return 0;
+}
+
 int64_t b200i_host_gemm_w(int64_t device, float *c, const float *a, const void *b, const void *bscale, int64_t wkind,
                           int64_t m, int64_t n, int64_t k, int64_t op, char *err, int64_t err_cap) {
     clear(err, err_cap);
@@ -1021,6 +1104,13 @@ int64_t b200i_host_gemm_w(int64_t device, float *c, const float *a, const void *
     std::lock_guard<std::mutex> lock(g_pool_mu);
     HostPool &pool = g_pool[dev];
     if (!pool.stream) CUDA_TRY(cudaStreamCreateWithFlags(&pool.stream, cudaStreamNonBlocking));
+    if (op != OP_NN && op != OP_NT && op != OP_TN) return fail(err, err_cap, "identical gemm: unknown op %lld", (long long)op);
+    if ((wkind == W_INT8_EXP || wkind == W_INT8_SCALE) && (op != OP_NT || !bscale))
+        return fail(err, err_cap, "identical gemm: int8 weight storage is row-scaled: it needs op NT and its per-row exponents or scales");
+    {
+        const int64_t piped = host_gemm_pipelined(dev, pool, c, a, b, bscale, (int)wkind, m, n, k, (int)op, err, err_cap);
+        if (piped >= 0) return piped;
+    }
     const size_t abytes = (size_t)m * k * 4, bbytes = (size_t)n * k * wkind_elem_bytes((int)wkind), cbytes = (size_t)m * n * 4;
     const size_t sbytes = (wkind >= W_INT8_EXP) ? (size_t)n * 4 : 0;
     const int64_t wsbytes = b200i_workspace_bytes(m, n, k);

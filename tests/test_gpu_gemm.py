@@ -65,6 +65,28 @@ def test_public_call_with_host_buffers(opname):
     assert ret is out and out.tobytes() == got.tobytes()
 
 
+@pytest.mark.parametrize("opname", ["NN", "NT"])
+def test_host_call_tall_operand_is_pipelined_in_row_chunks(opname):
+    """m >= 1024 with host buffers: the rows of A cross in chunks while earlier chunks are multiplied and their
+    rows of C return; every chunk is a product of its own, so the bits are the whole product's."""
+    op = OPS[opname]
+    m, n, k = 1100, 300, 264  # three chunks (384 + 384 + 332 rows), ragged tiles, three leaves with a short last one
+    a, b = _operands(m, n, k, op, 5)
+    a[7, ::5] = np.float32(1e-41)
+    want = oracle.nan_canon(oracle.gemm_rows(a, b, op))
+    got = linalg.matmul(a, b, transpose_b=(op == oracle.OP_NT))
+    assert got.tobytes() == want.tobytes()
+    again = linalg.matmul(a, b, transpose_b=(op == oracle.OP_NT))  # the pooled buffers and events are reused
+    assert again.tobytes() == want.tobytes()
+    if op == oracle.OP_NT:
+        rng = np.random.default_rng(6)
+        codes = rng.integers(-127, 128, (n, k)).astype(np.int8)
+        exps = rng.integers(-9, -5, n).astype(np.int32)
+        want8 = oracle.gemm_rows(a, oracle.dequantize_int8(codes, exps), oracle.OP_NT)
+        assert linalg.matmul_int8w(a, codes, exps).tobytes() == want8.tobytes()
+    assert _native.lib().b200i_decode_status(-1) == 0
+
+
 def test_subnormal_forcing_operands_take_the_flushed_path():
     rng = np.random.default_rng(0)
     a = (rng.standard_normal((150, 300)) * 2.0 ** -62).astype(np.float32)
