@@ -28,7 +28,7 @@ import torch
 
 from .. import _native
 from ..parallel import gather_columns, shard_bounds
-from ..transformer import Linear, TransformerBlock, TransformerState, _stream, _vector, _vp, add, norm, NORM_KINDS
+from ..transformer import Linear, ShardedLinear, TransformerBlock, TransformerState, _stream, _vector, _vp, add, norm, NORM_KINDS
 
 
 class CausalLMConfig(object):
@@ -55,19 +55,6 @@ class CausalLMState(object):
     @property
     def positions(self):
         return self.layers[0].cached_tokens if self.layers else 0
-
-
-class _ShardedLinear(object):
-    """Rows [r*N/g, (r+1)*N/g) of a layer on this rank; the call all-gathers the output columns."""
-
-    def __init__(self, full, group, rank, world):
-        n = full.out_features
-        lo, hi = shard_bounds(n, rank, world)
-        self.local = full.shard_rows(lo, hi)
-        self.group, self.world, self.out_features, self.in_features = group, world, n, full.in_features
-
-    def __call__(self, x2d):
-        return gather_columns(self.local(x2d), self.group)  # pure data movement: no arithmetic order is introduced
 
 
 class CausalLM(object):
@@ -103,11 +90,7 @@ class CausalLM(object):
                                    rope=cfg.positions == "rope", rope_theta=cfg.rope_theta, qkv_bias=cfg.qkv_bias,
                                    o_bias=cfg.o_bias, norm=cfg.norm, norm_eps=cfg.norm_eps, norm_bias=cfg.norm_bias, mlp=cfg.mlp,
                                    mlp_bias=cfg.mlp_bias, device=self.device)
-            if self.world > 1:
-                for slot in TransformerBlock.PROJECTIONS:
-                    full = getattr(blk, slot)
-                    if full is not None:
-                        setattr(blk, slot, _ShardedLinear(full, group, self.rank, self.world))
+            blk.shard(group, self.rank, self.world)
             self.blocks.append(blk)
         self.final_w = _vector(get("norm.weight"), "norm.weight", self.device)
         self.final_b = _vector(get("norm.bias"), "norm.bias", self.device) if cfg.norm_bias else None
@@ -116,7 +99,7 @@ class CausalLM(object):
         if self.head.out_features != cfg.vocab:
             raise ValueError("lm_head.weight must have %d rows" % cfg.vocab)
         if self.world > 1:
-            self.head = _ShardedLinear(self.head, group, self.rank, self.world)
+            self.head = ShardedLinear(self.head, group, self.rank, self.world)
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     def allocate_state(self, batch_size, max_tokens):

@@ -23,6 +23,7 @@ import torch
 from . import _native, lowbit
 from .linalg import OP_NT, W_BF16, W_F32, W_INT8_EXP, W_INT8_SCALE
 from . import torch_ops
+from .parallel import gather_columns, shard_bounds
 
 NORM_KINDS = {"rmsnorm": 0, "layernorm": 1, "rmsnorm_offset": 2}
 MLP_KINDS = {"swiglu": 0, "silu_gated": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "geglu": 4, "geglu_tanh": 5}
@@ -136,6 +137,19 @@ class Linear(object):
         return y
 
 
+class ShardedLinear(object):
+    """Rows [r*N/g, (r+1)*N/g) of a layer on this rank; the call all-gathers the output columns."""
+
+    def __init__(self, full, group, rank, world):
+        n = full.out_features
+        lo, hi = shard_bounds(n, rank, world)
+        self.local = full.shard_rows(lo, hi)
+        self.group, self.world, self.out_features, self.in_features = group, world, n, full.in_features
+
+    def __call__(self, x2d):
+        return gather_columns(self.local(x2d), self.group)  # pure data movement: no arithmetic order is introduced
+
+
 class TransformerState(object):
     """Caller-owned KV caches `[B, n_kv_heads, max_tokens, head_dim]` float32 and the tokens cached."""
 
@@ -238,10 +252,53 @@ class TransformerBlock(object):
         if self.gateup is not None:
             self.gate = self.up = None
 
+        self.group = None                      # set by shard(): the process group this block is cut across
+        self.heads_local, self.kv_local, self.inter_local = self.n_heads, self.n_kv_heads, self.inter
+
     PROJECTIONS = ("qkv", "q", "k", "v", "o", "gateup", "gate", "up", "down")
 
+    def shard(self, group, rank, world):
+        """Cut the block across `world` ranks along bit-neutral axes only. With the head counts divisible by the
+        world, a rank keeps its heads' rows of q, k, v (so rotary, the KV cache and the whole attention are local
+        to the rank: a head never reads another head), gathers the context columns, keeps its rows of o, of gate
+        and of up (the activation is elementwise, so it is local too), gathers the activation columns, and keeps
+        its rows of down. Four all-gathers of finished float32 words per block, no k is ever split. Otherwise
+        every projection is cut by output rows and gathered, and the seams between them run replicated."""
+        if world == 1:
+            return
+        by_heads = self.n_heads % world == 0 and self.n_kv_heads % world == 0 and self.inter % world == 0
+        if not by_heads:
+            for slot in self.PROJECTIONS:
+                full = getattr(self, slot)
+                if full is not None:
+                    setattr(self, slot, ShardedLinear(full, group, rank, world))
+            return
+        hd = self.head_dim
+        self.heads_local, self.kv_local = self.n_heads // world, self.n_kv_heads // world
+        self.inter_local = self.inter // world
+        wq, wk, wv = self.widths
+        q0, k0 = rank * self.heads_local * hd, rank * self.kv_local * hd
+        qn, kn = self.heads_local * hd, self.kv_local * hd
+        if self.qkv is not None:
+            parts = [self.qkv.shard_rows(q0, q0 + qn), self.qkv.shard_rows(wq + k0, wq + k0 + kn),
+                     self.qkv.shard_rows(wq + wk + k0, wq + wk + k0 + kn)]
+            self.qkv = Linear.concat(parts)
+        else:
+            self.q, self.k, self.v = self.q.shard_rows(q0, q0 + qn), self.k.shard_rows(k0, k0 + kn), self.v.shard_rows(k0, k0 + kn)
+        self.widths = (qn, kn, kn)
+        i0, i1 = rank * self.inter_local, (rank + 1) * self.inter_local
+        if self.gateup is not None:
+            self.gateup = Linear.concat([self.gateup.shard_rows(i0, i1), self.gateup.shard_rows(self.inter + i0, self.inter + i1)])
+        else:
+            self.up = self.up.shard_rows(i0, i1)
+            if self.gate is not None:
+                self.gate = self.gate.shard_rows(i0, i1)
+        self.o = ShardedLinear(self.o, group, rank, world)
+        self.down = ShardedLinear(self.down, group, rank, world)
+        self.group = group
+
     def allocate_state(self, batch, max_tokens):
-        return TransformerState(batch, self.n_kv_heads, int(max_tokens), self.head_dim, self.device)
+        return TransformerState(batch, self.kv_local, int(max_tokens), self.head_dim, self.device)
 
     # -- the block on device tensors: x [B, L, d_model] -> [B, L, d_model]; state is advanced by L
     def forward_device(self, x, state, position=None):
@@ -277,42 +334,46 @@ class TransformerBlock(object):
                              self.rope_theta)
             qr = torch.empty(q.shape, dtype=torch.float32, device=dev)
             kr = torch.empty(k.shape, dtype=torch.float32, device=dev)
-            _native.call("b200i_rope_apply", dev.index, st, _vp(qr), _vp(q), _vp(cosv), _vp(sinv), m, l, self.n_heads, self.head_dim,
+            _native.call("b200i_rope_apply", dev.index, st, _vp(qr), _vp(q), _vp(cosv), _vp(sinv), m, l, self.heads_local, self.head_dim,
                          ld)
-            _native.call("b200i_rope_apply", dev.index, st, _vp(kr), _vp(k), _vp(cosv), _vp(sinv), m, l, self.n_kv_heads,
+            _native.call("b200i_rope_apply", dev.index, st, _vp(kr), _vp(k), _vp(cosv), _vp(sinv), m, l, self.kv_local,
                          self.head_dim, ld)
         else:
             qr, kr = q.contiguous(), k.contiguous()
         cap = state.max_tokens
         used = pos0 + l
-        ctx = torch.empty((m, self.n_heads * self.head_dim), dtype=torch.float32, device=dev)
+        ctx = torch.empty((m, self.heads_local * self.head_dim), dtype=torch.float32, device=dev)
         if position is None:
-            _native.call("b200i_kv_append", dev.index, st, _vp(state.k), _vp(kr), b, l, self.n_kv_heads, self.head_dim, cap, pos0, 0)
-            _native.call("b200i_kv_append", dev.index, st, _vp(state.v), _vp(v), b, l, self.n_kv_heads, self.head_dim, cap, pos0, ld)
+            _native.call("b200i_kv_append", dev.index, st, _vp(state.k), _vp(kr), b, l, self.kv_local, self.head_dim, cap, pos0, 0)
+            _native.call("b200i_kv_append", dev.index, st, _vp(state.v), _vp(v), b, l, self.kv_local, self.head_dim, cap, pos0, ld)
             s = used - (max(0, pos0 - (self.window - 1)) if self.window else 0)
-            scores = torch.empty((b * self.n_heads * l * s,), dtype=torch.float32, device=dev)
+            scores = torch.empty((b * self.heads_local * l * s,), dtype=torch.float32, device=dev)
             _native.call("b200i_attention", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
-                         self.n_heads, self.n_kv_heads, self.head_dim, cap, used, self.window)
+                         self.heads_local, self.kv_local, self.head_dim, cap, used, self.window)
         else:
-            _native.call("b200i_kv_append_at", dev.index, st, _vp(state.k), _vp(kr), b, l, self.n_kv_heads, self.head_dim, cap,
+            _native.call("b200i_kv_append_at", dev.index, st, _vp(state.k), _vp(kr), b, l, self.kv_local, self.head_dim, cap,
                          _vp(position), 0)
-            _native.call("b200i_kv_append_at", dev.index, st, _vp(state.v), _vp(v), b, l, self.n_kv_heads, self.head_dim, cap,
+            _native.call("b200i_kv_append_at", dev.index, st, _vp(state.v), _vp(v), b, l, self.kv_local, self.head_dim, cap,
                          _vp(position), ld)
             s = min(cap, self.window - 1 + l) if self.window else cap  # the most keys any later position sees
-            scores = torch.empty((b * self.n_heads * l * s,), dtype=torch.float32, device=dev)
+            scores = torch.empty((b * self.heads_local * l * s,), dtype=torch.float32, device=dev)
             _native.call("b200i_attention_at", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
-                         self.n_heads, self.n_kv_heads, self.head_dim, cap, _vp(position), self.window)
+                         self.heads_local, self.kv_local, self.head_dim, cap, _vp(position), self.window)
         del scores
+        if self.group is not None:
+            ctx = gather_columns(ctx, self.group)  # heads are rank-major, so the gathered columns are in head order
         r1 = add(x2, self.o(ctx))
         n2 = norm(r1, self.norm2_w, self.norm2_b, self.norm_eps, self.norm_kind)
         if self.gateup is not None:
             fused = self.gateup(n2)
-            gate, up, gld = fused[:, :self.inter], fused[:, self.inter:], fused.shape[1]
+            gate, up, gld = fused[:, :self.inter_local], fused[:, self.inter_local:], fused.shape[1]
         else:
             up, gld = self.up(n2), 0
             gate = self.gate(n2) if self.gated else None
-        act = torch.empty((m, self.inter), dtype=torch.float32, device=dev)
-        _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(gate), _vp(up), m, self.inter, gld, self.mlp_kind)
+        act = torch.empty((m, self.inter_local), dtype=torch.float32, device=dev)
+        _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(gate), _vp(up), m, self.inter_local, gld, self.mlp_kind)
+        if self.group is not None:
+            act = gather_columns(act, self.group)
         y = add(r1, self.down(act))
         state.cached_tokens = used
         return y.reshape(b, l, dm)
