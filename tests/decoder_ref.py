@@ -111,6 +111,57 @@ def random_lm_weights(cfg, seed, scale=0.02):
     return w
 
 
+def lcg_floats(n, seed, lo=-0.125, hi=0.125):
+    """`n` float32 values in [lo, hi) from the 64-bit LCG of the reference's synthetic checkpoints
+    (python/mojolearn/_causal_lm_fixtures.py:38-47): hashed, not random, the same bytes on every machine."""
+    mask = (1 << 64) - 1
+    x = (seed * 6364136223846793005 + 1442695040888963407) & mask
+    out = np.empty(n, np.float32)
+    for i in range(n):
+        x = (x * 6364136223846793005 + 1442695040888963407) & mask
+        out[i] = np.float32(lo + (hi - lo) * ((x >> 11) / float(1 << 53)))
+    return out
+
+
+class LlamaFixtureConfig(object):
+    """The Llama row of the reference's loaded-model fixtures (_causal_lm_fixtures.py:68-79): two layers, two heads
+    over one KV head, head_dim 16, an untied head, a vocabulary of 64."""
+    vocab, d_model, n_layers, n_heads, n_kv_heads, head_dim, intermediate = 64, 32, 2, 2, 1, 16, 64
+    norm, norm_eps, norm_bias, mlp, mlp_bias, qkv_bias, o_bias = "rmsnorm", 1e-6, False, "swiglu", False, False, False
+    positions, rope_theta, max_positions, window = "rope", 10000.0, 128, 0
+
+
+def llama_fixture_weights(seed=1):
+    """The tensors of that checkpoint (_causal_lm_fixtures.py:81-102), by HuggingFace name."""
+    c = LlamaFixtureConfig
+    dm, nh, nkv, hd, it, v = c.d_model, c.n_heads, c.n_kv_heads, c.head_dim, c.intermediate, c.vocab
+
+    def f32(shape, sd, lo=-0.125, hi=0.125):
+        return lcg_floats(shape[0] * shape[1], sd, lo, hi).reshape(shape)
+
+    w = {"model.embed_tokens.weight": f32((v, dm), seed + 1, -0.5, 0.5), "model.norm.weight": np.ones(dm, np.float32),
+         "lm_head.weight": f32((v, dm), seed + 2, -0.5, 0.5)}
+    for i in range(c.n_layers):
+        p, s = "model.layers.%d." % i, seed + 10 * (i + 1)
+        w[p + "input_layernorm.weight"] = np.ones(dm, np.float32)
+        w[p + "post_attention_layernorm.weight"] = np.ones(dm, np.float32)
+        w[p + "self_attn.q_proj.weight"] = f32((nh * hd, dm), s + 1)
+        w[p + "self_attn.k_proj.weight"] = f32((nkv * hd, dm), s + 2)
+        w[p + "self_attn.v_proj.weight"] = f32((nkv * hd, dm), s + 3)
+        w[p + "self_attn.o_proj.weight"] = f32((dm, nh * hd), s + 4)
+        w[p + "mlp.gate_proj.weight"] = f32((it, dm), s + 5)
+        w[p + "mlp.up_proj.weight"] = f32((it, dm), s + 6)
+        w[p + "mlp.down_proj.weight"] = f32((dm, it), s + 7)
+    return w
+
+
+def fixture_ids(X, b, l, vocab):
+    """A (b, l) int32 token stream: the first b*l BYTES of the fixture, modulo the vocabulary
+    (the verify table's hf-causal-lm lane, tools/identity_break.py:3038-3044)."""
+    raw = np.frombuffer(np.ascontiguousarray(X).tobytes()[: b * l], dtype=np.uint8)
+    return np.ascontiguousarray((raw.astype(np.int32) % vocab).reshape(b, l))
+
+
 class OracleLM(object):
     def __init__(self, cfg, weights):
         self.cfg, self.w = cfg, weights

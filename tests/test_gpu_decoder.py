@@ -140,3 +140,23 @@ def test_norm_kernel_row_widths_and_kinds():
             got = transformer.norm(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(),
                                    None if b is None else torch.from_numpy(b).cuda(), 1e-6, kind)
             assert got.cpu().numpy().tobytes() == want.tobytes(), (rows, dm, kind)
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+def test_hf_causal_lm_infer_cell_on_gpu(kind):
+    """The verify table's `hf-causal-lm` lane, `infer` column, on the CUDA path: logits of the Llama-shaped synthetic
+    checkpoint on ids cut from the held-out fixture, against the reference's own hash; a prefill of 11 tokens plus
+    one step (launch by launch and replayed from the graph) gives the same last-position logits."""
+    c = decoder_ref.LlamaFixtureConfig
+    cfg = CausalLMConfig(vocab=c.vocab, d_model=c.d_model, n_layers=c.n_layers, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
+                         head_dim=c.head_dim, intermediate=c.intermediate, norm_eps=c.norm_eps, rope_theta=c.rope_theta,
+                         max_positions=c.max_positions)
+    lm = CausalLM(cfg, decoder_ref.llama_fixture_weights())
+    ids = decoder_ref.fixture_ids(fixtures.fixture(kind, seed=1), 4, 12, c.vocab)
+    logits = lm.forward(ids)
+    assert oracle.sha16(logits) == TABLE["cells"]["hf-causal-lm/%s" % kind]["infer"]
+    state = lm.allocate_state(4, 12)
+    lm.forward(ids[:, :11], state)
+    assert lm.step(ids[:, 11], state).tobytes() == np.ascontiguousarray(logits[:, 11, :]).tobytes()
+    seq = lm.generate(ids[:, :6], 6)
+    assert seq.tolist() == lm.generate(ids[:, :6], 6, graph=False).tolist()

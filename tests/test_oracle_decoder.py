@@ -87,3 +87,13 @@ def test_decode_equals_prefill_and_rows_are_independent(opts):
 def test_argmax_ties_go_to_the_lowest_id():
     logits = np.array([[1.0, 3.0, 3.0, -1.0], [0.0, -0.0, 0.0, 0.0], [np.nan, 2.0, 1.0, 2.0]], dtype=np.float32)
     assert oracle.argmax(logits).tolist() == [1, 0, 0]
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+def test_hf_causal_lm_infer_cell(kind):
+    """The verify table's `hf-causal-lm` lane, `infer` column: the logits of the Llama-shaped synthetic checkpoint
+    (embedding, two rotary GQA blocks, final RMSNorm, untied head) on 4 x 12 ids cut from the held-out fixture's
+    bytes. Pins the whole decoder, embedding to head, on the reference's own hash."""
+    ids = decoder_ref.fixture_ids(fixtures.fixture(kind, seed=1), 4, 12, decoder_ref.LlamaFixtureConfig.vocab)
+    lm = decoder_ref.OracleLM(decoder_ref.LlamaFixtureConfig, decoder_ref.llama_fixture_weights())
+    assert oracle.sha16(lm.forward(ids)) == TABLE["cells"]["hf-causal-lm/%s" % kind]["infer"]
