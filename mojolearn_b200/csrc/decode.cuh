@@ -44,7 +44,8 @@ constexpr int DEC_THREADS = 32 * (DEC_CONSUMERS + 1);
 constexpr int DEC_FOLD_ROWS = 64;            // rows whose partials are folded together
 __host__ __device__ constexpr int dec_max_chunk(int m) { return m <= 2 ? 4096 : 1024; } // bytes of one weight row per stage, at most
 constexpr int DEC_X_STAGE_BYTES = 16384;     // activation bytes per stage, at most
-constexpr int DEC_SMEM_LIMIT = 220 * 1024;
+constexpr int DEC_SMEM_LIMIT = 220 * 1024;      // one CTA per SM
+constexpr int DEC_SMEM_LIMIT_PAIR = 110 * 1024; // two CTAs per SM: twice the serial chains in flight, half the ring each
 constexpr unsigned DEC_SPIN_LIMIT = 1u << 22;
 
 __device__ int g_decode_status = 0; // 0 = ok; nonzero = a bounded wait ran out (value says where)
@@ -61,7 +62,7 @@ struct DecodeLayout {
 
 __host__ __device__ inline int dec_esize(int wkind) { return wkind == W_F32 ? 4 : (wkind == W_BF16 ? 2 : 1); }
 
-__host__ __device__ inline DecodeLayout decode_layout(int m, int k, int wkind) {
+__host__ __device__ inline DecodeLayout decode_layout(int m, int k, int wkind, int smem_limit = DEC_SMEM_LIMIT) {
     DecodeLayout l;
     const int es = dec_esize(wkind);
     const int leaf = (int)leaf_size(k), leaves = (int)leaf_count(k);
@@ -81,7 +82,7 @@ __host__ __device__ inline DecodeLayout decode_layout(int m, int k, int wkind) {
     off += (size_t)m * leaves * DEC_FOLD_ROWS * 4;
     off = (off + 127) / 128 * 128;
     l.stage_off = off;
-    long long room = (long long)DEC_SMEM_LIMIT - 256 - (long long)off;
+    long long room = (long long)smem_limit - 256 - (long long)off;
     int stages = room > 0 ? (int)(room / (long long)l.stage_bytes) : 0;
     if (stages > 6) stages = 6;
     l.stages = stages;
@@ -234,10 +235,10 @@ __device__ __forceinline__ unsigned leaf_x_key(const float *xs, int xstride, int
 }
 
 template <int WK, int M>
-__global__ void __launch_bounds__(DEC_THREADS, 1) decode_kernel(const GemmArgs g) {
+__global__ void __launch_bounds__(DEC_THREADS, 2) decode_kernel(const GemmArgs g) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int DEC_RW = dec_rw(M), DEC_SUBS = 32 / DEC_RW;
-    const DecodeLayout lay = decode_layout(M, g.k, WK);
+    const DecodeLayout lay = decode_layout(M, g.k, WK, g.dec_smem_limit);
     float *part = reinterpret_cast<float *>(smem + lay.part_off);
     unsigned char *stage_base = smem + lay.stage_off;
     unsigned long long *full = reinterpret_cast<unsigned long long *>(smem + lay.bar_off);
@@ -423,9 +424,16 @@ inline int launch_decode_m(const GemmArgs &g, int grid, size_t smem, cudaStream_
 }
 
 // Returns the number of kernels launched.
-inline int launch_decode(const GemmArgs &g, int sms, cudaStream_t st) {
-    const DecodeLayout lay = decode_layout(g.m, g.k, g.wkind);
-    int grid = sms;
+inline int launch_decode(const GemmArgs &g_in, int sms, cudaStream_t st) {
+    GemmArgs g = g_in;
+    // Low-bit weights at one or two activation rows are bound by the latency of the serial chains, not by the
+    // stream: two CTAs per SM (a ring of at least two stages each) double the chains in flight. Float32
+    // weights already run at the stream's rate with one CTA and the deeper ring.
+    const DecodeLayout pair = decode_layout(g.m, g.k, g.wkind, DEC_SMEM_LIMIT_PAIR);
+    const bool two = g.wkind != W_F32 && pair.stages >= 2 && (long long)g.n >= 16ll * sms;
+    g.dec_smem_limit = two ? DEC_SMEM_LIMIT_PAIR : DEC_SMEM_LIMIT;
+    const DecodeLayout lay = decode_layout(g.m, g.k, g.wkind, g.dec_smem_limit);
+    int grid = sms * (two ? 2 : 1);
     const int max_grid = (g.n + 7) / 8; // no CTA with fewer than ~8 rows
     if (grid > max_grid) grid = max_grid;
     if (grid < 1) grid = 1;

@@ -36,6 +36,7 @@ struct GemmArgs {
     int group_leaves, groups; // S (a power of two) and ceil(P / S)
     int vec_a, vec_b, vec_c;  // operand may be read / written with 128-bit accesses
     int tiles_n;
+    int dec_smem_limit;       // decode plan: shared memory a CTA may use (decides one or two CTAs per SM)
 };
 
 constexpr int KS = 16;       // k-steps per staged window
