@@ -188,6 +188,18 @@ int64_t b200i_host_gemm_int8(int64_t device, float *c, const int8_t *qa, const i
  * out and x are [rows, width]; transformer_oracle.mojo:1223-1341. */
 int64_t b200i_norm(int64_t device, void *stream, float *out, const float *x, const float *w, const float *bias, int64_t rows,
                    int64_t width, double eps, int64_t kind, char *err, int64_t err_cap);
+/* The residual add and the norm that follows it in one pass: sum_out = ftz(ftz(x) + ftz(delta)) (S22 / S23),
+ * out = norm(sum_out) as b200i_norm. Same bits as b200i_add then b200i_norm. */
+int64_t b200i_add_norm(int64_t device, void *stream, float *out, float *sum_out, const float *x, const float *delta, const float *w,
+                       const float *bias, int64_t rows, int64_t width, double eps, int64_t kind, char *err, int64_t err_cap);
+/* The fresh q | k | v rows of a call in one pass: q rotated into qr [b*l, n_heads*head_dim], k rotated into its cache
+ * slots, v copied into its cache slots: b200i_rope_apply on q and k plus b200i_kv_append on k and v, same bits.
+ * Sources share the row pitch src_ld (they may be column blocks of one fused product); cosv / sinv NULL = no rotation;
+ * `position` not NULL = the cached-token count is read from that device word (as the _at entries), else pos0. */
+int64_t b200i_qkv_rope_cache(int64_t device, void *stream, float *qr, float *kcache, float *vcache, const float *q, const float *k,
+                             const float *v, int64_t src_ld, const float *cosv, const float *sinv, int64_t b, int64_t l,
+                             int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap, int64_t pos0, const int32_t *position,
+                             char *err, int64_t err_cap);
 /* cos and sin [l, head_dim/2] for absolute positions pos0 .. pos0+l-1 (S6-S8); positions stay below 8192. */
 int64_t b200i_rope_table(int64_t device, void *stream, float *cosv, float *sinv, int64_t pos0, int64_t l, int64_t head_dim,
                          double theta, char *err, int64_t err_cap);

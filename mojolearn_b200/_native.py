@@ -68,6 +68,8 @@ SIGNATURES = {
     "b200i_host_gemm_int8": [I64, VP, VP, VP, VP, VP, I64, I64, I64, VP, I64],
     "b200i_decode_status": [I64],
     "b200i_norm": [I64, VP, VP, VP, VP, VP, I64, I64, F64, I64, VP, I64],
+    "b200i_add_norm": [I64, VP, VP, VP, VP, VP, VP, VP, I64, I64, F64, I64, VP, I64],
+    "b200i_qkv_rope_cache": [I64, VP, VP, VP, VP, VP, VP, VP, I64, VP, VP, I64, I64, I64, I64, I64, I64, I64, VP, VP, I64],
     "b200i_rope_table": [I64, VP, VP, VP, I64, I64, I64, F64, VP, I64],
     "b200i_rope_apply": [I64, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, VP, I64],
     "b200i_kv_append": [I64, VP, VP, VP, I64, I64, I64, I64, I64, I64, I64, VP, I64],

@@ -769,11 +769,67 @@ int64_t b200i_norm(int64_t device, void *stream, float *out, const float *x, con
             CUDA_TRY(cudaFuncSetAttribute(norm_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             configured[dev] = true;
         }
-        norm_rows_kernel<<<(unsigned)((rows + wpc - 1) / wpc), 32 * wpc, smem, st>>>(out, x, w, bias, rows, (int)width, (float)eps, (int)kind);
+        norm_rows_kernel<<<(unsigned)((rows + wpc - 1) / wpc), 32 * wpc, smem, st>>>(out, x, w, bias, rows, (int)width, (float)eps, (int)kind,
+                                                                                     nullptr, nullptr);
     } else {
         const long long threads = rows * 32;
         norm_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(out, x, w, bias, rows, (int)width, (float)eps, (int)kind);
     }
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_add_norm(int64_t device, void *stream, float *out, float *sum_out, const float *x, const float *delta, const float *w,
+                       const float *bias, int64_t rows, int64_t width, double eps, int64_t kind, char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (rows <= 0 || width <= 0 || !out || !sum_out || !x || !delta || !w) return fail(err, err_cap, "add_norm: bad arguments");
+    if (kind < NORM_RMS || kind > NORM_RMS_OFFSET) return fail(err, err_cap, "norm: norm kind %lld is not spelled", (long long)kind);
+    if (bias && kind != NORM_LAYER) return fail(err, err_cap, "norm: an RMSNorm carries no bias (norm_bias needs layernorm)");
+    const int wpc = rows >= 1024 ? 4 : 1;
+    const size_t smem = (size_t)wpc * (size_t)((width + 3) & ~3ll) * sizeof(float);
+    if (smem <= 200 * 1024) {
+        static bool configured[64] = {};
+        if (dev >= 0 && dev < 64 && !configured[dev]) {
+            CUDA_TRY(cudaFuncSetAttribute(norm_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            configured[dev] = true;
+        }
+        norm_rows_kernel<<<(unsigned)((rows + wpc - 1) / wpc), 32 * wpc, smem, st>>>(out, x, w, bias, rows, (int)width, (float)eps, (int)kind,
+                                                                                     delta, sum_out);
+        g_launches++;
+    } else { // a row too wide for shared memory: the two seams one after the other
+        const long long count = rows * width;
+        add_kernel<<<grid_for(count, 256, sm_count(dev)), 256, 0, st>>>(sum_out, x, delta, count);
+        norm_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(out, sum_out, w, bias, rows, (int)width, (float)eps, (int)kind);
+        g_launches += 2;
+    }
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_qkv_rope_cache(int64_t device, void *stream, float *qr, float *kcache, float *vcache, const float *q, const float *k,
+                             const float *v, int64_t src_ld, const float *cosv, const float *sinv, int64_t b, int64_t l,
+                             int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap, int64_t pos0, const int32_t *position,
+                             char *err, int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (b <= 0 || l <= 0 || n_heads <= 0 || n_kv <= 0 || head_dim <= 0 || (head_dim & 1) || !qr || !kcache || !vcache || !q || !k || !v ||
+        qr == q)
+        return fail(err, err_cap, "qkv_rope_cache: bad arguments");
+    if ((cosv == nullptr) != (sinv == nullptr)) return fail(err, err_cap, "qkv_rope_cache: give both tables or neither");
+    if (!position) {
+        if (pos0 < 0) return fail(err, err_cap, "qkv_rope_cache: bad arguments");
+        if (pos0 + l > cap)
+            return fail(err, err_cap, "transformer: this call would use %lld KV slots and the cache holds %lld REFUSED", (long long)(pos0 + l),
+                        (long long)cap);
+    } else if (l > cap) {
+        return fail(err, err_cap, "qkv_rope_cache: bad arguments");
+    }
+    const long long total = b * l * (n_heads + 2 * n_kv) * head_dim;
+    const long long ldq = src_ld ? src_ld : n_heads * head_dim, ldkv = src_ld ? src_ld : n_kv * head_dim;
+    if (ldq < n_heads * head_dim || ldkv < n_kv * head_dim) return fail(err, err_cap, "qkv_rope_cache: the row pitch is below the row width");
+    qkv_rope_cache_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(qr, kcache, vcache, q, k, v, ldq, ldkv, cosv, sinv, (int)b, (int)l,
+                                                                           (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, (int)pos0,
+                                                                           position, cosv ? 1 : 0);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;

@@ -40,8 +40,11 @@ constexpr int ACT_SWIGLU = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3,
 // magnitude each square is a normal number, the accumulator only grows, and no
 // step result can be subnormal, so the bare fma is the contract's step.
 constexpr unsigned NORM_ADMIT_MIN = (64u << 24) - 2u;
+// With `delta` the row normalised is the residual sum ftz(ftz(src) + ftz(delta)) (seam S22 / S23), which is
+// also written to `sum_out`: the residual add and the norm that always follows it, in one pass over the row.
 __global__ void norm_rows_kernel(float *__restrict__ out, const float *__restrict__ src, const float *__restrict__ w,
-                                 const float *__restrict__ bias, long long rows, int dm, float eps, int kind) {
+                                 const float *__restrict__ bias, long long rows, int dm, float eps, int kind,
+                                 const float *__restrict__ delta, float *__restrict__ sum_out) {
     extern __shared__ __align__(16) float norm_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
@@ -49,7 +52,10 @@ __global__ void norm_rows_kernel(float *__restrict__ out, const float *__restric
     const int pitch = (dm + 3) & ~3;
     float *xs = norm_smem + (size_t)warp * pitch;
     const float *x = src + row * dm;
-    const bool vec = (dm % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    const float *dl = delta ? delta + row * dm : nullptr;
+    float *so = sum_out ? sum_out + row * dm : nullptr;
+    const bool vec = (dm % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                     (!dl || ((reinterpret_cast<uintptr_t>(dl) & 15) == 0 && (reinterpret_cast<uintptr_t>(so) & 15) == 0));
     unsigned key = 0xFFFFFFFFu;
     if (vec) {
         // eight 128-bit loads per lane in flight: a lone warp has no other warp to hide a load behind
@@ -58,19 +64,33 @@ __global__ void norm_rows_kernel(float *__restrict__ out, const float *__restric
 #pragma unroll
             for (int u = 0; u < 8; u++)
                 v[u] = (j0 + u * 128 < dm) ? *reinterpret_cast<const float4 *>(x + j0 + u * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (dl) {
+                float4 d[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    d[u] = (j0 + u * 128 < dm) ? *reinterpret_cast<const float4 *>(dl + j0 + u * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    v[u].x = __fadd_rn(ftz_bits(v[u].x), ftz_bits(d[u].x)); v[u].y = __fadd_rn(ftz_bits(v[u].y), ftz_bits(d[u].y));
+                    v[u].z = __fadd_rn(ftz_bits(v[u].z), ftz_bits(d[u].z)); v[u].w = __fadd_rn(ftz_bits(v[u].w), ftz_bits(d[u].w));
+                }
+            }
 #pragma unroll
             for (int u = 0; u < 8; u++) {
                 if (j0 + u * 128 >= dm) break;
                 v[u].x = ftz_bits(v[u].x); v[u].y = ftz_bits(v[u].y); v[u].z = ftz_bits(v[u].z); v[u].w = ftz_bits(v[u].w);
                 key = min(min(key, admit_key(v[u].x)), min(admit_key(v[u].y), min(admit_key(v[u].z), admit_key(v[u].w))));
                 *reinterpret_cast<float4 *>(xs + j0 + u * 128) = v[u];
+                if (so) *reinterpret_cast<float4 *>(so + j0 + u * 128) = v[u];
             }
         }
     } else {
         for (int j = lane; j < dm; j += 32) {
-            const float v = ftz_bits(x[j]);
+            float v = ftz_bits(x[j]);
+            if (dl) v = ftz_bits(__fadd_rn(v, ftz_bits(dl[j])));
             key = min(key, admit_key(v));
             xs[j] = v;
+            if (so) so[j] = v;
         }
     }
     for (int j = dm + lane; j < pitch; j += 32) xs[j] = 0.f;
@@ -258,6 +278,45 @@ __global__ void kv_append_kernel(float *__restrict__ cache, const float *__restr
     const int bb = (int)(t / l), li = (int)(t % l);
     if (pos0 + li >= cap) return; // the host refuses such a call; a replayed graph must not write past the cache either
     cache[(((long long)bb * n_kv + kv) * cap + pos0 + li) * hd + d] = src[t * ld + (long long)kv * hd + d];
+}
+
+// One pass over the fresh q | k | v rows of a call: q rotated into `qr` (contiguous), k rotated straight into its
+// cache slot, v copied into its cache slot. The arithmetic per element is rope_apply_kernel's (S9-S10) and the
+// placement kv_append_kernel's; `rope` = 0 copies q and k unrotated. q has row pitch ldq, k and v ldkv.
+__global__ void qkv_rope_cache_kernel(float *__restrict__ qr, float *__restrict__ kcache, float *__restrict__ vcache,
+                                      const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                      long long ldq, long long ldkv, const float *__restrict__ cosv, const float *__restrict__ sinv, int b, int l,
+                                      int nh, int nkv, int hd, int cap, int pos0, const int *__restrict__ pos_dev, int rope) {
+    if (pos_dev) pos0 = *pos_dev;
+    const long long wq = (long long)nh * hd, wk = (long long)nkv * hd, per_row = wq + 2 * wk;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)b * l * per_row) return;
+    const long long t = idx / per_row;
+    const long long c = idx % per_row;
+    const int li = (int)(t % l), bb = (int)(t / l), half = hd / 2;
+    const float *src = c < wq ? q : (c < wq + wk ? k : v);
+    const long long col = c < wq ? c : (c < wq + wk ? c - wq : c - wq - wk);
+    const long long si = t * (c < wq ? ldq : ldkv) + col;
+    const int j = (int)(col % hd);
+    float val;
+    if (c < wq + wk && rope) {
+        const int ci = j < half ? j : j - half;
+        const float partner = j < half ? -ftz_bits(src[si + half]) : ftz_bits(src[si - half]);
+        const float cs = ftz_bits(cosv[li * half + ci]), sn = ftz_bits(sinv[li * half + ci]);
+        const float pa = ftz_bits(__fmul_rn(ftz_bits(src[si]), cs));
+        const float pb = ftz_bits(__fmul_rn(partner, sn));
+        val = ftz_bits(__fadd_rn(pa, pb));
+    } else {
+        val = src[si];
+    }
+    if (c < wq) {
+        qr[t * wq + col] = val;
+    } else {
+        if (pos0 + li >= cap) return; // the host refuses such a call; a replayed graph must not write past the cache either
+        float *cache = c < wq + wk ? kcache : vcache;
+        const int kv = (int)(col / hd);
+        cache[(((long long)bb * nkv + kv) * cap + pos0 + li) * hd + j] = val;
+    }
 }
 
 // ---- a position read on the device ------------------------------------------------------------

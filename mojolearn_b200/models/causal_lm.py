@@ -28,7 +28,7 @@ import torch
 
 from .. import _native
 from ..parallel import gather_columns, shard_bounds
-from ..transformer import Linear, ShardedLinear, TransformerBlock, TransformerState, _stream, _vector, _vp, add, norm, NORM_KINDS
+from ..transformer import Linear, ShardedLinear, TransformerBlock, TransformerState, _stream, _vector, _vp, add, add_norm, norm, NORM_KINDS
 
 
 class CausalLMConfig(object):
@@ -136,10 +136,16 @@ class CausalLM(object):
             else:
                 _native.call("b200i_add_positions_at", dev.index, st, _vp(x), _vp(self.pos_table), b * l, l, _vp(position),
                              cfg.d_model)
-        h = x.reshape(b, l, cfg.d_model)
+        h, delta = x.reshape(b, l, cfg.d_model), None
+        rope = None  # one rotary table per call: every block is at the same positions
+        if self.blocks and self.blocks[0].rope:
+            rope = self.blocks[0].rope_tables(state.positions, l, position)
         for blk, bs in zip(self.blocks, state.layers):
-            h = blk.forward_device(h, bs, position)
-        return norm(h.reshape(b * l, cfg.d_model), self.final_w, self.final_b, cfg.norm_eps, NORM_KINDS[cfg.norm])
+            h, delta = blk.forward_device(h, bs, position, rope, delta, defer_add=True)  # each block's last add rides in the next norm
+        h2 = h.reshape(b * l, cfg.d_model)
+        if delta is None:
+            return norm(h2, self.final_w, self.final_b, cfg.norm_eps, NORM_KINDS[cfg.norm])
+        return add_norm(h2, delta, self.final_w, self.final_b, cfg.norm_eps, NORM_KINDS[cfg.norm])[1]
 
     def check_ids(self):
         """Raise if any id given since the last check was outside the vocabulary (reads one device word)."""

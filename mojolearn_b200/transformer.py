@@ -174,6 +174,15 @@ def norm(x2d, w, bias, eps, kind):
     return out
 
 
+def add_norm(x2d, delta, w, bias, eps, kind):
+    """(x + delta, norm(x + delta)): the residual add and the norm that follows it, one pass over the rows."""
+    out, total = torch.empty_like(x2d), torch.empty_like(x2d)
+    dev = x2d.device
+    _native.call("b200i_add_norm", dev.index, _stream(dev), _vp(out), _vp(total), _vp(x2d), _vp(delta.contiguous()), _vp(w), _vp(bias),
+                 x2d.shape[0], x2d.shape[1], float(eps), kind)
+    return total, out
+
+
 def add(a, b):
     out = torch.empty_like(a)
     dev = a.device
@@ -300,11 +309,26 @@ class TransformerBlock(object):
     def allocate_state(self, batch, max_tokens):
         return TransformerState(batch, self.kv_local, int(max_tokens), self.head_dim, self.device)
 
+    def rope_tables(self, pos0, l, position=None):
+        """cos and sin [l, head_dim / 2] for this call's positions; the same for every block of a model."""
+        dev, st = self.device, _stream(self.device)
+        cosv = torch.empty((l, self.head_dim // 2), dtype=torch.float32, device=dev)
+        sinv = torch.empty_like(cosv)
+        if position is None:
+            _native.call("b200i_rope_table", dev.index, st, _vp(cosv), _vp(sinv), pos0, l, self.head_dim, self.rope_theta)
+        else:
+            _native.call("b200i_rope_table_at", dev.index, st, _vp(cosv), _vp(sinv), _vp(position), l, self.head_dim,
+                         self.rope_theta)
+        return cosv, sinv
+
     # -- the block on device tensors: x [B, L, d_model] -> [B, L, d_model]; state is advanced by L
-    def forward_device(self, x, state, position=None):
+    def forward_device(self, x, state, position=None, rope=None, delta=None, defer_add=False):
         """`position`, when given, is a device int32 word holding the tokens cached before this call: the
         position-dependent kernels read it instead of taking the host's count as an argument, so the launches
-        can be captured in a CUDA graph and replayed at later positions (the host count still sizes and checks)."""
+        can be captured in a CUDA graph and replayed at later positions (the host count still sizes and checks).
+        `rope` = the (cos, sin) tables of this call when the caller has them (a model computes them once for all
+        its blocks). `delta` [B*L, d_model] = a residual update of x not yet added: the add rides in the first
+        norm's pass. With `defer_add` the block returns (r, d) with its output = r + d left to the next norm."""
         b, l, dm = x.shape
         if dm != self.d_model:
             raise ValueError("x has width %d, the block %d" % (dm, self.d_model))
@@ -316,45 +340,31 @@ class TransformerBlock(object):
             raise ValueError("transformer: absolute position %d is at or beyond %d" % (pos0 + l - 1, MAX_POSITIONS))
         dev, st = x.device, _stream(x.device)
         x2 = x.reshape(m, dm).contiguous()
-        n1 = norm(x2, self.norm1_w, self.norm1_b, self.norm_eps, self.norm_kind)
+        if delta is None:
+            n1 = norm(x2, self.norm1_w, self.norm1_b, self.norm_eps, self.norm_kind)
+        else:
+            x2, n1 = add_norm(x2, delta, self.norm1_w, self.norm1_b, self.norm_eps, self.norm_kind)
         if self.qkv is not None:
             fused = self.qkv(n1)
             wq, wk, wv = self.widths
             q, k, v, ld = fused[:, :wq], fused[:, wq:wq + wk], fused[:, wq + wk:], fused.shape[1]
         else:
             q, k, v, ld = self.q(n1), self.k(n1), self.v(n1), 0
+        cosv = sinv = None
         if self.rope:
-            half = self.head_dim // 2
-            cosv = torch.empty((l, half), dtype=torch.float32, device=dev)
-            sinv = torch.empty_like(cosv)
-            if position is None:
-                _native.call("b200i_rope_table", dev.index, st, _vp(cosv), _vp(sinv), pos0, l, self.head_dim, self.rope_theta)
-            else:
-                _native.call("b200i_rope_table_at", dev.index, st, _vp(cosv), _vp(sinv), _vp(position), l, self.head_dim,
-                             self.rope_theta)
-            qr = torch.empty(q.shape, dtype=torch.float32, device=dev)
-            kr = torch.empty(k.shape, dtype=torch.float32, device=dev)
-            _native.call("b200i_rope_apply", dev.index, st, _vp(qr), _vp(q), _vp(cosv), _vp(sinv), m, l, self.heads_local, self.head_dim,
-                         ld)
-            _native.call("b200i_rope_apply", dev.index, st, _vp(kr), _vp(k), _vp(cosv), _vp(sinv), m, l, self.kv_local,
-                         self.head_dim, ld)
-        else:
-            qr, kr = q.contiguous(), k.contiguous()
+            cosv, sinv = rope if rope is not None else self.rope_tables(pos0, l, position)
         cap = state.max_tokens
         used = pos0 + l
+        qr = torch.empty((m, self.heads_local * self.head_dim), dtype=torch.float32, device=dev)
         ctx = torch.empty((m, self.heads_local * self.head_dim), dtype=torch.float32, device=dev)
+        _native.call("b200i_qkv_rope_cache", dev.index, st, _vp(qr), _vp(state.k), _vp(state.v), _vp(q), _vp(k), _vp(v), ld,
+                     _vp(cosv), _vp(sinv), b, l, self.heads_local, self.kv_local, self.head_dim, cap, pos0, _vp(position))
         if position is None:
-            _native.call("b200i_kv_append", dev.index, st, _vp(state.k), _vp(kr), b, l, self.kv_local, self.head_dim, cap, pos0, 0)
-            _native.call("b200i_kv_append", dev.index, st, _vp(state.v), _vp(v), b, l, self.kv_local, self.head_dim, cap, pos0, ld)
             s = used - (max(0, pos0 - (self.window - 1)) if self.window else 0)
             scores = torch.empty((b * self.heads_local * l * s,), dtype=torch.float32, device=dev)
             _native.call("b200i_attention", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
                          self.heads_local, self.kv_local, self.head_dim, cap, used, self.window)
         else:
-            _native.call("b200i_kv_append_at", dev.index, st, _vp(state.k), _vp(kr), b, l, self.kv_local, self.head_dim, cap,
-                         _vp(position), 0)
-            _native.call("b200i_kv_append_at", dev.index, st, _vp(state.v), _vp(v), b, l, self.kv_local, self.head_dim, cap,
-                         _vp(position), ld)
             s = min(cap, self.window - 1 + l) if self.window else cap  # the most keys any later position sees
             scores = torch.empty((b * self.heads_local * l * s,), dtype=torch.float32, device=dev)
             _native.call("b200i_attention_at", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
@@ -362,8 +372,7 @@ class TransformerBlock(object):
         del scores
         if self.group is not None:
             ctx = gather_columns(ctx, self.group)  # heads are rank-major, so the gathered columns are in head order
-        r1 = add(x2, self.o(ctx))
-        n2 = norm(r1, self.norm2_w, self.norm2_b, self.norm_eps, self.norm_kind)
+        r1, n2 = add_norm(x2, self.o(ctx), self.norm2_w, self.norm2_b, self.norm_eps, self.norm_kind)
         if self.gateup is not None:
             fused = self.gateup(n2)
             gate, up, gld = fused[:, :self.inter_local], fused[:, self.inter_local:], fused.shape[1]
@@ -374,9 +383,11 @@ class TransformerBlock(object):
         _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(gate), _vp(up), m, self.inter_local, gld, self.mlp_kind)
         if self.group is not None:
             act = gather_columns(act, self.group)
-        y = add(r1, self.down(act))
+        d = self.down(act)
         state.cached_tokens = used
-        return y.reshape(b, l, dm)
+        if defer_add:
+            return r1.reshape(b, l, dm), d
+        return add(r1, d).reshape(b, l, dm)
 
     def _run(self, x, state):
         host = not isinstance(x, torch.Tensor)
