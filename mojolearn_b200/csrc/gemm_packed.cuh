@@ -30,7 +30,10 @@
 namespace b200i {
 
 constexpr int PK_TILE = 128;                        // rows of A / columns of B per panel and per CTA
-constexpr int PK_STAGES = 6;                        // ring depth
+#ifndef B200I_PK_STAGES
+#define B200I_PK_STAGES 6
+#endif
+constexpr int PK_STAGES = B200I_PK_STAGES;          // ring depth
 constexpr int PK_STAGE_FLOATS = 2 * KS * PK_TILE;   // A window then B window
 constexpr int PK_CONSUMERS = 8;                     // warps (256 threads, 8 x 8 cells each)
 constexpr int PK_THREADS = 32 * PK_CONSUMERS;

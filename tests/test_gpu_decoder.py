@@ -78,7 +78,7 @@ def test_block_subnormal_forcing_inputs():
 
 
 def test_config4_shape_reduced_length():
-    """BASELINE config 4's architecture (12 layers would only repeat the block: 2 here), d_model 768, 12 heads,
+    """The GPT-2-small style benchmark architecture (12 layers would only repeat the block: 2 here), d_model 768, 12 heads,
     MLP 3072 GELU, LayerNorm, learned positions, vocab 50304, batch 8: prompt 24 tokens then 4 greedy steps."""
     cfg = CausalLMConfig(vocab=50304, d_model=768, n_layers=2, n_heads=12, intermediate=3072, norm="layernorm", norm_bias=True,
                          mlp="gelu", mlp_bias=True, qkv_bias=True, o_bias=True, positions="learned", max_positions=64)
@@ -90,7 +90,7 @@ def test_config4_shape_reduced_length():
 
 
 def test_config5_shape_int8_weights_reduced():
-    """BASELINE config 5's layer shapes (d_model 2048, 16 heads of 128, MLP 8192, vocab 50304, INT8 weights with
+    """The serving benchmark's layer shapes (d_model 2048, 16 heads of 128, MLP 8192, vocab 50304, INT8 weights with
     power-of-two row exponents), 1 layer, batch 4, prompt 20 then 3 steps, against the oracle on the materialised weights."""
     cfg = CausalLMConfig(vocab=50304, d_model=2048, n_layers=1, n_heads=16, intermediate=8192, max_positions=64)
     w = decoder_ref.random_lm_weights(cfg, seed=1, scale=0.02)

@@ -149,7 +149,7 @@ def test_tail_shape_1000_cubed_against_cpu_rows():
 
 
 def test_config1_1024_cubed_uniform_seed0():
-    """BASELINE config 1: M = N = K = 1024, U(-1, 1) from seed 0, bit for bit."""
+    """The reference's CPU-runnable benchmark case: M = N = K = 1024, U(-1, 1) from seed 0, bit for bit."""
     rng = np.random.default_rng(0)
     a = rng.uniform(-1.0, 1.0, (1024, 1024)).astype(np.float32)
     b = rng.uniform(-1.0, 1.0, (1024, 1024)).astype(np.float32)
@@ -161,7 +161,7 @@ def test_config1_1024_cubed_uniform_seed0():
 
 @pytest.mark.parametrize("m,n,k", [(4096, 4096, 4096), (8192, 8192, 1024), (128, 11008, 4096), (2048, 50304, 768)])
 def test_config2_full_size_rows_sampled_against_the_oracle(m, n, k):
-    """Full BASELINE sizes: the whole product on the GPU; sampled rows against the
+    """The full sizes of the headline benchmark shapes: the whole product on the GPU; sampled rows against the
     CPU oracle (a row's bits do not depend on the other rows); plans against
     each other on the full output (launch invariance is size independent)."""
     g = torch.Generator(device="cuda").manual_seed(0)

@@ -1,5 +1,5 @@
 """GPU parity for the weight-storage paths: conversions, the int8 / bf16 weight
-products at decode and prefill row counts (BASELINE config 3 shapes), and the
+products at decode and prefill row counts (the serving benchmark's Llama-7B projection shapes), and the
 launch invariance of the decode plan against the tiled and flat plans."""
 import numpy as np
 import pytest
