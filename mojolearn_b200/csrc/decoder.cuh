@@ -537,6 +537,9 @@ __global__ void __launch_bounds__(128) attn_scores_small_kernel(float *__restric
 // value tiles staged in shared memory. The masked scores are overwritten in place
 // by exp(s - max) and then by the weights.
 constexpr int CTX_ROWS = 8, CTX_KT = 32, CTX_MAX_HD = 256;
+// DPL = feature slots per lane (head_dim / 32 rounded up to 1, 2, 4 or 8): a template parameter so that absent
+// slots cost no issue slots.
+template <int DPL>
 __global__ void __launch_bounds__(32 * CTX_ROWS) attn_context_kernel(float *__restrict__ ctx, float *__restrict__ scores,
                                                                       const float *__restrict__ vcache, int b, int l, int nh,
                                                                       int nkv, int hd, int cap, int key_lo, int s, int own0,
@@ -568,11 +571,15 @@ __global__ void __launch_bounds__(32 * CTX_ROWS) attn_context_kernel(float *__re
                 row[j] = e;
             }
             const int cnt = min(32, jhi - j0 + 1);
-            for (int t = 0; t < cnt; t++) den = ftz_hw(__fadd_rn(den, __shfl_sync(0xFFFFFFFFu, e, t)));
+            if (cnt == 32) { // every term is already flushed: add.rn.ftz is the seam's add-then-flush in one instruction
+#pragma unroll
+                for (int t = 0; t < 32; t++) den = add_flushed(den, __shfl_sync(0xFFFFFFFFu, e, t));
+            } else {
+                for (int t = 0; t < cnt; t++) den = add_flushed(den, __shfl_sync(0xFFFFFFFFu, e, t));
+            }
         }
     }
     // S18 + S19 over value tiles shared by the CTA's rows
-    constexpr int DPL = CTX_MAX_HD / 32;
     float acc[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; i++) acc[i] = 0.f;
@@ -596,12 +603,21 @@ __global__ void __launch_bounds__(32 * CTX_ROWS) attn_context_kernel(float *__re
             row[j] = wgt;
         }
         const int a = max(jlo, j0), z = min(jhi, j0 + CTX_KT - 1);
-        for (int jk = a; jk <= z; jk++) {
-            const float wv = __shfl_sync(0xFFFFFFFFu, wgt, jk - j0);
+        if (a == j0 && z == j0 + CTX_KT - 1 && hd == 32 * DPL) { // a whole tile, every slot live: unrolled
 #pragma unroll
-            for (int i = 0; i < DPL; i++) {
-                const int d = lane + 32 * i;
-                if (d < hd) acc[i] = step_flush(wv, vtile[(jk - j0) * hd + d], acc[i]);
+            for (int t = 0; t < CTX_KT; t++) {
+                const float wv = __shfl_sync(0xFFFFFFFFu, wgt, t);
+#pragma unroll
+                for (int i = 0; i < DPL; i++) acc[i] = step_flush(wv, vtile[t * hd + lane + 32 * i], acc[i]);
+            }
+        } else {
+            for (int jk = a; jk <= z; jk++) {
+                const float wv = __shfl_sync(0xFFFFFFFFu, wgt, jk - j0);
+#pragma unroll
+                for (int i = 0; i < DPL; i++) {
+                    const int d = lane + 32 * i;
+                    if (d < hd) acc[i] = step_flush(wv, vtile[(jk - j0) * hd + d], acc[i]);
+                }
             }
         }
     }
