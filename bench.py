@@ -139,7 +139,7 @@ def reference_arm(args, rank, world):
     if rank != 0:
         return
     threads = host_threads()
-    shapes = cpu_sample_shapes(4.0, 25.0 * threads)
+    shapes = cpu_sample_shapes(min(4.0, 60.0 / max(args.steps, 1)), 25.0 * threads)  # the whole run stays near a minute
     gflops, dt = run_cpu(shapes, args.steps, min(args.warmup, 1), threads)
     sample = "first rows of A per sweep shape, n and k exact: " + ", ".join("%dx%dx%d" % s for s in shapes)
     line = {"impl": "reference", "metric": "identical_fp32_gemm_gflops", "value": gflops, "unit": "GFLOP/s",
@@ -156,8 +156,8 @@ def reference_arm(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=60)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
@@ -262,13 +262,14 @@ def main():
     # the dominant kernel: each product's main kernel (gemm_packed_kernel on four of the five shapes, the 128x128
     # tile kernel on 128x11008x4096), timed by the library's own event pairs: operand packing and the group fold
     # are outside these pairs and inside `value`
-    tile_flops = sweep_flops(SWEEP) * args.steps
+    tile_flops = sweep_flops(SWEEP) * (kernel_calls.value / float(len(SWEEP)))  # the pairs recorded (the library keeps 4096)
     tile_ms = float(kernel_ms.value)
     tile_tflops = tile_flops / (tile_ms * 1e-3) / 1e12 if tile_ms > 0 else 0.0
     sm_max = (clocks or {}).get("sm_max_mhz") or 1965.0
     roofline = {"bound": "fp32_ffma", "kernel": "gemm_packed_kernel (128x128 tiles, bulk-copy ring)", "achieved": tile_tflops,
                 "peak": fp32_peak, "unit": "TFLOP/s", "frac": tile_tflops / fp32_peak if fp32_peak else None,
-                "kernel_launches_timed": int(kernel_calls.value), "kernel_ms_per_step": tile_ms / max(args.steps, 1),
+                "kernel_launches_timed": int(kernel_calls.value),
+                "kernel_ms_per_step": tile_ms / max(kernel_calls.value / float(len(SWEEP)), 1.0),
                 "peak_source": "in-run fused-multiply-add probe (max of scalar %.1f and packed f32x2 %.1f TFLOP/s); nominal %d SMs x 128 lanes x 2 x %.0f MHz = %.1f"
                 % (peaks["scalar"], peaks["packed"], sms, sm_max, sms * 128 * 2 * sm_max * 1e6 / 1e12),
                 "launch_ms": {"%dx%dx%d" % SWEEP[i]: per_shape_ms[i] for i in range(len(SWEEP))},
