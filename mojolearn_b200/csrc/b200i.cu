@@ -1081,15 +1081,26 @@ int64_t b200i_argmax(int64_t device, void *stream, int32_t *out, const float *lo
 
 // ---- host-pointer twins -------------------------------------------------------------------
 
-// The host-pointer product for a tall left operand, pipelined: the weight crosses once and is packed once; the rows of
-// A cross in chunks on a second stream while earlier chunks are packed and multiplied on the compute stream and their
-// rows of C return on a third (PCIe is full duplex). Each chunk is a product of its own, so the bits are those of the
-// whole product (a cell reads one row of A). Returns 0 done, 1 error, -1 not applicable (the caller runs the plain path).
+// The host-pointer product, pipelined over three streams (PCIe is full duplex): host-to-device copies, packing and
+// multiplying, device-to-host copies. A tall left operand (m >= 1024) is cut by ROWS: the weight crosses and is
+// packed once, the rows of A cross in chunks while earlier chunks are multiplied and their rows of C return. A wide
+// k-contiguous weight under a short left operand (op NT, n >= 2048) is cut by weight rows, that is by COLUMNS of C:
+// A crosses and is packed once, the weight crosses in chunks, each chunk's columns are computed into a dense block
+// and return through a strided copy. Every chunk is a product of its own, so the bits are those of the whole
+// product (a cell reads one row of A and one row of the weight). Returns 0 done, 1 error, -1 not applicable (the
+// caller runs the plain path).
 static int64_t host_gemm_pipelined(int dev, HostPool &pool, float *c, const float *a, const void *b, const void *bscale, int wkind,
                                    int64_t m, int64_t n, int64_t k, int op, char *err, int64_t err_cap) {
-    if (op == OP_TN || m < 4 * PACKED_MIN_EXTENT || n < PACKED_MIN_EXTENT) return -1;
-    int64_t rows_per = ((m + 3) / 4 + PK_TILE - 1) / PK_TILE * PK_TILE; // about four chunks, whole tiles
-    const int nch = (int)((m + rows_per - 1) / rows_per);
+    // cut the larger operand: its copy is the one worth hiding under the arithmetic and the return copy
+    const bool rows_ok = op != OP_TN && m >= 4 * PACKED_MIN_EXTENT && n >= PACKED_MIN_EXTENT;
+    const bool cols_ok = op == OP_NT && n >= 8 * PACKED_MIN_EXTENT && m >= 1;
+    const bool weight_larger = (double)n * (double)wkind_elem_bytes(wkind) > 2.0 * (double)m * 4.0;
+    const bool by_cols = cols_ok && (!rows_ok || weight_larger);
+    const bool by_rows = rows_ok && !by_cols;
+    if (!by_rows && !by_cols) return -1;
+    const int64_t extent = by_rows ? m : n;
+    const int64_t per = ((extent + 3) / 4 + PK_TILE - 1) / PK_TILE * PK_TILE; // about four chunks, whole tiles
+    const int nch = (int)((extent + per - 1) / per);
     if (nch < 2 || nch > HOST_CHUNKS) return -1;
     if (!pool.pipe_ready) {
         CUDA_TRY(cudaStreamCreateWithFlags(&pool.s_in, cudaStreamNonBlocking));
@@ -1097,7 +1108,8 @@ static int64_t host_gemm_pipelined(int dev, HostPool &pool, float *c, const floa
         for (auto &e : pool.ev) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         pool.pipe_ready = true;
     }
-    const size_t abytes = (size_t)m * k * 4, bbytes = (size_t)n * k * wkind_elem_bytes(wkind), cbytes = (size_t)m * n * 4;
+    const size_t es = wkind_elem_bytes(wkind);
+    const size_t abytes = (size_t)m * k * 4, bbytes = (size_t)n * k * es, cbytes = (size_t)m * n * 4;
     const size_t sbytes = (wkind >= W_INT8_EXP) ? (size_t)n * 4 : 0;
     const size_t wsbytes = pk_workspace_bytes(m, n, k);
     void *da, *db, *dc, *ds = nullptr, *dw = nullptr;
@@ -1113,37 +1125,71 @@ static int64_t host_gemm_pipelined(int dev, HostPool &pool, float *c, const floa
     unsigned char *fa = reinterpret_cast<unsigned char *>(pb + pk_panel_floats(n, k));
     unsigned char *fb = fa + pk_flag_bytes(m, k);
     const bool k8 = (k % 8 == 0) && (leaves == 1 || leaf % 8 == 0);
+    const int tiles_m = (int)((m + PK_TILE - 1) / PK_TILE), tiles_n = (int)((n + PK_TILE - 1) / PK_TILE);
     // everything queued below waits for whatever the compute stream still holds from an earlier call
     CUDA_TRY(cudaEventRecord(pool.ev[0], pool.stream));
     CUDA_TRY(cudaStreamWaitEvent(pool.s_in, pool.ev[0], 0));
     CUDA_TRY(cudaStreamWaitEvent(pool.s_out, pool.ev[0], 0));
-    CUDA_TRY(cudaMemcpyAsync(db, b, bbytes, cudaMemcpyHostToDevice, pool.s_in));
-    if (sbytes) CUDA_TRY(cudaMemcpyAsync(ds, bscale, sbytes, cudaMemcpyHostToDevice, pool.s_in));
+    // the operand that is not cut crosses first and is packed once
+    if (by_rows) {
+        CUDA_TRY(cudaMemcpyAsync(db, b, bbytes, cudaMemcpyHostToDevice, pool.s_in));
+        if (sbytes) CUDA_TRY(cudaMemcpyAsync(ds, bscale, sbytes, cudaMemcpyHostToDevice, pool.s_in));
+    } else {
+        CUDA_TRY(cudaMemcpyAsync(da, a, abytes, cudaMemcpyHostToDevice, pool.s_in));
+    }
     CUDA_TRY(cudaEventRecord(pool.ev[0], pool.s_in));
     CUDA_TRY(cudaStreamWaitEvent(pool.stream, pool.ev[0], 0));
-    PackArgs pbargs{pb, fb, db, ds, (int)n, (int)k, leaf, leaves, wpl, op == OP_NT, op == OP_NT && k8};
-    launch_pack_b(pbargs, wkind, pool.stream);
-    g_launches++;
-    const int tiles_n = (int)((n + PK_TILE - 1) / PK_TILE);
-    for (int i = 0; i < nch; i++) {
-        const int64_t r0 = i * rows_per, rows = (m - r0 < rows_per) ? m - r0 : rows_per;
-        const int64_t tile0 = r0 / PK_TILE;
-        const float *ha = a + (size_t)r0 * k;
-        float *dai = static_cast<float *>(da) + (size_t)r0 * k, *dci = static_cast<float *>(dc) + (size_t)r0 * n;
-        CUDA_TRY(cudaMemcpyAsync(dai, ha, (size_t)rows * k * 4, cudaMemcpyHostToDevice, pool.s_in));
-        CUDA_TRY(cudaEventRecord(pool.ev[1 + 2 * i], pool.s_in));
-        CUDA_TRY(cudaStreamWaitEvent(pool.stream, pool.ev[1 + 2 * i], 0));
-        float *pai = pa + (size_t)tile0 * k * PK_TILE;
-        unsigned char *fai = fa + (size_t)tile0 * leaves * wpl;
-        PackArgs paargs{pai, fai, dai, nullptr, (int)rows, (int)k, leaf, leaves, wpl, 1, k8};
+    if (by_rows) {
+        PackArgs pbargs{pb, fb, db, ds, (int)n, (int)k, leaf, leaves, wpl, op == OP_NT, op == OP_NT && k8};
+        launch_pack_b(pbargs, wkind, pool.stream);
+    } else {
+        PackArgs paargs{pa, fa, da, nullptr, (int)m, (int)k, leaf, leaves, wpl, 1, k8};
         launch_pack<W_F32>(paargs, pool.stream);
-        PackedGemmArgs p{pai, pb, fai, fb, dci, nullptr, (int)rows, (int)n, (int)k, leaf, leaves, wpl, leaves, 1, tiles_n, (n % 4 == 0) ? 1 : 0};
-        dim3 grid((unsigned)(((rows + PK_TILE - 1) / PK_TILE) * tiles_n), 1u);
-        gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, pool.stream>>>(p);
+    }
+    g_launches++;
+    for (int i = 0; i < nch; i++) {
+        const int64_t x0 = i * per, cnt = (extent - x0 < per) ? extent - x0 : per;
+        const int64_t tile0 = x0 / PK_TILE;
+        if (by_rows) {
+            float *dai = static_cast<float *>(da) + (size_t)x0 * k, *dci = static_cast<float *>(dc) + (size_t)x0 * n;
+            CUDA_TRY(cudaMemcpyAsync(dai, a + (size_t)x0 * k, (size_t)cnt * k * 4, cudaMemcpyHostToDevice, pool.s_in));
+            CUDA_TRY(cudaEventRecord(pool.ev[1 + 2 * i], pool.s_in));
+            CUDA_TRY(cudaStreamWaitEvent(pool.stream, pool.ev[1 + 2 * i], 0));
+            float *pai = pa + (size_t)tile0 * k * PK_TILE;
+            unsigned char *fai = fa + (size_t)tile0 * leaves * wpl;
+            PackArgs paargs{pai, fai, dai, nullptr, (int)cnt, (int)k, leaf, leaves, wpl, 1, k8};
+            launch_pack<W_F32>(paargs, pool.stream);
+            PackedGemmArgs p{pai, pb, fai, fb, dci, nullptr, (int)cnt, (int)n, (int)k, leaf, leaves, wpl, leaves, 1, tiles_n, (n % 4 == 0) ? 1 : 0};
+            dim3 grid((unsigned)(((cnt + PK_TILE - 1) / PK_TILE) * tiles_n), 1u);
+            gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, pool.stream>>>(p);
+            CUDA_TRY(cudaEventRecord(pool.ev[2 + 2 * i], pool.stream));
+            CUDA_TRY(cudaStreamWaitEvent(pool.s_out, pool.ev[2 + 2 * i], 0));
+            CUDA_TRY(cudaMemcpyAsync(c + (size_t)x0 * n, dci, (size_t)cnt * n * 4, cudaMemcpyDeviceToHost, pool.s_out));
+        } else {
+            unsigned char *dbi = static_cast<unsigned char *>(db) + (size_t)x0 * k * es;
+            float *dci = static_cast<float *>(dc) + (size_t)m * x0; // a dense [m, cnt] block
+            CUDA_TRY(cudaMemcpyAsync(dbi, static_cast<const unsigned char *>(b) + (size_t)x0 * k * es, (size_t)cnt * k * es,
+                                     cudaMemcpyHostToDevice, pool.s_in));
+            if (sbytes)
+                CUDA_TRY(cudaMemcpyAsync(static_cast<unsigned char *>(ds) + (size_t)x0 * 4, static_cast<const unsigned char *>(bscale) + (size_t)x0 * 4,
+                                         (size_t)cnt * 4, cudaMemcpyHostToDevice, pool.s_in));
+            CUDA_TRY(cudaEventRecord(pool.ev[1 + 2 * i], pool.s_in));
+            CUDA_TRY(cudaStreamWaitEvent(pool.stream, pool.ev[1 + 2 * i], 0));
+            float *pbi = pb + (size_t)tile0 * k * PK_TILE;
+            unsigned char *fbi = fb + (size_t)tile0 * leaves * wpl;
+            PackArgs pbargs{pbi, fbi, dbi, sbytes ? static_cast<unsigned char *>(ds) + (size_t)x0 * 4 : nullptr, (int)cnt, (int)k, leaf, leaves,
+                            wpl, 1, k8};
+            launch_pack_b(pbargs, wkind, pool.stream);
+            const int tiles_nc = (int)((cnt + PK_TILE - 1) / PK_TILE);
+            PackedGemmArgs p{pa, pbi, fa, fbi, dci, nullptr, (int)m, (int)cnt, (int)k, leaf, leaves, wpl, leaves, 1, tiles_nc,
+                             (cnt % 4 == 0 && (m * x0) % 4 == 0) ? 1 : 0};
+            dim3 grid((unsigned)(tiles_m * tiles_nc), 1u);
+            gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, pool.stream>>>(p);
+            CUDA_TRY(cudaEventRecord(pool.ev[2 + 2 * i], pool.stream));
+            CUDA_TRY(cudaStreamWaitEvent(pool.s_out, pool.ev[2 + 2 * i], 0));
+            CUDA_TRY(cudaMemcpy2DAsync(c + x0, (size_t)n * 4, dci, (size_t)cnt * 4, (size_t)cnt * 4, (size_t)m, cudaMemcpyDeviceToHost, pool.s_out));
+        }
         g_launches += 2;
-        CUDA_TRY(cudaEventRecord(pool.ev[2 + 2 * i], pool.stream));
-        CUDA_TRY(cudaStreamWaitEvent(pool.s_out, pool.ev[2 + 2 * i], 0));
-        CUDA_TRY(cudaMemcpyAsync(c + (size_t)r0 * n, dci, (size_t)rows * n * 4, cudaMemcpyDeviceToHost, pool.s_out));
     }
     CUDA_TRY(cudaGetLastError());
     CUDA_TRY(cudaStreamSynchronize(pool.s_out));

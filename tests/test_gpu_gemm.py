@@ -87,6 +87,26 @@ def test_host_call_tall_operand_is_pipelined_in_row_chunks(opname):
     assert _native.lib().b200i_decode_status(-1) == 0
 
 
+def test_host_call_wide_weight_is_pipelined_in_column_chunks():
+    """A short left operand against a wide k-contiguous weight with host buffers: the weight crosses in row chunks,
+    each chunk's columns of C are computed densely and return through a strided copy."""
+    m, n, k = 40, 2300, 136  # four chunks (640 + 640 + 640 + 380 weight rows), two leaves with a short last one
+    a, b = _operands(m, n, k, oracle.OP_NT, 9)
+    b[5, ::3] = np.float32(1e-41)
+    want = oracle.nan_canon(oracle.gemm_rows(a, b, oracle.OP_NT))
+    for _ in range(2):  # the pooled buffers and events are reused
+        assert linalg.matmul(a, b, transpose_b=True).tobytes() == want.tobytes()
+    rng = np.random.default_rng(10)
+    codes = rng.integers(-127, 128, (n, k)).astype(np.int8)
+    exps = rng.integers(-9, -5, n).astype(np.int32)
+    want8 = oracle.gemm_rows(a, oracle.dequantize_int8(codes, exps), oracle.OP_NT)
+    assert linalg.matmul_int8w(a, codes, exps).tobytes() == want8.tobytes()
+    bits = oracle.to_bf16((b * 0.02).astype(np.float32))
+    wantb = oracle.gemm_rows(a, oracle.from_bf16(bits), oracle.OP_NT)
+    assert linalg.matmul_bf16(a, bits, transpose_b=True).tobytes() == wantb.tobytes()
+    assert _native.lib().b200i_decode_status(-1) == 0
+
+
 def test_subnormal_forcing_operands_take_the_flushed_path():
     rng = np.random.default_rng(0)
     a = (rng.standard_normal((150, 300)) * 2.0 ** -62).astype(np.float32)
