@@ -162,6 +162,51 @@ def fixture_ids(X, b, l, vocab):
     return np.ascontiguousarray((raw.astype(np.int32) % vocab).reshape(b, l))
 
 
+def batch_cell_hash_block(y):
+    """The verify table's `batch` column of a block forward over a (B, L, d) slab (tools/identity_break.py:9591-9604):
+    the whole-batch rows, then the whole output as the full-length answer of the prefix part."""
+    y = np.ascontiguousarray(y)
+    b, l, d = y.shape
+    h = hashlib.sha256()
+    h.update(("rows:forward:%d" % b).encode())
+    for i in range(b):
+        h.update(("<f4(%d, %d)" % (l, d)).encode())
+        h.update(y[i].tobytes())
+    h.update(("prefix:forward:%d:1" % l).encode())
+    h.update(("<f4(%d, %d, %d)" % (b, l, d)).encode())
+    h.update(y.tobytes())
+    return h.hexdigest()[:16]
+
+
+def stepfull_cell_hash(y):
+    """The verify table's `stepfull` column of a block (tools/identity_break.py:10345-10382): one fresh-state forward
+    over (2, 16, d) hashed under the call's label; valid when allocate_state + one step per position reproduces it."""
+    y = np.ascontiguousarray(y)
+    h = hashlib.sha256()
+    h.update(("stepfull:forward(x) vs allocate_state + step, L=%d:%s" % (y.shape[1], list(y.shape))).encode())
+    h.update(("<f4%s" % (tuple(y.shape),)).encode())
+    h.update(y.tobytes())
+    return h.hexdigest()[:16]
+
+
+def batch_cell_hash(logits):
+    """The verify table's `batch` column for a causal LM forward over (B, L) ids (tools/identity_break.py:8624-8644,
+    :8731-8767, :9446-9460): sha256 over the whole-batch rows (each with its dtype and shape) and then the whole
+    output as the full-length answer of the prefix part; valid when every row alone, every split and every prefix
+    reproduces the whole batch's bytes, which the tests hold separately."""
+    logits = np.ascontiguousarray(logits)
+    b, l, v = logits.shape
+    h = hashlib.sha256()
+    h.update(("rows:forward:%d" % b).encode())
+    for i in range(b):
+        h.update(("<f4(%d, %d)" % (l, v)).encode())
+        h.update(logits[i].tobytes())
+    h.update(("prefix:forward:%d:1" % l).encode())
+    h.update(("<f4(%d, %d, %d)" % (b, l, v)).encode())
+    h.update(logits.tobytes())
+    return h.hexdigest()[:16]
+
+
 class OracleLM(object):
     def __init__(self, cfg, weights):
         self.cfg, self.w = cfg, weights

@@ -93,6 +93,71 @@ def lowbit_conversions(impl, X):
                 f32_copy=sha16(a2), linalg=sha16(lin), flags=sha16(flags))
 
 
+def _rows_digest(h, label, out):
+    """One row-wise call of the table's `batch` column (tools/identity_break.py:8624-8644, :8726-8727): a label, then
+    every row of the whole-batch output with its dtype and shape."""
+    out = np.ascontiguousarray(out)
+    h.update(("rows:%s:%d" % (label, out.shape[0])).encode())
+    head = ("%s%s" % (out.dtype.str, tuple(out.shape[1:]))).encode()
+    for row in out:
+        h.update(head)
+        h.update(row.tobytes())
+
+
+def gemm_pinned_batch(impl, Xh):
+    """`batch` cell of gemm-pinned (tools/identity_break.py:9100-9105): the rows of A alone against the whole A, OP_NN;
+    the hash is of the whole-batch rows, valid because a row alone and a split give the same bytes."""
+    b = np.ascontiguousarray(Xh[256:320].T).astype(np.float32)
+    a = Xh[:256].astype(np.float32)
+    h = hashlib.sha256()
+    _rows_digest(h, "matmul OP_NN", impl.matmul(a, b))
+    return h.hexdigest()[:16], [(lambda r: impl.matmul(r, b), a)]
+
+
+def gemm_transposed_batch(impl, Xh):
+    """`batch` cell of gemm-transposed (tools/identity_break.py:9108-9115): OP_NT then OP_TN over the same rows."""
+    b = np.ascontiguousarray(Xh[256:384]).astype(np.float32)
+    c = np.ascontiguousarray(Xh[384:384 + Xh.shape[1]]).astype(np.float32)
+    a = Xh[:256].astype(np.float32)
+    nt = lambda r: impl.matmul(r, b, transpose_b=True)
+    tn = lambda r: impl.matmul(np.ascontiguousarray(r.T), c, transpose_a=True)
+    h = hashlib.sha256()
+    _rows_digest(h, "matmul OP_NT", nt(a))
+    _rows_digest(h, "matmul OP_TN", tn(a))
+    return h.hexdigest()[:16], [(nt, a), (tn, a)]
+
+
+def _rows_digest_multi(h, label, outs):
+    """A row-wise call with several outputs: per row, every output's (dtype, shape, bytes) in order
+    (tools/identity_break.py:8636-8644; a 1-D output's row is shape (1,))."""
+    outs = [np.ascontiguousarray(o) for o in outs]
+    n = outs[0].shape[0]
+    h.update(("rows:%s:%d" % (label, n)).encode())
+    heads = [("%s%s" % (o.dtype.str, tuple(o.shape[1:]) if o.ndim > 1 else (1,))).encode() for o in outs]
+    for i in range(n):
+        for o, head in zip(outs, heads):
+            h.update(head)
+            h.update(o[i].tobytes())
+
+
+def lowbit_conversions_batch(impl, Xh, cols):
+    """`batch` cell of lowbit-conversions (tools/identity_break.py:9330-9346): pack and materialise held-out rows; the
+    int8 exponent is per row, so a row packed alone gives the bytes it gives inside the block."""
+    r = np.ascontiguousarray(Xh[:64, :cols]).astype(np.float32)
+
+    def fn(rows):
+        bits = np.asarray(impl.to_bf16(rows))
+        codes, exps = impl.quantize_int8(rows)
+        return (bits, np.asarray(codes), np.asarray(exps), np.asarray(impl.from_bf16(bits)),
+                np.asarray(impl.dequantize_int8(codes, exps)))
+
+    h = hashlib.sha256()
+    _rows_digest_multi(h, "pack_one + materialize_one", fn(r))
+    return h.hexdigest()[:16], fn, r
+
+
+BATCH_LANES = {"gemm-pinned": gemm_pinned_batch, "gemm-transposed": gemm_transposed_batch}
+
 LANES = {"gemm-pinned": gemm_pinned, "gemm-transposed": gemm_transposed, "gemm-bf16": gemm_bf16,
          "gemm-int8": gemm_int8, "lowbit-conversions": lowbit_conversions}
 

@@ -32,6 +32,28 @@ def test_transformer_infer_cell_on_gpu(lane, fmt, kind):
     x = decoder_ref.seq(fixtures.fixture(kind, seed=1), 2, 16, dims["d_model"])
     y = blk.forward(x)
     assert oracle.sha16(y) == TABLE["cells"]["%s/%s" % (lane, kind)]["infer"]
+    # the `stepfull` column: allocate_state + one step per position reproduces the forward, which hashes to the cell
+    state = blk.allocate_state(2, 16)
+    steps = [blk.step(np.ascontiguousarray(x[:, t:t + 1]), state) for t in range(16)]
+    assert np.concatenate(steps, axis=1).tobytes() == y.tobytes()
+    assert decoder_ref.stepfull_cell_hash(y) == TABLE["cells"]["%s/%s" % (lane, kind)]["stepfull"]
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+def test_transformer_batch_cell_on_gpu(lane, fmt, kind):
+    """The table's `batch` column on the CUDA path: forward of the held-out (8, 16, 32) slab; every sequence alone,
+    the split 1 / 7 and the prefixes 1, 7, 15 reproduce the whole batch's bytes, which hash to the reference's cell."""
+    w, dims = decoder_ref.transformer_lane_weights()
+    packed = lowbit.pack(w, fmt) if fmt != "float32" else w
+    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"])
+    x = decoder_ref.seq(fixtures.fixture(kind, seed=1), 8, 16, dims["d_model"])
+    y = blk.forward(x)
+    assert decoder_ref.batch_cell_hash_block(y) == TABLE["cells"]["%s/%s" % (lane, kind)]["batch"]
+    for a, b in ((0, 1), (1, 8), (3, 4)):
+        assert blk.forward(np.ascontiguousarray(x[a:b])).tobytes() == y[a:b].tobytes()
+    for p in (1, 7, 15):
+        assert blk.forward(np.ascontiguousarray(x[:, :p])).tobytes() == np.ascontiguousarray(y[:, :p]).tobytes()
 
 
 OPTION_SETS = [
@@ -155,6 +177,11 @@ def test_hf_causal_lm_infer_cell_on_gpu(kind):
     ids = decoder_ref.fixture_ids(fixtures.fixture(kind, seed=1), 4, 12, c.vocab)
     logits = lm.forward(ids)
     assert oracle.sha16(logits) == TABLE["cells"]["hf-causal-lm/%s" % kind]["infer"]
+    assert decoder_ref.batch_cell_hash(logits) == TABLE["cells"]["hf-causal-lm/%s" % kind]["batch"]
+    for rows in (slice(0, 1), slice(1, 2), slice(1, 4)):  # a row alone and a split reproduce the whole batch's bytes
+        assert lm.forward(ids[rows]).tobytes() == logits[rows].tobytes()
+    for p in (1, 7, 11):  # and so does every prefix
+        assert lm.forward(ids[:, :p]).tobytes() == np.ascontiguousarray(logits[:, :p]).tobytes()
     state = lm.allocate_state(4, 12)
     lm.forward(ids[:, :11], state)
     assert lm.step(ids[:, 11], state).tobytes() == np.ascontiguousarray(logits[:, 11, :]).tobytes()

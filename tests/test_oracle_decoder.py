@@ -34,8 +34,29 @@ def test_transformer_infer_cell(lane, fmt, kind):
     w, dims = decoder_ref.transformer_lane_weights()
     cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"])
     x = decoder_ref.seq(fixtures.fixture(kind, seed=1), 2, 16, dims["d_model"])
-    y = oracle.block_forward(cfg, decoder_ref.block_slots(_materialise(w, fmt)), x)
+    slots = decoder_ref.block_slots(_materialise(w, fmt))
+    y = oracle.block_forward(cfg, slots, x)
     assert oracle.sha16(y) == TABLE["cells"]["%s/%s" % (lane, kind)]["infer"]
+    # the `stepfull` column: the same forward against a zero state stepped one position at a time
+    state = oracle.KVState(2, dims["n_kv_heads"], 16, dims["head_dim"])
+    steps = [oracle.block_forward(cfg, slots, x[:, t:t + 1].copy(), state) for t in range(16)]
+    assert np.concatenate(steps, axis=1).tobytes() == y.tobytes()
+    assert decoder_ref.stepfull_cell_hash(y) == TABLE["cells"]["%s/%s" % (lane, kind)]["stepfull"]
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+def test_transformer_batch_cell(lane, fmt, kind):
+    """The `batch` column: forward of the held-out (8, 16, 32) slab; a sequence alone and a prefix reproduce the whole
+    batch's bytes, and the whole-batch rows hash to the reference's cell (tools/identity_break.py:9591-9604)."""
+    w, dims = decoder_ref.transformer_lane_weights()
+    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"])
+    slots = decoder_ref.block_slots(_materialise(w, fmt))
+    x = decoder_ref.seq(fixtures.fixture(kind, seed=1), 8, 16, dims["d_model"])
+    y = oracle.block_forward(cfg, slots, x)
+    assert decoder_ref.batch_cell_hash_block(y) == TABLE["cells"]["%s/%s" % (lane, kind)]["batch"]
+    assert oracle.block_forward(cfg, slots, x[2:3].copy()).tobytes() == y[2:3].tobytes()
+    assert oracle.block_forward(cfg, slots, x[:, :7].copy()).tobytes() == np.ascontiguousarray(y[:, :7]).tobytes()
 
 
 def test_portable_math_is_close_to_libm_and_exact_at_anchors():
@@ -96,4 +117,10 @@ def test_hf_causal_lm_infer_cell(kind):
     bytes. Pins the whole decoder, embedding to head, on the reference's own hash."""
     ids = decoder_ref.fixture_ids(fixtures.fixture(kind, seed=1), 4, 12, decoder_ref.LlamaFixtureConfig.vocab)
     lm = decoder_ref.OracleLM(decoder_ref.LlamaFixtureConfig, decoder_ref.llama_fixture_weights())
-    assert oracle.sha16(lm.forward(ids)) == TABLE["cells"]["hf-causal-lm/%s" % kind]["infer"]
+    logits = lm.forward(ids)
+    assert oracle.sha16(logits) == TABLE["cells"]["hf-causal-lm/%s" % kind]["infer"]
+    # the `batch` column: the same logits hashed row by row and as the full-length prefix answer; a row alone and a
+    # prefix give the whole batch's bytes
+    assert decoder_ref.batch_cell_hash(logits) == TABLE["cells"]["hf-causal-lm/%s" % kind]["batch"]
+    assert lm.forward(ids[1:2]).tobytes() == logits[1:2].tobytes()
+    assert lm.forward(ids[:, :7]).tobytes() == np.ascontiguousarray(logits[:, :7]).tobytes()

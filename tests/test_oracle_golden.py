@@ -56,3 +56,29 @@ def test_denormal_fixture_exercises_the_flush():
     a = oracle.gemm(np.ascontiguousarray(d[:64].T), d[:64])
     b = oracle.gemm(np.ascontiguousarray(z[:64].T), z[:64])
     assert a.tobytes() == b.tobytes()
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+@pytest.mark.parametrize("lane", sorted(lanes.BATCH_LANES))
+def test_verify_table_batch_cell(lane, kind):
+    """The table's `batch` column: the product's rows alone, split 1 / 7 / rest and whole give the same bytes (the
+    leaf size may not read m), and the whole-batch rows hash to the reference's cell."""
+    Xh = fixtures.fixture(kind, seed=1)
+    digest, calls = lanes.BATCH_LANES[lane](lanes.OracleImpl(oracle), Xh)
+    assert digest == TABLE["cells"]["%s/%s" % (lane, kind)]["batch"]
+    for fn, rows in calls:
+        whole = np.asarray(fn(rows))
+        assert np.asarray(fn(rows[3:4])).tobytes() == whole[3:4].tobytes()
+        parts = [np.asarray(fn(rows[a:b])) for a, b in ((0, 1), (1, 8), (8, rows.shape[0]))]
+        assert np.concatenate(parts, axis=0).tobytes() == whole.tobytes()
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+def test_lowbit_conversions_batch_cell(kind):
+    """The `batch` column of lowbit-conversions: held-out rows packed and materialised; a row packed alone gives the
+    bytes it gives inside the block (the int8 exponent belongs to the row)."""
+    digest, fn, rows = lanes.lowbit_conversions_batch(lanes.OracleImpl(oracle), fixtures.fixture(kind, seed=1), lanes.LOWBIT_COLS)
+    assert digest == TABLE["cells"]["lowbit-conversions/%s" % kind]["batch"]
+    whole, alone = fn(rows), fn(rows[5:6])
+    for w, a in zip(whole, alone):
+        assert np.asarray(a).tobytes() == np.asarray(w)[5:6].tobytes()
