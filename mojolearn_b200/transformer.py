@@ -407,8 +407,32 @@ class TransformerBlock(object):
         y = self.forward_device(xt, state)
         return y.cpu().numpy() if host else y
 
-    def forward(self, x, state=None):
-        return self._run(x, state)
+    def forward(self, x, state=None, *, lengths=None):
+        """`lengths` makes the batch ragged (reference `_transformer_impl.py:527-553`): B lengths in [1, L]; row i is real
+        at positions [0, lengths[i]) and padding after. Each real position's output equals the row run alone at its own
+        length and padding positions output exactly +0.0; whatever sits in the padding of x is never read. Not allowed
+        together with a state. The rows are run one by one: a row's bits do not depend on its batch."""
+        if lengths is None:
+            return self._run(x, state)
+        if state is not None:
+            raise ValueError("lengths is not allowed together with a state")
+        host = not isinstance(x, torch.Tensor)
+        shape = tuple(np.asarray(x).shape) if host else tuple(x.shape)
+        if len(shape) != 3:
+            raise ValueError("x must be [B, L, d_model]")
+        lens = [int(n) for n in lengths]
+        if len(lens) != shape[0] or any(n < 1 or n > shape[1] for n in lens):
+            raise ValueError("lengths must hold B values in [1, L]")
+        if host:
+            xa = np.asarray(x)
+            out = np.zeros(shape, dtype=np.float32)
+            for i, n in enumerate(lens):
+                out[i, :n] = self._run(np.ascontiguousarray(xa[i:i + 1, :n]), None)[0]
+            return out
+        out = torch.zeros(shape, dtype=torch.float32, device=x.device)
+        for i, n in enumerate(lens):
+            out[i, :n] = self._run(x[i:i + 1, :n].contiguous(), None)[0]
+        return out
 
     def step(self, x, state):
         """One decode step: x [B, 1, d_model] (or [B, d_model]) against the cached tokens."""

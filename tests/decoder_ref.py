@@ -189,6 +189,67 @@ def stepfull_cell_hash(y):
     return h.hexdigest()[:16]
 
 
+RAGGED_LENGTHS = (16, 1, 7, 9, 16, 3, 12, 15)
+RAGGED_LONG_LENGTHS = (300, 1, 65, 129, 257, 128)
+
+
+def tiled(X, shape):
+    """`shape` float32 values from the fixture, row-major and wrapped (tools/identity_break.py:10054-10058)."""
+    return np.ascontiguousarray(np.resize(np.ascontiguousarray(X).reshape(-1), int(np.prod(shape))).reshape(shape))
+
+
+def ragged_inputs(Xh, dm):
+    """The two ragged calls of a block (tools/identity_break.py:10249-10257): junk (NaN) at the padding positions."""
+    calls = []
+    for x, lens in ((seq(Xh, len(RAGGED_LENGTHS), 16, dm), RAGGED_LENGTHS),
+                    (tiled(Xh, (len(RAGGED_LONG_LENGTHS), max(RAGGED_LONG_LENGTHS), dm)), RAGGED_LONG_LENGTHS)):
+        x = np.array(x, dtype=np.float32, copy=True)
+        for i, n in enumerate(lens):
+            x[i, n:] = np.float32("nan")
+        calls.append((x, lens))
+    return calls
+
+
+def ragged_cell_hash(outs):
+    """The verify table's `ragged` column (tools/identity_break.py:10207-10234): per call a label with the input shape
+    and the lengths, then the padded output; valid when every row's real positions equal the row alone and the
+    padding is exactly +0.0, which the tests hold separately. `outs` = [(x, lengths, y), ...]."""
+    h = hashlib.sha256()
+    for x, lens, y in outs:
+        y = np.ascontiguousarray(y)
+        h.update(("ragged:forward(lengths) L=%d:%s:%s" % (x.shape[1], list(x.shape), tuple(lens))).encode())
+        h.update(("<f4%s" % (tuple(y.shape),)).encode())
+        h.update(y.tobytes())
+    return h.hexdigest()[:16]
+
+
+def batchscale_inputs(Xh, dm):
+    """The serving-size calls of a block (tools/identity_break.py:10086-10093) at the sizes the committed table was
+    recorded with (1024 rows and a long length of 1024; the harness has since shrunk both, :9989-9995, :10084):
+    1024 rows of 16 positions, and two rows of 1024 positions cut from the reversed fixture."""
+    return tiled(Xh, (1024, 16, dm)), tiled(Xh[::-1], (2, 1024, dm))
+
+
+def batchscale_cell_hash(y_rows, y_long):
+    """The verify table's `batchscale` column of a block (tools/identity_break.py:10018-10052, :8731-8767): the
+    1024-row call's rows under the sub-batch sizes it was asked at (1, 17, 64, 256), then the 1024-position call as
+    the full-length answer of its prefix part."""
+    y_rows, y_long = np.ascontiguousarray(y_rows), np.ascontiguousarray(y_long)
+    n, l, d = y_rows.shape
+    h = hashlib.sha256()
+    h.update(("scale:forward L=%d:%d:1,17,64,256" % (l, n)).encode())
+    for i in range(n):
+        h.update(("<f4(%d, %d)" % (l, d)).encode())
+        h.update(y_rows[i].tobytes())
+    h.update(("prefix:forward B=2 L=%d:%d:1" % (y_long.shape[1], y_long.shape[1])).encode())
+    h.update(("<f4%s" % (tuple(y_long.shape),)).encode())
+    h.update(y_long.tobytes())
+    return h.hexdigest()[:16]
+
+
+SCALE_PREFIXES = (1, 7, 63, 64, 65, 127, 128, 129, 255, 256, 257, 511, 513, 1023)
+
+
 def batch_cell_hash(logits):
     """The verify table's `batch` column for a causal LM forward over (B, L) ids (tools/identity_break.py:8624-8644,
     :8731-8767, :9446-9460): sha256 over the whole-batch rows (each with its dtype and shape) and then the whole

@@ -56,6 +56,46 @@ def test_transformer_batch_cell_on_gpu(lane, fmt, kind):
         assert blk.forward(np.ascontiguousarray(x[:, :p])).tobytes() == np.ascontiguousarray(y[:, :p]).tobytes()
 
 
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+def test_transformer_ragged_cell_on_gpu(lane, fmt, kind):
+    """The table's `ragged` column on the CUDA path: forward(x, lengths=...) with NaN junk in the padding; real positions
+    equal the row alone, padding is exactly +0.0, and the padded outputs hash to the reference's cell."""
+    w, dims = decoder_ref.transformer_lane_weights()
+    packed = lowbit.pack(w, fmt) if fmt != "float32" else w
+    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"])
+    outs = []
+    for x, lens in decoder_ref.ragged_inputs(fixtures.fixture(kind, seed=1), dims["d_model"]):
+        y = blk.forward(x, lengths=lens)
+        assert not np.isnan(y).any()
+        for i, n in enumerate(lens):
+            assert y[i, n:].tobytes() == bytes(y[i, n:].nbytes)
+        i = 2
+        assert blk.forward(np.ascontiguousarray(x[i:i + 1, :lens[i]])).tobytes() == np.ascontiguousarray(y[i:i + 1, :lens[i]]).tobytes()
+        outs.append((x, lens, y))
+    assert decoder_ref.ragged_cell_hash(outs) == TABLE["cells"]["%s/%s" % (lane, kind)]["ragged"]
+    with pytest.raises(ValueError):
+        blk.forward(outs[0][0], state=blk.allocate_state(8, 16), lengths=outs[0][1])
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+def test_transformer_batchscale_cell_on_gpu(lane, fmt, kind):
+    """The table's `batchscale` column on the CUDA path: the 1024-row call against sub-batches of 1, 17, 64 and 256 rows
+    at three offsets, the 1024-position call against prefixes around the 64 / 128 / 256 / 512 boundaries."""
+    w, dims = decoder_ref.transformer_lane_weights()
+    packed = lowbit.pack(w, fmt) if fmt != "float32" else w
+    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"])
+    x, xl = decoder_ref.batchscale_inputs(fixtures.fixture(kind, seed=1), dims["d_model"])
+    y, yl = blk.forward(x), blk.forward(xl)
+    assert decoder_ref.batchscale_cell_hash(y, yl) == TABLE["cells"]["%s/%s" % (lane, kind)]["batchscale"]
+    for b in (1, 17, 64, 256):
+        for a in sorted({0, (1024 - b) // 2, 1024 - b}):
+            assert blk.forward(np.ascontiguousarray(x[a:a + b])).tobytes() == y[a:a + b].tobytes(), (b, a)
+    for p in decoder_ref.SCALE_PREFIXES:
+        assert blk.forward(np.ascontiguousarray(xl[:, :p])).tobytes() == np.ascontiguousarray(yl[:, :p]).tobytes(), p
+
+
 OPTION_SETS = [
     dict(),
     dict(norm="layernorm", norm_bias=True, mlp="gelu", mlp_bias=True, qkv_bias=True, o_bias=True, positions="learned"),

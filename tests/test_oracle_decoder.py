@@ -59,6 +59,39 @@ def test_transformer_batch_cell(lane, fmt, kind):
     assert oracle.block_forward(cfg, slots, x[:, :7].copy()).tobytes() == np.ascontiguousarray(y[:, :7]).tobytes()
 
 
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+def test_transformer_ragged_cell(lane, fmt, kind):
+    """The `ragged` column: every row at its own length (up to 300 positions, past the 128-step leaf of the products
+    inside), padding exactly +0.0; the padded outputs hash to the reference's cell."""
+    w, dims = decoder_ref.transformer_lane_weights()
+    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"])
+    slots = decoder_ref.block_slots(_materialise(w, fmt))
+    outs = []
+    for x, lens in decoder_ref.ragged_inputs(fixtures.fixture(kind, seed=1), dims["d_model"]):
+        y = np.zeros_like(x)
+        for i, n in enumerate(lens):
+            y[i, :n] = oracle.block_forward(cfg, slots, np.ascontiguousarray(x[i:i + 1, :n]))[0]
+        outs.append((x, lens, y))
+    assert decoder_ref.ragged_cell_hash(outs) == TABLE["cells"]["%s/%s" % (lane, kind)]["ragged"]
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+def test_transformer_batchscale_cell(lane, fmt, kind):
+    """The `batchscale` column: 1024 sequences in one call and a 1024-position call whose key axis crosses seven
+    128-step boundaries; sub-batches and prefixes give the whole call's bytes, which hash to the reference's cell."""
+    w, dims = decoder_ref.transformer_lane_weights()
+    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"])
+    slots = decoder_ref.block_slots(_materialise(w, fmt))
+    x, xl = decoder_ref.batchscale_inputs(fixtures.fixture(kind, seed=1), dims["d_model"])
+    y, yl = oracle.block_forward(cfg, slots, x), oracle.block_forward(cfg, slots, xl)
+    assert decoder_ref.batchscale_cell_hash(y, yl) == TABLE["cells"]["%s/%s" % (lane, kind)]["batchscale"]
+    assert oracle.block_forward(cfg, slots, np.ascontiguousarray(x[503:520])).tobytes() == y[503:520].tobytes()
+    for p in (129, 257):
+        assert oracle.block_forward(cfg, slots, np.ascontiguousarray(xl[:, :p])).tobytes() == np.ascontiguousarray(yl[:, :p]).tobytes()
+
+
 def test_portable_math_is_close_to_libm_and_exact_at_anchors():
     assert oracle.math("powf", 10000.0, 0.0) == 1.0
     assert oracle.math("rsqrtf", 16.0) == 0.25 and oracle.math("rsqrtf", 64.0) == 0.125
