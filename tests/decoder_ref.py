@@ -111,6 +111,16 @@ def random_lm_weights(cfg, seed, scale=0.02):
     return w
 
 
+# the block lanes of the verify table that share the `transformer` weights: (lane, weight format); the window lane
+# is the same block with window = 8 (tools/identity_break.py:3639-3653, :3729-3737, :5081-5096)
+LANE_FORMATS = [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8"),
+                ("transformer-window", "float32")]
+
+
+def lane_window(lane):
+    return 8 if lane == "transformer-window" else 0
+
+
 def lcg_floats(n, seed, lo=-0.125, hi=0.125):
     """`n` float32 values in [lo, hi) from the 64-bit LCG of the reference's synthetic checkpoints
     (python/mojolearn/_causal_lm_fixtures.py:38-47): hashed, not random, the same bytes on every machine."""

@@ -23,11 +23,11 @@ TABLE = json.load(open(os.path.join(GOLDEN, "verify_table_cells.json")))
 
 
 @pytest.mark.parametrize("kind", fixtures.KINDS)
-@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+@pytest.mark.parametrize("lane,fmt", decoder_ref.LANE_FORMATS)
 def test_transformer_infer_cell_on_gpu(lane, fmt, kind):
     w, dims = decoder_ref.transformer_lane_weights()
     packed = lowbit.pack(w, fmt) if fmt != "float32" else w
-    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"])
+    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"], window=decoder_ref.lane_window(lane))
     assert blk.weight_format == fmt
     x = decoder_ref.seq(fixtures.fixture(kind, seed=1), 2, 16, dims["d_model"])
     y = blk.forward(x)
@@ -40,13 +40,13 @@ def test_transformer_infer_cell_on_gpu(lane, fmt, kind):
 
 
 @pytest.mark.parametrize("kind", fixtures.KINDS)
-@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+@pytest.mark.parametrize("lane,fmt", decoder_ref.LANE_FORMATS)
 def test_transformer_batch_cell_on_gpu(lane, fmt, kind):
     """The table's `batch` column on the CUDA path: forward of the held-out (8, 16, 32) slab; every sequence alone,
     the split 1 / 7 and the prefixes 1, 7, 15 reproduce the whole batch's bytes, which hash to the reference's cell."""
     w, dims = decoder_ref.transformer_lane_weights()
     packed = lowbit.pack(w, fmt) if fmt != "float32" else w
-    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"])
+    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"], window=decoder_ref.lane_window(lane))
     x = decoder_ref.seq(fixtures.fixture(kind, seed=1), 8, 16, dims["d_model"])
     y = blk.forward(x)
     assert decoder_ref.batch_cell_hash_block(y) == TABLE["cells"]["%s/%s" % (lane, kind)]["batch"]
@@ -57,13 +57,13 @@ def test_transformer_batch_cell_on_gpu(lane, fmt, kind):
 
 
 @pytest.mark.parametrize("kind", fixtures.KINDS)
-@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+@pytest.mark.parametrize("lane,fmt", decoder_ref.LANE_FORMATS)
 def test_transformer_ragged_cell_on_gpu(lane, fmt, kind):
     """The table's `ragged` column on the CUDA path: forward(x, lengths=...) with NaN junk in the padding; real positions
     equal the row alone, padding is exactly +0.0, and the padded outputs hash to the reference's cell."""
     w, dims = decoder_ref.transformer_lane_weights()
     packed = lowbit.pack(w, fmt) if fmt != "float32" else w
-    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"])
+    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"], window=decoder_ref.lane_window(lane))
     outs = []
     for x, lens in decoder_ref.ragged_inputs(fixtures.fixture(kind, seed=1), dims["d_model"]):
         y = blk.forward(x, lengths=lens)
@@ -79,13 +79,13 @@ def test_transformer_ragged_cell_on_gpu(lane, fmt, kind):
 
 
 @pytest.mark.parametrize("kind", fixtures.KINDS)
-@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+@pytest.mark.parametrize("lane,fmt", decoder_ref.LANE_FORMATS)
 def test_transformer_batchscale_cell_on_gpu(lane, fmt, kind):
     """The table's `batchscale` column on the CUDA path: the 1024-row call against sub-batches of 1, 17, 64 and 256 rows
     at three offsets, the 1024-position call against prefixes around the 64 / 128 / 256 / 512 boundaries."""
     w, dims = decoder_ref.transformer_lane_weights()
     packed = lowbit.pack(w, fmt) if fmt != "float32" else w
-    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"])
+    blk = TransformerBlock(packed, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"], window=decoder_ref.lane_window(lane))
     x, xl = decoder_ref.batchscale_inputs(fixtures.fixture(kind, seed=1), dims["d_model"])
     y, yl = blk.forward(x), blk.forward(xl)
     assert decoder_ref.batchscale_cell_hash(y, yl) == TABLE["cells"]["%s/%s" % (lane, kind)]["batchscale"]

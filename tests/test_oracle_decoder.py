@@ -28,11 +28,12 @@ def _materialise(w, fmt):
 
 
 @pytest.mark.parametrize("kind", fixtures.KINDS)
-@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+@pytest.mark.parametrize("lane,fmt", decoder_ref.LANE_FORMATS)
 def test_transformer_infer_cell(lane, fmt, kind):
     """forward of the held-out (2, 16, 32) slab hashes to the table's `infer` cell (tools/identity_break.py:3639-3653, :3729-3737)."""
     w, dims = decoder_ref.transformer_lane_weights()
-    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"])
+    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"],
+                           window=decoder_ref.lane_window(lane))
     x = decoder_ref.seq(fixtures.fixture(kind, seed=1), 2, 16, dims["d_model"])
     slots = decoder_ref.block_slots(_materialise(w, fmt))
     y = oracle.block_forward(cfg, slots, x)
@@ -45,12 +46,13 @@ def test_transformer_infer_cell(lane, fmt, kind):
 
 
 @pytest.mark.parametrize("kind", fixtures.KINDS)
-@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+@pytest.mark.parametrize("lane,fmt", decoder_ref.LANE_FORMATS)
 def test_transformer_batch_cell(lane, fmt, kind):
     """The `batch` column: forward of the held-out (8, 16, 32) slab; a sequence alone and a prefix reproduce the whole
     batch's bytes, and the whole-batch rows hash to the reference's cell (tools/identity_break.py:9591-9604)."""
     w, dims = decoder_ref.transformer_lane_weights()
-    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"])
+    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"],
+                           window=decoder_ref.lane_window(lane))
     slots = decoder_ref.block_slots(_materialise(w, fmt))
     x = decoder_ref.seq(fixtures.fixture(kind, seed=1), 8, 16, dims["d_model"])
     y = oracle.block_forward(cfg, slots, x)
@@ -60,12 +62,13 @@ def test_transformer_batch_cell(lane, fmt, kind):
 
 
 @pytest.mark.parametrize("kind", fixtures.KINDS)
-@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+@pytest.mark.parametrize("lane,fmt", decoder_ref.LANE_FORMATS)
 def test_transformer_ragged_cell(lane, fmt, kind):
     """The `ragged` column: every row at its own length (up to 300 positions, past the 128-step leaf of the products
     inside), padding exactly +0.0; the padded outputs hash to the reference's cell."""
     w, dims = decoder_ref.transformer_lane_weights()
-    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"])
+    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"],
+                           window=decoder_ref.lane_window(lane))
     slots = decoder_ref.block_slots(_materialise(w, fmt))
     outs = []
     for x, lens in decoder_ref.ragged_inputs(fixtures.fixture(kind, seed=1), dims["d_model"]):
@@ -77,12 +80,13 @@ def test_transformer_ragged_cell(lane, fmt, kind):
 
 
 @pytest.mark.parametrize("kind", fixtures.KINDS)
-@pytest.mark.parametrize("lane,fmt", [("transformer", "float32"), ("transformer-bf16w", "bfloat16"), ("transformer-int8w", "int8")])
+@pytest.mark.parametrize("lane,fmt", decoder_ref.LANE_FORMATS)
 def test_transformer_batchscale_cell(lane, fmt, kind):
     """The `batchscale` column: 1024 sequences in one call and a 1024-position call whose key axis crosses seven
     128-step boundaries; sub-batches and prefixes give the whole call's bytes, which hash to the reference's cell."""
     w, dims = decoder_ref.transformer_lane_weights()
-    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"])
+    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"],
+                           window=decoder_ref.lane_window(lane))
     slots = decoder_ref.block_slots(_materialise(w, fmt))
     x, xl = decoder_ref.batchscale_inputs(fixtures.fixture(kind, seed=1), dims["d_model"])
     y, yl = oracle.block_forward(cfg, slots, x), oracle.block_forward(cfg, slots, xl)
