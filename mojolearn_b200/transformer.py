@@ -151,19 +151,92 @@ class ShardedLinear(object):
 
 
 class TransformerState(object):
-    """Caller-owned KV caches `[B, n_kv_heads, max_tokens, head_dim]` float32 and the tokens cached."""
+    """Caller-owned KV caches `[B, n_kv_heads, max_tokens, head_dim]` float32 on the device and the tokens cached
+    (the reference's state, `_transformer_impl.py:194-236`; its host buffers are packed at stride `cached_tokens`,
+    which `k_cache` / `v_cache` below reproduce on request). `window` records the sliding window the state was
+    allocated for; a session checks it against the block's."""
 
-    def __init__(self, batch, n_kv_heads, max_tokens, head_dim, device):
+    def __init__(self, batch, n_kv_heads, max_tokens, head_dim, device, window=0):
         self.k = torch.zeros((batch, n_kv_heads, max_tokens, head_dim), dtype=torch.float32, device=device)
         self.v = torch.zeros_like(self.k)
         self.cached_tokens = 0
         self.max_tokens = max_tokens
+        self.window = int(window or 0)
+        self.session = None  # the open decode session that owns this state, if any
+
+    @property
+    def batch_size(self):
+        return self.k.shape[0]
 
     def clone(self):
         other = TransformerState.__new__(TransformerState)
         other.k, other.v = self.k.clone(), self.v.clone()
-        other.cached_tokens, other.max_tokens = self.cached_tokens, self.max_tokens
+        other.cached_tokens, other.max_tokens, other.window, other.session = self.cached_tokens, self.max_tokens, self.window, None
         return other
+
+    def keys(self):
+        """The used part of the key cache, (B, n_kv_heads, cached_tokens, head_dim), as a host array."""
+        return self.k[:, :, :self.cached_tokens, :].contiguous().cpu().numpy()
+
+    def values(self):
+        return self.v[:, :, :self.cached_tokens, :].contiguous().cpu().numpy()
+
+    def _packed(self, cache):
+        flat = np.zeros(cache.numel(), dtype=np.float32)
+        used = cache[:, :, :self.cached_tokens, :].contiguous().cpu().numpy().reshape(-1)
+        flat[:used.size] = used
+        return flat
+
+    @property
+    def k_cache(self):
+        """The reference's flat host buffer: the used keys packed as [B, KV, cached_tokens, HD], then spare zeros."""
+        return self._packed(self.k)
+
+    @property
+    def v_cache(self):
+        return self._packed(self.v)
+
+
+class TransformerDecodeSession(object):
+    """A resident decode session over one block and one state (the reference's `TransformerBlock.decode_session`,
+    `_transformer_impl.py:609-633`). Every output is byte for byte the per-call `step` / `forward` on the same
+    block and state: here the state already lives on the device between calls, so the session is the ownership
+    protocol around it (one open session per state, a fixed batch size, the block's window) and `sync_state`
+    only waits for the device."""
+
+    def __init__(self, block, state):
+        self.block, self.state, self.is_open = block, state, True
+        state.session = self
+
+    def _check(self, x):
+        if not self.is_open:
+            raise RuntimeError("the decode session is closed")
+        if x.shape[0] != self.state.batch_size:
+            raise ValueError("the session was opened for %d sequences, got %d" % (self.state.batch_size, x.shape[0]))
+
+    def step(self, x):
+        self._check(x)
+        return self.block.step(x, self.state)
+
+    def forward(self, x):
+        self._check(x)
+        return self.block.forward(x, self.state)
+
+    def sync_state(self):
+        torch.cuda.synchronize(self.block.device)
+        return self.state
+
+    def close(self):
+        if self.is_open:
+            self.is_open = False
+            self.state.session = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+        return False
 
 
 def norm(x2d, w, bias, eps, kind):
@@ -306,8 +379,20 @@ class TransformerBlock(object):
         self.down = ShardedLinear(self.down, group, rank, world)
         self.group = group
 
-    def allocate_state(self, batch, max_tokens):
-        return TransformerState(batch, self.kv_local, int(max_tokens), self.head_dim, self.device)
+    def allocate_state(self, batch, max_tokens, window=None):
+        return TransformerState(batch, self.kv_local, int(max_tokens), self.head_dim, self.device,
+                                self.window if window is None else window)
+
+    def decode_session(self, state):
+        """Open a resident decode session on `state` (see TransformerDecodeSession)."""
+        if state is None:
+            raise ValueError("decode_session: a state is required")
+        if state.session is not None and state.session.is_open:
+            raise RuntimeError("decode_session: the state is already resident in an open session")
+        if int(state.window) != int(self.window):
+            raise ValueError("decode_session: the state was allocated for window %d, the block has window %d" %
+                             (state.window, self.window))
+        return TransformerDecodeSession(self, state)
 
     def rope_tables(self, pos0, l, position=None):
         """cos and sin [l, head_dim / 2] for this call's positions; the same for every block of a model."""

@@ -188,12 +188,32 @@ def batch_cell_hash_block(y):
     return h.hexdigest()[:16]
 
 
-def stepfull_cell_hash(y):
-    """The verify table's `stepfull` column of a block (tools/identity_break.py:10345-10382): one fresh-state forward
-    over (2, 16, d) hashed under the call's label; valid when allocate_state + one step per position reproduces it."""
+def decode_session_parts(steps, prefill, k_cache, v_cache):
+    """The parts of the `transformer-decode-session` lane (tools/identity_break.py:8239-8272): the 16 stepped outputs,
+    the chunked prefill, the resident caches as the reference's flat host buffers, and the six refusal flags (all
+    true). `oracle.train_hash` of the result is the lane's `train` cell."""
+    import lanes
+    flags = np.ones(6, dtype=np.int64)
+    return dict(step=lanes.sha16(*steps), prefill=lanes.sha16(prefill), state=lanes.sha16(k_cache, v_cache), flags=lanes.sha16(flags))
+
+
+def packed_cache(cache, used):
+    """[B, KV, cap, HD] -> the reference's flat state buffer: the used positions packed as [B, KV, used, HD], then
+    spare zeros (python/mojolearn/_transformer_impl.py:194-213)."""
+    cache = np.asarray(cache, dtype=np.float32)
+    flat = np.zeros(cache.size, dtype=np.float32)
+    part = np.ascontiguousarray(cache[:, :, :used, :]).reshape(-1)
+    flat[:part.size] = part
+    return flat
+
+
+def stepfull_cell_hash(y, how="allocate_state + step"):
+    """The verify table's `stepfull` column of a block (tools/identity_break.py:10345-10382, :10402-10430): one
+    fresh-state forward over (2, 16, d) hashed under the call's label; valid when one step per position (per-call,
+    or through a decode session) reproduces it."""
     y = np.ascontiguousarray(y)
     h = hashlib.sha256()
-    h.update(("stepfull:forward(x) vs allocate_state + step, L=%d:%s" % (y.shape[1], list(y.shape))).encode())
+    h.update(("stepfull:forward(x) vs %s, L=%d:%s" % (how, y.shape[1], list(y.shape))).encode())
     h.update(("<f4%s" % (tuple(y.shape),)).encode())
     h.update(y.tobytes())
     return h.hexdigest()[:16]

@@ -227,3 +227,47 @@ def test_hf_causal_lm_infer_cell_on_gpu(kind):
     assert lm.step(ids[:, 11], state).tobytes() == np.ascontiguousarray(logits[:, 11, :]).tobytes()
     seq = lm.generate(ids[:, :6], 6)
     assert seq.tolist() == lm.generate(ids[:, :6], 6, graph=False).tolist()
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+def test_transformer_decode_session_cells_on_gpu(kind):
+    """The `transformer-decode-session` lane on the CUDA path: a session's 16 steps and its chunked forward are the
+    per-call step and forward byte for byte, its state is the per-call state, the refusals hold, and the parts hash
+    to the reference's `train`, `stepfull` and `infer` cells."""
+    from mojolearn_b200.transformer import TransformerDecodeSession
+    w, dims = decoder_ref.transformer_lane_weights()
+    blk = TransformerBlock(w, n_heads=dims["n_heads"], n_kv_heads=dims["n_kv_heads"])
+    X, dm = fixtures.fixture(kind), dims["d_model"]
+    x = decoder_ref.seq(X, 2, 16, dm)
+    st = blk.allocate_state(2, max_tokens=32)
+    with blk.decode_session(st) as sess:
+        steps = [np.ascontiguousarray(sess.step(np.ascontiguousarray(x[:, t:t + 1]))) for t in range(16)]
+        sess.sync_state()
+        resident = (st.k_cache, st.v_cache)
+    plain = blk.allocate_state(2, max_tokens=32)
+    per_call = [blk.step(np.ascontiguousarray(x[:, t:t + 1]), plain) for t in range(16)]
+    assert np.concatenate(steps, axis=1).tobytes() == np.concatenate(per_call, axis=1).tobytes()
+    assert resident[0].tobytes() == plain.k_cache.tobytes() and resident[1].tobytes() == plain.v_cache.tobytes()
+    chunk = decoder_ref.seq(X, 2, 16, dm, skip=1024)
+    with blk.decode_session(blk.allocate_state(2, max_tokens=32)) as sess:
+        prefill = np.ascontiguousarray(sess.forward(chunk))
+    assert prefill.tobytes() == blk.forward(chunk, blk.allocate_state(2, max_tokens=32)).tobytes()
+    closed = blk.decode_session(blk.allocate_state(2, max_tokens=32))
+    closed.close()
+    busy = blk.allocate_state(2, max_tokens=32)
+    open_session = blk.decode_session(busy)
+    assert type(open_session) is TransformerDecodeSession and open_session.is_open and not closed.is_open
+    with pytest.raises(RuntimeError, match="session is closed"):
+        closed.step(np.zeros((2, 1, dm), dtype=np.float32))
+    with pytest.raises(RuntimeError, match="resident"):
+        blk.decode_session(busy)
+    with pytest.raises(ValueError, match="state is required"):
+        blk.decode_session(None)
+    with pytest.raises(ValueError, match="window"):
+        blk.decode_session(blk.allocate_state(2, max_tokens=32, window=8))
+    open_session.close()
+    cell = TABLE["cells"]["transformer-decode-session/%s" % kind]
+    assert oracle.train_hash(decoder_ref.decode_session_parts(steps, prefill, *resident)) == cell["train"]
+    y = blk.forward(decoder_ref.seq(fixtures.fixture(kind, seed=1), 2, 16, dm))
+    assert decoder_ref.stepfull_cell_hash(y, "decode_session step") == cell["stepfull"]
+    assert oracle.sha16(y) == cell["infer"]

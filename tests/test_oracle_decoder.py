@@ -96,6 +96,26 @@ def test_transformer_batchscale_cell(lane, fmt, kind):
         assert oracle.block_forward(cfg, slots, np.ascontiguousarray(xl[:, :p])).tobytes() == np.ascontiguousarray(yl[:, :p]).tobytes()
 
 
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+def test_transformer_decode_session_cells(kind):
+    """The `transformer-decode-session` lane: `train` = the 16 stepped positions, the chunked prefill, the resident
+    caches and the refusal flags; `stepfull` = the forward under the session's label; `infer` = the transformer lane's."""
+    w, dims = decoder_ref.transformer_lane_weights()
+    cfg = oracle.block_cfg(dims["d_model"], dims["n_heads"], dims["n_kv_heads"], dims["head_dim"], dims["inter"])
+    slots = decoder_ref.block_slots(_materialise(w, "float32"))
+    X, dm = fixtures.fixture(kind), dims["d_model"]
+    x = decoder_ref.seq(X, 2, 16, dm)
+    state = oracle.KVState(2, dims["n_kv_heads"], 32, dims["head_dim"])
+    steps = [oracle.block_forward(cfg, slots, x[:, t:t + 1].copy(), state) for t in range(16)]
+    prefill = oracle.block_forward(cfg, slots, decoder_ref.seq(X, 2, 16, dm, skip=1024), oracle.KVState(2, dims["n_kv_heads"], 32, dims["head_dim"]))
+    parts = decoder_ref.decode_session_parts(steps, prefill, decoder_ref.packed_cache(state.k, 16), decoder_ref.packed_cache(state.v, 16))
+    cell = TABLE["cells"]["transformer-decode-session/%s" % kind]
+    assert oracle.train_hash(parts) == cell["train"]
+    y = oracle.block_forward(cfg, slots, decoder_ref.seq(fixtures.fixture(kind, seed=1), 2, 16, dm))
+    assert decoder_ref.stepfull_cell_hash(y, "decode_session step") == cell["stepfull"]
+    assert oracle.sha16(y) == cell["infer"]
+
+
 def test_portable_math_is_close_to_libm_and_exact_at_anchors():
     assert oracle.math("powf", 10000.0, 0.0) == 1.0
     assert oracle.math("rsqrtf", 16.0) == 0.25 and oracle.math("rsqrtf", 64.0) == 0.125
