@@ -121,6 +121,27 @@ def lane_window(lane):
     return 8 if lane == "transformer-window" else 0
 
 
+def embedding_lane(Xh):
+    """The forward half of the verify table's `embedding` lane (tools/identity_break.py:7601-7621, :9530-9534): a hashed
+    (128, 16) table, the 512 held-out ids of the `infer` column and the 64 of the `batch` column."""
+    w = hashed_weight((128, 16), "emb:w", -0.25, 0.25)
+    ids = (fixture_ids(Xh, 1, 512, 256).reshape(512) % 128).astype(np.int32)
+    ids64 = (fixture_ids(Xh, 1, 64, 256).reshape(64) % 128).astype(np.int32)
+    return w, ids, ids64
+
+
+def rows_cell_hash(label, out):
+    """A `batch` column made of one row-wise call (tools/identity_break.py:8624-8644, :8726-8727)."""
+    out = np.ascontiguousarray(out)
+    h = hashlib.sha256()
+    h.update(("rows:%s:%d" % (label, out.shape[0])).encode())
+    head = ("%s%s" % (out.dtype.str, tuple(out.shape[1:]))).encode()
+    for row in out:
+        h.update(head)
+        h.update(row.tobytes())
+    return h.hexdigest()[:16]
+
+
 def lcg_floats(n, seed, lo=-0.125, hi=0.125):
     """`n` float32 values in [lo, hi) from the 64-bit LCG of the reference's synthetic checkpoints
     (python/mojolearn/_causal_lm_fixtures.py:38-47): hashed, not random, the same bytes on every machine."""

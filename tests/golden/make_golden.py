@@ -22,7 +22,7 @@ import os
 import sys
 
 LANES = ["gemm-pinned", "gemm-transposed", "gemm-bf16", "gemm-int8", "lowbit-conversions",
-         "transformer", "transformer-bf16w", "transformer-int8w", "transformer-window", "transformer-decode-session", "hf-causal-lm"]
+         "transformer", "transformer-bf16w", "transformer-int8w", "transformer-window", "transformer-decode-session", "embedding", "hf-causal-lm"]
 
 
 def main(ref):

@@ -271,3 +271,24 @@ def test_transformer_decode_session_cells_on_gpu(kind):
     y = blk.forward(decoder_ref.seq(fixtures.fixture(kind, seed=1), 2, 16, dm))
     assert decoder_ref.stepfull_cell_hash(y, "decode_session step") == cell["stepfull"]
     assert oracle.sha16(y) == cell["infer"]
+
+
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+def test_embedding_lane_infer_and_batch_cells_on_gpu(kind):
+    """The `embedding` lane's forward on the CUDA path (b200i_embedding): `infer` and `batch` cells of the verify table."""
+    w, ids, ids64 = decoder_ref.embedding_lane(fixtures.fixture(kind, seed=1))
+    dw, status = torch.from_numpy(w).cuda(), torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def gather(some):
+        di = torch.from_numpy(np.ascontiguousarray(some)).cuda()
+        y = torch.empty((len(some), w.shape[1]), dtype=torch.float32, device="cuda")
+        _native.call("b200i_embedding", 0, None, ctypes.c_void_p(y.data_ptr()), ctypes.c_void_p(dw.data_ptr()),
+                     ctypes.c_void_p(di.data_ptr()), len(some), w.shape[0], w.shape[1], ctypes.c_void_p(status.data_ptr()))
+        return y.cpu().numpy()
+
+    assert oracle.sha16(gather(ids)) == TABLE["cells"]["embedding/%s" % kind]["infer"]
+    y64 = gather(ids64)
+    assert decoder_ref.rows_cell_hash("forward", y64) == TABLE["cells"]["embedding/%s" % kind]["batch"]
+    for a, b in ((0, 1), (1, 8), (8, 64)):
+        assert gather(ids64[a:b]).tobytes() == y64[a:b].tobytes()
+    assert int(status.item()) == 0

@@ -116,6 +116,18 @@ def test_transformer_decode_session_cells(kind):
     assert oracle.sha16(y) == cell["infer"]
 
 
+@pytest.mark.parametrize("kind", fixtures.KINDS)
+def test_embedding_lane_infer_and_batch_cells(kind):
+    """The gather Y = ftz(W[id]) on the verify table's `embedding` lane: 512 held-out ids (`infer`), and 64 ids whose
+    rows alone give the whole call's bytes (`batch`)."""
+    w, ids, ids64 = decoder_ref.embedding_lane(fixtures.fixture(kind, seed=1))
+    y = oracle.embedding(w, ids.reshape(1, -1)).reshape(len(ids), -1)
+    assert oracle.sha16(y) == TABLE["cells"]["embedding/%s" % kind]["infer"]
+    y64 = oracle.embedding(w, ids64.reshape(1, -1)).reshape(64, -1)
+    assert decoder_ref.rows_cell_hash("forward", y64) == TABLE["cells"]["embedding/%s" % kind]["batch"]
+    assert oracle.embedding(w, ids64[5:6].reshape(1, 1)).reshape(1, -1).tobytes() == y64[5:6].tobytes()
+
+
 def test_portable_math_is_close_to_libm_and_exact_at_anchors():
     assert oracle.math("powf", 10000.0, 0.0) == 1.0
     assert oracle.math("rsqrtf", 16.0) == 0.25 and oracle.math("rsqrtf", 64.0) == 0.125
