@@ -14,6 +14,10 @@
 #include "gemm_skinny.cuh"
 #include "gemm_packed.cuh"
 #include "gemm_skinny_packed.cuh"
+#include "gemm_skinny_reg.cuh"
+#ifndef B200I_SK_REG
+#define B200I_SK_REG 1
+#endif
 #include "lowbit.cuh"
 
 using namespace b200i;
@@ -130,19 +134,40 @@ Plan choose_plan(long long m, long long n, long long k, int sms) {
     return best;
 }
 
-// The skinny plan's leaf split: the largest power-of-two group that still gives
-// every CTA slot of the device a CTA (the kernel is latency-bound, so resident
-// warps matter more than the few extra group nodes), else single leaves.
-Plan choose_skinny(long long m, long long n, long long k, int sms) {
+// The skinny plan's leaf split. Float32 weights (shared-memory kernel): the largest
+// power-of-two group that still gives every CTA slot of the device a CTA, else
+// single leaves. Low-bit weights (register kernel): the split minimises a modelled
+// time in microseconds fitted to measurements on B200 -- rounds of CTAs per SM times
+// (leaves per CTA at the kernel's sustained rate, slower while an SM holds fewer than
+// three CTAs, plus a fixed cost per CTA), plus the second launch and the L2-resident
+// node traffic of the group fold.
+Plan choose_skinny(long long m, long long n, long long k, int sms, bool lowbit) {
     const int leaves = (int)leaf_count(k) > 0 ? (int)leaf_count(k) : 1;
-    const long long col_ctas = (n + skinny_bn((int)m) - 1) / skinny_bn((int)m);
-    const long long want = (long long)sms * skinny_per_sm((int)m) * 9 / 10;
     const int max_s = pow2_floor(leaves) * ((leaves & (leaves - 1)) ? 2 : 1);
     int min_s = 1;
     while ((leaves + min_s - 1) / min_s > MAX_GROUPS) min_s *= 2;
     int best = min_s;
-    for (int s = max_s; s >= min_s; s /= 2)
-        if (col_ctas * ((leaves + s - 1) / s) >= want) { best = s; break; }
+    if (lowbit && B200I_SK_REG) {
+        const int bm = skr_bm((int)m), bn = skr_bn((int)m);
+        const long long tiles = ((n + bn - 1) / bn) * ((m + bm - 1) / bm);
+        const double rate = bm >= 32 ? 0.25e6 : (bm >= 16 ? 0.20e6 : 0.15e6); // flops per microsecond per SM
+        const double leaf_us = 2.0 * bm * bn * (double)leaf_size(k) / rate;
+        double best_t = 1e300;
+        for (int s = max_s; s >= min_s; s /= 2) {
+            const int groups = (leaves + s - 1) / s;
+            const long long ctas = tiles * groups;
+            const long long rounds = (ctas + sms - 1) / sms;
+            const double thin = ctas <= sms ? 1.25 : (ctas <= 2 * sms ? 1.08 : 1.0);
+            double t = (double)rounds * (s * leaf_us * thin + 0.4);
+            if (groups > 1) t += 2.5 + (double)groups * m * n * 8.0 / 7.5e6;
+            if (t < best_t) { best_t = t; best = s; }
+        }
+    } else {
+        const long long col_ctas = (n + skinny_bn((int)m) - 1) / skinny_bn((int)m);
+        const long long want = (long long)sms * skinny_per_sm((int)m) * 9 / 10;
+        for (int s = max_s; s >= min_s; s /= 2)
+            if (col_ctas * ((leaves + s - 1) / s) >= want) { best = s; break; }
+    }
     Plan p{PLAN_SKINNY, best, (leaves + best - 1) / best};
     if (p.groups <= 1) p.group_leaves = leaves;
     return p;
@@ -340,7 +365,7 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
         const bool al16 = aligned(b, 16) && aligned(a, 16);
         const bool dec = decode_plan_fits(m, n, k, op, wkind) && al16;
         if (dec && m <= DECODE_PREFER_M) plan = Plan{PLAN_DECODE, g.leaves, 1};
-        else if (skinny_plan_fits(m, n, k, op) && al16) plan = choose_skinny(m, n, k, sm_count(dev));
+        else if (skinny_plan_fits(m, n, k, op) && al16) plan = choose_skinny(m, n, k, sm_count(dev), wkind != W_F32);
         else if (dec) plan = Plan{PLAN_DECODE, g.leaves, 1};
     } else {
         plan.kind = plan_kind;
@@ -406,7 +431,9 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     } else if (plan.kind == PLAN_SKINNY) {
         if (!skinny_plan_fits(m, n, k, op) || !aligned(b, 16) || !aligned(a, 16))
             return fail(err, err_cap, "identical gemm: the skinny plan needs op NT, m <= 32, k a multiple of 16 and 16-byte aligned operands");
-        launch_skinny(g, plan.groups, st);
+        // low-bit weights stay in registers; float32 windows are too wide for that and go through shared memory
+        if (B200I_SK_REG && g.wkind != W_F32) launch_skinny_reg(g, plan.groups, st);
+        else launch_skinny(g, plan.groups, st);
         g_launches++;
     } else {
         return fail(err, err_cap, "identical gemm: unknown plan %d", plan.kind);
@@ -496,8 +523,10 @@ int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (p.kind == PLAN_T128 && m >= PACKED_MIN_EXTENT && n >= PACKED_MIN_EXTENT)
         return (int64_t)packed_need(m, n, k, packed_split(p, m, n, sm_count(dev)).groups);
     if (skinny_plan_fits(m, n, k, OP_NT)) { // the plan an NT product with aligned operands takes instead
-        const Plan q = choose_skinny(m, n, k, sm_count(dev));
-        if (q.groups > groups) groups = q.groups;
+        for (int lowbit = 0; lowbit < 2; lowbit++) {
+            const Plan q = choose_skinny(m, n, k, sm_count(dev), lowbit != 0);
+            if (q.groups > groups) groups = q.groups;
+        }
     }
     return groups > 1 ? (int64_t)groups * m * n * 4 : 0;
 }

@@ -125,6 +125,12 @@ def test_decode_plan_edges():
     for plan in (torch_ops.PLAN_DECODE, torch_ops.PLAN_T64, torch_ops.PLAN_FLAT, torch_ops.PLAN_AUTO, torch_ops.PLAN_PACKED):
         got = torch_ops.product(dx, dc, de, linalg.W_INT8_EXP, oracle.OP_NT, plan=plan)
         assert got.cpu().numpy().tobytes() == want.tobytes(), plan
+    scales = (rng.uniform(0.5, 2.0, n) * 2.0 ** -66).astype(np.float32)
+    scales[:4] = [np.float32(2e-42), np.float32(3e37), np.float32(1.0), np.float32(0.0)]
+    wants = oracle.nan_canon(oracle.gemm(x, oracle.dequantize_int8_scaled(codes, scales), oracle.OP_NT))
+    got = torch_ops.product(dx, torch.from_numpy(codes).cuda(), torch.from_numpy(scales).cuda(), linalg.W_INT8_SCALE, oracle.OP_NT,
+                            plan=torch_ops.PLAN_SKINNY)
+    assert got.cpu().numpy().tobytes() == wants.tobytes()
     wb = oracle.to_bf16((rng.standard_normal((n, k)) * 2.0 ** -64).astype(np.float32))
     wantb = oracle.gemm(x, oracle.from_bf16(wb), oracle.OP_NT)
     for plan in (torch_ops.PLAN_DECODE, torch_ops.PLAN_T128, torch_ops.PLAN_PACKED):
@@ -167,6 +173,12 @@ def test_skinny_plan_every_storage_kind():
     for plan in (torch_ops.PLAN_SKINNY, torch_ops.PLAN_AUTO):
         got = torch_ops.product(dx, torch.from_numpy(codes).cuda(), torch.from_numpy(exps).cuda(), linalg.W_INT8_EXP, oracle.OP_NT, plan=plan)
         assert got.cpu().numpy().tobytes() == want.tobytes(), plan
+    scales = (rng.uniform(0.5, 2.0, n) * 2.0 ** -66).astype(np.float32)
+    scales[:4] = [np.float32(2e-42), np.float32(3e37), np.float32(1.0), np.float32(0.0)]
+    wants = oracle.nan_canon(oracle.gemm(x, oracle.dequantize_int8_scaled(codes, scales), oracle.OP_NT))
+    got = torch_ops.product(dx, torch.from_numpy(codes).cuda(), torch.from_numpy(scales).cuda(), linalg.W_INT8_SCALE, oracle.OP_NT,
+                            plan=torch_ops.PLAN_SKINNY)
+    assert got.cpu().numpy().tobytes() == wants.tobytes()
     wb = oracle.to_bf16((rng.standard_normal((n, k)) * 2.0 ** -64).astype(np.float32))
     wantb = oracle.gemm(x, oracle.from_bf16(wb), oracle.OP_NT)
     got = torch_ops.product(dx, torch.from_numpy(wb).cuda(), None, linalg.W_BF16, oracle.OP_NT, plan=torch_ops.PLAN_SKINNY)
