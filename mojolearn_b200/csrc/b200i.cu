@@ -78,7 +78,16 @@ int select_device(int64_t device, char *err, int64_t err_cap, int *out) {
 // ---- plans -----------------------------------------------------------------------------
 enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4, PLAN_T128X64 = 5, PLAN_SKINNY = 6, PLAN_PACKED = 7 };
 
-constexpr int DECODE_PREFER_M = 4; // up to this many rows the weight-streaming decode plan wins; above, the skinny plan
+// Up to this many rows the weight-streaming decode plan wins; above, the skinny plan. Low-bit weights
+// switch earlier: at three and four rows the decode kernel's serial chains cost more than the register
+// skinny kernel's eight-row tile (int8 [11008, 4096]: 44 us against 37 us at four rows, 40 against 36 at
+// three), except on a very wide weight, where the decode kernel's row streams run at their best
+// ([50304, 2048]: bf16 79 us against 98 at four rows, int8 60 against 69 at three).
+constexpr int DECODE_PREFER_M = 4;
+constexpr long long DECODE_WIDE_N = 32768;
+#ifndef B200I_DECODE_PREFER_M_LOWBIT
+#define B200I_DECODE_PREFER_M_LOWBIT 2
+#endif
 
 struct Plan {
     int kind;
@@ -151,13 +160,14 @@ Plan choose_skinny(long long m, long long n, long long k, int sms, bool lowbit) 
         const int bm = skr_bm((int)m), bn = skr_bn((int)m);
         const long long tiles = ((n + bn - 1) / bn) * ((m + bm - 1) / bm);
         const double rate = bm >= 32 ? 0.25e6 : (bm >= 16 ? 0.20e6 : 0.15e6); // flops per microsecond per SM
-        const double leaf_us = 2.0 * bm * bn * (double)leaf_size(k) / rate;
+        // a CTA's leaf: its multiply-adds at that rate, or its weight bytes at an SM's share of the HBM stream
+        const double leaf_us = std::max(2.0 * bm * bn * (double)leaf_size(k) / rate, (double)bn * (double)leaf_size(k) / 40.0e3);
         double best_t = 1e300;
         for (int s = max_s; s >= min_s; s /= 2) {
             const int groups = (leaves + s - 1) / s;
             const long long ctas = tiles * groups;
             const long long rounds = (ctas + sms - 1) / sms;
-            const double thin = ctas <= sms ? 1.25 : (ctas <= 2 * sms ? 1.08 : 1.0);
+            double thin = ctas <= sms ? 1.25 : (ctas <= 2 * sms ? 1.08 : 1.0);
             double t = (double)rounds * (s * leaf_us * thin + 0.4);
             if (groups > 1) t += 2.5 + (double)groups * m * n * 8.0 / 7.5e6;
             if (t < best_t) { best_t = t; best = s; }
@@ -364,8 +374,11 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
         }
         const bool al16 = aligned(b, 16) && aligned(a, 16);
         const bool dec = decode_plan_fits(m, n, k, op, wkind) && al16;
-        if (dec && m <= DECODE_PREFER_M) plan = Plan{PLAN_DECODE, g.leaves, 1};
-        else if (skinny_plan_fits(m, n, k, op) && al16) plan = choose_skinny(m, n, k, sm_count(dev), wkind != W_F32);
+        const bool skinny = skinny_plan_fits(m, n, k, op) && al16;
+        const bool wide = n >= DECODE_WIDE_N && (wkind == W_BF16 || m == 3);
+        const int prefer_m = (wkind != W_F32 && skinny && B200I_SK_REG && !wide) ? B200I_DECODE_PREFER_M_LOWBIT : DECODE_PREFER_M;
+        if (dec && m <= prefer_m) plan = Plan{PLAN_DECODE, g.leaves, 1};
+        else if (skinny) plan = choose_skinny(m, n, k, sm_count(dev), wkind != W_F32);
         else if (dec) plan = Plan{PLAN_DECODE, g.leaves, 1};
     } else {
         plan.kind = plan_kind;

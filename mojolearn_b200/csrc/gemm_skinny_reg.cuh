@@ -6,7 +6,7 @@
 // shared memory: each window is one 128-bit load per weight row (int8; two for
 // bf16) straight into registers, fetched one window ahead and widened exactly, one
 // element per k-step, right where it is used. Only the activations are staged: a
-// chunk of up to SKR_CHUNK_LEAVES leaves of the CTA's rows is transposed into shared
+// chunk of up to skr_chunk_leaves(BM) leaves of the CTA's rows is transposed into shared
 // memory once, with one admission key per 16-step window, so the k loop itself has
 // no barrier at all.
 // (2) CPT columns per thread and an optional split of the rows over blockIdx.z are
@@ -23,13 +23,11 @@
 
 namespace b200i {
 
-#ifndef B200I_SKR_CHUNK_LEAVES
-#define B200I_SKR_CHUNK_LEAVES 2
-#endif
-constexpr int SKR_CHUNK_LEAVES = B200I_SKR_CHUNK_LEAVES;
+// leaves of activations staged at a time: 32 KiB at 32 rows, 16 KiB at 16 and 8
+constexpr int skr_chunk_leaves(int bm) { return bm >= 16 ? 2 : 32 / bm; }
 
 constexpr int skr_smem_bytes(int bm, int leaf) {
-    return SKR_CHUNK_LEAVES * leaf * bm * 4 + SKR_CHUNK_LEAVES * (leaf / KS) * 4;
+    return skr_chunk_leaves(bm) * leaf * bm * 4 + skr_chunk_leaves(bm) * (leaf / KS) * 4;
 }
 
 template <int WK>
@@ -69,6 +67,7 @@ __global__ void __launch_bounds__(SK_THREADS, MINB) gemm_skinny_reg_kernel(const
     static_assert(WK != W_F32, "float32 weights use the shared-memory skinny kernel");
     constexpr int CELLS = BM * CPT, ES = WK == W_BF16 ? 2 : 1, BN = SK_THREADS * CPT;
     constexpr bool INT8 = WK != W_BF16;
+    constexpr int SKR_CHUNK_LEAVES = BM >= 16 ? 2 : 32 / BM; // skr_chunk_leaves(BM)
     extern __shared__ __align__(16) float skr_smem[];
     const int chunk_k = SKR_CHUNK_LEAVES * g.leaf;
     float *As = skr_smem;                                                            // [chunk_k][BM]
@@ -304,8 +303,8 @@ __global__ void __launch_bounds__(SK_THREADS, MINB) gemm_skinny_reg_kernel(const
 #ifndef B200I_SKR_MINB8
 #define B200I_SKR_MINB8 5
 #endif
-inline int skr_bn(int m) { return SK_THREADS * (m <= 8 ? B200I_SKR_CPT8 : (m <= 16 ? B200I_SKR_CPT16 : B200I_SKR_CPT32)); }
 inline int skr_bm(int m) { return m <= 8 ? 8 : (m <= 16 ? 16 : B200I_SKR_BM32); }
+inline int skr_bn(int m) { return SK_THREADS * (m <= 8 ? B200I_SKR_CPT8 : (m <= 16 ? B200I_SKR_CPT16 : B200I_SKR_CPT32)); }
 inline int skr_per_sm(int m) { return m <= 8 ? B200I_SKR_MINB8 : (m <= 16 ? B200I_SKR_MINB16 : B200I_SKR_MINB32); }
 
 template <int WK, int BM, int CPT, int MINB>
