@@ -989,12 +989,11 @@ static int64_t attention_launch(int dev, cudaStream_t st, float *ctx, const floa
     } else {
         dim3 g2((unsigned)((l + CTX_ROWS - 1) / CTX_ROWS), (unsigned)(b * n_heads));
 #define CONTEXT_ROWS(DPL)                                                                                                     \
-    attn_context_kernel<DPL><<<g2, 32 * CTX_ROWS, (size_t)CTX_KT * head_dim * sizeof(float), st>>>(                           \
+    attn_context_kernel<DPL><<<g2, 32 * CTX_WARPS, attn_context_smem((int)head_dim), st>>>(                                   \
         ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, key_lo, s, own0, (int)window, position)
         if (head_dim <= 32) CONTEXT_ROWS(1);
         else if (head_dim <= 64) CONTEXT_ROWS(2);
-        else if (head_dim <= 128) CONTEXT_ROWS(4);
-        else CONTEXT_ROWS(8);
+        else CONTEXT_ROWS(4);
 #undef CONTEXT_ROWS
     }
     g_launches += 2;

@@ -349,40 +349,84 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(float *__restrict__ sc
     if ((int)blockIdx.x * ATT_T >= s) return;
     // the attention scale, ftz(rsqrt(head_dim)) in the portable spelling: a pure function of head_dim
     const float scale = ftz_bits(p_rsqrtf((float)hd));
-    __shared__ float qs[ATT_KC][ATT_T + 1];
-    __shared__ float ks[ATT_KC][ATT_T + 1];
+    __shared__ __align__(16) float qs[ATT_KC][ATT_T + 4]; // pitch 68 words: rows stay 16-byte aligned
+    __shared__ __align__(16) float ks[ATT_KC][ATT_T + 4];
     const int bh = blockIdx.z, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
     const int q0 = blockIdx.y * ATT_T, j0 = blockIdx.x * ATT_T;
     const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
     const long long qw = (long long)nh * hd;
     const float *qbase = q + ((long long)bb * l) * qw + (long long)h * hd;
     const float *kbase = kcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
+    const float mfill = __uint_as_float(0xFF7FFFFFu);
+    // A tile no query of which can see any of its keys: every cell is ftz(score + (-FLT_MAX)). When every
+    // operand word of the tile is finite and below 2^40 in magnitude, |score| < 2^88 is under half an ulp of
+    // FLT_MAX (2^103), so the sum IS -FLT_MAX and the dot products need not be formed.
+    const int q_hi = min(q0 + ATT_T, l) - 1;
+    const bool tile_masked = j0 > own0 + q_hi || (window > 0 && j0 + ATT_T - 1 < own0 + q0 - window + 1);
+    if (tile_masked) {
+        bool small = true;
+        for (int idx = tid; idx < ATT_T * hd; idx += 256) {
+            const int r = idx / hd, p = idx % hd;
+            if (q0 + r < l) small = small && ((__float_as_uint(qbase[(long long)(q0 + r) * qw + p]) >> 23) & 0xFFu) < 167u;
+            if (j0 + r < s) small = small && ((__float_as_uint(kbase[(long long)(j0 + r) * hd + p]) >> 23) & 0xFFu) < 167u;
+        }
+        if (__syncthreads_and(small)) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int qi = q0 + ty * 4 + i;
+                if (qi >= l) continue;
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++) {
+                    const int j = j0 + tx * 4 + jj;
+                    if (j < s) scores[((long long)bh * l + qi) * s + j] = mfill;
+                }
+            }
+            return;
+        }
+    }
     float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    bool clean = true; // every chunk so far passed admission: the chains have only taken bare steps
     for (int p0 = 0; p0 < hd; p0 += ATT_KC) {
+        unsigned key = 0xFFFFFFFFu;
         for (int idx = tid; idx < ATT_T * ATT_KC; idx += 256) {
             const int r = idx / ATT_KC, p = idx % ATT_KC;
             const bool pk = p0 + p < hd;
-            qs[p][r] = (pk && q0 + r < l) ? ftz_bits(qbase[(long long)(q0 + r) * qw + p0 + p]) : 0.f;
-            ks[p][r] = (pk && j0 + r < s) ? ftz_bits(kbase[(long long)(j0 + r) * hd + p0 + p]) : 0.f;
+            const float qv = (pk && q0 + r < l) ? ftz_bits(qbase[(long long)(q0 + r) * qw + p0 + p]) : 0.f;
+            const float kvv = (pk && j0 + r < s) ? ftz_bits(kbase[(long long)(j0 + r) * hd + p0 + p]) : 0.f;
+            key = min(key, min(admit_key(qv), admit_key(kvv)));
+            qs[p][r] = qv;
+            ks[p][r] = kvv;
         }
-        __syncthreads();
+        clean = __syncthreads_and(key >= ADMIT_MIN) && clean;
         const int pn = min(ATT_KC, hd - p0);
-        for (int p = 0; p < pn; p++) {
-            float a[4], c[4];
+        if (clean) {
+#pragma unroll 8
+            for (int p = 0; p < pn; p++) {
+                const float4 a4 = *reinterpret_cast<const float4 *>(&qs[p][ty * 4]);
+                const float4 c4 = *reinterpret_cast<const float4 *>(&ks[p][tx * 4]);
+                const float a[4] = {a4.x, a4.y, a4.z, a4.w}, c[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
-            for (int i = 0; i < 4; i++) { a[i] = qs[p][ty * 4 + i]; c[i] = ks[p][tx * 4 + i]; }
+                for (int i = 0; i < 4; i++)
 #pragma unroll
-            for (int i = 0; i < 4; i++)
+                    for (int j = 0; j < 4; j++) acc[i][j] = step_bare(a[i], c[j], acc[i][j]);
+            }
+        } else {
+            for (int p = 0; p < pn; p++) {
+                const float4 a4 = *reinterpret_cast<const float4 *>(&qs[p][ty * 4]);
+                const float4 c4 = *reinterpret_cast<const float4 *>(&ks[p][tx * 4]);
+                const float a[4] = {a4.x, a4.y, a4.z, a4.w}, c[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
-                for (int j = 0; j < 4; j++) acc[i][j] = step_flush(a[i], c[j], acc[i][j]);
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[i][j] = step_flush(a[i], c[j], acc[i][j]);
+            }
         }
         __syncthreads();
     }
-    const float mfill = __uint_as_float(0xFF7FFFFFu);
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int qi = q0 + ty * 4 + i;
@@ -533,100 +577,239 @@ __global__ void __launch_bounds__(128) attn_scores_small_kernel(float *__restric
 }
 
 // ---- softmax and value sum ----------------------------------------------------------------------
-// One warp per query row; the eight rows of a CTA share one (batch, head) and the
-// value tiles staged in shared memory. The masked scores are overwritten in place
-// by exp(s - max) and then by the weights.
-constexpr int CTX_ROWS = 8, CTX_KT = 32, CTX_MAX_HD = 256;
-// DPL = feature slots per lane (head_dim / 32 rounded up to 1, 2, 4 or 8): a template parameter so that absent
+// A CTA owns 32 consecutive query rows of one (batch, head): eight warps of four rows.
+// The masked scores are overwritten in place by exp(s - max) and then by the weights.
+// Every chain of the seam stays serial per row; the four rows of a warp are four
+// independent chains walked together, so a value word read from the staged tile serves
+// four rows and a 128-bit broadcast read delivers the four rows' weights of one key.
+// A lane owns DPL consecutive features. A tile of 32 keys runs the bare fma when the
+// staged values and the four rows' weights pass admission and no earlier tile of the
+// warp needed the flushed step (a flushed accumulator need not be a multiple of 2^-126).
+constexpr int CTX_WARPS = 8, CTX_RPW = 4, CTX_ROWS = CTX_WARPS * CTX_RPW, CTX_KT = 32, CTX_MAX_HD = 256;
+inline size_t attn_context_smem(int hd) { return ((size_t)CTX_KT * hd + (size_t)CTX_KT * CTX_ROWS) * sizeof(float); }
+// DPL = feature slots per lane (head_dim / 32 rounded up to 1, 2 or 4): a template parameter so that absent
 // slots cost no issue slots.
 template <int DPL>
-__global__ void __launch_bounds__(32 * CTX_ROWS) attn_context_kernel(float *__restrict__ ctx, float *__restrict__ scores,
-                                                                      const float *__restrict__ vcache, int b, int l, int nh,
-                                                                      int nkv, int hd, int cap, int key_lo, int s, int own0,
-                                                                      int window, const int *__restrict__ pos_dev) {
+__global__ void __launch_bounds__(32 * CTX_WARPS) attn_context_kernel(float *__restrict__ ctx, float *__restrict__ scores,
+                                                                       const float *__restrict__ vcache, int b, int l, int nh,
+                                                                       int nkv, int hd, int cap, int key_lo, int s, int own0,
+                                                                       int window, const int *__restrict__ pos_dev) {
     attn_geometry(pos_dev, l, cap, window, key_lo, s, own0);
-    extern __shared__ float vtile[]; // [CTX_KT][hd]
+    extern __shared__ __align__(16) float ctx_smem[];
+    float *vtile = ctx_smem;                         // [CTX_KT][hd], flushed
+    float *wt = ctx_smem + (size_t)CTX_KT * hd;      // [CTX_KT][CTX_ROWS]: a key's values for the CTA's rows
     const int bh = blockIdx.y, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qi = blockIdx.x * CTX_ROWS + warp;
-    const bool active = qi < l;
-    float *row = scores + ((long long)bh * l + (active ? qi : 0)) * s;
-    int jlo = 0, jhi = own0 + qi;
-    if (jhi > s - 1) jhi = s - 1;
-    if (window > 0) { jlo = own0 + qi - window + 1; if (jlo < 0) jlo = 0; }
-    float den = 0.f;
-    if (active) {
-        // S14: the row maximum over the WHOLE row, as a total-order key (fold shape is free)
-        unsigned best = 0u;
-        for (int j = lane; j < s; j += 32) best = max(best, order_key(ftz_bits(row[j])));
+    const int q_first = blockIdx.x * CTX_ROWS, q0 = q_first + warp * CTX_RPW;
+    float *mine = wt + warp * CTX_RPW;               // this warp's four columns of wt
+    bool active[CTX_RPW];
+    float *row[CTX_RPW];
+    int jlo[CTX_RPW], jhi[CTX_RPW];
+    float den[CTX_RPW], fm[CTX_RPW];
+    bool all_active = true;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, off));
-        const float fm = ftz_bits(order_unkey(best));
-        // S15, S16 in parallel; S17 serial ascending over the visible keys
-        for (int j0 = jlo; j0 <= jhi; j0 += 32) {
+    for (int r = 0; r < CTX_RPW; r++) {
+        const int qi = q0 + r;
+        active[r] = qi < l;
+        all_active = all_active && active[r];
+        row[r] = scores + ((long long)bh * l + (active[r] ? qi : 0)) * s;
+        jlo[r] = 0;
+        jhi[r] = min(own0 + qi, s - 1);
+        if (window > 0) jlo[r] = max(own0 + qi - window + 1, 0);
+        if (!active[r]) { jlo[r] = 0; jhi[r] = -1; }
+        den[r] = 0.f;
+        fm[r] = 0.f;
+        if (active[r]) {
+            // S14: the row maximum over the WHOLE row, as a total-order key (fold shape is free)
+            unsigned best = 0u;
+            for (int j = lane; j < s; j += 32) best = max(best, order_key(ftz_bits(row[r][j])));
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, off));
+            fm[r] = ftz_bits(order_unkey(best));
+        }
+    }
+    // S15, S16 in parallel; S17 serial ascending over the visible keys of each row
+    if (window == 0 && all_active) {
+        // the four rows start at key 0: walk the tiles together, the exponentials of a key side by side in wt
+        for (int j0 = 0; j0 <= jhi[CTX_RPW - 1]; j0 += 32) {
             const int j = j0 + lane;
-            float e = 0.f;
-            if (j <= jhi) {
-                e = ftz_bits(p_expf(ftz_bits(__fsub_rn(ftz_bits(row[j]), fm))));
-                row[j] = e;
-            }
-            const int cnt = min(32, jhi - j0 + 1);
-            if (cnt == 32) { // every term is already flushed: add.rn.ftz is the seam's add-then-flush in one instruction
+            float e[CTX_RPW];
 #pragma unroll
-                for (int t = 0; t < 32; t++) den = add_flushed(den, __shfl_sync(0xFFFFFFFFu, e, t));
-            } else {
-                for (int t = 0; t < cnt; t++) den = add_flushed(den, __shfl_sync(0xFFFFFFFFu, e, t));
+            for (int r = 0; r < CTX_RPW; r++) {
+                e[r] = 0.f;
+                if (j <= jhi[r]) {
+                    e[r] = ftz_bits(p_expf(ftz_bits(__fsub_rn(ftz_bits(row[r][j]), fm[r]))));
+                    row[r][j] = e[r];
+                }
+            }
+            *reinterpret_cast<float4 *>(mine + lane * CTX_ROWS) = make_float4(e[0], e[1], e[2], e[CTX_RPW - 1]);
+            __syncwarp();
+            if (j0 + 31 <= jhi[0]) { // whole tile visible to all four rows (jhi ascends with the row)
+#pragma unroll
+                for (int t = 0; t < 32; t++) {
+                    const float4 e4 = *reinterpret_cast<const float4 *>(mine + t * CTX_ROWS);
+                    den[0] = add_flushed(den[0], e4.x);
+                    den[1] = add_flushed(den[1], e4.y);
+                    den[2] = add_flushed(den[2], e4.z);
+                    den[CTX_RPW - 1] = add_flushed(den[CTX_RPW - 1], e4.w);
+                }
+            } else { // the rows end inside the tile, each at its own key: one walk, a row steps while the key is its own
+                const int tmax = min(31, jhi[CTX_RPW - 1] - j0);
+#pragma unroll 4
+                for (int t = 0; t <= tmax; t++) {
+                    const float4 e4 = *reinterpret_cast<const float4 *>(mine + t * CTX_ROWS);
+                    const float ev[CTX_RPW] = {e4.x, e4.y, e4.z, e4.w};
+#pragma unroll
+                    for (int r = 0; r < CTX_RPW; r++)
+                        if (j0 + t <= jhi[r]) den[r] = add_flushed(den[r], ev[r]);
+                }
+            }
+            __syncwarp();
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < CTX_RPW; r++) {
+            if (!active[r]) continue;
+            for (int j0 = jlo[r]; j0 <= jhi[r]; j0 += 32) {
+                const int j = j0 + lane;
+                float e = 0.f;
+                if (j <= jhi[r]) {
+                    e = ftz_bits(p_expf(ftz_bits(__fsub_rn(ftz_bits(row[r][j]), fm[r]))));
+                    row[r][j] = e;
+                }
+                const int cnt = min(32, jhi[r] - j0 + 1);
+                // every term is already flushed: add.rn.ftz is the seam's add-then-flush in one instruction
+                for (int t = 0; t < cnt; t++) den[r] = add_flushed(den[r], __shfl_sync(0xFFFFFFFFu, e, t));
             }
         }
     }
     // S18 + S19 over value tiles shared by the CTA's rows
-    float acc[DPL];
+    float acc[CTX_RPW][DPL];
 #pragma unroll
-    for (int i = 0; i < DPL; i++) acc[i] = 0.f;
+    for (int r = 0; r < CTX_RPW; r++)
+#pragma unroll
+        for (int i = 0; i < DPL; i++) acc[r][i] = 0.f;
     const float *vbase = vcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
+    const bool vec = (hd % 4 == 0) && ((reinterpret_cast<uintptr_t>(vbase) & 15u) == 0);
     // keys any row of this CTA can see
-    const int q_first = blockIdx.x * CTX_ROWS, q_last = min(l - 1, q_first + CTX_ROWS - 1);
+    const int q_last = min(l - 1, q_first + CTX_ROWS - 1);
     int t_lo = 0, t_hi = min(s - 1, own0 + q_last);
     if (window > 0) { t_lo = own0 + q_first - window + 1; if (t_lo < 0) t_lo = 0; }
+    bool clean = true; // every step of this warp's rows so far was an admitted bare fma
+    int jmax = -1;
+#pragma unroll
+    for (int r = 0; r < CTX_RPW; r++) jmax = max(jmax, jhi[r]);
     for (int j0 = (t_lo / CTX_KT) * CTX_KT; j0 <= t_hi; j0 += CTX_KT) {
         __syncthreads();
-        for (int idx = threadIdx.x; idx < CTX_KT * hd; idx += 32 * CTX_ROWS) {
-            const int jj = idx / hd;
-            vtile[idx] = (j0 + jj < s) ? ftz_bits(vbase[(long long)(j0 + jj) * hd + idx % hd]) : 0.f;
-        }
-        __syncthreads();
-        if (!active) continue;
-        const int j = j0 + lane;
-        float wgt = 0.f;
-        if (j >= jlo && j <= jhi) {
-            wgt = ftz_bits(p_divf(ftz_bits(row[j]), den));
-            row[j] = wgt;
-        }
-        const int a = max(jlo, j0), z = min(jhi, j0 + CTX_KT - 1);
-        if (a == j0 && z == j0 + CTX_KT - 1 && hd == 32 * DPL) { // a whole tile, every slot live: unrolled
-#pragma unroll
-            for (int t = 0; t < CTX_KT; t++) {
-                const float wv = __shfl_sync(0xFFFFFFFFu, wgt, t);
-#pragma unroll
-                for (int i = 0; i < DPL; i++) acc[i] = step_flush(wv, vtile[t * hd + lane + 32 * i], acc[i]);
+        unsigned vkey = 0xFFFFFFFFu;
+        if (vec && j0 + CTX_KT <= s) { // the tile is one contiguous block of the cache
+            const float4 *src = reinterpret_cast<const float4 *>(vbase + (long long)j0 * hd);
+            float4 *dst = reinterpret_cast<float4 *>(vtile);
+            for (int idx = threadIdx.x; idx < CTX_KT * hd / 4; idx += 32 * CTX_WARPS) {
+                float4 v = src[idx];
+                v.x = ftz_bits(v.x); v.y = ftz_bits(v.y); v.z = ftz_bits(v.z); v.w = ftz_bits(v.w);
+                vkey = min(vkey, key_of4(v));
+                dst[idx] = v;
             }
         } else {
-            for (int jk = a; jk <= z; jk++) {
-                const float wv = __shfl_sync(0xFFFFFFFFu, wgt, jk - j0);
+            for (int idx = threadIdx.x; idx < CTX_KT * hd; idx += 32 * CTX_WARPS) {
+                const int jj = idx / hd;
+                const float v = (j0 + jj < s) ? ftz_bits(vbase[(long long)(j0 + jj) * hd + idx % hd]) : 0.f;
+                vkey = min(vkey, admit_key(v));
+                vtile[idx] = v;
+            }
+        }
+        const bool v_ok = __syncthreads_and(vkey >= ADMIT_MIN);
+        if (jmax < j0) continue; // no row of this warp sees the tile (uniform per warp)
+        const int j = j0 + lane;
+        float wgt[CTX_RPW];
+        unsigned wkey = 0xFFFFFFFFu;
+        bool full = hd == DPL * 32, heads = hd == DPL * 32; // heads: every live row's range starts at or before the tile
 #pragma unroll
-                for (int i = 0; i < DPL; i++) {
-                    const int d = lane + 32 * i;
-                    if (d < hd) acc[i] = step_flush(wv, vtile[(jk - j0) * hd + d], acc[i]);
+        for (int r = 0; r < CTX_RPW; r++) {
+            wgt[r] = 0.f;
+            if (j >= jlo[r] && j <= jhi[r]) {
+                wgt[r] = ftz_bits(p_divf(ftz_bits(row[r][j]), den[r]));
+                row[r][j] = wgt[r];
+            }
+            wkey = min(wkey, admit_key(wgt[r]));
+            full = full && jlo[r] <= j0 && jhi[r] >= j0 + CTX_KT - 1;
+            heads = heads && (jlo[r] <= j0 || jhi[r] < j0);
+        }
+        *reinterpret_cast<float4 *>(mine + lane * CTX_ROWS) = make_float4(wgt[0], wgt[1], wgt[2], wgt[CTX_RPW - 1]);
+        __syncwarp();
+        const bool w_ok = __all_sync(0xFFFFFFFFu, wkey >= ADMIT_MIN);
+        if (full) { // a whole tile for all four rows, every feature slot live: unrolled
+            const bool bare = clean && v_ok && w_ok;
+            clean = bare;
+#pragma unroll
+            for (int t = 0; t < CTX_KT; t++) {
+                const float4 w4 = *reinterpret_cast<const float4 *>(mine + t * CTX_ROWS);
+                const float w[CTX_RPW] = {w4.x, w4.y, w4.z, w4.w};
+                float v[DPL];
+                if (DPL == 4) {
+                    const float4 x = *reinterpret_cast<const float4 *>(vtile + t * hd + lane * 4);
+                    v[0] = x.x; v[1 % DPL] = x.y; v[2 % DPL] = x.z; v[3 % DPL] = x.w;
+                } else if (DPL == 2) {
+                    const float2 x = *reinterpret_cast<const float2 *>(vtile + t * hd + lane * 2);
+                    v[0] = x.x; v[1 % DPL] = x.y;
+                } else {
+                    v[0] = vtile[t * hd + lane];
+                }
+#pragma unroll
+                for (int r = 0; r < CTX_RPW; r++)
+#pragma unroll
+                    for (int i = 0; i < DPL; i++) acc[r][i] = bare ? step_bare(w[r], v[i], acc[r][i]) : step_flush(w[r], v[i], acc[r][i]);
+            }
+        } else if (heads) { // the rows end inside the tile, each at its own key (the diagonal tile of a causal prompt)
+            const bool bare = clean && v_ok && w_ok;
+            clean = bare;
+            const int tmax = min(CTX_KT - 1, jmax - j0);
+#pragma unroll 4
+            for (int t = 0; t <= tmax; t++) {
+                const float4 w4 = *reinterpret_cast<const float4 *>(mine + t * CTX_ROWS);
+                const float w[CTX_RPW] = {w4.x, w4.y, w4.z, w4.w};
+                float v[DPL];
+                if (DPL == 4) {
+                    const float4 x = *reinterpret_cast<const float4 *>(vtile + t * hd + lane * 4);
+                    v[0] = x.x; v[1 % DPL] = x.y; v[2 % DPL] = x.z; v[3 % DPL] = x.w;
+                } else if (DPL == 2) {
+                    const float2 x = *reinterpret_cast<const float2 *>(vtile + t * hd + lane * 2);
+                    v[0] = x.x; v[1 % DPL] = x.y;
+                } else {
+                    v[0] = vtile[t * hd + lane];
+                }
+#pragma unroll
+                for (int r = 0; r < CTX_RPW; r++) {
+                    if (j0 + t > jhi[r]) continue;
+#pragma unroll
+                    for (int i = 0; i < DPL; i++) acc[r][i] = bare ? step_bare(w[r], v[i], acc[r][i]) : step_flush(w[r], v[i], acc[r][i]);
+                }
+            }
+        } else {
+            clean = false;
+#pragma unroll
+            for (int r = 0; r < CTX_RPW; r++) {
+                const int a = max(jlo[r], j0), z = min(jhi[r], j0 + CTX_KT - 1);
+                for (int jk = a; jk <= z; jk++) {
+                    const float wv = mine[(jk - j0) * CTX_ROWS + r];
+#pragma unroll
+                    for (int i = 0; i < DPL; i++) {
+                        const int d = lane * DPL + i;
+                        if (d < hd) acc[r][i] = step_flush(wv, vtile[(jk - j0) * hd + d], acc[r][i]);
+                    }
                 }
             }
         }
     }
-    if (active) {
-        float *o = ctx + ((long long)bb * l + qi) * ((long long)nh * hd) + (long long)h * hd;
+#pragma unroll
+    for (int r = 0; r < CTX_RPW; r++) {
+        if (!active[r]) continue;
+        float *o = ctx + ((long long)bb * l + q0 + r) * ((long long)nh * hd) + (long long)h * hd;
 #pragma unroll
         for (int i = 0; i < DPL; i++) {
-            const int d = lane + 32 * i;
-            if (d < hd) o[d] = acc[i];
+            const int d = lane * DPL + i;
+            if (d < hd) o[d] = acc[r][i];
         }
     }
 }
