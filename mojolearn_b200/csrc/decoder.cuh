@@ -365,10 +365,30 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(float *__restrict__ sc
     const bool tile_masked = j0 > own0 + q_hi || (window > 0 && j0 + ATT_T - 1 < own0 + q0 - window + 1);
     if (tile_masked) {
         bool small = true;
-        for (int idx = tid; idx < ATT_T * hd; idx += 256) {
-            const int r = idx / hd, p = idx % hd;
-            if (q0 + r < l) small = small && ((__float_as_uint(qbase[(long long)(q0 + r) * qw + p]) >> 23) & 0xFFu) < 167u;
-            if (j0 + r < s) small = small && ((__float_as_uint(kbase[(long long)(j0 + r) * hd + p]) >> 23) & 0xFFu) < 167u;
+        const int warp = tid >> 5, lane = tid & 31;
+        const bool vec = (hd % 4 == 0) && (((reinterpret_cast<uintptr_t>(qbase) | reinterpret_cast<uintptr_t>(kbase)) & 15u) == 0);
+        for (int r = warp; r < ATT_T; r += 8) { // a warp per row, lanes along the row: no division by head_dim
+            const float *qr = qbase + (long long)(q0 + r) * qw, *kr = kbase + (long long)(j0 + r) * hd;
+            const bool qlive = q0 + r < l, klive = j0 + r < s;
+            if (vec) {
+                for (int p = lane * 4; p < hd; p += 128) {
+                    if (qlive) {
+                        const float4 v = *reinterpret_cast<const float4 *>(qr + p);
+                        small = small && ((__float_as_uint(v.x) >> 23) & 0xFFu) < 167u && ((__float_as_uint(v.y) >> 23) & 0xFFu) < 167u &&
+                                ((__float_as_uint(v.z) >> 23) & 0xFFu) < 167u && ((__float_as_uint(v.w) >> 23) & 0xFFu) < 167u;
+                    }
+                    if (klive) {
+                        const float4 v = *reinterpret_cast<const float4 *>(kr + p);
+                        small = small && ((__float_as_uint(v.x) >> 23) & 0xFFu) < 167u && ((__float_as_uint(v.y) >> 23) & 0xFFu) < 167u &&
+                                ((__float_as_uint(v.z) >> 23) & 0xFFu) < 167u && ((__float_as_uint(v.w) >> 23) & 0xFFu) < 167u;
+                    }
+                }
+            } else {
+                for (int p = lane; p < hd; p += 32) {
+                    if (qlive) small = small && ((__float_as_uint(qr[p]) >> 23) & 0xFFu) < 167u;
+                    if (klive) small = small && ((__float_as_uint(kr[p]) >> 23) & 0xFFu) < 167u;
+                }
+            }
         }
         if (__syncthreads_and(small)) {
 #pragma unroll
@@ -739,52 +759,47 @@ __global__ void __launch_bounds__(32 * CTX_WARPS) attn_context_kernel(float *__r
         *reinterpret_cast<float4 *>(mine + lane * CTX_ROWS) = make_float4(wgt[0], wgt[1], wgt[2], wgt[CTX_RPW - 1]);
         __syncwarp();
         const bool w_ok = __all_sync(0xFFFFFFFFu, wkey >= ADMIT_MIN);
+        // one key of the tile for the warp's four rows; `bare_c` and `ragged` are constants at every call site
+        auto key_step = [&](int t, const bool bare_c, const bool ragged) {
+            const float4 w4 = *reinterpret_cast<const float4 *>(mine + t * CTX_ROWS);
+            const float w[CTX_RPW] = {w4.x, w4.y, w4.z, w4.w};
+            float v[DPL];
+            if (DPL == 4) {
+                const float4 x = *reinterpret_cast<const float4 *>(vtile + t * hd + lane * 4);
+                v[0] = x.x; v[1 % DPL] = x.y; v[2 % DPL] = x.z; v[3 % DPL] = x.w;
+            } else if (DPL == 2) {
+                const float2 x = *reinterpret_cast<const float2 *>(vtile + t * hd + lane * 2);
+                v[0] = x.x; v[1 % DPL] = x.y;
+            } else {
+                v[0] = vtile[t * hd + lane];
+            }
+#pragma unroll
+            for (int r = 0; r < CTX_RPW; r++) {
+                if (ragged && j0 + t > jhi[r]) continue;
+#pragma unroll
+                for (int i = 0; i < DPL; i++) acc[r][i] = bare_c ? step_bare(w[r], v[i], acc[r][i]) : step_flush(w[r], v[i], acc[r][i]);
+            }
+        };
         if (full) { // a whole tile for all four rows, every feature slot live: unrolled
             const bool bare = clean && v_ok && w_ok;
             clean = bare;
+            if (bare) {
 #pragma unroll
-            for (int t = 0; t < CTX_KT; t++) {
-                const float4 w4 = *reinterpret_cast<const float4 *>(mine + t * CTX_ROWS);
-                const float w[CTX_RPW] = {w4.x, w4.y, w4.z, w4.w};
-                float v[DPL];
-                if (DPL == 4) {
-                    const float4 x = *reinterpret_cast<const float4 *>(vtile + t * hd + lane * 4);
-                    v[0] = x.x; v[1 % DPL] = x.y; v[2 % DPL] = x.z; v[3 % DPL] = x.w;
-                } else if (DPL == 2) {
-                    const float2 x = *reinterpret_cast<const float2 *>(vtile + t * hd + lane * 2);
-                    v[0] = x.x; v[1 % DPL] = x.y;
-                } else {
-                    v[0] = vtile[t * hd + lane];
-                }
-#pragma unroll
-                for (int r = 0; r < CTX_RPW; r++)
-#pragma unroll
-                    for (int i = 0; i < DPL; i++) acc[r][i] = bare ? step_bare(w[r], v[i], acc[r][i]) : step_flush(w[r], v[i], acc[r][i]);
+                for (int t = 0; t < CTX_KT; t++) key_step(t, true, false);
+            } else {
+#pragma unroll 8
+                for (int t = 0; t < CTX_KT; t++) key_step(t, false, false);
             }
         } else if (heads) { // the rows end inside the tile, each at its own key (the diagonal tile of a causal prompt)
             const bool bare = clean && v_ok && w_ok;
             clean = bare;
             const int tmax = min(CTX_KT - 1, jmax - j0);
+            if (bare) {
 #pragma unroll 4
-            for (int t = 0; t <= tmax; t++) {
-                const float4 w4 = *reinterpret_cast<const float4 *>(mine + t * CTX_ROWS);
-                const float w[CTX_RPW] = {w4.x, w4.y, w4.z, w4.w};
-                float v[DPL];
-                if (DPL == 4) {
-                    const float4 x = *reinterpret_cast<const float4 *>(vtile + t * hd + lane * 4);
-                    v[0] = x.x; v[1 % DPL] = x.y; v[2 % DPL] = x.z; v[3 % DPL] = x.w;
-                } else if (DPL == 2) {
-                    const float2 x = *reinterpret_cast<const float2 *>(vtile + t * hd + lane * 2);
-                    v[0] = x.x; v[1 % DPL] = x.y;
-                } else {
-                    v[0] = vtile[t * hd + lane];
-                }
-#pragma unroll
-                for (int r = 0; r < CTX_RPW; r++) {
-                    if (j0 + t > jhi[r]) continue;
-#pragma unroll
-                    for (int i = 0; i < DPL; i++) acc[r][i] = bare ? step_bare(w[r], v[i], acc[r][i]) : step_flush(w[r], v[i], acc[r][i]);
-                }
+                for (int t = 0; t <= tmax; t++) key_step(t, true, true);
+            } else {
+#pragma unroll 4
+                for (int t = 0; t <= tmax; t++) key_step(t, false, true);
             }
         } else {
             clean = false;
