@@ -267,6 +267,14 @@ void launch_skinny_packed_wk(const SkinnyPackedArgs &g, float *at, unsigned char
 
 // rows below which packing the operands costs more than the bulk-copy pipeline returns
 constexpr long long PACKED_MIN_EXTENT = 256;
+// The packed plan replaces the 128 x 128 tile plan from 256 rows and columns up, and any tile plan when the rows
+// are one or two (nearly) full rows of 128 x 128 tiles over a wide, deep product (128 x 11008 x 4096: 305 us
+// against 370 us for the 32 x 128 tiles).
+inline bool packed_candidate(int tile_kind, long long m, long long n, long long k) {
+    if (tile_kind == PLAN_T128 && m >= PACKED_MIN_EXTENT && n >= PACKED_MIN_EXTENT) return true;
+    const long long padded = (m + PK_TILE - 1) / PK_TILE * PK_TILE;
+    return tile_kind != PLAN_FLAT && m >= 117 && m <= 256 && padded * 10 <= m * 11 && n >= 2048 && k >= 1024;
+}
 size_t packed_need(long long m, long long n, long long k, int groups) {
     return round256(groups > 1 ? (size_t)groups * m * n * 4 : 0) + pk_workspace_bytes(m, n, k);
 }
@@ -274,11 +282,34 @@ size_t packed_need(long long m, long long n, long long k, int groups) {
 // The packed plan's leaf split: with at least two CTAs per slot of the device the tiles alone keep every SM busy
 // (a CTA left alone on an SM in the last wave runs at nearly twice the speed, so a partial wave costs little)
 // and a split would only add group nodes; below that, the tile plan's split stands.
-Plan packed_split(const Plan &tile_plan, long long m, long long n, int sms) {
+Plan packed_split(const Plan &tile_plan, long long m, long long n, long long k, int sms) {
     const long long tiles = ((m + PK_TILE - 1) / PK_TILE) * ((n + PK_TILE - 1) / PK_TILE);
     Plan p = tile_plan;
     p.kind = PLAN_PACKED;
-    if (tiles >= 4ll * sms) { p.groups = 1; p.group_leaves = tile_plan.group_leaves * tile_plan.groups; }
+    const int leaves = (int)leaf_count(k) > 0 ? (int)leaf_count(k) : 1;
+    if (tiles >= 4ll * sms) { p.groups = 1; p.group_leaves = leaves; return p; }
+    // Few tiles: split the leaves so that the CTA slots (two per SM) fill in whole waves. Modelled time in
+    // microseconds: waves x (leaves per CTA at 21.8 us per 128-step leaf -- a 128 x 128 tile at the kernel's
+    // measured rate -- plus 1 us per CTA), plus the second launch and the L2-resident node traffic of the fold.
+    const long long slots = 2ll * sms;
+    const double leaf_us = 21.8 * (double)leaf_size(k) / 128.0;
+    const int max_s = pow2_floor(leaves) * ((leaves & (leaves - 1)) ? 2 : 1);
+    int min_s = 1;
+    while ((leaves + min_s - 1) / min_s > MAX_GROUPS) min_s *= 2;
+    int best = max_s;
+    double best_t = 1e300;
+    for (int sl = max_s; sl >= min_s; sl /= 2) {
+        const int groups = (leaves + sl - 1) / sl;
+        // a last wave that fills at most half the slots leaves its CTAs alone on their SMs, at nearly twice the speed
+        const long long ctas = tiles * groups, whole = ctas / slots, rest = ctas % slots;
+        const double waves = (double)whole + (rest == 0 ? 0.0 : (2 * rest <= slots ? 0.55 : 1.0));
+        double t = waves * (sl * leaf_us + 1.0);
+        if (groups > 1) t += 3.0 + (double)groups * m * n * 8.0 / 7.5e6;
+        if (t < best_t) { best_t = t; best = sl; }
+    }
+    p.group_leaves = best;
+    p.groups = (leaves + best - 1) / best;
+    if (p.groups <= 1) p.group_leaves = leaves;
     return p;
 }
 
@@ -368,8 +399,8 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     Plan plan;
     if (plan_kind == PLAN_AUTO) {
         plan = choose_plan(m, n, k, sm_count(dev));
-        if (plan.kind == PLAN_T128 && m >= PACKED_MIN_EXTENT && n >= PACKED_MIN_EXTENT) {
-            const Plan packed = packed_split(plan, m, n, sm_count(dev));
+        if (packed_candidate(plan.kind, m, n, k)) {
+            const Plan packed = packed_split(plan, m, n, k, sm_count(dev));
             if (ws && aligned(ws, 256) && (size_t)ws_bytes >= packed_need(m, n, k, packed.groups)) plan = packed;
         }
         const bool al16 = aligned(b, 16) && aligned(a, 16);
@@ -533,8 +564,8 @@ int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = -1; }
     Plan p = choose_plan(m, n, k, sm_count(dev));
     int groups = p.groups;
-    if (p.kind == PLAN_T128 && m >= PACKED_MIN_EXTENT && n >= PACKED_MIN_EXTENT)
-        return (int64_t)packed_need(m, n, k, packed_split(p, m, n, sm_count(dev)).groups);
+    if (packed_candidate(p.kind, m, n, k))
+        return (int64_t)packed_need(m, n, k, packed_split(p, m, n, k, sm_count(dev)).groups);
     if (skinny_plan_fits(m, n, k, OP_NT)) { // the plan an NT product with aligned operands takes instead
         for (int lowbit = 0; lowbit < 2; lowbit++) {
             const Plan q = choose_skinny(m, n, k, sm_count(dev), lowbit != 0);
