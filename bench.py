@@ -259,9 +259,8 @@ def main():
         peaks["packed" if packed else "scalar"] = fl / (e0.elapsed_time(e1) * 1e-3) / 1e12
     fp32_peak = max(peaks.values())
 
-    # the dominant kernel: each product's main kernel (gemm_packed_kernel on four of the five shapes, the 128x128
-    # tile kernel on 128x11008x4096), timed by the library's own event pairs: operand packing and the group fold
-    # are outside these pairs and inside `value`
+    # the dominant kernel: each product's main kernel (gemm_packed_kernel on all five shapes), timed by the
+    # library's own event pairs: operand packing and the group fold are outside these pairs and inside `value`
     tile_flops = sweep_flops(SWEEP) * (kernel_calls.value / float(len(SWEEP)))  # the pairs recorded (the library keeps 4096)
     tile_ms = float(kernel_ms.value)
     tile_tflops = tile_flops / (tile_ms * 1e-3) / 1e12 if tile_ms > 0 else 0.0
