@@ -485,7 +485,7 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     timing_end(tslot, st);
     if (plan.groups > 1) {
         const long long cells = (long long)m * n;
-        fold_groups_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(g.ws, c, cells, plan.groups);
+        launch_fold_groups(g.ws, c, cells, plan.groups, st);
         g_launches++;
     }
     CUDA_TRY(cudaGetLastError());
@@ -640,7 +640,7 @@ int64_t b200i_gemm_packed_w(int64_t device, void *stream, float *c, const float 
     g_launches += 2;
     if (plan.groups > 1) {
         const long long cells = (long long)m * n;
-        fold_groups_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(nodes, c, cells, plan.groups);
+        launch_fold_groups(nodes, c, cells, plan.groups, st);
         g_launches++;
     }
     CUDA_TRY(cudaGetLastError());

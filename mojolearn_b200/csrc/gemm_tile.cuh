@@ -415,21 +415,63 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
 
 // Folds the group nodes of a split product: node g of cell c is ws[g][c]; the
 // nodes are the level-log2(S) row of the contract's tree, so the same
-// adjacent-pair fold with an odd tail carried finishes it.
+// adjacent-pair fold with an odd tail carried finishes it. The fold is streamed
+// through the binary-counter stack the product kernels use (a node is pushed,
+// merging while the counter's low bits are set; the last node drains the
+// stack): the stack lives in registers, VEC consecutive cells per thread.
 constexpr int MAX_GROUPS = 64;
-__global__ void fold_groups_kernel(const float *__restrict__ ws, float *__restrict__ c, long long cells, int groups) {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+constexpr int GROUP_LEVELS = 6; // 2^6 = MAX_GROUPS
+template <int VEC>
+__global__ void __launch_bounds__(256) fold_groups_kernel(const float *__restrict__ ws, float *__restrict__ c, long long cells,
+                                                          int groups) {
+    const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (idx >= cells) return;
-    float v[MAX_GROUPS];
-    for (int gi = 0; gi < groups; gi++) v[gi] = ws[(size_t)gi * (size_t)cells + idx];
-    int width = groups;
-    while (width > 1) {
-        const int pairs = width / 2;
-        for (int q = 0; q < pairs; q++) v[q] = fold_add(v[2 * q], v[2 * q + 1]);
-        if (width & 1) v[pairs] = v[width - 1];
-        width = pairs + (width & 1);
+    float stack[GROUP_LEVELS][VEC];
+    float v[VEC];
+    auto load = [&](int gi) {
+        const float *src = ws + (size_t)gi * (size_t)cells + idx;
+        if (VEC == 4) {
+            const float4 x = __ldcg(reinterpret_cast<const float4 *>(src));
+            v[0] = x.x; v[1 % VEC] = x.y; v[2 % VEC] = x.z; v[3 % VEC] = x.w;
+        } else {
+            v[0] = __ldcg(src);
+        }
+    };
+    for (int gi = 0; gi + 1 < groups; gi++) {
+        load(gi);
+        bool placed = false;
+#pragma unroll
+        for (int lvl = 0; lvl < GROUP_LEVELS; lvl++) {
+            if (placed) continue;
+            if ((gi >> lvl) & 1) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) v[e] = fold_add(stack[lvl][e], v[e]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) stack[lvl][e] = v[e];
+                placed = true;
+            }
+        }
     }
-    c[idx] = nan_canon(ftz_hw(v[0]));
+    const int last = groups - 1;
+    load(last);
+#pragma unroll
+    for (int lvl = 0; lvl < GROUP_LEVELS; lvl++)
+        if ((last >> lvl) & 1) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) v[e] = fold_add(stack[lvl][e], v[e]);
+        }
+    if (VEC == 4) {
+        *reinterpret_cast<float4 *>(c + idx) = make_float4(nan_canon(ftz_hw(v[0])), nan_canon(ftz_hw(v[1 % VEC])),
+                                                           nan_canon(ftz_hw(v[2 % VEC])), nan_canon(ftz_hw(v[3 % VEC])));
+    } else {
+        c[idx] = nan_canon(ftz_hw(v[0]));
+    }
+}
+inline void launch_fold_groups(const float *ws, float *c, long long cells, int groups, cudaStream_t st) {
+    const bool vec = cells % 4 == 0 && ((reinterpret_cast<uintptr_t>(ws) | reinterpret_cast<uintptr_t>(c)) & 15u) == 0;
+    if (vec) fold_groups_kernel<4><<<(unsigned)((cells / 4 + 255) / 256), 256, 0, st>>>(ws, c, cells, groups);
+    else fold_groups_kernel<1><<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(ws, c, cells, groups);
 }
 
 // One thread per cell, whole product serial: the on-device restatement of the
