@@ -193,3 +193,17 @@ def test_hf_causal_lm_infer_cell(kind):
     assert decoder_ref.batch_cell_hash(logits) == TABLE["cells"]["hf-causal-lm/%s" % kind]["batch"]
     assert lm.forward(ids[1:2]).tobytes() == logits[1:2].tobytes()
     assert lm.forward(ids[:, :7]).tobytes() == np.ascontiguousarray(logits[:, :7]).tobytes()
+
+
+def test_masked_score_is_the_fill_when_operands_are_small():
+    """The prefill score kernel writes -FLT_MAX for a tile no query can see without forming its dot products when
+    every operand word is finite and below 2^40: a dot of up to 128 such products stays under 2^88, half an ulp of
+    FLT_MAX is 2^103, so score + (-FLT_MAX) rounds back to -FLT_MAX. Checked here at the bound and just above it."""
+    fill = np.frombuffer(np.uint32(0xFF7FFFFF).tobytes(), dtype=np.float32)[0]
+    for mag in (0.0, 1.0, 2.0 ** 87, 2.0 ** 88, 2.0 ** 102):
+        for sign in (1.0, -1.0):
+            assert np.float32(np.float32(sign * mag) + fill) == fill
+    assert np.float32(np.float32(2.0 ** 104) + fill) != fill  # a score this large does move the sum: the kernel computes such tiles
+    # the largest dot the shortcut admits: 128 products of two words just below 2^40
+    x = np.float32(np.nextafter(np.float32(2.0 ** 40), np.float32(0)))
+    assert float(x) * float(x) * 128 < 2.0 ** 88
