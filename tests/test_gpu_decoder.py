@@ -139,6 +139,24 @@ def test_block_subnormal_forcing_inputs():
     assert blk.forward(x).tobytes() == want.tobytes()
 
 
+def test_prefill_attention_extreme_operands():
+    """A prompt longer than two score tiles with queries and keys near 2^48 (a tile no query can see must then form
+    its dot products: they are large enough to move the masked sum) and values near 2^-100 (the value chain must
+    take the flushed step), and the same block with ordinary weights for the tiles written without dot products."""
+    w, dims = decoder_ref.transformer_lane_weights()
+    cfg = oracle.block_cfg(32, 2, 1, 16, 64)
+    x = decoder_ref.seq(np.asarray(decoder_ref.lcg_floats(2 * 130 * 32, 5, -1.0, 1.0), dtype=np.float32), 2, 130, 32)
+    for qk, v in ((np.float32(2.0 ** 48), np.float32(2.0 ** -100)), (np.float32(1.0), np.float32(1.0)),
+                  (np.float32(2.0 ** 54), np.float32(1.0))):
+        w2 = dict(w)
+        w2["q_proj.weight"] = w["q_proj.weight"] * qk
+        w2["k_proj.weight"] = w["k_proj.weight"] * qk
+        w2["v_proj.weight"] = w["v_proj.weight"] * v
+        want = oracle.block_forward(cfg, decoder_ref.block_slots(w2), x)
+        got = TransformerBlock(w2, n_heads=2, n_kv_heads=1).forward(x)
+        assert got.tobytes() == want.tobytes(), (float(qk), float(v))
+
+
 def test_config4_shape_reduced_length():
     """The GPT-2-small style benchmark architecture (12 layers would only repeat the block: 2 here), d_model 768, 12 heads,
     MLP 3072 GELU, LayerNorm, learned positions, vocab 50304, batch 8: prompt 24 tokens then 4 greedy steps."""
