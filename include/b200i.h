@@ -128,18 +128,32 @@ int64_t b200i_decode_plan_fits(int64_t m, int64_t n, int64_t k, int64_t op, int6
  * it cudaMalloc. It has no counterpart in the reference. Same arithmetic and same
  * bits as b200i_gemm_f32; the difference is where the split plan's scratch (the
  * leaf-group nodes) lives: in a fixed 16 MiB array inside the library image, which
- * every GPU that loads the library holds until the process exits. The call makes no
- * cudaMalloc, cudaFree or other allocating call. A shape whose plan needs more than
- * 16 MiB of scratch is refused with a message naming both sizes (use b200i_gemm_f32
- * and caller scratch for it). The first call on each device looks up the array's
- * device address (a synchronous runtime query), so make that first call before any
- * stream capture begins. All calls on a device share the one array: nothing in it has
- * to start at zero (every node a launch reads was written by that launch), but two
- * calls that overlap on the GPU, on different streams or threads, race on it. */
+ * every GPU that loads the library holds until the process exits. The call itself
+ * makes no cudaMalloc, cudaFree or other allocating call, and records no timing
+ * events. The 16 MiB are the limit of the scratch, not of the shapes: when the
+ * leaf split the cost model prefers would need more, the call runs the same tiles
+ * with the leaves in fewer, larger groups (down to no split, which needs no
+ * scratch) -- the same bits from fewer CTAs, so a very deep product with few
+ * output tiles runs slower here than through b200i_gemm_f32 with caller scratch.
+ * b200i_noalloc_scratch_bytes says how much of the array a shape will use; a need
+ * above 16 MiB would be refused with a message naming both sizes. The first call
+ * on each device looks up the array's device address (a synchronous runtime
+ * query), so make that first call before any stream capture begins. What the CUDA
+ * driver does on the first launch of a kernel is outside this library: with lazy
+ * module loading it may load code, and the first use of a tile shape sets a
+ * function attribute. A caller entering a no-allocation region should first run
+ * one product of each kind it will need (one split, one unsplit; small, medium and
+ * large outputs pick different tile shapes), or set CUDA_MODULE_LOADING=EAGER.
+ * All calls on a device share the one array: nothing in it has to start at zero
+ * (every node a launch reads was written by that launch), but two calls that
+ * overlap on the GPU, on different streams or threads, race on it. */
 int64_t b200i_gemm_f32_noalloc(int64_t device, void *stream, float *c, const float *a, const float *b, int64_t m, int64_t n,
                                int64_t k, int64_t op, char *err, int64_t err_cap);
+int64_t b200i_noalloc_scratch_bytes(int64_t m, int64_t n, int64_t k);
 
-/* Scratch bytes the product needs for this shape on the current device. */
+/* Scratch bytes the product needs for this shape. The answer depends on the SM count of the
+ * device that is CURRENT when this is called: call it with the device current that the product
+ * will later be given. */
 int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k);
 
 /* --- conversions, device pointers ----------------------------------------------------------
@@ -257,12 +271,22 @@ int64_t b200i_advance_position(int64_t device, void *stream, int32_t *position, 
 int64_t b200i_argmax(int64_t device, void *stream, int32_t *out, const float *logits, int64_t rows, int64_t vocab, char *err,
                      int64_t err_cap);
 
-/* Status word of the decode plan's bounded waits on `device` (synchronises the
- * device): 0 = no wait ever ran out; 1 / 2 = the producer / a consumer gave up
- * waiting on a stage; -1 = the word could not be read. A nonzero word is cleared
- * by the read. No reference counterpart:
- * the reference has no device-side wait. */
+/* Status word of the bounded device-side waits on `device` (synchronises the
+ * device): 0 = no wait ever ran out; 1 / 2 = the decode plan's producer / a consumer
+ * gave up waiting on a stage, 3 = the decode attention's value ring, 4 / 5 = the
+ * packed plan's ring, 6 / 7 = the prepacked skinny plan's ring, 8 = a wait for a
+ * peer GPU's arrival flag; -1 = the word could not be read. A nonzero word is
+ * cleared by the read. A kernel whose wait ran out skips its stores, so its output
+ * is incomplete. The b200i_host_* calls read the word after their final
+ * synchronise and return status 1 with a message, like any other error (the
+ * reference's status + message buffer, adapters/native/c_api.mojo:64-72). The
+ * device-pointer calls are asynchronous and cannot: their caller reads this word
+ * when it next synchronises (mojolearn_b200.torch_ops.check_status, CausalLM.generate
+ * and the decode sessions do). The reference has no device-side wait.
+ * b200i_debug_set_status writes the word from the host, for tests of that reporting
+ * path: no kernel is ever made to time out to produce a nonzero word. */
 int64_t b200i_decode_status(int64_t device);
+int64_t b200i_debug_set_status(int64_t device, int64_t value);
 
 /* Roofline probe: `blocks` CTAs of 256 threads, each thread 16 independent
  * chains of `iters` bare fused multiply-adds (scalar, or fma.rn.f32x2 pairs when

@@ -67,6 +67,8 @@ SIGNATURES = {
     "b200i_host_dequantize_int8": [I64, VP, VP, VP, I64, I64, VP, I64],
     "b200i_host_gemm_int8": [I64, VP, VP, VP, VP, VP, I64, I64, I64, VP, I64],
     "b200i_decode_status": [I64],
+    "b200i_debug_set_status": [I64, I64],
+    "b200i_noalloc_scratch_bytes": [I64, I64, I64],
     "b200i_norm": [I64, VP, VP, VP, VP, VP, I64, I64, F64, I64, VP, I64],
     "b200i_add_norm": [I64, VP, VP, VP, VP, VP, VP, VP, I64, I64, F64, I64, VP, I64],
     "b200i_qkv_rope_cache": [I64, VP, VP, VP, VP, VP, VP, VP, I64, VP, VP, I64, I64, I64, I64, I64, I64, I64, VP, VP, I64],

@@ -45,15 +45,16 @@ void clear(char *err, int64_t cap) {
         if (e_ != cudaSuccess) return fail(err, err_cap, "b200i: %s failed: %s", #expr, cudaGetErrorString(e_)); \
     } while (0)
 
+constexpr int MAX_DEVICES = 64;
 struct DeviceInfo {
     int sms = 148;
     bool known = false;
 };
-DeviceInfo g_info[64];
+DeviceInfo g_info[MAX_DEVICES];
 std::mutex g_mu;
 
 int sm_count(int device) {
-    if (device < 0 || device >= 64) return 148;
+    if (device < 0 || device >= MAX_DEVICES) return 148;
     std::lock_guard<std::mutex> lock(g_mu);
     if (!g_info[device].known) {
         int v = 0;
@@ -71,8 +72,20 @@ int select_device(int64_t device, char *err, int64_t err_cap, int *out) {
     } else {
         CUDA_TRY(cudaGetDevice(&dev));
     }
+    if (dev < 0 || dev >= MAX_DEVICES) return fail(err, err_cap, "b200i: device %d is outside the %d devices this library tracks", dev, MAX_DEVICES);
     *out = dev;
     return 0;
+}
+
+// The status word of the bounded device-side waits, read and cleared. Every host-pointer entry calls this after its
+// final synchronise, so a wait that ran out can never return as a silent success; device-pointer callers read it
+// through b200i_decode_status when they next synchronise.
+int64_t check_wait_status(char *err, int64_t err_cap, const char *who) {
+    int v = 0, zero = 0;
+    CUDA_TRY(cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)));
+    if (v == 0) return 0;
+    CUDA_TRY(cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int)));
+    return fail(err, err_cap, "%s: a bounded device-side wait ran out (status %d); the output is incomplete", who, v);
 }
 
 // ---- plans -----------------------------------------------------------------------------
@@ -196,7 +209,9 @@ struct KernelTiming {
 KernelTiming g_timing;
 std::mutex g_timing_mu;
 constexpr int TIMING_MAX_PAIRS = 4096;
+thread_local bool t_no_timing = false; // set by the allocation-free entry: creating an event may allocate
 int timing_begin(cudaStream_t st) {
+    if (t_no_timing) return -1;
     std::lock_guard<std::mutex> lock(g_timing_mu);
     if (!g_timing.on || g_timing.used >= TIMING_MAX_PAIRS) return -1;
     const int slot = g_timing.used++;
@@ -239,7 +254,7 @@ size_t skp_call_bytes(long long m, long long n, long long k, int groups) {
 
 template <int WK, int BM>
 void launch_skinny_packed_cfg(const SkinnyPackedArgs &g, cudaStream_t st) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
     constexpr int smem = skp_smem_bytes(WK, BM);
@@ -321,7 +336,7 @@ void launch_pack(const PackArgs &a, cudaStream_t st) {
 
 // Packs both operands into `scratch` (panels, then flags) and runs the packed kernel.
 void packed_configure() {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
@@ -360,7 +375,7 @@ int launch_packed(const GemmArgs &g, int groups, unsigned char *scratch, cudaStr
 template <int BM, int BN, int RM, int RN, int MINB>
 void launch_tile(GemmArgs &g, int groups, cudaStream_t st) {
     using S = TileShape<BM, BN, RM, RN>;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
@@ -556,6 +571,13 @@ int64_t b200i_decode_status(int64_t device) {
     if (cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return -1; }
     if (v != 0 && cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return -1; }
     return v;
+}
+
+int64_t b200i_debug_set_status(int64_t device, int64_t value) {
+    if (device >= 0 && cudaSetDevice((int)device) != cudaSuccess) { cudaGetLastError(); return -1; }
+    const int v = (int)value;
+    if (cudaMemcpyToSymbol(g_decode_status, &v, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return -1; }
+    return 0;
 }
 
 int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k) {
@@ -792,32 +814,63 @@ int64_t b200i_ffma_probe(int64_t device, void *stream, float *scratch, int64_t b
 // that every GPU loading the library carries until the process exits.
 constexpr size_t STATIC_SCRATCH_BYTES = 16u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
-static void *g_static_scratch_ptr[64]; // per device: the array's DEVICE address (the symbol itself is only a host-side stand-in)
+static void *g_static_scratch_ptr[MAX_DEVICES]; // per device: the array's DEVICE address (the symbol itself is only a host-side stand-in)
+static std::mutex g_static_scratch_mu;
+
+// The plan the allocation-free entry runs: the tile plan the cost model prefers when its leaf-group nodes fit the
+// built-in scratch, else the same tiles with the leaves split into fewer, larger groups (powers of two, so every
+// group is still a subtree of the contract's fold), down to no split at all, which needs no scratch. The bits do
+// not depend on the split; only the number of CTAs does.
+static Plan noalloc_plan(int64_t m, int64_t n, int64_t k, int sms) {
+    Plan plan = choose_plan(m, n, k, sms);
+    const int leaves = (int)leaf_count(k) > 0 ? (int)leaf_count(k) : 1;
+    while (plan.groups > 1 && (int64_t)plan.groups * m * n * 4 > (int64_t)STATIC_SCRATCH_BYTES) {
+        plan.group_leaves *= 2;
+        plan.groups = (leaves + plan.group_leaves - 1) / plan.group_leaves;
+    }
+    if (plan.groups <= 1) { plan.groups = 1; plan.group_leaves = leaves; }
+    return plan;
+}
+
+int64_t b200i_noalloc_scratch_bytes(int64_t m, int64_t n, int64_t k) {
+    if (m <= 0 || n <= 0 || k <= 0) return 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = -1; }
+    const Plan plan = noalloc_plan(m, n, k, sm_count(dev));
+    return plan.groups > 1 ? (int64_t)plan.groups * m * n * 4 : 0;
+}
 
 int64_t b200i_gemm_f32_noalloc(int64_t device, void *stream, float *c, const float *a, const float *b, int64_t m, int64_t n,
                                int64_t k, int64_t op, char *err, int64_t err_cap) {
     clear(err, err_cap);
     int dev;
     if (select_device(device, err, err_cap, &dev)) return 1;
-    if (dev < 0 || dev >= 64) return fail(err, err_cap, "identical gemm: device %d out of range", dev);
-    if (!g_static_scratch_ptr[dev]) {
-        // once per device, with that device current: ask the runtime where the array lives on it
-        void *p = nullptr;
-        CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
-        g_static_scratch_ptr[dev] = p;
+    void *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+        if (!g_static_scratch_ptr[dev]) {
+            // once per device, with that device current: ask the runtime where the array lives on it
+            void *p = nullptr;
+            CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+            g_static_scratch_ptr[dev] = p;
+        }
+        scratch = g_static_scratch_ptr[dev];
     }
     if (m <= 0 || n <= 0 || k <= 0)
         return fail(err, err_cap, "identical gemm: m, n and k must be positive (got m=%lld n=%lld k=%lld)", (long long)m,
                     (long long)n, (long long)k);
-    const Plan plan = choose_plan(m, n, k, sm_count(dev));
+    const Plan plan = noalloc_plan(m, n, k, sm_count(dev));
     const int64_t need = plan.groups > 1 ? (int64_t)plan.groups * m * n * 4 : 0;
-    if (need > (int64_t)STATIC_SCRATCH_BYTES)
+    if (need > (int64_t)STATIC_SCRATCH_BYTES) // cannot happen while an unsplit plan needs no scratch; kept as the guard of that assumption
         return fail(err, err_cap,
                     "identical gemm: this shape needs %lld bytes of scratch and the built-in scratch holds %lld; "
                     "call b200i_gemm_f32 with scratch of b200i_workspace_bytes(m, n, k) bytes instead",
                     (long long)need, (long long)STATIC_SCRATCH_BYTES);
-    return launch_product(dev, static_cast<cudaStream_t>(stream), c, a, b, nullptr, W_F32, m, n, k, (int)op, plan.kind,
-                          plan.groups > 1 ? plan.group_leaves : 0, g_static_scratch_ptr[dev], (int64_t)STATIC_SCRATCH_BYTES, err, err_cap);
+    t_no_timing = true; // the benchmark's event pairs are created on demand, which may allocate
+    const int64_t rc = launch_product(dev, static_cast<cudaStream_t>(stream), c, a, b, nullptr, W_F32, m, n, k, (int)op, plan.kind,
+                                      plan.groups > 1 ? plan.group_leaves : 0, scratch, (int64_t)STATIC_SCRATCH_BYTES, err, err_cap);
+    t_no_timing = false;
+    return rc;
 }
 
 // ---- decoder-block seams (device pointers, asynchronous on the caller's stream) ----------------
@@ -837,7 +890,7 @@ int64_t b200i_norm(int64_t device, void *stream, float *out, const float *x, con
     const int wpc = rows >= 1024 ? 4 : 1; // warps (rows) per CTA: few rows spread over the SMs
     const size_t smem = (size_t)wpc * (size_t)((width + 3) & ~3ll) * sizeof(float);
     if (smem <= 200 * 1024) {
-        static bool configured[64] = {};
+        static std::atomic<bool> configured[64];
         if (dev >= 0 && dev < 64 && !configured[dev]) {
             CUDA_TRY(cudaFuncSetAttribute(norm_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             configured[dev] = true;
@@ -862,7 +915,7 @@ int64_t b200i_add_norm(int64_t device, void *stream, float *out, float *sum_out,
     const int wpc = rows >= 1024 ? 4 : 1;
     const size_t smem = (size_t)wpc * (size_t)((width + 3) & ~3ll) * sizeof(float);
     if (smem <= 200 * 1024) {
-        static bool configured[64] = {};
+        static std::atomic<bool> configured[64];
         if (dev >= 0 && dev < 64 && !configured[dev]) {
             CUDA_TRY(cudaFuncSetAttribute(norm_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             configured[dev] = true;
@@ -987,7 +1040,7 @@ static int64_t attention_launch(int dev, cudaStream_t st, float *ctx, const floa
         dim3 gs((unsigned)((s_grid + 127) / 128), (unsigned)(b * n_heads));
 #define SCORES_SMALL(LQ)                                                                                                          \
     do {                                                                                                                          \
-        static bool configured[64] = {};                                                                                          \
+        static std::atomic<bool> configured[64];                                                                                          \
         if (dev >= 0 && dev < 64 && !configured[dev]) {                                                                           \
             CUDA_TRY(cudaFuncSetAttribute(attn_scores_small_kernel<LQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
                                           attn_scores_small_smem<LQ>()));                                                         \
@@ -1008,7 +1061,7 @@ static int64_t attention_launch(int dev, cudaStream_t st, float *ctx, const floa
                                                  own0, (int)window, position);
     }
     if (l <= ATT_SMALL_Q && (size_t)s_grid * sizeof(float) <= 40 * 1024) {
-        static bool configured[64] = {};
+        static std::atomic<bool> configured[64];
         if (dev >= 0 && dev < 64 && !configured[dev]) {
             CUDA_TRY(cudaFuncSetAttribute(attn_context_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)attn_context_row_smem(40 * 1024 / 4, K_LEAF_MIN)));
@@ -1267,8 +1320,7 @@ static int64_t host_gemm_pipelined(int dev, HostPool &pool, float *c, const floa
     CUDA_TRY(cudaStreamSynchronize(pool.s_out));
     CUDA_TRY(cudaStreamSynchronize(pool.stream));
     CUDA_TRY(cudaStreamSynchronize(pool.s_in));
-    (void)err; (void)err_cap;
-    return 0;
+    return check_wait_status(err, err_cap, "identical gemm");
 }
 
 int64_t b200i_host_gemm_w(int64_t device, float *c, const float *a, const void *b, const void *bscale, int64_t wkind,
@@ -1311,7 +1363,7 @@ int64_t b200i_host_gemm_w(int64_t device, float *c, const float *a, const void *
         return 1;
     CUDA_TRY(cudaMemcpyAsync(c, dc, cbytes, cudaMemcpyDeviceToHost, pool.stream));
     CUDA_TRY(cudaStreamSynchronize(pool.stream));
-    return 0;
+    return check_wait_status(err, err_cap, "identical gemm");
 }
 
 #define HOST_PREP()                                                                  \
@@ -1333,7 +1385,7 @@ int64_t b200i_host_to_bf16(int64_t device, uint16_t *dst, const float *src, int6
     if (b200i_to_bf16(dev, pool.stream, static_cast<uint16_t *>(dd), static_cast<const float *>(ds), count, err, err_cap)) return 1;
     CUDA_TRY(cudaMemcpyAsync(dst, dd, (size_t)count * 2, cudaMemcpyDeviceToHost, pool.stream));
     CUDA_TRY(cudaStreamSynchronize(pool.stream));
-    return 0;
+    return check_wait_status(err, err_cap, "b200i host call");
 }
 
 int64_t b200i_host_from_bf16(int64_t device, float *dst, const uint16_t *src, int64_t count, char *err, int64_t err_cap) {
@@ -1347,7 +1399,7 @@ int64_t b200i_host_from_bf16(int64_t device, float *dst, const uint16_t *src, in
     if (b200i_from_bf16(dev, pool.stream, static_cast<float *>(dd), static_cast<const uint16_t *>(ds), count, err, err_cap)) return 1;
     CUDA_TRY(cudaMemcpyAsync(dst, dd, (size_t)count * 4, cudaMemcpyDeviceToHost, pool.stream));
     CUDA_TRY(cudaStreamSynchronize(pool.stream));
-    return 0;
+    return check_wait_status(err, err_cap, "b200i host call");
 }
 
 int64_t b200i_host_quantize_int8(int64_t device, int8_t *codes, int32_t *exponents, const float *x, int64_t rows,
@@ -1365,7 +1417,7 @@ int64_t b200i_host_quantize_int8(int64_t device, int8_t *codes, int32_t *exponen
     CUDA_TRY(cudaMemcpyAsync(codes, dq, (size_t)rows * cols, cudaMemcpyDeviceToHost, pool.stream));
     CUDA_TRY(cudaMemcpyAsync(exponents, de, (size_t)rows * 4, cudaMemcpyDeviceToHost, pool.stream));
     CUDA_TRY(cudaStreamSynchronize(pool.stream));
-    return 0;
+    return check_wait_status(err, err_cap, "b200i host call");
 }
 
 int64_t b200i_host_dequantize_int8(int64_t device, float *y, const int8_t *codes, const int32_t *exponents, int64_t rows,
@@ -1383,7 +1435,7 @@ int64_t b200i_host_dequantize_int8(int64_t device, float *y, const int8_t *codes
         return 1;
     CUDA_TRY(cudaMemcpyAsync(y, dy, (size_t)rows * cols * 4, cudaMemcpyDeviceToHost, pool.stream));
     CUDA_TRY(cudaStreamSynchronize(pool.stream));
-    return 0;
+    return check_wait_status(err, err_cap, "b200i host call");
 }
 
 int64_t b200i_host_gemm_int8(int64_t device, float *c, const int8_t *qa, const int32_t *ea, const int8_t *qb,
@@ -1406,7 +1458,7 @@ int64_t b200i_host_gemm_int8(int64_t device, float *c, const int8_t *qa, const i
         return 1;
     CUDA_TRY(cudaMemcpyAsync(c, dc, (size_t)m * n * 4, cudaMemcpyDeviceToHost, pool.stream));
     CUDA_TRY(cudaStreamSynchronize(pool.stream));
-    return 0;
+    return check_wait_status(err, err_cap, "b200i host call");
 }
 
 } // extern "C"

@@ -316,7 +316,7 @@ inline bool skinny_plan_fits(long long m, long long n, long long k, int op) {
 template <int WK, int BM, int CPT, int RSPLIT, int MINB>
 inline void launch_skinny_cfg(const GemmArgs &g, int groups, cudaStream_t st) {
     using S = SkinnyShape<BM, CPT, RSPLIT>;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {

@@ -309,7 +309,7 @@ inline int skr_per_sm(int m) { return m <= 8 ? B200I_SKR_MINB8 : (m <= 16 ? B200
 
 template <int WK, int BM, int CPT, int MINB>
 inline void launch_skinny_reg_cfg(const GemmArgs &g, int groups, cudaStream_t st) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {

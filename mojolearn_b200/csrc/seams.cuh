@@ -16,6 +16,7 @@
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
+#include <atomic>
 
 namespace b200i {
 

@@ -153,6 +153,11 @@ class CausalLM(object):
             self._status.zero_()
             raise ValueError("a token id is outside the embedding table")
 
+    def check_status(self):
+        """Raise if a bounded device-side wait ran out since the last check (synchronises the device)."""
+        from .. import torch_ops
+        torch_ops.check_status(self.device)
+
     def forward_device(self, ids, state=None, last_only=False, position=None):
         ids = self._ids(ids)
         b, l = ids.shape
@@ -169,6 +174,8 @@ class CausalLM(object):
         host = not isinstance(ids, torch.Tensor)
         out = self.forward_device(ids, state)
         self.check_ids()
+        if host:
+            self.check_status()
         return out.cpu().numpy() if host else out
 
     def step(self, ids, state):
@@ -177,6 +184,8 @@ class CausalLM(object):
         t = self._ids(ids if (isinstance(ids, torch.Tensor) and ids.dim() == 2) or np.ndim(ids) == 2 else np.asarray(ids)[:, None])
         out = self.forward_device(t, state)[:, -1, :]
         self.check_ids()
+        if host:
+            self.check_status()
         return out.cpu().numpy() if host else out
 
     def argmax_device(self, logits2d):
@@ -210,6 +219,7 @@ class CausalLM(object):
             if step + 1 < max_new_tokens:
                 session.step()
         self.check_ids()
+        self.check_status()  # once per call, not per step
         seq = torch.cat(out, dim=1)
         seq = seq.cpu().numpy() if host else seq
         if return_logits:
@@ -235,6 +245,10 @@ class DecodeSession(object):
         self.position = torch.zeros(1, dtype=torch.int32, device=lm.device)
         self.graph, self.steps, self._fresh = None, 0, False
         self.graph_launches, self.replays = 0, 0  # kernels in the captured step; times it was replayed
+
+    def check_status(self):
+        """Raise if a bounded device-side wait ran out in any step so far (synchronises the device)."""
+        self.lm.check_status()
 
     def next_ids(self):
         """(B, 1) int32 on the device: the greedy choice from the current logits."""

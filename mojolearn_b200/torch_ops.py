@@ -40,6 +40,18 @@ def _stream(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+def check_status(device=None):
+    """Synchronise `device` and raise if a bounded device-side wait ran out since the last check (the word is
+    cleared by the read). The device-pointer entry points are asynchronous and cannot report this themselves;
+    callers that keep results on the device call this once where they would synchronise anyway."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    v = int(_native.lib().b200i_decode_status(index))
+    if v != 0:
+        raise _native.NativeError("mojolearn_b200: a bounded device-side wait ran out (status %d); results computed "
+                                  "since the last check are incomplete" % v)
+
+
 _W_DTYPES = {W_F32: torch.float32, W_BF16: torch.uint16, W_INT8_EXP: torch.int8, W_INT8_SCALE: torch.int8}
 
 

@@ -490,6 +490,8 @@ class TransformerBlock(object):
         if state is None:
             state = self.allocate_state(xt.shape[0], xt.shape[1])
         y = self.forward_device(xt, state)
+        if host:
+            torch_ops.check_status(self.device)  # a host caller gets the answer or an error, never a partial answer
         return y.cpu().numpy() if host else y
 
     def forward(self, x, state=None, *, lengths=None):
