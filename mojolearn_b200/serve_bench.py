@@ -58,6 +58,13 @@ def build_weights(cfg, fmt, seed=0):
     return w
 
 
+def build_ids(cfg, batch, prompt, device=None):
+    """The benchmark's prompt: uniform random token ids from a fixed device generator."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    gen = torch.Generator(device=dev).manual_seed(1)
+    return torch.randint(0, cfg.vocab, (batch, prompt), generator=gen, device=dev, dtype=torch.int32)
+
+
 def run(args):
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -73,8 +80,7 @@ def run(args):
     cfg = CausalLMConfig(vocab=args.vocab, d_model=args.d_model, n_layers=args.layers, n_heads=args.heads,
                          intermediate=args.mlp, max_positions=8192)
     lm = CausalLM(cfg, build_weights(cfg, args.format), device=dev, group=group)
-    gen = torch.Generator(device="cuda").manual_seed(1)
-    ids = torch.randint(0, cfg.vocab, (args.batch, args.prompt), generator=gen, device=dev, dtype=torch.int32)
+    ids = build_ids(cfg, args.batch, args.prompt, dev)
     state = lm.allocate_state(args.batch, args.prompt + args.decode)
     launches0 = _native.lib().b200i_launch_count()
     e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]

@@ -334,6 +334,24 @@ def block_forward(cfg, weights, x, state=None, threads=None):
     return y
 
 
+def attention(q, kcache, vcache, l, used, window=0, threads=None):
+    """Eager attention of one call: q [b*l, n_heads, head_dim] rotated queries, caches [b, n_kv, cap, head_dim] holding
+    `used` positions (this call's l included) -> ctx [b*l, n_heads*head_dim]."""
+    q, kcache, vcache = _f32(q), _f32(kcache), _f32(vcache)
+    b, nkv, cap, hd = kcache.shape
+    nh = q.shape[1]
+    if q.shape[0] != b * l or q.shape[2] != hd:
+        raise ValueError("q must be [b*l, n_heads, head_dim]")
+    ctx = np.empty((b * l, nh * hd), np.float32)
+    f = lib().dec_attention
+    f.restype = ctypes.c_int
+    f.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64] * 8 + [ctypes.c_int]
+    if f(_ptr(ctx), _ptr(q), _ptr(kcache), _ptr(vcache), b, l, nh, nkv, hd, cap, used, window,
+         int(threads or (os.cpu_count() or 1))) != 0:
+        raise ValueError("attention oracle refused the call")
+    return ctx
+
+
 def embedding(table, ids):
     table = _f32(table)
     ids = np.ascontiguousarray(ids, dtype=np.int32)

@@ -24,6 +24,7 @@
  * `transformer-int8w` infer cells on nine fixtures (tests/test_oracle_decoder.py).
  */
 #include <math.h>
+#include <pthread.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -312,6 +313,32 @@ DEC_API float p_fmaxf(float a_in, float b_in) {
     return order_key(b) > order_key(a) ? b : a;
 }
 
+/* ---- a parallel loop over independent items (rows, heads): which thread runs an item moves no bit ---- */
+typedef void (*par_body_t)(int64_t item, void *ctx);
+typedef struct { par_body_t body; void *ctx; int64_t lo, hi; } par_span_t;
+static void *par_run(void *arg) {
+    par_span_t *sp = (par_span_t *)arg;
+    unsigned env = _mm_getcsr();
+    _mm_setcsr(env & ~(0x8000u | 0x0040u)); /* IEEE gradual underflow in this thread too: the flush is spelled, not inherited */
+    for (int64_t i = sp->lo; i < sp->hi; i++) sp->body(i, sp->ctx);
+    _mm_setcsr(env);
+    return NULL;
+}
+static void par_for(int64_t items, int threads, par_body_t body, void *ctx) {
+    if (threads < 1) threads = 1;
+    if (threads > 64) threads = 64;
+    if ((int64_t)threads > items) threads = (int)(items > 0 ? items : 1);
+    par_span_t sp[64];
+    pthread_t th[64];
+    for (int t = 0; t < threads; t++) {
+        sp[t].body = body; sp[t].ctx = ctx;
+        sp[t].lo = items * t / threads; sp[t].hi = items * (t + 1) / threads;
+        if (t + 1 < threads) pthread_create(&th[t], NULL, par_run, &sp[t]);
+    }
+    par_run(&sp[threads - 1]);
+    for (int t = 0; t + 1 < threads; t++) pthread_join(th[t], NULL);
+}
+
 /* ---- block configuration -------------------------------------------------------- */
 
 enum { NORM_RMS = 0, NORM_LAYER = 1, NORM_RMS_OFFSET = 2 };
@@ -329,47 +356,56 @@ typedef struct {
 } block_cfg_t;
 
 /* transformer/checks/transformer_oracle.mojo:1223-1341 */
+typedef struct { float *out; const float *src, *w, *bias; int64_t dm; float eps; int kind; } norm_ctx_t;
+static void norm_row(int64_t t, void *vctx) {
+    const norm_ctx_t *c = (const norm_ctx_t *)vctx;
+    const int64_t dm = c->dm;
+    const float *x = c->src + t * dm, *w = c->w, *bias = c->bias;
+    float *out = c->out;
+    const float eps = c->eps;
+    const int kind = c->kind;
+    if (kind == NORM_LAYER) {
+        float acc = 0.0f;
+        for (int64_t j = 0; j < dm; j++) acc = ftz(add(ftz(acc), ftz(x[j])));
+        float mean = ftz(p_divf(acc, (float)dm));
+        float acc2 = 0.0f;
+        for (int64_t j = 0; j < dm; j++) {
+            float dev = ftz(sub(ftz(x[j]), mean));
+            acc2 = ftz(fmaf(dev, dev, acc2));
+        }
+        float variance = ftz(p_divf(acc2, (float)dm));
+        float rstd = ftz(p_rsqrtf(ftz(add(variance, eps))));
+        for (int64_t j = 0; j < dm; j++) {
+            float dev = ftz(sub(ftz(x[j]), mean));
+            float inner = ftz(mul(dev, rstd));
+            float y = ftz(mul(ftz(w[j]), inner));
+            if (bias) y = ftz(add(ftz(y), ftz(bias[j])));
+            out[t * dm + j] = y;
+        }
+        return;
+    }
+    float acc = 0.0f;
+    for (int64_t j = 0; j < dm; j++) {
+        float xj = ftz(x[j]);
+        acc = ftz(fmaf(xj, xj, acc));
+    }
+    float mean = ftz(p_divf(acc, (float)dm));
+    float rstd = ftz(p_rsqrtf(ftz(add(mean, eps))));
+    for (int64_t j = 0; j < dm; j++) {
+        float inner = ftz(mul(ftz(x[j]), rstd));
+        float wj = ftz(w[j]);
+        if (kind == NORM_RMS_OFFSET) wj = ftz(add(1.0f, wj));
+        out[t * dm + j] = ftz(mul(wj, inner));
+    }
+}
+static void norm_rows(float *out, const float *src, const float *w, const float *bias, int64_t m, int64_t dm, float eps, int kind,
+                      int threads) {
+    norm_ctx_t c = {out, src, w, bias, dm, eps, kind};
+    par_for(m, m * dm >= 65536 ? threads : 1, norm_row, &c);
+}
 DEC_API void dec_norm(float *out, const float *src, const float *w, const float *bias, int64_t m, int64_t dm, float eps,
                       int kind) {
-    unsigned env = _mm_getcsr();
-    _mm_setcsr(env & ~(0x8000u | 0x0040u));
-    for (int64_t t = 0; t < m; t++) {
-        const float *x = src + t * dm;
-        if (kind == NORM_LAYER) {
-            float acc = 0.0f;
-            for (int64_t j = 0; j < dm; j++) acc = ftz(add(ftz(acc), ftz(x[j])));
-            float mean = ftz(p_divf(acc, (float)dm));
-            float acc2 = 0.0f;
-            for (int64_t j = 0; j < dm; j++) {
-                float dev = ftz(sub(ftz(x[j]), mean));
-                acc2 = ftz(fmaf(dev, dev, acc2));
-            }
-            float variance = ftz(p_divf(acc2, (float)dm));
-            float rstd = ftz(p_rsqrtf(ftz(add(variance, eps))));
-            for (int64_t j = 0; j < dm; j++) {
-                float dev = ftz(sub(ftz(x[j]), mean));
-                float inner = ftz(mul(dev, rstd));
-                float y = ftz(mul(ftz(w[j]), inner));
-                if (bias) y = ftz(add(ftz(y), ftz(bias[j])));
-                out[t * dm + j] = y;
-            }
-            continue;
-        }
-        float acc = 0.0f;
-        for (int64_t j = 0; j < dm; j++) {
-            float xj = ftz(x[j]);
-            acc = ftz(fmaf(xj, xj, acc));
-        }
-        float mean = ftz(p_divf(acc, (float)dm));
-        float rstd = ftz(p_rsqrtf(ftz(add(mean, eps))));
-        for (int64_t j = 0; j < dm; j++) {
-            float inner = ftz(mul(ftz(x[j]), rstd));
-            float wj = ftz(w[j]);
-            if (kind == NORM_RMS_OFFSET) wj = ftz(add(1.0f, wj));
-            out[t * dm + j] = ftz(mul(wj, inner));
-        }
-    }
-    _mm_setcsr(env);
+    norm_rows(out, src, w, bias, m, dm, eps, kind, 1);
 }
 
 /* transformer/checks/transformer_oracle.mojo:1344-1372 */
@@ -418,6 +454,90 @@ static void apply_rope(float *out, const float *src, int64_t n_head, int64_t hd,
 static float *falloc(int64_t n) { return (float *)malloc(sizeof(float) * (size_t)(n > 0 ? n : 1)); }
 
 /*
+ * Eager attention of one call (S11-S19): ctx[b*l, n_heads*head_dim] from rotated queries q[b*l, n_heads*head_dim] and
+ * caches [b, n_kv_heads, cap, head_dim] holding `used` positions, this call's l included; window 0 = full causal.
+ * transformer/checks/transformer_oracle.mojo:2373-2546. One (sequence, head) pair per item: heads never read each other.
+ */
+typedef struct {
+    float *ctx; const float *qr, *kcache, *vcache;
+    int64_t l, nh, nkv, hd, cap, key_lo, s, own0, window;
+} attn_ctx_t;
+static void attn_pair(int64_t item, void *vctx) {
+    const attn_ctx_t *c = (const attn_ctx_t *)vctx;
+    const int64_t l = c->l, nh = c->nh, nkv = c->nkv, hd = c->hd, cap = c->cap, key_lo = c->key_lo, s = c->s, own0 = c->own0,
+                  window = c->window, qw = nh * hd, n_rep = nh / nkv;
+    const int64_t bb = item / nh, h = item % nh, kv = h / n_rep;
+    /* attention scale, computed once: ftz(rsqrt(head_dim)) (transformer/checks/transformer_fixture.mojo:134-136) */
+    const float scale = ftz(p_rsqrtf((float)hd));
+    const float mfill = u2f(0xFF7FFFFFu), ufill = 0.0f;
+    float *qmat = falloc(l * hd), *kmat = falloc(s * hd), *cell = falloc(l * s), *ex = falloc(s), *acc = falloc(hd);
+    for (int64_t qi = 0; qi < l; qi++) memcpy(qmat + qi * hd, c->qr + (bb * l + qi) * qw + h * hd, sizeof(float) * hd);
+    const float *kbase = c->kcache + ((bb * nkv + kv) * cap + key_lo) * hd;
+    const float *vbase = c->vcache + ((bb * nkv + kv) * cap + key_lo) * hd;
+    memcpy(kmat, kbase, sizeof(float) * s * hd);
+    rows_gemm(cell, qmat, kmat, 1, l, s, hd, 1); /* S11: gemm fp32.v1, k = head_dim */
+    _mm_setcsr(_mm_getcsr() & ~(0x8000u | 0x0040u));
+    for (int64_t qi = 0; qi < l; qi++) {
+        int64_t jlo = 0, jhi = own0 + qi;
+        if (jhi > s - 1) jhi = s - 1;
+        if (window > 0) { jlo = own0 + qi - window + 1; if (jlo < 0) jlo = 0; }
+        float *row = cell + qi * s;
+        /* S12 scale, S13 mask ADD (never a select), S14 row max over the WHOLE row */
+        float mx = 0.0f;
+        for (int64_t j = 0; j < s; j++) {
+            float sc = ftz(mul(ftz(row[j]), scale));
+            float mk = ftz(add(ftz(sc), (j < jlo || j > jhi) ? mfill : ufill));
+            row[j] = mk;
+            mx = j == 0 ? ftz(mk) : p_fmaxf(mx, ftz(mk));
+        }
+        float fm = ftz(mx);
+        /* S15, S16 over the visible keys; S17 serial denominator; S18 one division per weight */
+        float den = 0.0f;
+        for (int64_t j = jlo; j <= jhi; j++) {
+            ex[j] = ftz(p_expf(ftz(sub(ftz(row[j]), fm))));
+            den = ftz(add(ftz(den), ftz(ex[j])));
+        }
+        den = ftz(den);
+        for (int64_t j = jlo; j <= jhi; j++) ex[j] = ftz(p_divf(ftz(ex[j]), den));
+        /* S19: serial ascending value sum, one fused multiply-add per key (not a GEMM). The keys are the outer loop and
+         * the features the inner one: each feature's chain still sees its keys in ascending order, one accumulator. */
+        float *o = c->ctx + (bb * l + qi) * qw + h * hd;
+        for (int64_t d = 0; d < hd; d++) acc[d] = 0.0f;
+        for (int64_t j = jlo; j <= jhi; j++) {
+            const float wj = ftz(ex[j]);
+            const float *vr = vbase + j * hd;
+            for (int64_t d = 0; d < hd; d++) acc[d] = ftz(fmaf(wj, ftz(vr[d]), acc[d]));
+        }
+        for (int64_t d = 0; d < hd; d++) o[d] = acc[d];
+    }
+    free(qmat); free(kmat); free(cell); free(ex); free(acc);
+}
+DEC_API int dec_attention(float *ctx, const float *qr, const float *kcache, const float *vcache, int64_t b, int64_t l, int64_t nh,
+                          int64_t nkv, int64_t hd, int64_t cap, int64_t used, int64_t window, int threads) {
+    if (b <= 0 || l <= 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || used < l || used > cap) return 1;
+    const int64_t pos0 = used - l;
+    int64_t key_lo = 0;
+    if (window > 0 && pos0 - (window - 1) > 0) key_lo = pos0 - (window - 1);
+    attn_ctx_t c = {ctx, qr, kcache, vcache, l, nh, nkv, hd, cap, key_lo, used - key_lo, pos0 - key_lo, window};
+    par_for(b * nh, threads, attn_pair, &c);
+    return 0;
+}
+
+/* S20, S21: the activation of one row of the MLP (rows are independent) */
+typedef struct { float *act; const float *gate, *up; int64_t inter; int mlp_kind, gated; } act_ctx_t;
+static void act_row(int64_t t, void *vctx) {
+    const act_ctx_t *c = (const act_ctx_t *)vctx;
+    for (int64_t i = t * c->inter; i < (t + 1) * c->inter; i++) {
+        float z = ftz(c->gated ? c->gate[i] : c->up[i]);
+        float a;
+        if (c->mlp_kind == MLP_SWIGLU || c->mlp_kind == MLP_SILU) a = ftz(p_siluf(z)); /* S20 */
+        else if (c->mlp_kind == MLP_GELU_TANH || c->mlp_kind == MLP_GEGLU_TANH) a = ftz(p_gelu_tanh(z));
+        else a = ftz(p_gelu_erf(z));
+        c->act[i] = c->gated ? ftz(mul(ftz(a), ftz(c->up[i]))) : a; /* S21 */
+    }
+}
+
+/*
  * One decoder block, forward, with its KV cache. x and y are [b, l, d_model];
  * kcache / vcache are [b, n_kv_heads, cap, head_dim] and hold `used` positions
  * on entry, `used + l` on exit. Returns 0, or 1 on a refusal.
@@ -427,17 +547,15 @@ DEC_API int dec_block_forward(const block_cfg_t *cfg, const float *const *w, con
                               float *kcache, float *vcache, int64_t cap, int64_t used, int threads) {
     const int64_t dm = cfg->d_model, nh = cfg->n_heads, nkv = cfg->n_kv_heads, hd = cfg->head_dim, inter = cfg->inter;
     if (b <= 0 || l <= 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || (hd & 1) || dm <= 0 || inter <= 0) return 1;
-    const int64_t qw = nh * hd, kw = nkv * hd, n_rep = nh / nkv, m = b * l;
+    const int64_t qw = nh * hd, kw = nkv * hd, m = b * l;
     const int64_t pos0 = used, s_abs = pos0 + l;
     if (s_abs > cap) return 1;
-    int64_t key_lo = 0;
-    if (cfg->window > 0 && pos0 - (cfg->window - 1) > 0) key_lo = pos0 - (cfg->window - 1);
-    const int64_t s = s_abs - key_lo, own0 = pos0 - key_lo, window = cfg->window;
+    const int64_t window = cfg->window;
     unsigned env = _mm_getcsr();
     _mm_setcsr(env & ~(0x8000u | 0x0040u));
 
     float *n1 = falloc(m * dm), *q = falloc(m * qw), *k = falloc(m * kw), *v = falloc(m * kw);
-    dec_norm(n1, x, w[W_NORM1], cfg->norm_bias ? w[W_NORM1_B] : NULL, m, dm, cfg->norm_eps, cfg->norm_kind);
+    norm_rows(n1, x, w[W_NORM1], cfg->norm_bias ? w[W_NORM1_B] : NULL, m, dm, cfg->norm_eps, cfg->norm_kind, threads);
     rows_gemm(q, n1, w[W_Q], 1, m, qw, dm, threads);
     rows_gemm(k, n1, w[W_K], 1, m, kw, dm, threads);
     rows_gemm(v, n1, w[W_V], 1, m, kw, dm, threads);
@@ -463,59 +581,16 @@ DEC_API int dec_block_forward(const block_cfg_t *cfg, const float *const *w, con
                 vcache[dst] = v[t * kw + kv * hd + d];
             }
     }
-    /* attention scale, computed once: ftz(rsqrt(head_dim)) (transformer/checks/transformer_fixture.mojo:134-136) */
-    const float scale = ftz(p_rsqrtf((float)hd));
-    const float mfill = u2f(0xFF7FFFFFu), ufill = 0.0f;
     float *ctx = falloc(m * qw);
-    float *qmat = falloc(l * hd), *kmat = falloc(s * hd), *cell = falloc(l * s), *ex = falloc(s);
-    for (int64_t bb = 0; bb < b; bb++)
-        for (int64_t h = 0; h < nh; h++) {
-            int64_t kv = h / n_rep;
-            for (int64_t qi = 0; qi < l; qi++) memcpy(qmat + qi * hd, qr + (bb * l + qi) * qw + h * hd, sizeof(float) * hd);
-            const float *kbase = kcache + ((bb * nkv + kv) * cap + key_lo) * hd;
-            const float *vbase = vcache + ((bb * nkv + kv) * cap + key_lo) * hd;
-            memcpy(kmat, kbase, sizeof(float) * s * hd);
-            rows_gemm(cell, qmat, kmat, 1, l, s, hd, threads); /* S11: gemm fp32.v1, k = head_dim */
-            _mm_setcsr(env & ~(0x8000u | 0x0040u));
-            for (int64_t qi = 0; qi < l; qi++) {
-                int64_t jlo = 0, jhi = own0 + qi;
-                if (jhi > s - 1) jhi = s - 1;
-                if (window > 0) { jlo = own0 + qi - window + 1; if (jlo < 0) jlo = 0; }
-                float *row = cell + qi * s;
-                /* S12 scale, S13 mask ADD (never a select), S14 row max over the WHOLE row */
-                float mx = 0.0f;
-                for (int64_t j = 0; j < s; j++) {
-                    float sc = ftz(mul(ftz(row[j]), scale));
-                    float mk = ftz(add(ftz(sc), (j < jlo || j > jhi) ? mfill : ufill));
-                    row[j] = mk;
-                    mx = j == 0 ? ftz(mk) : p_fmaxf(mx, ftz(mk));
-                }
-                float fm = ftz(mx);
-                /* S15, S16 over the visible keys; S17 serial denominator; S18 one division per weight */
-                float den = 0.0f;
-                for (int64_t j = jlo; j <= jhi; j++) {
-                    ex[j] = ftz(p_expf(ftz(sub(ftz(row[j]), fm))));
-                    den = ftz(add(ftz(den), ftz(ex[j])));
-                }
-                den = ftz(den);
-                for (int64_t j = jlo; j <= jhi; j++) ex[j] = ftz(p_divf(ftz(ex[j]), den));
-                /* S19: serial ascending value sum, one fused multiply-add per key (not a GEMM) */
-                float *o = ctx + (bb * l + qi) * qw + h * hd;
-                for (int64_t d = 0; d < hd; d++) {
-                    float acc = 0.0f;
-                    for (int64_t j = jlo; j <= jhi; j++) acc = ftz(fmaf(ftz(ex[j]), ftz(vbase[j * hd + d]), acc));
-                    o[d] = acc;
-                }
-            }
-        }
-    free(qmat); free(kmat); free(cell); free(ex);
+    dec_attention(ctx, qr, kcache, vcache, b, l, nh, nkv, hd, cap, s_abs, window, threads);
+    _mm_setcsr(env & ~(0x8000u | 0x0040u));
     float *op = falloc(m * dm), *r1 = falloc(m * dm);
     rows_gemm(op, ctx, w[W_O], 1, m, dm, qw, threads);
     _mm_setcsr(env & ~(0x8000u | 0x0040u));
     if (cfg->o_bias) add_bias(op, w[W_O_B], m, dm);
     for (int64_t i = 0; i < m * dm; i++) r1[i] = ftz(add(ftz(x[i]), ftz(op[i]))); /* S22 */
     float *n2 = falloc(m * dm), *up = falloc(m * inter), *gate = NULL, *act = falloc(m * inter), *down = falloc(m * dm);
-    dec_norm(n2, r1, w[W_NORM2], cfg->norm_bias ? w[W_NORM2_B] : NULL, m, dm, cfg->norm_eps, cfg->norm_kind);
+    norm_rows(n2, r1, w[W_NORM2], cfg->norm_bias ? w[W_NORM2_B] : NULL, m, dm, cfg->norm_eps, cfg->norm_kind, threads);
     const int gated = cfg->mlp_kind == MLP_SWIGLU || cfg->mlp_kind == MLP_GEGLU_ERF || cfg->mlp_kind == MLP_GEGLU_TANH;
     if (gated) {
         gate = falloc(m * inter);
@@ -525,14 +600,8 @@ DEC_API int dec_block_forward(const block_cfg_t *cfg, const float *const *w, con
     rows_gemm(up, n2, w[W_UP], 1, m, inter, dm, threads);
     _mm_setcsr(env & ~(0x8000u | 0x0040u));
     if (cfg->mlp_bias) add_bias(up, w[W_UP_B], m, inter);
-    for (int64_t i = 0; i < m * inter; i++) {
-        float z = ftz(gated ? gate[i] : up[i]);
-        float a;
-        if (cfg->mlp_kind == MLP_SWIGLU || cfg->mlp_kind == MLP_SILU) a = ftz(p_siluf(z)); /* S20 */
-        else if (cfg->mlp_kind == MLP_GELU_TANH || cfg->mlp_kind == MLP_GEGLU_TANH) a = ftz(p_gelu_tanh(z));
-        else a = ftz(p_gelu_erf(z));
-        act[i] = gated ? ftz(mul(ftz(a), ftz(up[i]))) : a; /* S21 */
-    }
+    act_ctx_t actx = {act, gate, up, inter, cfg->mlp_kind, gated};
+    par_for(m, m * inter >= 65536 ? threads : 1, act_row, &actx);
     rows_gemm(down, act, w[W_DOWN], 1, m, dm, inter, threads);
     _mm_setcsr(env & ~(0x8000u | 0x0040u));
     if (cfg->mlp_bias) add_bias(down, w[W_DOWN_B], m, dm);

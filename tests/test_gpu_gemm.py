@@ -179,19 +179,20 @@ def test_config1_1024_cubed_uniform_seed0():
     assert oracle.gemm(a[:8], b).tobytes() == want[:8].tobytes()  # the scalar oracle on a sample of rows
 
 
-@pytest.mark.parametrize("m,n,k", [(4096, 4096, 4096), (8192, 8192, 1024), (128, 11008, 4096), (2048, 50304, 768)])
-def test_config2_full_size_rows_sampled_against_the_oracle(m, n, k):
-    """The full sizes of the headline benchmark shapes: the whole product on the GPU; sampled rows against the
-    CPU oracle (a row's bits do not depend on the other rows); plans against
-    each other on the full output (launch invariance is size independent)."""
+@pytest.mark.parametrize("m,n,k", [(4096, 4096, 4096), (8192, 8192, 1024), (128, 11008, 4096), (2048, 50304, 768),
+                                   (1000, 1000, 1000)])
+def test_config2_full_size_whole_output_against_the_oracle(m, n, k):
+    """The full sizes of the headline benchmark shapes: EVERY cell of the product against the CPU oracle's threaded
+    form (which tests/test_oracle_rows.py holds to the scalar oracle), then the plans against each other on the full
+    output. Plan-against-plan equality alone could not see an error that every plan shares (the group fold, the
+    NaN canonicalisation, the store)."""
     g = torch.Generator(device="cuda").manual_seed(0)
     a = torch.randn((m, k), generator=g, device="cuda", dtype=torch.float32)
     b = torch.randn((n, k), generator=g, device="cuda", dtype=torch.float32)
     c = torch_ops.matmul(a, b, transpose_b=True)
-    rows = sorted(set([0, 1, m // 2, m - 1] + [int(v) for v in np.random.default_rng(1).integers(0, m, 4)]))
-    bh = b.cpu().numpy()
-    want = oracle.gemm_rows(a[rows].cpu().numpy(), bh, oracle.OP_NT)
-    assert c[rows].cpu().numpy().tobytes() == want.tobytes()
+    want = oracle.gemm_rows(a.cpu().numpy(), b.cpu().numpy(), oracle.OP_NT)
+    assert c.cpu().numpy().tobytes() == want.tobytes()
+    del want
     other = torch_ops.product(a, b, None, linalg.W_F32, oracle.OP_NT, plan=torch_ops.PLAN_T64,
                               group_leaves=2 if k >= 256 else 0)
     assert torch.equal(c.view(torch.int32), other.view(torch.int32))
@@ -205,6 +206,43 @@ def test_config2_full_size_rows_sampled_against_the_oracle(m, n, k):
         bt = b.t().contiguous()
         nn = torch_ops.matmul(a, bt)
         assert torch.equal(c.view(torch.int32), nn.view(torch.int32))  # orientations agree
+
+
+FOLD_PLANS = [torch_ops.PLAN_T128, torch_ops.PLAN_T64, torch_ops.PLAN_T32, torch_ops.PLAN_PACKED, torch_ops.PLAN_SKINNY]
+
+
+def _fold_sweep_counts():
+    rng = np.random.default_rng(2049)
+    return list(range(1, 65)) + sorted(set(int(v) for v in rng.integers(65, 1025, 40)))
+
+
+@pytest.mark.parametrize("chunk", range(8))
+def test_fold_over_every_leaf_count(chunk):
+    """The streaming fold against the oracle's tree for every leaf count P in 1..64 and 40 random P up to 1024
+    (the reference sweeps its stack fold over every P in 1..2049, gemm/checks/gemm_device_check.mojo:284): a 3 x 3
+    product, every plan that keeps a fold stack, unsplit and in leaf groups of 1, 2 and 4 (a ragged last group
+    included), a short last leaf on the odd counts. Operands of mixed magnitude make every addition order visible."""
+    counts = _fold_sweep_counts()[chunk::8]
+    for p in counts:
+        k = (p - 1) * 128 + (128 if p % 2 == 0 else 48)  # a multiple of 16 so that the skinny and decode plans accept it
+        assert oracle.leaf_count(k) == p
+        rng = np.random.default_rng(p)
+        a = (rng.standard_normal((3, k)) * np.exp2(rng.integers(-12, 13, (3, k)))).astype(np.float32)
+        b = (rng.standard_normal((3, k)) * np.exp2(rng.integers(-12, 13, (3, k)))).astype(np.float32)
+        want = oracle.nan_canon(oracle.gemm(a, b, oracle.OP_NT))
+        da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+        got = {}
+        for plan in FOLD_PLANS:
+            for groups in (0, 1, 2, 4):
+                if groups and (p + groups - 1) // groups > 64:
+                    continue  # more leaf groups than a launch takes
+                got[(plan, groups)] = torch_ops.product(da, db, None, linalg.W_F32, oracle.OP_NT, plan=plan, group_leaves=groups)
+        if _native.lib().b200i_decode_plan_fits(3, 3, k, oracle.OP_NT, linalg.W_F32):
+            got[(torch_ops.PLAN_DECODE, 0)] = torch_ops.product(da, db, None, linalg.W_F32, oracle.OP_NT, plan=torch_ops.PLAN_DECODE)
+        got[(torch_ops.PLAN_AUTO, 0)] = torch_ops.product(da, db, None, linalg.W_F32, oracle.OP_NT)
+        for key, c in got.items():
+            assert c.cpu().numpy().tobytes() == want.tobytes(), (p, k) + key
+    assert _native.lib().b200i_decode_status(-1) == 0
 
 
 def test_c_abi_refusals_on_device():
