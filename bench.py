@@ -41,6 +41,10 @@ if ROOT not in sys.path:
 
 SWEEP = [(4096, 4096, 4096), (8192, 8192, 1024), (128, 11008, 4096), (2048, 50304, 768), (1000, 1000, 1000)]
 DECODE_N, DECODE_K = 11008, 4096
+CONFIG1 = (1024, 1024, 1024)
+# DRAM bytes of one launch from the committed ncu captures (profiles/): the bench cannot read counters itself
+DECODE_INT8_M1_DRAM_BYTES = 45177000
+PACKED_4096_DRAM_BYTES = None  # set from profiles/gemm_packed_kernel_4096cubed.md
 
 
 def sweep_flops(shapes):
@@ -272,7 +276,38 @@ def main():
                 "peak_source": "in-run fused-multiply-add probe (max of scalar %.1f and packed f32x2 %.1f TFLOP/s); nominal %d SMs x 128 lanes x 2 x %.0f MHz = %.1f"
                 % (peaks["scalar"], peaks["packed"], sms, sm_max, sms * 128 * 2 * sm_max * 1e6 / 1e12),
                 "launch_ms": {"%dx%dx%d" % SWEEP[i]: per_shape_ms[i] for i in range(len(SWEEP))},
-                "traffic": None}
+                "per_shape": {"%dx%dx%d" % SWEEP[i]: {"ms": per_shape_ms[i], "tflops": 2.0 * SWEEP[i][0] * SWEEP[i][1] * SWEEP[i][2] / (per_shape_ms[i] * 1e-3) / 1e12,
+                                                       "frac_fp32": 2.0 * SWEEP[i][0] * SWEEP[i][1] * SWEEP[i][2] / (per_shape_ms[i] * 1e-3) / 1e12 / fp32_peak}
+                              for i in range(len(SWEEP))},
+                "algorithmic_bytes_per_step": int(sum(4 * (m * k + n * k + m * n) for m, n, k in SWEEP)),
+                # DRAM bytes cannot be read inside the bench: the committed ncu capture of the 4096-cubed launch is scaled to the
+                # sweep by multiply-adds (the panels and the fold traffic both grow with m * n * k / tile)
+                "traffic": (PACKED_4096_DRAM_BYTES * sweep_flops(SWEEP) / (2.0 * 4096 ** 3)) if PACKED_4096_DRAM_BYTES else None,
+                "traffic_source": "profiles/gemm_packed_kernel_4096cubed.md (one 4096-cubed launch), scaled to a step by multiply-adds"}
+
+    # ---- configuration 1: M = N = K = 1024, U(-1, 1) from seed 0, row-major C = A . B, timed on its own ----
+    g1 = torch.Generator(device=dev).manual_seed(0)
+    a1 = torch.rand((CONFIG1[0], CONFIG1[2]), generator=g1, device=dev) * 2.0 - 1.0
+    b1 = torch.rand((CONFIG1[2], CONFIG1[1]), generator=g1, device=dev) * 2.0 - 1.0
+    c1 = torch.empty((CONFIG1[0], CONFIG1[1]), device=dev)
+    flush = torch.empty((160 << 20,), dtype=torch.uint8, device=dev)  # larger than L2: written between timed launches
+    for _ in range(3):
+        torch_ops.matmul(a1, b1, out=c1)
+    c1_ms = []
+    for _ in range(10):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch_ops.matmul(a1, b1, out=c1)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        c1_ms.append(e0.elapsed_time(e1))
+    c1_us = statistics.median(c1_ms) * 1e3
+    config1 = {"shape": list(CONFIG1), "op": "NN", "operands": "U(-1, 1) float32, torch generator seed 0", "us": c1_us,
+               "tflops": 2.0 * CONFIG1[0] * CONFIG1[1] * CONFIG1[2] / (c1_us * 1e-6) / 1e12,
+               "frac_fp32": 2.0 * CONFIG1[0] * CONFIG1[1] * CONFIG1[2] / (c1_us * 1e-6) / 1e12 / fp32_peak,
+               "l2": "a 160 MB buffer is written between timed launches", "launches_timed": 10}
+    del flush, a1, b1, c1
 
     # ---- decode kernel against HBM: weights [11008, 4096] in three storage kinds, one activation row ----
     peaks_file = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -282,20 +317,22 @@ def main():
             hbm_peak, hbm_src = float(json.load(open(peaks_file))["hbm_gbs"]), "measured"
         except (ValueError, KeyError):
             pass
-    from mojolearn_b200.linalg import OP_NT, W_BF16, W_F32, W_INT8_EXP
+    from mojolearn_b200.linalg import OP_NT, W_BF16, W_F32, W_INT8_EXP, W_INT8_SCALE
     g2 = torch.Generator(device=dev).manual_seed(100 + rank)
     we = torch.randint(-10, -5, (DECODE_N,), generator=g2, device=dev, dtype=torch.int32)
+    ws = torch.rand((DECODE_N,), generator=g2, device=dev) * 0.019 + 0.001  # per-row float32 scales U(0.001, 0.02)
     decode = {}
-    for kind_name, wkind, wbytes, nbuf in (("int8", W_INT8_EXP, 1, 6), ("bf16", W_BF16, 2, 4), ("f32", W_F32, 4, 3)):
+    for kind_name, wkind, wbytes, nbuf, rows in (("int8", W_INT8_EXP, 1, 6, (1, 8, 32, 128)), ("int8_f32scale", W_INT8_SCALE, 1, 6, (1, 8, 32, 128)),
+                                                 ("bf16", W_BF16, 2, 4, (1, 8, 32, 128)), ("f32", W_F32, 4, 3, (1, 8))):
         # nbuf weight buffers rotate through, so no launch finds its weights in the 126 MB L2
-        if wkind == W_INT8_EXP:
+        if wbytes == 1:
             wq = [torch.randint(-127, 128, (DECODE_N, DECODE_K), generator=g2, device=dev, dtype=torch.int8) for _ in range(nbuf)]
         elif wkind == W_BF16:
             wq = [torch_ops.to_bf16(torch.randn((DECODE_N, DECODE_K), generator=g2, device=dev) * 0.02) for _ in range(nbuf)]
         else:
             wq = [torch.randn((DECODE_N, DECODE_K), generator=g2, device=dev) * 0.02 for _ in range(nbuf)]
-        scale = we if wkind == W_INT8_EXP else None
-        for mrows in (1, 8):
+        scale = we if wkind == W_INT8_EXP else (ws if wkind == W_INT8_SCALE else None)
+        for mrows in rows:
             x = torch.randn((mrows, DECODE_K), generator=g2, device=dev)
             y = torch.empty((mrows, DECODE_N), device=dev)
             reps = 4
@@ -319,14 +356,23 @@ def main():
             torch.cuda.synchronize(dev)
             us = e0.elapsed_time(e1) * 1e3 / (reps * nbuf)
             nbytes = mrows * DECODE_K * 4 + DECODE_N * DECODE_K * wbytes + (DECODE_N * 4 if scale is not None else 0) + mrows * DECODE_N * 4
+            flops = 2.0 * mrows * DECODE_N * DECODE_K
+            # the floor of one launch: the slower of its bytes at the measured HBM rate and its flops at the FP32 peak
+            floor_us = max(nbytes / (hbm_peak * 1e9), flops / (fp32_peak * 1e12)) * 1e6
             decode[(kind_name, mrows)] = {"us": us, "gbs": nbytes / (us * 1e-6) / 1e9, "bytes": nbytes, "frac_hbm": nbytes / (us * 1e-6) / 1e9 / hbm_peak,
-                                          "tflops": 2.0 * mrows * DECODE_N * DECODE_K / (us * 1e-6) / 1e12}
+                                          "tflops": flops / (us * 1e-6) / 1e12, "frac_fp32": flops / (us * 1e-6) / 1e12 / fp32_peak,
+                                          "floor_us": floor_us, "frac_of_floor": floor_us / us,
+                                          "bound": "hbm" if nbytes / (hbm_peak * 1e9) >= flops / (fp32_peak * 1e12) else "fp32"}
             del graph
         del wq
     d1 = decode[("int8", 1)]
     roofline_decode = {"bound": "hbm", "kernel": "decode_kernel<int8,1>", "achieved": d1["gbs"], "peak": hbm_peak, "unit": "GB/s",
                        "frac": d1["gbs"] / hbm_peak, "peak_source": hbm_src + " HBM copy bandwidth", "us_per_launch": d1["us"],
-                       "algorithmic_bytes": d1["bytes"], "traffic": None, "timing": "CUDA events around one graph replay of 24 launches",
+                       "algorithmic_bytes": d1["bytes"], "traffic": DECODE_INT8_M1_DRAM_BYTES,
+                       "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, profiles/decode_kernel_int8_m1_11008x4096.md",
+                       "timing": "CUDA events around one graph replay of 24 launches",
+                       "workload": "W[11008, 4096] (baseline configuration 3), rows M in {1, 8, 32, 128}: int8 + int32 row exponents, "
+                                   "int8 + float32 row scales U(0.001, 0.02), bf16; float32 at 1 and 8 rows",
                        "all": {"%s_m%d" % k: v for k, v in decode.items()}}
     nbuf = 6
 
@@ -382,11 +428,29 @@ def main():
     if not args.skip_serve:
         import argparse as _ap
         from mojolearn_b200 import serve_bench
-        sargs = _ap.Namespace(layers=24, d_model=2048, heads=16, mlp=8192, vocab=50304, batch=32, prompt=1024, decode=48,
-                              timed_steps=32, format="int8", no_graph=False)
+        # all 256 greedy steps are run; the last 64 are the timed ones (the caches are then at 1216 .. 1279 positions)
+        sargs = _ap.Namespace(layers=24, d_model=2048, heads=16, mlp=8192, vocab=50304, batch=32, prompt=1024, decode=256,
+                              timed_steps=64, format="int8", no_graph=False)
         del ops
         torch.cuda.empty_cache()
         serve, _ = serve_bench.run(sargs)
+        if world > 1:
+            # the single-GPU figure of the same run, on rank 0 alone while the others wait: the sharded tokens/s over
+            # N times this one is the scaling efficiency, and the hashes say the sharded logits are the same words
+            solo = None
+            torch.cuda.empty_cache()
+            if rank == 0:
+                solo, _ = serve_bench.run(sargs, solo=True)
+            dist.barrier()
+            if rank == 0:
+                serve["scaling"] = {"1": {"tokens_per_s": solo["value"], "ms_per_decode_step": solo["ms_per_decode_step"],
+                                          "prefill_ms": solo["prefill_ms"]},
+                                    str(world): {"tokens_per_s": serve["value"], "ms_per_decode_step": serve["ms_per_decode_step"],
+                                                 "prefill_ms": serve["prefill_ms"],
+                                                 "decode_efficiency": serve["value"] / (world * solo["value"]),
+                                                 "prefill_efficiency": solo["prefill_ms"] / (world * serve["prefill_ms"])},
+                                    "kind": "strong (the batch of 32 is fixed)",
+                                    "bit_identical_to_1gpu": solo["ids_sha256"] == serve["ids_sha256"] and solo["logits_sha256"] == serve["logits_sha256"]}
 
     if rank == 0:
         line = {"metric": "identical_fp32_gemm_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world,
@@ -397,7 +461,7 @@ def main():
                            "l2": "inputs larger than L2: one pass reads 1.5 GB of operands",
                            "bit_exact": "every product is the oracle's bits (tests/test_gpu_gemm.py)"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
-                "roofline_decode": roofline_decode, "cpu_baseline": cpu,
+                "roofline_decode": roofline_decode, "cpu_baseline": cpu, "config1": config1,
                 "decode": {"metric": "int8w_matvec_rows_per_s", "value": 1e6 / d1["us"], "unit": "rows/s",
                            "weights": "int8 [11008, 4096] + int32 row exponents", "rotating_weight_buffers": nbuf},
                 "serve": serve}

@@ -77,7 +77,8 @@ int64_t b200i_gemm_w(int64_t device, void *stream, float *c, const float *a, con
  * on-device restatement of the oracle), 1 = 128x128 tiles, 2 = 64x64 tiles,
  * 3 = the row-streaming decode plan (up to 8 rows), 4 = 32x128 tiles, 5 = 128x64 tiles,
  * 6 = the skinny plan (op NT, up to 32 activation rows, k a multiple of 16, 16-byte aligned
- * operands), 7 = the packed plan (operands repacked into tile-major panels in the workspace,
+ * operands; low-bit weights fold up to 16 leaf groups inside thread-block clusters), 8 = the skinny plan with the
+ * group nodes always in the workspace and a separate fold, 7 = the packed plan (operands repacked into tile-major panels in the workspace,
  * then 128x128 tiles fed by bulk copies; needs a 256-byte aligned workspace of
  * b200i_plan_workspace_bytes); `group_leaves` = leaves per group (a power of two, 0 = no split). Every plan returns the same bits; the tests
  * hold them to that (the reference's launch-invariance gate,
@@ -86,23 +87,15 @@ int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a
                           int64_t wkind, int64_t m, int64_t n, int64_t k, int64_t op, int64_t plan,
                           int64_t group_leaves, void *ws, int64_t ws_bytes, char *err, int64_t err_cap);
 
-/* A static weight laid out once for the decode-step product (up to 32 activation rows).
- * b200i_pack_weight rewrites W[n, k] (storage kind `wkind`, `scale` as for b200i_gemm_w) into
- * column-tile-major panels of the same storage type, with per-column factors and per-window
- * admission flags, in `packed` (256-byte aligned, b200i_packed_weight_bytes(n, k, wkind) bytes;
- * k a multiple of 16 with 128-step leaves, else 0 bytes and a refusal). b200i_gemm_packed_w is
- * then C[m, n] = A[m, k] . W^T for m <= 32 with the same bits as b200i_gemm_w: the panels let one
- * thread feed the CTA with bulk copies instead of staging the weight through registers. `ws` is
- * per-call scratch of b200i_gemm_packed_w_workspace_bytes(m, n, k) bytes, 256-byte aligned. The
- * reference packs its weights for the same reason (python/mojolearn/lowbit.py pack / pack_one keep a
- * layer's storage form; gemm/checks/gemm_lowbit.mojo:369-395 consumes it); the panel layout itself
- * has no reference counterpart. */
-int64_t b200i_packed_weight_bytes(int64_t n, int64_t k, int64_t wkind);
-int64_t b200i_pack_weight(int64_t device, void *stream, void *packed, const void *w, const void *scale, int64_t wkind, int64_t n,
-                          int64_t k, char *err, int64_t err_cap);
-int64_t b200i_gemm_packed_w_workspace_bytes(int64_t m, int64_t n, int64_t k);
-int64_t b200i_gemm_packed_w(int64_t device, void *stream, float *c, const float *a, const void *packed, int64_t wkind, int64_t m,
-                            int64_t n, int64_t k, void *ws, int64_t ws_bytes, char *err, int64_t err_cap);
+/* The product with a store epilogue: bias (one float32 per output column, or NULL) is added to the
+ * finished word, then `act` is applied: 0 = none, 1 = gelu (erf), 2 = gelu (tanh), 3 = silu. Replaces
+ * the reference's GEMM_EPI_PLUS_BIAS and GEMM_EPI_BIAS_ACT stores (gemm/checks/gemm_identical.mojo
+ * :8869-8912, :9483-9491): the words are those of b200i_gemm_w followed by b200i_bias_add and the
+ * ungated b200i_act_mul, with one launch instead of three. `plan` and `group_leaves` as for
+ * b200i_gemm_w_plan (-1, 0 = automatic). */
+int64_t b200i_gemm_w_epilogue(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale, int64_t wkind,
+                              int64_t m, int64_t n, int64_t k, int64_t op, const float *bias, int64_t act, int64_t plan,
+                              int64_t group_leaves, void *ws, int64_t ws_bytes, char *err, int64_t err_cap);
 
 /* Device timing of the product's main kernel, for benchmarks. While enabled (enable = 1 also
  * clears the record) every product call records a CUDA event pair on its stream around its main
@@ -270,6 +263,44 @@ int64_t b200i_advance_position(int64_t device, void *stream, int32_t *position, 
 /* out[rows] = index of the largest logit, ties to the lowest id (python/mojolearn/models/causal_lm.py:190). */
 int64_t b200i_argmax(int64_t device, void *stream, int32_t *out, const float *logits, int64_t rows, int64_t vocab, char *err,
                      int64_t err_cap);
+
+/* --- exchange of finished output columns between the GPUs of one node ------------------------------
+ * Output-column sharding (weight rows [r*N/g, (r+1)*N/g) on rank r, full k) needs the column slices
+ * [m, N/g] of all ranks side by side as [m, N] on every rank. The reference's multi-device rule is
+ * that such an exchange only copies finished words and never chooses an arithmetic order
+ * (training/byte_lm_parallel.mojo:2-8, core/multi_gpu.mojo:46-50); this is that copy as one small
+ * kernel per gather over peer-mapped memory instead of a collective library call. The owner of a
+ * slice stores each word, paired with the step's epoch number in one 64-bit store, into a receive
+ * area in every other rank's exchange buffer; the same kernel reads the areas the other ranks fill
+ * in its own buffer, waiting (bounded: a word that has not arrived after 4 s sets status 8 of
+ * b200i_decode_status) for each pair's tag, and writes the gathered matrix. One process per GPU,
+ * all on one node.
+ *   b200i_comm_create    allocates this rank's exchange buffer of `bytes` (zeroed) and returns an
+ *                        opaque object in *comm.
+ *   b200i_comm_export    writes the buffer's 64-byte CUDA IPC handle; the caller carries it to the
+ *                        other processes (any host channel), which pass it to b200i_comm_attach.
+ *                        After every rank attached every other rank, and before the first gather,
+ *                        the caller runs a host barrier.
+ *   b200i_comm_attach_local  the same for two exchanges inside one process on one device (tests).
+ *   b200i_comm_advance   asynchronous on `stream`: starts a new epoch (one model step). Every rank
+ *                        calls it once per step, before the step's first gather.
+ *   b200i_comm_gather    asynchronous on `stream`: out[m, world * w] (row pitch out_ld floats, 0 =
+ *                        world * w; caller-owned device memory) from this rank's src[m, w] (row pitch
+ *                        src_ld, 0 = w) and the other ranks' slices. `area_bytes` places the gather's
+ *                        receive areas (m * w * world * 8 bytes) in the exchange buffers; every rank
+ *                        issues the same gathers in the same order with the same areas. Areas of
+ *                        one step must not overlap, a step must have at least two gathers, and the
+ *                        first gather's area must not overlap any other gather's of any step.
+ *                        mode 0 = send and receive; 1 = send only; 2 = receive only (src ignored).
+ *   b200i_comm_destroy   after a host barrier: unmaps the peers and frees the buffer. */
+int64_t b200i_comm_create(int64_t device, int64_t rank, int64_t world, int64_t bytes, void **comm, char *err, int64_t err_cap);
+int64_t b200i_comm_export(void *comm, void *handle, int64_t handle_bytes, char *err, int64_t err_cap);
+int64_t b200i_comm_attach(void *comm, int64_t peer, const void *handle, char *err, int64_t err_cap);
+int64_t b200i_comm_attach_local(void *comm, int64_t peer, void *other, char *err, int64_t err_cap);
+int64_t b200i_comm_advance(void *comm, void *stream, char *err, int64_t err_cap);
+int64_t b200i_comm_gather(void *comm, void *stream, int64_t mode, int64_t area_bytes, float *out, int64_t out_ld, const float *src,
+                          int64_t m, int64_t w, int64_t src_ld, char *err, int64_t err_cap);
+int64_t b200i_comm_destroy(void *comm);
 
 /* Status word of the bounded device-side waits on `device` (synchronises the
  * device): 0 = no wait ever ran out; 1 / 2 = the decode plan's producer / a consumer

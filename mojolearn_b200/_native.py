@@ -44,16 +44,13 @@ SIGNATURES = {
     "b200i_launch_count": [],
     "b200i_workspace_bytes": [I64, I64, I64],
     "b200i_plan_workspace_bytes": [I64, I64, I64, I64, I64],
-    "b200i_packed_weight_bytes": [I64, I64, I64],
-    "b200i_pack_weight": [I64, VP, VP, VP, VP, I64, I64, I64, VP, I64],
-    "b200i_gemm_packed_w_workspace_bytes": [I64, I64, I64],
-    "b200i_gemm_packed_w": [I64, VP, VP, VP, VP, I64, I64, I64, I64, VP, I64, VP, I64],
     "b200i_kernel_timing": [I64],
     "b200i_kernel_timing_read": [VP, VP],
     "b200i_decode_plan_fits": [I64, I64, I64, I64, I64],
     "b200i_gemm_f32": [I64, VP, VP, VP, VP, I64, I64, I64, I64, VP, I64, VP, I64],
     "b200i_gemm_f32_noalloc": [I64, VP, VP, VP, VP, I64, I64, I64, I64, VP, I64],
     "b200i_gemm_w": [I64, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, VP, I64, VP, I64],
+    "b200i_gemm_w_epilogue": [I64, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, VP, I64, I64, I64, VP, I64, VP, I64],
     "b200i_gemm_w_plan": [I64, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, I64, I64, VP, I64, VP, I64],
     "b200i_to_bf16": [I64, VP, VP, VP, I64, VP, I64],
     "b200i_from_bf16": [I64, VP, VP, VP, I64, VP, I64],
@@ -88,8 +85,16 @@ SIGNATURES = {
     "b200i_add_positions_at": [I64, VP, VP, VP, I64, I64, VP, I64, VP, I64],
     "b200i_advance_position": [I64, VP, VP, I64, VP, I64],
     "b200i_ffma_probe": [I64, VP, VP, I64, I64, I64, VP, I64],
+    "b200i_comm_create": [I64, I64, I64, I64, VP, VP, I64],
+    "b200i_comm_export": [VP, VP, I64, VP, I64],
+    "b200i_comm_attach": [VP, I64, VP, VP, I64],
+    "b200i_comm_attach_local": [VP, I64, VP, VP, I64],
+    "b200i_comm_advance": [VP, VP, VP, I64],
+    "b200i_comm_gather": [VP, VP, I64, I64, VP, I64, VP, I64, I64, I64, VP, I64],
+    "b200i_comm_destroy": [VP],
 }
 STRING_FUNCTIONS = ["b200i_numerical_profile", "b200i_vendor"]
+POINTER_FUNCTIONS = {}
 
 
 def _declare(l):
@@ -101,6 +106,10 @@ def _declare(l):
         fn = getattr(l, name)
         fn.restype = CP
         fn.argtypes = []
+    for name, args in POINTER_FUNCTIONS.items():
+        fn = getattr(l, name)
+        fn.restype = VP
+        fn.argtypes = args
 
 
 def call(name, *args):

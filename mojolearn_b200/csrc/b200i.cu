@@ -8,16 +8,13 @@
 #include <vector>
 
 #include "../../include/b200i.h"
+#include "comm.cuh"
 #include "decode.cuh"
 #include "decoder.cuh"
 #include "gemm_tile.cuh"
 #include "gemm_skinny.cuh"
 #include "gemm_packed.cuh"
-#include "gemm_skinny_packed.cuh"
 #include "gemm_skinny_reg.cuh"
-#ifndef B200I_SK_REG
-#define B200I_SK_REG 1
-#endif
 #include "lowbit.cuh"
 
 using namespace b200i;
@@ -89,7 +86,8 @@ int64_t check_wait_status(char *err, int64_t err_cap, const char *who) {
 }
 
 // ---- plans -----------------------------------------------------------------------------
-enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4, PLAN_T128X64 = 5, PLAN_SKINNY = 6, PLAN_PACKED = 7 };
+enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4, PLAN_T128X64 = 5, PLAN_SKINNY = 6, PLAN_PACKED = 7,
+       PLAN_SKINNY_NODES = 8 }; // the skinny plan with its leaf-group nodes in global memory and a separate fold (never folded in clusters)
 
 // Up to this many rows the weight-streaming decode plan wins; above, the skinny plan. Low-bit weights
 // switch earlier: at three and four rows the decode kernel's serial chains cost more than the register
@@ -98,9 +96,7 @@ enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE =
 // ([50304, 2048]: bf16 79 us against 98 at four rows, int8 60 against 69 at three).
 constexpr int DECODE_PREFER_M = 4;
 constexpr long long DECODE_WIDE_N = 32768;
-#ifndef B200I_DECODE_PREFER_M_LOWBIT
-#define B200I_DECODE_PREFER_M_LOWBIT 2
-#endif
+constexpr int DECODE_PREFER_M_LOWBIT = 2;
 
 struct Plan {
     int kind;
@@ -169,7 +165,7 @@ Plan choose_skinny(long long m, long long n, long long k, int sms, bool lowbit) 
     int min_s = 1;
     while ((leaves + min_s - 1) / min_s > MAX_GROUPS) min_s *= 2;
     int best = min_s;
-    if (lowbit && B200I_SK_REG) {
+    if (lowbit) {
         const int bm = skr_bm((int)m), bn = skr_bn((int)m);
         const long long tiles = ((n + bn - 1) / bn) * ((m + bm - 1) / bm);
         const double rate = bm >= 32 ? 0.25e6 : (bm >= 16 ? 0.20e6 : 0.15e6); // flops per microsecond per SM
@@ -182,7 +178,12 @@ Plan choose_skinny(long long m, long long n, long long k, int sms, bool lowbit) 
             const long long rounds = (ctas + sms - 1) / sms;
             double thin = ctas <= sms ? 1.25 : (ctas <= 2 * sms ? 1.08 : 1.0);
             double t = (double)rounds * (s * leaf_us * thin + 0.4);
-            if (groups > 1) t += 2.5 + (double)groups * m * n * 8.0 / 7.5e6;
+            if (groups > SKR_MAX_CLUSTER) t += 2.5 + (double)groups * m * n * 8.0 / 7.5e6; // global nodes and a second launch
+            else if (groups > 1) {                                                             // folded inside a cluster: a barrier and a
+                int levels = 0;                                                                // shared-memory pass per tree level
+                while ((1 << levels) < groups) levels++;
+                t += 0.5 * (levels + 1);
+            }
             if (t < best_t) { best_t = t; best = s; }
         }
     } else {
@@ -231,54 +232,6 @@ void timing_end(int slot, cudaStream_t st) {
 
 size_t round256(size_t v) { return (v + 255) / 256 * 256; }
 size_t round256_sz(size_t v) { return round256(v); }
-
-// ---- the skinny product against a prepacked weight ------------------------------------------
-Plan choose_skinny_packed(long long n, long long k, int sms) {
-    const int leaves = (int)leaf_count(k) > 0 ? (int)leaf_count(k) : 1;
-    const long long col_ctas = (n + SKP_BN - 1) / SKP_BN;
-    const long long want = (long long)sms * SKP_PER_SM * 9 / 10;
-    const int max_s = pow2_floor(leaves) * ((leaves & (leaves - 1)) ? 2 : 1);
-    int min_s = 1;
-    while ((leaves + min_s - 1) / min_s > MAX_GROUPS) min_s *= 2;
-    int best = min_s;
-    for (int s = max_s; s >= min_s; s /= 2)
-        if (col_ctas * ((leaves + s - 1) / s) >= want) { best = s; break; }
-    Plan p{PLAN_SKINNY, best, (leaves + best - 1) / best};
-    if (p.groups <= 1) p.group_leaves = leaves;
-    return p;
-}
-int skp_bm(long long m) { return m <= 8 ? 8 : (m <= 16 ? 16 : 32); }
-size_t skp_call_bytes(long long m, long long n, long long k, int groups) {
-    return round256_sz((size_t)k * skp_bm(m) * 4) + round256_sz((size_t)(k / KS)) + (groups > 1 ? (size_t)groups * m * n * 4 : 0);
-}
-
-template <int WK, int BM>
-void launch_skinny_packed_cfg(const SkinnyPackedArgs &g, cudaStream_t st) {
-    static std::atomic<bool> configured[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    constexpr int smem = skp_smem_bytes(WK, BM);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaFuncSetAttribute(gemm_skinny_packed_kernel<WK, BM, SKP_PER_SM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        configured[dev] = true;
-    }
-    dim3 grid((unsigned)((g.n + SKP_BN - 1) / SKP_BN), (unsigned)g.groups);
-    gemm_skinny_packed_kernel<WK, BM, SKP_PER_SM><<<grid, SKP_THREADS, smem, st>>>(g);
-}
-template <int WK>
-void launch_skinny_packed_wk(const SkinnyPackedArgs &g, float *at, unsigned char *aflags, const float *a, cudaStream_t st) {
-    const unsigned windows = (unsigned)(g.k / KS);
-    if (g.m <= 8) {
-        skinny_pack_a_kernel<8><<<windows, 128, 0, st>>>(at, aflags, a, g.m, g.k);
-        launch_skinny_packed_cfg<WK, 8>(g, st);
-    } else if (g.m <= 16) {
-        skinny_pack_a_kernel<16><<<windows, 128, 0, st>>>(at, aflags, a, g.m, g.k);
-        launch_skinny_packed_cfg<WK, 16>(g, st);
-    } else {
-        skinny_pack_a_kernel<32><<<windows, 128, 0, st>>>(at, aflags, a, g.m, g.k);
-        launch_skinny_packed_cfg<WK, 32>(g, st);
-    }
-}
 
 // rows below which packing the operands costs more than the bulk-copy pipeline returns
 constexpr long long PACKED_MIN_EXTENT = 256;
@@ -364,7 +317,7 @@ int launch_packed(const GemmArgs &g, int groups, unsigned char *scratch, cudaStr
     PackArgs b{pb, fb, g.b, g.bscale, g.n, g.k, g.leaf, g.leaves, wpl, g.op == OP_NT, g.op == OP_NT && k8 && aligned(g.b, 16)};
     launch_pack_b(b, g.wkind, st);
     PackedGemmArgs p{pa, pb, fa, fb, g.c, g.ws, g.m, g.n, g.k, g.leaf, g.leaves, wpl, g.group_leaves, groups,
-                     (g.n + PK_TILE - 1) / PK_TILE, g.vec_c};
+                     (g.n + PK_TILE - 1) / PK_TILE, g.vec_c, g.epi};
     dim3 grid((unsigned)(((g.m + PK_TILE - 1) / PK_TILE) * p.tiles_n), (unsigned)groups);
     const int tslot = timing_begin(st);
     gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, st>>>(p);
@@ -389,7 +342,7 @@ void launch_tile(GemmArgs &g, int groups, cudaStream_t st) {
 
 int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const void *b, const void *bscale, int wkind,
                        int64_t m, int64_t n, int64_t k, int op, int plan_kind, int64_t group_leaves, void *ws,
-                       int64_t ws_bytes, char *err, int64_t err_cap) {
+                       int64_t ws_bytes, char *err, int64_t err_cap, Epilogue epi = Epilogue{nullptr, EPI_ACT_NONE}) {
     if (m <= 0 || n <= 0 || k <= 0)
         return fail(err, err_cap, "identical gemm: m, n and k must be positive (got m=%lld n=%lld k=%lld)", (long long)m,
                     (long long)n, (long long)k);
@@ -410,6 +363,7 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     g.m = (int)m; g.n = (int)n; g.k = (int)k; g.op = op; g.wkind = wkind;
     g.leaf = (int)leaf_size(k);
     g.leaves = (int)leaf_count(k);
+    g.epi = epi;
 
     Plan plan;
     if (plan_kind == PLAN_AUTO) {
@@ -422,12 +376,12 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
         const bool dec = decode_plan_fits(m, n, k, op, wkind) && al16;
         const bool skinny = skinny_plan_fits(m, n, k, op) && al16;
         const bool wide = n >= DECODE_WIDE_N && (wkind == W_BF16 || m == 3);
-        const int prefer_m = (wkind != W_F32 && skinny && B200I_SK_REG && !wide) ? B200I_DECODE_PREFER_M_LOWBIT : DECODE_PREFER_M;
+        const int prefer_m = (wkind != W_F32 && skinny && !wide) ? DECODE_PREFER_M_LOWBIT : DECODE_PREFER_M;
         if (dec && m <= prefer_m) plan = Plan{PLAN_DECODE, g.leaves, 1};
         else if (skinny) plan = choose_skinny(m, n, k, sm_count(dev), wkind != W_F32);
         else if (dec) plan = Plan{PLAN_DECODE, g.leaves, 1};
     } else {
-        plan.kind = plan_kind;
+        plan.kind = plan_kind == PLAN_SKINNY_NODES ? PLAN_SKINNY : plan_kind;
         int s = group_leaves > 0 ? (int)group_leaves : g.leaves;
         if (s & (s - 1)) {
             if (s < g.leaves) return fail(err, err_cap, "identical gemm: a leaf group must be a power of two");
@@ -457,6 +411,7 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     g.vec_c = (n % 4 == 0) && aligned(c, 16) && (plan.groups == 1 || aligned(ws, 16));
 
     int tslot = -1;
+    bool folded = false; // the plan's own launch already folded the leaf groups
     if (plan.kind != PLAN_PACKED) tslot = timing_begin(st);
     if (plan.kind == PLAN_FLAT) {
         const long long cells = (long long)m * n;
@@ -467,10 +422,7 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
             return fail(err, err_cap, "identical gemm: the decode plan needs op NT, m <= %d, k a multiple of 16 and 16-byte aligned weights", DECODE_MAX_M);
         g_launches += launch_decode(g, sm_count(dev), st);
     } else if (plan.kind == PLAN_T128) {
-#ifndef B200I_T128_MINB
-#define B200I_T128_MINB 2
-#endif
-        launch_tile<128, 128, 2, 2, B200I_T128_MINB>(g, plan.groups, st);
+        launch_tile<128, 128, 2, 2, 2>(g, plan.groups, st);
         g_launches++;
     } else if (plan.kind == PLAN_T64) {
         launch_tile<64, 64, 1, 1, 3>(g, plan.groups, st);
@@ -491,16 +443,17 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
         if (!skinny_plan_fits(m, n, k, op) || !aligned(b, 16) || !aligned(a, 16))
             return fail(err, err_cap, "identical gemm: the skinny plan needs op NT, m <= 32, k a multiple of 16 and 16-byte aligned operands");
         // low-bit weights stay in registers; float32 windows are too wide for that and go through shared memory
-        if (B200I_SK_REG && g.wkind != W_F32) launch_skinny_reg(g, plan.groups, st);
+        g.cluster_fold = plan_kind != PLAN_SKINNY_NODES;
+        if (g.wkind != W_F32) folded = launch_skinny_reg(g, plan.groups, st);
         else launch_skinny(g, plan.groups, st);
         g_launches++;
     } else {
         return fail(err, err_cap, "identical gemm: unknown plan %d", plan.kind);
     }
     timing_end(tslot, st);
-    if (plan.groups > 1) {
+    if (plan.groups > 1 && !folded) {
         const long long cells = (long long)m * n;
-        launch_fold_groups(g.ws, c, cells, plan.groups, st);
+        launch_fold_groups(g.ws, c, cells, plan.groups, st, g.epi, g.n);
         g_launches++;
     }
     CUDA_TRY(cudaGetLastError());
@@ -597,78 +550,6 @@ int64_t b200i_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     return groups > 1 ? (int64_t)groups * m * n * 4 : 0;
 }
 
-int64_t b200i_packed_weight_bytes(int64_t n, int64_t k, int64_t wkind) {
-    if (n <= 0 || k <= 0 || k % KS != 0 || wkind < W_F32 || wkind > W_INT8_SCALE) return 0;
-    return (int64_t)skp_weight_layout(n, k, (int)wkind).total;
-}
-
-int64_t b200i_pack_weight(int64_t device, void *stream, void *packed, const void *w, const void *scale, int64_t wkind, int64_t n,
-                          int64_t k, char *err, int64_t err_cap) {
-    clear(err, err_cap);
-    int dev;
-    if (select_device(device, err, err_cap, &dev)) return 1;
-    if (n <= 0 || k <= 0 || !packed || !w || wkind < W_F32 || wkind > W_INT8_SCALE) return fail(err, err_cap, "pack_weight: bad arguments");
-    if (k % KS != 0 || k > 131072 || (k > K_LEAF_MIN && leaf_size(k) != K_LEAF_MIN))
-        return fail(err, err_cap, "pack_weight: k must be a multiple of 16 with 128-step leaves (got %lld)", (long long)k);
-    if ((wkind == W_INT8_EXP || wkind == W_INT8_SCALE) && !scale)
-        return fail(err, err_cap, "pack_weight: int8 weight storage needs its per-row exponents or scales");
-    if (!aligned(packed, 256)) return fail(err, err_cap, "pack_weight: the packed buffer must be 256-byte aligned");
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const SkpWeightLayout l = skp_weight_layout(n, k, (int)wkind);
-    dim3 grid((unsigned)(k / KS), (unsigned)l.tiles);
-    unsigned char *p = static_cast<unsigned char *>(packed);
-    if (wkind == W_F32) skinny_pack_w_kernel<W_F32><<<grid, SKP_BN, 0, st>>>(p, w, scale, (int)n, (int)k, l.factor_off, l.flag_off);
-    else if (wkind == W_BF16) skinny_pack_w_kernel<W_BF16><<<grid, SKP_BN, 0, st>>>(p, w, scale, (int)n, (int)k, l.factor_off, l.flag_off);
-    else if (wkind == W_INT8_EXP) skinny_pack_w_kernel<W_INT8_EXP><<<grid, SKP_BN, 0, st>>>(p, w, scale, (int)n, (int)k, l.factor_off, l.flag_off);
-    else skinny_pack_w_kernel<W_INT8_SCALE><<<grid, SKP_BN, 0, st>>>(p, w, scale, (int)n, (int)k, l.factor_off, l.flag_off);
-    g_launches++;
-    CUDA_TRY(cudaGetLastError());
-    return 0;
-}
-
-int64_t b200i_gemm_packed_w_workspace_bytes(int64_t m, int64_t n, int64_t k) {
-    if (m <= 0 || n <= 0 || k <= 0 || !skinny_packed_fits(m, n, k)) return 0;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = -1; }
-    return (int64_t)skp_call_bytes(m, n, k, choose_skinny_packed(n, k, sm_count(dev)).groups);
-}
-
-int64_t b200i_gemm_packed_w(int64_t device, void *stream, float *c, const float *a, const void *packed, int64_t wkind, int64_t m,
-                            int64_t n, int64_t k, void *ws, int64_t ws_bytes, char *err, int64_t err_cap) {
-    clear(err, err_cap);
-    int dev;
-    if (select_device(device, err, err_cap, &dev)) return 1;
-    if (m <= 0 || n <= 0 || k <= 0) return fail(err, err_cap, "identical gemm: m, n and k must be positive");
-    if (!c || !a || !packed || wkind < W_F32 || wkind > W_INT8_SCALE) return fail(err, err_cap, "identical gemm: bad arguments");
-    if (!skinny_packed_fits(m, n, k) || !aligned(a, 16) || !aligned(packed, 256))
-        return fail(err, err_cap, "identical gemm: the prepacked plan needs m <= 32, k a multiple of 16 with 128-step leaves and aligned operands");
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const Plan plan = choose_skinny_packed(n, k, sm_count(dev));
-    const size_t need = skp_call_bytes(m, n, k, plan.groups);
-    if (!ws || !aligned(ws, 256) || (size_t)ws_bytes < need)
-        return fail(err, err_cap, "identical gemm: a 256-byte aligned workspace of %lld bytes is needed, %lld given", (long long)need,
-                    (long long)ws_bytes);
-    unsigned char *w8 = static_cast<unsigned char *>(ws);
-    float *at = reinterpret_cast<float *>(w8);
-    unsigned char *aflags = w8 + round256((size_t)k * skp_bm(m) * 4);
-    float *nodes = reinterpret_cast<float *>(aflags + round256((size_t)(k / KS)));
-    const SkpWeightLayout l = skp_weight_layout(n, k, (int)wkind);
-    SkinnyPackedArgs g{at, aflags, static_cast<const unsigned char *>(packed), l.factor_off, l.flag_off, c, nodes,
-                       (int)m, (int)n, (int)k, (int)leaf_size(k), (int)leaf_count(k), plan.group_leaves, plan.groups};
-    if (wkind == W_F32) launch_skinny_packed_wk<W_F32>(g, at, aflags, a, st);
-    else if (wkind == W_BF16) launch_skinny_packed_wk<W_BF16>(g, at, aflags, a, st);
-    else if (wkind == W_INT8_EXP) launch_skinny_packed_wk<W_INT8_EXP>(g, at, aflags, a, st);
-    else launch_skinny_packed_wk<W_INT8_SCALE>(g, at, aflags, a, st);
-    g_launches += 2;
-    if (plan.groups > 1) {
-        const long long cells = (long long)m * n;
-        launch_fold_groups(nodes, c, cells, plan.groups, st);
-        g_launches++;
-    }
-    CUDA_TRY(cudaGetLastError());
-    return 0;
-}
-
 int64_t b200i_kernel_timing(int64_t enable) {
     std::lock_guard<std::mutex> lock(g_timing_mu);
     g_timing.on = enable != 0;
@@ -724,6 +605,18 @@ int64_t b200i_gemm_w(int64_t device, void *stream, float *c, const float *a, con
 int64_t b200i_gemm_f32(int64_t device, void *stream, float *c, const float *a, const float *b, int64_t m, int64_t n,
                        int64_t k, int64_t op, void *ws, int64_t ws_bytes, char *err, int64_t err_cap) {
     return b200i_gemm_w_plan(device, stream, c, a, b, nullptr, W_F32, m, n, k, op, PLAN_AUTO, 0, ws, ws_bytes, err, err_cap);
+}
+
+int64_t b200i_gemm_w_epilogue(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale, int64_t wkind,
+                              int64_t m, int64_t n, int64_t k, int64_t op, const float *bias, int64_t act, int64_t plan,
+                              int64_t group_leaves, void *ws, int64_t ws_bytes, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    if (act < EPI_ACT_NONE || act > EPI_ACT_SILU) return fail(err, err_cap, "identical gemm: unknown store activation %lld", (long long)act);
+    if (bias && !aligned(bias, 4)) return fail(err, err_cap, "identical gemm: misaligned storage");
+    return launch_product(dev, static_cast<cudaStream_t>(stream), c, a, b, bscale, (int)wkind, m, n, k, (int)op, (int)plan, group_leaves, ws,
+                          ws_bytes, err, err_cap, Epilogue{bias, (int)act});
 }
 
 
@@ -1204,6 +1097,140 @@ int64_t b200i_argmax(int64_t device, void *stream, int32_t *out, const float *lo
     return 0;
 }
 
+// ---- exchange of finished output columns between the GPUs of one node (see comm.cuh) ---------------
+
+namespace {
+struct Comm {
+    int dev = 0, rank = 0, world = 1;
+    size_t bytes = 0;          // the exchange buffer: the receive areas of every site
+    unsigned char *base = nullptr;
+    int *epoch = nullptr;      // this rank's epoch word
+    CommPeers peers{};
+    bool mapped[COMM_MAX_WORLD] = {};
+    bool local[COMM_MAX_WORLD] = {}; // attached by pointer inside this process (tests), not through an IPC handle
+};
+constexpr unsigned long long COMM_WAIT_NS = 4000000000ull; // a peer that has not delivered after 4 s is reported, not awaited
+} // namespace
+
+int64_t b200i_comm_create(int64_t device, int64_t rank, int64_t world, int64_t bytes, void **comm, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    if (!comm || world < 1 || world > COMM_MAX_WORLD || rank < 0 || rank >= world || bytes <= 0 || bytes % 16)
+        return fail(err, err_cap, "comm_create: bad arguments (1 <= world <= %d, bytes a positive multiple of 16)", COMM_MAX_WORLD);
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    Comm *c = new Comm();
+    c->dev = dev; c->rank = (int)rank; c->world = (int)world;
+    c->bytes = (size_t)bytes;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&c->base), c->bytes);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&c->epoch), 256);
+    if (e == cudaSuccess) e = cudaMemset(c->base, 0, c->bytes); // tag 0 everywhere: no epoch ever has it
+    if (e == cudaSuccess) e = cudaMemset(c->epoch, 0, 256);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        if (c->base) cudaFree(c->base);
+        if (c->epoch) cudaFree(c->epoch);
+        delete c;
+        return fail(err, err_cap, "comm_create: %s", cudaGetErrorString(e));
+    }
+    c->peers.base[rank] = c->base;
+    c->mapped[rank] = true;
+    *comm = c;
+    return 0;
+}
+
+int64_t b200i_comm_export(void *comm, void *handle, int64_t handle_bytes, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    Comm *c = static_cast<Comm *>(comm);
+    if (!c || !handle || handle_bytes < (int64_t)sizeof(cudaIpcMemHandle_t)) return fail(err, err_cap, "comm_export: the handle buffer must hold %d bytes", (int)sizeof(cudaIpcMemHandle_t));
+    CUDA_TRY(cudaSetDevice(c->dev));
+    cudaIpcMemHandle_t h;
+    CUDA_TRY(cudaIpcGetMemHandle(&h, c->base));
+    memcpy(handle, &h, sizeof(h));
+    return 0;
+}
+
+int64_t b200i_comm_attach(void *comm, int64_t peer, const void *handle, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    Comm *c = static_cast<Comm *>(comm);
+    if (!c || !handle || peer < 0 || peer >= c->world || peer == c->rank || c->mapped[peer]) return fail(err, err_cap, "comm_attach: bad peer %lld", (long long)peer);
+    CUDA_TRY(cudaSetDevice(c->dev));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void *p = nullptr;
+    CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    c->peers.base[peer] = static_cast<unsigned char *>(p);
+    c->mapped[peer] = true;
+    return 0;
+}
+
+int64_t b200i_comm_attach_local(void *comm, int64_t peer, void *other, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    Comm *c = static_cast<Comm *>(comm), *o = static_cast<Comm *>(other);
+    if (!c || !o || peer < 0 || peer >= c->world || peer == c->rank || c->mapped[peer] || o->rank != peer || o->world != c->world ||
+        o->bytes != c->bytes || o->dev != c->dev)
+        return fail(err, err_cap, "comm_attach_local: the other exchange must be rank %lld of the same world, size and device", (long long)peer);
+    c->peers.base[peer] = o->base;
+    c->mapped[peer] = c->local[peer] = true;
+    return 0;
+}
+
+int64_t b200i_comm_advance(void *comm, void *stream, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    Comm *c = static_cast<Comm *>(comm);
+    if (!c) return fail(err, err_cap, "comm_advance: no exchange");
+    CUDA_TRY(cudaSetDevice(c->dev));
+    comm_advance_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(c->epoch);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_comm_gather(void *comm, void *stream, int64_t mode, int64_t area_bytes, float *out, int64_t out_ld, const float *src,
+                          int64_t m, int64_t w, int64_t src_ld, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    Comm *c = static_cast<Comm *>(comm);
+    if (!c) return fail(err, err_cap, "comm_gather: no exchange");
+    if (mode < COMM_SEND_RECV || mode > COMM_RECV) return fail(err, err_cap, "comm_gather: bad mode");
+    for (int p = 0; p < c->world; p++)
+        if (!c->mapped[p]) return fail(err, err_cap, "comm_gather: rank %d's buffer is not attached", p);
+    if (!out || m <= 0 || w <= 0 || area_bytes < 0 || area_bytes % 16 || (mode != COMM_RECV && !src)) return fail(err, err_cap, "comm_gather: bad arguments");
+    if (src_ld == 0) src_ld = w;
+    if (out_ld == 0) out_ld = w * c->world;
+    if (src_ld < w || out_ld < w * c->world) return fail(err, err_cap, "comm_gather: a row pitch is below its row width");
+    if ((size_t)area_bytes + (size_t)m * (size_t)w * c->world * 8 > c->bytes)
+        return fail(err, err_cap, "comm_gather: the site's receive areas do not fit the exchange buffer");
+    CUDA_TRY(cudaSetDevice(c->dev));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool pair = w % 2 == 0 && src_ld % 2 == 0 && out_ld % 2 == 0 && aligned(out, 8) && (mode == COMM_RECV || aligned(src, 8));
+    const long long items = pair ? m * (w / 2) : m * w;
+    long long blocks = (items + COMM_THREADS - 1) / COMM_THREADS;
+    const long long cap = 2ll * sm_count(c->dev);
+    const unsigned grid = (unsigned)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+    if (pair)
+        comm_gather_kernel<true><<<grid, COMM_THREADS, 0, st>>>(c->peers, c->epoch, src, src_ld, out, out_ld, area_bytes, (int)m, (int)w, c->world,
+                                                                c->rank, (int)mode, COMM_WAIT_NS);
+    else
+        comm_gather_kernel<false><<<grid, COMM_THREADS, 0, st>>>(c->peers, c->epoch, src, src_ld, out, out_ld, area_bytes, (int)m, (int)w, c->world,
+                                                                 c->rank, (int)mode, COMM_WAIT_NS);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_comm_destroy(void *comm) {
+    Comm *c = static_cast<Comm *>(comm);
+    if (!c) return 0;
+    cudaSetDevice(c->dev);
+    cudaDeviceSynchronize();
+    for (int p = 0; p < c->world; p++)
+        if (p != c->rank && c->mapped[p] && !c->local[p]) cudaIpcCloseMemHandle(c->peers.base[p]);
+    cudaFree(c->base);
+    cudaFree(c->epoch);
+    cudaGetLastError();
+    delete c;
+    return 0;
+}
+
 // ---- host-pointer twins -------------------------------------------------------------------
 
 // The host-pointer product, pipelined over three streams (PCIe is full duplex): host-to-device copies, packing and
@@ -1284,7 +1311,8 @@ static int64_t host_gemm_pipelined(int dev, HostPool &pool, float *c, const floa
             unsigned char *fai = fa + (size_t)tile0 * leaves * wpl;
             PackArgs paargs{pai, fai, dai, nullptr, (int)cnt, (int)k, leaf, leaves, wpl, 1, k8};
             launch_pack<W_F32>(paargs, pool.stream);
-            PackedGemmArgs p{pai, pb, fai, fb, dci, nullptr, (int)cnt, (int)n, (int)k, leaf, leaves, wpl, leaves, 1, tiles_n, (n % 4 == 0) ? 1 : 0};
+            PackedGemmArgs p{pai, pb, fai, fb, dci, nullptr, (int)cnt, (int)n, (int)k, leaf, leaves, wpl, leaves, 1, tiles_n, (n % 4 == 0) ? 1 : 0,
+                             Epilogue{nullptr, EPI_ACT_NONE}};
             dim3 grid((unsigned)(((cnt + PK_TILE - 1) / PK_TILE) * tiles_n), 1u);
             gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, pool.stream>>>(p);
             CUDA_TRY(cudaEventRecord(pool.ev[2 + 2 * i], pool.stream));
@@ -1307,7 +1335,7 @@ static int64_t host_gemm_pipelined(int dev, HostPool &pool, float *c, const floa
             launch_pack_b(pbargs, wkind, pool.stream);
             const int tiles_nc = (int)((cnt + PK_TILE - 1) / PK_TILE);
             PackedGemmArgs p{pa, pbi, fa, fbi, dci, nullptr, (int)m, (int)cnt, (int)k, leaf, leaves, wpl, leaves, 1, tiles_nc,
-                             (cnt % 4 == 0 && (m * x0) % 4 == 0) ? 1 : 0};
+                             (cnt % 4 == 0 && (m * x0) % 4 == 0) ? 1 : 0, Epilogue{nullptr, EPI_ACT_NONE}};
             dim3 grid((unsigned)(tiles_m * tiles_nc), 1u);
             gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, pool.stream>>>(p);
             CUDA_TRY(cudaEventRecord(pool.ev[2 + 2 * i], pool.stream));

@@ -22,6 +22,7 @@
 // tree evaluated in streaming order.
 #pragma once
 #include "seams.cuh"
+#include "seams_math.cuh"
 
 namespace b200i {
 
@@ -37,6 +38,8 @@ struct GemmArgs {
     int vec_a, vec_b, vec_c;  // operand may be read / written with 128-bit accesses
     int tiles_n;
     int dec_smem_limit;       // decode plan: shared memory a CTA may use (decides one or two CTAs per SM)
+    Epilogue epi;             // bias / activation applied where the product's output is stored
+    int cluster_fold;         // register skinny plan: the leaf groups of a tile are one thread-block cluster and fold there
 };
 
 constexpr int KS = 16;       // k-steps per staged window
@@ -259,16 +262,6 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
     auto step_fast = [&](int buf, int kk) {
         float av[TM], bv[TN];
         read_operands(buf, kk, av, bv);
-#ifdef B200I_SCALAR_FMA
-#pragma unroll
-        for (int i = 0; i < TM; i++)
-#pragma unroll
-            for (int j = 0; j < TN / 2; j++) {
-                float lo, hi;
-                unpack2(acc[i][j], lo, hi);
-                acc[i][j] = pack2(step_bare(av[i], bv[2 * j], lo), step_bare(av[i], bv[2 * j + 1], hi));
-            }
-#else
         unsigned long long b2[TN / 2];
 #pragma unroll
         for (int j = 0; j < TN / 2; j++) b2[j] = pack2(bv[2 * j], bv[2 * j + 1]);
@@ -278,7 +271,6 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
 #pragma unroll
             for (int j = 0; j < TN / 2; j++) acc[i][j] = fma2_bare(a2, b2[j], acc[i][j]);
         }
-#endif
     };
     auto step_slow = [&](int buf, int kk) {
         float av[TM], bv[TN];
@@ -400,8 +392,9 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
         for (int jr = 0; jr < RN; jr++) {
             float vals[4];
 #pragma unroll
-            for (int e = 0; e < 4; e++) vals[e] = nan_canon(ftz_hw(v[i * TN + jr * 4 + e]));
             const int col = bn0 + jr * (BN / RN) + tx * 4;
+#pragma unroll
+            for (int e = 0; e < 4; e++) vals[e] = finish_cell(v[i * TN + jr * 4 + e], g.epi, col + e < g.n ? col + e : 0, g.groups == 1);
             if (row < g.m) {
                 float *dst = out + (size_t)row * (size_t)g.n + col;
                 if (g.vec_c && col + 3 < g.n) *reinterpret_cast<float4 *>(dst) = make_float4(vals[0], vals[1], vals[2], vals[3]);
@@ -423,7 +416,7 @@ constexpr int MAX_GROUPS = 64;
 constexpr int GROUP_LEVELS = 6; // 2^6 = MAX_GROUPS
 template <int VEC>
 __global__ void __launch_bounds__(256) fold_groups_kernel(const float *__restrict__ ws, float *__restrict__ c, long long cells,
-                                                          int groups) {
+                                                          int groups, Epilogue epi, int n) {
     const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (idx >= cells) return;
     float stack[GROUP_LEVELS][VEC];
@@ -461,17 +454,20 @@ __global__ void __launch_bounds__(256) fold_groups_kernel(const float *__restric
 #pragma unroll
             for (int e = 0; e < VEC; e++) v[e] = fold_add(stack[lvl][e], v[e]);
         }
+    const bool epi_on = epilogue_on(epi);
+#pragma unroll
+    for (int e = 0; e < VEC; e++) v[e] = finish_cell(v[e], epi, epi_on ? (idx + e) % n : 0, true);
     if (VEC == 4) {
-        *reinterpret_cast<float4 *>(c + idx) = make_float4(nan_canon(ftz_hw(v[0])), nan_canon(ftz_hw(v[1 % VEC])),
-                                                           nan_canon(ftz_hw(v[2 % VEC])), nan_canon(ftz_hw(v[3 % VEC])));
+        *reinterpret_cast<float4 *>(c + idx) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
     } else {
-        c[idx] = nan_canon(ftz_hw(v[0]));
+        c[idx] = v[0];
     }
 }
-inline void launch_fold_groups(const float *ws, float *c, long long cells, int groups, cudaStream_t st) {
+inline void launch_fold_groups(const float *ws, float *c, long long cells, int groups, cudaStream_t st, Epilogue epi = Epilogue{nullptr, 0},
+                               int n = 1) {
     const bool vec = cells % 4 == 0 && ((reinterpret_cast<uintptr_t>(ws) | reinterpret_cast<uintptr_t>(c)) & 15u) == 0;
-    if (vec) fold_groups_kernel<4><<<(unsigned)((cells / 4 + 255) / 256), 256, 0, st>>>(ws, c, cells, groups);
-    else fold_groups_kernel<1><<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(ws, c, cells, groups);
+    if (vec) fold_groups_kernel<4><<<(unsigned)((cells / 4 + 255) / 256), 256, 0, st>>>(ws, c, cells, groups, epi, n);
+    else fold_groups_kernel<1><<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(ws, c, cells, groups, epi, n);
 }
 
 // One thread per cell, whole product serial: the on-device restatement of the
@@ -510,7 +506,7 @@ __global__ void gemm_flat_kernel(const GemmArgs g) {
             v = have ? fold_add(stack[lvl], v) : stack[lvl];
             have = true;
         }
-    g.c[idx] = nan_canon(ftz_hw(v));
+    g.c[idx] = finish_cell(v, g.epi, j, true);
 }
 
 } // namespace b200i

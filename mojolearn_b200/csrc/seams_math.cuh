@@ -268,4 +268,30 @@ __device__ __forceinline__ float order_unkey(unsigned k) {
     return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
 }
 
+// ---- store epilogues of the product -------------------------------------------------------------
+// The reference's GEMM_EPI_PLUS_BIAS and GEMM_EPI_BIAS_ACT (gemm/checks/gemm_identical.mojo:8869-8912, :9483-9491):
+// the finished product word, then one plain add of the column's bias (transformer_oracle.mojo:1344-1372), then the
+// activation of an ungated MLP (S20 and the GELU variants), each with the flush the separate seams apply. The words
+// are those of the product followed by b200i_bias_add and b200i_act_mul; only the launches are saved. `c` is the
+// product's stored word (root flushed, NaN canonical).
+struct Epilogue {
+    const float *bias; // one word per output column, or NULL
+    int act;           // EPI_ACT_*
+};
+enum { EPI_ACT_NONE = 0, EPI_ACT_GELU_ERF = 1, EPI_ACT_GELU_TANH = 2, EPI_ACT_SILU = 3 };
+__device__ __forceinline__ bool epilogue_on(const Epilogue &e) { return e.bias != nullptr || e.act != EPI_ACT_NONE; }
+__device__ __noinline__ float epilogue_apply(float c, const float *bias, int act, long long col) {
+    if (bias) c = ftz_bits(__fadd_rn(ftz_bits(c), ftz_bits(__ldg(bias + col))));
+    if (act == EPI_ACT_GELU_ERF) c = ftz_bits(p_gelu_erf(ftz_bits(c)));
+    else if (act == EPI_ACT_GELU_TANH) c = ftz_bits(p_gelu_tanh(ftz_bits(c)));
+    else if (act == EPI_ACT_SILU) c = ftz_bits(p_siluf(ftz_bits(c)));
+    return c;
+}
+// the word a product stores for a cell whose tree root is `root`; `last` = this store is the product's output
+// (not a leaf-group node that a later fold finishes)
+__device__ __forceinline__ float finish_cell(float root, const Epilogue &e, long long col, bool last) {
+    const float c = nan_canon(ftz_hw(root));
+    return (last && epilogue_on(e)) ? epilogue_apply(c, e.bias, e.act, col) : c;
+}
+
 } // namespace b200i

@@ -21,13 +21,15 @@ their rows [r*N/g, (r+1)*N/g) and the full activation is rebuilt by an NCCL
 all-gather. A cell reads one weight row and all of k, so the shard moves no bit:
 the logits equal the single-GPU logits word for word.
 """
+import copy
 import ctypes
+import os
 
 import numpy as np
 import torch
 
 from .. import _native
-from ..parallel import gather_columns, shard_bounds
+from ..parallel import PeerExchange, exchange_heads, gather_columns, shard_bounds
 from ..transformer import Linear, ShardedLinear, TransformerBlock, TransformerState, _stream, _vector, _vp, add, add_norm, norm, NORM_KINDS
 
 
@@ -58,7 +60,17 @@ class CausalLMState(object):
 
 
 class CausalLM(object):
-    def __init__(self, config, weights, *, device=None, group=None):
+    #: rows (batch x new tokens) up to which a sharded model's gathers go through the peer exchange
+    EXCHANGE_ROWS = 64
+
+    def __init__(self, config, weights, *, device=None, group=None, exchange=None, prefill_by_batch=True, emulate_world=0):
+        """`group`: a torch.distributed group of one process per GPU; the model is then cut by output columns
+        (see the module text). `exchange`: True / False forces or forbids the store-side peer exchange for the
+        decode-step gathers (default: on, unless MOJOLEARN_B200_EXCHANGE=0). `prefill_by_batch`: a prompt on a
+        fresh state is cut by SEQUENCES instead (each rank runs its share of the batch through the whole model,
+        then the KV caches are re-cut to the decode layout by one all-to-all): the other bit-neutral axis.
+        `emulate_world` (timing only): build rank 0's share of a model cut over that many ranks, with no process
+        group and `parallel.LoopbackExchange` in place of the exchange; the outputs are then not the model's."""
         _native.require_device()
         self.config = cfg = config
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -79,7 +91,20 @@ class CausalLM(object):
         self.pos_table = None
         if cfg.positions == "learned":
             self.pos_table = _vector(get("embed_positions.weight"), "embed_positions.weight", self.device)
-        self.blocks = []
+        self.blocks, self.full_blocks = [], []
+        self.exchange = None
+        if emulate_world and emulate_world > 1 and group is None:
+            from ..parallel import LoopbackExchange
+            self.world, self.exchange, prefill_by_batch = int(emulate_world), LoopbackExchange(emulate_world), False
+        self.prefill_by_batch = bool(prefill_by_batch) and self.world > 1
+        if self.world > 1 and self.exchange is None:
+            want = exchange if exchange is not None else os.environ.get("MOJOLEARN_B200_EXCHANGE", "1") != "0"
+            if want:
+                rows = self.EXCHANGE_ROWS
+                hd = cfg.head_dim
+                per_block = rows * (cfg.n_heads * hd + 2 * cfg.d_model + cfg.intermediate) + 4 * 64  # words of a block's four gathers
+                self.exchange = PeerExchange(group, self.device, rows, max(cfg.vocab, cfg.intermediate, cfg.d_model, cfg.n_heads * hd),
+                                             cfg.n_layers * per_block + rows * cfg.vocab + 64)
         for i in range(cfg.n_layers):
             bw = {}
             for key, val in weights.items():
@@ -90,7 +115,10 @@ class CausalLM(object):
                                    rope=cfg.positions == "rope", rope_theta=cfg.rope_theta, qkv_bias=cfg.qkv_bias,
                                    o_bias=cfg.o_bias, norm=cfg.norm, norm_eps=cfg.norm_eps, norm_bias=cfg.norm_bias, mlp=cfg.mlp,
                                    mlp_bias=cfg.mlp_bias, device=self.device)
-            blk.shard(group, self.rank, self.world)
+            self.full_blocks.append(blk)
+            if self.world > 1:
+                blk = copy.copy(blk)  # the shards are row views of the same weights; only the fused q|k|v and gate|up shards are copies
+                blk.shard(group, self.rank, self.world, self.exchange)
             self.blocks.append(blk)
         self.final_w = _vector(get("norm.weight"), "norm.weight", self.device)
         self.final_b = _vector(get("norm.bias"), "norm.bias", self.device) if cfg.norm_bias else None
@@ -98,8 +126,9 @@ class CausalLM(object):
         self.head = Linear(head if head is not None else self.embed, self.device)
         if self.head.out_features != cfg.vocab:
             raise ValueError("lm_head.weight must have %d rows" % cfg.vocab)
+        self.full_head = self.head
         if self.world > 1:
-            self.head = ShardedLinear(self.head, group, self.rank, self.world)
+            self.head = ShardedLinear(self.head, group, self.rank, self.world, self.exchange)
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     def allocate_state(self, batch_size, max_tokens):
@@ -117,9 +146,12 @@ class CausalLM(object):
             raise ValueError("token ids must be (batch, length)")
         return t.contiguous()
 
-    def hidden_device(self, ids, state, position=None):
+    def hidden_device(self, ids, state, position=None, blocks=None):
         """Final-normed hidden states [B*L, d_model] for the ids, advancing the state. `position`: see
-        TransformerBlock.forward_device."""
+        TransformerBlock.forward_device. `blocks`: the unsharded blocks, for a prompt cut by sequences."""
+        blocks = self.blocks if blocks is None else blocks
+        if self.exchange is not None and blocks is self.blocks:
+            self.exchange.begin_step()
         b, l = ids.shape
         dev, st, cfg = self.device, _stream(self.device), self.config
         if state.positions + l > cfg.max_positions:
@@ -138,9 +170,9 @@ class CausalLM(object):
                              cfg.d_model)
         h, delta = x.reshape(b, l, cfg.d_model), None
         rope = None  # one rotary table per call: every block is at the same positions
-        if self.blocks and self.blocks[0].rope:
-            rope = self.blocks[0].rope_tables(state.positions, l, position)
-        for blk, bs in zip(self.blocks, state.layers):
+        if blocks and blocks[0].rope:
+            rope = blocks[0].rope_tables(state.positions, l, position)
+        for blk, bs in zip(blocks, state.layers):
             h, delta = blk.forward_device(h, bs, position, rope, delta, defer_add=True)  # each block's last add rides in the next norm
         h2 = h.reshape(b * l, cfg.d_model)
         if delta is None:
@@ -158,11 +190,40 @@ class CausalLM(object):
         from .. import torch_ops
         torch_ops.check_status(self.device)
 
+    def _prefill_by_batch(self, ids, state, last_only):
+        """A prompt on a fresh state, cut by sequences: this rank runs rows [r*B/g, (r+1)*B/g) through the WHOLE model
+        (a sequence's bits do not depend on its batch), the logits are all-gathered in rank = batch order, and every
+        layer's keys and values move to the decode layout (this rank's heads of every sequence) by one all-to-all."""
+        import torch.distributed as dist
+        b, l = ids.shape
+        bl, cfg = b // self.world, self.config
+        mine = ids[self.rank * bl:(self.rank + 1) * bl].contiguous()
+        local = CausalLMState([blk.allocate_state(bl, l) for blk in self.full_blocks], bl, l)
+        hn = self.hidden_device(mine, local, None, self.full_blocks)
+        if last_only:
+            hn = hn.reshape(bl, l, -1)[:, -1, :].contiguous()
+        part = self.full_head(hn)
+        logits = torch.empty((self.world * part.shape[0], cfg.vocab), dtype=torch.float32, device=self.device)
+        dist.all_gather_into_tensor(logits, part.contiguous(), group=self.group)
+        for src, dst, blk in zip(local.layers, state.layers, self.blocks):
+            for a, z in ((src.k, dst.k), (src.v, dst.v)):
+                if blk.kv_local != blk.n_kv_heads:   # decode keeps this rank's heads of every sequence
+                    z[:, :, :l, :] = exchange_heads(a[:, :, :l, :], self.world, self.group)
+                else:                                # decode keeps every head (the block is cut by rows only)
+                    whole = torch.empty((b,) + tuple(a.shape[1:]), dtype=torch.float32, device=self.device)
+                    dist.all_gather_into_tensor(whole, a.contiguous(), group=self.group)
+                    z[:, :, :l, :] = whole[:, :, :l, :]
+            dst.cached_tokens = l
+            src.k = src.v = None
+        return logits if last_only else logits.reshape(b, l, cfg.vocab)
+
     def forward_device(self, ids, state=None, last_only=False, position=None):
         ids = self._ids(ids)
         b, l = ids.shape
         if state is None:
             state = self.allocate_state(b, l)
+        if self.prefill_by_batch and position is None and state.positions == 0 and l > 1 and b % self.world == 0 and b >= self.world:
+            return self._prefill_by_batch(ids, state, last_only)
         hn = self.hidden_device(ids, state, position)
         if last_only:
             hn = hn.reshape(b, l, -1)[:, -1, :].contiguous()
@@ -291,6 +352,10 @@ class DecodeSession(object):
                 self.graph_launches = int(_native.lib().b200i_launch_count() - counted)
                 for s, n in zip(self.state.layers, before):  # capturing launched nothing
                     s.cached_tokens = n
+                if self.lm.group is not None and self.lm.world > 1:  # capture takes the ranks different times: start the replays together
+                    import torch.distributed as dist
+                    torch.cuda.synchronize(self.lm.device)
+                    dist.barrier(self.lm.group)
             self.graph.replay()
             self.replays += 1
             for s in self.state.layers:

@@ -11,6 +11,8 @@ float32 words and performs no arithmetic. The reference's own multi-device rule
 is the same: byte copies only, never a collective that picks an order
 (training/byte_lm_parallel.py:2-8, core/multi_gpu.mojo:2-6).
 """
+import ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -24,8 +26,13 @@ def shard_bounds(n, rank, world):
     return rank * n // world, (rank + 1) * n // world
 
 
-def gather_columns(part, group=None):
-    """[m, n/g] column slices on every rank -> the full [m, n] on every rank (rank order = column order)."""
+def gather_columns(part, group=None, exchange=None):
+    """[m, n/g] column slices on every rank -> the full [m, n] on every rank (rank order = column order). With a
+    `PeerExchange` that takes the slice the ranks store their slices straight into each other's gathered matrix
+    (one small kernel, no layout copy); otherwise an all-gather of the process group and a rank-major to
+    column-major copy."""
+    if exchange is not None and exchange.takes(part):
+        return exchange.gather(part)
     world = dist.get_world_size(group)
     if world == 1:
         return part
@@ -34,3 +41,145 @@ def gather_columns(part, group=None):
     gathered = torch.empty((world * m, w), dtype=part.dtype, device=part.device)  # rank-major concatenation
     dist.all_gather_into_tensor(gathered, part, group=group)
     return gathered.view(world, m, w).permute(1, 0, 2).reshape(m, world * w).contiguous()
+
+
+class ExchangePlan(object):
+    """Where the receive areas of a step's gathers live in an exchange buffer (host arithmetic only).
+
+    A gather of [m, w] slices needs m * w * world pairs of 8 bytes in every rank's buffer. The first gather of a
+    step lives alone in [0, first_zone): the next step's first gather may be written by a fast rank while a slow
+    rank still reads this step's last area, so those two must never overlap; every later gather is bump-allocated
+    behind that zone and the cursor returns there at `begin_step()`. Every rank runs the same sequence of calls,
+    so every rank computes the same offsets."""
+
+    ALIGN = 256
+
+    def __init__(self, world, first_zone, total_bytes):
+        self.world, self.first_zone, self.total_bytes = int(world), int(first_zone), int(total_bytes)
+        self.site, self.cursor = 0, self.first_zone
+
+    def needs_closing_gather(self):
+        """True when the step so far has exactly one gather: the caller must add a second one (of anything) before the
+        next step begins, because only a later gather of the same step orders the reuse of the first one's area."""
+        return self.site == 1
+
+    def begin_step(self):
+        if self.site == 1:
+            raise RuntimeError("a step with a single gather cannot use the peer exchange (two gathers order the reuse of the areas)")
+        self.site, self.cursor = 0, self.first_zone
+
+    def size(self, m, w):
+        return (m * w * self.world * 8 + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+
+    def fits(self, m, w):
+        size = self.size(m, w)
+        return size <= self.first_zone if self.site == 0 else self.cursor + size <= self.total_bytes
+
+    def place(self, m, w):
+        """(index of the gather in its step, byte offset of its receive areas), advancing the plan."""
+        if not self.fits(m, w):
+            raise ValueError("the gather's receive areas do not fit the exchange")
+        site, offset = self.site, (0 if self.site == 0 else self.cursor)
+        if site > 0:
+            self.cursor += self.size(m, w)
+        self.site += 1
+        return site, offset
+
+
+class PeerExchange(object):
+    """This rank's end of the store-side exchange of the CUDA library (`b200i_comm_*`): a buffer every rank of the
+    node maps, into which the owners of column slices store their words. One object per model; `begin_step()` at
+    the start of every model step, then `gather()` in the same order on every rank. A slice it cannot take (more
+    rows than it was sized for, or the step's areas are used up) goes through the process group instead, which is
+    always correct."""
+
+    def __init__(self, group, device, max_rows, max_width, step_words):
+        """`max_width`: the widest gathered matrix of a step's FIRST gather; `step_words`: float32 words of all the
+        other gathered matrices of one step at `max_rows` rows."""
+        from . import _native
+        self.group, self.device = group, torch.device(device)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.max_rows = int(max_rows)
+        first_zone = (self.max_rows * int(max_width) * 8 + 255) // 256 * 256
+        self.total_bytes = first_zone + (int(step_words) * 8 + 255) // 256 * 256
+        self.plan = ExchangePlan(self.world, first_zone, self.total_bytes)
+        self._native = _native
+        comm = ctypes.c_void_p()
+        _native.call("b200i_comm_create", self.device.index, self.rank, self.world, self.total_bytes, ctypes.byref(comm))
+        self.comm = comm
+        handle = ctypes.create_string_buffer(64)
+        _native.call("b200i_comm_export", comm, ctypes.cast(handle, ctypes.c_void_p), 64)
+        mine = torch.tensor(list(handle.raw), dtype=torch.uint8, device=self.device)
+        everyone = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(everyone, mine, group=group)
+        for peer, h in enumerate(everyone):
+            if peer != self.rank:
+                raw = bytes(h.cpu().tolist())
+                _native.call("b200i_comm_attach", comm, peer, ctypes.cast(ctypes.create_string_buffer(raw, 64), ctypes.c_void_p))
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)  # every rank has zeroed its buffer and mapped every peer before anyone sends
+        self._token = None
+
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def begin_step(self):
+        if self.plan.needs_closing_gather():
+            # the step that just ended gathered once (a long prompt whose only small gather was the head's): give it a
+            # second, two-word gather so that the reuse of the first area stays ordered
+            if self._token is None:
+                self._token = torch.zeros((1, 2), dtype=torch.float32, device=self.device)
+            self.gather(self._token)
+        self.plan.begin_step()
+        self._native.call("b200i_comm_advance", self.comm, self._stream())
+
+    def takes(self, part):
+        if part.dim() != 2 or part.dtype != torch.float32 or part.stride(1) != 1 or part.shape[0] > self.max_rows:
+            return False
+        return self.plan.fits(part.shape[0], part.shape[1])
+
+    def gather(self, part, mode=0):
+        m, w = part.shape
+        _, offset = self.plan.place(m, w)
+        out = torch.empty((m, self.world * w), dtype=torch.float32, device=self.device)
+        self._native.call("b200i_comm_gather", self.comm, self._stream(), mode, offset, ctypes.c_void_p(out.data_ptr()), 0,
+                          ctypes.c_void_p(part.data_ptr()), m, w, part.stride(0))
+        return out
+
+    def close(self):
+        if self.comm is not None:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
+            self._native.lib().b200i_comm_destroy(self.comm)
+            self.comm = None
+
+
+class LoopbackExchange(object):
+    """A stand-in exchange for TIMING one rank's share of a sharded step on a single GPU, with no other rank: a
+    "gather" repeats the local slice `world` times, so every shape, launch and byte count is the real rank's but the
+    values are not the model's. Used by `serve_bench --emulate-world` to separate a sharded step's own kernels from
+    its communication; never by the model proper."""
+
+    def __init__(self, world):
+        self.world, self.rank = int(world), 0
+
+    def begin_step(self):
+        pass
+
+    def takes(self, part):
+        return True
+
+    def gather(self, part, mode=0):
+        return part.repeat(1, self.world)
+
+
+def exchange_heads(cache_rows, world, group=None):
+    """Re-cut KV caches from batch shards to head shards. `cache_rows` is this rank's [b/g, heads, length, head_dim]
+    (all heads of its own sequences); the result is [b, heads/g, length, head_dim] (this rank's heads of every
+    sequence, sequences in rank order). One all-to-all of finished words: a copy, no arithmetic."""
+    bl, heads, length, hd = cache_rows.shape
+    hl = heads // world
+    send = cache_rows.reshape(bl, world, hl, length, hd).permute(1, 0, 2, 3, 4).contiguous()  # [dest, b/g, heads/g, L, hd]
+    recv = torch.empty_like(send)                                                              # [src,  b/g, heads/g, L, hd]
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.reshape(world * bl, hl, length, hd)

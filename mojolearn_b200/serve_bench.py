@@ -18,7 +18,7 @@ import os
 import numpy as np
 import torch
 
-from . import _native
+from . import _native, _prof
 from .models import CausalLM, CausalLMConfig
 
 
@@ -65,8 +65,12 @@ def build_ids(cfg, batch, prompt, device=None):
     return torch.randint(0, cfg.vocab, (batch, prompt), generator=gen, device=dev, dtype=torch.int32)
 
 
-def run(args):
+def run(args, solo=False):
+    """One serving run. `solo`: ignore the process group and run the whole model on this rank's GPU alone (the
+    single-GPU figure a sharded run is compared with)."""
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if solo:
+        rank, world = 0, 1
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -79,8 +83,14 @@ def run(args):
         group = dist.group.WORLD
     cfg = CausalLMConfig(vocab=args.vocab, d_model=args.d_model, n_layers=args.layers, n_heads=args.heads,
                          intermediate=args.mlp, max_positions=8192)
-    lm = CausalLM(cfg, build_weights(cfg, args.format), device=dev, group=group)
+    emulate = int(getattr(args, "emulate_world", 0) or 0) if world == 1 else 0
+    lm = CausalLM(cfg, build_weights(cfg, args.format), device=dev, group=group, emulate_world=emulate,
+                  prefill_by_batch=os.environ.get("MOJOLEARN_B200_PREFILL", "batch") != "columns")
     ids = build_ids(cfg, args.batch, args.prompt, dev)
+    # warm-up, untimed: a short prompt and three steps load every kernel, open the collectives' connections and
+    # the peer exchange, and capture a decode graph once
+    lm.generate(ids[:, :min(16, args.prompt)].contiguous(), 3, graph=not args.no_graph)
+    torch.cuda.synchronize(dev)
     state = lm.allocate_state(args.batch, args.prompt + args.decode)
     launches0 = _native.lib().b200i_launch_count()
     e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
@@ -95,11 +105,17 @@ def run(args):
             if world > 1:
                 torch.distributed.barrier()
             torch.cuda.synchronize(dev)
+            if getattr(args, "breakdown", False):
+                _prof.enable(True)
             e[2].record()
         toks.append(session.next_ids().clone())
         logits = session.step()
     e[3].record()
     torch.cuda.synchronize(dev)
+    breakdown = None
+    if getattr(args, "breakdown", False):
+        breakdown = {k: {"us_per_step": v["us"] / timed, "spans_per_step": v["spans"] / timed} for k, v in sorted(_prof.report().items())}
+        _prof.enable(False)
     t = torch.tensor([e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])], device=dev, dtype=torch.float64)
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
@@ -112,12 +128,18 @@ def run(args):
            "config": {"layers": args.layers, "d_model": args.d_model, "heads": args.heads, "mlp": args.mlp, "vocab": args.vocab,
                       "batch": args.batch, "prompt": args.prompt, "decode": args.decode, "weights": args.format,
                       "decode_step": "launch by launch" if args.no_graph else "CUDA graph replay",
-                      "sharding": "output columns over %d ranks, NCCL all-gather" % world if world > 1 else "none"},
+                      "sharding": ("output columns over %d ranks" % world if world > 1 else
+                                   ("rank 0's share of %d ranks on one GPU, loopback gathers: TIMING ONLY, not the model's outputs" % emulate
+                                    if emulate else "none")),
+                      "gathers": ("peer stores" if lm.exchange is not None else "NCCL all-gather") if world > 1 else "none",
+                      "prefill": ("cut by sequences, KV re-cut by one all-to-all" if lm.prefill_by_batch else "cut by output columns") if world > 1 else "one GPU"},
            "ids_sha256": hashlib.sha256(seq.tobytes()).hexdigest()[:16],
            "logits_sha256": hashlib.sha256(logits.cpu().numpy().tobytes()).hexdigest()[:16],
            # the library counts a captured launch once, at capture, when nothing runs; replays are counted here
            "gpu_launches": int(_native.lib().b200i_launch_count() - launches0 + (session.replays - 1) * session.graph_launches
                                if session.replays else _native.lib().b200i_launch_count() - launches0)}
+    if breakdown is not None:
+        out["breakdown_rank0"] = breakdown
     return out, rank
 
 
@@ -134,6 +156,10 @@ def main():
     ap.add_argument("--timed-steps", type=int, default=32)
     ap.add_argument("--format", default="int8", choices=["int8", "bfloat16", "float32"])
     ap.add_argument("--no-graph", action="store_true", help="launch every decode step kernel by kernel")
+    ap.add_argument("--emulate-world", type=int, default=0,
+                    help="one process, one GPU: time rank 0's share of a model cut over this many ranks (loopback gathers)")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="with --no-graph: CUDA event pairs around each class of work of the timed steps (rank 0's are printed)")
     args = ap.parse_args()
     out, rank = run(args)
     if rank == 0:

@@ -20,6 +20,7 @@ from . import _native
 from .linalg import OP_NN, OP_NT, OP_TN, W_BF16, W_F32, W_INT8_EXP, W_INT8_SCALE, leaf_count
 
 PLAN_AUTO, PLAN_FLAT, PLAN_T128, PLAN_T64, PLAN_DECODE, PLAN_T32, PLAN_T128X64, PLAN_SKINNY, PLAN_PACKED = -1, 0, 1, 2, 3, 4, 5, 6, 7
+PLAN_SKINNY_NODES = 8  # the skinny plan with global leaf-group nodes and a separate fold, never folded in clusters
 
 
 def _check(t, name, dtype):
@@ -55,9 +56,14 @@ def check_status(device=None):
 _W_DTYPES = {W_F32: torch.float32, W_BF16: torch.uint16, W_INT8_EXP: torch.int8, W_INT8_SCALE: torch.int8}
 
 
-def product(a, b, bscale=None, wkind=W_F32, op=OP_NN, out=None, plan=PLAN_AUTO, group_leaves=0):
+ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3
+
+
+def product(a, b, bscale=None, wkind=W_F32, op=OP_NN, out=None, plan=PLAN_AUTO, group_leaves=0, bias=None, act=ACT_NONE):
     """C = op(a) . op(b) with b in weight storage `wkind`. `plan` forces an
-    execution plan (tests); every plan gives the same bits."""
+    execution plan (tests); every plan gives the same bits. `bias` (one float32 per
+    output column) and `act` are applied where the product stores its output: the
+    words of the product followed by the separate bias and activation seams."""
     _check(a, "a", torch.float32)
     wdtype = _W_DTYPES[wkind]
     if wkind == W_BF16 and b.dtype in (torch.int16, torch.bfloat16):
@@ -92,42 +98,16 @@ def product(a, b, bscale=None, wkind=W_F32, op=OP_NN, out=None, plan=PLAN_AUTO, 
     with torch.cuda.device(dev):
         ws_bytes = int(lib.b200i_plan_workspace_bytes(m, n, k, plan, group_leaves))
         ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=dev) if ws_bytes else None
-        _native.call("b200i_gemm_w_plan", dev.index, _stream(dev), _vp(out), _vp(a), _vp(b), _vp(bscale), wkind, m, n, k,
-                     op, plan, group_leaves, _vp(ws), ws_bytes)
-    return out
-
-
-def pack_weight(w, scale=None, wkind=W_F32):
-    """A static weight [n, k] laid out once for the decode-step product: a uint8 tensor holding the panels, the
-    per-column factors and the admission flags. None when the shape is outside the prepacked plan."""
-    wdtype = _W_DTYPES[wkind]
-    if wkind == W_BF16 and w.dtype in (torch.int16, torch.bfloat16):
-        w = w.view(torch.uint16)
-    _check(w, "w", wdtype)
-    n, k = w.shape
-    lib = _native.lib()
-    nbytes = int(lib.b200i_packed_weight_bytes(n, k, wkind))
-    if nbytes == 0:
-        return None
-    dev = w.device
-    packed = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev):
-        _native.call("b200i_pack_weight", dev.index, _stream(dev), _vp(packed), _vp(w), _vp(scale), wkind, n, k)
-    return packed
-
-
-def product_packed(a, packed, wkind, n, out=None):
-    """a [m, k] (m <= 32) times the prepacked weight [n, k]: the bits of product(a, w, ..., OP_NT)."""
-    _check(a, "a", torch.float32)
-    m, k = a.shape
-    dev = a.device
-    if out is None:
-        out = torch.empty((m, n), dtype=torch.float32, device=dev)
-    lib = _native.lib()
-    with torch.cuda.device(dev):
-        ws_bytes = int(lib.b200i_gemm_packed_w_workspace_bytes(m, n, k))
-        ws = torch.empty((max(ws_bytes, 256),), dtype=torch.uint8, device=dev)
-        _native.call("b200i_gemm_packed_w", dev.index, _stream(dev), _vp(out), _vp(a), _vp(packed), wkind, m, n, k, _vp(ws), ws_bytes)
+        if bias is None and act == ACT_NONE:
+            _native.call("b200i_gemm_w_plan", dev.index, _stream(dev), _vp(out), _vp(a), _vp(b), _vp(bscale), wkind, m, n, k,
+                         op, plan, group_leaves, _vp(ws), ws_bytes)
+        else:
+            if bias is not None:
+                _check(bias, "bias", torch.float32)
+                if bias.shape != (n,):
+                    raise ValueError("one bias word per output column")
+            _native.call("b200i_gemm_w_epilogue", dev.index, _stream(dev), _vp(out), _vp(a), _vp(b), _vp(bscale), wkind, m, n, k,
+                         op, _vp(bias), act, plan, group_leaves, _vp(ws), ws_bytes)
     return out
 
 

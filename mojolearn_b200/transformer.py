@@ -20,7 +20,7 @@ import ctypes
 import numpy as np
 import torch
 
-from . import _native, lowbit
+from . import _native, _prof, lowbit
 from .linalg import OP_NT, W_BF16, W_F32, W_INT8_EXP, W_INT8_SCALE
 from . import torch_ops
 from .parallel import gather_columns, shard_bounds
@@ -110,44 +110,29 @@ class Linear(object):
         part.scale = self.scale[lo:hi].contiguous() if self.scale is not None else None
         part.bias = self.bias[lo:hi].contiguous() if self.bias is not None else None
         part.out_features = hi - lo
-        part.__dict__.pop("_packed", None)
         return part
 
-    # Calls of up to this many rows go through a weight prepacked on first use (0 = never). Off by default: on B200 the
-    # prepacked plan measures within a few percent of the skinny plan on the decode shapes, and it keeps a second copy
-    # of the weight.
-    PREPACK_ROWS = 0
-
-    def packed_weight(self):
-        """The weight laid out for the decode-step product, built on first use (a second copy of the weight
-        in its storage type); None when the shape is outside that plan."""
-        if not hasattr(self, "_packed"):
-            self._packed = torch_ops.pack_weight(self.w, self.scale, self.kind)
-        return self._packed
-
-    def __call__(self, x2d):
-        packed = self.packed_weight() if 0 < x2d.shape[0] <= self.PREPACK_ROWS else None
-        if packed is not None:
-            y = torch_ops.product_packed(x2d.contiguous(), packed, self.kind, self.out_features)
-        else:
-            y = torch_ops.product(x2d, self.w, self.scale, self.kind, OP_NT)
-        if self.bias is not None:
-            dev = y.device
-            _native.call("b200i_bias_add", dev.index, _stream(dev), _vp(y), _vp(self.bias), y.shape[0], y.shape[1])
-        return y
+    def __call__(self, x2d, act=0):
+        """x @ W^T (+ bias) (then the ungated activation `act` of torch_ops.ACT_*), the bias and the activation
+        applied where the product stores its output."""
+        with _prof.span("product"):
+            return torch_ops.product(x2d, self.w, self.scale, self.kind, OP_NT, bias=self.bias, act=act)
 
 
 class ShardedLinear(object):
     """Rows [r*N/g, (r+1)*N/g) of a layer on this rank; the call all-gathers the output columns."""
 
-    def __init__(self, full, group, rank, world):
+    def __init__(self, full, group, rank, world, exchange=None):
         n = full.out_features
         lo, hi = shard_bounds(n, rank, world)
         self.local = full.shard_rows(lo, hi)
         self.group, self.world, self.out_features, self.in_features = group, world, n, full.in_features
+        self.exchange = exchange
 
-    def __call__(self, x2d):
-        return gather_columns(self.local(x2d), self.group)  # pure data movement: no arithmetic order is introduced
+    def __call__(self, x2d, act=0):
+        part = self.local(x2d, act)
+        with _prof.span("gather"):
+            return gather_columns(part, self.group, self.exchange)  # pure data movement: no arithmetic order is introduced
 
 
 class TransformerState(object):
@@ -242,6 +227,11 @@ class TransformerDecodeSession(object):
 def norm(x2d, w, bias, eps, kind):
     out = torch.empty_like(x2d)
     dev = x2d.device
+    with _prof.span("norm"):
+        return _norm(out, x2d, w, bias, eps, kind, dev)
+
+
+def _norm(out, x2d, w, bias, eps, kind, dev):
     _native.call("b200i_norm", dev.index, _stream(dev), _vp(out), _vp(x2d), _vp(w), _vp(bias), x2d.shape[0], x2d.shape[1],
                  float(eps), kind)
     return out
@@ -251,8 +241,9 @@ def add_norm(x2d, delta, w, bias, eps, kind):
     """(x + delta, norm(x + delta)): the residual add and the norm that follows it, one pass over the rows."""
     out, total = torch.empty_like(x2d), torch.empty_like(x2d)
     dev = x2d.device
-    _native.call("b200i_add_norm", dev.index, _stream(dev), _vp(out), _vp(total), _vp(x2d), _vp(delta.contiguous()), _vp(w), _vp(bias),
-                 x2d.shape[0], x2d.shape[1], float(eps), kind)
+    with _prof.span("norm"):
+        _native.call("b200i_add_norm", dev.index, _stream(dev), _vp(out), _vp(total), _vp(x2d), _vp(delta.contiguous()), _vp(w), _vp(bias),
+                     x2d.shape[0], x2d.shape[1], float(eps), kind)
     return total, out
 
 
@@ -334,26 +325,28 @@ class TransformerBlock(object):
         if self.gateup is not None:
             self.gate = self.up = None
 
-        self.group = None                      # set by shard(): the process group this block is cut across
+        self.group, self.exchange, self.by_heads = None, None, False  # set by shard(): the process group this block is cut across, its peer exchange
         self.heads_local, self.kv_local, self.inter_local = self.n_heads, self.n_kv_heads, self.inter
 
     PROJECTIONS = ("qkv", "q", "k", "v", "o", "gateup", "gate", "up", "down")
 
-    def shard(self, group, rank, world):
+    def shard(self, group, rank, world, exchange=None):
         """Cut the block across `world` ranks along bit-neutral axes only. With the head counts divisible by the
         world, a rank keeps its heads' rows of q, k, v (so rotary, the KV cache and the whole attention are local
         to the rank: a head never reads another head), gathers the context columns, keeps its rows of o, of gate
         and of up (the activation is elementwise, so it is local too), gathers the activation columns, and keeps
         its rows of down. Four all-gathers of finished float32 words per block, no k is ever split. Otherwise
-        every projection is cut by output rows and gathered, and the seams between them run replicated."""
+        every projection is cut by output rows and gathered, and the seams between them run replicated.
+        `exchange` (a `parallel.PeerExchange`) carries the gathers of calls it can take; the rest use the group."""
         if world == 1:
             return
+        self.exchange = exchange
         by_heads = self.n_heads % world == 0 and self.n_kv_heads % world == 0 and self.inter % world == 0
         if not by_heads:
             for slot in self.PROJECTIONS:
                 full = getattr(self, slot)
                 if full is not None:
-                    setattr(self, slot, ShardedLinear(full, group, rank, world))
+                    setattr(self, slot, ShardedLinear(full, group, rank, world, exchange))
             return
         hd = self.head_dim
         self.heads_local, self.kv_local = self.n_heads // world, self.n_kv_heads // world
@@ -375,9 +368,9 @@ class TransformerBlock(object):
             self.up = self.up.shard_rows(i0, i1)
             if self.gate is not None:
                 self.gate = self.gate.shard_rows(i0, i1)
-        self.o = ShardedLinear(self.o, group, rank, world)
-        self.down = ShardedLinear(self.down, group, rank, world)
-        self.group = group
+        self.o = ShardedLinear(self.o, group, rank, world, exchange)
+        self.down = ShardedLinear(self.down, group, rank, world, exchange)
+        self.group, self.by_heads = group, True
 
     def allocate_state(self, batch, max_tokens, window=None):
         return TransformerState(batch, self.kv_local, int(max_tokens), self.head_dim, self.device,
@@ -442,8 +435,11 @@ class TransformerBlock(object):
         used = pos0 + l
         qr = torch.empty((m, self.heads_local * self.head_dim), dtype=torch.float32, device=dev)
         ctx = torch.empty((m, self.heads_local * self.head_dim), dtype=torch.float32, device=dev)
-        _native.call("b200i_qkv_rope_cache", dev.index, st, _vp(qr), _vp(state.k), _vp(state.v), _vp(q), _vp(k), _vp(v), ld,
-                     _vp(cosv), _vp(sinv), b, l, self.heads_local, self.kv_local, self.head_dim, cap, pos0, _vp(position))
+        with _prof.span("rope_cache"):
+            _native.call("b200i_qkv_rope_cache", dev.index, st, _vp(qr), _vp(state.k), _vp(state.v), _vp(q), _vp(k), _vp(v), ld,
+                         _vp(cosv), _vp(sinv), b, l, self.heads_local, self.kv_local, self.head_dim, cap, pos0, _vp(position))
+        att = _prof.span("attention")
+        att.__enter__()
         if position is None:
             s = used - (max(0, pos0 - (self.window - 1)) if self.window else 0)
             scores = torch.empty((b * self.heads_local * l * s,), dtype=torch.float32, device=dev)
@@ -454,20 +450,29 @@ class TransformerBlock(object):
             scores = torch.empty((b * self.heads_local * l * s,), dtype=torch.float32, device=dev)
             _native.call("b200i_attention_at", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
                          self.heads_local, self.kv_local, self.head_dim, cap, _vp(position), self.window)
+        att.__exit__()
         del scores
-        if self.group is not None:
-            ctx = gather_columns(ctx, self.group)  # heads are rank-major, so the gathered columns are in head order
+        if self.by_heads:
+            with _prof.span("gather"):
+                ctx = gather_columns(ctx, self.group, self.exchange)  # heads are rank-major, so the gathered columns are in head order
         r1, n2 = add_norm(x2, self.o(ctx), self.norm2_w, self.norm2_b, self.norm_eps, self.norm_kind)
-        if self.gateup is not None:
-            fused = self.gateup(n2)
-            gate, up, gld = fused[:, :self.inter_local], fused[:, self.inter_local:], fused.shape[1]
+        if not self.gated:
+            # an ungated MLP's activation is elementwise on the up projection: it rides in that product's store
+            # (mlp kinds 1, 2, 3 = gelu, gelu_tanh, silu are the store's activation codes)
+            act = self.up(n2, act=self.mlp_kind)
         else:
-            up, gld = self.up(n2), 0
-            gate = self.gate(n2) if self.gated else None
-        act = torch.empty((m, self.inter_local), dtype=torch.float32, device=dev)
-        _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(gate), _vp(up), m, self.inter_local, gld, self.mlp_kind)
-        if self.group is not None:
-            act = gather_columns(act, self.group)
+            if self.gateup is not None:
+                fused = self.gateup(n2)
+                gate, up, gld = fused[:, :self.inter_local], fused[:, self.inter_local:], fused.shape[1]
+            else:
+                up, gld = self.up(n2), 0
+                gate = self.gate(n2)
+            act = torch.empty((m, self.inter_local), dtype=torch.float32, device=dev)
+            with _prof.span("activation"):
+                _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(gate), _vp(up), m, self.inter_local, gld, self.mlp_kind)
+        if self.by_heads:
+            with _prof.span("gather"):
+                act = gather_columns(act, self.group, self.exchange)
         d = self.down(act)
         state.cached_tokens = used
         if defer_add:

@@ -270,3 +270,47 @@ def test_custom_op_registration():
     c = torch.ops.mojolearn_b200.matmul(a, b, 0)
     want = oracle.gemm(a.cpu().numpy(), b.cpu().numpy())
     assert c.cpu().numpy().tobytes() == want.tobytes()
+
+
+def _seams_after(c, bias, act):
+    """The oracle's words of the product followed by the separate bias and activation seams."""
+    out = np.array(c, copy=True)
+    if bias is not None:
+        out = np.vectorize(lambda v, b: oracle.ftz(np.float32(oracle.ftz(v)) + np.float32(oracle.ftz(b))), otypes=[np.float32])(out, bias[None, :])
+    name = {0: None, 1: "gelu_erf", 2: "gelu_tanh", 3: "siluf"}[act]
+    if name:
+        out = np.vectorize(lambda v: oracle.ftz(oracle.math(name, oracle.ftz(v))), otypes=[np.float32])(out)
+    return out.astype(np.float32)
+
+
+@pytest.mark.parametrize("m,n,k", [(9, 20, 300), (5, 131, 640), (40, 70, 129), (3, 64, 2048)])
+def test_store_epilogue_bias_and_activation_on_every_plan(m, n, k):
+    """GEMM_EPI_PLUS_BIAS / GEMM_EPI_BIAS_ACT (reference gemm/checks/gemm_identical.mojo:8869-8912): the bias add and
+    the ungated activation inside the product's store give the words of the product followed by the separate seams,
+    on every plan, split and unsplit (a split plan applies them in the group fold, never to a node)."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    a[0, :] = 0.0  # a zero row: the word is the bias (or its activation) alone
+    c = oracle.nan_canon(oracle.gemm(a, b, oracle.OP_NT))
+    da, db, dbias = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(), torch.from_numpy(bias).cuda()
+    leaves = oracle.leaf_count(k)
+    plans = [(torch_ops.PLAN_AUTO, 0), (torch_ops.PLAN_FLAT, 0), (torch_ops.PLAN_T128, 0), (torch_ops.PLAN_T64, 2), (torch_ops.PLAN_T32, 1),
+             (torch_ops.PLAN_PACKED, 0), (torch_ops.PLAN_PACKED, 2), (torch_ops.PLAN_SKINNY, 0), (torch_ops.PLAN_SKINNY, 1)]
+    if k % 16 == 0 and m <= 8:
+        plans.append((torch_ops.PLAN_DECODE, 0))
+    for use_bias, act in ((True, 0), (True, 1), (True, 2), (False, 3), (True, 3), (False, 1)):
+        want = _seams_after(c, bias if use_bias else None, act)
+        for plan, groups in plans:
+            if plan == torch_ops.PLAN_SKINNY and k % 16:
+                continue
+            if groups and groups >= leaves:
+                groups = 0
+            got = torch_ops.product(da, db, None, linalg.W_F32, oracle.OP_NT, plan=plan, group_leaves=groups,
+                                    bias=dbias if use_bias else None, act=act)
+            assert got.cpu().numpy().tobytes() == want.tobytes(), (use_bias, act, plan, groups)
+    codes, exps = oracle.quantize_int8(b)
+    c8 = oracle.nan_canon(oracle.gemm(a, oracle.dequantize_int8(codes, exps), oracle.OP_NT))
+    got = torch_ops.product(da, torch.from_numpy(codes).cuda(), torch.from_numpy(exps).cuda(), linalg.W_INT8_EXP, oracle.OP_NT, bias=dbias, act=1)
+    assert got.cpu().numpy().tobytes() == _seams_after(c8, bias, 1).tobytes()

@@ -193,41 +193,6 @@ def test_skinny_plan_every_storage_kind():
         torch_ops.product(torch.zeros(4, 64).cuda(), torch.zeros(64, 8).cuda(), None, linalg.W_F32, oracle.OP_NN, plan=torch_ops.PLAN_SKINNY)
 
 
-def test_prepacked_weight_plan_every_storage_kind():
-    """A weight packed once into column-tile panels, then decode-size products against it: the bits of the
-    ordinary product, for every storage kind, ragged shapes and operands that force the flushed path."""
-    rng = np.random.default_rng(12)
-    for (m, n, k) in [(5, 300, 512), (8, 1030, 4096), (16, 1000, 1024), (17, 700, 4096), (32, 513, 2048), (32, 256, 64),
-                      (12, 99, 4096 + 128), (1, 40, 16)]:
-        x = rng.standard_normal((m, k)).astype(np.float32)
-        codes = rng.integers(-127, 128, (n, k)).astype(np.int8)
-        exps = rng.integers(-9, -5, n).astype(np.int32)
-        scales = rng.uniform(0.001, 0.02, n).astype(np.float32)
-        wb = oracle.to_bf16((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
-        wf = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
-        dx = torch.from_numpy(x).cuda()
-        cases = [(wf, None, linalg.W_F32, wf), (wb, None, linalg.W_BF16, oracle.from_bf16(wb)),
-                 (codes, exps, linalg.W_INT8_EXP, oracle.dequantize_int8(codes, exps)),
-                 (codes, scales, linalg.W_INT8_SCALE, oracle.dequantize_int8_scaled(codes, scales))]
-        for w, sc, kind, wref in cases:
-            want = oracle.gemm_rows(x, wref, oracle.OP_NT)
-            packed = torch_ops.pack_weight(torch.from_numpy(w).cuda(), None if sc is None else torch.from_numpy(sc).cuda(), kind)
-            got = torch_ops.product_packed(dx, packed, kind, n)
-            assert got.cpu().numpy().tobytes() == want.tobytes(), (m, n, k, kind)
-    m, n, k = 12, 200, 512
-    x = (rng.standard_normal((m, k)) * 2.0 ** -62).astype(np.float32)
-    x[0, ::9] = np.float32(3e-42)
-    codes = rng.integers(-127, 128, (n, k)).astype(np.int8)
-    exps = rng.integers(-70, -58, n).astype(np.int32)
-    exps[:4] = [-140, 127, 121, -127]
-    want = oracle.nan_canon(oracle.gemm(x, oracle.dequantize_int8(codes, exps), oracle.OP_NT))
-    packed = torch_ops.pack_weight(torch.from_numpy(codes).cuda(), torch.from_numpy(exps).cuda(), linalg.W_INT8_EXP)
-    got = torch_ops.product_packed(torch.from_numpy(x).cuda(), packed, linalg.W_INT8_EXP, n)
-    assert got.cpu().numpy().tobytes() == want.tobytes()
-    assert torch_ops.pack_weight(torch.zeros(8, 40).cuda()) is None  # k not a multiple of 16: outside the plan
-    assert _native.lib().b200i_decode_status(-1) == 0
-
-
 def test_int8_product_profile():
     rng = np.random.default_rng(9)
     a = rng.standard_normal((37, 1000)).astype(np.float32)
