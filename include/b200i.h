@@ -77,8 +77,7 @@ int64_t b200i_gemm_w(int64_t device, void *stream, float *c, const float *a, con
  * on-device restatement of the oracle), 1 = 128x128 tiles, 2 = 64x64 tiles,
  * 3 = the row-streaming decode plan (up to 8 rows), 4 = 32x128 tiles, 5 = 128x64 tiles,
  * 6 = the skinny plan (op NT, up to 32 activation rows, k a multiple of 16, 16-byte aligned
- * operands; low-bit weights fold up to 16 leaf groups inside thread-block clusters), 8 = the skinny plan with the
- * group nodes always in the workspace and a separate fold, 7 = the packed plan (operands repacked into tile-major panels in the workspace,
+ * operands), 7 = the packed plan (operands repacked into tile-major panels in the workspace,
  * then 128x128 tiles fed by bulk copies; needs a 256-byte aligned workspace of
  * b200i_plan_workspace_bytes); `group_leaves` = leaves per group (a power of two, 0 = no split). Every plan returns the same bits; the tests
  * hold them to that (the reference's launch-invariance gate,
@@ -92,10 +91,16 @@ int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a
  * the reference's GEMM_EPI_PLUS_BIAS and GEMM_EPI_BIAS_ACT stores (gemm/checks/gemm_identical.mojo
  * :8869-8912, :9483-9491): the words are those of b200i_gemm_w followed by b200i_bias_add and the
  * ungated b200i_act_mul, with one launch instead of three. `plan` and `group_leaves` as for
- * b200i_gemm_w_plan (-1, 0 = automatic). */
+ * b200i_gemm_w_plan (-1, 0 = automatic).
+ * act 4 / 5 / 6 = the GATED activations silu(gate)*up / gelu(gate)*up / gelu_tanh(gate)*up (S20-S21) over a weight
+ * whose rows were interleaved by the caller (row 2j = gate_j, row 2j + 1 = up_j; a bias interleaved the same way):
+ * c is then [m, n / 2]. Only the skinny plans spell it (a thread there owns both columns of a pair); it is refused
+ * by name for a shape outside them (b200i_pair_epilogue_fits says which), and the caller then runs the product
+ * and b200i_act_mul with `interleaved` = 1. */
 int64_t b200i_gemm_w_epilogue(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale, int64_t wkind,
                               int64_t m, int64_t n, int64_t k, int64_t op, const float *bias, int64_t act, int64_t plan,
                               int64_t group_leaves, void *ws, int64_t ws_bytes, char *err, int64_t err_cap);
+int64_t b200i_pair_epilogue_fits(int64_t m, int64_t n, int64_t k, int64_t op);
 
 /* Device timing of the product's main kernel, for benchmarks. While enabled (enable = 1 also
  * clears the record) every product call records a CUDA event pair on its stream around its main
@@ -202,33 +207,49 @@ int64_t b200i_add_norm(int64_t device, void *stream, float *out, float *sum_out,
 /* The fresh q | k | v rows of a call in one pass: q rotated into qr [b*l, n_heads*head_dim], k rotated into its cache
  * slots, v copied into its cache slots: b200i_rope_apply on q and k plus b200i_kv_append on k and v, same bits.
  * Sources share the row pitch src_ld (they may be column blocks of one fused product); cosv / sinv NULL = no rotation;
- * `position` not NULL = the cached-token count is read from that device word (as the _at entries), else pos0. */
+ * `position` not NULL = the cached-token count is read from that device word (as the _at entries), else pos0.
+ * `rope_dim` = rotated columns of a head (0 = head_dim; the tables are then [l, rope_dim / 2]): the rest of a head's
+ * columns pass through, flushed (partial rotary, transformer/checks/transformer_oracle.mojo:1433-1440). */
 int64_t b200i_qkv_rope_cache(int64_t device, void *stream, float *qr, float *kcache, float *vcache, const float *q, const float *k,
                              const float *v, int64_t src_ld, const float *cosv, const float *sinv, int64_t b, int64_t l,
                              int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap, int64_t pos0, const int32_t *position,
-                             char *err, int64_t err_cap);
+                             int64_t rope_dim, char *err, int64_t err_cap);
 /* cos and sin [l, head_dim/2] for absolute positions pos0 .. pos0+l-1 (S6-S8); positions stay below 8192. */
 int64_t b200i_rope_table(int64_t device, void *stream, float *cosv, float *sinv, int64_t pos0, int64_t l, int64_t head_dim,
                          double theta, char *err, int64_t err_cap);
+/* The table under the block's option record (transformer/block_options.mojo:40-70, spelled as
+ * transformer/checks/transformer_oracle.mojo:423-497): cos and sin [l, rope_dim / 2]; scaling 0 = none, 1 = linear
+ * (inverse frequencies divided by `factor`), 2 = llama3 (rescaled by wavelength between the two frequency factors
+ * against original_max_positions). `position` not NULL = the first position is read from that device word, else pos0. */
+int64_t b200i_rope_table_opts(int64_t device, void *stream, float *cosv, float *sinv, int64_t pos0, const int32_t *position, int64_t l,
+                              int64_t rope_dim, double theta, int64_t scaling, double factor, double low_freq_factor,
+                              double high_freq_factor, int64_t original_max_positions, char *err, int64_t err_cap);
 /* out[rows, n_heads*head_dim] = rotate(src) with the table of the call's l positions (S9-S10); not in place.
  * `src_ld` is the row pitch of src in floats (0 = contiguous rows): the projection may be a column block of
  * one fused q|k|v product. */
 int64_t b200i_rope_apply(int64_t device, void *stream, float *out, const float *src, const float *cosv, const float *sinv,
-                         int64_t rows, int64_t l, int64_t n_heads, int64_t head_dim, int64_t src_ld, char *err, int64_t err_cap);
+                         int64_t rows, int64_t l, int64_t n_heads, int64_t head_dim, int64_t src_ld, int64_t rope_dim, char *err,
+                         int64_t err_cap);
 /* cache[b, n_kv, cap, head_dim] <- src[b*l, n_kv*head_dim] (row pitch src_ld, 0 = contiguous) at positions
  * pos0 .. pos0+l-1 (a copy). */
 int64_t b200i_kv_append(int64_t device, void *stream, float *cache, const float *src, int64_t b, int64_t l, int64_t n_kv,
                         int64_t head_dim, int64_t cap, int64_t pos0, int64_t src_ld, char *err, int64_t err_cap);
 /* ctx[b*l, n_heads*head_dim] from rotated queries q[b*l, n_heads*head_dim] and caches holding `used`
  * positions, this call's l included (S11-S19: eager attention, serial key-axis chains). `scores` is
- * scratch of b*n_heads*l*min(used, window or used) floats. head_dim <= 128. */
+ * scratch of b*n_heads*l*min(used, window or used) floats; a call of 2 to 8 query rows per sequence with
+ * head_dim a multiple of 4 runs as one kernel that keeps its score rows in shared memory (the reference's fused
+ * attention, transformer/impl/llama/fused_attention.mojo:5: same fold order, nothing materialised) and leaves
+ * the scratch untouched. head_dim <= 128. `softcap` (0 = none) caps every scaled score as cap * tanh(score / cap)
+ * before the mask is added (transformer_oracle.mojo:2269-2281). */
 int64_t b200i_attention(int64_t device, void *stream, float *ctx, const float *q, const float *kcache, const float *vcache,
                         float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
-                        int64_t used, int64_t window, char *err, int64_t err_cap);
+                        int64_t used, int64_t window, double softcap, char *err, int64_t err_cap);
 /* kind 0 = silu(gate)*up, 1 = gelu_erf(up), 2 = gelu_tanh(up), 3 = silu(up), 4 / 5 = gelu(gate)*up (S20-S21).
- * out is [rows, width] contiguous; gate and up are [rows, width] with row pitch in_ld (0 = contiguous). */
+ * out is [rows, width] contiguous; gate and up are [rows, width] with row pitch in_ld (0 = contiguous).
+ * `interleaved` = 1: gate and up are the even and odd columns of ONE [rows, 2 * width] matrix (pass its first
+ * element as `gate`, `up` is ignored, in_ld its row pitch): the layout of a product over interleaved weight rows. */
 int64_t b200i_act_mul(int64_t device, void *stream, float *out, const float *gate, const float *up, int64_t rows, int64_t width,
-                      int64_t in_ld, int64_t kind, char *err, int64_t err_cap);
+                      int64_t in_ld, int64_t kind, int64_t interleaved, char *err, int64_t err_cap);
 /* out = ftz(ftz(a) + ftz(b)) (S22, S23); may be in place. */
 int64_t b200i_add(int64_t device, void *stream, float *out, const float *a, const float *b, int64_t count, char *err, int64_t err_cap);
 /* buf[rows, width] += bias[width], one plain add per cell (transformer_oracle.mojo:1344-1372). */
@@ -256,7 +277,7 @@ int64_t b200i_kv_append_at(int64_t device, void *stream, float *cache, const flo
                            int64_t head_dim, int64_t cap, const int32_t *position, int64_t src_ld, char *err, int64_t err_cap);
 int64_t b200i_attention_at(int64_t device, void *stream, float *ctx, const float *q, const float *kcache, const float *vcache,
                            float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
-                           const int32_t *position, int64_t window, char *err, int64_t err_cap);
+                           const int32_t *position, int64_t window, double softcap, char *err, int64_t err_cap);
 int64_t b200i_add_positions_at(int64_t device, void *stream, float *x, const float *pos, int64_t rows, int64_t l,
                                const int32_t *position, int64_t width, char *err, int64_t err_cap);
 int64_t b200i_advance_position(int64_t device, void *stream, int32_t *position, int64_t delta, char *err, int64_t err_cap);

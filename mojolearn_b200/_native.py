@@ -68,12 +68,14 @@ SIGNATURES = {
     "b200i_noalloc_scratch_bytes": [I64, I64, I64],
     "b200i_norm": [I64, VP, VP, VP, VP, VP, I64, I64, F64, I64, VP, I64],
     "b200i_add_norm": [I64, VP, VP, VP, VP, VP, VP, VP, I64, I64, F64, I64, VP, I64],
-    "b200i_qkv_rope_cache": [I64, VP, VP, VP, VP, VP, VP, VP, I64, VP, VP, I64, I64, I64, I64, I64, I64, I64, VP, VP, I64],
+    "b200i_qkv_rope_cache": [I64, VP, VP, VP, VP, VP, VP, VP, I64, VP, VP, I64, I64, I64, I64, I64, I64, I64, VP, I64, VP, I64],
+    "b200i_rope_table_opts": [I64, VP, VP, VP, I64, VP, I64, I64, F64, I64, F64, F64, F64, I64, VP, I64],
     "b200i_rope_table": [I64, VP, VP, VP, I64, I64, I64, F64, VP, I64],
-    "b200i_rope_apply": [I64, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, VP, I64],
+    "b200i_rope_apply": [I64, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, I64, VP, I64],
     "b200i_kv_append": [I64, VP, VP, VP, I64, I64, I64, I64, I64, I64, I64, VP, I64],
-    "b200i_attention": [I64, VP, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, I64, I64, I64, VP, I64],
-    "b200i_act_mul": [I64, VP, VP, VP, VP, I64, I64, I64, I64, VP, I64],
+    "b200i_attention": [I64, VP, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, I64, I64, I64, F64, VP, I64],
+    "b200i_act_mul": [I64, VP, VP, VP, VP, I64, I64, I64, I64, I64, VP, I64],
+    "b200i_pair_epilogue_fits": [I64, I64, I64, I64],
     "b200i_add": [I64, VP, VP, VP, VP, I64, VP, I64],
     "b200i_bias_add": [I64, VP, VP, VP, I64, I64, VP, I64],
     "b200i_embedding": [I64, VP, VP, VP, VP, I64, I64, I64, VP, VP, I64],
@@ -81,7 +83,7 @@ SIGNATURES = {
     "b200i_argmax": [I64, VP, VP, VP, I64, I64, VP, I64],
     "b200i_rope_table_at": [I64, VP, VP, VP, VP, I64, I64, F64, VP, I64],
     "b200i_kv_append_at": [I64, VP, VP, VP, I64, I64, I64, I64, I64, VP, I64, VP, I64],
-    "b200i_attention_at": [I64, VP, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, I64, VP, I64, VP, I64],
+    "b200i_attention_at": [I64, VP, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, I64, VP, I64, F64, VP, I64],
     "b200i_add_positions_at": [I64, VP, VP, VP, I64, I64, VP, I64, VP, I64],
     "b200i_advance_position": [I64, VP, VP, I64, VP, I64],
     "b200i_ffma_probe": [I64, VP, VP, I64, I64, I64, VP, I64],

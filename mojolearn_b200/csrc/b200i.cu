@@ -86,8 +86,7 @@ int64_t check_wait_status(char *err, int64_t err_cap, const char *who) {
 }
 
 // ---- plans -----------------------------------------------------------------------------
-enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4, PLAN_T128X64 = 5, PLAN_SKINNY = 6, PLAN_PACKED = 7,
-       PLAN_SKINNY_NODES = 8 }; // the skinny plan with its leaf-group nodes in global memory and a separate fold (never folded in clusters)
+enum { PLAN_AUTO = -1, PLAN_FLAT = 0, PLAN_T128 = 1, PLAN_T64 = 2, PLAN_DECODE = 3, PLAN_T32 = 4, PLAN_T128X64 = 5, PLAN_SKINNY = 6, PLAN_PACKED = 7 };
 
 // Up to this many rows the weight-streaming decode plan wins; above, the skinny plan. Low-bit weights
 // switch earlier: at three and four rows the decode kernel's serial chains cost more than the register
@@ -178,12 +177,7 @@ Plan choose_skinny(long long m, long long n, long long k, int sms, bool lowbit) 
             const long long rounds = (ctas + sms - 1) / sms;
             double thin = ctas <= sms ? 1.25 : (ctas <= 2 * sms ? 1.08 : 1.0);
             double t = (double)rounds * (s * leaf_us * thin + 0.4);
-            if (groups > SKR_MAX_CLUSTER) t += 2.5 + (double)groups * m * n * 8.0 / 7.5e6; // global nodes and a second launch
-            else if (groups > 1) {                                                             // folded inside a cluster: a barrier and a
-                int levels = 0;                                                                // shared-memory pass per tree level
-                while ((1 << levels) < groups) levels++;
-                t += 0.5 * (levels + 1);
-            }
+            if (groups > 1) t += 2.5 + (double)groups * m * n * 8.0 / 7.5e6;
             if (t < best_t) { best_t = t; best = s; }
         }
     } else {
@@ -317,7 +311,7 @@ int launch_packed(const GemmArgs &g, int groups, unsigned char *scratch, cudaStr
     PackArgs b{pb, fb, g.b, g.bscale, g.n, g.k, g.leaf, g.leaves, wpl, g.op == OP_NT, g.op == OP_NT && k8 && aligned(g.b, 16)};
     launch_pack_b(b, g.wkind, st);
     PackedGemmArgs p{pa, pb, fa, fb, g.c, g.ws, g.m, g.n, g.k, g.leaf, g.leaves, wpl, g.group_leaves, groups,
-                     (g.n + PK_TILE - 1) / PK_TILE, g.vec_c, g.epi};
+                     (g.n + PK_TILE - 1) / PK_TILE, g.vec_c};
     dim3 grid((unsigned)(((g.m + PK_TILE - 1) / PK_TILE) * p.tiles_n), (unsigned)groups);
     const int tslot = timing_begin(st);
     gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, st>>>(p);
@@ -338,6 +332,14 @@ void launch_tile(GemmArgs &g, int groups, cudaStream_t st) {
     g.tiles_n = (g.n + BN - 1) / BN;
     dim3 grid((unsigned)(((g.m + BM - 1) / BM) * g.tiles_n), (unsigned)groups);
     gemm_tile_kernel<BM, BN, RM, RN, MINB><<<grid, S::THREADS, S::SMEM_BYTES, st>>>(g);
+}
+
+unsigned grid_for(long long work_items, int block, int sms) {
+    long long blocks = (work_items + block - 1) / block;
+    const long long cap = (long long)sms * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (unsigned)blocks;
 }
 
 int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const void *b, const void *bscale, int wkind,
@@ -377,11 +379,11 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
         const bool skinny = skinny_plan_fits(m, n, k, op) && al16;
         const bool wide = n >= DECODE_WIDE_N && (wkind == W_BF16 || m == 3);
         const int prefer_m = (wkind != W_F32 && skinny && !wide) ? DECODE_PREFER_M_LOWBIT : DECODE_PREFER_M;
-        if (dec && m <= prefer_m) plan = Plan{PLAN_DECODE, g.leaves, 1};
+        if (dec && m <= prefer_m && !(skinny && epilogue_pairs(g.epi))) plan = Plan{PLAN_DECODE, g.leaves, 1}; // (a gated store needs the skinny plan)
         else if (skinny) plan = choose_skinny(m, n, k, sm_count(dev), wkind != W_F32);
         else if (dec) plan = Plan{PLAN_DECODE, g.leaves, 1};
     } else {
-        plan.kind = plan_kind == PLAN_SKINNY_NODES ? PLAN_SKINNY : plan_kind;
+        plan.kind = plan_kind;
         int s = group_leaves > 0 ? (int)group_leaves : g.leaves;
         if (s & (s - 1)) {
             if (s < g.leaves) return fail(err, err_cap, "identical gemm: a leaf group must be a power of two");
@@ -410,8 +412,14 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     g.vec_b = b_kc ? (k % 4 == 0 && leaf_ok && aligned(b, balign)) : (n % 4 == 0 && aligned(b, balign));
     g.vec_c = (n % 4 == 0) && aligned(c, 16) && (plan.groups == 1 || aligned(ws, 16));
 
+    if (epilogue_pairs(g.epi)) {
+        // a gated activation needs both columns of a pair in one thread: the skinny plans, whose threads own adjacent
+        // columns, apply it in their own store or in the group fold; no other plan spells it
+        const bool fold_ok = plan.groups == 1 || (((long long)m * n) % 4 == 0 && aligned(ws, 16) && aligned(c, 8));
+        if (plan.kind != PLAN_SKINNY || n % 4 != 0 || !fold_ok)
+            return fail(err, err_cap, "identical gemm: the gated store activation needs the skinny plan (up to 32 rows, op NT, k a multiple of 16) and n a multiple of 4");
+    }
     int tslot = -1;
-    bool folded = false; // the plan's own launch already folded the leaf groups
     if (plan.kind != PLAN_PACKED) tslot = timing_begin(st);
     if (plan.kind == PLAN_FLAT) {
         const long long cells = (long long)m * n;
@@ -443,17 +451,21 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
         if (!skinny_plan_fits(m, n, k, op) || !aligned(b, 16) || !aligned(a, 16))
             return fail(err, err_cap, "identical gemm: the skinny plan needs op NT, m <= 32, k a multiple of 16 and 16-byte aligned operands");
         // low-bit weights stay in registers; float32 windows are too wide for that and go through shared memory
-        g.cluster_fold = plan_kind != PLAN_SKINNY_NODES;
-        if (g.wkind != W_F32) folded = launch_skinny_reg(g, plan.groups, st);
+        if (g.wkind != W_F32) launch_skinny_reg(g, plan.groups, st);
         else launch_skinny(g, plan.groups, st);
         g_launches++;
     } else {
         return fail(err, err_cap, "identical gemm: unknown plan %d", plan.kind);
     }
     timing_end(tslot, st);
-    if (plan.groups > 1 && !folded) {
+    if (plan.groups > 1) {
         const long long cells = (long long)m * n;
         launch_fold_groups(g.ws, c, cells, plan.groups, st, g.epi, g.n);
+        g_launches++;
+    } else if (epilogue_on(g.epi) && plan.kind != PLAN_SKINNY && plan.kind != PLAN_DECODE) {
+        // the tiled, packed and flat plans store plain product words; their epilogue is a pass of its own
+        const long long cells = (long long)m * n;
+        epilogue_rows_kernel<<<grid_for(cells, 256, sm_count(dev)), 256, 0, st>>>(c, cells, (int)n, g.epi);
         g_launches++;
     }
     CUDA_TRY(cudaGetLastError());
@@ -492,13 +504,6 @@ size_t wkind_elem_bytes(int wkind) { return wkind == W_F32 ? 4 : (wkind == W_BF1
 
 } // namespace
 
-static unsigned grid_for(long long work_items, int block, int sms) {
-    long long blocks = (work_items + block - 1) / block;
-    const long long cap = (long long)sms * 16;
-    if (blocks > cap) blocks = cap;
-    if (blocks < 1) blocks = 1;
-    return (unsigned)blocks;
-}
 
 extern "C" {
 
@@ -586,6 +591,10 @@ int64_t b200i_plan_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t plan
     return groups > 1 ? groups * m * n * 4 : 0;
 }
 
+int64_t b200i_pair_epilogue_fits(int64_t m, int64_t n, int64_t k, int64_t op) {
+    return (skinny_plan_fits(m, n, k, (int)op) && n % 4 == 0) ? 1 : 0;
+}
+
 int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale,
                           int64_t wkind, int64_t m, int64_t n, int64_t k, int64_t op, int64_t plan, int64_t group_leaves,
                           void *ws, int64_t ws_bytes, char *err, int64_t err_cap) {
@@ -613,7 +622,7 @@ int64_t b200i_gemm_w_epilogue(int64_t device, void *stream, float *c, const floa
     clear(err, err_cap);
     int dev;
     if (select_device(device, err, err_cap, &dev)) return 1;
-    if (act < EPI_ACT_NONE || act > EPI_ACT_SILU) return fail(err, err_cap, "identical gemm: unknown store activation %lld", (long long)act);
+    if (act < EPI_ACT_NONE || act > EPI_PAIR_GEGLU_TANH) return fail(err, err_cap, "identical gemm: unknown store activation %lld", (long long)act);
     if (bias && !aligned(bias, 4)) return fail(err, err_cap, "identical gemm: misaligned storage");
     return launch_product(dev, static_cast<cudaStream_t>(stream), c, a, b, bscale, (int)wkind, m, n, k, (int)op, (int)plan, group_leaves, ws,
                           ws_bytes, err, err_cap, Epilogue{bias, (int)act});
@@ -653,8 +662,7 @@ int64_t b200i_quantize_int8(int64_t device, void *stream, int8_t *codes, int32_t
     if (!codes || !exponents || !x) return fail(err, err_cap, "quantize_int8: null storage");
     int dev;
     if (select_device(device, err, err_cap, &dev)) return 1;
-    quantize_int8_kernel<<<grid_for(rows * 32, 256, sm_count(dev)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<signed char *>(codes), exponents, x, rows, cols);
+    quantize_int8_kernel<<<grid_for(rows * 32, 256, sm_count(dev)), 256, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<signed char *>(codes), exponents, x, rows, cols);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -667,8 +675,7 @@ int64_t b200i_dequantize_int8(int64_t device, void *stream, float *y, const int8
     if (!codes || !exponents || !y) return fail(err, err_cap, "dequantize_int8: null storage");
     int dev;
     if (select_device(device, err, err_cap, &dev)) return 1;
-    dequantize_int8_kernel<<<grid_for(rows * cols, 256, sm_count(dev)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        y, reinterpret_cast<const signed char *>(codes), exponents, rows, cols);
+    dequantize_int8_kernel<<<grid_for(rows * cols, 256, sm_count(dev)), 256, 0, static_cast<cudaStream_t>(stream)>>>(y, reinterpret_cast<const signed char *>(codes), exponents, rows, cols);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -683,8 +690,7 @@ int64_t b200i_gemm_int8(int64_t device, void *stream, float *c, const int8_t *qa
     int dev;
     if (select_device(device, err, err_cap, &dev)) return 1;
     const long long cells = m * n;
-    gemm_int8_flat_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        c, reinterpret_cast<const signed char *>(qa), ea, reinterpret_cast<const signed char *>(qb), eb, (int)m, (int)n, (int)k);
+    gemm_int8_flat_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(c, reinterpret_cast<const signed char *>(qa), ea, reinterpret_cast<const signed char *>(qb), eb, (int)m, (int)n, (int)k);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -829,8 +835,11 @@ int64_t b200i_add_norm(int64_t device, void *stream, float *out, float *sum_out,
 int64_t b200i_qkv_rope_cache(int64_t device, void *stream, float *qr, float *kcache, float *vcache, const float *q, const float *k,
                              const float *v, int64_t src_ld, const float *cosv, const float *sinv, int64_t b, int64_t l,
                              int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap, int64_t pos0, const int32_t *position,
-                             char *err, int64_t err_cap) {
+                             int64_t rope_dim, char *err, int64_t err_cap) {
     SEAM_PROLOGUE();
+    if (rope_dim == 0) rope_dim = head_dim;
+    if (rope_dim < 0 || rope_dim > head_dim || (rope_dim & 1))
+        return fail(err, err_cap, "transformer: the rotary table's rope_dim %lld does not fit head_dim %lld REFUSED", (long long)rope_dim, (long long)head_dim);
     if (b <= 0 || l <= 0 || n_heads <= 0 || n_kv <= 0 || head_dim <= 0 || (head_dim & 1) || !qr || !kcache || !vcache || !q || !k || !v ||
         qr == q)
         return fail(err, err_cap, "qkv_rope_cache: bad arguments");
@@ -848,7 +857,7 @@ int64_t b200i_qkv_rope_cache(int64_t device, void *stream, float *qr, float *kca
     if (ldq < n_heads * head_dim || ldkv < n_kv * head_dim) return fail(err, err_cap, "qkv_rope_cache: the row pitch is below the row width");
     qkv_rope_cache_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(qr, kcache, vcache, q, k, v, ldq, ldkv, cosv, sinv, (int)b, (int)l,
                                                                            (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, (int)pos0,
-                                                                           position, cosv ? 1 : 0);
+                                                                           position, cosv ? 1 : 0, (int)rope_dim);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -879,15 +888,39 @@ int64_t b200i_rope_table_at(int64_t device, void *stream, float *cosv, float *si
     return 0;
 }
 
-int64_t b200i_rope_apply(int64_t device, void *stream, float *out, const float *src, const float *cosv, const float *sinv,
-                         int64_t rows, int64_t l, int64_t n_heads, int64_t head_dim, int64_t src_ld, char *err, int64_t err_cap) {
+int64_t b200i_rope_table_opts(int64_t device, void *stream, float *cosv, float *sinv, int64_t pos0, const int32_t *position, int64_t l,
+                              int64_t rope_dim, double theta, int64_t scaling, double factor, double low_freq_factor,
+                              double high_freq_factor, int64_t original_max_positions, char *err, int64_t err_cap) {
     SEAM_PROLOGUE();
+    if (l <= 0 || rope_dim <= 0 || (rope_dim & 1) || !cosv || !sinv) return fail(err, err_cap, "rope_table: bad arguments");
+    if (scaling < 0 || scaling > 2) return fail(err, err_cap, "transformer options: rope_scaling %lld is not spelled", (long long)scaling);
+    if (!(theta > 0.0) || (scaling != 0 && !(factor > 0.0))) return fail(err, err_cap, "transformer options: rope_theta and the rope_scaling factor must be positive");
+    if (scaling == 2 && (!(low_freq_factor > 0.0) || !(high_freq_factor > 0.0) || high_freq_factor == low_freq_factor || original_max_positions <= 0))
+        return fail(err, err_cap, "transformer options: llama3 rope_scaling needs positive, distinct frequency factors and original positions");
+    if (!position && (pos0 < 0 || pos0 + l > 8192 * (scaling == 1 ? (long long)factor : 1)))
+        return fail(err, err_cap, "rope_table: absolute position %lld puts the angle at or beyond 8192, the domain of the sine and cosine reduction",
+                    (long long)(pos0 + l - 1));
+    const long long n = l * (rope_dim / 2);
+    RopeOptions o{(float)theta, (int)scaling, (float)factor, (float)low_freq_factor, (float)high_freq_factor, (int)original_max_positions};
+    rope_table_opts_kernel<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(cosv, sinv, (int)pos0, (int)l, (int)rope_dim, o, position);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_rope_apply(int64_t device, void *stream, float *out, const float *src, const float *cosv, const float *sinv,
+                         int64_t rows, int64_t l, int64_t n_heads, int64_t head_dim, int64_t src_ld, int64_t rope_dim, char *err,
+                         int64_t err_cap) {
+    SEAM_PROLOGUE();
+    if (rope_dim == 0) rope_dim = head_dim;
+    if (rope_dim < 0 || rope_dim > head_dim || (rope_dim & 1))
+        return fail(err, err_cap, "transformer: the rotary table's rope_dim %lld does not fit head_dim %lld REFUSED", (long long)rope_dim, (long long)head_dim);
     if (rows <= 0 || l <= 0 || n_heads <= 0 || head_dim <= 0 || (head_dim & 1) || !out || !src || out == src)
         return fail(err, err_cap, "rope_apply: bad arguments (the rotation is not in place)");
     if (src_ld == 0) src_ld = n_heads * head_dim;
     if (src_ld < n_heads * head_dim) return fail(err, err_cap, "rope_apply: the row pitch is below the row width");
     const long long n = rows * n_heads * head_dim;
-    rope_apply_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(out, src, cosv, sinv, rows, (int)l, (int)n_heads, (int)head_dim, src_ld);
+    rope_apply_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(out, src, cosv, sinv, rows, (int)l, (int)n_heads, (int)head_dim, src_ld, (int)rope_dim);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -927,8 +960,56 @@ int64_t b200i_kv_append_at(int64_t device, void *stream, float *cache, const flo
 // `s_grid` sizes the launch (the key count, or its upper bound when the position is read on the device)
 static int64_t attention_launch(int dev, cudaStream_t st, float *ctx, const float *q, const float *kcache, const float *vcache,
                                 float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
-                                int key_lo, int s, int own0, int s_grid, int64_t window, const int32_t *position, char *err,
-                                int64_t err_cap) {
+                                int key_lo, int s, int own0, int s_grid, int64_t window, const int32_t *position, float softcap,
+                                char *err, int64_t err_cap) {
+    if (l >= 2 && l <= ATT_SMALL_Q && head_dim % 4 == 0 && head_dim <= K_LEAF_MIN) {
+        // A few query rows per sequence (a chunked prompt's tail, speculative steps): scores, softmax and value sum in
+        // one kernel, the score rows in shared memory, every key and value row read once for all the query rows. The
+        // fewer CTAs the call has, the more shared memory each one spends on bytes in flight. A single query row
+        // stays on the two kernels below: measured on B200 (batch 32, 16 heads, 1030 keys) the fused form is 8 %
+        // slower on the whole decode step there, because its CTAs run their score, softmax and value phases in step
+        // and the memory system idles through everyone's serial softmax, and with few (sequence, head) pairs the
+        // scores kernel's split over key tiles is what keeps all SMs loading.
+        const int lq = l == 1 ? 1 : (l == 2 ? 2 : (l <= 4 ? 4 : 8));
+        const long long ctas = b * n_heads;
+        const int sms = sm_count(dev);
+        long long per_sm = (ctas + sms - 1) / sms; // CTAs an SM must hold for the call to be one wave
+        if (per_sm > 6) per_sm = 6;
+        const long long fixed = (long long)lq * K_LEAF_MIN + (long long)lq * ((s_grid + 3) & ~3);
+        const long long room = (226ll * 1024 / per_sm - 1280) / 4 - fixed; // floats for the key tiles / the value ring
+        int kkeys = 32, nkb = (int)(room / (ATD_WARPS * 32 * ATT_KT_PITCH));
+        if (nkb > 3) nkb = 3;
+        if (nkb < 1) { // not even one full tile per warp: fewer keys per tile
+            nkb = 1;
+            kkeys = (int)(room / (ATD_WARPS * ATT_KT_PITCH));
+        }
+        const int vkeys = room >= 4ll * 32 * head_dim ? 32 : 16;
+        int stages = (int)(room / (vkeys * head_dim));
+        if (stages > ATD_MAX_STAGES) stages = ATD_MAX_STAGES;
+        if (kkeys >= 8 && stages >= 2) {
+            const size_t smem = attn_decode_smem(lq, s_grid, (int)head_dim, kkeys, nkb, vkeys, stages);
+#define DECODE_FUSED(LQ)                                                                                                          \
+    do {                                                                                                                          \
+        static std::atomic<bool> configured[64];                                                                                  \
+        if (dev >= 0 && dev < 64 && !configured[dev]) {                                                                           \
+            CUDA_TRY(cudaFuncSetAttribute(attn_decode_kernel<LQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));      \
+            configured[dev] = true;                                                                                               \
+        }                                                                                                                         \
+        attn_decode_kernel<LQ><<<(unsigned)ctas, ATD_THREADS, smem, st>>>(ctx, q, kcache, vcache, (int)b, (int)l, (int)n_heads,   \
+                                                                          (int)n_kv, (int)head_dim, (int)cap, key_lo, s, own0,   \
+                                                                          (int)window, position, s_grid, kkeys, nkb, vkeys,      \
+                                                                          stages, softcap);                                      \
+    } while (0)
+            if (lq == 1) DECODE_FUSED(1);
+            else if (lq == 2) DECODE_FUSED(2);
+            else if (lq == 4) DECODE_FUSED(4);
+            else DECODE_FUSED(8);
+#undef DECODE_FUSED
+            g_launches++;
+            CUDA_TRY(cudaGetLastError());
+            return 0;
+        }
+    }
     if (l <= ATT_SMALL_Q) {
         dim3 gs((unsigned)((s_grid + 127) / 128), (unsigned)(b * n_heads));
 #define SCORES_SMALL(LQ)                                                                                                          \
@@ -939,9 +1020,9 @@ static int64_t attention_launch(int dev, cudaStream_t st, float *ctx, const floa
                                           attn_scores_small_smem<LQ>()));                                                         \
             configured[dev] = true;                                                                                               \
         }                                                                                                                         \
-        attn_scores_small_kernel<LQ><<<gs, 128, attn_scores_small_smem<LQ>(), st>>>(                                              \
+        attn_scores_small_kernel<LQ><<<gs, 128, attn_scores_small_smem<LQ>(), st>>>(\
             scores, q, kcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, key_lo, s, own0, (int)window,    \
-            position);                                                                                                            \
+            position, softcap);                                                                                                   \
     } while (0)
         if (l == 1) SCORES_SMALL(1);
         else if (l == 2) SCORES_SMALL(2);
@@ -951,22 +1032,28 @@ static int64_t attention_launch(int dev, cudaStream_t st, float *ctx, const floa
     } else {
         dim3 g1((unsigned)((s_grid + ATT_T - 1) / ATT_T), (unsigned)((l + ATT_T - 1) / ATT_T), (unsigned)(b * n_heads));
         attn_scores_kernel<<<g1, 256, 0, st>>>(scores, q, kcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, key_lo, s,
-                                                 own0, (int)window, position);
+                                                 own0, (int)window, position, softcap);
     }
     if (l <= ATT_SMALL_Q && (size_t)s_grid * sizeof(float) <= 40 * 1024) {
         static std::atomic<bool> configured[64];
         if (dev >= 0 && dev < 64 && !configured[dev]) {
-            CUDA_TRY(cudaFuncSetAttribute(attn_context_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)attn_context_row_smem(40 * 1024 / 4, K_LEAF_MIN)));
+            CUDA_TRY(cudaFuncSetAttribute(attn_context_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
             configured[dev] = true;
         }
-        attn_context_row_kernel<<<(unsigned)(b * n_heads * l), 128, attn_context_row_smem(s_grid, (int)head_dim), st>>>(
+        // enough CTAs per SM for one wave (four at most); the shared memory that leaves a CTA becomes ring stages
+        const long long rows = b * n_heads * l;
+        long long per_sm = (rows + sm_count(dev) - 1) / sm_count(dev);
+        if (per_sm > 4) per_sm = 4;
+        long long stages = ((226ll * 1024 / per_sm - 1280) / 4 - ((s_grid + 3) & ~3)) / (CTX_NB * head_dim);
+        if (stages > CTX_ST_MAX) stages = CTX_ST_MAX;
+        if (stages < CTX_ST) stages = CTX_ST;
+        attn_context_row_kernel<<<(unsigned)rows, 128, attn_context_row_smem(s_grid, (int)head_dim, (int)stages), st>>>(
             ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, key_lo, s, own0, (int)window, position,
-            s_grid);
+            s_grid, (int)stages);
     } else {
         dim3 g2((unsigned)((l + CTX_ROWS - 1) / CTX_ROWS), (unsigned)(b * n_heads));
 #define CONTEXT_ROWS(DPL)                                                                                                     \
-    attn_context_kernel<DPL><<<g2, 32 * CTX_WARPS, attn_context_smem((int)head_dim), st>>>(                                   \
+    attn_context_kernel<DPL><<<g2, 32 * CTX_WARPS, attn_context_smem((int)head_dim), st>>>(\
         ctx, scores, vcache, (int)b, (int)l, (int)n_heads, (int)n_kv, (int)head_dim, (int)cap, key_lo, s, own0, (int)window, position)
         if (head_dim <= 32) CONTEXT_ROWS(1);
         else if (head_dim <= 64) CONTEXT_ROWS(2);
@@ -991,7 +1078,7 @@ static int64_t attention_check(int64_t b, int64_t l, int64_t n_heads, int64_t n_
 
 int64_t b200i_attention(int64_t device, void *stream, float *ctx, const float *q, const float *kcache, const float *vcache,
                         float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
-                        int64_t used, int64_t window, char *err, int64_t err_cap) {
+                        int64_t used, int64_t window, double softcap, char *err, int64_t err_cap) {
     SEAM_PROLOGUE();
     if (attention_check(b, l, n_heads, n_kv, head_dim, ctx, q, kcache, vcache, scores, err, err_cap)) return 1;
     if (used < l || used > cap) return fail(err, err_cap, "attention: the cache holds %lld positions, this call's %lld included", (long long)used, (long long)l);
@@ -1000,30 +1087,37 @@ int64_t b200i_attention(int64_t device, void *stream, float *ctx, const float *q
     if (window > 0 && pos0 - (window - 1) > 0) key_lo = pos0 - (window - 1);
     const int s = (int)(used - key_lo), own0 = (int)(pos0 - key_lo);
     return attention_launch(dev, st, ctx, q, kcache, vcache, scores, b, l, n_heads, n_kv, head_dim, cap, (int)key_lo, s, own0, s, window,
-                            nullptr, err, err_cap);
+                            nullptr, (float)softcap, err, err_cap);
 }
 
 int64_t b200i_attention_at(int64_t device, void *stream, float *ctx, const float *q, const float *kcache, const float *vcache,
                            float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
-                           const int32_t *position, int64_t window, char *err, int64_t err_cap) {
+                           const int32_t *position, int64_t window, double softcap, char *err, int64_t err_cap) {
     SEAM_PROLOGUE();
     if (attention_check(b, l, n_heads, n_kv, head_dim, ctx, q, kcache, vcache, scores, err, err_cap)) return 1;
     if (!position || l > cap) return fail(err, err_cap, "attention: bad arguments");
     int64_t s_max = cap; // the most keys any position can see
     if (window > 0 && window - 1 + l < s_max) s_max = window - 1 + l;
     return attention_launch(dev, st, ctx, q, kcache, vcache, scores, b, l, n_heads, n_kv, head_dim, cap, 0, (int)s_max, 0, (int)s_max, window,
-                            position, err, err_cap);
+                            position, (float)softcap, err, err_cap);
 }
 
 int64_t b200i_act_mul(int64_t device, void *stream, float *out, const float *gate, const float *up, int64_t rows, int64_t width,
-                      int64_t in_ld, int64_t kind, char *err, int64_t err_cap) {
+                      int64_t in_ld, int64_t kind, int64_t interleaved, char *err, int64_t err_cap) {
     SEAM_PROLOGUE();
-    if (in_ld == 0) in_ld = width;
-    if (rows <= 0 || width <= 0 || in_ld < width || !out || !up || kind < ACT_SWIGLU || kind > ACT_GEGLU_TANH)
-        return fail(err, err_cap, "act_mul: bad arguments");
     const bool gated = kind == ACT_SWIGLU || kind == ACT_GEGLU_ERF || kind == ACT_GEGLU_TANH;
+    if (interleaved) {
+        if (!gated || !gate) return fail(err, err_cap, "act_mul: the interleaved layout is the gated MLP's");
+        if (in_ld == 0) in_ld = 2 * width;
+        if (in_ld < 2 * width) return fail(err, err_cap, "act_mul: bad arguments");
+        up = gate + 1;
+    } else if (in_ld == 0) {
+        in_ld = width;
+    }
+    if (rows <= 0 || width <= 0 || (!interleaved && in_ld < width) || !out || !up || kind < ACT_SWIGLU || kind > ACT_GEGLU_TANH)
+        return fail(err, err_cap, "act_mul: bad arguments");
     if (gated && !gate) return fail(err, err_cap, "act_mul: a gated MLP needs its gate projection");
-    act_mul_kernel<<<grid_for(rows * width, 256, sm_count(dev)), 256, 0, st>>>(out, gate, up, rows, width, in_ld, (int)kind);
+    act_mul_kernel<<<grid_for(rows * width, 256, sm_count(dev)), 256, 0, st>>>(out, gate, up, rows, width, in_ld, (int)kind, interleaved ? 2 : 1);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -1311,8 +1405,7 @@ static int64_t host_gemm_pipelined(int dev, HostPool &pool, float *c, const floa
             unsigned char *fai = fa + (size_t)tile0 * leaves * wpl;
             PackArgs paargs{pai, fai, dai, nullptr, (int)cnt, (int)k, leaf, leaves, wpl, 1, k8};
             launch_pack<W_F32>(paargs, pool.stream);
-            PackedGemmArgs p{pai, pb, fai, fb, dci, nullptr, (int)cnt, (int)n, (int)k, leaf, leaves, wpl, leaves, 1, tiles_n, (n % 4 == 0) ? 1 : 0,
-                             Epilogue{nullptr, EPI_ACT_NONE}};
+            PackedGemmArgs p{pai, pb, fai, fb, dci, nullptr, (int)cnt, (int)n, (int)k, leaf, leaves, wpl, leaves, 1, tiles_n, (n % 4 == 0) ? 1 : 0};
             dim3 grid((unsigned)(((cnt + PK_TILE - 1) / PK_TILE) * tiles_n), 1u);
             gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, pool.stream>>>(p);
             CUDA_TRY(cudaEventRecord(pool.ev[2 + 2 * i], pool.stream));
@@ -1335,7 +1428,7 @@ static int64_t host_gemm_pipelined(int dev, HostPool &pool, float *c, const floa
             launch_pack_b(pbargs, wkind, pool.stream);
             const int tiles_nc = (int)((cnt + PK_TILE - 1) / PK_TILE);
             PackedGemmArgs p{pa, pbi, fa, fbi, dci, nullptr, (int)m, (int)cnt, (int)k, leaf, leaves, wpl, leaves, 1, tiles_nc,
-                             (cnt % 4 == 0 && (m * x0) % 4 == 0) ? 1 : 0, Epilogue{nullptr, EPI_ACT_NONE}};
+                             (cnt % 4 == 0 && (m * x0) % 4 == 0) ? 1 : 0};
             dim3 grid((unsigned)(tiles_m * tiles_nc), 1u);
             gemm_packed_kernel<<<grid, PK_THREADS, PK_SMEM_BYTES, pool.stream>>>(p);
             CUDA_TRY(cudaEventRecord(pool.ev[2 + 2 * i], pool.stream));

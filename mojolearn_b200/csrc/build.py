@@ -13,6 +13,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libb200i.so")
+#: the negative-control build: every window admitted (-DB200I_SABOTAGE_ADMIT_ALWAYS); loaded only by the tests
+SABOTAGE_LIB = os.path.join(HERE, "libb200i_sabotage_admit.so")
 SOURCES = ["b200i.cu"]
 HEADERS = sorted(f for f in os.listdir(HERE) if f.endswith(".cuh")) + [os.path.join("..", "..", "include", "b200i.h")]
 NVCC_FLAGS = [
@@ -22,22 +24,24 @@ NVCC_FLAGS = [
 ]
 
 
-def stale():
-    if not os.path.exists(LIB):
+def stale(lib=LIB):
+    if not os.path.exists(lib):
         return True
-    t = os.path.getmtime(LIB)
+    t = os.path.getmtime(lib)
     deps = [os.path.join(HERE, s) for s in SOURCES + HEADERS] + [os.path.abspath(__file__)]
     return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
-    if not force and not stale():
-        return LIB
+def build(force=False, verbose=False, sabotage=False):
+    lib = SABOTAGE_LIB if sabotage else LIB
+    if not force and not stale(lib):
+        return lib
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + [os.path.join(HERE, s) for s in SOURCES] + ["-o", LIB]
+    cmd = [nvcc] + NVCC_FLAGS + (["-DB200I_SABOTAGE_ADMIT_ALWAYS"] if sabotage else []) + (["-Xptxas", "-v"] if verbose else []) \
+        + [os.path.join(HERE, s) for s in SOURCES] + ["-o", lib]
     subprocess.run(cmd, check=True)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, sabotage="--sabotage" in sys.argv))

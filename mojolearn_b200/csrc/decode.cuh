@@ -394,7 +394,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) decode_kernel(const GemmArgs g
         for (int idx = tid; idx < M * DEC_FOLD_ROWS; idx += NCONS) {
             const int r = idx % DEC_FOLD_ROWS, mi = idx / DEC_FOLD_ROWS;
             if (r < fold_valid && alive)
-                g.c[(size_t)mi * n + fold_row0 + r] = finish_cell(part[(size_t)mi * leaves * DEC_FOLD_ROWS + r], g.epi, fold_row0 + r, true);
+                g.c[(size_t)mi * n + fold_row0 + r] = nan_canon(ftz_hw(part[(size_t)mi * leaves * DEC_FOLD_ROWS + r]));
+            if (r < fold_valid && alive && epilogue_on(g.epi)) epilogue_cell(g.c + (size_t)mi * n + fold_row0 + r, g.epi, fold_row0 + r);
         }
         consumer_sync();
     }

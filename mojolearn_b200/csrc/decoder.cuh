@@ -39,16 +39,30 @@ constexpr int ACT_SWIGLU = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3,
 // Admission for the sum of squares: with every nonzero term at or above 2^-63 in
 // magnitude each square is a normal number, the accumulator only grows, and no
 // step result can be subnormal, so the bare fma is the contract's step.
+#ifdef B200I_SABOTAGE_ADMIT_ALWAYS
+constexpr unsigned NORM_ADMIT_MIN = 0u;
+#else
 constexpr unsigned NORM_ADMIT_MIN = (64u << 24) - 2u;
+#endif
 // With `delta` the row normalised is the residual sum ftz(ftz(src) + ftz(delta)) (seam S22 / S23), which is
 // also written to `sum_out`: the residual add and the norm that always follows it, in one pass over the row.
-__global__ void norm_rows_kernel(float *__restrict__ out, const float *__restrict__ src, const float *__restrict__ w,
-                                 const float *__restrict__ bias, long long rows, int dm, float eps, int kind,
-                                 const float *__restrict__ delta, float *__restrict__ sum_out) {
+constexpr int NORM_WREG = 16; // 128-bit words of the weight row a lane can hold: rows up to 2048 wide
+__global__ void __launch_bounds__(128) norm_rows_kernel(float *__restrict__ out, const float *__restrict__ src, const float *__restrict__ w,
+                                                        const float *__restrict__ bias, long long rows, int dm, float eps, int kind,
+                                                        const float *__restrict__ delta, float *__restrict__ sum_out) {
     extern __shared__ __align__(16) float norm_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= rows) return; // warps are independent: only warp-level barriers below
+    // The weight row does not depend on the chain: a lane asks for its words of it before anything else, so that the
+    // last phase finds them in registers instead of paying a round trip to L2 per 512 columns after the chain.
+    const bool w_early = (dm % 4 == 0) && dm <= NORM_WREG * 128 && ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
+    float4 wreg[NORM_WREG];
+    if (w_early) {
+#pragma unroll
+        for (int u = 0; u < NORM_WREG; u++)
+            wreg[u] = (lane * 4 + u * 128 < dm) ? __ldg(reinterpret_cast<const float4 *>(w + lane * 4 + u * 128)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     const int pitch = (dm + 3) & ~3;
     float *xs = norm_smem + (size_t)warp * pitch;
     const float *x = src + row * dm;
@@ -151,23 +165,35 @@ __global__ void norm_rows_kernel(float *__restrict__ out, const float *__restric
                          (!bias || (reinterpret_cast<uintptr_t>(bias) & 15) == 0);
     if (vec_out) {
         const bool has_bias = kind == NORM_LAYER && bias;
-        for (int j0 = lane * 4; j0 < dm; j0 += 4 * 128) {
-            float4 wv[4], bv[4];
+        auto finish4 = [&](int j, const float4 wq, const float4 bq) {
+            const float4 xv = *reinterpret_cast<const float4 *>(xs + j);
+            float4 y;
+            y.x = finish(xv.x, wq.x, bq.x); y.y = finish(xv.y, wq.y, bq.y);
+            y.z = finish(xv.z, wq.z, bq.z); y.w = finish(xv.w, wq.w, bq.w);
+            *reinterpret_cast<float4 *>(out + row * dm + j) = y;
+        };
+        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (w_early && !has_bias) { // the weights are already in registers
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const bool in = j0 + u * 128 < dm;
-                wv[u] = in ? *reinterpret_cast<const float4 *>(w + j0 + u * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
-                bv[u] = (in && has_bias) ? *reinterpret_cast<const float4 *>(bias + j0 + u * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int u = 0; u < NORM_WREG; u++) {
+                const int j = lane * 4 + u * 128;
+                if (j < dm) finish4(j, wreg[u], zero4);
             }
+        } else {
+            for (int j0 = lane * 4; j0 < dm; j0 += 4 * 128) {
+                float4 wv[4], bv[4];
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int j = j0 + u * 128;
-                if (j >= dm) break;
-                const float4 xv = *reinterpret_cast<const float4 *>(xs + j);
-                float4 y;
-                y.x = finish(xv.x, wv[u].x, bv[u].x); y.y = finish(xv.y, wv[u].y, bv[u].y);
-                y.z = finish(xv.z, wv[u].z, bv[u].z); y.w = finish(xv.w, wv[u].w, bv[u].w);
-                *reinterpret_cast<float4 *>(out + row * dm + j) = y;
+                for (int u = 0; u < 4; u++) {
+                    const bool in = j0 + u * 128 < dm;
+                    wv[u] = in ? *reinterpret_cast<const float4 *>(w + j0 + u * 128) : zero4;
+                    bv[u] = (in && has_bias) ? *reinterpret_cast<const float4 *>(bias + j0 + u * 128) : zero4;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int j = j0 + u * 128;
+                    if (j >= dm) break;
+                    finish4(j, wv[u], bv[u]);
+                }
             }
         }
     } else {
@@ -235,6 +261,55 @@ __global__ void norm_kernel(float *__restrict__ out, const float *__restrict__ s
 }
 
 // ---- rotary table and application -----------------------------------------------------------
+// The option record of the rotary table (transformer/block_options.mojo:40-70 of the reference): scaling 0 none,
+// 1 linear (one division of the inverse frequency by the factor), 2 llama3 (rescaling by wavelength), spelled as
+// transformer/checks/transformer_oracle.mojo:423-497: every division the portable one, both products of the
+// interpolation rounded on their own, the final add unfused. `rope_dim` = rotated columns of a head.
+struct RopeOptions {
+    float theta;
+    int scaling;
+    float factor, low_freq_factor, high_freq_factor;
+    int original_max_positions;
+};
+__device__ __forceinline__ float rope_inv_freq(int i, int rope_dim, const RopeOptions &o) {
+    const float e = ftz_bits(p_divf((float)(2 * i), (float)rope_dim));
+    float inv = ftz_bits(p_divf(1.0f, p_powf(o.theta, e)));
+    if (o.scaling == 1) {
+        inv = ftz_bits(p_divf(inv, ftz_bits(o.factor)));
+    } else if (o.scaling == 2) {
+        const float factor = ftz_bits(o.factor), lo_f = ftz_bits(o.low_freq_factor), hi_f = ftz_bits(o.high_freq_factor);
+        const float old = (float)o.original_max_positions;
+        const float low_wl = ftz_bits(p_divf(old, lo_f)), high_wl = ftz_bits(p_divf(old, hi_f));
+        const float wl = ftz_bits(p_divf(__uint_as_float(0x40C90FDBu), inv)); // 2 pi
+        float inv_l = inv;
+        if (wl > low_wl) inv_l = ftz_bits(p_divf(inv, factor));
+        if (!(wl < high_wl) && !(wl > low_wl)) {
+            const float ratio = ftz_bits(p_divf(old, wl));
+            const float num = ftz_bits(__fsub_rn(ratio, lo_f)), den = ftz_bits(__fsub_rn(hi_f, lo_f));
+            const float smooth = ftz_bits(p_divf(num, den));
+            const float one_minus = ftz_bits(__fsub_rn(1.0f, smooth));
+            float t1 = ftz_bits(__fmul_rn(one_minus, inv_l));
+            t1 = ftz_bits(p_divf(t1, factor));
+            const float t2 = ftz_bits(__fmul_rn(smooth, inv_l));
+            inv_l = ftz_bits(__fadd_rn(ftz_bits(t1), ftz_bits(t2)));
+        }
+        inv = inv_l;
+    }
+    return inv;
+}
+__global__ void rope_table_opts_kernel(float *__restrict__ cosv, float *__restrict__ sinv, int pos0, int l, int rope_dim, RopeOptions o,
+                                       const int *__restrict__ pos_dev) {
+    if (pos_dev) pos0 = *pos_dev;
+    const int half = rope_dim / 2;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= l * half) return;
+    const int p = idx / half, i = idx % half;
+    const float inv = rope_inv_freq(i, rope_dim, o);
+    const float angle = ftz_bits(__fmul_rn((float)(pos0 + p), ftz_bits(inv)));
+    cosv[idx] = ftz_bits(p_cosf(angle));
+    sinv[idx] = ftz_bits(p_sinf(angle));
+}
+
 __global__ void rope_table_kernel(float *__restrict__ cosv, float *__restrict__ sinv, int pos0, int l, int head_dim,
                                   float theta, const int *__restrict__ pos_dev) {
     if (pos_dev) pos0 = *pos_dev;
@@ -251,12 +326,14 @@ __global__ void rope_table_kernel(float *__restrict__ cosv, float *__restrict__ 
 
 // `ld` is the row pitch of src in floats (the projections may be column blocks of one fused product).
 __global__ void rope_apply_kernel(float *__restrict__ out, const float *__restrict__ src, const float *__restrict__ cosv,
-                                  const float *__restrict__ sinv, long long m, int l, int n_head, int hd, long long ld) {
+                                  const float *__restrict__ sinv, long long m, int l, int n_head, int hd, long long ld, int rd) {
+    // rd = rotated columns of a head (partial rotary, transformer_oracle.mojo:1433-1440): the rest pass through, flushed
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long width = (long long)n_head * hd;
     if (idx >= m * width) return;
     const long long t = idx / width, si = t * ld + idx % width;
-    const int j = (int)(idx % hd), half = hd / 2, li = (int)(t % l);
+    const int j = (int)(idx % hd), half = rd / 2, li = (int)(t % l);
+    if (j >= rd) { out[idx] = ftz_bits(src[si]); return; }
     const int ci = j < half ? j : j - half;
     const float partner = j < half ? -ftz_bits(src[si + half]) : ftz_bits(src[si - half]);
     const float c = ftz_bits(cosv[li * half + ci]), s = ftz_bits(sinv[li * half + ci]);
@@ -286,20 +363,22 @@ __global__ void kv_append_kernel(float *__restrict__ cache, const float *__restr
 __global__ void qkv_rope_cache_kernel(float *__restrict__ qr, float *__restrict__ kcache, float *__restrict__ vcache,
                                       const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                       long long ldq, long long ldkv, const float *__restrict__ cosv, const float *__restrict__ sinv, int b, int l,
-                                      int nh, int nkv, int hd, int cap, int pos0, const int *__restrict__ pos_dev, int rope) {
+                                      int nh, int nkv, int hd, int cap, int pos0, const int *__restrict__ pos_dev, int rope, int rd) {
     if (pos_dev) pos0 = *pos_dev;
     const long long wq = (long long)nh * hd, wk = (long long)nkv * hd, per_row = wq + 2 * wk;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)b * l * per_row) return;
     const long long t = idx / per_row;
     const long long c = idx % per_row;
-    const int li = (int)(t % l), bb = (int)(t / l), half = hd / 2;
+    const int li = (int)(t % l), bb = (int)(t / l), half = rd / 2;
     const float *src = c < wq ? q : (c < wq + wk ? k : v);
     const long long col = c < wq ? c : (c < wq + wk ? c - wq : c - wq - wk);
     const long long si = t * (c < wq ? ldq : ldkv) + col;
     const int j = (int)(col % hd);
     float val;
-    if (c < wq + wk && rope) {
+    if (c < wq + wk && rope && j >= rd) {
+        val = ftz_bits(src[si]); // partial rotary: a column past the rotated ones passes through, flushed on load
+    } else if (c < wq + wk && rope) {
         const int ci = j < half ? j : j - half;
         const float partner = j < half ? -ftz_bits(src[si + half]) : ftz_bits(src[si - half]);
         const float cs = ftz_bits(cosv[li * half + ci]), sn = ftz_bits(sinv[li * half + ci]);
@@ -336,6 +415,20 @@ __device__ __forceinline__ void attn_geometry(const int *pos_dev, int l, int cap
 }
 __global__ void advance_position_kernel(int *pos_dev, int delta) { *pos_dev += delta; }
 
+
+// Score seams S12 (scale) and the optional soft cap between it and the mask (transformer_oracle.mojo:2269-2281,
+// Gemma 2's attn_logit_softcapping): cap * tanh(score / cap), one portable division, one portable tanh and one
+// product, each flushed. `softcap` 0 (all bits) = none.
+__device__ __forceinline__ float score_scale_cap(float dot, float scale, float softcap) {
+    float sc = ftz_bits(__fmul_rn(ftz_hw(dot), scale));
+    if (__float_as_uint(softcap) != 0u) {
+        const float cap = ftz_bits(softcap);
+        const float th = ftz_bits(p_tanhf(ftz_bits(p_divf(sc, cap))));
+        sc = ftz_bits(__fmul_rn(th, cap));
+    }
+    return sc;
+}
+
 // ---- attention scores -------------------------------------------------------------------------
 // scores[b, h, qi, j] = ftz(ftz(ftz(q . k) * scale) + fill), the dot being one
 // gemm fp32.v1 leaf (k = head_dim <= 128: a single serial chain from +0.0).
@@ -344,7 +437,7 @@ constexpr int ATT_T = 64, ATT_KC = 32;
 __global__ void __launch_bounds__(256) attn_scores_kernel(float *__restrict__ scores, const float *__restrict__ q,
                                                           const float *__restrict__ kcache, int b, int l, int nh, int nkv, int hd,
                                                           int cap, int key_lo, int s, int own0, int window,
-                                                          const int *__restrict__ pos_dev) {
+                                                          const int *__restrict__ pos_dev, float softcap) {
     attn_geometry(pos_dev, l, cap, window, key_lo, s, own0);
     if ((int)blockIdx.x * ATT_T >= s) return;
     // the attention scale, ftz(rsqrt(head_dim)) in the portable spelling: a pure function of head_dim
@@ -362,7 +455,9 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(float *__restrict__ sc
     // operand word of the tile is finite and below 2^40 in magnitude, |score| < 2^88 is under half an ulp of
     // FLT_MAX (2^103), so the sum IS -FLT_MAX and the dot products need not be formed.
     const int q_hi = min(q0 + ATT_T, l) - 1;
-    const bool tile_masked = j0 > own0 + q_hi || (window > 0 && j0 + ATT_T - 1 < own0 + q0 - window + 1);
+    // (with a soft cap the scores are bounded by the cap instead; the shortcut is simply not taken then)
+    const bool tile_masked = __float_as_uint(softcap) == 0u &&
+                             (j0 > own0 + q_hi || (window > 0 && j0 + ATT_T - 1 < own0 + q0 - window + 1));
     if (tile_masked) {
         bool small = true;
         const int warp = tid >> 5, lane = tid & 31;
@@ -458,7 +553,7 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(float *__restrict__ sc
         for (int jj = 0; jj < 4; jj++) {
             const int j = j0 + tx * 4 + jj;
             if (j >= s) continue;
-            const float sc = ftz_bits(__fmul_rn(ftz_hw(acc[i][jj]), scale));
+            const float sc = score_scale_cap(acc[i][jj], scale, softcap);
             const float fill = (j < jlo || j > jhi) ? mfill : 0.0f;
             scores[((long long)bh * l + qi) * s + j] = ftz_bits(__fadd_rn(sc, fill));
         }
@@ -507,7 +602,7 @@ template <int LQ>
 __global__ void __launch_bounds__(128) attn_scores_small_kernel(float *__restrict__ scores, const float *__restrict__ q,
                                                                 const float *__restrict__ kcache, int b, int l, int nh, int nkv,
                                                                 int hd, int cap, int key_lo, int s, int own0, int window,
-                                                                const int *__restrict__ pos_dev) {
+                                                                const int *__restrict__ pos_dev, float softcap) {
     attn_geometry(pos_dev, l, cap, window, key_lo, s, own0);
     if ((int)blockIdx.x * 128 >= s) return;
     extern __shared__ __align__(16) float att_smem[];
@@ -591,7 +686,7 @@ __global__ void __launch_bounds__(128) attn_scores_small_kernel(float *__restric
         int jlo = 0, jhi = own0 + i;
         if (jhi > s - 1) jhi = s - 1;
         if (window > 0) { jlo = own0 + i - window + 1; if (jlo < 0) jlo = 0; }
-        const float sc = ftz_bits(__fmul_rn(ftz_hw(acc[i]), scale));
+        const float sc = score_scale_cap(acc[i], scale, softcap);
         scores[((long long)bh * l + i) * s + j] = ftz_bits(__fadd_rn(sc, (j < jlo || j > jhi) ? mfill : 0.0f));
     }
 }
@@ -840,21 +935,23 @@ __global__ void __launch_bounds__(32 * CTX_WARPS) attn_context_kernel(float *__r
 // copy needs; those caches go through per-thread cp.async instead.
 // Every wait on an mbarrier is bounded; one that runs out sets the status word read by
 // b200i_decode_status (value 3) and the kernel carries on to its end.
-constexpr int CTX_NB = 32, CTX_ST = 3; // three stages and a 4K-key weight row fit four CTAs on an SM
-inline size_t attn_context_row_smem(int s_grid, int hd) {
-    return ((size_t)((s_grid + 3) & ~3) + (size_t)CTX_ST * CTX_NB * hd) * sizeof(float);
+// Three stages and a 4K-key weight row fit four CTAs on an SM. A call with few CTAs (a head-sharded rank, a small
+// batch) gets up to CTX_ST_MAX stages instead: what bounds it is the bytes one CTA keeps in flight.
+constexpr int CTX_NB = 32, CTX_ST = 3, CTX_ST_MAX = 12;
+inline size_t attn_context_row_smem(int s_grid, int hd, int stages = CTX_ST) {
+    return ((size_t)((s_grid + 3) & ~3) + (size_t)stages * CTX_NB * hd) * sizeof(float);
 }
 __global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict__ ctx, float *__restrict__ scores,
                                                                 const float *__restrict__ vcache, int b, int l, int nh, int nkv,
                                                                 int hd, int cap, int key_lo, int s, int own0, int window,
-                                                                const int *__restrict__ pos_dev, int s_grid) {
+                                                                const int *__restrict__ pos_dev, int s_grid, int stages) {
     attn_geometry(pos_dev, l, cap, window, key_lo, s, own0);
     extern __shared__ __align__(16) float ctx_smem[];
     float *wrow = ctx_smem;                        // [s] weights of this row
-    float *ring = ctx_smem + ((s_grid + 3) & ~3);  // [CTX_ST][CTX_NB * hd]
+    float *ring = ctx_smem + ((s_grid + 3) & ~3);  // [stages][CTX_NB * hd]
     __shared__ unsigned red[4];
     __shared__ float den_s;
-    __shared__ __align__(8) unsigned long long full[CTX_ST];
+    __shared__ __align__(8) unsigned long long full[CTX_ST_MAX];
     const int r = blockIdx.x; // (bh, qi)
     const int bh = r / l, qi = r % l, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -864,31 +961,30 @@ __global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict
     if (window > 0) { jlo = own0 + qi - window + 1; if (jlo < 0) jlo = 0; }
     const float *vbase = vcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
     const bool bulk = (hd % 4) == 0;
+    if (!bulk) stages = CTX_ST; // the per-thread copies count their groups at compile time
     const int nstages = (jhi - jlo + CTX_NB) / CTX_NB;
     if (bulk && tid == 0) {
-#pragma unroll
-        for (int i = 0; i < CTX_ST; i++) mbar_init(&full[i], 1);
+        for (int i = 0; i < stages; i++) mbar_init(&full[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    auto issue = [&](int k) { // stage k: keys jlo + 32k ..., into slot k % CTX_ST
+    auto issue = [&](int k) { // stage k: keys jlo + 32k ..., into slot k % stages
         if (bulk) {
             if (tid == 0 && k < nstages) {
                 const int first = jlo + k * CTX_NB, keys = min(CTX_NB, jhi - first + 1);
                 const unsigned bytes = (unsigned)(keys * hd) * 4u;
-                mbar_expect_tx(&full[k % CTX_ST], bytes);
-                bulk_copy_g2s(ring + (size_t)(k % CTX_ST) * CTX_NB * hd, vbase + (long long)first * hd, bytes, &full[k % CTX_ST]);
+                mbar_expect_tx(&full[k % stages], bytes);
+                bulk_copy_g2s(ring + (size_t)(k % stages) * CTX_NB * hd, vbase + (long long)first * hd, bytes, &full[k % stages]);
             }
         } else { // always one commit, so that the groups count stages
             if (k < nstages) {
                 const int first = jlo + k * CTX_NB, keys = min(CTX_NB, jhi - first + 1);
-                cp_async_floats(ring + (size_t)(k % CTX_ST) * CTX_NB * hd, vbase + (long long)first * hd, keys * hd, false, tid, 128);
+                cp_async_floats(ring + (size_t)(k % stages) * CTX_NB * hd, vbase + (long long)first * hd, keys * hd, false, tid, 128);
             }
             cp_async_commit();
         }
     };
-#pragma unroll
-    for (int k = 0; k < CTX_ST - 1; k++) issue(k);
+    for (int k = 0; k < stages - 1; k++) issue(k);
     unsigned best = 0u;
     for (int j = tid; j < s; j += 128) best = max(best, order_key(ftz_bits(row[j])));
 #pragma unroll
@@ -920,21 +1016,41 @@ __global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict
         row[j] = wgt;
     }
     float acc = 0.f;
+    bool clean = true; // every step of this thread's chain so far was an admitted bare fma
     for (int k = 0; k < nstages; k++) {
-        issue(k + CTX_ST - 1); // refills the slot the previous turn finished with
+        issue(k + stages - 1); // refills the slot the previous turn finished with
         if (bulk) {
-            if (!mbar_wait(&full[k % CTX_ST], (unsigned)(k / CTX_ST) & 1u) && lane == 0) atomicExch(&g_decode_status, 3);
+            if (!mbar_wait(&full[k % stages], (unsigned)(k / stages) & 1u) && lane == 0) atomicExch(&g_decode_status, 3);
         } else {
             cp_async_wait<CTX_ST - 1>(); // this thread's copies of stage k have landed
         }
         __syncthreads(); // everyone's copies are visible (the first turn also orders the weights above)
         if (tid < hd) {
-            const float *vs = ring + (size_t)(k % CTX_ST) * CTX_NB * hd + tid;
+            const float *vs = ring + (size_t)(k % stages) * CTX_NB * hd + tid;
             const int first = jlo + k * CTX_NB;
             if (first + CTX_NB - 1 <= jhi) {
+                // A thread's chain reads its own feature of the 32 values and the 32 weights: when all of them pass
+                // the product's admission test and every earlier step of the chain was admitted too, the bare fma is
+                // the contract's step (no result can be subnormal). The walk runs bare while folding the key and is
+                // redone with the flushed step only when the key fails.
+                const float before = acc;
+                unsigned key = 0xFFFFFFFFu;
+                if (clean) {
 #pragma unroll
-                for (int u = 0; u < CTX_NB; u++) acc = step_flush(wrow[first + u], ftz_bits(vs[u * hd]), acc);
+                    for (int u = 0; u < CTX_NB; u++) {
+                        const float wj = wrow[first + u], vj = vs[u * hd];
+                        key = min(key, min(admit_key(wj), admit_key(vj)));
+                        acc = step_bare(wj, vj, acc);
+                    }
+                }
+                if (!clean || key < ADMIT_MIN) {
+                    clean = false;
+                    acc = before;
+#pragma unroll
+                    for (int u = 0; u < CTX_NB; u++) acc = step_flush(wrow[first + u], ftz_bits(vs[u * hd]), acc);
+                }
             } else {
+                clean = false;
                 for (int u = 0; first + u <= jhi; u++) acc = step_flush(wrow[first + u], ftz_bits(vs[u * hd]), acc);
             }
         }
@@ -943,14 +1059,260 @@ __global__ void __launch_bounds__(128) attn_context_row_kernel(float *__restrict
     if (tid < hd) ctx[((long long)bb * l + qi) * ((long long)nh * hd) + (long long)h * hd + tid] = acc;
 }
 
+// ---- decode-step attention in one kernel ------------------------------------------------------------
+// Scores, softmax and value sum of up to eight query rows of one (sequence, head) in ONE CTA: the masked score rows
+// live in shared memory and never reach global memory (the reference's fused attention: "same fold order, nothing
+// materialised in HBM", transformer/impl/llama/fused_attention.mojo:5 of the reference). The seams and their order
+// are those of attn_scores_small_kernel and attn_context_row_kernel above, spelled once more around one shared
+// score buffer:
+//   scores   a warp stages the cache rows of `kkeys` keys (up to 32) with cp.async (`nkb` tiles in flight per warp) and
+//            lane j walks row j: one serial chain per (query, key) over head_dim, bare while its operands pass
+//            admission, flushed otherwise; S12 scale, S13 mask ADD;
+//   softmax  S14 row max over the WHOLE row, S15-S16 exp, S17 the serial denominator (one warp per row, shuffle
+//            rounds), S18 one division per weight;
+//   values   thread d walks feature d down the keys, one chain per query row, the cache rows of `vkeys` keys moved by
+//            one bulk copy into a ring of `stages` slots (the key tiles' shared memory, reused).
+// The host picks kkeys, nkb, vkeys and stages from the number of CTAs in the call: enough CTAs per SM that the call
+// is one wave, and whatever shared memory that leaves each CTA is spent on bytes in flight.
+// head_dim must be a multiple of 4 and at most 128. Every mbarrier wait is bounded (status 3).
+constexpr int ATD_THREADS = 128, ATD_WARPS = 4;
+__host__ __device__ inline size_t atd_region_floats(int hd, int kkeys, int nkb, int vkeys, int stages) {
+    const size_t ktiles = (size_t)ATD_WARPS * nkb * kkeys * ATT_KT_PITCH, ring = (size_t)stages * vkeys * hd;
+    return ktiles > ring ? ktiles : ring;
+}
+inline size_t attn_decode_smem(int lq, int s_grid, int hd, int kkeys, int nkb, int vkeys, int stages) {
+    return ((size_t)lq * K_LEAF_MIN + (size_t)lq * ((s_grid + 3) & ~3) + atd_region_floats(hd, kkeys, nkb, vkeys, stages)) * sizeof(float);
+}
+constexpr int ATD_MAX_STAGES = 12;
+template <int LQ>
+__global__ void __launch_bounds__(ATD_THREADS) attn_decode_kernel(float *__restrict__ ctx, const float *__restrict__ q,
+                                                                  const float *__restrict__ kcache, const float *__restrict__ vcache,
+                                                                  int b, int l, int nh, int nkv, int hd, int cap, int key_lo, int s,
+                                                                  int own0, int window, const int *__restrict__ pos_dev, int s_grid,
+                                                                  int kkeys, int nkb, int vkeys, int stages, float softcap) {
+    attn_geometry(pos_dev, l, cap, window, key_lo, s, own0);
+    extern __shared__ __align__(16) float atd_smem[];
+    const int spitch = (s_grid + 3) & ~3;
+    float (*qs)[K_LEAF_MIN] = reinterpret_cast<float (*)[K_LEAF_MIN]>(atd_smem);
+    float *sc = atd_smem + LQ * K_LEAF_MIN;            // [LQ][spitch]: masked scores, then exponentials, then weights
+    float *region = sc + (size_t)LQ * spitch;          // key tiles first, the value ring afterwards
+    __shared__ unsigned red[LQ][ATD_WARPS];
+    __shared__ float fm_s[LQ], den_s[LQ], scale_s;
+    __shared__ __align__(8) unsigned long long full[ATD_MAX_STAGES];
+    const int bh = blockIdx.x, bb = bh / nh, h = bh % nh, kv = h / (nh / nkv);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float *kbase = kcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
+    const float *vbase = vcache + (((long long)bb * nkv + kv) * cap + key_lo) * hd;
+    const long long qw = (long long)nh * hd;
+    const float mfill = __uint_as_float(0xFF7FFFFFu);
+
+    // ---- the query rows, flushed, and their admission key ----
+    if (tid == 0) {
+        scale_s = ftz_bits(p_rsqrtf((float)hd)); // a pure function of head_dim: one thread spells it
+        for (int i = 0; i < stages; i++) mbar_init(&full[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    unsigned qkey = 0xFFFFFFFFu;
+    for (int idx = tid; idx < LQ * hd; idx += ATD_THREADS) {
+        const int i = idx / hd, p = idx % hd;
+        const float v = i < l ? ftz_bits(q[((long long)bb * l + i) * qw + (long long)h * hd + p]) : 0.f;
+        qkey = min(qkey, admit_key(v));
+        qs[i][p] = v;
+    }
+    const bool q_ok = __syncthreads_and(qkey >= ADMIT_MIN);
+    const float scale = scale_s;
+
+    // ---- scores: this warp's key tiles, NKB of them in flight ----
+    const int tiles = (s + kkeys - 1) / kkeys;
+    float *kt_w = region + (size_t)warp * nkb * kkeys * ATT_KT_PITCH;
+    auto fetch = [&](int n) { // the n-th tile of this warp into buffer n % nkb; always one commit group
+        const int tile = warp + n * ATD_WARPS;
+        if (tile < tiles) {
+            const int j0 = tile * kkeys, rows = min(kkeys, s - j0);
+            float *dst = kt_w + (size_t)(n % nkb) * kkeys * ATT_KT_PITCH + lane * 4;
+            const float *src = kbase + (long long)j0 * hd + lane * 4;
+            if (lane * 4 < hd)
+                for (int r = 0; r < rows; r++) cp_async16(dst + r * ATT_KT_PITCH, src + (long long)r * hd);
+        }
+        cp_async_commit();
+    };
+    for (int n = 0; n < nkb - 1; n++) fetch(n);
+    for (int n = 0; warp + n * ATD_WARPS < tiles; n++) {
+        fetch(n + nkb - 1);
+        if (nkb == 1) cp_async_wait<0>();
+        else if (nkb == 2) cp_async_wait<1>();
+        else cp_async_wait<2>();
+        __syncwarp();
+        const int j0 = (warp + n * ATD_WARPS) * kkeys, j = j0 + lane;
+        const float *krow = kt_w + (size_t)(n % nkb) * kkeys * ATT_KT_PITCH + (size_t)lane * ATT_KT_PITCH;
+        float acc[LQ];
+        bool exact = false;
+        if (lane < kkeys && j < s) {
+            if (q_ok) {
+                unsigned kkey = 0xFFFFFFFFu;
+#pragma unroll
+                for (int i = 0; i < LQ; i++) acc[i] = 0.f;
+#pragma unroll 8
+                for (int p = 0; p < hd; p += 4) {
+                    const float4 kvv = *reinterpret_cast<const float4 *>(krow + p);
+                    kkey = min(kkey, key_of4(kvv));
+#pragma unroll
+                    for (int i = 0; i < LQ; i++) {
+                        const float4 qv = *reinterpret_cast<const float4 *>(&qs[i][p]);
+                        acc[i] = step_bare(qv.x, kvv.x, acc[i]);
+                        acc[i] = step_bare(qv.y, kvv.y, acc[i]);
+                        acc[i] = step_bare(qv.z, kvv.z, acc[i]);
+                        acc[i] = step_bare(qv.w, kvv.w, acc[i]);
+                    }
+                }
+                exact = kkey >= ADMIT_MIN;
+            }
+            if (!exact) {
+#pragma unroll
+                for (int i = 0; i < LQ; i++) acc[i] = 0.f;
+                for (int p = 0; p < hd; p++) {
+                    const float kvv = ftz_bits(krow[p]);
+#pragma unroll
+                    for (int i = 0; i < LQ; i++) acc[i] = step_flush(qs[i][p], kvv, acc[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < LQ; i++) {
+                if (i >= l) break;
+                int jlo = 0, jhi = own0 + i;
+                if (jhi > s - 1) jhi = s - 1;
+                if (window > 0) { jlo = own0 + i - window + 1; if (jlo < 0) jlo = 0; }
+                const float v = score_scale_cap(acc[i], scale, softcap);
+                sc[(size_t)i * spitch + j] = ftz_bits(__fadd_rn(v, (j < jlo || j > jhi) ? mfill : 0.0f));
+            }
+        }
+        __syncwarp(); // the buffer is free for the fetch of the next turn
+    }
+    cp_async_wait<0>();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the bulk copies below rewrite memory these threads wrote and read
+    __syncthreads(); // every score is in place; the key tiles are dead and their memory becomes the value ring
+
+    // ---- the value ring starts while the softmax runs ----
+    int jlo_all = 0, jhi_all = min(own0 + l - 1, s - 1); // the keys any row of this call can see
+    if (window > 0) jlo_all = max(own0 - window + 1, 0);
+    const int nstages = (jhi_all - jlo_all + vkeys) / vkeys;
+    auto issue = [&](int k) { // stage k: keys jlo_all + vkeys * k ..., into slot k % stages
+        if (tid == 0 && k < nstages) {
+            const int first = jlo_all + k * vkeys, keys = min(vkeys, jhi_all - first + 1);
+            const unsigned bytes = (unsigned)(keys * hd) * 4u;
+            mbar_expect_tx(&full[k % stages], bytes);
+            bulk_copy_g2s(region + (size_t)(k % stages) * vkeys * hd, vbase + (long long)first * hd, bytes, &full[k % stages]);
+        }
+    };
+    for (int k = 0; k < stages - 1; k++) issue(k);
+
+    // ---- softmax, row by row seams, rows side by side ----
+#pragma unroll
+    for (int i = 0; i < LQ; i++) {
+        if (i >= l) break;
+        unsigned best = 0u;
+        for (int j = tid; j < s; j += ATD_THREADS) best = max(best, order_key(ftz_bits(sc[(size_t)i * spitch + j])));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, off));
+        if (lane == 0) red[i][warp] = best;
+    }
+    __syncthreads();
+    if (tid < LQ && tid < l) fm_s[tid] = ftz_bits(order_unkey(max(max(red[tid][0], red[tid][1]), max(red[tid][2], red[tid][3]))));
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < LQ; i++) {
+        if (i >= l) break;
+        int jlo = 0, jhi = min(own0 + i, s - 1);
+        if (window > 0) jlo = max(own0 + i - window + 1, 0);
+        const float fm = fm_s[i];
+        float *row = sc + (size_t)i * spitch;
+        for (int j = jlo + tid; j <= jhi; j += ATD_THREADS) row[j] = ftz_bits(p_expf(ftz_bits(__fsub_rn(ftz_bits(row[j]), fm))));
+    }
+    __syncthreads();
+    for (int i = warp; i < l; i += ATD_WARPS) { // S17: serial ascending, every value already flushed; one warp per row
+        int jlo = 0, jhi = min(own0 + i, s - 1);
+        if (window > 0) jlo = max(own0 + i - window + 1, 0);
+        const float *row = sc + (size_t)i * spitch;
+        float den = 0.f;
+        for (int j0 = jlo; j0 <= jhi; j0 += 32) {
+            const float e = (j0 + lane <= jhi) ? row[j0 + lane] : 0.f;
+            if (j0 + 31 <= jhi) {
+#pragma unroll
+                for (int t = 0; t < 32; t++) den = add_flushed(den, __shfl_sync(0xFFFFFFFFu, e, t));
+            } else {
+                for (int t = 0; t < jhi - j0 + 1; t++) den = add_flushed(den, __shfl_sync(0xFFFFFFFFu, e, t));
+            }
+        }
+        if (lane == 0) den_s[i] = den;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < LQ; i++) {
+        if (i >= l) break;
+        int jlo = 0, jhi = min(own0 + i, s - 1);
+        if (window > 0) jlo = max(own0 + i - window + 1, 0);
+        const float den = den_s[i];
+        float *row = sc + (size_t)i * spitch;
+        for (int j = jlo + tid; j <= jhi; j += ATD_THREADS) row[j] = ftz_bits(p_divf(row[j], den));
+    }
+    // (the first turn's barrier below orders the weights before the chains read them)
+
+    // ---- S19: thread d walks feature d down the keys, one chain per query row ----
+    float acc[LQ];
+    int rlo[LQ], rhi[LQ];
+#pragma unroll
+    for (int i = 0; i < LQ; i++) {
+        acc[i] = 0.f;
+        rhi[i] = i < l ? min(own0 + i, s - 1) : -1;
+        rlo[i] = (window > 0) ? max(own0 + i - window + 1, 0) : 0;
+    }
+    bool alive = true;
+    for (int k = 0; k < nstages; k++) {
+        issue(k + stages - 1); // refills the slot the previous turn finished with
+        if (alive && !mbar_wait(&full[k % stages], (unsigned)(k / stages) & 1u)) {
+            if (lane == 0) atomicExch(&g_decode_status, 3);
+            alive = false;
+        }
+        __syncthreads();
+        if (tid < hd) {
+            const float *vs = region + (size_t)(k % stages) * vkeys * hd + tid;
+            const int first = jlo_all + k * vkeys;
+            const int keys = min(vkeys, jhi_all - first + 1);
+            if (LQ == 1) {
+                int u = 0;
+                for (; u + 16 <= keys; u += 16) {
+#pragma unroll
+                    for (int t = 0; t < 16; t++) acc[0] = step_flush(sc[first + u + t], ftz_bits(vs[(u + t) * hd]), acc[0]);
+                }
+                for (; u < keys; u++) acc[0] = step_flush(sc[first + u], ftz_bits(vs[u * hd]), acc[0]);
+            } else {
+                for (int u = 0; u < keys; u++) {
+                    const float v = ftz_bits(vs[u * hd]);
+                    const int j = first + u;
+#pragma unroll
+                    for (int i = 0; i < LQ; i++)
+                        if (j >= rlo[i] && j <= rhi[i]) acc[i] = step_flush(sc[(size_t)i * spitch + j], v, acc[i]);
+                }
+            }
+        }
+        __syncthreads(); // the slot is free for the copy the next turn issues
+    }
+    if (tid < hd) {
+#pragma unroll
+        for (int i = 0; i < LQ; i++)
+            if (i < l) ctx[((long long)bb * l + i) * qw + (long long)h * hd + tid] = acc[i];
+    }
+}
+
 // ---- elementwise seams --------------------------------------------------------------------------
-// out is [rows, width] contiguous; gate and up have row pitch ld
-__global__ void act_mul_kernel(float *__restrict__ out, const float *__restrict__ gate, const float *__restrict__ up,
-                               long long rows, long long width, long long ld, int kind) {
+// out is [rows, width] contiguous; gate and up have row pitch ld and column step cs (2 when they are the even and
+// odd columns of one matrix: a product over interleaved weight rows)
+__global__ void act_mul_kernel(float *__restrict__ out, const float *gate, const float *up, long long rows, long long width, long long ld,
+                               int kind, int cs) {
     const long long stride = (long long)gridDim.x * blockDim.x, count = rows * width;
     const bool gated = kind == ACT_SWIGLU || kind == ACT_GEGLU_ERF || kind == ACT_GEGLU_TANH;
     for (long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x; o < count; o += stride) {
-        const long long i = (o / width) * ld + o % width;
+        const long long i = (o / width) * ld + (o % width) * cs;
         const float z = ftz_bits(gated ? gate[i] : up[i]);
         float a;
         if (kind == ACT_SWIGLU || kind == ACT_SILU) a = ftz_bits(p_siluf(z));

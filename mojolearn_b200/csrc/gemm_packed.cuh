@@ -131,7 +131,6 @@ struct PackedGemmArgs {
     float *c, *ws;
     int m, n, k, leaf, leaves, wpl;
     int group_leaves, groups, tiles_n, vec_c;
-    Epilogue epi;
 };
 
 __global__ void __launch_bounds__(PK_THREADS, 2) gemm_packed_kernel(const PackedGemmArgs g) {
@@ -309,9 +308,8 @@ __global__ void __launch_bounds__(PK_THREADS, 2) gemm_packed_kernel(const Packed
         for (int jr = 0; jr < 2; jr++) {
             float vals[4];
 #pragma unroll
+            for (int e = 0; e < 4; e++) vals[e] = nan_canon(ftz_hw(v[i * TN + jr * 4 + e]));
             const int col = bn0 + jr * 64 + tx * 4;
-#pragma unroll
-            for (int e = 0; e < 4; e++) vals[e] = finish_cell(v[i * TN + jr * 4 + e], g.epi, col + e < g.n ? col + e : 0, g.groups == 1);
             if (row < g.m) {
                 float *dst = out + (size_t)row * (size_t)g.n + col;
                 if (g.vec_c && col + 3 < g.n) *reinterpret_cast<float4 *>(dst) = make_float4(vals[0], vals[1], vals[2], vals[3]);

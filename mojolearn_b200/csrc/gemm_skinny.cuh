@@ -295,14 +295,29 @@ __global__ void __launch_bounds__(SK_THREADS, MINB) gemm_skinny_kernel(const Gem
                 for (int c = 0; c < CELLS; c++) v[c] = fold_add(stack[lvl][c], v[c]);
             }
     }
+    if (CPT == 2 && g.groups == 1 && epilogue_pairs(g.epi)) { // this thread's two columns are one (gate, up) pair
+        const int col = bn0 + col_of(0);
+        if (col + 1 < g.n)
+            for (int i = 0; i < TR && row0 + i < g.m; i++)
+                g.c[(size_t)(row0 + i) * (g.n / 2) + col / 2] =
+                    epilogue_pair_apply(nan_canon(ftz_hw(v[i * CPT])), nan_canon(ftz_hw(v[i * CPT + 1])), g.epi.bias, g.epi.act, col / 2);
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < TR; i++) {
         if (row0 + i >= g.m) break;
 #pragma unroll
         for (int c = 0; c < CPT; c++) {
             const int col = bn0 + col_of(c);
-            if (col < g.n) out[(size_t)(row0 + i) * g.n + col] = finish_cell(v[i * CPT + c], g.epi, col, g.groups == 1);
+            if (col < g.n) out[(size_t)(row0 + i) * g.n + col] = nan_canon(ftz_hw(v[i * CPT + c]));
         }
+    }
+    if (g.groups == 1 && epilogue_on(g.epi)) { // this thread's own cells once more (see epilogue_cell)
+        for (int i = 0; i < TR && row0 + i < g.m; i++)
+            for (int c = 0; c < CPT; c++) {
+                const int col = bn0 + col_of(c);
+                if (col < g.n) epilogue_cell(out + (size_t)(row0 + i) * g.n + col, g.epi, col);
+            }
     }
 }
 

@@ -18,18 +18,7 @@
 // Admission is decided per thread (the chunk's activation key and the thread's own
 // weight rows); the bare chain and the flushing chain give the same bits whenever a
 // window is admitted, so threads of a warp may disagree without changing a result.
-// (3) The leaf groups of a tile meet inside a thread-block cluster. The CTAs that share
-// a tile (one per leaf group, up to 16) are launched as one cluster; each finishes its
-// group's subtree in registers, and the group nodes are then folded pairwise through
-// distributed shared memory in the contract's own tree order: in round r the CTA whose
-// rank has bit r as its lowest set bit parks its node in its shared memory, its partner
-// 2^r below adds it, and a rank with no partner carries its node unchanged (the odd
-// tail). Rank 0 ends with the root and stores the output. No node ever reaches global
-// memory and there is no second launch. A product with more than 16 leaf groups keeps
-// the global nodes and the separate group fold.
 #pragma once
-#include <cooperative_groups.h>
-
 #include "gemm_skinny.cuh"
 
 namespace b200i {
@@ -281,40 +270,25 @@ __global__ void __launch_bounds__(SK_THREADS, MINB) gemm_skinny_reg_kernel(const
                 for (int c = 0; c < CELLS; c++) v[c] = fold_add(stack[lvl][c], v[c]);
             }
     }
-    bool last_store = g.groups == 1;
     float *out = g.groups > 1 ? g.ws + (size_t)blockIdx.y * (size_t)g.m * (size_t)g.n : g.c;
-    if (g.cluster_fold) {
-        // the tile's leaf groups are the CTAs of this cluster, rank = group index
-        namespace cg = cooperative_groups;
-        cg::cluster_group cluster = cg::this_cluster();
-        const unsigned rank = blockIdx.y, G = gridDim.y;
-        float *park = skr_smem; // the activation staging area is free now: [cell][thread], CELLS * 128 floats
-        __syncthreads();        // every thread of this CTA is done reading the staged activations
-        bool sent = false;
-        for (unsigned stride = 1; stride < G; stride <<= 1) {
-            if (!sent && (rank & stride)) { // the lowest set bit of the rank: this CTA's one turn to hand its node over
-#pragma unroll
-                for (int c = 0; c < CELLS; c++) park[c * SK_THREADS + tid] = ftz_hw(v[c]);
-                sent = true;
-            }
-            cluster.sync();
-            if (!sent && rank + stride < G) {
-                const float *theirs = cluster.map_shared_rank(park, rank + stride);
-#pragma unroll
-                for (int c = 0; c < CELLS; c++) v[c] = fold_add(v[c], theirs[c * SK_THREADS + tid]);
-            }
-        }
-        cluster.sync(); // nobody leaves while a partner may still be reading its shared memory
-        if (rank != 0) return;
-        out = g.c;
-        last_store = true;
+    if (CPT == 2 && g.groups == 1 && epilogue_pairs(g.epi)) { // this thread's two columns are one (gate, up) pair
+        if (wrow + 1 < g.n)
+            for (int i = 0; i < rows; i++)
+                g.c[(size_t)(row0 + i) * (g.n / 2) + wrow / 2] =
+                    epilogue_pair_apply(nan_canon(ftz_hw(v[i * CPT])), nan_canon(ftz_hw(v[i * CPT + 1])), g.epi.bias, g.epi.act, wrow / 2);
+        return;
     }
 #pragma unroll
     for (int i = 0; i < BM; i++) {
         if (i >= rows) break;
 #pragma unroll
         for (int c = 0; c < CPT; c++)
-            if (wrow + c < g.n) out[(size_t)(row0 + i) * g.n + wrow + c] = finish_cell(v[i * CPT + c], g.epi, wrow + c, last_store);
+            if (wrow + c < g.n) out[(size_t)(row0 + i) * g.n + wrow + c] = nan_canon(ftz_hw(v[i * CPT + c]));
+    }
+    if (g.groups == 1 && epilogue_on(g.epi)) { // this thread's own cells once more (see epilogue_cell)
+        for (int i = 0; i < rows; i++)
+            for (int c = 0; c < CPT; c++)
+                if (wrow + c < g.n) epilogue_cell(out + (size_t)(row0 + i) * g.n + wrow + c, g.epi, wrow + c);
     }
 }
 
@@ -326,58 +300,32 @@ inline int skr_bm(int m) { return m <= 8 ? 8 : (m <= 16 ? 16 : 32); }
 inline int skr_bn(int) { return SK_THREADS * SKR_CPT; }
 inline int skr_per_sm(int m) { return m <= 8 ? SKR_MINB8 : (m <= 16 ? SKR_MINB16 : SKR_MINB32); }
 
-// leaf groups a cluster can hold: 8 is the portable cluster size, 16 needs the kernel's opt-in
-constexpr int SKR_MAX_CLUSTER = 16;
-
-// returns true when the leaf groups were folded inside clusters (no group fold has to follow)
 template <int WK, int BM, int CPT, int MINB>
-inline bool launch_skinny_reg_cfg(const GemmArgs &g_in, int groups, cudaStream_t st) {
+inline void launch_skinny_reg_cfg(const GemmArgs &g, int groups, cudaStream_t st) {
     static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kernel = gemm_skinny_reg_kernel<WK, BM, CPT, MINB>;
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, skr_smem_bytes(BM, K_LEAF_MIN));
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaFuncSetAttribute(gemm_skinny_reg_kernel<WK, BM, CPT, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, skr_smem_bytes(BM, K_LEAF_MIN));
         configured[dev] = true;
     }
-    GemmArgs g = g_in;
     dim3 grid((unsigned)((g.n + SK_THREADS * CPT - 1) / (SK_THREADS * CPT)), (unsigned)groups, (unsigned)((g.m + BM - 1) / BM));
-    const size_t smem = skr_smem_bytes(BM, g.leaf);
-    if (g.cluster_fold && groups > 1 && groups <= SKR_MAX_CLUSTER) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(SK_THREADS);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 1;
-        attr[0].val.clusterDim.y = (unsigned)groups;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, kernel, g) == cudaSuccess) return true;
-        cudaGetLastError(); // the cluster could not be placed: fall through to global nodes (the caller sized the scratch for them)
-    }
-    g.cluster_fold = 0;
-    kernel<<<grid, SK_THREADS, smem, st>>>(g);
-    return false;
+    gemm_skinny_reg_kernel<WK, BM, CPT, MINB><<<grid, SK_THREADS, skr_smem_bytes(BM, g.leaf), st>>>(g);
 }
 
 template <int WK>
-inline bool launch_skinny_reg_wk(const GemmArgs &g, int groups, cudaStream_t st) {
-    if (g.m <= 8) return launch_skinny_reg_cfg<WK, 8, SKR_CPT, SKR_MINB8>(g, groups, st);
-    if (g.m <= 16) return launch_skinny_reg_cfg<WK, 16, SKR_CPT, SKR_MINB16>(g, groups, st);
-    return launch_skinny_reg_cfg<WK, 32, SKR_CPT, SKR_MINB32>(g, groups, st);
+inline void launch_skinny_reg_wk(const GemmArgs &g, int groups, cudaStream_t st) {
+    if (g.m <= 8) launch_skinny_reg_cfg<WK, 8, SKR_CPT, SKR_MINB8>(g, groups, st);
+    else if (g.m <= 16) launch_skinny_reg_cfg<WK, 16, SKR_CPT, SKR_MINB16>(g, groups, st);
+    else launch_skinny_reg_cfg<WK, 32, SKR_CPT, SKR_MINB32>(g, groups, st);
 }
 
 // low-bit weight kinds only; the caller keeps float32 weights on launch_skinny
-inline bool launch_skinny_reg(const GemmArgs &g, int groups, cudaStream_t st) {
+inline void launch_skinny_reg(const GemmArgs &g, int groups, cudaStream_t st) {
     switch (g.wkind) {
-    case W_BF16: return launch_skinny_reg_wk<W_BF16>(g, groups, st);
-    case W_INT8_EXP: return launch_skinny_reg_wk<W_INT8_EXP>(g, groups, st);
-    default: return launch_skinny_reg_wk<W_INT8_SCALE>(g, groups, st);
+    case W_BF16: launch_skinny_reg_wk<W_BF16>(g, groups, st); break;
+    case W_INT8_EXP: launch_skinny_reg_wk<W_INT8_EXP>(g, groups, st); break;
+    default: launch_skinny_reg_wk<W_INT8_SCALE>(g, groups, st); break;
     }
 }
 

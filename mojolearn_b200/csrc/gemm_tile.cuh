@@ -39,7 +39,6 @@ struct GemmArgs {
     int tiles_n;
     int dec_smem_limit;       // decode plan: shared memory a CTA may use (decides one or two CTAs per SM)
     Epilogue epi;             // bias / activation applied where the product's output is stored
-    int cluster_fold;         // register skinny plan: the leaf groups of a tile are one thread-block cluster and fold there
 };
 
 constexpr int KS = 16;       // k-steps per staged window
@@ -392,9 +391,8 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
         for (int jr = 0; jr < RN; jr++) {
             float vals[4];
 #pragma unroll
+            for (int e = 0; e < 4; e++) vals[e] = nan_canon(ftz_hw(v[i * TN + jr * 4 + e]));
             const int col = bn0 + jr * (BN / RN) + tx * 4;
-#pragma unroll
-            for (int e = 0; e < 4; e++) vals[e] = finish_cell(v[i * TN + jr * 4 + e], g.epi, col + e < g.n ? col + e : 0, g.groups == 1);
             if (row < g.m) {
                 float *dst = out + (size_t)row * (size_t)g.n + col;
                 if (g.vec_c && col + 3 < g.n) *reinterpret_cast<float4 *>(dst) = make_float4(vals[0], vals[1], vals[2], vals[3]);
@@ -404,6 +402,14 @@ __global__ void __launch_bounds__((TileShape<BM, BN, RM, RN>::THREADS), MINB) ge
             }
         }
     }
+}
+
+// The store epilogue of the tiled and packed plans, as a pass of its own over the finished output: those kernels'
+// store loops hold 64 live cells per thread and are left exactly as they are (a product large enough for them does
+// not notice one more elementwise launch; the plans for small products apply the epilogue where they store).
+__global__ void epilogue_rows_kernel(float *__restrict__ c, long long cells, int n, Epilogue epi) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < cells; i += stride) epilogue_cell(c + i, epi, i % n);
 }
 
 // Folds the group nodes of a split product: node g of cell c is ws[g][c]; the
@@ -421,47 +427,70 @@ __global__ void __launch_bounds__(256) fold_groups_kernel(const float *__restric
     if (idx >= cells) return;
     float stack[GROUP_LEVELS][VEC];
     float v[VEC];
-    auto load = [&](int gi) {
-        const float *src = ws + (size_t)gi * (size_t)cells + idx;
-        if (VEC == 4) {
-            const float4 x = __ldcg(reinterpret_cast<const float4 *>(src));
-            v[0] = x.x; v[1 % VEC] = x.y; v[2 % VEC] = x.z; v[3 % VEC] = x.w;
-        } else {
-            v[0] = __ldcg(src);
-        }
-    };
-    for (int gi = 0; gi + 1 < groups; gi++) {
-        load(gi);
-        bool placed = false;
+    // Eight nodes are requested at a time: a lone thread's chain of additions waits on memory once per eight nodes
+    // instead of once per node (a deep product split into 64 single-leaf groups was 64 L2 round trips long).
+    constexpr int AHEAD = 8;
+    const int last = groups - 1;
+    for (int g0 = 0; g0 < groups; g0 += AHEAD) {
+        float x[AHEAD][VEC];
 #pragma unroll
-        for (int lvl = 0; lvl < GROUP_LEVELS; lvl++) {
-            if (placed) continue;
-            if ((gi >> lvl) & 1) {
-#pragma unroll
-                for (int e = 0; e < VEC; e++) v[e] = fold_add(stack[lvl][e], v[e]);
+        for (int j = 0; j < AHEAD; j++) {
+            if (g0 + j >= groups) break;
+            const float *src = ws + (size_t)(g0 + j) * (size_t)cells + idx;
+            if (VEC == 4) {
+                const float4 t = __ldcg(reinterpret_cast<const float4 *>(src));
+                x[j][0] = t.x; x[j][1 % VEC] = t.y; x[j][2 % VEC] = t.z; x[j][3 % VEC] = t.w;
             } else {
+                x[j][0] = __ldcg(src);
+            }
+        }
 #pragma unroll
-                for (int e = 0; e < VEC; e++) stack[lvl][e] = v[e];
-                placed = true;
+        for (int j = 0; j < AHEAD; j++) {
+            const int gi = g0 + j;
+            if (gi >= groups) break;
+#pragma unroll
+            for (int e = 0; e < VEC; e++) v[e] = x[j][e];
+            if (gi == last) { // the last node drains the stack
+#pragma unroll
+                for (int lvl = 0; lvl < GROUP_LEVELS; lvl++)
+                    if ((last >> lvl) & 1) {
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) v[e] = fold_add(stack[lvl][e], v[e]);
+                    }
+            } else {
+                bool placed = false;
+#pragma unroll
+                for (int lvl = 0; lvl < GROUP_LEVELS; lvl++) {
+                    if (placed) continue;
+                    if ((gi >> lvl) & 1) {
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) v[e] = fold_add(stack[lvl][e], v[e]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) stack[lvl][e] = v[e];
+                        placed = true;
+                    }
+                }
             }
         }
     }
-    const int last = groups - 1;
-    load(last);
-#pragma unroll
-    for (int lvl = 0; lvl < GROUP_LEVELS; lvl++)
-        if ((last >> lvl) & 1) {
-#pragma unroll
-            for (int e = 0; e < VEC; e++) v[e] = fold_add(stack[lvl][e], v[e]);
-        }
-    const bool epi_on = epilogue_on(epi);
-#pragma unroll
-    for (int e = 0; e < VEC; e++) v[e] = finish_cell(v[e], epi, epi_on ? (idx + e) % n : 0, true);
-    if (VEC == 4) {
-        *reinterpret_cast<float4 *>(c + idx) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
-    } else {
-        c[idx] = v[0];
+    if (VEC == 4 && epilogue_pairs(epi)) {
+        // gated activation: the four cells are two (gate, up) pairs of one row; the output has n / 2 columns
+        const long long row = idx / n, col = idx - row * n;
+        float2 o;
+        o.x = epilogue_pair_apply(nan_canon(ftz_hw(v[0])), nan_canon(ftz_hw(v[1 % VEC])), epi.bias, epi.act, col / 2);
+        o.y = epilogue_pair_apply(nan_canon(ftz_hw(v[2 % VEC])), nan_canon(ftz_hw(v[3 % VEC])), epi.bias, epi.act, col / 2 + 1);
+        *reinterpret_cast<float2 *>(c + row * (n / 2) + col / 2) = o;
+        return;
     }
+    if (VEC == 4) {
+        *reinterpret_cast<float4 *>(c + idx) = make_float4(nan_canon(ftz_hw(v[0])), nan_canon(ftz_hw(v[1 % VEC])),
+                                                           nan_canon(ftz_hw(v[2 % VEC])), nan_canon(ftz_hw(v[3 % VEC])));
+    } else {
+        c[idx] = nan_canon(ftz_hw(v[0]));
+    }
+    if (epilogue_on(epi))
+        for (int e = 0; e < VEC; e++) epilogue_cell(c + idx + e, epi, (idx + e) % n);
 }
 inline void launch_fold_groups(const float *ws, float *c, long long cells, int groups, cudaStream_t st, Epilogue epi = Epilogue{nullptr, 0},
                                int n = 1) {
@@ -506,7 +535,7 @@ __global__ void gemm_flat_kernel(const GemmArgs g) {
             v = have ? fold_add(stack[lvl], v) : stack[lvl];
             have = true;
         }
-    g.c[idx] = finish_cell(v, g.epi, j, true);
+    g.c[idx] = nan_canon(ftz_hw(v));
 }
 
 } // namespace b200i

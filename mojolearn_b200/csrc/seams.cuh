@@ -20,6 +20,8 @@
 
 namespace b200i {
 
+
+
 constexpr int OP_NN = 0, OP_NT = 1, OP_TN = 2;
 constexpr int K_LEAF_MIN = 128, MAX_LEAVES = 1024;
 
@@ -112,8 +114,17 @@ __device__ __forceinline__ float fold_add(float x, float y) { return ftz_hw(__fa
 // every product is a multiple of 2^-126, and so is every accumulator that
 // started a leaf at +0.0 and has only taken admitted steps: no step result can
 // be subnormal and the flush is the identity.
+#ifdef B200I_SABOTAGE_ADMIT_ALWAYS
+// Negative control (the reference's MOJOLEARN_GEMM_SABOTAGE_ADMIT_ALWAYS, gemm/checks/gemm_identical.mojo:1444): a
+// second build in which every window is admitted, whatever it holds. The tests load it next to the real library and
+// require the subnormal-forcing cases to FAIL under it, which shows that those cases would catch a broken admission
+// test. Wrong bits are its only effect; it is never the library the package loads by default.
+constexpr unsigned ADMIT_EXP = 0u;
+constexpr unsigned ADMIT_MIN = 0u;
+#else
 constexpr unsigned ADMIT_EXP = 87u;
 constexpr unsigned ADMIT_MIN = (ADMIT_EXP << 24) - 2u;
+#endif
 __device__ __forceinline__ unsigned admit_key(float x) { return (__float_as_uint(x) << 1) - 2u; }
 
 // ---- NaN canonicalisation -----------------------------------------------------

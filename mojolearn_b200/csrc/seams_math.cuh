@@ -278,8 +278,26 @@ struct Epilogue {
     const float *bias; // one word per output column, or NULL
     int act;           // EPI_ACT_*
 };
-enum { EPI_ACT_NONE = 0, EPI_ACT_GELU_ERF = 1, EPI_ACT_GELU_TANH = 2, EPI_ACT_SILU = 3 };
-__device__ __forceinline__ bool epilogue_on(const Epilogue &e) { return e.bias != nullptr || e.act != EPI_ACT_NONE; }
+// Codes 4 to 6 are the GATED activations over a product whose weight rows were interleaved (row 2j = gate_j, row
+// 2j + 1 = up_j): output column j of the [m, n / 2] result is ftz(act(gate) * up), S20-S21 with SiLU, or GELU in its
+// place (transformer_oracle.mojo:2580-2620). A thread that owns two adjacent product columns owns one such pair.
+enum { EPI_ACT_NONE = 0, EPI_ACT_GELU_ERF = 1, EPI_ACT_GELU_TANH = 2, EPI_ACT_SILU = 3, EPI_PAIR_SWIGLU = 4, EPI_PAIR_GEGLU_ERF = 5,
+       EPI_PAIR_GEGLU_TANH = 6 };
+__host__ __device__ __forceinline__ bool epilogue_on(const Epilogue &e) { return e.bias != nullptr || e.act != EPI_ACT_NONE; }
+__host__ __device__ __forceinline__ bool epilogue_pairs(const Epilogue &e) { return e.act >= EPI_PAIR_SWIGLU; }
+// gate and up are the product's stored words of columns 2j and 2j + 1
+__device__ __noinline__ float epilogue_pair_apply(float gate, float up, const float *bias, int act, long long j) {
+    if (bias) {
+        gate = ftz_bits(__fadd_rn(ftz_bits(gate), ftz_bits(__ldg(bias + 2 * j))));
+        up = ftz_bits(__fadd_rn(ftz_bits(up), ftz_bits(__ldg(bias + 2 * j + 1))));
+    }
+    const float z = ftz_bits(gate);
+    float a;
+    if (act == EPI_PAIR_SWIGLU) a = ftz_bits(p_siluf(z));
+    else if (act == EPI_PAIR_GEGLU_TANH) a = ftz_bits(p_gelu_tanh(z));
+    else a = ftz_bits(p_gelu_erf(z));
+    return ftz_bits(__fmul_rn(a, ftz_bits(up)));
+}
 __device__ __noinline__ float epilogue_apply(float c, const float *bias, int act, long long col) {
     if (bias) c = ftz_bits(__fadd_rn(ftz_bits(c), ftz_bits(__ldg(bias + col))));
     if (act == EPI_ACT_GELU_ERF) c = ftz_bits(p_gelu_erf(ftz_bits(c)));
@@ -287,11 +305,12 @@ __device__ __noinline__ float epilogue_apply(float c, const float *bias, int act
     else if (act == EPI_ACT_SILU) c = ftz_bits(p_siluf(ftz_bits(c)));
     return c;
 }
-// the word a product stores for a cell whose tree root is `root`; `last` = this store is the product's output
-// (not a leaf-group node that a later fold finishes)
-__device__ __forceinline__ float finish_cell(float root, const Epilogue &e, long long col, bool last) {
-    const float c = nan_canon(ftz_hw(root));
-    return (last && epilogue_on(e)) ? epilogue_apply(c, e.bias, e.act, col) : c;
+// A product kernel stores its words exactly as it does without an epilogue and then, only when one is asked for,
+// walks its own cells once more through this function (a thread re-reads what it wrote itself). The call is kept out
+// of line and out of the store loops on purpose: inlined there, or called from there, it costs every product
+// registers and spills in its hottest code for the sake of the few that carry a bias.
+__device__ __forceinline__ void epilogue_cell(float *cell, const Epilogue &e, long long col) {
+    *cell = epilogue_apply(*cell, e.bias, e.act, col);
 }
 
 } // namespace b200i

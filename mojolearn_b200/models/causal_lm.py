@@ -34,9 +34,13 @@ from ..transformer import Linear, ShardedLinear, TransformerBlock, TransformerSt
 
 
 class CausalLMConfig(object):
+    """The architecture of a decoder LM: what the reference's `ModelPlan` (python/mojolearn/models/config.py) carries
+    for a transformer family: the shape and every block option."""
+
     def __init__(self, vocab, d_model, n_layers, n_heads, n_kv_heads=None, head_dim=None, intermediate=None, norm="rmsnorm",
                  norm_eps=1e-6, norm_bias=False, mlp="swiglu", mlp_bias=False, qkv_bias=False, o_bias=False,
-                 positions="rope", rope_theta=10000.0, max_positions=8192, window=0):
+                 positions="rope", rope_theta=10000.0, max_positions=8192, window=0, rope_scaling=None, rope_dim=None,
+                 qk_norm=False, attn_softcap=None, tie_word_embeddings=False):
         self.vocab, self.d_model, self.n_layers, self.n_heads = vocab, d_model, n_layers, n_heads
         self.n_kv_heads = n_kv_heads or n_heads
         self.head_dim = head_dim or d_model // n_heads
@@ -46,6 +50,8 @@ class CausalLMConfig(object):
         if positions not in ("rope", "learned"):
             raise ValueError("positions must be 'rope' or 'learned'")
         self.positions, self.rope_theta, self.max_positions, self.window = positions, rope_theta, max_positions, window
+        self.rope_scaling, self.rope_dim, self.qk_norm, self.attn_softcap = rope_scaling, rope_dim, qk_norm, attn_softcap
+        self.tie_word_embeddings = bool(tie_word_embeddings)
 
 
 class CausalLMState(object):
@@ -63,15 +69,35 @@ class CausalLM(object):
     #: rows (batch x new tokens) up to which a sharded model's gathers go through the peer exchange
     EXCHANGE_ROWS = 64
 
-    def __init__(self, config, weights, *, device=None, group=None, exchange=None, prefill_by_batch=True, emulate_world=0):
+    def __init__(self, config, weights, *, weight_format="float32", max_positions=None, device=None, numeric_profile=None,
+                 group=None, exchange=None, prefill_by_batch=True, emulate_world=0):
         """`group`: a torch.distributed group of one process per GPU; the model is then cut by output columns
         (see the module text). `exchange`: True / False forces or forbids the store-side peer exchange for the
         decode-step gathers (default: on, unless MOJOLEARN_B200_EXCHANGE=0). `prefill_by_batch`: a prompt on a
         fresh state is cut by SEQUENCES instead (each rank runs its share of the batch through the whole model,
         then the KV caches are re-cut to the decode layout by one all-to-all): the other bit-neutral axis.
         `emulate_world` (timing only): build rank 0's share of a model cut over that many ranks, with no process
-        group and `parallel.LoopbackExchange` in place of the exchange; the outputs are then not the model's."""
+        group and `parallel.LoopbackExchange` in place of the exchange; the outputs are then not the model's.
+        `weight_format` ("float32", "bfloat16" or "int8"), `max_positions` and `numeric_profile` are the reference's
+        keywords (python/mojolearn/models/causal_lm.py:126-131): float32 projection weights are packed into the asked
+        storage format on the way in (weights that arrive packed keep their own), a smaller `max_positions` lowers
+        the model's position ceiling, and a profile this build does not compute is refused."""
         _native.require_device()
+        if weight_format not in ("float32", "bfloat16", "int8"):
+            raise ValueError("weight_format must be 'float32', 'bfloat16' or 'int8', got %r" % (weight_format,))
+        if numeric_profile not in (None, TransformerBlock.NUMERIC_PROFILE, "fp32", "float32"):
+            raise ValueError("numeric_profile %r is not spelled by this build" % (numeric_profile,))
+        if device == "auto":
+            device = None
+        self.weight_format = weight_format
+        if weight_format != "float32":
+            from .. import lowbit
+            weights = {k: (lowbit.pack_one(np.asarray(v, dtype=np.float32), weight_format)
+                           if (isinstance(v, np.ndarray) and v.ndim == 2 and v.dtype == np.float32 and "embed" not in k) else v)
+                       for k, v in weights.items()}
+        if max_positions is not None:
+            config = copy.copy(config)
+            config.max_positions = min(int(max_positions), config.max_positions)
         self.config = cfg = config
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.group, self.rank, self.world = group, 0, 1
@@ -112,9 +138,10 @@ class CausalLM(object):
                     if key.startswith(prefix):
                         bw[key[len(prefix):].replace("self_attn.", "").replace("mlp.", "")] = val
             blk = TransformerBlock(bw, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim, window=cfg.window,
-                                   rope=cfg.positions == "rope", rope_theta=cfg.rope_theta, qkv_bias=cfg.qkv_bias,
+                                   rope=cfg.positions == "rope", rope_theta=cfg.rope_theta, rope_scaling=cfg.rope_scaling,
+                                   rope_dim=cfg.rope_dim, max_positions=cfg.max_positions, qkv_bias=cfg.qkv_bias,
                                    o_bias=cfg.o_bias, norm=cfg.norm, norm_eps=cfg.norm_eps, norm_bias=cfg.norm_bias, mlp=cfg.mlp,
-                                   mlp_bias=cfg.mlp_bias, device=self.device)
+                                   mlp_bias=cfg.mlp_bias, qk_norm=cfg.qk_norm, attn_softcap=cfg.attn_softcap, device=self.device)
             self.full_blocks.append(blk)
             if self.world > 1:
                 blk = copy.copy(blk)  # the shards are row views of the same weights; only the fused q|k|v and gate|up shards are copies
@@ -131,8 +158,53 @@ class CausalLM(object):
             self.head = ShardedLinear(self.head, group, self.rank, self.world, self.exchange)
         self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
+    @classmethod
+    def load(cls, path, *, weight_format="float32", max_positions=None, device=None, numeric_profile=None, **kw):
+        """A checkpoint directory: `config.json` plus `model.safetensors`, or `model.safetensors.index.json` and its
+        shards (reference python/mojolearn/models/causal_lm.py:139-150). The config is mapped family by family
+        (`models.config.plan_for`; a field the blocks cannot honor is refused by name), the tensors are read exactly
+        (BF16 and F16 checkpoints widen exactly to float32; with weight_format "bfloat16" BF16 matrices stay as their
+        bits), and a tensor the plan needs and the checkpoint lacks is refused by name."""
+        from . import config as _config, safetensors as _safetensors
+        plan = _config.plan_for(_config.read_config(path))
+        weights = {}
+        with _safetensors.Checkpoint.open(path) as ckpt:
+            for name in _config.checkpoint_names(plan):
+                if name not in ckpt:
+                    raise ValueError("the checkpoint lacks %r, which a %d-layer model of this family needs" % (name, plan.n_layers))
+                keep_bits = weight_format == "bfloat16" and name.endswith("_proj.weight") or (weight_format == "bfloat16" and name == "lm_head.weight")
+                weights[name] = ckpt.read(name, bf16="bits" if keep_bits else "widen")
+        return cls(plan, weights, weight_format=weight_format, max_positions=max_positions, device=device,
+                   numeric_profile=numeric_profile, **kw)
+
     def allocate_state(self, batch_size, max_tokens):
         return CausalLMState([b.allocate_state(batch_size, max_tokens) for b in self.blocks], batch_size, int(max_tokens))
+
+    def reset_state(self, state):
+        """Empty the caches of `state`, keeping its batch size and capacity (reference causal_lm.py:177)."""
+        for layer in state.layers:
+            layer.cached_tokens = 0
+            layer.session = None
+        return state
+
+    def parameters(self):
+        """The model's tensors by checkpoint name, as they live on the device (packed weights as (storage, scale))."""
+        out = {"model.embed_tokens.weight": self.embed, "model.norm.weight": self.final_w, "lm_head.weight": self.full_head.w}
+        for i, blk in enumerate(self.full_blocks):
+            for slot, name in blk._NAMES.items():
+                for holder in (getattr(blk, slot, None), getattr(blk, slot + "_w", None)):
+                    if isinstance(holder, torch.Tensor):
+                        out["model.layers.%d.%s" % (i, name)] = holder
+                    elif isinstance(holder, Linear):
+                        out["model.layers.%d.%s" % (i, name)] = holder.w if holder.scale is None else (holder.w, holder.scale)
+        return out
+
+    def stream(self, ids, max_new_tokens, greedy=True):
+        """A continuation stream (reference causal_lm.py:211): `read(n)` returns at most n new ids per row, (B, <= n)
+        int32 on the host, and an empty (B, 0) array once `max_new_tokens` have been read."""
+        if not greedy:
+            raise ValueError("only greedy decoding is spelled")
+        return _Stream(self, ids, int(max_new_tokens))
 
     def _ids(self, ids):
         if isinstance(ids, torch.Tensor):
@@ -287,6 +359,29 @@ class CausalLM(object):
             stack = torch.stack(kept, dim=1)
             return seq, (stack.cpu().numpy() if host else stack)
         return seq
+
+
+class _Stream(object):
+    def __init__(self, lm, ids, budget):
+        t = lm._ids(ids)
+        self.lm, self.left, self.batch = lm, budget, t.shape[0]
+        self.state = lm.allocate_state(t.shape[0], t.shape[1] + budget)
+        self.session = lm.decode_session(self.state, lm.forward_device(t, self.state, last_only=True))
+        self.first = True
+
+    def read(self, n):
+        take = max(0, min(int(n), self.left))
+        out = []
+        for _ in range(take):
+            if not self.first:
+                self.session.step()
+            self.first = False
+            out.append(self.session.next_ids().clone())
+        self.left -= take
+        self.lm.check_ids()
+        if not out:
+            return np.zeros((self.batch, 0), dtype=np.int32)
+        return torch.cat(out, dim=1).cpu().numpy()
 
 
 class DecodeSession(object):

@@ -20,7 +20,6 @@ from . import _native
 from .linalg import OP_NN, OP_NT, OP_TN, W_BF16, W_F32, W_INT8_EXP, W_INT8_SCALE, leaf_count
 
 PLAN_AUTO, PLAN_FLAT, PLAN_T128, PLAN_T64, PLAN_DECODE, PLAN_T32, PLAN_T128X64, PLAN_SKINNY, PLAN_PACKED = -1, 0, 1, 2, 3, 4, 5, 6, 7
-PLAN_SKINNY_NODES = 8  # the skinny plan with global leaf-group nodes and a separate fold, never folded in clusters
 
 
 def _check(t, name, dtype):
@@ -57,6 +56,7 @@ _W_DTYPES = {W_F32: torch.float32, W_BF16: torch.uint16, W_INT8_EXP: torch.int8,
 
 
 ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3
+ACT_PAIR_SWIGLU, ACT_PAIR_GEGLU_ERF, ACT_PAIR_GEGLU_TANH = 4, 5, 6  # over interleaved (gate, up) weight rows: output [m, n / 2]
 
 
 def product(a, b, bscale=None, wkind=W_F32, op=OP_NN, out=None, plan=PLAN_AUTO, group_leaves=0, bias=None, act=ACT_NONE):
@@ -88,12 +88,13 @@ def product(a, b, bscale=None, wkind=W_F32, op=OP_NN, out=None, plan=PLAN_AUTO, 
     dev = a.device
     if b.device != dev:
         raise ValueError("operands live on different devices")
+    n_out = n // 2 if act >= ACT_PAIR_SWIGLU else n  # a gated store activation folds each (gate, up) column pair into one
     if out is None:
-        out = torch.empty((m, n), dtype=torch.float32, device=dev)
+        out = torch.empty((m, n_out), dtype=torch.float32, device=dev)
     else:
         _check(out, "out", torch.float32)
-        if tuple(out.shape) != (m, n):
-            raise ValueError("out must be (%d, %d)" % (m, n))
+        if tuple(out.shape) != (m, n_out):
+            raise ValueError("out must be (%d, %d)" % (m, n_out))
     lib = _native.lib()
     with torch.cuda.device(dev):
         ws_bytes = int(lib.b200i_plan_workspace_bytes(m, n, k, plan, group_leaves))

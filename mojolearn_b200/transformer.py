@@ -102,6 +102,23 @@ class Linear(object):
         self.out_features, self.in_features = self.w.shape
         return self
 
+    @classmethod
+    def interleave(cls, first, second):
+        """One layer whose output columns alternate between the two parts' (weight row 2j = first's row j, row 2j + 1 =
+        second's), or None when the parts differ in storage kind, shape or in having a bias. Bit-neutral like
+        `concat`; the layout puts a gated MLP's gate_j and up_j in adjacent product columns, where one thread of the
+        skinny plans owns both and can apply the gated activation as it stores."""
+        if (type(first) is not Linear or type(second) is not Linear or first.kind != second.kind or first.w.shape != second.w.shape or
+                (first.bias is None) != (second.bias is None)):
+            return None
+        self = cls.__new__(cls)
+        n, k = first.w.shape
+        self.w, self.kind = torch.stack([first.w, second.w], dim=1).reshape(2 * n, k).contiguous(), first.kind
+        self.scale = torch.stack([first.scale, second.scale], dim=1).reshape(2 * n).contiguous() if first.scale is not None else None
+        self.bias = torch.stack([first.bias, second.bias], dim=1).reshape(2 * n).contiguous() if first.bias is not None else None
+        self.out_features, self.in_features = self.w.shape
+        return self
+
     def shard_rows(self, lo, hi):
         """The same layer restricted to output rows [lo, hi): a bit-neutral shard (a cell reads one weight row)."""
         part = Linear.__new__(Linear)
@@ -255,17 +272,30 @@ def add(a, b):
 
 
 class TransformerBlock(object):
-    _NAMES = {"norm1": "input_layernorm.weight", "norm1_b": "input_layernorm.bias", "q": "q_proj.weight", "q_b": "q_proj.bias",
+    #: the profile this build computes in; a block asked for another one is refused
+    NUMERIC_PROFILE = "mojolearn.identical.transformer.fp32.v1"
+
+    _NAMES = {"q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "norm1": "input_layernorm.weight", "norm1_b": "input_layernorm.bias", "q": "q_proj.weight", "q_b": "q_proj.bias",
               "k": "k_proj.weight", "k_b": "k_proj.bias", "v": "v_proj.weight", "v_b": "v_proj.bias", "o": "o_proj.weight",
               "o_b": "o_proj.bias", "norm2": "post_attention_layernorm.weight", "norm2_b": "post_attention_layernorm.bias",
               "gate": "gate_proj.weight", "gate_b": "gate_proj.bias", "up": "up_proj.weight", "up_b": "up_proj.bias",
               "down": "down_proj.weight", "down_b": "down_proj.bias"}
 
-    def __init__(self, weights, *, n_heads, n_kv_heads=None, head_dim=None, window=0, rope=True, rope_theta=10000.0,
-                 qkv_bias=False, o_bias=False, norm="rmsnorm", norm_eps=1e-6, norm_bias=False, mlp="swiglu", mlp_bias=False,
-                 device=None, numeric_mode="identical"):
-        if numeric_mode != "identical":
+    def __init__(self, weights, *, n_heads, n_kv_heads=None, head_dim=None, window=0, rope_theta=10000.0, rope_scaling=None,
+                 rope_dim=None, max_positions=MAX_POSITIONS, qkv_bias=False, o_bias=False, norm="rmsnorm", norm_eps=1e-6,
+                 norm_bias=False, mlp="swiglu", mlp_bias=False, qk_norm=False, attn_softcap=None, numeric_profile=None,
+                 numeric_mode=None, rope=True, device=None):
+        """The reference's constructor (python/mojolearn/_transformer_impl.py:408-419), option for option:
+        `rope_scaling` None or a dict in the HuggingFace spelling ({"rope_type": "linear", "factor": f}, or "llama3"
+        with low_freq_factor, high_freq_factor and original_max_position_embeddings); `rope_dim` the rotated columns
+        of a head (partial rotary); `max_positions` the absolute-position ceiling the model declares; `qk_norm` an
+        RMSNorm over each head's vector of q and k before the rotation (`q_norm.weight`, `k_norm.weight`, [head_dim]);
+        `attn_softcap` caps every scaled score as cap * tanh(score / cap). `rope=False` and `device` are this
+        package's own (learned positions are an extension; the reference's block always rotates)."""
+        if numeric_mode not in (None, "identical"):
             raise RuntimeError("mojolearn_b200 has only the identical build")
+        if numeric_profile not in (None, self.NUMERIC_PROFILE, "fp32", "float32"):
+            raise ValueError("numeric_profile %r is not spelled by this build (it computes %s)" % (numeric_profile, self.NUMERIC_PROFILE))
         _native.require_device()
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         if self.device.index is None:
@@ -276,6 +306,16 @@ class TransformerBlock(object):
             raise ValueError("an RMSNorm carries no bias (norm_bias needs layernorm)")
         self.n_heads, self.n_kv_heads = int(n_heads), int(n_kv_heads or n_heads)
         self.window, self.rope, self.rope_theta = int(window or 0), bool(rope), float(rope_theta)
+        self.rope_scaling = self._rope_scaling_fields(rope_scaling)
+        self.max_positions = int(max_positions)
+        if self.max_positions < 1:
+            raise ValueError("max_positions must be positive")
+        self.qk_norm = bool(qk_norm)
+        if self.qk_norm and norm == "layernorm":
+            raise ValueError("qk_norm is an RMSNorm over each head: it cannot follow a layernorm block REFUSED")
+        self.attn_softcap = float(attn_softcap) if attn_softcap else 0.0
+        if attn_softcap is not None and not (np.isfinite(float(attn_softcap)) and float(attn_softcap) > 0.0):
+            raise ValueError("attn_softcap must be a finite positive float, got %r" % (attn_softcap,))
         self.norm_kind, self.norm_eps, self.norm_bias = NORM_KINDS[norm], float(norm_eps), bool(norm_bias)
         self.mlp_kind, self.mlp_bias, self.qkv_bias, self.o_bias = MLP_KINDS[mlp], bool(mlp_bias), bool(qkv_bias), bool(o_bias)
         self.weight_format = lowbit.format_of({k: v for k, v in weights.items() if lowbit.is_packed(v)})
@@ -300,6 +340,11 @@ class TransformerBlock(object):
                 bias = weights[bname]
             return Linear(weights[name], self.device, bias)
 
+        self.q_norm_w = vec("q_norm") if self.qk_norm else None
+        self.k_norm_w = vec("k_norm") if self.qk_norm else None
+        for slot in ("q_norm", "k_norm"):
+            if not self.qk_norm and self._NAMES[slot] in weights:
+                raise ValueError("weights carry %r but qk_norm is off REFUSED" % self._NAMES[slot])
         self.norm1_w, self.norm2_w = vec("norm1"), vec("norm2")
         self.norm1_b = vec("norm1_b") if self.norm_bias else None
         self.norm2_b = vec("norm2_b") if self.norm_bias else None
@@ -315,13 +360,18 @@ class TransformerBlock(object):
             raise ValueError("projection widths do not match n_heads * head_dim")
         if self.n_heads % self.n_kv_heads or self.head_dim % 2:
             raise ValueError("n_heads must be a multiple of n_kv_heads and head_dim even")
+        self.rope_dim = int(rope_dim or self.head_dim)
+        if self.rope_dim <= 0 or self.rope_dim > self.head_dim or self.rope_dim % 2:
+            raise ValueError("transformer: the rotary table's rope_dim %d does not fit head_dim %d REFUSED" % (self.rope_dim, self.head_dim))
+        if self.qk_norm and (tuple(self.q_norm_w.shape) != (self.head_dim,) or tuple(self.k_norm_w.shape) != (self.head_dim,)):
+            raise ValueError("q_norm.weight and k_norm.weight must be (%d,)" % self.head_dim)
         self.inter = self.up.out_features
         # q|k|v and gate|up as one product each: fewer, wider launches, the same cells
         self.widths = (self.q.out_features, self.k.out_features, self.v.out_features)
         self.qkv = Linear.concat([self.q, self.k, self.v])
         if self.qkv is not None:
             self.q = self.k = self.v = None
-        self.gateup = Linear.concat([self.gate, self.up]) if self.gated else None
+        self.gateup = Linear.interleave(self.gate, self.up) if self.gated else None  # rows gate_0, up_0, gate_1, up_1, ...
         if self.gateup is not None:
             self.gate = self.up = None
 
@@ -363,7 +413,7 @@ class TransformerBlock(object):
         self.widths = (qn, kn, kn)
         i0, i1 = rank * self.inter_local, (rank + 1) * self.inter_local
         if self.gateup is not None:
-            self.gateup = Linear.concat([self.gateup.shard_rows(i0, i1), self.gateup.shard_rows(self.inter + i0, self.inter + i1)])
+            self.gateup = self.gateup.shard_rows(2 * i0, 2 * i1)  # the interleaved rows of this rank's activation columns
         else:
             self.up = self.up.shard_rows(i0, i1)
             if self.gate is not None:
@@ -387,16 +437,36 @@ class TransformerBlock(object):
                              (state.window, self.window))
         return TransformerDecodeSession(self, state)
 
+    @staticmethod
+    def _rope_scaling_fields(rope_scaling):
+        """(kind, factor, low_freq_factor, high_freq_factor, original_max_positions): kind 0 none, 1 linear, 2 llama3."""
+        if not rope_scaling:
+            return (0, 1.0, 1.0, 4.0, 8192)
+        kind = rope_scaling.get("rope_type", rope_scaling.get("type"))
+        if kind in (None, "default"):
+            return (0, 1.0, 1.0, 4.0, 8192)
+        if kind not in ("linear", "llama3"):
+            raise ValueError("rope_scaling %r is not spelled (linear and llama3 are) REFUSED" % (kind,))
+        if "factor" not in rope_scaling:
+            raise ValueError("rope_scaling %r needs its factor" % (kind,))
+        return ({"linear": 1, "llama3": 2}[kind], float(rope_scaling["factor"]), float(rope_scaling.get("low_freq_factor", 1.0)),
+                float(rope_scaling.get("high_freq_factor", 4.0)), int(rope_scaling.get("original_max_position_embeddings", 8192)))
+
     def rope_tables(self, pos0, l, position=None):
-        """cos and sin [l, head_dim / 2] for this call's positions; the same for every block of a model."""
+        """cos and sin [l, rope_dim / 2] for this call's positions; the same for every block of a model."""
         dev, st = self.device, _stream(self.device)
-        cosv = torch.empty((l, self.head_dim // 2), dtype=torch.float32, device=dev)
+        cosv = torch.empty((l, self.rope_dim // 2), dtype=torch.float32, device=dev)
         sinv = torch.empty_like(cosv)
-        if position is None:
-            _native.call("b200i_rope_table", dev.index, st, _vp(cosv), _vp(sinv), pos0, l, self.head_dim, self.rope_theta)
+        kind, factor, lo, hi, old = self.rope_scaling
+        if kind == 0 and self.rope_dim == self.head_dim:  # the default record: the frozen v1 entry points
+            if position is None:
+                _native.call("b200i_rope_table", dev.index, st, _vp(cosv), _vp(sinv), pos0, l, self.head_dim, self.rope_theta)
+            else:
+                _native.call("b200i_rope_table_at", dev.index, st, _vp(cosv), _vp(sinv), _vp(position), l, self.head_dim,
+                             self.rope_theta)
         else:
-            _native.call("b200i_rope_table_at", dev.index, st, _vp(cosv), _vp(sinv), _vp(position), l, self.head_dim,
-                         self.rope_theta)
+            _native.call("b200i_rope_table_opts", dev.index, st, _vp(cosv), _vp(sinv), pos0, _vp(position), l, self.rope_dim,
+                         self.rope_theta, kind, factor, lo, hi, old)
         return cosv, sinv
 
     # -- the block on device tensors: x [B, L, d_model] -> [B, L, d_model]; state is advanced by L
@@ -414,8 +484,9 @@ class TransformerBlock(object):
         if pos0 + l > state.max_tokens:
             raise ValueError("transformer: this call would use %d KV slots and the cache holds %d REFUSED" %
                              (pos0 + l, state.max_tokens))
-        if pos0 + l > MAX_POSITIONS:
-            raise ValueError("transformer: absolute position %d is at or beyond %d" % (pos0 + l - 1, MAX_POSITIONS))
+        ceiling = min(self.max_positions, MAX_POSITIONS * (int(self.rope_scaling[1]) if self.rope_scaling[0] == 1 else 1))
+        if pos0 + l > ceiling:
+            raise ValueError("transformer: absolute position %d is at or beyond %d" % (pos0 + l - 1, ceiling))
         dev, st = x.device, _stream(x.device)
         x2 = x.reshape(m, dm).contiguous()
         if delta is None:
@@ -428,6 +499,14 @@ class TransformerBlock(object):
             q, k, v, ld = fused[:, :wq], fused[:, wq:wq + wk], fused[:, wq + wk:], fused.shape[1]
         else:
             q, k, v, ld = self.q(n1), self.k(n1), self.v(n1), 0
+        if self.qk_norm:
+            # an RMSNorm over each head's vector of q and of k, before the rotation (the plain form, or the offset form
+            # when the block's norm is the offset form): rows of width head_dim with the shared [head_dim] weight
+            kind = 2 if self.norm_kind == 2 else 0
+            q = norm(q.contiguous().reshape(m * self.heads_local, self.head_dim), self.q_norm_w, None, self.norm_eps, kind).reshape(m, -1)
+            k = norm(k.contiguous().reshape(m * self.kv_local, self.head_dim), self.k_norm_w, None, self.norm_eps, kind).reshape(m, -1)
+            if ld:
+                v, ld = v.contiguous(), 0
         cosv = sinv = None
         if self.rope:
             cosv, sinv = rope if rope is not None else self.rope_tables(pos0, l, position)
@@ -437,19 +516,20 @@ class TransformerBlock(object):
         ctx = torch.empty((m, self.heads_local * self.head_dim), dtype=torch.float32, device=dev)
         with _prof.span("rope_cache"):
             _native.call("b200i_qkv_rope_cache", dev.index, st, _vp(qr), _vp(state.k), _vp(state.v), _vp(q), _vp(k), _vp(v), ld,
-                         _vp(cosv), _vp(sinv), b, l, self.heads_local, self.kv_local, self.head_dim, cap, pos0, _vp(position))
+                         _vp(cosv), _vp(sinv), b, l, self.heads_local, self.kv_local, self.head_dim, cap, pos0, _vp(position),
+                         self.rope_dim)
         att = _prof.span("attention")
         att.__enter__()
         if position is None:
             s = used - (max(0, pos0 - (self.window - 1)) if self.window else 0)
             scores = torch.empty((b * self.heads_local * l * s,), dtype=torch.float32, device=dev)
             _native.call("b200i_attention", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
-                         self.heads_local, self.kv_local, self.head_dim, cap, used, self.window)
+                         self.heads_local, self.kv_local, self.head_dim, cap, used, self.window, self.attn_softcap)
         else:
             s = min(cap, self.window - 1 + l) if self.window else cap  # the most keys any later position sees
             scores = torch.empty((b * self.heads_local * l * s,), dtype=torch.float32, device=dev)
             _native.call("b200i_attention_at", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
-                         self.heads_local, self.kv_local, self.head_dim, cap, _vp(position), self.window)
+                         self.heads_local, self.kv_local, self.head_dim, cap, _vp(position), self.window, self.attn_softcap)
         att.__exit__()
         del scores
         if self.by_heads:
@@ -461,15 +541,24 @@ class TransformerBlock(object):
             # (mlp kinds 1, 2, 3 = gelu, gelu_tanh, silu are the store's activation codes)
             act = self.up(n2, act=self.mlp_kind)
         else:
-            if self.gateup is not None:
-                fused = self.gateup(n2)
-                gate, up, gld = fused[:, :self.inter_local], fused[:, self.inter_local:], fused.shape[1]
+            gu = self.gateup
+            if gu is not None and _native.lib().b200i_pair_epilogue_fits(m, gu.out_features, gu.in_features, OP_NT):
+                # a decode-sized call: the gated activation rides in the store of the gate|up product (mlp kinds 0, 4,
+                # 5 = swiglu, geglu, geglu_tanh are the store's pair codes 4, 5, 6)
+                with _prof.span("product"):
+                    act = torch_ops.product(n2, gu.w, gu.scale, gu.kind, OP_NT, bias=gu.bias, act={0: 4, 4: 5, 5: 6}[self.mlp_kind],
+                                            out=torch.empty((m, self.inter_local), dtype=torch.float32, device=dev))
             else:
-                up, gld = self.up(n2), 0
-                gate = self.gate(n2)
-            act = torch.empty((m, self.inter_local), dtype=torch.float32, device=dev)
-            with _prof.span("activation"):
-                _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(gate), _vp(up), m, self.inter_local, gld, self.mlp_kind)
+                act = torch.empty((m, self.inter_local), dtype=torch.float32, device=dev)
+                if gu is not None:
+                    fused = gu(n2)
+                    with _prof.span("activation"):
+                        _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(fused), None, m, self.inter_local, fused.shape[1],
+                                     self.mlp_kind, 1)
+                else:
+                    up, gate = self.up(n2), self.gate(n2)
+                    with _prof.span("activation"):
+                        _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(gate), _vp(up), m, self.inter_local, 0, self.mlp_kind, 0)
         if self.by_heads:
             with _prof.span("gather"):
                 act = gather_columns(act, self.group, self.exchange)

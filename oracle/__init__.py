@@ -248,21 +248,41 @@ def train_hash(parts):
 NORM_KINDS = {"rmsnorm": 0, "layernorm": 1, "rmsnorm_offset": 2}
 MLP_KINDS = {"swiglu": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "geglu": 4, "geglu_tanh": 5}
 WEIGHT_SLOTS = ["norm1", "norm1_b", "q", "q_b", "k", "k_b", "v", "v_b", "o", "o_b", "norm2", "norm2_b", "gate", "gate_b",
-                "up", "up_b", "down", "down_b"]
+                "up", "up_b", "down", "down_b", "q_norm", "k_norm"]
+ROPE_SCALINGS = {None: 0, "none": 0, "linear": 1, "llama3": 2}
 
 
 class BlockCfg(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in ("d_model", "n_heads", "n_kv_heads", "head_dim", "inter", "norm_kind",
                                               "norm_bias", "qkv_bias", "o_bias", "mlp_kind", "mlp_bias", "rope", "window")] + \
-               [("norm_eps", ctypes.c_float), ("rope_theta", ctypes.c_float)]
+               [("norm_eps", ctypes.c_float), ("rope_theta", ctypes.c_float), ("rope_scaling", ctypes.c_int32),
+                ("rope_factor", ctypes.c_float), ("rope_low_freq_factor", ctypes.c_float), ("rope_high_freq_factor", ctypes.c_float),
+                ("rope_original_max_positions", ctypes.c_int32), ("rope_dim", ctypes.c_int32), ("qk_norm", ctypes.c_int32),
+                ("attn_softcap", ctypes.c_float)]
+
+
+def rope_scaling_fields(rope_scaling):
+    """(kind, factor, low_freq_factor, high_freq_factor, original_max_positions) of a `rope_scaling` option: None, or a
+    dict in the HuggingFace spelling ({"rope_type": "linear", "factor": f} / {"rope_type": "llama3", "factor": f,
+    "low_freq_factor": a, "high_freq_factor": b, "original_max_position_embeddings": n})."""
+    if not rope_scaling:
+        return 0, 1.0, 1.0, 4.0, 8192
+    kind = rope_scaling.get("rope_type", rope_scaling.get("type"))
+    if kind not in ("linear", "llama3"):
+        raise ValueError("rope_scaling %r is not spelled" % (kind,))
+    return (ROPE_SCALINGS[kind], float(rope_scaling["factor"]), float(rope_scaling.get("low_freq_factor", 1.0)),
+            float(rope_scaling.get("high_freq_factor", 4.0)), int(rope_scaling.get("original_max_position_embeddings", 8192)))
 
 
 def block_cfg(d_model, n_heads, n_kv_heads=None, head_dim=None, inter=None, norm="rmsnorm", norm_eps=1e-6, norm_bias=False,
-              qkv_bias=False, o_bias=False, mlp="swiglu", mlp_bias=False, rope=True, rope_theta=10000.0, window=0):
+              qkv_bias=False, o_bias=False, mlp="swiglu", mlp_bias=False, rope=True, rope_theta=10000.0, window=0,
+              rope_scaling=None, rope_dim=None, qk_norm=False, attn_softcap=None):
     n_kv_heads = n_kv_heads or n_heads
     head_dim = head_dim or d_model // n_heads
+    kind, factor, lo, hi, old = rope_scaling_fields(rope_scaling)
     return BlockCfg(d_model, n_heads, n_kv_heads, head_dim, inter, NORM_KINDS[norm], int(norm_bias), int(qkv_bias),
-                    int(o_bias), MLP_KINDS[mlp], int(mlp_bias), int(rope), int(window), norm_eps, rope_theta)
+                    int(o_bias), MLP_KINDS[mlp], int(mlp_bias), int(rope), int(window), norm_eps, rope_theta, kind, factor, lo, hi,
+                    old, int(rope_dim or 0), int(bool(qk_norm)), float(attn_softcap or 0.0))
 
 
 def _math1(name):
@@ -291,6 +311,19 @@ def norm(x, w, bias=None, eps=1e-6, kind="rmsnorm"):
     f.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_int]
     f(_ptr(out), _ptr(x), _ptr(w), _ptr(b) if b is not None else None, m, dm, ctypes.c_float(eps), NORM_KINDS[kind])
     return out
+
+
+def rope_table_opts(pos0, l, rope_dim, theta=10000.0, rope_scaling=None):
+    """cos and sin [l, rope_dim / 2] under the option record (linear or llama3 scaling)."""
+    kind, factor, lo, hi, old = rope_scaling_fields(rope_scaling)
+    cosv = np.empty((l, rope_dim // 2), np.float32)
+    sinv = np.empty((l, rope_dim // 2), np.float32)
+    f = lib().dec_rope_table_opts
+    f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_float, ctypes.c_int,
+                  ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_int64]
+    f(_ptr(cosv), _ptr(sinv), pos0, l, rope_dim, ctypes.c_float(theta), kind, ctypes.c_float(factor), ctypes.c_float(lo),
+      ctypes.c_float(hi), old)
+    return cosv, sinv
 
 
 def rope_table(pos0, l, head_dim, theta=10000.0):
@@ -334,7 +367,7 @@ def block_forward(cfg, weights, x, state=None, threads=None):
     return y
 
 
-def attention(q, kcache, vcache, l, used, window=0, threads=None):
+def attention(q, kcache, vcache, l, used, window=0, threads=None, softcap=0.0):
     """Eager attention of one call: q [b*l, n_heads, head_dim] rotated queries, caches [b, n_kv, cap, head_dim] holding
     `used` positions (this call's l included) -> ctx [b*l, n_heads*head_dim]."""
     q, kcache, vcache = _f32(q), _f32(kcache), _f32(vcache)
@@ -345,8 +378,8 @@ def attention(q, kcache, vcache, l, used, window=0, threads=None):
     ctx = np.empty((b * l, nh * hd), np.float32)
     f = lib().dec_attention
     f.restype = ctypes.c_int
-    f.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64] * 8 + [ctypes.c_int]
-    if f(_ptr(ctx), _ptr(q), _ptr(kcache), _ptr(vcache), b, l, nh, nkv, hd, cap, used, window,
+    f.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64] * 8 + [ctypes.c_float, ctypes.c_int]
+    if f(_ptr(ctx), _ptr(q), _ptr(kcache), _ptr(vcache), b, l, nh, nkv, hd, cap, used, window, ctypes.c_float(softcap),
          int(threads or (os.cpu_count() or 1))) != 0:
         raise ValueError("attention oracle refused the call")
     return ctx

@@ -353,7 +353,16 @@ typedef struct {
     int32_t rope;   /* 1 = rotary on q and k (the reference's block); 0 = none (extension for learned positions) */
     int32_t window; /* 0 = full causal */
     float norm_eps, rope_theta;
+    /* the option record of transformer/block_options.mojo:40-70 beyond the fields above */
+    int32_t rope_scaling;              /* 0 none, 1 linear, 2 llama3 */
+    float rope_factor, rope_low_freq_factor, rope_high_freq_factor;
+    int32_t rope_original_max_positions;
+    int32_t rope_dim;                  /* 0 = head_dim (partial rotary otherwise) */
+    int32_t qk_norm;                   /* an RMSNorm over each head's vector of q and of k, before the rotation */
+    float attn_softcap;                /* 0 = none */
 } block_cfg_t;
+/* two more weight slots when qk_norm is on */
+enum { W_Q_NORM = W_SLOTS, W_K_NORM, W_SLOTS_OPT };
 
 /* transformer/checks/transformer_oracle.mojo:1223-1341 */
 typedef struct { float *out; const float *src, *w, *bias; int64_t dm; float eps; int kind; } norm_ctx_t;
@@ -414,6 +423,55 @@ static void add_bias(float *buf, const float *bias, int64_t rows, int64_t width)
         for (int64_t j = 0; j < width; j++) buf[t * width + j] = ftz(add(ftz(buf[t * width + j]), ftz(bias[j])));
 }
 
+/* Seam S6 with the options: transformer/checks/transformer_oracle.mojo:423-497 (rope_inv_freq_scaled). Linear scaling
+ * is one division by the factor; llama3 rescales by wavelength, every division through the portable division, both
+ * products rounded on their own and the final add unfused. */
+static float rope_inv_freq(int64_t i, int64_t rope_dim, float theta, int scaling, float factor_in, float lo_in, float hi_in,
+                           int64_t original) {
+    float e = ftz(p_divf((float)(2 * i), (float)rope_dim));
+    float inv = ftz(p_divf(1.0f, p_powf(theta, e)));
+    if (scaling == 1) {
+        inv = ftz(p_divf(inv, ftz(factor_in)));
+    } else if (scaling == 2) {
+        float factor = ftz(factor_in), lo_f = ftz(lo_in), hi_f = ftz(hi_in), old = (float)original;
+        float low_wl = ftz(p_divf(old, lo_f)), high_wl = ftz(p_divf(old, hi_f));
+        float two_pi = u2f(0x40C90FDBu);
+        float wl = ftz(p_divf(two_pi, inv));
+        float inv_l = inv;
+        if (wl > low_wl) inv_l = ftz(p_divf(inv, factor));
+        int medium = !(wl < high_wl) && !(wl > low_wl);
+        if (medium) {
+            float ratio = ftz(p_divf(old, wl));
+            float num = ftz(sub(ratio, lo_f)), den = ftz(sub(hi_f, lo_f));
+            float smooth = ftz(p_divf(num, den));
+            float one_minus = ftz(sub(1.0f, smooth));
+            float t1 = ftz(mul(one_minus, inv_l));
+            t1 = ftz(p_divf(t1, factor));
+            float t2 = ftz(mul(smooth, inv_l));
+            inv_l = ftz(add(ftz(t1), ftz(t2)));
+        }
+        inv = inv_l;
+    }
+    return inv;
+}
+
+/* S6-S8 with the option record: cos and sin [l, rope_dim / 2] for positions [pos0, pos0 + l) */
+DEC_API void dec_rope_table_opts(float *cosv, float *sinv, int64_t pos0, int64_t l, int64_t rope_dim, float theta, int scaling,
+                                 float factor, float lo, float hi, int64_t original) {
+    unsigned env = _mm_getcsr();
+    _mm_setcsr(env & ~(0x8000u | 0x0040u));
+    int64_t half = rope_dim / 2;
+    for (int64_t i = 0; i < half; i++) {
+        float inv = rope_inv_freq(i, rope_dim, theta, scaling, factor, lo, hi, original);
+        for (int64_t p = 0; p < l; p++) {
+            float angle = ftz(mul((float)(pos0 + p), ftz(inv)));
+            cosv[p * half + i] = ftz(p_cosf(angle));
+            sinv[p * half + i] = ftz(p_sinf(angle));
+        }
+    }
+    _mm_setcsr(env);
+}
+
 /* transformer/checks/transformer_oracle.mojo:539-640 (S6, S7, S8) for positions [pos0, pos0 + l) */
 DEC_API void dec_rope_table(float *cosv, float *sinv, int64_t pos0, int64_t l, int64_t head_dim, float theta) {
     unsigned env = _mm_getcsr();
@@ -433,13 +491,15 @@ DEC_API void dec_rope_table(float *cosv, float *sinv, int64_t pos0, int64_t l, i
 
 /* transformer/checks/transformer_oracle.mojo:1375-1500 (S9, S10): halves pairing, three roundings */
 static void apply_rope(float *out, const float *src, int64_t n_head, int64_t hd, int64_t m, int64_t l, const float *cosv,
-                       const float *sinv) {
-    int64_t half = hd / 2, width = n_head * hd;
+                       const float *sinv, int64_t rd) {
+    /* rd = rotated columns of a head (:1433-1440 of the reference oracle): the rest pass through, flushed on load */
+    int64_t half = rd / 2, width = n_head * hd;
     for (int64_t t = 0; t < m; t++) {
         int64_t li = t % l;
         for (int64_t h = 0; h < n_head; h++) {
             int64_t base = t * width + h * hd;
             for (int64_t j = 0; j < hd; j++) {
+                if (j >= rd) { out[base + j] = ftz(src[base + j]); continue; }
                 int64_t ci = j < half ? j : j - half;
                 float rot = j < half ? -ftz(src[base + j + half]) : ftz(src[base + j - half]);
                 float c = ftz(cosv[li * half + ci]), s = ftz(sinv[li * half + ci]);
@@ -461,6 +521,7 @@ static float *falloc(int64_t n) { return (float *)malloc(sizeof(float) * (size_t
 typedef struct {
     float *ctx; const float *qr, *kcache, *vcache;
     int64_t l, nh, nkv, hd, cap, key_lo, s, own0, window;
+    float softcap;
 } attn_ctx_t;
 static void attn_pair(int64_t item, void *vctx) {
     const attn_ctx_t *c = (const attn_ctx_t *)vctx;
@@ -486,6 +547,11 @@ static void attn_pair(int64_t item, void *vctx) {
         float mx = 0.0f;
         for (int64_t j = 0; j < s; j++) {
             float sc = ftz(mul(ftz(row[j]), scale));
+            if (f2u(c->softcap) != 0u) { /* transformer_oracle.mojo:2269-2281: after the scale, before the mask */
+                const float cap_f = ftz(c->softcap);
+                const float th = ftz(p_tanhf(ftz(p_divf(sc, cap_f))));
+                sc = ftz(mul(th, cap_f));
+            }
             float mk = ftz(add(ftz(sc), (j < jlo || j > jhi) ? mfill : ufill));
             row[j] = mk;
             mx = j == 0 ? ftz(mk) : p_fmaxf(mx, ftz(mk));
@@ -513,12 +579,12 @@ static void attn_pair(int64_t item, void *vctx) {
     free(qmat); free(kmat); free(cell); free(ex); free(acc);
 }
 DEC_API int dec_attention(float *ctx, const float *qr, const float *kcache, const float *vcache, int64_t b, int64_t l, int64_t nh,
-                          int64_t nkv, int64_t hd, int64_t cap, int64_t used, int64_t window, int threads) {
+                          int64_t nkv, int64_t hd, int64_t cap, int64_t used, int64_t window, float softcap, int threads) {
     if (b <= 0 || l <= 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || used < l || used > cap) return 1;
     const int64_t pos0 = used - l;
     int64_t key_lo = 0;
     if (window > 0 && pos0 - (window - 1) > 0) key_lo = pos0 - (window - 1);
-    attn_ctx_t c = {ctx, qr, kcache, vcache, l, nh, nkv, hd, cap, key_lo, used - key_lo, pos0 - key_lo, window};
+    attn_ctx_t c = {ctx, qr, kcache, vcache, l, nh, nkv, hd, cap, key_lo, used - key_lo, pos0 - key_lo, window, softcap};
     par_for(b * nh, threads, attn_pair, &c);
     return 0;
 }
@@ -560,15 +626,30 @@ DEC_API int dec_block_forward(const block_cfg_t *cfg, const float *const *w, con
     rows_gemm(k, n1, w[W_K], 1, m, kw, dm, threads);
     rows_gemm(v, n1, w[W_V], 1, m, kw, dm, threads);
     if (cfg->qkv_bias) { add_bias(q, w[W_Q_B], m, qw); add_bias(k, w[W_K_B], m, kw); add_bias(v, w[W_V_B], m, kw); }
+    if (cfg->qk_norm) {
+        /* transformer_oracle.mojo:1950-1975: an RMSNorm over each head's vector of q and of k, before the rotation; the
+         * offset form when the block's norm is the offset form, the plain form otherwise, never a bias */
+        const int kind = cfg->norm_kind == NORM_RMS_OFFSET ? NORM_RMS_OFFSET : NORM_RMS;
+        float *qn = falloc(m * qw), *kn = falloc(m * kw);
+        norm_rows(qn, q, w[W_Q_NORM], NULL, m * nh, hd, cfg->norm_eps, kind, threads);
+        norm_rows(kn, k, w[W_K_NORM], NULL, m * nkv, hd, cfg->norm_eps, kind, threads);
+        memcpy(q, qn, sizeof(float) * (size_t)(m * qw));
+        memcpy(k, kn, sizeof(float) * (size_t)(m * kw));
+        free(qn); free(kn);
+        _mm_setcsr(env & ~(0x8000u | 0x0040u));
+    }
     float *qr = q, *kr = k;
     if (cfg->rope) {
-        float *cosv = falloc(l * (hd / 2)), *sinv = falloc(l * (hd / 2));
-        dec_rope_table(cosv, sinv, pos0, l, hd, cfg->rope_theta);
+        const int64_t rd = cfg->rope_dim > 0 ? cfg->rope_dim : hd;
+        if (rd > hd || (rd & 1)) return 1;
+        float *cosv = falloc(l * (rd / 2)), *sinv = falloc(l * (rd / 2));
+        dec_rope_table_opts(cosv, sinv, pos0, l, rd, cfg->rope_theta, cfg->rope_scaling, cfg->rope_factor, cfg->rope_low_freq_factor,
+                            cfg->rope_high_freq_factor, cfg->rope_original_max_positions);
         _mm_setcsr(env & ~(0x8000u | 0x0040u));
         qr = falloc(m * qw);
         kr = falloc(m * kw);
-        apply_rope(qr, q, nh, hd, m, l, cosv, sinv);
-        apply_rope(kr, k, nkv, hd, m, l, cosv, sinv);
+        apply_rope(qr, q, nh, hd, m, l, cosv, sinv, rd);
+        apply_rope(kr, k, nkv, hd, m, l, cosv, sinv, rd);
         free(cosv); free(sinv);
     }
     /* cache append (a copy, not a seam) */
@@ -582,7 +663,7 @@ DEC_API int dec_block_forward(const block_cfg_t *cfg, const float *const *w, con
             }
     }
     float *ctx = falloc(m * qw);
-    dec_attention(ctx, qr, kcache, vcache, b, l, nh, nkv, hd, cap, s_abs, window, threads);
+    dec_attention(ctx, qr, kcache, vcache, b, l, nh, nkv, hd, cap, s_abs, window, cfg->attn_softcap, threads);
     _mm_setcsr(env & ~(0x8000u | 0x0040u));
     float *op = falloc(m * dm), *r1 = falloc(m * dm);
     rows_gemm(op, ctx, w[W_O], 1, m, dm, qw, threads);

@@ -13,7 +13,7 @@ BLOCK_NAMES = {"norm1": "input_layernorm.weight", "norm1_b": "input_layernorm.bi
                "o_b": "self_attn.o_proj.bias", "norm2": "post_attention_layernorm.weight",
                "norm2_b": "post_attention_layernorm.bias", "gate": "mlp.gate_proj.weight", "gate_b": "mlp.gate_proj.bias",
                "up": "mlp.up_proj.weight", "up_b": "mlp.up_proj.bias", "down": "mlp.down_proj.weight",
-               "down_b": "mlp.down_proj.bias"}
+               "down_b": "mlp.down_proj.bias", "q_norm": "self_attn.q_norm.weight", "k_norm": "self_attn.k_norm.weight"}
 
 
 def hashed_uniform(n, seed):
@@ -103,6 +103,9 @@ def random_lm_weights(cfg, seed, scale=0.02):
                 w[p + "self_attn.%s_proj.bias" % n_] = mat(width)
         if cfg.o_bias:
             w[p + "self_attn.o_proj.bias"] = mat(dm)
+        if getattr(cfg, "qk_norm", False):
+            w[p + "self_attn.q_norm.weight"] = (1 + mat(hd)).astype(np.float32)
+            w[p + "self_attn.k_norm.weight"] = (1 + mat(hd)).astype(np.float32)
         if cfg.mlp_bias:
             w[p + "mlp.up_proj.bias"] = mat(it)
             w[p + "mlp.down_proj.bias"] = mat(dm)
@@ -325,7 +328,9 @@ class OracleLM(object):
         self.bcfg = oracle.block_cfg(cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.intermediate, norm=cfg.norm,
                                      norm_eps=cfg.norm_eps, norm_bias=cfg.norm_bias, qkv_bias=cfg.qkv_bias, o_bias=cfg.o_bias,
                                      mlp=cfg.mlp, mlp_bias=cfg.mlp_bias, rope=cfg.positions == "rope",
-                                     rope_theta=cfg.rope_theta, window=cfg.window)
+                                     rope_theta=cfg.rope_theta, window=cfg.window, rope_scaling=getattr(cfg, "rope_scaling", None),
+                                     rope_dim=getattr(cfg, "rope_dim", None), qk_norm=getattr(cfg, "qk_norm", False),
+                                     attn_softcap=getattr(cfg, "attn_softcap", None))
         self.slots = [block_slots(weights, "model.layers.%d." % i) for i in range(cfg.n_layers)]
 
     def allocate_state(self, b, cap):

@@ -27,7 +27,7 @@ def _vp(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
-def _run(q, kc, vc, l, used, window, at):
+def _run(q, kc, vc, l, used, window, at, softcap=0.0):
     """ctx through the C ABI; `at` = the device-position twin."""
     b, nkv, cap, hd = kc.shape
     nh = q.shape[1]
@@ -38,12 +38,12 @@ def _run(q, kc, vc, l, used, window, at):
         scores = torch.empty((b * nh * l * smax,), device="cuda")
         pos = torch.tensor([used - l], dtype=torch.int32, device="cuda")
         _native.call("b200i_attention_at", 0, None, _vp(ctx), _vp(dq), _vp(dk), _vp(dv), _vp(scores), b, l, nh, nkv, hd, cap,
-                     _vp(pos), window)
+                     _vp(pos), window, softcap)
     else:
         s = used - (max(0, used - l - (window - 1)) if window else 0)
         scores = torch.empty((b * nh * l * s,), device="cuda")
         _native.call("b200i_attention", 0, None, _vp(ctx), _vp(dq), _vp(dk), _vp(dv), _vp(scores), b, l, nh, nkv, hd, cap, used,
-                     window)
+                     window, softcap)
     torch.cuda.synchronize()
     assert _native.lib().b200i_decode_status(0) == 0
     return ctx.cpu().numpy()

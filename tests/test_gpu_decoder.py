@@ -101,6 +101,13 @@ OPTION_SETS = [
     dict(norm="layernorm", norm_bias=True, mlp="gelu", mlp_bias=True, qkv_bias=True, o_bias=True, positions="learned"),
     dict(mlp="gelu_tanh", n_kv_heads=4, norm="rmsnorm_offset"),
     dict(mlp="geglu", window=5),
+    # the option record of transformer/block_options.mojo:40-70 of the reference: q/k norms, score soft cap, partial
+    # rotary, linear and llama3 frequency scaling (their spellings are the reference oracle's; no committed hash pins them)
+    dict(qk_norm=True, attn_softcap=30.0),
+    dict(qk_norm=True, norm="rmsnorm_offset", rope_dim=8, rope_theta=500000.0),
+    dict(rope_scaling={"rope_type": "linear", "factor": 4.0}, mlp="silu"),
+    dict(rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                       "original_max_position_embeddings": 16}, attn_softcap=2.5, qkv_bias=True),
 ]
 
 
@@ -127,6 +134,41 @@ def test_causal_lm_matches_the_oracle_and_decode_equals_prefill(opts):
     assert seq2.tolist() == rseq.tolist() and logits2.tobytes() == rlogits.tobytes()
     with pytest.raises(ValueError):
         lm.forward(np.full((1, 2), cfg.vocab, np.int32))
+    # the reference's other doors on the same model: a stream reads the same continuation, a reset state is a fresh one
+    stream = lm.stream(ids[:, :4], 6)
+    got = np.concatenate([stream.read(4), stream.read(4), stream.read(4)], axis=1)
+    assert got.tolist() == rseq[:, 4:].tolist() and stream.read(1).shape == (3, 0)
+    state = lm.reset_state(state)
+    assert state.positions == 0 and lm.forward(ids, state).tobytes() == want.tobytes()
+
+
+def test_block_option_refusals_and_weight_format():
+    cfg = CausalLMConfig(vocab=97, d_model=48, n_layers=1, n_heads=4, n_kv_heads=2, head_dim=12, intermediate=64, max_positions=64)
+    w = decoder_ref.random_lm_weights(cfg, seed=4, scale=0.2)
+    bw = {k[len("model.layers.0."):].replace("self_attn.", "").replace("mlp.", ""): v for k, v in w.items() if k.startswith("model.layers.0.")}
+    with pytest.raises(ValueError, match="rope_dim"):
+        TransformerBlock(bw, n_heads=4, n_kv_heads=2, rope_dim=7)
+    with pytest.raises(ValueError, match="rope_scaling"):
+        TransformerBlock(bw, n_heads=4, n_kv_heads=2, rope_scaling={"rope_type": "yarn", "factor": 2.0})
+    with pytest.raises(ValueError, match="q_norm.weight"):
+        TransformerBlock(bw, n_heads=4, n_kv_heads=2, qk_norm=True)
+    with pytest.raises(ValueError, match="attn_softcap"):
+        TransformerBlock(bw, n_heads=4, n_kv_heads=2, attn_softcap=-1.0)
+    with pytest.raises(ValueError, match="numeric_profile"):
+        TransformerBlock(bw, n_heads=4, n_kv_heads=2, numeric_profile="int15")
+    with pytest.raises(ValueError, match="weight_format"):
+        CausalLM(cfg, w, weight_format="fp8")
+    ids = np.random.default_rng(1).integers(0, cfg.vocab, (2, 7)).astype(np.int32)
+    # weight_format packs the float32 projections on the way in: the logits are the oracle's on the materialised weights
+    for fmt in ("bfloat16", "int8"):
+        lm = CausalLM(cfg, w, weight_format=fmt, max_positions=32)
+        assert lm.config.max_positions == 32 and lm.blocks[0].weight_format == fmt
+        mat = {k: (lowbit.materialize_one(lowbit.pack_one(v, fmt)) if (v.ndim == 2 and "embed" not in k) else v) for k, v in w.items()}
+        assert lm.forward(ids).tobytes() == decoder_ref.OracleLM(cfg, mat).forward(ids).tobytes()
+        with pytest.raises(ValueError, match="max_positions"):
+            lm.forward(np.zeros((1, 33), np.int32))
+    names = CausalLM(cfg, w).parameters()
+    assert "model.layers.0.q_proj.weight" in names or "model.layers.0.input_layernorm.weight" in names
 
 
 def test_block_subnormal_forcing_inputs():
@@ -310,3 +352,42 @@ def test_embedding_lane_infer_and_batch_cells_on_gpu(kind):
     for a, b in ((0, 1), (1, 8), (8, 64)):
         assert gather(ids64[a:b]).tobytes() == y64[a:b].tobytes()
     assert int(status.item()) == 0
+
+
+def test_causal_lm_load_from_a_checkpoint_directory(tmp_path):
+    """`CausalLM.load` (reference python/mojolearn/models/causal_lm.py:139-150): config.json + model.safetensors of a
+    Qwen3-shaped model (q/k norms, grouped heads, llama3 frequency scaling) and of a tied-embedding Llama written as
+    BF16; the loaded model's logits are the oracle's on the same tensors, bit for bit."""
+    import json
+    from mojolearn_b200.models import config as model_config, safetensors
+    hf = {"model_type": "qwen3", "vocab_size": 97, "hidden_size": 48, "num_hidden_layers": 2, "num_attention_heads": 4,
+          "num_key_value_heads": 2, "head_dim": 12, "intermediate_size": 80, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+          "max_position_embeddings": 64, "hidden_act": "silu",
+          "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                           "original_max_position_embeddings": 16}}
+    plan = model_config.plan_for(hf)
+    w = decoder_ref.random_lm_weights(plan, seed=11, scale=0.2)
+    os.makedirs(tmp_path / "qwen3")
+    json.dump(hf, open(tmp_path / "qwen3" / "config.json", "w"))
+    safetensors.write_file(tmp_path / "qwen3" / "model.safetensors", w)
+    lm = CausalLM.load(tmp_path / "qwen3")
+    ids = np.random.default_rng(3).integers(0, 97, (2, 9)).astype(np.int32)
+    assert lm.forward(ids).tobytes() == decoder_ref.OracleLM(plan, w).forward(ids).tobytes()
+    # a tied head and BF16 storage: widened exactly, or kept as bits when asked for bfloat16 weights
+    hf2 = dict(hf, model_type="llama", tie_word_embeddings=True)
+    hf2.pop("rope_scaling")
+    plan2 = model_config.plan_for(hf2)
+    w2 = decoder_ref.random_lm_weights(plan2, seed=12, scale=0.2)
+    w2.pop("lm_head.weight")
+    as_bf16 = {k: oracle.to_bf16(v.reshape(1, -1) if v.ndim == 1 else v).reshape(v.shape) for k, v in w2.items()}
+    os.makedirs(tmp_path / "llama")
+    json.dump(hf2, open(tmp_path / "llama" / "config.json", "w"))
+    safetensors.write_file(tmp_path / "llama" / "model.safetensors", as_bf16)
+    wide = {k: oracle.from_bf16(v.reshape(1, -1) if v.ndim == 1 else v).reshape(v.shape) for k, v in as_bf16.items()}
+    wide["lm_head.weight"] = wide["model.embed_tokens.weight"]
+    want = decoder_ref.OracleLM(plan2, wide).forward(ids)
+    assert CausalLM.load(tmp_path / "llama").forward(ids).tobytes() == want.tobytes()
+    assert CausalLM.load(tmp_path / "llama", weight_format="bfloat16").forward(ids).tobytes() == want.tobytes()
+    os.remove(tmp_path / "llama" / "model.safetensors")
+    with pytest.raises(FileNotFoundError):
+        CausalLM.load(tmp_path / "llama")

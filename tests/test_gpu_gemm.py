@@ -314,3 +314,42 @@ def test_store_epilogue_bias_and_activation_on_every_plan(m, n, k):
     c8 = oracle.nan_canon(oracle.gemm(a, oracle.dequantize_int8(codes, exps), oracle.OP_NT))
     got = torch_ops.product(da, torch.from_numpy(codes).cuda(), torch.from_numpy(exps).cuda(), linalg.W_INT8_EXP, oracle.OP_NT, bias=dbias, act=1)
     assert got.cpu().numpy().tobytes() == _seams_after(c8, bias, 1).tobytes()
+
+
+@pytest.mark.parametrize("m,n,k", [(9, 20, 304), (32, 132, 640), (1, 64, 2048), (3, 8, 128)])
+def test_gated_store_activation_over_interleaved_rows(m, n, k):
+    """The gated activations (S20-S21: silu(gate) * up, and GELU in SiLU's place) inside the store of a product whose
+    weight rows alternate gate_j, up_j: the output [m, n / 2] is the words of the product followed by the separate
+    activation seam, on the skinny plan unsplit and split (the group fold applies it), with and without a bias."""
+    rng = np.random.default_rng(m * 1000 + n + k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    c = oracle.nan_canon(oracle.gemm(a, w, oracle.OP_NT))
+    da, dw, dbias = torch.from_numpy(a).cuda(), torch.from_numpy(w).cuda(), torch.from_numpy(bias).cuda()
+    leaves = oracle.leaf_count(k)
+    ftz, f32 = oracle.ftz, np.float32
+    for use_bias in (False, True):
+        cb = np.vectorize(lambda v, b: ftz(f32(ftz(v)) + f32(ftz(b))), otypes=[np.float32])(c, bias[None, :]) if use_bias else c
+        for act, name in ((4, "siluf"), (5, "gelu_erf"), (6, "gelu_tanh")):
+            gate, up = cb[:, 0::2], cb[:, 1::2]
+            want = np.vectorize(lambda g, u: ftz(f32(ftz(oracle.math(name, ftz(g)))) * f32(ftz(u))), otypes=[np.float32])(gate, up)
+            for plan, groups in ((torch_ops.PLAN_AUTO, 0), (torch_ops.PLAN_SKINNY, 0), (torch_ops.PLAN_SKINNY, 1), (torch_ops.PLAN_SKINNY, 2)):
+                if groups and groups >= leaves:
+                    continue
+                got = torch_ops.product(da, dw, None, linalg.W_F32, oracle.OP_NT, plan=plan, group_leaves=groups,
+                                        bias=dbias if use_bias else None, act=act)
+                assert got.shape == (m, n // 2) and got.cpu().numpy().tobytes() == want.tobytes(), (use_bias, act, plan, groups)
+            # the same seam as its own kernel over the interleaved product
+            full = torch_ops.product(da, dw, None, linalg.W_F32, oracle.OP_NT, bias=dbias if use_bias else None)
+            out = torch.empty((m, n // 2), device="cuda")
+            _native.call("b200i_act_mul", 0, None, ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(full.data_ptr()), None, m, n // 2, n,
+                         {4: 0, 5: 4, 6: 5}[act], 1)
+            assert out.cpu().numpy().tobytes() == want.tobytes()
+    codes, exps = oracle.quantize_int8(w)
+    c8 = oracle.nan_canon(oracle.gemm(a, oracle.dequantize_int8(codes, exps), oracle.OP_NT))
+    want8 = np.vectorize(lambda g, u: ftz(f32(ftz(oracle.math("siluf", ftz(g)))) * f32(ftz(u))), otypes=[np.float32])(c8[:, 0::2], c8[:, 1::2])
+    got8 = torch_ops.product(da, torch.from_numpy(codes).cuda(), torch.from_numpy(exps).cuda(), linalg.W_INT8_EXP, oracle.OP_NT, act=4)
+    assert got8.cpu().numpy().tobytes() == want8.tobytes()
+    with pytest.raises(_native.NativeError, match="gated store activation"):
+        torch_ops.product(torch.zeros((40, 64), device="cuda"), torch.zeros((8, 64), device="cuda"), None, linalg.W_F32, oracle.OP_NT, act=4)

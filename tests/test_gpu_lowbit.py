@@ -201,3 +201,33 @@ def test_int8_product_profile():
     qb, eb = oracle.quantize_int8(b)
     assert linalg.matmul_int8((qa, ea), (qb, eb)).tobytes() == oracle.gemm_int8(qa, ea, qb, eb).tobytes()
     assert linalg.matmul_int8(a, b).tobytes() == oracle.gemm_int8(qa, ea, qb, eb).tobytes()
+
+
+@pytest.mark.parametrize("chunk", range(4))
+def test_skinny_register_plan_over_leaf_counts(chunk):
+    """The register skinny plan (low-bit weights) over every leaf count from 1 to 40 and a few up to 1024, leaf groups
+    of 1, 2, 4 and 8 (ragged last groups included), 8, 16 and 32-row tiles, int8 and bf16 weights, two column tiles
+    with a ragged edge: the bits of the oracle's tree."""
+    counts = (list(range(1, 41)) + [48, 63, 64, 65, 100, 255, 256, 257, 1000, 1024])[chunk::4]
+    n = 300
+    for p in counts:
+        k = (p - 1) * 128 + (128 if p % 2 == 0 else 32)
+        rng = np.random.default_rng(1000 + p)
+        m = (3, 8, 13, 32)[p % 4]
+        x = (rng.standard_normal((m, k)) * np.exp2(rng.integers(-10, 11, (m, k)))).astype(np.float32)
+        w = (rng.standard_normal((n, k)) * np.exp2(rng.integers(-10, 11, (n, k)))).astype(np.float32)
+        dx = torch.from_numpy(x).cuda()
+        codes, exps = oracle.quantize_int8(w)
+        bits = oracle.to_bf16(w)
+        for kind, dw, ds, wf in ((linalg.W_INT8_EXP, torch.from_numpy(codes).cuda(), torch.from_numpy(exps).cuda(), oracle.dequantize_int8(codes, exps)),
+                                 (linalg.W_BF16, torch.from_numpy(bits).cuda(), None, oracle.from_bf16(bits))):
+            if kind == linalg.W_BF16 and p > 40:
+                continue
+            want = oracle.nan_canon(oracle.gemm_rows(x, wf, oracle.OP_NT))
+            for plan in (torch_ops.PLAN_SKINNY, torch_ops.PLAN_AUTO):
+                for gl in ((0,) if plan == torch_ops.PLAN_AUTO else (0, 1, 2, 4, 8)):
+                    if gl and (p + gl - 1) // gl > 64:
+                        continue
+                    got = torch_ops.product(dx, dw, ds, kind, oracle.OP_NT, plan=plan, group_leaves=gl)
+                    assert got.cpu().numpy().tobytes() == want.tobytes(), (p, m, kind, plan, gl)
+    assert _native.lib().b200i_decode_status(-1) == 0

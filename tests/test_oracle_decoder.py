@@ -207,3 +207,20 @@ def test_masked_score_is_the_fill_when_operands_are_small():
     # the largest dot the shortcut admits: 128 products of two words just below 2^40
     x = np.float32(np.nextafter(np.float32(2.0 ** 40), np.float32(0)))
     assert float(x) * float(x) * 128 < 2.0 ** 88
+
+
+def test_rotary_table_options_default_record_is_the_frozen_table():
+    """The option record at its defaults (no scaling, rope_dim = head_dim) is the v1 table bit for bit; a linear factor
+    divides every inverse frequency once, so the table at position p is not the default table anywhere but p = 0."""
+    cos0, sin0 = oracle.rope_table(3, 20, 16, 10000.0)
+    cos1, sin1 = oracle.rope_table_opts(3, 20, 16, 10000.0, None)
+    assert cos0.tobytes() == cos1.tobytes() and sin0.tobytes() == sin1.tobytes()
+    cos2, sin2 = oracle.rope_table_opts(0, 20, 16, 10000.0, {"rope_type": "linear", "factor": 4.0})
+    base_c, base_s = oracle.rope_table(0, 20, 16, 10000.0)
+    assert cos2[0].tobytes() == base_c[0].tobytes() and cos2[4, 0] == base_c[1, 0] and not np.array_equal(cos2[1], base_c[1])
+    cos3, _ = oracle.rope_table_opts(0, 20, 16, 10000.0, {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                          "high_freq_factor": 4.0, "original_max_position_embeddings": 64})
+    assert np.isfinite(cos3).all() and cos3[:, 0].tobytes() == base_c[:, 0].tobytes()  # the highest frequency keeps its wavelength
+    assert not np.array_equal(cos3[:, 7], base_c[:, 7])  # the lowest one is slowed by the factor
+    cos4, _ = oracle.rope_table_opts(0, 20, 8, 10000.0, None)  # a partial rotary's table is the table of a narrower head
+    assert cos4.tobytes() == oracle.rope_table(0, 20, 8, 10000.0)[0].tobytes()
