@@ -136,6 +136,36 @@ def run_cpu(shapes, steps, warmup, threads):
     return sweep_flops(shapes) * steps / dt / 1e9, dt
 
 
+def serve_oracle_row0(serve_bench, kept, sargs, gpu_hash):
+    """Sequence 0 of the serving run through the CPU oracle: one teacher-forced forward over its prompt and its
+    generated ids, whose last position holds the logits the run ended on. Checker only, never timed as product."""
+    import hashlib
+    import oracle
+    cfg, row = kept["cfg"], kept["row0_ids"]
+    w = serve_bench.build_weights(cfg, sargs.format)  # the run's own weights again (fixed device generator)
+
+    def host(layer):
+        if getattr(layer, "scale", None) is None:
+            return layer.w.cpu().numpy()
+        return oracle.dequantize_int8(layer.w.cpu().numpy(), layer.scale.cpu().numpy())
+
+    def slots(i):
+        p = "model.layers.%d." % i
+        names = dict(q="self_attn.q_proj", k="self_attn.k_proj", v="self_attn.v_proj", o="self_attn.o_proj",
+                     gate="mlp.gate_proj", up="mlp.up_proj", down="mlp.down_proj")
+        out = {slot: host(w[p + name + ".weight"]) for slot, name in names.items()}
+        out["norm1"] = w[p + "input_layernorm.weight"].cpu().numpy()
+        out["norm2"] = w[p + "post_attention_layernorm.weight"].cpu().numpy()
+        return out
+
+    t0 = time.perf_counter()
+    want = oracle.teacher_forced_logits(cfg, row, len(row) - 1, slots, w["model.embed_tokens.weight"].cpu().numpy(), None,
+                                        w["model.norm.weight"].cpu().numpy(), None, host(w["lm_head.weight"]))
+    digest = hashlib.sha256(want[0].tobytes()).hexdigest()[:16]
+    return {"logits_sha256": digest, "equal": digest == gpu_hash, "positions": int(len(row)), "cpu_seconds": time.perf_counter() - t0,
+            "what": "sequence 0 (prompt + generated ids) through the CPU oracle, logits after the last token"}
+
+
 def reference_arm(args, rank, world):
     """The reference's CPU implementation of the path (its AVX2 host product,
     restated; the reference itself is Mojo and cannot be built here), all host
@@ -433,7 +463,10 @@ def main():
                               timed_steps=64, format="int8", no_graph=False)
         del ops
         torch.cuda.empty_cache()
-        serve, _ = serve_bench.run(sargs)
+        kept = {}
+        serve, _ = serve_bench.run(sargs, keep=kept)
+        if rank == 0 and world == 1 and not args.skip_cpu:
+            serve["oracle_row0"] = serve_oracle_row0(serve_bench, kept, sargs, serve["row0_logits_sha256"])
         if world > 1:
             # the single-GPU figure of the same run, on rank 0 alone while the others wait: the sharded tokens/s over
             # N times this one is the scaling efficiency, and the hashes say the sharded logits are the same words

@@ -10,6 +10,7 @@
 #include "../../include/b200i.h"
 #include "comm.cuh"
 #include "decode.cuh"
+#include "decode_pair.cuh"
 #include "decoder.cuh"
 #include "gemm_tile.cuh"
 #include "gemm_skinny.cuh"
@@ -428,7 +429,7 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
     } else if (plan.kind == PLAN_DECODE) {
         if (!decode_plan_fits(m, n, k, op, wkind) || !aligned(b, 16) || !aligned(a, 16))
             return fail(err, err_cap, "identical gemm: the decode plan needs op NT, m <= %d, k a multiple of 16 and 16-byte aligned weights", DECODE_MAX_M);
-        g_launches += launch_decode(g, sm_count(dev), st);
+        g_launches += launch_decode_plan(g, sm_count(dev), st);
     } else if (plan.kind == PLAN_T128) {
         launch_tile<128, 128, 2, 2, 2>(g, plan.groups, st);
         g_launches++;

@@ -65,9 +65,10 @@ def build_ids(cfg, batch, prompt, device=None):
     return torch.randint(0, cfg.vocab, (batch, prompt), generator=gen, device=dev, dtype=torch.int32)
 
 
-def run(args, solo=False):
+def run(args, solo=False, keep=None):
     """One serving run. `solo`: ignore the process group and run the whole model on this rank's GPU alone (the
-    single-GPU figure a sharded run is compared with)."""
+    single-GPU figure a sharded run is compared with). `keep`: a dict that receives what a checker needs to replay
+    sequence 0 elsewhere (its prompt + generated ids, the plan)."""
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     if solo:
         rank, world = 0, 1
@@ -135,11 +136,17 @@ def run(args, solo=False):
                       "prefill": ("cut by sequences, KV re-cut by one all-to-all" if lm.prefill_by_batch else "cut by output columns") if world > 1 else "one GPU"},
            "ids_sha256": hashlib.sha256(seq.tobytes()).hexdigest()[:16],
            "logits_sha256": hashlib.sha256(logits.cpu().numpy().tobytes()).hexdigest()[:16],
+           # sequence 0 alone: the logits after its last generated token
+           "row0_logits_sha256": hashlib.sha256(logits[0].cpu().numpy().tobytes()).hexdigest()[:16],
            # the library counts a captured launch once, at capture, when nothing runs; replays are counted here
            "gpu_launches": int(_native.lib().b200i_launch_count() - launches0 + (session.replays - 1) * session.graph_launches
                                if session.replays else _native.lib().b200i_launch_count() - launches0)}
     if breakdown is not None:
         out["breakdown_rank0"] = breakdown
+    if keep is not None:
+        import numpy as np
+        keep["cfg"] = cfg
+        keep["row0_ids"] = np.concatenate([ids[0].cpu().numpy().reshape(-1), seq[0].reshape(-1)]).astype(np.int32)
     return out, rank
 
 

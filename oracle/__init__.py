@@ -414,3 +414,24 @@ def argmax(logits):
     f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64]
     f(_ptr(out), _ptr(logits), rows, vocab)
     return out
+
+
+def teacher_forced_logits(cfg, ids_row, first, layer_slots, embed, pos_table, final_w, final_b, head):
+    """Logits [len - first, vocab] of positions first .. len-1 of ONE sequence through a decoder LM whose plan is `cfg`
+    (the attributes of a CausalLMConfig: d_model, n_layers, n_heads, ...). `layer_slots(i)` returns the float32 slot
+    dict of block i, materialised on demand so that only one layer's weights are held at a time. A position's row
+    reads only earlier keys and every product cell is independent of the rows beside it, so the logits at position
+    p are what a stepped decode produces after p tokens (decode equals prefill,
+    transformer/IDENTICAL_TRANSFORMER_CONTRACT.md:540-565 of the reference)."""
+    ids = np.asarray(ids_row, dtype=np.int32).reshape(1, -1)
+    x = embedding(embed, ids)
+    if pos_table is not None:
+        x = add_positions(x, pos_table, 0)
+    bcfg = block_cfg(cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.intermediate, norm=cfg.norm,
+                     norm_eps=cfg.norm_eps, norm_bias=cfg.norm_bias, qkv_bias=cfg.qkv_bias, o_bias=cfg.o_bias,
+                     mlp=cfg.mlp, mlp_bias=cfg.mlp_bias, rope=cfg.positions == "rope", rope_theta=cfg.rope_theta,
+                     window=cfg.window)
+    for i in range(cfg.n_layers):
+        x = block_forward(bcfg, layer_slots(i), x)
+    hn = norm(x[0, first:], final_w, final_b, cfg.norm_eps, cfg.norm)
+    return gemm_rows(hn, head, OP_NT)

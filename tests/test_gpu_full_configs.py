@@ -26,21 +26,7 @@ from mojolearn_b200 import serve_bench  # noqa: E402
 from mojolearn_b200.models import CausalLM, CausalLMConfig  # noqa: E402
 
 
-def oracle_teacher_forced(cfg, ids_row, first, layer_slots, embed, pos_table, final_w, final_b, head):
-    """Logits [len - first, vocab] of positions first .. len-1 of one sequence. `layer_slots(i)` returns the
-    float32 slot dict of block i (materialised on demand, so only one layer's weights are held at a time)."""
-    ids = np.asarray(ids_row, dtype=np.int32).reshape(1, -1)
-    x = oracle.embedding(embed, ids)
-    if pos_table is not None:
-        x = oracle.add_positions(x, pos_table, 0)
-    bcfg = oracle.block_cfg(cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.intermediate, norm=cfg.norm,
-                            norm_eps=cfg.norm_eps, norm_bias=cfg.norm_bias, qkv_bias=cfg.qkv_bias, o_bias=cfg.o_bias,
-                            mlp=cfg.mlp, mlp_bias=cfg.mlp_bias, rope=cfg.positions == "rope", rope_theta=cfg.rope_theta,
-                            window=cfg.window)
-    for i in range(cfg.n_layers):
-        x = oracle.block_forward(bcfg, layer_slots(i), x)
-    hn = oracle.norm(x[0, first:], final_w, final_b, cfg.norm_eps, cfg.norm)
-    return oracle.gemm_rows(hn, head, oracle.OP_NT)
+oracle_teacher_forced = oracle.teacher_forced_logits
 
 
 def check_continuation(seq_row, kept_row, want_logits, prompt):

@@ -231,3 +231,56 @@ def test_skinny_register_plan_over_leaf_counts(chunk):
                     got = torch_ops.product(dx, dw, ds, kind, oracle.OP_NT, plan=plan, group_leaves=gl)
                     assert got.cpu().numpy().tobytes() == want.tobytes(), (p, m, kind, plan, gl)
     assert _native.lib().b200i_decode_status(-1) == 0
+
+
+@pytest.mark.parametrize("m", [1, 2])
+def test_leaf_pair_decode_kernel(m):
+    """Weights wide enough (n >= 16 rows per SM) that the decode plan takes its leaf-pair kernel for bf16 / int8 at one and
+    two activation rows: k below one leaf, short last leaves, leaf counts that leave the lane fold an odd tail, a row count
+    that leaves the last block of a CTA ragged; then operands that fail admission (the flushed per-row fallback) and row
+    scales outside the range of the one-fma dequantisation."""
+    rng = np.random.default_rng(20 + m)
+    n = 2403 + 8 * 148  # > 16 * 148 rows, odd
+    dec = torch_ops.PLAN_DECODE
+    for k in (16, 112, 128, 144, 400, 1024, 1168, 2048, 2112, 4096, 11008):
+        codes, scales, exps, wb = _weights(n, k, 30 + k)
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        dx = torch.from_numpy(x).cuda()
+        got = torch_ops.product(dx, torch.from_numpy(codes).cuda(), torch.from_numpy(exps).cuda(), linalg.W_INT8_EXP, oracle.OP_NT, plan=dec)
+        assert got.cpu().numpy().tobytes() == oracle.gemm_rows(x, oracle.dequantize_int8(codes, exps), oracle.OP_NT).tobytes(), ("int8", k)
+        got = torch_ops.product(dx, torch.from_numpy(codes).cuda(), torch.from_numpy(scales).cuda(), linalg.W_INT8_SCALE, oracle.OP_NT, plan=dec)
+        assert got.cpu().numpy().tobytes() == oracle.gemm_rows(x, oracle.dequantize_int8_scaled(codes, scales), oracle.OP_NT).tobytes(), ("int8s", k)
+        got = torch_ops.product(dx, torch.from_numpy(wb).cuda(), None, linalg.W_BF16, oracle.OP_NT, plan=dec)
+        assert got.cpu().numpy().tobytes() == oracle.gemm_rows(x, oracle.from_bf16(wb), oracle.OP_NT).tobytes(), ("bf16", k)
+        assert _native.lib().b200i_decode_status(-1) == 0, k
+    # admission fails: tiny activations with subnormals among them, small weights; exotic exponents and scales on some rows
+    k = 1168
+    x = (rng.standard_normal((m, k)) * 2.0 ** -62).astype(np.float32)
+    x[0, ::9] = np.float32(3e-42)
+    codes = rng.integers(-127, 128, (n, k)).astype(np.int8)
+    exps = rng.integers(-70, -58, n).astype(np.int32)
+    exps[:6] = [-140, 127, 121, -127, -101, 101]
+    exps[1000:1003] = [-150, 100, -126]
+    dx, dc = torch.from_numpy(x).cuda(), torch.from_numpy(codes).cuda()
+    want = oracle.nan_canon(oracle.gemm_rows(x, oracle.dequantize_int8(codes, exps), oracle.OP_NT))
+    got = torch_ops.product(dx, dc, torch.from_numpy(exps).cuda(), linalg.W_INT8_EXP, oracle.OP_NT, plan=dec)
+    assert got.cpu().numpy().tobytes() == want.tobytes()
+    scales = (rng.uniform(0.5, 2.0, n) * 2.0 ** -66).astype(np.float32)
+    scales[:5] = [np.float32(2e-42), np.float32(3e37), np.float32(1.0), np.float32(0.0), np.float32(-0.75)]
+    want = oracle.nan_canon(oracle.gemm_rows(x, oracle.dequantize_int8_scaled(codes, scales), oracle.OP_NT))
+    got = torch_ops.product(dx, dc, torch.from_numpy(scales).cuda(), linalg.W_INT8_SCALE, oracle.OP_NT, plan=dec)
+    assert got.cpu().numpy().tobytes() == want.tobytes()
+    wb = oracle.to_bf16((rng.standard_normal((n, k)) * 2.0 ** -64).astype(np.float32))
+    want = oracle.nan_canon(oracle.gemm_rows(x, oracle.from_bf16(wb), oracle.OP_NT))
+    got = torch_ops.product(dx, torch.from_numpy(wb).cuda(), None, linalg.W_BF16, oracle.OP_NT, plan=dec)
+    assert got.cpu().numpy().tobytes() == want.tobytes()
+    # ordinary activations against weights of which only a few rows fail admission
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    wf = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    wf[5] *= np.float32(2.0 ** -120)
+    wf[n - 2, 100:130] = np.float32(1e-40)
+    wb = oracle.to_bf16(wf)
+    want = oracle.nan_canon(oracle.gemm_rows(x, oracle.from_bf16(wb), oracle.OP_NT))
+    got = torch_ops.product(torch.from_numpy(x).cuda(), torch.from_numpy(wb).cuda(), None, linalg.W_BF16, oracle.OP_NT, plan=dec)
+    assert got.cpu().numpy().tobytes() == want.tobytes()
+    assert _native.lib().b200i_decode_status(-1) == 0
