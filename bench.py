@@ -43,8 +43,8 @@ SWEEP = [(4096, 4096, 4096), (8192, 8192, 1024), (128, 11008, 4096), (2048, 5030
 DECODE_N, DECODE_K = 11008, 4096
 CONFIG1 = (1024, 1024, 1024)
 # DRAM bytes of one launch from the committed ncu captures (profiles/): the bench cannot read counters itself
-DECODE_INT8_M1_DRAM_BYTES = 45177000
-PACKED_4096_DRAM_BYTES = None  # set from profiles/gemm_packed_kernel_4096cubed.md
+DECODE_INT8_M1_DRAM_BYTES = 45202944  # profiles/decode_pair_kernel_int8_m1_11008x4096.md
+PACKED_4096_DRAM_BYTES = 1060e6 + 940.4e6  # dram__bytes_read + dram__bytes_write of one 4096-cubed launch (profiles/gemm_packed_kernel_4096cubed.md)
 
 
 def sweep_flops(shapes):
@@ -396,10 +396,10 @@ def main():
             del graph
         del wq
     d1 = decode[("int8", 1)]
-    roofline_decode = {"bound": "hbm", "kernel": "decode_kernel<int8,1>", "achieved": d1["gbs"], "peak": hbm_peak, "unit": "GB/s",
+    roofline_decode = {"bound": "hbm", "kernel": "decode_pair_kernel<int8,1>", "achieved": d1["gbs"], "peak": hbm_peak, "unit": "GB/s",
                        "frac": d1["gbs"] / hbm_peak, "peak_source": hbm_src + " HBM copy bandwidth", "us_per_launch": d1["us"],
                        "algorithmic_bytes": d1["bytes"], "traffic": DECODE_INT8_M1_DRAM_BYTES,
-                       "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, profiles/decode_kernel_int8_m1_11008x4096.md",
+                       "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, profiles/decode_pair_kernel_int8_m1_11008x4096.md",
                        "timing": "CUDA events around one graph replay of 24 launches",
                        "workload": "W[11008, 4096] (baseline configuration 3), rows M in {1, 8, 32, 128}: int8 + int32 row exponents, "
                                    "int8 + float32 row scales U(0.001, 0.02), bf16; float32 at 1 and 8 rows",

@@ -67,15 +67,22 @@ __host__ __device__ inline PairLayout pair_layout(int m, int k, int wkind, int r
     l.fac_off = off;
     if (wkind != W_BF16) off += ((size_t)rows * 4 + 127) / 128 * 128;
     l.stage_off = off;
-    const long long room = (long long)DP_SMEM_LIMIT - 256 - (long long)off;
+    const long long room = (long long)DP_SMEM_LIMIT - 384 - (long long)off;
     int stages = room > 0 ? (int)(room / (long long)l.stage_bytes) : 0;
     if (stages > 16) stages = 16;
     l.stages = stages;
     off += (size_t)(stages > 0 ? stages : 0) * l.stage_bytes;
-    l.bar_off = off;
-    off += 256;
+    l.bar_off = off; // full[16], empty[16], the producer's stage counter
+    off += 384;
     l.total = off;
     return l;
+}
+
+// Stages in work at once (one group of warps each) for a ring of `stages` slots: all the warps if the ring leaves two
+// slots of look-ahead, never more than the ring.
+__host__ __device__ inline int dp_groups(int stages, int tps) {
+    int g = DP_CONSUMERS / tps, cap = stages - 2 > stages / 2 ? stages - 2 : stages / 2;
+    return g < cap ? g : cap;
 }
 
 inline bool decode_pair_fits(long long m, long long n, long long k, int op, int wkind, int grid) {
@@ -85,9 +92,7 @@ inline bool decode_pair_fits(long long m, long long n, long long k, int op, int 
     if ((size_t)m * l.xstride * 4 > (size_t)DP_X_BYTES_MAX || l.stages < 2) return false;
     // at least four warps at work: with long activation rows the ring is too short and decode_kernel does better
     const int tps = (l.lps + DP_TASK_LEAVES - 1) / DP_TASK_LEAVES;
-    int groups = DP_CONSUMERS / tps;
-    if (groups > l.stages / 2) groups = l.stages / 2;
-    return groups * tps >= 4;
+    return dp_groups(l.stages, tps) * tps >= 4;
 }
 
 __device__ __forceinline__ void dp_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * DP_CONSUMERS) : "memory"); }
@@ -171,11 +176,13 @@ __global__ void __launch_bounds__(DP_THREADS, 1) decode_pair_kernel(const GemmAr
     const int nodes = (leaves + DP_TASK_LEAVES - 1) / DP_TASK_LEAVES; // fold-tree nodes of level 3 per cell: what reaches shared memory
     const int chunks = (leaves + lps - 1) / lps;
     const int tps = (lps + DP_TASK_LEAVES - 1) / DP_TASK_LEAVES; // warp tasks per stage = warps per group
-    // Stages in work at once, one group of warps each. A group owns two ring slots (stage s goes to group s % groups and to
-    // slot s % (2 * groups)): one fills while the other is walked, and because every use of a slot is seen by the same
-    // warps in order, a phase-parity wait can never mistake an older phase for the one it wants.
-    const int groups = min(DP_CONSUMERS / tps, lay.stages / 2);
-    const int nst = 2 * groups;
+    // Stages in work at once, one group of warps each: stage s goes to group s % groups and to ring slot s % nst. A group
+    // does not see every use of a slot, and a phase-parity wait cannot tell "one phase behind" from "done"; so the
+    // producer publishes how many stages it has issued, and a group looks for a stage's data only once that stage has
+    // been issued: by then the slot's previous use has been consumed, so its phase is the one before the awaited one.
+    const int groups = dp_groups(lay.stages, tps);
+    const int nst = lay.stages;
+    volatile int *issued = reinterpret_cast<volatile int *>(full + 32);
     const size_t row_bytes = (size_t)k * ES;
     const size_t chunk_bytes = (size_t)lay.chunk_k * ES;
 
@@ -187,6 +194,7 @@ __global__ void __launch_bounds__(DP_THREADS, 1) decode_pair_kernel(const GemmAr
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], tps);
         }
+        *issued = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -217,6 +225,8 @@ __global__ void __launch_bounds__(DP_THREADS, 1) decode_pair_kernel(const GemmAr
                 __syncwarp();
                 if (lane < valid)
                     bulk_copy_g2s(slot_base + (size_t)lane * pitch, wbase + (size_t)(row0 + lane) * row_bytes + koff, bytes, &full[slot]);
+                __syncwarp();
+                if (lane == 0) *issued = s_index + 1;
             }
         }
         return;
@@ -287,7 +297,13 @@ __global__ void __launch_bounds__(DP_THREADS, 1) decode_pair_kernel(const GemmAr
             const bool ok0 = j0 < lps && t0 < leaves, ok1 = ok0 && j0 + 1 < lps && t0 + 1 < leaves;
             const int len0 = ok0 ? min(leaf, k - t0 * leaf) : 0, len1 = ok1 ? min(leaf, k - (t0 + 1) * leaf) : 0;
             // every lane observes the completion itself: it reads what the copy engine wrote
-            const bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(&full[slot], round & 1u));
+            bool ok = true;
+            for (unsigned spin = 0; *issued <= s; spin++)
+                if (spin >= DEC_SPIN_LIMIT) {
+                    ok = false;
+                    break;
+                }
+            ok = __all_sync(0xFFFFFFFFu, ok && mbar_wait(&full[slot], round & 1u));
             if (!ok) {
                 if (lane == 0) atomicExch(&g_decode_status, 2);
                 alive = false;

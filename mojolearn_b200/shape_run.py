@@ -25,7 +25,8 @@ def main():
     ap.add_argument("n", type=int)
     ap.add_argument("k", type=int)
     ap.add_argument("--op", default="NT", choices=sorted(OPS))
-    ap.add_argument("--wkind", default="f32", choices=["f32", "bf16", "int8", "int8s"])
+    ap.add_argument("--wkind", default="f32", choices=["f32", "bf16", "int8", "int8s", "int8i32"],
+                    help="int8i32: the int8 x int8 -> int32 product profile (both operands int8 codes with row exponents, op NT)")
     ap.add_argument("--plan", type=int, default=-1)
     ap.add_argument("--groups", type=int, default=0)
     ap.add_argument("--reps", type=int, default=5)
@@ -36,6 +37,8 @@ def main():
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(0)
     m, n, k, op = args.m, args.n, args.k, OPS[args.op]
+    if args.wkind == "int8i32":
+        return int8_product(args, dev, g)
     a = torch.randn((k, m) if op == linalg.OP_TN else (m, k), generator=g, device=dev)
     wshape = (n, k) if op == linalg.OP_NT else (k, n)
     ws, scale, wkind, wbytes = [], None, linalg.W_F32, 4
@@ -86,6 +89,26 @@ def main():
     nbytes = m * k * 4 + n * k * wbytes + (n * 4 if scale is not None else 0) + m * n * 4
     print(json.dumps({"m": m, "n": n, "k": k, "op": args.op, "wkind": args.wkind, "plan": args.plan, "groups": args.groups, "graph": bool(args.graph),
                       "ms": ms, "tflops": 2.0 * m * n * k / (ms * 1e-3) / 1e12, "algorithmic_gbs": nbytes / (ms * 1e-3) / 1e9}))
+
+
+def int8_product(args, dev, g):
+    m, n, k = args.m, args.n, args.k
+    qa = torch.randint(-127, 128, (m, k), generator=g, device=dev, dtype=torch.int8)
+    ea = torch.randint(-10, -5, (m,), generator=g, device=dev, dtype=torch.int32)
+    qbs = [torch.randint(-127, 128, (n, k), generator=g, device=dev, dtype=torch.int8) for _ in range(args.buffers)]
+    eb = torch.randint(-10, -5, (n,), generator=g, device=dev, dtype=torch.int32)
+    for i in range(args.warmup):
+        torch_ops.matmul_int8(qa, ea, qbs[i % len(qbs)], eb)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.reps):
+        torch_ops.matmul_int8(qa, ea, qbs[i % len(qbs)], eb)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.reps
+    print(json.dumps({"m": m, "n": n, "k": k, "op": "NT", "wkind": "int8i32", "ms": ms, "tops": 2.0 * m * n * k / (ms * 1e-3) / 1e12,
+                      "algorithmic_gbs": (m * k + n * k + 4 * m * n) / (ms * 1e-3) / 1e9}))
 
 
 if __name__ == "__main__":

@@ -203,6 +203,28 @@ def test_int8_product_profile():
     assert linalg.matmul_int8(a, b).tobytes() == oracle.gemm_int8(qa, ea, qb, eb).tobytes()
 
 
+def test_int8_product_on_tensor_cores():
+    """k a multiple of 16: the product runs as tcgen05 int8 MMAs into an int32 accumulator in tensor memory. Ragged tiles
+    in m and n, k below / at / across the 128-byte stage, the largest sums an int32 can hold, extreme exponents."""
+    rng = np.random.default_rng(10)
+    for (m, n, k) in [(1, 7, 16), (37, 41, 1008), (128, 128, 128), (130, 257, 400), (300, 515, 4096), (5, 129, 144)]:
+        qa = rng.integers(-127, 128, (m, k)).astype(np.int8)
+        qb = rng.integers(-127, 128, (n, k)).astype(np.int8)
+        ea = rng.integers(-20, 20, m).astype(np.int32)
+        eb = rng.integers(-20, 20, n).astype(np.int32)
+        assert linalg.matmul_int8((qa, ea), (qb, eb)).tobytes() == oracle.gemm_int8(qa, ea, qb, eb).tobytes(), (m, n, k)
+    m, n, k = 3, 5, 131072  # |sum| up to 127 * 127 * 131072 < 2^31
+    qa = np.full((m, k), 127, np.int8)
+    qb = np.full((n, k), 127, np.int8)
+    qa[1] = -127
+    qb[2, ::2] = -128
+    qa[2, : k // 2] = 0
+    ea = np.array([0, -140, 100], np.int32)
+    eb = np.array([0, 120, -130, 5, -5], np.int32)
+    assert linalg.matmul_int8((qa, ea), (qb, eb)).tobytes() == oracle.gemm_int8(qa, ea, qb, eb).tobytes()
+    assert _native.lib().b200i_decode_status(-1) == 0
+
+
 @pytest.mark.parametrize("chunk", range(4))
 def test_skinny_register_plan_over_leaf_counts(chunk):
     """The register skinny plan (low-bit weights) over every leaf count from 1 to 40 and a few up to 1024, leaf groups
