@@ -693,8 +693,8 @@ int64_t b200i_gemm_int8(int64_t device, void *stream, float *c, const int8_t *qa
     if (select_device(device, err, err_cap, &dev)) return 1;
     const long long cells = m * n;
     // the tensor-core kernel wherever its 16-byte copies are aligned (k a multiple of 16); one thread per cell otherwise
-    if (gemm_int8_mma_fits(qa, qb, k) && (m + I8_TILE - 1) / I8_TILE <= 0x7FFFFFFFll && (n + I8_TILE - 1) / I8_TILE <= 65535)
-        launch_gemm_int8_mma(c, reinterpret_cast<const signed char *>(qa), ea, reinterpret_cast<const signed char *>(qb), eb, (int)m, (int)n, (int)k, static_cast<cudaStream_t>(stream));
+    if (gemm_int8_mma_fits(qa, qb, m, n, k))
+        launch_gemm_int8_mma(c, reinterpret_cast<const signed char *>(qa), ea, reinterpret_cast<const signed char *>(qb), eb, (int)m, (int)n, (int)k, sm_count(dev), static_cast<cudaStream_t>(stream));
     else
         gemm_int8_flat_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(c, reinterpret_cast<const signed char *>(qa), ea, reinterpret_cast<const signed char *>(qb), eb, (int)m, (int)n, (int)k);
     g_launches++;

@@ -207,7 +207,7 @@ def test_int8_product_on_tensor_cores():
     """k a multiple of 16: the product runs as tcgen05 int8 MMAs into an int32 accumulator in tensor memory. Ragged tiles
     in m and n, k below / at / across the 128-byte stage, the largest sums an int32 can hold, extreme exponents."""
     rng = np.random.default_rng(10)
-    for (m, n, k) in [(1, 7, 16), (37, 41, 1008), (128, 128, 128), (130, 257, 400), (300, 515, 4096), (5, 129, 144)]:
+    for (m, n, k) in [(1, 7, 16), (37, 41, 1008), (128, 128, 128), (130, 257, 400), (300, 515, 4096), (5, 129, 144), (2048, 2600, 272), (1300, 4100, 640)]:
         qa = rng.integers(-127, 128, (m, k)).astype(np.int8)
         qb = rng.integers(-127, 128, (n, k)).astype(np.int8)
         ea = rng.integers(-20, 20, m).astype(np.int32)
