@@ -169,7 +169,11 @@ int64_t b200i_dequantize_int8(int64_t device, void *stream, float *y, const int8
 
 /* int8i32.v1 product at OP_NT: exact int32 sum of code products, one
  * dequantisation per cell. Replaces identical_gemm_int8_into
- * (gemm/checks/gemm_lowbit.mojo:557-589). Refuses k > 131072. */
+ * (gemm/checks/gemm_lowbit.mojo:557-589) and the tensor-core form
+ * gemm/checks/gemm_int8_mma.mojo:545-620. Refuses k > 131072. With k a multiple
+ * of 16 and 16-byte aligned code storage the sum runs as tcgen05 int8 MMAs into
+ * an int32 accumulator in tensor memory (any order of an exact integer sum gives
+ * the same word); otherwise one thread walks each cell. */
 int64_t b200i_gemm_int8(int64_t device, void *stream, float *c, const int8_t *qa, const int32_t *ea, const int8_t *qb,
                         const int32_t *eb, int64_t m, int64_t n, int64_t k, char *err, int64_t err_cap);
 
@@ -326,8 +330,8 @@ int64_t b200i_comm_destroy(void *comm);
 /* Status word of the bounded device-side waits on `device` (synchronises the
  * device): 0 = no wait ever ran out; 1 / 2 = the decode plan's producer / a consumer
  * gave up waiting on a stage, 3 = the decode attention's value ring, 4 / 5 = the
- * packed plan's ring, 6 / 7 = the prepacked skinny plan's ring, 8 = a wait for a
- * peer GPU's arrival flag; -1 = the word could not be read. A nonzero word is
+ * packed plan's ring, 8 = a wait for a peer GPU's tagged words, 9 = the int8
+ * tensor-core product's stage or completion barrier; -1 = the word could not be read. A nonzero word is
  * cleared by the read. A kernel whose wait ran out skips its stores, so its output
  * is incomplete. The b200i_host_* calls read the word after their final
  * synchronise and return status 1 with a message, like any other error (the
