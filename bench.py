@@ -337,7 +337,33 @@ def main():
                "tflops": 2.0 * CONFIG1[0] * CONFIG1[1] * CONFIG1[2] / (c1_us * 1e-6) / 1e12,
                "frac_fp32": 2.0 * CONFIG1[0] * CONFIG1[1] * CONFIG1[2] / (c1_us * 1e-6) / 1e12 / fp32_peak,
                "l2": "a 160 MB buffer is written between timed launches", "launches_timed": 10}
-    del flush, a1, b1, c1
+    del a1, b1, c1
+
+    # ---- the int8 x int8 -> int32 product profile (tensor cores): 4096 cubed, timed on its own like configuration 1 ----
+    gi = torch.Generator(device=dev).manual_seed(3)
+    qa8 = torch.randint(-127, 128, (4096, 4096), generator=gi, device=dev, dtype=torch.int8)
+    qb8 = torch.randint(-127, 128, (4096, 4096), generator=gi, device=dev, dtype=torch.int8)
+    ea8 = torch.randint(-10, -5, (4096,), generator=gi, device=dev, dtype=torch.int32)
+    eb8 = torch.randint(-10, -5, (4096,), generator=gi, device=dev, dtype=torch.int32)
+    for _ in range(3):
+        torch_ops.matmul_int8(qa8, ea8, qb8, eb8)
+    i8_ms = []
+    for _ in range(10):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch_ops.matmul_int8(qa8, ea8, qb8, eb8)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        i8_ms.append(e0.elapsed_time(e1))
+    i8_us = statistics.median(i8_ms) * 1e3
+    i8_tops = 2.0 * 4096 ** 3 / (i8_us * 1e-6) / 1e12
+    int8_product = {"kernel": "gemm_int8_mma_kernel (tcgen05.mma kind::i8, int32 accumulator in tensor memory)", "shape": [4096, 4096, 4096],
+                    "us": i8_us, "tops": i8_tops, "bound": "tensor", "peak": 4500.0, "unit": "TOP/s", "frac": i8_tops / 4500.0,
+                    "peak_source": "nominal dense int8 rate of the part (twice the nominal bf16 rate; no measured int8 figure exists)",
+                    "l2": "a 160 MB buffer is written between timed launches", "launches_timed": 10,
+                    "note": "no baseline configuration uses this product profile; it is the one place of the path where an MMA is contract-legal"}
+    del flush, qa8, qb8, ea8, eb8
 
     # ---- decode kernel against HBM: weights [11008, 4096] in three storage kinds, one activation row ----
     peaks_file = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -494,7 +520,7 @@ def main():
                            "l2": "inputs larger than L2: one pass reads 1.5 GB of operands",
                            "bit_exact": "every product is the oracle's bits (tests/test_gpu_gemm.py)"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
-                "roofline_decode": roofline_decode, "cpu_baseline": cpu, "config1": config1,
+                "roofline_decode": roofline_decode, "cpu_baseline": cpu, "config1": config1, "int8_product": int8_product,
                 "decode": {"metric": "int8w_matvec_rows_per_s", "value": 1e6 / d1["us"], "unit": "rows/s",
                            "weights": "int8 [11008, 4096] + int32 row exponents", "rotating_weight_buffers": nbuf},
                 "serve": serve}

@@ -380,7 +380,9 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
         const bool dec = decode_plan_fits(m, n, k, op, wkind) && al16;
         const bool skinny = skinny_plan_fits(m, n, k, op) && al16;
         const bool wide = n >= DECODE_WIDE_N && (wkind == W_BF16 || m == 3);
-        const int prefer_m = (wkind != W_F32 && skinny && !wide) ? DECODE_PREFER_M_LOWBIT : DECODE_PREFER_M;
+        // low-bit weights: the leaf-pair decode kernel wherever it fits (up to four rows), else the rule above
+        const bool pair = wkind != W_F32 && decode_pair_fits(m, n, k, op, wkind, sm_count(dev));
+        const int prefer_m = pair ? DP_MAX_M : ((wkind != W_F32 && skinny && !wide) ? DECODE_PREFER_M_LOWBIT : DECODE_PREFER_M);
         if (dec && m <= prefer_m && !(skinny && epilogue_pairs(g.epi))) plan = Plan{PLAN_DECODE, g.leaves, 1}; // (a gated store needs the skinny plan)
         else if (skinny) plan = choose_skinny(m, n, k, sm_count(dev), wkind != W_F32);
         else if (dec) plan = Plan{PLAN_DECODE, g.leaves, 1};

@@ -1,4 +1,4 @@
-// The row-streaming decode plan for low-bit weights at one or two activation rows.
+// The row-streaming decode plan for low-bit weights at one to four activation rows.
 //
 // decode_kernel (decode.cuh) gives a lane one weight row and one leaf. For bf16 and int8 weights that
 // plan is bound by its own instruction stream, not by HBM: with valid data already resident in the ring
@@ -26,6 +26,7 @@
 
 namespace b200i {
 
+constexpr int DP_MAX_M = 4;           // activation rows
 constexpr int DP_CONSUMERS = 16;
 constexpr int DP_THREADS = 32 * (DP_CONSUMERS + 1);
 constexpr int DP_ROWS = 8;            // weight rows per stage
@@ -86,7 +87,7 @@ __host__ __device__ inline int dp_groups(int stages, int tps) {
 }
 
 inline bool decode_pair_fits(long long m, long long n, long long k, int op, int wkind, int grid) {
-    if (wkind == W_F32 || m > 2 || !decode_plan_fits(m, n, k, op, wkind)) return false;
+    if (wkind == W_F32 || m > DP_MAX_M || !decode_plan_fits(m, n, k, op, wkind)) return false;
     if (n < 16ll * grid || dp_rows_per_cta(n, grid) > DP_ROWS_MAX) return false;
     const PairLayout l = pair_layout((int)m, (int)k, wkind, dp_rows_per_cta(n, grid));
     if ((size_t)m * l.xstride * 4 > (size_t)DP_X_BYTES_MAX || l.stages < 2) return false;
@@ -391,13 +392,20 @@ __global__ void __launch_bounds__(DP_THREADS, 1) decode_pair_kernel(const GemmAr
 
 template <int WK>
 inline int launch_decode_pair_m(const GemmArgs &g, int grid, size_t smem, cudaStream_t st) {
-    if (g.m == 1) {
-        cudaFuncSetAttribute(decode_pair_kernel<WK, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, DP_SMEM_LIMIT);
-        decode_pair_kernel<WK, 1><<<grid, DP_THREADS, smem, st>>>(g);
-    } else {
-        cudaFuncSetAttribute(decode_pair_kernel<WK, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, DP_SMEM_LIMIT);
-        decode_pair_kernel<WK, 2><<<grid, DP_THREADS, smem, st>>>(g);
+#define B200I_DP_CASE(MM)                                                                                             \
+    case MM:                                                                                                          \
+        cudaFuncSetAttribute(decode_pair_kernel<WK, MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, DP_SMEM_LIMIT); \
+        decode_pair_kernel<WK, MM><<<grid, DP_THREADS, smem, st>>>(g);                                                \
+        break;
+    switch (g.m) {
+        B200I_DP_CASE(1)
+        B200I_DP_CASE(2)
+        B200I_DP_CASE(3)
+        B200I_DP_CASE(4)
+    default:
+        return 0;
     }
+#undef B200I_DP_CASE
     return 1;
 }
 

@@ -255,10 +255,10 @@ def test_skinny_register_plan_over_leaf_counts(chunk):
     assert _native.lib().b200i_decode_status(-1) == 0
 
 
-@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
 def test_leaf_pair_decode_kernel(m):
-    """Weights wide enough (n >= 16 rows per SM) that the decode plan takes its leaf-pair kernel for bf16 / int8 at one and
-    two activation rows: k below one leaf, short last leaves, leaf counts that leave the lane fold an odd tail, a row count
+    """Weights wide enough (n >= 16 rows per SM) that the decode plan takes its leaf-pair kernel for bf16 / int8 at one to
+    four activation rows: k below one leaf, short last leaves, leaf counts that leave the lane fold an odd tail, a row count
     that leaves the last block of a CTA ragged; then operands that fail admission (the flushed per-row fallback) and row
     scales outside the range of the one-fma dequantisation."""
     rng = np.random.default_rng(20 + m)
