@@ -420,6 +420,96 @@ __global__ void epilogue_rows_kernel(float *__restrict__ c, long long cells, int
 // stack): the stack lives in registers, VEC consecutive cells per thread.
 constexpr int MAX_GROUPS = 64;
 constexpr int GROUP_LEVELS = 6; // 2^6 = MAX_GROUPS
+// The finished cells of one thread: canonical NaN, the store, and the store epilogue where one is asked for.
+template <int VEC>
+__device__ __forceinline__ void fold_finish(const float (&v)[VEC], float *__restrict__ c, long long idx, Epilogue epi, int n) {
+    if (VEC == 4 && epilogue_pairs(epi)) {
+        // gated activation: the four cells are two (gate, up) pairs of one row; the output has n / 2 columns
+        const long long row = idx / n, col = idx - row * n;
+        float2 o;
+        o.x = epilogue_pair_apply(nan_canon(ftz_hw(v[0])), nan_canon(ftz_hw(v[1 % VEC])), epi.bias, epi.act, col / 2);
+        o.y = epilogue_pair_apply(nan_canon(ftz_hw(v[2 % VEC])), nan_canon(ftz_hw(v[3 % VEC])), epi.bias, epi.act, col / 2 + 1);
+        *reinterpret_cast<float2 *>(c + row * (n / 2) + col / 2) = o;
+        return;
+    }
+    if (VEC == 4) {
+        *reinterpret_cast<float4 *>(c + idx) = make_float4(nan_canon(ftz_hw(v[0])), nan_canon(ftz_hw(v[1 % VEC])),
+                                                           nan_canon(ftz_hw(v[2 % VEC])), nan_canon(ftz_hw(v[3 % VEC])));
+    } else {
+        c[idx] = nan_canon(ftz_hw(v[0]));
+    }
+    if (epilogue_on(epi))
+        for (int e = 0; e < VEC; e++) epilogue_cell(c + idx + e, epi, (idx + e) % n);
+}
+
+// One step of the binary-counter fold: node number `gi` of `count` arrives in v; on return v is the root when gi was the
+// last node, otherwise it has been merged into the stack.
+template <int VEC, int LEVELS>
+__device__ __forceinline__ void fold_push(float (&stack)[LEVELS][VEC], float (&v)[VEC], int gi, int last) {
+    if (gi == last) { // the last node drains the stack
+#pragma unroll
+        for (int lvl = 0; lvl < LEVELS; lvl++)
+            if ((last >> lvl) & 1) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) v[e] = fold_add(stack[lvl][e], v[e]);
+            }
+    } else {
+        bool placed = false;
+#pragma unroll
+        for (int lvl = 0; lvl < LEVELS; lvl++) {
+            if (placed) continue;
+            if ((gi >> lvl) & 1) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) v[e] = fold_add(stack[lvl][e], v[e]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) stack[lvl][e] = v[e];
+                placed = true;
+            }
+        }
+    }
+}
+
+// The same fold for a product split into MANY groups over FEW cells (a narrow weight cut into 32 or 64 single-leaf
+// groups: the column shard of one rank): a thread walking all nodes of its cells alone is a chain of L2 round trips, so
+// the groups are cut into blocks of eight (aligned subtrees of the fold tree, the last one possibly ragged), warp s of
+// the CTA folds block s of 32 x 4 cells with all eight nodes in flight at once, and warp 0 folds the block roots, which
+// form the same adjacent-pair tree three levels up.
+constexpr int FOLD_SUB = 8;
+__global__ void __launch_bounds__(32 * MAX_GROUPS / FOLD_SUB) fold_groups_split_kernel(const float *__restrict__ ws, float *__restrict__ c, long long cells,
+                                                                                       int groups, Epilogue epi, int n) {
+    __shared__ float4 roots[MAX_GROUPS / FOLD_SUB][32];
+    const int lane = threadIdx.x & 31, sub = threadIdx.x >> 5;
+    const int subs = (groups + FOLD_SUB - 1) / FOLD_SUB;
+    const long long idx = ((long long)blockIdx.x * 32 + lane) * 4;
+    const bool live = idx < cells;
+    const int g0 = sub * FOLD_SUB, count = min(FOLD_SUB, groups - g0);
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        float4 x[FOLD_SUB];
+#pragma unroll
+        for (int j = 0; j < FOLD_SUB; j++)
+            if (j < count) x[j] = __ldcg(reinterpret_cast<const float4 *>(ws + (size_t)(g0 + j) * (size_t)cells + idx));
+        float stack[3][4];
+#pragma unroll
+        for (int j = 0; j < FOLD_SUB; j++) {
+            if (j >= count) break;
+            v[0] = x[j].x; v[1] = x[j].y; v[2] = x[j].z; v[3] = x[j].w;
+            fold_push<4, 3>(stack, v, j, count - 1);
+        }
+        roots[sub][lane] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    __syncthreads();
+    if (sub != 0 || !live) return;
+    float stack[3][4];
+    for (int s2 = 0; s2 < subs; s2++) {
+        const float4 t = roots[s2][lane];
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        fold_push<4, 3>(stack, v, s2, subs - 1);
+    }
+    fold_finish<4>(v, c, idx, epi, n);
+}
+
 template <int VEC>
 __global__ void __launch_bounds__(256) fold_groups_kernel(const float *__restrict__ ws, float *__restrict__ c, long long cells,
                                                           int groups, Epilogue epi, int n) {
@@ -474,28 +564,15 @@ __global__ void __launch_bounds__(256) fold_groups_kernel(const float *__restric
             }
         }
     }
-    if (VEC == 4 && epilogue_pairs(epi)) {
-        // gated activation: the four cells are two (gate, up) pairs of one row; the output has n / 2 columns
-        const long long row = idx / n, col = idx - row * n;
-        float2 o;
-        o.x = epilogue_pair_apply(nan_canon(ftz_hw(v[0])), nan_canon(ftz_hw(v[1 % VEC])), epi.bias, epi.act, col / 2);
-        o.y = epilogue_pair_apply(nan_canon(ftz_hw(v[2 % VEC])), nan_canon(ftz_hw(v[3 % VEC])), epi.bias, epi.act, col / 2 + 1);
-        *reinterpret_cast<float2 *>(c + row * (n / 2) + col / 2) = o;
-        return;
-    }
-    if (VEC == 4) {
-        *reinterpret_cast<float4 *>(c + idx) = make_float4(nan_canon(ftz_hw(v[0])), nan_canon(ftz_hw(v[1 % VEC])),
-                                                           nan_canon(ftz_hw(v[2 % VEC])), nan_canon(ftz_hw(v[3 % VEC])));
-    } else {
-        c[idx] = nan_canon(ftz_hw(v[0]));
-    }
-    if (epilogue_on(epi))
-        for (int e = 0; e < VEC; e++) epilogue_cell(c + idx + e, epi, (idx + e) % n);
+    fold_finish<VEC>(v, c, idx, epi, n);
 }
+
 inline void launch_fold_groups(const float *ws, float *c, long long cells, int groups, cudaStream_t st, Epilogue epi = Epilogue{nullptr, 0},
                                int n = 1) {
     const bool vec = cells % 4 == 0 && ((reinterpret_cast<uintptr_t>(ws) | reinterpret_cast<uintptr_t>(c)) & 15u) == 0;
-    if (vec) fold_groups_kernel<4><<<(unsigned)((cells / 4 + 255) / 256), 256, 0, st>>>(ws, c, cells, groups, epi, n);
+    if (vec && groups > FOLD_SUB)
+        fold_groups_split_kernel<<<(unsigned)((cells / 4 + 31) / 32), 32 * ((groups + FOLD_SUB - 1) / FOLD_SUB), 0, st>>>(ws, c, cells, groups, epi, n);
+    else if (vec) fold_groups_kernel<4><<<(unsigned)((cells / 4 + 255) / 256), 256, 0, st>>>(ws, c, cells, groups, epi, n);
     else fold_groups_kernel<1><<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(ws, c, cells, groups, epi, n);
 }
 
