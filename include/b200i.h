@@ -177,6 +177,21 @@ int64_t b200i_dequantize_int8(int64_t device, void *stream, float *y, const int8
 int64_t b200i_gemm_int8(int64_t device, void *stream, float *c, const int8_t *qa, const int32_t *ea, const int8_t *qb,
                         const int32_t *eb, int64_t m, int64_t n, int64_t k, char *err, int64_t err_cap);
 
+/* The fifteen-bit profile, mojolearn.identical.gemm.int15i64.v1 (gemm/IDENTICAL_LOWBIT_CONTRACT.md section 6; seams
+ * checks/numerics_int15.mojo, answers gemm/host/gemm_int15_oracle.mojo). An operand is two int8 planes (code = hi * 128 +
+ * lo, lo in [0, 127], hi in [-128, 127]) and one int32 exponent per row, e = floor(log2 absmax) - 13. Replace
+ * quantize_rows_int15_kernel, dequantize and identical_gemm_int15 (gemm/checks/gemm_int15.mojo; door
+ * family_lin_quantize_int15 / _dequantize_int15 / _matmul_int15, python/mojolearn/_linalg_impl.py:381-419). The product is
+ * OP_NT: the exact int64 sum of code products, one rounding to float32, one power-of-two scaling per cell. With k a multiple
+ * of 16 and 16-byte aligned planes it runs as tcgen05 int8 MMAs on the planes into three int32 accumulators (HH, HL + LH,
+ * LL) recombined in int64 in the store; otherwise one thread walks each cell. Refuses k > 65536. */
+int64_t b200i_quantize_int15(int64_t device, void *stream, int8_t *hi, int8_t *lo, int32_t *exponents, const float *x, int64_t rows,
+                             int64_t cols, char *err, int64_t err_cap);
+int64_t b200i_dequantize_int15(int64_t device, void *stream, float *y, const int8_t *hi, const int8_t *lo, const int32_t *exponents,
+                               int64_t rows, int64_t cols, char *err, int64_t err_cap);
+int64_t b200i_gemm_int15(int64_t device, void *stream, float *c, const int8_t *ah, const int8_t *al, const int32_t *ea, const int8_t *bh,
+                         const int8_t *bl, const int32_t *eb, int64_t m, int64_t n, int64_t k, char *err, int64_t err_cap);
+
 /* --- host-pointer twins (synchronous) -----------------------------------------------------------
  * The reference's public calls take host buffers and return when the answer
  * is in host memory (gemm/host_entry.mojo:79-197). */
@@ -191,6 +206,12 @@ int64_t b200i_host_dequantize_int8(int64_t device, float *y, const int8_t *codes
                                    int64_t rows, int64_t cols, char *err, int64_t err_cap);
 int64_t b200i_host_gemm_int8(int64_t device, float *c, const int8_t *qa, const int32_t *ea, const int8_t *qb,
                              const int32_t *eb, int64_t m, int64_t n, int64_t k, char *err, int64_t err_cap);
+int64_t b200i_host_quantize_int15(int64_t device, int8_t *hi, int8_t *lo, int32_t *exponents, const float *x, int64_t rows, int64_t cols,
+                                  char *err, int64_t err_cap);
+int64_t b200i_host_dequantize_int15(int64_t device, float *y, const int8_t *hi, const int8_t *lo, const int32_t *exponents, int64_t rows,
+                                    int64_t cols, char *err, int64_t err_cap);
+int64_t b200i_host_gemm_int15(int64_t device, float *c, const int8_t *ah, const int8_t *al, const int32_t *ea, const int8_t *bh,
+                              const int8_t *bl, const int32_t *eb, int64_t m, int64_t n, int64_t k, char *err, int64_t err_cap);
 
 /* --- decoder-block seams, device pointers, asynchronous on the caller's stream -------------------
  * The non-GEMM steps of the reference's decoder block, each spelled as the

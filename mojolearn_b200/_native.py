@@ -57,6 +57,12 @@ SIGNATURES = {
     "b200i_quantize_int8": [I64, VP, VP, VP, VP, I64, I64, VP, I64],
     "b200i_dequantize_int8": [I64, VP, VP, VP, VP, I64, I64, VP, I64],
     "b200i_gemm_int8": [I64, VP, VP, VP, VP, VP, VP, I64, I64, I64, VP, I64],
+    "b200i_quantize_int15": [I64, VP, VP, VP, VP, VP, I64, I64, VP, I64],
+    "b200i_dequantize_int15": [I64, VP, VP, VP, VP, VP, I64, I64, VP, I64],
+    "b200i_gemm_int15": [I64, VP, VP, VP, VP, VP, VP, VP, VP, I64, I64, I64, VP, I64],
+    "b200i_host_quantize_int15": [I64, VP, VP, VP, VP, I64, I64, VP, I64],
+    "b200i_host_dequantize_int15": [I64, VP, VP, VP, VP, I64, I64, VP, I64],
+    "b200i_host_gemm_int15": [I64, VP, VP, VP, VP, VP, VP, VP, I64, I64, I64, VP, I64],
     "b200i_host_gemm_w": [I64, VP, VP, VP, VP, I64, I64, I64, I64, I64, VP, I64],
     "b200i_host_to_bf16": [I64, VP, VP, I64, VP, I64],
     "b200i_host_from_bf16": [I64, VP, VP, I64, VP, I64],

@@ -12,6 +12,7 @@
 #include "decode.cuh"
 #include "decode_pair.cuh"
 #include "gemm_int8_mma.cuh"
+#include "gemm_int15.cuh"
 #include "decoder.cuh"
 #include "gemm_tile.cuh"
 #include "gemm_skinny.cuh"
@@ -699,6 +700,52 @@ int64_t b200i_gemm_int8(int64_t device, void *stream, float *c, const int8_t *qa
         launch_gemm_int8_mma(c, reinterpret_cast<const signed char *>(qa), ea, reinterpret_cast<const signed char *>(qb), eb, (int)m, (int)n, (int)k, sm_count(dev), static_cast<cudaStream_t>(stream));
     else
         gemm_int8_flat_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(c, reinterpret_cast<const signed char *>(qa), ea, reinterpret_cast<const signed char *>(qb), eb, (int)m, (int)n, (int)k);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_quantize_int15(int64_t device, void *stream, int8_t *hi, int8_t *lo, int32_t *exponents, const float *x, int64_t rows,
+                             int64_t cols, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    if (rows <= 0 || cols <= 0) return fail(err, err_cap, "quantize_int15: rows and cols must be positive");
+    if (!hi || !lo || !exponents || !x) return fail(err, err_cap, "quantize_int15: null storage");
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    quantize_int15_kernel<<<grid_for(rows * 32, 256, sm_count(dev)), 256, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<signed char *>(hi), reinterpret_cast<signed char *>(lo), exponents, x, rows, cols);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_dequantize_int15(int64_t device, void *stream, float *y, const int8_t *hi, const int8_t *lo, const int32_t *exponents,
+                               int64_t rows, int64_t cols, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    if (rows <= 0 || cols <= 0) return fail(err, err_cap, "dequantize_int15: rows and cols must be positive");
+    if (!hi || !lo || !exponents || !y) return fail(err, err_cap, "dequantize_int15: null storage");
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    dequantize_int15_kernel<<<grid_for(rows * cols, 256, sm_count(dev)), 256, 0, static_cast<cudaStream_t>(stream)>>>(y, reinterpret_cast<const signed char *>(hi), reinterpret_cast<const signed char *>(lo), exponents, rows, cols);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_gemm_int15(int64_t device, void *stream, float *c, const int8_t *ah, const int8_t *al, const int32_t *ea, const int8_t *bh,
+                         const int8_t *bl, const int32_t *eb, int64_t m, int64_t n, int64_t k, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    if (m <= 0 || n <= 0 || k <= 0) return fail(err, err_cap, "identical int15 gemm: m, n and k must be positive");
+    if (k > INT15_MAX_K) return fail(err, err_cap, "identical int15 gemm: k = %lld exceeds INT15_MAX_K = 65536", (long long)k);
+    if (!c || !ah || !al || !ea || !bh || !bl || !eb) return fail(err, err_cap, "identical int15 gemm: null storage");
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    const signed char *sah = reinterpret_cast<const signed char *>(ah), *sal = reinterpret_cast<const signed char *>(al);
+    const signed char *sbh = reinterpret_cast<const signed char *>(bh), *sbl = reinterpret_cast<const signed char *>(bl);
+    // the tensor-core plan wherever its 16-byte copies are aligned (k a multiple of 16); one thread per cell otherwise
+    if (gemm_int15_mma_fits(ah, al, bh, bl, m, n, k))
+        launch_gemm_int15_mma(c, sah, sal, ea, sbh, sbl, eb, (int)m, (int)n, (int)k, static_cast<cudaStream_t>(stream));
+    else
+        gemm_int15_flat_kernel<<<(unsigned)((m * n + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(c, sah, sal, ea, sbh, sbl, eb, (int)m, (int)n, (int)k);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -1584,6 +1631,74 @@ int64_t b200i_host_gemm_int8(int64_t device, float *c, const int8_t *qa, const i
     CUDA_TRY(cudaMemcpyAsync(deb, eb, (size_t)n * 4, cudaMemcpyHostToDevice, pool.stream));
     if (b200i_gemm_int8(dev, pool.stream, static_cast<float *>(dc), static_cast<const int8_t *>(dqa), static_cast<const int32_t *>(dea),
                         static_cast<const int8_t *>(dqb), static_cast<const int32_t *>(deb), m, n, k, err, err_cap))
+        return 1;
+    CUDA_TRY(cudaMemcpyAsync(c, dc, (size_t)m * n * 4, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaStreamSynchronize(pool.stream));
+    return check_wait_status(err, err_cap, "b200i host call");
+}
+
+int64_t b200i_host_quantize_int15(int64_t device, int8_t *hi, int8_t *lo, int32_t *exponents, const float *x, int64_t rows, int64_t cols,
+                                  char *err, int64_t err_cap) {
+    if (rows <= 0 || cols <= 0) return fail(err, err_cap, "quantize_int15: rows and cols must be positive");
+    HOST_PREP();
+    void *dx, *dh, *dl, *de;
+    CUDA_TRY(pool_get(dev, 0, (size_t)rows * cols * 4, &dx));
+    CUDA_TRY(pool_get(dev, 1, (size_t)rows * cols, &dh));
+    CUDA_TRY(pool_get(dev, 2, (size_t)rows * cols, &dl));
+    CUDA_TRY(pool_get(dev, 3, (size_t)rows * 4, &de));
+    CUDA_TRY(cudaMemcpyAsync(dx, x, (size_t)rows * cols * 4, cudaMemcpyHostToDevice, pool.stream));
+    if (b200i_quantize_int15(dev, pool.stream, static_cast<int8_t *>(dh), static_cast<int8_t *>(dl), static_cast<int32_t *>(de),
+                             static_cast<const float *>(dx), rows, cols, err, err_cap))
+        return 1;
+    CUDA_TRY(cudaMemcpyAsync(hi, dh, (size_t)rows * cols, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(lo, dl, (size_t)rows * cols, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(exponents, de, (size_t)rows * 4, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaStreamSynchronize(pool.stream));
+    return check_wait_status(err, err_cap, "b200i host call");
+}
+
+int64_t b200i_host_dequantize_int15(int64_t device, float *y, const int8_t *hi, const int8_t *lo, const int32_t *exponents, int64_t rows,
+                                    int64_t cols, char *err, int64_t err_cap) {
+    if (rows <= 0 || cols <= 0) return fail(err, err_cap, "dequantize_int15: rows and cols must be positive");
+    HOST_PREP();
+    void *dy, *dh, *dl, *de;
+    CUDA_TRY(pool_get(dev, 0, (size_t)rows * cols * 4, &dy));
+    CUDA_TRY(pool_get(dev, 1, (size_t)rows * cols, &dh));
+    CUDA_TRY(pool_get(dev, 2, (size_t)rows * cols, &dl));
+    CUDA_TRY(pool_get(dev, 3, (size_t)rows * 4, &de));
+    CUDA_TRY(cudaMemcpyAsync(dh, hi, (size_t)rows * cols, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(dl, lo, (size_t)rows * cols, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(de, exponents, (size_t)rows * 4, cudaMemcpyHostToDevice, pool.stream));
+    if (b200i_dequantize_int15(dev, pool.stream, static_cast<float *>(dy), static_cast<const int8_t *>(dh), static_cast<const int8_t *>(dl),
+                               static_cast<const int32_t *>(de), rows, cols, err, err_cap))
+        return 1;
+    CUDA_TRY(cudaMemcpyAsync(y, dy, (size_t)rows * cols * 4, cudaMemcpyDeviceToHost, pool.stream));
+    CUDA_TRY(cudaStreamSynchronize(pool.stream));
+    return check_wait_status(err, err_cap, "b200i host call");
+}
+
+int64_t b200i_host_gemm_int15(int64_t device, float *c, const int8_t *ah, const int8_t *al, const int32_t *ea, const int8_t *bh,
+                              const int8_t *bl, const int32_t *eb, int64_t m, int64_t n, int64_t k, char *err, int64_t err_cap) {
+    if (m <= 0 || n <= 0 || k <= 0) return fail(err, err_cap, "identical int15 gemm: m, n and k must be positive");
+    if (k > INT15_MAX_K) return fail(err, err_cap, "identical int15 gemm: k = %lld exceeds INT15_MAX_K = 65536", (long long)k);
+    HOST_PREP();
+    // the two planes of an operand share one pool slot, the second one 256-byte aligned behind the first
+    const size_t aplane = ((size_t)m * k + 255) / 256 * 256, bplane = ((size_t)n * k + 255) / 256 * 256;
+    void *da, *db, *dc, *dea, *deb;
+    CUDA_TRY(pool_get(dev, 0, 2 * aplane, &da));
+    CUDA_TRY(pool_get(dev, 1, 2 * bplane, &db));
+    CUDA_TRY(pool_get(dev, 2, (size_t)m * n * 4, &dc));
+    CUDA_TRY(pool_get(dev, 3, (size_t)m * 4, &dea));
+    CUDA_TRY(pool_get(dev, 4, (size_t)n * 4, &deb));
+    int8_t *dah = static_cast<int8_t *>(da), *dal = dah + aplane, *dbh = static_cast<int8_t *>(db), *dbl = dbh + bplane;
+    CUDA_TRY(cudaMemcpyAsync(dah, ah, (size_t)m * k, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(dal, al, (size_t)m * k, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(dbh, bh, (size_t)n * k, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(dbl, bl, (size_t)n * k, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(dea, ea, (size_t)m * 4, cudaMemcpyHostToDevice, pool.stream));
+    CUDA_TRY(cudaMemcpyAsync(deb, eb, (size_t)n * 4, cudaMemcpyHostToDevice, pool.stream));
+    if (b200i_gemm_int15(dev, pool.stream, static_cast<float *>(dc), dah, dal, static_cast<const int32_t *>(dea), dbh, dbl,
+                         static_cast<const int32_t *>(deb), m, n, k, err, err_cap))
         return 1;
     CUDA_TRY(cudaMemcpyAsync(c, dc, (size_t)m * n * 4, cudaMemcpyDeviceToHost, pool.stream));
     CUDA_TRY(cudaStreamSynchronize(pool.stream));

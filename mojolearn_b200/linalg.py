@@ -21,6 +21,7 @@ LOWBIT_PROFILE_VERSION = 1
 PROFILE_BF16 = "mojolearn.identical.gemm.bf16f32.v%d" % LOWBIT_PROFILE_VERSION
 PROFILE_INT8 = "mojolearn.identical.gemm.int8i32.v%d" % LOWBIT_PROFILE_VERSION
 INT8_MAX_K = 131072
+INT15_MAX_K = 65536
 
 OP_NN, OP_NT, OP_TN = 0, 1, 2
 W_F32, W_BF16, W_INT8_EXP, W_INT8_SCALE = 0, 1, 2, 3
@@ -217,6 +218,66 @@ def matmul_int8(a, b, *, out=None):
     c = _out(out, m, n)
     _native.require_device()
     _native.call("b200i_host_gemm_int8", DEVICE, _ptr(c), _ptr(qa), _ptr(ea), _ptr(qb), _ptr(eb), m, n, k)
+    return c if out is None else out
+
+
+def quantize_int15(x):
+    """(hi, lo int8 [rows, cols], exponents int32 [rows]): fifteen-bit codes as two planes, code = hi * 128 + lo with lo in
+    [0, 127]; per row e = floor(log2 absmax) - 13 (reference _linalg_impl.py:381-396)."""
+    a = _operand(x, "x")
+    _native.require_device()
+    rows, cols = a.shape
+    hi = np.empty((rows, cols), dtype=np.int8)
+    lo = np.empty((rows, cols), dtype=np.int8)
+    exps = np.empty((rows,), dtype=np.int32)
+    _native.call("b200i_host_quantize_int15", DEVICE, _ptr(hi), _ptr(lo), _ptr(exps), _ptr(a), rows, cols)
+    return hi, lo, exps
+
+
+def dequantize_int15(hi, lo, exponents):
+    """float32 values (hi * 128 + lo) * 2**exponents[row] (reference _linalg_impl.py:399-401)."""
+    h = _operand(hi, "hi", dtype=np.int8)
+    l = _operand(lo, "lo", dtype=np.int8)
+    e = _operand(exponents, "exponents", dtype=np.int32, ndim=1)
+    rows, cols = h.shape
+    if l.shape != h.shape:
+        raise ValueError("hi and lo planes must have one shape, got %s and %s" % (h.shape, l.shape))
+    if e.shape != (rows,):
+        raise ValueError("exponents must have one entry per row (%d), got %s" % (rows, e.shape))
+    _native.require_device()
+    y = np.empty((rows, cols), dtype=np.float32)
+    _native.call("b200i_host_dequantize_int15", DEVICE, _ptr(y), _ptr(h), _ptr(l), _ptr(e), rows, cols)
+    return y
+
+
+def _int15_operand(x, name):
+    if isinstance(x, (tuple, list)) and len(x) == 3:
+        h = _operand(x[0], name + " hi", dtype=np.int8)
+        l = _operand(x[1], name + " lo", dtype=np.int8)
+        e = _operand(x[2], name + " exponents", dtype=np.int32, ndim=1)
+        if l.shape != h.shape or e.shape != (h.shape[0],):
+            raise ValueError("%s: two planes of one shape and one exponent per row" % name)
+        return h, l, e
+    return quantize_int15(_operand(x, name))
+
+
+def matmul_int15(a, b, *, out=None):
+    """`a @ b.T` under mojolearn.identical.gemm.int15i64.v1: each operand a float32 matrix (quantised by the profile's rule)
+    or a (hi, lo, exponents) triple; the exact integer sum of the code products, rounded once to float32 and scaled by a
+    power of two. k <= 65536 (reference _linalg_impl.py:404-419)."""
+    require_identical()
+    if not isinstance(a, (tuple, list)) and np.asarray(a).ndim == 2 and np.asarray(a).shape[1] > INT15_MAX_K:
+        raise ValueError("identical int15 gemm: k = %d exceeds INT15_MAX_K = %d" % (np.asarray(a).shape[1], INT15_MAX_K))
+    ah, al, ea = _int15_operand(a, "a")
+    bh, bl, eb = _int15_operand(b, "b")
+    (m, k), (n, k2) = ah.shape, bh.shape
+    if k != k2:
+        raise ValueError("contracted extents disagree: %d and %d" % (k, k2))
+    if k > INT15_MAX_K:
+        raise ValueError("identical int15 gemm: k = %d exceeds INT15_MAX_K = %d" % (k, INT15_MAX_K))
+    c = _out(out, m, n)
+    _native.require_device()
+    _native.call("b200i_host_gemm_int15", DEVICE, _ptr(c), _ptr(ah), _ptr(al), _ptr(ea), _ptr(bh), _ptr(bl), _ptr(eb), m, n, k)
     return c if out is None else out
 
 

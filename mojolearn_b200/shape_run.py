@@ -25,8 +25,8 @@ def main():
     ap.add_argument("n", type=int)
     ap.add_argument("k", type=int)
     ap.add_argument("--op", default="NT", choices=sorted(OPS))
-    ap.add_argument("--wkind", default="f32", choices=["f32", "bf16", "int8", "int8s", "int8i32"],
-                    help="int8i32: the int8 x int8 -> int32 product profile (both operands int8 codes with row exponents, op NT)")
+    ap.add_argument("--wkind", default="f32", choices=["f32", "bf16", "int8", "int8s", "int8i32", "int15i64"],
+                    help="int8i32 / int15i64: the integer product profiles (both operands codes with row exponents, op NT)")
     ap.add_argument("--plan", type=int, default=-1)
     ap.add_argument("--groups", type=int, default=0)
     ap.add_argument("--reps", type=int, default=5)
@@ -37,7 +37,7 @@ def main():
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(0)
     m, n, k, op = args.m, args.n, args.k, OPS[args.op]
-    if args.wkind == "int8i32":
+    if args.wkind in ("int8i32", "int15i64"):
         return int8_product(args, dev, g)
     a = torch.randn((k, m) if op == linalg.OP_TN else (m, k), generator=g, device=dev)
     wshape = (n, k) if op == linalg.OP_NT else (k, n)
@@ -97,17 +97,26 @@ def int8_product(args, dev, g):
     ea = torch.randint(-10, -5, (m,), generator=g, device=dev, dtype=torch.int32)
     qbs = [torch.randint(-127, 128, (n, k), generator=g, device=dev, dtype=torch.int8) for _ in range(args.buffers)]
     eb = torch.randint(-10, -5, (n,), generator=g, device=dev, dtype=torch.int32)
+    if args.wkind == "int15i64":  # the low planes hold [0, 127]
+        al = torch.randint(0, 128, (m, k), generator=g, device=dev, dtype=torch.int8)
+        bl = torch.randint(0, 128, (n, k), generator=g, device=dev, dtype=torch.int8)
+
+        def run(i):
+            torch_ops.matmul_int15(qa, al, ea, qbs[i % len(qbs)], bl, eb)
+    else:
+        def run(i):
+            torch_ops.matmul_int8(qa, ea, qbs[i % len(qbs)], eb)
     for i in range(args.warmup):
-        torch_ops.matmul_int8(qa, ea, qbs[i % len(qbs)], eb)
+        run(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.reps):
-        torch_ops.matmul_int8(qa, ea, qbs[i % len(qbs)], eb)
+        run(i)
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.reps
-    print(json.dumps({"m": m, "n": n, "k": k, "op": "NT", "wkind": "int8i32", "ms": ms, "tops": 2.0 * m * n * k / (ms * 1e-3) / 1e12,
+    print(json.dumps({"m": m, "n": n, "k": k, "op": "NT", "wkind": args.wkind, "ms": ms, "tops": 2.0 * m * n * k / (ms * 1e-3) / 1e12,
                       "algorithmic_gbs": (m * k + n * k + 4 * m * n) / (ms * 1e-3) / 1e9}))
 
 

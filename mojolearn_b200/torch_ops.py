@@ -196,6 +196,21 @@ def matmul_int8(qa, ea, qb, eb):
     return c
 
 
+def matmul_int15(ah, al, ea, bh, bl, eb):
+    """int15i64.v1 at OP_NT on device tensors: two int8 planes and one int32 exponent per row for each operand."""
+    for t, name in ((ah, "ah"), (al, "al"), (bh, "bh"), (bl, "bl")):
+        _check(t, name, torch.int8)
+    _check(ea, "ea", torch.int32)
+    _check(eb, "eb", torch.int32)
+    (m, k), (n, k2) = ah.shape, bh.shape
+    if k != k2 or al.shape != ah.shape or bl.shape != bh.shape:
+        raise ValueError("planes of one operand must have one shape and the contracted extents must agree")
+    c = torch.empty((m, n), dtype=torch.float32, device=ah.device)
+    with torch.cuda.device(ah.device):
+        _native.call("b200i_gemm_int15", ah.device.index, _stream(ah.device), _vp(c), _vp(ah), _vp(al), _vp(ea), _vp(bh), _vp(bl), _vp(eb), m, n, k)
+    return c
+
+
 # ---- torch.library registration ---------------------------------------------------------------
 
 @torch.library.custom_op("mojolearn_b200::matmul", mutates_args=())

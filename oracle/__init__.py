@@ -64,6 +64,9 @@ def lib():
         _LIB.oracle_dequantize_int8.argtypes = [f32p, f32p, f32p, i64, i64]
         _LIB.oracle_dequantize_int8_scaled.argtypes = [f32p, f32p, f32p, i64, i64]
         _LIB.oracle_gemm_int8.argtypes = [f32p, f32p, f32p, f32p, f32p, i64, i64, i64]
+        _LIB.oracle_quantize_int15.argtypes = [f32p, f32p, f32p, f32p, i64, i64]
+        _LIB.oracle_dequantize_int15.argtypes = [f32p, f32p, f32p, f32p, i64, i64]
+        _LIB.oracle_gemm_int15.argtypes = [f32p] * 7 + [i64, i64, i64]
         _LIB.oracle_fnv1a64.restype = ctypes.c_uint64
         _LIB.oracle_fnv1a64.argtypes = [f32p, i64]
         _LIB.oracle_card_fill.argtypes = [f32p, i64, i64]
@@ -210,6 +213,44 @@ def gemm_int8(qa, ea, qb, eb):
     rc = lib().oracle_gemm_int8(_ptr(c), _ptr(qa), _ptr(ea), _ptr(qb), _ptr(eb), m, n, k)
     if rc != 0:
         raise ValueError("oracle refused the int8 product")
+    return c
+
+
+INT15_MAX_K = 65536
+
+
+def quantize_int15(x):
+    """(hi, lo, exponents): the two int8 planes of the fifteen-bit codes (code = hi * 128 + lo) and one exponent per row."""
+    x = _f32(x)
+    rows, cols = x.shape
+    hi = np.empty((rows, cols), dtype=np.int8)
+    lo = np.empty((rows, cols), dtype=np.int8)
+    e = np.empty((rows,), dtype=np.int32)
+    lib().oracle_quantize_int15(_ptr(hi), _ptr(lo), _ptr(e), _ptr(x), rows, cols)
+    return hi, lo, e
+
+
+def dequantize_int15(hi, lo, e):
+    hi = np.ascontiguousarray(hi, dtype=np.int8)
+    lo = np.ascontiguousarray(lo, dtype=np.int8)
+    e = np.ascontiguousarray(e, dtype=np.int32)
+    rows, cols = hi.shape
+    y = np.empty((rows, cols), dtype=np.float32)
+    lib().oracle_dequantize_int15(_ptr(y), _ptr(hi), _ptr(lo), _ptr(e), rows, cols)
+    return y
+
+
+def gemm_int15(ah, al, ea, bh, bl, eb):
+    ah, al, bh, bl = (np.ascontiguousarray(v, dtype=np.int8) for v in (ah, al, bh, bl))
+    ea = np.ascontiguousarray(ea, dtype=np.int32)
+    eb = np.ascontiguousarray(eb, dtype=np.int32)
+    (m, k), (n, k2) = ah.shape, bh.shape
+    if k != k2:
+        raise ValueError("contraction extents disagree")
+    c = np.empty((m, n), dtype=np.float32)
+    rc = lib().oracle_gemm_int15(_ptr(c), _ptr(ah), _ptr(al), _ptr(ea), _ptr(bh), _ptr(bl), _ptr(eb), m, n, k)
+    if rc != 0:
+        raise ValueError("oracle refused the int15 product: k must be at most %d" % INT15_MAX_K)
     return c
 
 

@@ -401,6 +401,108 @@ ORACLE_API int oracle_gemm_int8(float *c, const int8_t *qa, const int32_t *ea, c
     return 0;
 }
 
+/* ---- the fifteen-bit profile, mojolearn.identical.gemm.int15i64.v1 (gemm/IDENTICAL_LOWBIT_CONTRACT.md section 6) ---- */
+
+/* checks/numerics_int15.mojo:57-68 (clause W-1): e = floor(log2 absmax) - 13; an all-zero row takes 0. */
+static inline int int15_row_exponent(float absmax) {
+    float a = ftz(absmax);
+    if (a == 0.0f || a != a) return 0;
+    return f32_exponent(a) - 13;
+}
+
+/* checks/numerics_int15.mojo:71-104 (W-2): clamp(rne(ftz(ftz(x) * 2^-e)), -16383, 16383); a NaN, before or after the
+ * scaling (0 * inf), codes to 0. */
+static inline int16_t quantize_int15_value(float x, int e) {
+    if (x != x) return 0;
+    volatile float prod = ftz(x) * pow2_f32(-(int64_t)e);
+    float s = ftz(prod);
+    if (s != s) return 0;
+    float r = round_half_even(s);
+    if (r > 16383.0f) r = 16383.0f;
+    if (r < -16383.0f) r = -16383.0f;
+    return (int16_t)(int)r;
+}
+
+/* checks/numerics_int15.mojo:139-182 (W-6): the Int64 sum as a float32, round to nearest even: a 24-bit high part and a
+ * 24-bit low part, one exact scaling and ONE rounding addition; at and above 2^48 the low sixteen bits become a sticky bit. */
+static inline float i64_to_f32_pinned(int64_t v) {
+    int neg = v < 0;
+    uint64_t mag = (uint64_t)v;
+    if (neg) mag = (uint64_t)0 - mag;
+    int reduced = 0;
+    if (mag >= ((uint64_t)1 << 48)) {
+        uint64_t lost = mag & 0xFFFFu;
+        mag >>= 16;
+        if (lost != 0) mag |= 1u;
+        reduced = 1;
+    }
+    float hi = (float)(int32_t)(mag >> 24);
+    float lo = (float)(int32_t)(mag & 0xFFFFFFu);
+    volatile float scaled = hi * 16777216.0f;
+    volatile float r = scaled + lo;
+    if (reduced) r = r * 65536.0f;
+    return neg ? -r : r;
+}
+
+/* checks/numerics_int15.mojo:185-192 (W-7) */
+static inline float dequant_int15_pinned(int64_t acc, int64_t e_sum) {
+    volatile float prod = i64_to_f32_pinned(acc) * pow2_f32(e_sum);
+    return ftz(prod);
+}
+
+/* gemm/host/gemm_int15_oracle.mojo:71-86 and :109-116: the row's absmax (int8i32.v1's), the codes, and their two int8
+ * planes: lo = code mod 128 as a floor modulus in [0, 127], hi = floor(code / 128) in [-128, 127] (W-3). */
+ORACLE_API void oracle_quantize_int15(int8_t *hi, int8_t *lo, int32_t *e, const float *x, int64_t rows, int64_t cols) {
+    unsigned env = fpenv_enter();
+    for (int64_t r = 0; r < rows; r++) {
+        float best = 0.0f;
+        for (int64_t c = 0; c < cols; c++) {
+            float v = ftz(x[r * cols + c]);
+            if (v < 0.0f) v = -v;
+            if (v > best) best = v;
+        }
+        int ex = int15_row_exponent(best);
+        e[r] = ex;
+        for (int64_t c = 0; c < cols; c++) {
+            int32_t code = quantize_int15_value(x[r * cols + c], ex);
+            lo[r * cols + c] = (int8_t)(code & 127);
+            hi[r * cols + c] = (int8_t)(code >> 7); /* arithmetic shift of a negative int32: gcc and clang, as the reference's */
+        }
+    }
+    fpenv_leave(env);
+}
+
+/* gemm/host/gemm_int15_oracle.mojo:98-108: ftz(code * 2^e) through the pinned seam. */
+ORACLE_API void oracle_dequantize_int15(float *y, const int8_t *hi, const int8_t *lo, const int32_t *e, int64_t rows, int64_t cols) {
+    unsigned env = fpenv_enter();
+    for (int64_t r = 0; r < rows; r++)
+        for (int64_t c = 0; c < cols; c++) {
+            int64_t code = (int64_t)hi[r * cols + c] * 128 + (int64_t)lo[r * cols + c];
+            y[r * cols + c] = dequant_int15_pinned(code, e[r]);
+        }
+    fpenv_leave(env);
+}
+
+/* gemm/host/gemm_int15_oracle.mojo:124-134, :185-210: OP_NT, the exact Int64 sum of code products, one dequantisation per
+ * cell; k above INT15_MAX_K = 65536 is refused. */
+ORACLE_API int oracle_gemm_int15(float *c, const int8_t *ah, const int8_t *al, const int32_t *ea, const int8_t *bh, const int8_t *bl,
+                                 const int32_t *eb, int64_t m, int64_t n, int64_t k) {
+    if (m < 0 || n < 0 || k < 0 || k > 65536) return 1;
+    unsigned env = fpenv_enter();
+    for (int64_t i = 0; i < m; i++)
+        for (int64_t j = 0; j < n; j++) {
+            int64_t acc = 0;
+            for (int64_t p = 0; p < k; p++) {
+                int32_t a = (int32_t)ah[i * k + p] * 128 + (int32_t)al[i * k + p];
+                int32_t b = (int32_t)bh[j * k + p] * 128 + (int32_t)bl[j * k + p];
+                acc += (int64_t)(a * b);
+            }
+            c[i * n + j] = dequant_int15_pinned(acc, (int64_t)ea[i] + (int64_t)eb[j]);
+        }
+    fpenv_leave(env);
+    return 0;
+}
+
 /* ---- identity-card helpers -------------------------------------------------- */
 
 /* core/identity_trace.mojo:22-31, :89-114: FNV-1a 64 over little-endian bytes. */

@@ -11,7 +11,8 @@ API predicates and agreements that hold by construction here).
 `impl` provides: matmul(a, b, transpose_a=False, transpose_b=False),
 matmul_bf16(a, b_bits, transpose_b=False) with a float32 or uint16 bits,
 matmul_int8((qa, ea), (qb, eb)), to_bf16, from_bf16, quantize_int8,
-dequantize_int8.
+dequantize_int8, and for gemm-int15 (:3852-3879) quantize_int15, dequantize_int15,
+matmul_int15 and INT15_MAX_K.
 """
 import hashlib
 
@@ -70,6 +71,31 @@ def gemm_int8(impl, X):
     c = impl.matmul_int8((qa, ea), (qb, eb))
     return dict(codes=sha16(np.asarray(qa), np.asarray(qb)), exps=sha16(np.asarray(ea), np.asarray(eb)),
                 product=sha16(c), dequant=sha16(impl.dequantize_int8(qb, eb)))
+
+
+def _refuses(fn, text):
+    try:
+        fn()
+    except Exception as exc:  # noqa: BLE001
+        return text in str(exc)
+    return False
+
+
+def gemm_int15(impl, X):
+    """tools/identity_break.py:3852-3879 of the reference: the planes and exponents of the fifteen-bit quantizer, the
+    product from the planes and from the float32 operands (which must be the same bytes), the refusal above INT15_MAX_K."""
+    a = np.ascontiguousarray(X[:256]).astype(np.float32)
+    b = np.ascontiguousarray(X[256:256 + 128]).astype(np.float32)
+    ah, al, ea = impl.quantize_int15(a)
+    bh, bl, eb = impl.quantize_int15(b)
+    c = impl.matmul_int15((ah, al, ea), (bh, bl, eb))
+    c1 = impl.matmul_int15(a, b)
+    same = np.array([int(np.asarray(c).tobytes() == np.asarray(c1).tobytes())], dtype=np.int32)
+    wide = np.zeros((1, impl.INT15_MAX_K + 1), dtype=np.float32)
+    refuses = np.array([int(_refuses(lambda: impl.matmul_int15(wide, wide), "65536"))], dtype=np.int32)
+    return dict(planes=sha16(np.asarray(ah), np.asarray(al), np.asarray(bh), np.asarray(bl)),
+                exps=sha16(np.asarray(ea), np.asarray(eb)), product=sha16(c), onecall=sha16(c1), flags=sha16(same, refuses),
+                dequant=sha16(impl.dequantize_int15(bh, bl, eb)))
 
 
 LOWBIT_ROWS, LOWBIT_COLS = 64, 16
@@ -159,7 +185,7 @@ def lowbit_conversions_batch(impl, Xh, cols):
 BATCH_LANES = {"gemm-pinned": gemm_pinned_batch, "gemm-transposed": gemm_transposed_batch}
 
 LANES = {"gemm-pinned": gemm_pinned, "gemm-transposed": gemm_transposed, "gemm-bf16": gemm_bf16,
-         "gemm-int8": gemm_int8, "lowbit-conversions": lowbit_conversions}
+         "gemm-int8": gemm_int8, "gemm-int15": gemm_int15, "lowbit-conversions": lowbit_conversions}
 
 
 class OracleImpl:
@@ -181,6 +207,19 @@ class OracleImpl:
 
     def matmul_int8(self, a, b):
         return self.o.nan_canon(self.o.gemm_int8(a[0], a[1], b[0], b[1]))
+
+    INT15_MAX_K = 65536
+
+    def matmul_int15(self, a, b):
+        a = a if isinstance(a, tuple) else self.o.quantize_int15(a)
+        b = b if isinstance(b, tuple) else self.o.quantize_int15(b)
+        return self.o.nan_canon(self.o.gemm_int15(a[0], a[1], a[2], b[0], b[1], b[2]))
+
+    def quantize_int15(self, x):
+        return self.o.quantize_int15(x)
+
+    def dequantize_int15(self, hi, lo, e):
+        return self.o.dequantize_int15(hi, lo, e)
 
     def to_bf16(self, x):
         return self.o.to_bf16(x)

@@ -21,7 +21,7 @@ import json
 import os
 import sys
 
-LANES = ["gemm-pinned", "gemm-transposed", "gemm-bf16", "gemm-int8", "lowbit-conversions",
+LANES = ["gemm-pinned", "gemm-transposed", "gemm-bf16", "gemm-int8", "gemm-int15", "lowbit-conversions",
          "transformer", "transformer-bf16w", "transformer-int8w", "transformer-window", "transformer-decode-session", "embedding", "hf-causal-lm"]
 
 

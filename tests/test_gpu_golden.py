@@ -39,6 +39,10 @@ class GpuImpl:
     from_bf16 = staticmethod(linalg.from_bf16)
     quantize_int8 = staticmethod(linalg.quantize_int8)
     dequantize_int8 = staticmethod(linalg.dequantize_int8)
+    INT15_MAX_K = linalg.INT15_MAX_K
+    matmul_int15 = staticmethod(linalg.matmul_int15)
+    quantize_int15 = staticmethod(linalg.quantize_int15)
+    dequantize_int15 = staticmethod(linalg.dequantize_int15)
 
 
 @pytest.mark.parametrize("kind", fixtures.KINDS)

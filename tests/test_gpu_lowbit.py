@@ -225,6 +225,43 @@ def test_int8_product_on_tensor_cores():
     assert _native.lib().b200i_decode_status(-1) == 0
 
 
+def test_int15_profile_against_the_oracle():
+    """The fifteen-bit profile: quantiser (planes and exponents, NaN / Inf / zero / tiny rows), dequantiser, and the product on
+    the tensor cores (k a multiple of 16: ragged tiles, k below / at / across a stage, the largest codes at the largest k)
+    and one thread per cell (any other k), against the CPU oracle, which reproduces the reference's `gemm-int15` cells."""
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal((67, 131)) * np.exp2(rng.integers(-140, 120, (67, 1)))).astype(np.float32)
+    x[0, :6] = [np.nan, np.inf, -np.inf, 1e-41, -1e-41, 0.0]
+    x[1] = 0.0
+    x[2, :] = np.float32(1e-40)
+    x[3, 5] = np.nan
+    hi, lo, e = linalg.quantize_int15(x)
+    ohi, olo, oe = oracle.quantize_int15(x)
+    assert hi.tobytes() == ohi.tobytes() and lo.tobytes() == olo.tobytes() and e.tobytes() == oe.tobytes()
+    assert linalg.dequantize_int15(hi, lo, e).tobytes() == oracle.dequantize_int15(ohi, olo, oe).tobytes()
+    for (m, n, k) in [(1, 7, 16), (37, 41, 1008), (128, 64, 128), (130, 257, 400), (300, 515, 2048), (5, 129, 144), (1300, 2100, 640),
+                      (37, 41, 1000), (3, 5, 7)]:
+        a = (rng.standard_normal((m, k)) * np.exp2(rng.integers(-20, 20, (m, 1)))).astype(np.float32)
+        b = (rng.standard_normal((n, k)) * np.exp2(rng.integers(-20, 20, (n, 1)))).astype(np.float32)
+        qa, qb = oracle.quantize_int15(a), oracle.quantize_int15(b)
+        want = oracle.nan_canon(oracle.gemm_int15(*qa, *qb))
+        assert linalg.matmul_int15(qa, qb).tobytes() == want.tobytes(), (m, n, k)
+        assert linalg.matmul_int15(a, b).tobytes() == want.tobytes(), (m, n, k)
+    m, n, k = 3, 5, 65536  # |sum| up to 16383^2 * 65536 < 2^44: every piece sum at its bound
+    ah = np.full((m, k), 127, np.int8); al = np.full((m, k), 127, np.int8)
+    bh = np.full((n, k), 127, np.int8); bl = np.full((n, k), 127, np.int8)
+    ah[1] = -128; al[1] = 1
+    bh[2, ::2] = -128; bl[2, ::2] = 1
+    al[2, : k // 2] = 0
+    ea = np.array([0, -140, 100], np.int32)
+    eb = np.array([0, 120, -130, 5, -5], np.int32)
+    want = oracle.nan_canon(oracle.gemm_int15(ah, al, ea, bh, bl, eb))
+    assert linalg.matmul_int15((ah, al, ea), (bh, bl, eb)).tobytes() == want.tobytes()
+    with pytest.raises(ValueError, match="65536"):
+        linalg.matmul_int15(np.zeros((1, 65537), np.float32), np.zeros((1, 65537), np.float32))
+    assert _native.lib().b200i_decode_status(-1) == 0
+
+
 @pytest.mark.parametrize("chunk", range(4))
 def test_skinny_register_plan_over_leaf_counts(chunk):
     """The register skinny plan (low-bit weights) over every leaf count from 1 to 40 and a few up to 1024, leaf groups
