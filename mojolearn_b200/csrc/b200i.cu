@@ -13,6 +13,7 @@
 #include "decode_pair.cuh"
 #include "gemm_int8_mma.cuh"
 #include "gemm_int15.cuh"
+#include "gemm_int8_tma.cuh"
 #include "decoder.cuh"
 #include "gemm_tile.cuh"
 #include "gemm_skinny.cuh"
@@ -696,8 +697,14 @@ int64_t b200i_gemm_int8(int64_t device, void *stream, float *c, const int8_t *qa
     if (select_device(device, err, err_cap, &dev)) return 1;
     const long long cells = m * n;
     // the tensor-core kernel wherever its 16-byte copies are aligned (k a multiple of 16); one thread per cell otherwise
-    if (gemm_int8_mma_fits(qa, qb, m, n, k))
-        launch_gemm_int8_mma(c, reinterpret_cast<const signed char *>(qa), ea, reinterpret_cast<const signed char *>(qb), eb, (int)m, (int)n, (int)k, sm_count(dev), static_cast<cudaStream_t>(stream));
+    if (gemm_int8_mma_fits(qa, qb, m, n, k)) {
+        const signed char *sa = reinterpret_cast<const signed char *>(qa), *sb = reinterpret_cast<const signed char *>(qb);
+        const int sms = sm_count(dev);
+        // enough 128 x 256 tiles for every SM: the persistent kernel fed by tensor-map copies; else the per-tile kernel
+        const long long wide = ((m + T8_BM - 1) / T8_BM) * ((n + T8_BN - 1) / T8_BN);
+        if (wide < sms || !launch_gemm_int8_tma(c, sa, ea, sb, eb, (int)m, (int)n, (int)k, sms, static_cast<cudaStream_t>(stream)))
+            launch_gemm_int8_mma(c, sa, ea, sb, eb, (int)m, (int)n, (int)k, sms, static_cast<cudaStream_t>(stream));
+    }
     else
         gemm_int8_flat_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(c, reinterpret_cast<const signed char *>(qa), ea, reinterpret_cast<const signed char *>(qb), eb, (int)m, (int)n, (int)k);
     g_launches++;
