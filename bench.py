@@ -358,7 +358,7 @@ def main():
         i8_ms.append(e0.elapsed_time(e1))
     i8_us = statistics.median(i8_ms) * 1e3
     i8_tops = 2.0 * 4096 ** 3 / (i8_us * 1e-6) / 1e12
-    int8_product = {"kernel": "gemm_int8_mma_kernel (tcgen05.mma kind::i8, int32 accumulator in tensor memory)", "shape": [4096, 4096, 4096],
+    int8_product = {"kernel": "gemm_int8_tma_kernel (tensor-map copies, tcgen05.mma kind::i8, two int32 accumulators in tensor memory)", "shape": [4096, 4096, 4096],
                     "us": i8_us, "tops": i8_tops, "bound": "tensor", "peak": 4500.0, "unit": "TOP/s", "frac": i8_tops / 4500.0,
                     "peak_source": "nominal dense int8 rate of the part (twice the nominal bf16 rate; no measured int8 figure exists)",
                     "l2": "a 160 MB buffer is written between timed launches", "launches_timed": 10,
