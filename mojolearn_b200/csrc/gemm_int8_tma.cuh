@@ -2,7 +2,7 @@
 //
 // gemm_int8_mma.cuh moves its operand tiles with per-thread cp.async copies and a CTA barrier per 128 bytes of k, and
 // that is what bounds it (tensor pipe 12 % busy, long-scoreboard stalls). Here the tile traffic is taken off the threads:
-//   - warp 0, one lane: the producer. Two tensor-map bulk copies (cp.async.bulk.tensor.2d, no multicast) per k-block bring
+//   - warp 0, one lane: the producer. Two tensor-map bulk copies (cp.async.bulk.tensor.2d; every CTA fetches its own tiles) per k-block bring
 //     128 rows of A and 256 rows of B, 128 bytes of k each, into a ring of four 48 KB stages in the 128-byte swizzled
 //     K-major layout; edges and the k tail are zero-filled by the copy engine; completion is counted on the stage's mbarrier;
 //   - warp 1, one lane: the MMA issuer. Four tcgen05.mma.kind::i8 (M 128, N 256, K 32) per stage, the shared-memory
