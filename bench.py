@@ -363,7 +363,25 @@ def main():
                     "peak_source": "nominal dense int8 rate of the part (twice the nominal bf16 rate; no measured int8 figure exists)",
                     "l2": "a 160 MB buffer is written between timed launches", "launches_timed": 10,
                     "note": "no baseline configuration uses this product profile; it is the one place of the path where an MMA is contract-legal"}
-    del flush, qa8, qb8, ea8, eb8
+    # the fifteen-bit profile on the same shape: four int8 plane products per cell (2 * m * n * k counted once)
+    al8 = torch.randint(0, 128, (4096, 4096), generator=gi, device=dev, dtype=torch.int8)
+    bl8 = torch.randint(0, 128, (4096, 4096), generator=gi, device=dev, dtype=torch.int8)
+    for _ in range(3):
+        torch_ops.matmul_int15(qa8, al8, ea8, qb8, bl8, eb8)
+    i15_ms = []
+    for _ in range(10):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch_ops.matmul_int15(qa8, al8, ea8, qb8, bl8, eb8)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        i15_ms.append(e0.elapsed_time(e1))
+    i15_us = statistics.median(i15_ms) * 1e3
+    int8_product["int15i64"] = {"kernel": "gemm_int15_tma_kernel (two int8 planes per operand, three int32 accumulators, recombined in int64)",
+                                "shape": [4096, 4096, 4096], "us": i15_us, "tops": 2.0 * 4096 ** 3 / (i15_us * 1e-6) / 1e12,
+                                "mma_tops": 4 * 2.0 * 4096 ** 3 / (i15_us * 1e-6) / 1e12, "frac_mma": 4 * 2.0 * 4096 ** 3 / (i15_us * 1e-6) / 1e12 / 4500.0}
+    del flush, qa8, qb8, ea8, eb8, al8, bl8
 
     # ---- decode kernel against HBM: weights [11008, 4096] in three storage kinds, one activation row ----
     peaks_file = os.path.join(ROOT, "MEASURED_PEAKS.json")

@@ -12,8 +12,8 @@
 #include "decode.cuh"
 #include "decode_pair.cuh"
 #include "gemm_int8_mma.cuh"
-#include "gemm_int15.cuh"
 #include "gemm_int8_tma.cuh"
+#include "gemm_int15.cuh"
 #include "decoder.cuh"
 #include "gemm_tile.cuh"
 #include "gemm_skinny.cuh"
@@ -749,8 +749,13 @@ int64_t b200i_gemm_int15(int64_t device, void *stream, float *c, const int8_t *a
     const signed char *sah = reinterpret_cast<const signed char *>(ah), *sal = reinterpret_cast<const signed char *>(al);
     const signed char *sbh = reinterpret_cast<const signed char *>(bh), *sbl = reinterpret_cast<const signed char *>(bl);
     // the tensor-core plan wherever its 16-byte copies are aligned (k a multiple of 16); one thread per cell otherwise
-    if (gemm_int15_mma_fits(ah, al, bh, bl, m, n, k))
-        launch_gemm_int15_mma(c, sah, sal, ea, sbh, sbl, eb, (int)m, (int)n, (int)k, static_cast<cudaStream_t>(stream));
+    if (gemm_int15_mma_fits(ah, al, bh, bl, m, n, k)) {
+        // enough 128 x 64 tiles for every SM: the persistent kernel fed by tensor-map copies; else the per-tile kernel
+        const int sms = sm_count(dev);
+        const long long tiles = ((m + T8_BM - 1) / T8_BM) * ((n + I15_TN - 1) / I15_TN);
+        if (tiles < 2ll * sms || !launch_gemm_int15_tma(c, sah, sal, ea, sbh, sbl, eb, (int)m, (int)n, (int)k, sms, static_cast<cudaStream_t>(stream)))
+            launch_gemm_int15_mma(c, sah, sal, ea, sbh, sbl, eb, (int)m, (int)n, (int)k, static_cast<cudaStream_t>(stream));
+    }
     else
         gemm_int15_flat_kernel<<<(unsigned)((m * n + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(c, sah, sal, ea, sbh, sbl, eb, (int)m, (int)n, (int)k);
     g_launches++;

@@ -10,6 +10,7 @@
 // the sum in int64) serves k that is not a multiple of 16. Both are the profile: an exact sum has one value.
 #pragma once
 #include "gemm_int8_mma.cuh"
+#include "gemm_int8_tma.cuh"
 
 namespace b200i {
 
@@ -244,6 +245,181 @@ inline void launch_gemm_int15_mma(float *c, const signed char *ah, const signed 
     cudaFuncSetAttribute(gemm_int15_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, I15_SMEM_BYTES);
     const dim3 grid((unsigned)((m + I8_TILE_M - 1) / I8_TILE_M), (unsigned)((n + I15_TN - 1) / I15_TN));
     gemm_int15_mma_kernel<<<grid, I8_THREADS, I15_SMEM_BYTES, st>>>(c, ah, al, ea, bh, bl, eb, m, n, k);
+}
+
+// ---- the same plan as a persistent, warp-specialised kernel (the structure of gemm_int8_tma_kernel) --------------------------
+// One CTA per SM walks 128 x 64 tiles. A stage is 128 bytes of k of the four planes (A hi, A lo: 128 rows; B hi, B lo: 64
+// rows; 48 KB), brought by four tensor-map copies into the 128-byte swizzled K-major layout, three stages; the MMA lane
+// issues HH, HL, LH, LL per 32 steps of k into three accumulators of 64 columns; two such accumulator sets (at columns 0 and
+// 256 of tensor memory) let the eight store warps recombine, convert and store one tile under the next tile's MMAs.
+constexpr int F15_STAGES = 3, F15_STAGE_BYTES = 2 * T8_A_BYTES + 2 * I15_TN * T8_BK, F15_ACC_STRIDE = 256;
+constexpr int F15_TURN_BYTES = T8_STORE_WARPS * 32 * 33 * 8;
+constexpr int F15_SMEM_BYTES = 1024 + F15_STAGES * F15_STAGE_BYTES + F15_TURN_BYTES + 256;
+
+__global__ void __launch_bounds__(T8_THREADS, 1)
+gemm_int15_tma_kernel(const __grid_constant__ CUtensorMap map_ah, const __grid_constant__ CUtensorMap map_al, const __grid_constant__ CUtensorMap map_bh,
+                      const __grid_constant__ CUtensorMap map_bl, float *__restrict__ c, const int *__restrict__ ea, const int *__restrict__ eb, int m,
+                      int n, int k, int tiles_n, int tiles) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int B_BYTES = I15_TN * T8_BK;
+    unsigned char *ring = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
+    unsigned long long *turn_all = reinterpret_cast<unsigned long long *>(ring + F15_STAGES * F15_STAGE_BYTES);
+    unsigned long long *full = reinterpret_cast<unsigned long long *>(ring + F15_STAGES * F15_STAGE_BYTES + F15_TURN_BYTES);
+    unsigned long long *empty = full + F15_STAGES, *tfull = empty + F15_STAGES, *tempty = tfull + 2;
+    unsigned *tmem_slot = reinterpret_cast<unsigned *>(tempty + 2);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kt_count = (k + T8_BK - 1) / T8_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < F15_STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], T8_STORE_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(T8_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) { // ---------------- producer ----------------
+            int it = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
+                const int tm = tile / tiles_n, tn = tile - tm * tiles_n;
+                for (int kt = 0; kt < kt_count; kt++, it++) {
+                    const int s = it % F15_STAGES;
+                    const unsigned ph = (unsigned)(it / F15_STAGES) & 1u;
+                    if (!mbar_wait(&empty[s], ph ^ 1u)) {
+                        atomicExch(&g_decode_status, 9);
+                        alive = false;
+                        break;
+                    }
+                    unsigned char *st = ring + s * F15_STAGE_BYTES;
+                    mbar_expect_tx(&full[s], (unsigned)F15_STAGE_BYTES);
+                    t8_tma_load(st, &map_ah, &full[s], kt * T8_BK, tm * T8_BM);
+                    t8_tma_load(st + T8_A_BYTES, &map_al, &full[s], kt * T8_BK, tm * T8_BM);
+                    t8_tma_load(st + 2 * T8_A_BYTES, &map_bh, &full[s], kt * T8_BK, tn * I15_TN);
+                    t8_tma_load(st + 2 * T8_A_BYTES + B_BYTES, &map_bl, &full[s], kt * T8_BK, tn * I15_TN);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) { // ---------------- MMA issuer ----------------
+            int it = 0, ti = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ti++) {
+                const int acc = ti & 1;
+                const unsigned aph = (unsigned)(ti >> 1) & 1u;
+                if (!mbar_wait(&tempty[acc], aph ^ 1u)) {
+                    atomicExch(&g_decode_status, 9);
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned d = tmem + (unsigned)(acc * F15_ACC_STRIDE);
+                for (int kt = 0; kt < kt_count; kt++, it++) {
+                    const int s = it % F15_STAGES;
+                    const unsigned ph = (unsigned)(it / F15_STAGES) & 1u;
+                    if (!mbar_wait(&full[s], ph)) {
+                        atomicExch(&g_decode_status, 9);
+                        alive = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned a_hi = smem_u32(ring + s * F15_STAGE_BYTES), a_lo = a_hi + T8_A_BYTES, b_hi = a_hi + 2 * T8_A_BYTES, b_lo = b_hi + B_BYTES;
+#pragma unroll
+                    for (int j = 0; j < T8_BK / 32; j++) {
+                        const unsigned more = (kt > 0 || j > 0) ? 1u : 0u;
+                        const unsigned long long dah = t8_smem_desc(a_hi + j * 32), dal = t8_smem_desc(a_lo + j * 32);
+                        const unsigned long long dbh = t8_smem_desc(b_hi + j * 32), dbl = t8_smem_desc(b_lo + j * 32);
+                        i8_mma(d, dah, dbh, i8_idesc(I15_TN), more);              // HH
+                        i8_mma(d + I15_TN, dah, dbl, i8_idesc(I15_TN), more);     // HL ...
+                        i8_mma(d + I15_TN, dal, dbh, i8_idesc(I15_TN), 1u);       // ... + LH
+                        i8_mma(d + 2 * I15_TN, dal, dbl, i8_idesc(I15_TN), more); // LL
+                    }
+                    i8_commit(&empty[s]);
+                }
+                if (alive) i8_commit(&tfull[acc]);
+            }
+        }
+    } else { // ---------------- store warps: quarter of the lanes (warp % 4), half of the 64 columns each ----------------
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        unsigned long long *turn = turn_all + (warp - 2) * (32 * 33);
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ti++) {
+            const int tm = tile / tiles_n, tn = tile - tm * tiles_n;
+            const int acc = ti & 1;
+            const unsigned aph = (unsigned)(ti >> 1) & 1u;
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(&tfull[acc], aph))) {
+                if (lane == 0) atomicExch(&g_decode_status, 9);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int rbase = tm * T8_BM + q * 32, cb = half * 32, col0 = tn * I15_TN;
+            if (col0 + cb < n) { // uniform over the warp
+                const int ea_mine = rbase + lane < m ? ea[rbase + lane] : 0;
+                long long sum[32];
+#pragma unroll
+                for (int part = 0; part < 3; part++) {
+                    unsigned v[32];
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+                        "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                        : "r"(tmem + ((unsigned)(q * 32) << 16) + (unsigned)(acc * F15_ACC_STRIDE + part * I15_TN + cb))
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const long long piece = (long long)(int)v[j];
+                        sum[j] = part == 0 ? piece * 16384 : (part == 1 ? sum[j] + piece * 128 : sum[j] + piece);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 32; j++) turn[lane * 33 + j] = (unsigned long long)sum[j];
+                __syncwarp();
+                const int col = col0 + cb + lane;
+                const long long eb_mine = col < n ? (long long)__ldg(eb + col) : 0;
+#pragma unroll 4
+                for (int rr = 0; rr < 32; rr++) {
+                    const long long esum = (long long)__shfl_sync(0xFFFFFFFFu, ea_mine, rr) + eb_mine;
+                    if (rbase + rr < m && col < n)
+                        c[(size_t)(rbase + rr) * n + col] = nan_canon(dequant_int15_pinned((long long)turn[rr * 33 + lane], esum));
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[acc]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(T8_TMEM_COLS) : "memory");
+}
+
+// Returns false when the tensor maps cannot be made (the caller then takes gemm_int15_mma_kernel).
+inline bool launch_gemm_int15_tma(float *c, const signed char *ah, const signed char *al, const int *ea, const signed char *bh, const signed char *bl,
+                                  const int *eb, int m, int n, int k, int sms, cudaStream_t st) {
+    alignas(64) CUtensorMap map_ah, map_al, map_bh, map_bl;
+    if (!t8_make_map(&map_ah, ah, m, k, T8_BM) || !t8_make_map(&map_al, al, m, k, T8_BM) || !t8_make_map(&map_bh, bh, n, k, I15_TN) ||
+        !t8_make_map(&map_bl, bl, n, k, I15_TN))
+        return false;
+    const int tiles_m = (m + T8_BM - 1) / T8_BM, tiles_n = (n + I15_TN - 1) / I15_TN, tiles = tiles_m * tiles_n;
+    cudaFuncSetAttribute(gemm_int15_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F15_SMEM_BYTES);
+    gemm_int15_tma_kernel<<<tiles < sms ? tiles : sms, T8_THREADS, F15_SMEM_BYTES, st>>>(map_ah, map_al, map_bh, map_bl, c, ea, eb, m, n, k, tiles_n, tiles);
+    return true;
 }
 
 } // namespace b200i
