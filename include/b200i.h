@@ -266,6 +266,10 @@ int64_t b200i_kv_append(int64_t device, void *stream, float *cache, const float 
  * attention, transformer/impl/llama/fused_attention.mojo:5: same fold order, nothing materialised) and leaves
  * the scratch untouched. head_dim <= 128. `softcap` (0 = none) caps every scaled score as cap * tanh(score / cap)
  * before the mask is added (transformer_oracle.mojo:2269-2281). */
+/* Floats of score scratch b200i_attention / b200i_attention_at need for (b, l, n_heads, s keys): the whole block for a
+ * decode step; for a prompt the block of as many sequences as fit 4 GB (at least one): a larger batch is walked through
+ * that scratch a few sequences at a time. */
+int64_t b200i_attention_scratch_floats(int64_t b, int64_t l, int64_t n_heads, int64_t s);
 int64_t b200i_attention(int64_t device, void *stream, float *ctx, const float *q, const float *kcache, const float *vcache,
                         float *scores, int64_t b, int64_t l, int64_t n_heads, int64_t n_kv, int64_t head_dim, int64_t cap,
                         int64_t used, int64_t window, double softcap, char *err, int64_t err_cap);

@@ -56,6 +56,7 @@ SIGNATURES = {
     "b200i_from_bf16": [I64, VP, VP, VP, I64, VP, I64],
     "b200i_quantize_int8": [I64, VP, VP, VP, VP, I64, I64, VP, I64],
     "b200i_dequantize_int8": [I64, VP, VP, VP, VP, I64, I64, VP, I64],
+    "b200i_attention_scratch_floats": [I64, I64, I64, I64],
     "b200i_gemm_int8": [I64, VP, VP, VP, VP, VP, VP, I64, I64, I64, VP, I64],
     "b200i_quantize_int15": [I64, VP, VP, VP, VP, VP, I64, I64, VP, I64],
     "b200i_dequantize_int15": [I64, VP, VP, VP, VP, VP, I64, I64, VP, I64],

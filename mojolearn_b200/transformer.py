@@ -522,12 +522,12 @@ class TransformerBlock(object):
         att.__enter__()
         if position is None:
             s = used - (max(0, pos0 - (self.window - 1)) if self.window else 0)
-            scores = torch.empty((b * self.heads_local * l * s,), dtype=torch.float32, device=dev)
+            scores = torch.empty((_native.lib().b200i_attention_scratch_floats(b, l, self.heads_local, s),), dtype=torch.float32, device=dev)
             _native.call("b200i_attention", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
                          self.heads_local, self.kv_local, self.head_dim, cap, used, self.window, self.attn_softcap)
         else:
             s = min(cap, self.window - 1 + l) if self.window else cap  # the most keys any later position sees
-            scores = torch.empty((b * self.heads_local * l * s,), dtype=torch.float32, device=dev)
+            scores = torch.empty((_native.lib().b200i_attention_scratch_floats(b, l, self.heads_local, s),), dtype=torch.float32, device=dev)
             _native.call("b200i_attention_at", dev.index, st, _vp(ctx), _vp(qr), _vp(state.k), _vp(state.v), _vp(scores), b, l,
                          self.heads_local, self.kv_local, self.head_dim, cap, _vp(position), self.window, self.attn_softcap)
         att.__exit__()
