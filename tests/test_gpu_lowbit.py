@@ -207,7 +207,7 @@ def test_int8_product_on_tensor_cores():
     """k a multiple of 16: the product runs as tcgen05 int8 MMAs into an int32 accumulator in tensor memory. Ragged tiles
     in m and n, k below / at / across the 128-byte stage, the largest sums an int32 can hold, extreme exponents."""
     rng = np.random.default_rng(10)
-    for (m, n, k) in [(1, 7, 16), (37, 41, 1008), (128, 128, 128), (130, 257, 400), (300, 515, 4096), (5, 129, 144), (2048, 2600, 272), (1300, 4100, 640)]:
+    for (m, n, k) in [(1, 7, 16), (37, 41, 1008), (128, 128, 128), (130, 257, 400), (300, 515, 4096), (5, 129, 144), (2048, 2600, 272), (1300, 4100, 640), (256, 70003, 64)]:
         qa = rng.integers(-127, 128, (m, k)).astype(np.int8)
         qb = rng.integers(-127, 128, (n, k)).astype(np.int8)
         ea = rng.integers(-20, 20, m).astype(np.int32)
@@ -240,7 +240,7 @@ def test_int15_profile_against_the_oracle():
     assert hi.tobytes() == ohi.tobytes() and lo.tobytes() == olo.tobytes() and e.tobytes() == oe.tobytes()
     assert linalg.dequantize_int15(hi, lo, e).tobytes() == oracle.dequantize_int15(ohi, olo, oe).tobytes()
     for (m, n, k) in [(1, 7, 16), (37, 41, 1008), (128, 64, 128), (130, 257, 400), (300, 515, 2048), (5, 129, 144), (1300, 2100, 640),
-                      (37, 41, 1000), (3, 5, 7)]:
+                      (37, 41, 1000), (3, 5, 7), (130, 70003, 48)]:
         a = (rng.standard_normal((m, k)) * np.exp2(rng.integers(-20, 20, (m, 1)))).astype(np.float32)
         b = (rng.standard_normal((n, k)) * np.exp2(rng.integers(-20, 20, (n, 1)))).astype(np.float32)
         qa, qb = oracle.quantize_int15(a), oracle.quantize_int15(b)
