@@ -29,7 +29,7 @@ import numpy as np
 import torch
 
 from .. import _native
-from ..parallel import PeerExchange, exchange_heads, gather_columns, shard_bounds
+from ..parallel import ExchangeUnavailable, PeerExchange, exchange_heads, gather_columns, shard_bounds
 from ..transformer import Linear, ShardedLinear, TransformerBlock, TransformerState, _stream, _vector, _vp, add, add_norm, norm, NORM_KINDS
 
 
@@ -129,8 +129,11 @@ class CausalLM(object):
                 rows = self.EXCHANGE_ROWS
                 hd = cfg.head_dim
                 per_block = rows * (cfg.n_heads * hd + 2 * cfg.d_model + cfg.intermediate) + 4 * 64  # words of a block's four gathers
-                self.exchange = PeerExchange(group, self.device, rows, max(cfg.vocab, cfg.intermediate, cfg.d_model, cfg.n_heads * hd),
-                                             cfg.n_layers * per_block + rows * cfg.vocab + 64)
+                try:
+                    self.exchange = PeerExchange(group, self.device, rows, max(cfg.vocab, cfg.intermediate, cfg.d_model, cfg.n_heads * hd),
+                                                 cfg.n_layers * per_block + rows * cfg.vocab + 64)
+                except ExchangeUnavailable:  # raised by every rank together: the gathers go through NCCL
+                    self.exchange = None
         for i in range(cfg.n_layers):
             bw = {}
             for key, val in weights.items():

@@ -12,6 +12,7 @@ is the same: byte copies only, never a collective that picks an order
 (training/byte_lm_parallel.py:2-8, core/multi_gpu.mojo:2-6).
 """
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -86,6 +87,10 @@ class ExchangePlan(object):
         return site, offset
 
 
+class ExchangeUnavailable(RuntimeError):
+    """Raised by every rank together when the peer exchange cannot be set up on some rank."""
+
+
 class PeerExchange(object):
     """This rank's end of the store-side exchange of the CUDA library (`b200i_comm_*`): a buffer every rank of the
     node maps, into which the owners of column slices store their words. One object per model; `begin_step()` at
@@ -104,20 +109,42 @@ class PeerExchange(object):
         self.total_bytes = first_zone + (int(step_words) * 8 + 255) // 256 * 256
         self.plan = ExchangePlan(self.world, first_zone, self.total_bytes)
         self._native = _native
-        comm = ctypes.c_void_p()
-        _native.call("b200i_comm_create", self.device.index, self.rank, self.world, self.total_bytes, ctypes.byref(comm))
-        self.comm = comm
+        # Every rank takes every collective below whatever happens to it, and the ranks agree at the end whether the
+        # exchange stands: a rank that cannot create or map a buffer (no peer access, no IPC) must not leave the others
+        # waiting, and all of them then raise ExchangeUnavailable together (the caller falls back to NCCL gathers).
+        comm, ok = ctypes.c_void_p(), 1
         handle = ctypes.create_string_buffer(64)
-        _native.call("b200i_comm_export", comm, ctypes.cast(handle, ctypes.c_void_p), 64)
-        mine = torch.tensor(list(handle.raw), dtype=torch.uint8, device=self.device)
+        try:
+            if os.environ.get("MOJOLEARN_B200_EXCHANGE_FAIL_RANK") == str(self.rank):  # failure injection for the tests, on the host
+                raise RuntimeError("injected exchange set-up failure")
+            _native.call("b200i_comm_create", self.device.index, self.rank, self.world, self.total_bytes, ctypes.byref(comm))
+            _native.call("b200i_comm_export", comm, ctypes.cast(handle, ctypes.c_void_p), 64)
+        except Exception:  # noqa: BLE001
+            ok = 0
+        self.comm = comm
+        mine = torch.tensor(list(handle.raw) + [ok], dtype=torch.uint8, device=self.device)
         everyone = [torch.empty_like(mine) for _ in range(self.world)]
         dist.all_gather(everyone, mine, group=group)
-        for peer, h in enumerate(everyone):
-            if peer != self.rank:
-                raw = bytes(h.cpu().tolist())
-                _native.call("b200i_comm_attach", comm, peer, ctypes.cast(ctypes.create_string_buffer(raw, 64), ctypes.c_void_p))
-        torch.cuda.synchronize(self.device)
-        dist.barrier(group)  # every rank has zeroed its buffer and mapped every peer before anyone sends
+        rows = [bytes(h.cpu().tolist()) for h in everyone]
+        ok = int(all(r[64] == 1 for r in rows))
+        if ok:
+            try:
+                for peer, raw in enumerate(rows):
+                    if peer != self.rank:
+                        _native.call("b200i_comm_attach", comm, peer, ctypes.cast(ctypes.create_string_buffer(raw[:64], 64), ctypes.c_void_p))
+                torch.cuda.synchronize(self.device)
+            except Exception:  # noqa: BLE001
+                ok = 0
+        agreed = torch.tensor([ok], dtype=torch.int32, device=self.device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)  # also the barrier: every rank has zeroed its buffer and mapped every peer before anyone sends
+        if int(agreed.item()) != 1:
+            if comm:
+                try:
+                    _native.lib().b200i_comm_destroy(comm)
+                except Exception:  # noqa: BLE001
+                    pass
+            self.comm = None
+            raise ExchangeUnavailable("a rank could not create or map the peer exchange buffers")
         self._token = None
 
     def _stream(self):

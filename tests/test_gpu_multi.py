@@ -31,11 +31,13 @@ def _run(cmd, **extra):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_sharded_serving_equals_single_gpu():
     one = _run([sys.executable, "-m", "mojolearn_b200.serve_bench"] + ARGS)
-    variants = (dict(), dict(MOJOLEARN_B200_EXCHANGE="0"), dict(MOJOLEARN_B200_PREFILL="columns"))
+    # the last variant injects a host-side failure into rank 1's exchange set-up: every rank must then agree to fall back
+    variants = (dict(), dict(MOJOLEARN_B200_EXCHANGE="0"), dict(MOJOLEARN_B200_PREFILL="columns"), dict(MOJOLEARN_B200_EXCHANGE_FAIL_RANK="1"))
     for i, extra in enumerate(variants):
         launch = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
                   "--master-port", str(29517 + i), "-m", "mojolearn_b200.serve_bench"] + ARGS  # a port of its own: the last run's may linger
         two = _run(launch, **extra)
         assert two["n_gpus"] == 2, extra
         assert one["ids_sha256"] == two["ids_sha256"] and one["logits_sha256"] == two["logits_sha256"], extra
-        assert two["config"]["gathers"] == ("NCCL all-gather" if extra.get("MOJOLEARN_B200_EXCHANGE") == "0" else "peer stores"), extra
+        nccl = extra.get("MOJOLEARN_B200_EXCHANGE") == "0" or "MOJOLEARN_B200_EXCHANGE_FAIL_RANK" in extra
+        assert two["config"]["gathers"] == ("NCCL all-gather" if nccl else "peer stores"), extra
