@@ -100,6 +100,15 @@ int64_t b200i_gemm_w_plan(int64_t device, void *stream, float *c, const float *a
 int64_t b200i_gemm_w_epilogue(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale, int64_t wkind,
                               int64_t m, int64_t n, int64_t k, int64_t op, const float *bias, int64_t act, int64_t plan,
                               int64_t group_leaves, void *ws, int64_t ws_bytes, char *err, int64_t err_cap);
+
+/* b200i_gemm_w_epilogue with the automatic plan, except that a product split into leaf groups is
+ * left unfolded for a caller that folds it elsewhere (b200i_comm_gather_nodes, the gather after a
+ * column-sharded product): *nodes = the number of nodes per cell left in ws[nodes][m * n], and c is
+ * untouched; *nodes = 1 means c holds the finished product with its epilogue, as usual (the plan did
+ * not split, or n is not a multiple of 4). */
+int64_t b200i_gemm_w_nodes(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale, int64_t wkind,
+                           int64_t m, int64_t n, int64_t k, int64_t op, const float *bias, int64_t act, void *ws, int64_t ws_bytes,
+                           int64_t *nodes, char *err, int64_t err_cap);
 int64_t b200i_pair_epilogue_fits(int64_t m, int64_t n, int64_t k, int64_t op);
 
 /* Device timing of the product's main kernel, for benchmarks. While enabled (enable = 1 also
@@ -342,6 +351,12 @@ int64_t b200i_argmax(int64_t device, void *stream, int32_t *out, const float *lo
  *                        one step must not overlap, a step must have at least two gathers, and the
  *                        first gather's area must not overlap any other gather's of any step.
  *                        mode 0 = send and receive; 1 = send only; 2 = receive only (src ignored).
+ *   b200i_comm_gather_nodes  the same gather for a slice that b200i_gemm_w_nodes left as `nodes`
+ *                        (2 to 64) leaf-group nodes ws[nodes][m * n]: the kernel folds them in the
+ *                        contract's order, applies the store epilogue (bias, act; a gated act halves
+ *                        the slice's width w to n / 2) and sends the finished words. n a multiple of
+ *                        4; mode 0 or 1. Bitwise the result of the finished product followed by
+ *                        b200i_comm_gather, in one launch instead of two.
  *   b200i_comm_destroy   after a host barrier: unmaps the peers and frees the buffer. */
 int64_t b200i_comm_create(int64_t device, int64_t rank, int64_t world, int64_t bytes, void **comm, char *err, int64_t err_cap);
 int64_t b200i_comm_export(void *comm, void *handle, int64_t handle_bytes, char *err, int64_t err_cap);
@@ -350,6 +365,8 @@ int64_t b200i_comm_attach_local(void *comm, int64_t peer, void *other, char *err
 int64_t b200i_comm_advance(void *comm, void *stream, char *err, int64_t err_cap);
 int64_t b200i_comm_gather(void *comm, void *stream, int64_t mode, int64_t area_bytes, float *out, int64_t out_ld, const float *src,
                           int64_t m, int64_t w, int64_t src_ld, char *err, int64_t err_cap);
+int64_t b200i_comm_gather_nodes(void *comm, void *stream, int64_t mode, int64_t area_bytes, float *out, int64_t out_ld, const float *ws,
+                                int64_t nodes, int64_t m, int64_t n, const float *bias, int64_t act, char *err, int64_t err_cap);
 int64_t b200i_comm_destroy(void *comm);
 
 /* Status word of the bounded device-side waits on `device` (synchronises the

@@ -51,6 +51,7 @@ SIGNATURES = {
     "b200i_gemm_f32_noalloc": [I64, VP, VP, VP, VP, I64, I64, I64, I64, VP, I64],
     "b200i_gemm_w": [I64, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, VP, I64, VP, I64],
     "b200i_gemm_w_epilogue": [I64, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, VP, I64, I64, I64, VP, I64, VP, I64],
+    "b200i_gemm_w_nodes": [I64, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, VP, I64, VP, I64, VP, VP, I64],
     "b200i_gemm_w_plan": [I64, VP, VP, VP, VP, VP, I64, I64, I64, I64, I64, I64, I64, VP, I64, VP, I64],
     "b200i_to_bf16": [I64, VP, VP, VP, I64, VP, I64],
     "b200i_from_bf16": [I64, VP, VP, VP, I64, VP, I64],
@@ -100,6 +101,7 @@ SIGNATURES = {
     "b200i_comm_attach_local": [VP, I64, VP, VP, I64],
     "b200i_comm_advance": [VP, VP, VP, I64],
     "b200i_comm_gather": [VP, VP, I64, I64, VP, I64, VP, I64, I64, I64, VP, I64],
+    "b200i_comm_gather_nodes": [VP, VP, I64, I64, VP, I64, VP, I64, I64, I64, VP, I64, VP, I64],
     "b200i_comm_destroy": [VP],
 }
 STRING_FUNCTIONS = ["b200i_numerical_profile", "b200i_vendor"]

@@ -348,7 +348,11 @@ unsigned grid_for(long long work_items, int block, int sms) {
 
 int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const void *b, const void *bscale, int wkind,
                        int64_t m, int64_t n, int64_t k, int op, int plan_kind, int64_t group_leaves, void *ws,
-                       int64_t ws_bytes, char *err, int64_t err_cap, Epilogue epi = Epilogue{nullptr, EPI_ACT_NONE}) {
+                       int64_t ws_bytes, char *err, int64_t err_cap, Epilogue epi = Epilogue{nullptr, EPI_ACT_NONE},
+                       int64_t *leave_nodes = nullptr) {
+    // leave_nodes: the caller folds the leaf-group nodes itself (the gather that follows a sharded product does); on
+    // return it holds the number of nodes per cell left in ws, 1 when c is finished as usual
+    if (leave_nodes) *leave_nodes = 1;
     if (m <= 0 || n <= 0 || k <= 0)
         return fail(err, err_cap, "identical gemm: m, n and k must be positive (got m=%lld n=%lld k=%lld)", (long long)m,
                     (long long)n, (long long)k);
@@ -464,7 +468,9 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
         return fail(err, err_cap, "identical gemm: unknown plan %d", plan.kind);
     }
     timing_end(tslot, st);
-    if (plan.groups > 1) {
+    if (plan.groups > 1 && leave_nodes && n % 4 == 0 && aligned(ws, 16)) {
+        *leave_nodes = plan.groups;
+    } else if (plan.groups > 1) {
         const long long cells = (long long)m * n;
         launch_fold_groups(g.ws, c, cells, plan.groups, st, g.epi, g.n);
         g_launches++;
@@ -634,6 +640,18 @@ int64_t b200i_gemm_w_epilogue(int64_t device, void *stream, float *c, const floa
                           ws_bytes, err, err_cap, Epilogue{bias, (int)act});
 }
 
+int64_t b200i_gemm_w_nodes(int64_t device, void *stream, float *c, const float *a, const void *b, const void *bscale, int64_t wkind,
+                           int64_t m, int64_t n, int64_t k, int64_t op, const float *bias, int64_t act, void *ws, int64_t ws_bytes,
+                           int64_t *nodes, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    int dev;
+    if (select_device(device, err, err_cap, &dev)) return 1;
+    if (!nodes) return fail(err, err_cap, "identical gemm: nowhere to report the node count");
+    if (act < EPI_ACT_NONE || act > EPI_PAIR_GEGLU_TANH) return fail(err, err_cap, "identical gemm: unknown store activation %lld", (long long)act);
+    if (bias && !aligned(bias, 4)) return fail(err, err_cap, "identical gemm: misaligned storage");
+    return launch_product(dev, static_cast<cudaStream_t>(stream), c, a, b, bscale, (int)wkind, m, n, k, (int)op, PLAN_AUTO, 0, ws, ws_bytes, err,
+                          err_cap, Epilogue{bias, (int)act}, nodes);
+}
 
 int64_t b200i_to_bf16(int64_t device, void *stream, uint16_t *dst, const float *src, int64_t count, char *err,
                       int64_t err_cap) {
@@ -1406,6 +1424,33 @@ int64_t b200i_comm_gather(void *comm, void *stream, int64_t mode, int64_t area_b
     else
         comm_gather_kernel<false><<<grid, COMM_THREADS, 0, st>>>(c->peers, c->epoch, src, src_ld, out, out_ld, area_bytes, (int)m, (int)w, c->world,
                                                                  c->rank, (int)mode, COMM_WAIT_NS);
+    g_launches++;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int64_t b200i_comm_gather_nodes(void *comm, void *stream, int64_t mode, int64_t area_bytes, float *out, int64_t out_ld, const float *ws,
+                                int64_t nodes, int64_t m, int64_t n, const float *bias, int64_t act, char *err, int64_t err_cap) {
+    clear(err, err_cap);
+    Comm *c = static_cast<Comm *>(comm);
+    if (!c) return fail(err, err_cap, "comm_gather_nodes: no exchange");
+    if (mode != COMM_SEND_RECV && mode != COMM_SEND) return fail(err, err_cap, "comm_gather_nodes: bad mode");
+    for (int p = 0; p < c->world; p++)
+        if (!c->mapped[p]) return fail(err, err_cap, "comm_gather_nodes: rank %d's buffer is not attached", p);
+    if (act < EPI_ACT_NONE || act > EPI_PAIR_GEGLU_TANH) return fail(err, err_cap, "comm_gather_nodes: unknown store activation %lld", (long long)act);
+    if (!out || !ws || m <= 0 || n <= 0 || n % 4 || nodes < 2 || nodes > MAX_GROUPS || area_bytes < 0 || area_bytes % 16 || m * n > 0x7FFFFFFFll)
+        return fail(err, err_cap, "comm_gather_nodes: bad arguments (n a multiple of 4, 2 to %d nodes)", MAX_GROUPS);
+    const int64_t w = act >= EPI_PAIR_SWIGLU ? n / 2 : n;
+    if (out_ld == 0) out_ld = w * c->world;
+    if (out_ld < w * c->world || out_ld % 2 || !aligned(out, 8) || !aligned(ws, 16) || (bias && !aligned(bias, 4)))
+        return fail(err, err_cap, "comm_gather_nodes: misaligned storage or a row pitch below the row width");
+    if ((size_t)area_bytes + (size_t)m * (size_t)w * c->world * 8 > c->bytes)
+        return fail(err, err_cap, "comm_gather_nodes: the site's receive areas do not fit the exchange buffer");
+    CUDA_TRY(cudaSetDevice(c->dev));
+    const long long cells = m * n;
+    const unsigned subs = (unsigned)((nodes + FOLD_SUB - 1) / FOLD_SUB);
+    comm_fold_gather_kernel<<<(unsigned)((cells / 4 + 31) / 32), 32 * subs, 0, static_cast<cudaStream_t>(stream)>>>(
+        c->peers, c->epoch, ws, (int)nodes, Epilogue{bias, (int)act}, out, out_ld, area_bytes, (int)m, (int)n, c->world, c->rank, (int)mode, COMM_WAIT_NS);
     g_launches++;
     CUDA_TRY(cudaGetLastError());
     return 0;

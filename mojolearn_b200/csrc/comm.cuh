@@ -30,7 +30,8 @@
 #pragma once
 #include <cuda_runtime.h>
 
-#include "decode.cuh" // g_decode_status
+#include "decode.cuh"    // g_decode_status
+#include "gemm_tile.cuh" // fold_push, FOLD_SUB, MAX_GROUPS and the store epilogue
 
 namespace b200i {
 
@@ -131,6 +132,103 @@ comm_gather_kernel(CommPeers peers, const int *epoch_word, const float *__restri
                 }
                 if (alive) out[r * out_ld + (long long)p * w + c] = __uint_as_float((unsigned)v);
             }
+        }
+    }
+    if (!alive) atomicExch(&g_decode_status, 8);
+}
+
+// The same gather for a slice that is still a set of leaf-group nodes: ws[groups][m * n] as a split product leaves
+// them. The kernel folds the nodes exactly as fold_groups_split_kernel does (blocks of eight groups per warp, the
+// block roots three levels up by warp 0), finishes the cells (canonical NaN, bias and activation, or the gated pair
+// store that halves the width), writes them to its own columns of `out` and to every peer, and then receives the
+// peers' columns. One launch instead of a fold launch plus a gather launch after every sharded product of a decode
+// step, and the finished slice is never written to memory on its own. n a multiple of 4; a thread owns four
+// consecutive cells of one row.
+__global__ void __launch_bounds__(32 * MAX_GROUPS / FOLD_SUB)
+comm_fold_gather_kernel(CommPeers peers, const int *epoch_word, const float *__restrict__ ws, int groups, Epilogue epi, float *__restrict__ out,
+                        long long out_ld, long long area, int m, int n, int world, int rank, int mode, unsigned long long wait_ns) {
+    __shared__ float4 roots[MAX_GROUPS / FOLD_SUB][32];
+    const unsigned e = (unsigned)*epoch_word;
+    const bool gated = epilogue_pairs(epi);
+    const int w = gated ? n / 2 : n; // width of the finished slice
+    const long long cells = (long long)m * n, count = (long long)m * w;
+    const int lane = threadIdx.x & 31, sub = threadIdx.x >> 5;
+    const int subs = (groups + FOLD_SUB - 1) / FOLD_SUB;
+    const long long idx = ((long long)blockIdx.x * 32 + lane) * 4;
+    const bool live = idx < cells;
+    const int g0 = sub * FOLD_SUB, gcount = min(FOLD_SUB, groups - g0);
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        float4 x[FOLD_SUB];
+#pragma unroll
+        for (int j = 0; j < FOLD_SUB; j++)
+            if (j < gcount) x[j] = __ldcg(reinterpret_cast<const float4 *>(ws + (size_t)(g0 + j) * (size_t)cells + idx));
+        float stack[3][4];
+#pragma unroll
+        for (int j = 0; j < FOLD_SUB; j++) {
+            if (j >= gcount) break;
+            v[0] = x[j].x; v[1] = x[j].y; v[2] = x[j].z; v[3] = x[j].w;
+            fold_push<4, 3>(stack, v, j, gcount - 1);
+        }
+        roots[sub][lane] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    __syncthreads();
+    if (sub == 0 && live) {
+        float stack[3][4];
+        for (int s2 = 0; s2 < subs; s2++) {
+            const float4 t = roots[s2][lane];
+            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+            fold_push<4, 3>(stack, v, s2, subs - 1);
+        }
+        const long long r = idx / n, col = idx - r * n;
+        float f[4];
+        int nf;
+        long long c0; // first column of this thread's finished words inside the slice
+        if (gated) {
+            f[0] = epilogue_pair_apply(nan_canon(ftz_hw(v[0])), nan_canon(ftz_hw(v[1])), epi.bias, epi.act, col / 2);
+            f[1] = epilogue_pair_apply(nan_canon(ftz_hw(v[2])), nan_canon(ftz_hw(v[3])), epi.bias, epi.act, col / 2 + 1);
+            nf = 2; c0 = col / 2;
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                f[q] = nan_canon(ftz_hw(v[q]));
+                if (epilogue_on(epi)) f[q] = epilogue_apply(f[q], epi.bias, epi.act, col + q);
+            }
+            nf = 4; c0 = col;
+        }
+        float *own = out + r * out_ld + (long long)rank * w + c0;
+        *reinterpret_cast<float2 *>(own) = make_float2(f[0], f[1]);
+        if (nf == 4) *reinterpret_cast<float2 *>(own + 2) = make_float2(f[2], f[3]);
+        const long long at = r * w + c0;
+        for (int j = 1; j < world; j++) {
+            const int p = rank + j < world ? rank + j : rank + j - world;
+            unsigned char *q = peers.base[p] + area + ((long long)rank * count + at) * 8;
+            comm_put2(q, comm_pair(__float_as_uint(f[0]), e), comm_pair(__float_as_uint(f[1]), e));
+            if (nf == 4) comm_put2(q + 16, comm_pair(__float_as_uint(f[2]), e), comm_pair(__float_as_uint(f[3]), e));
+        }
+    }
+    if (mode == COMM_SEND) return;
+    // receive: two words per thread and step over the whole grid, as comm_gather_kernel<true> does
+    const int wv = w / 2;
+    const long long items = (long long)m * wv;
+    const long long stride = (long long)gridDim.x * blockDim.x, i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned long long t0 = comm_now_ns();
+    bool alive = true;
+    const unsigned char *mine = peers.base[rank] + area;
+    for (int j = 1; j < world && alive; j++) {
+        const int p = rank + j < world ? rank + j : rank + j - world;
+        for (long long i = i0; i < items && alive; i += stride) {
+            const long long r = i / wv;
+            const int c = (int)(i - r * wv) * 2;
+            const unsigned char *q = mine + ((long long)p * count + r * w + c) * 8;
+            unsigned spins = 0;
+            unsigned long long a, b;
+            comm_poll2(q, a, b);
+            while ((unsigned)(a >> 32) != e || (unsigned)(b >> 32) != e) {
+                if ((++spins & 63u) == 0u && comm_now_ns() - t0 > wait_ns) { alive = false; break; }
+                comm_poll2(q, a, b);
+            }
+            if (alive) *reinterpret_cast<float2 *>(out + r * out_ld + (long long)p * w + c) = make_float2(__uint_as_float((unsigned)a), __uint_as_float((unsigned)b));
         }
     }
     if (!alive) atomicExch(&g_decode_status, 8);

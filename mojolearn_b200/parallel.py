@@ -173,6 +173,20 @@ class PeerExchange(object):
                           ctypes.c_void_p(part.data_ptr()), m, w, part.stride(0))
         return out
 
+    def takes_shape(self, m, w):
+        """Whether a finished slice of m rows and w columns can go through this exchange (`takes` before the slice exists)."""
+        return m <= self.max_rows and self.plan.fits(m, w)
+
+    def gather_nodes(self, ws, nodes, m, n, bias, act, mode=0):
+        """`gather` for a slice `torch_ops.product_nodes` left as leaf-group nodes: fold, store epilogue, send and
+        receive in one launch (`b200i_comm_gather_nodes`)."""
+        w = n // 2 if act >= 4 else n
+        _, offset = self.plan.place(m, w)
+        out = torch.empty((m, self.world * w), dtype=torch.float32, device=self.device)
+        self._native.call("b200i_comm_gather_nodes", self.comm, self._stream(), mode, offset, ctypes.c_void_p(out.data_ptr()), 0,
+                          ctypes.c_void_p(ws.data_ptr()), nodes, m, n, ctypes.c_void_p(bias.data_ptr()) if bias is not None else None, act)
+        return out
+
     def close(self):
         if self.comm is not None:
             torch.cuda.synchronize(self.device)
@@ -189,6 +203,24 @@ class LoopbackExchange(object):
 
     def __init__(self, world):
         self.world, self.rank = int(world), 0
+        self._comm = None
+
+    def takes_shape(self, m, w):
+        return m * w * 8 <= 16 << 20
+
+    def gather_nodes(self, ws, nodes, m, n, bias, act, mode=0):
+        """The fold-and-send launch of the real exchange with nobody to send to: this rank's columns of the gathered
+        matrix are the model's, the others are left as allocated."""
+        from . import _native
+        if self._comm is None:
+            self._comm = ctypes.c_void_p()
+            _native.call("b200i_comm_create", ws.device.index, 0, 1, 16 << 20, ctypes.byref(self._comm))
+        w = n // 2 if act >= 4 else n
+        out = torch.empty((m, self.world * w), dtype=torch.float32, device=ws.device)
+        _native.call("b200i_comm_gather_nodes", self._comm, ctypes.c_void_p(torch.cuda.current_stream(ws.device).cuda_stream), mode, 0,
+                     ctypes.c_void_p(out.data_ptr()), out.stride(0), ctypes.c_void_p(ws.data_ptr()), nodes, m, n,
+                     ctypes.c_void_p(bias.data_ptr()) if bias is not None else None, act)
+        return out
 
     def begin_step(self):
         pass

@@ -112,6 +112,38 @@ def product(a, b, bscale=None, wkind=W_F32, op=OP_NN, out=None, plan=PLAN_AUTO, 
     return out
 
 
+def product_nodes(a, b, bscale=None, wkind=W_F32, bias=None, act=ACT_NONE):
+    """The NT product of `product` for a caller that folds leaf-group nodes itself (the gather after a column-sharded
+    product). Returns (out, ws, nodes): with nodes == 1 `out` is the finished product; with nodes > 1 `out` is None
+    and ws holds nodes x m x n float32 node words, to be finished by `PeerExchange.gather_nodes`."""
+    _check(a, "a", torch.float32)
+    if wkind == W_BF16 and b.dtype in (torch.int16, torch.bfloat16):
+        b = b.view(torch.uint16)
+    _check(b, "b", _W_DTYPES[wkind])
+    (m, k), (n, k2) = a.shape, b.shape
+    if k != k2:
+        raise ValueError("contracted extents disagree: %d and %d" % (k, k2))
+    if bscale is not None:
+        _check(bscale, "bscale", torch.int32 if wkind == W_INT8_EXP else torch.float32)
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if bias.shape != (n,):
+            raise ValueError("one bias word per output column")
+    dev = a.device
+    n_out = n // 2 if act >= ACT_PAIR_SWIGLU else n
+    out = torch.empty((m, n_out), dtype=torch.float32, device=dev)
+    lib = _native.lib()
+    nodes = ctypes.c_int64(1)
+    with torch.cuda.device(dev):
+        ws_bytes = int(lib.b200i_plan_workspace_bytes(m, n, k, PLAN_AUTO, 0))
+        ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=dev) if ws_bytes else None
+        _native.call("b200i_gemm_w_nodes", dev.index, _stream(dev), _vp(out), _vp(a), _vp(b), _vp(bscale), wkind, m, n, k, OP_NT,
+                     _vp(bias), act, _vp(ws), ws_bytes, ctypes.byref(nodes))
+    if nodes.value > 1:
+        return None, ws, int(nodes.value)
+    return out, None, 1
+
+
 def matmul(a, b, *, transpose_a=False, transpose_b=False, out=None):
     if transpose_a and transpose_b:
         raise ValueError("both transposes are not an operation of the profile; compute (b @ a).T instead")

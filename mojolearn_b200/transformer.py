@@ -16,6 +16,7 @@ Activations may be numpy arrays (copied to the device and back, like the
 reference's host surface) or CUDA torch tensors (stay on the device).
 """
 import ctypes
+import os
 
 import numpy as np
 import torch
@@ -136,6 +137,30 @@ class Linear(object):
             return torch_ops.product(x2d, self.w, self.scale, self.kind, OP_NT, bias=self.bias, act=act)
 
 
+_FOLD_IN_GATHER = os.environ.get("MOJOLEARN_B200_FOLD_IN_GATHER", "1") != "0"  # 0: fold launch and gather launch apart (for timing the difference)
+
+
+def product_gather(lin, x2d, act, group, exchange):
+    """A rank's column slice `lin` of a sharded layer applied to x2d, gathered over the ranks. When the exchange takes
+    the slice, a product that the plan split into leaf groups is left as nodes and the gather kernel folds, finishes and
+    sends them itself (one launch fewer per sharded product of a decode step; the same words either way). `act` may be a
+    gated pair code (the slice then has half the layer's columns)."""
+    m = x2d.shape[0]
+    w = lin.out_features // 2 if act >= torch_ops.ACT_PAIR_SWIGLU else lin.out_features
+    if (_FOLD_IN_GATHER and exchange is not None and hasattr(exchange, "gather_nodes") and lin.out_features % 4 == 0 and x2d.dtype == torch.float32 and
+            x2d.is_contiguous() and exchange.takes_shape(m, w)):
+        with _prof.span("product"):
+            part, ws, nodes = torch_ops.product_nodes(x2d, lin.w, lin.scale, lin.kind, bias=lin.bias, act=act)
+        with _prof.span("gather"):
+            if nodes > 1:
+                return exchange.gather_nodes(ws, nodes, m, lin.out_features, lin.bias, act)
+            return exchange.gather(part)
+    with _prof.span("product"):
+        part = torch_ops.product(x2d, lin.w, lin.scale, lin.kind, OP_NT, bias=lin.bias, act=act)
+    with _prof.span("gather"):
+        return gather_columns(part, group, exchange)  # pure data movement: no arithmetic order is introduced
+
+
 class ShardedLinear(object):
     """Rows [r*N/g, (r+1)*N/g) of a layer on this rank; the call all-gathers the output columns."""
 
@@ -147,9 +172,7 @@ class ShardedLinear(object):
         self.exchange = exchange
 
     def __call__(self, x2d, act=0):
-        part = self.local(x2d, act)
-        with _prof.span("gather"):
-            return gather_columns(part, self.group, self.exchange)  # pure data movement: no arithmetic order is introduced
+        return product_gather(self.local, x2d, act, self.group, self.exchange)
 
 
 class TransformerState(object):
@@ -542,7 +565,11 @@ class TransformerBlock(object):
             act = self.up(n2, act=self.mlp_kind)
         else:
             gu = self.gateup
-            if gu is not None and _native.lib().b200i_pair_epilogue_fits(m, gu.out_features, gu.in_features, OP_NT):
+            gathered = False
+            if gu is not None and _native.lib().b200i_pair_epilogue_fits(m, gu.out_features, gu.in_features, OP_NT) and self.by_heads:
+                # the same, sharded: the gather that follows folds the product's leaf groups and applies the gated store itself
+                act, gathered = product_gather(gu, n2, {0: 4, 4: 5, 5: 6}[self.mlp_kind], self.group, self.exchange), True
+            elif gu is not None and _native.lib().b200i_pair_epilogue_fits(m, gu.out_features, gu.in_features, OP_NT):
                 # a decode-sized call: the gated activation rides in the store of the gate|up product (mlp kinds 0, 4,
                 # 5 = swiglu, geglu, geglu_tanh are the store's pair codes 4, 5, 6)
                 with _prof.span("product"):
@@ -559,7 +586,7 @@ class TransformerBlock(object):
                     up, gate = self.up(n2), self.gate(n2)
                     with _prof.span("activation"):
                         _native.call("b200i_act_mul", dev.index, st, _vp(act), _vp(gate), _vp(up), m, self.inter_local, 0, self.mlp_kind, 0)
-        if self.by_heads:
+        if self.by_heads and not gathered:
             with _prof.span("gather"):
                 act = gather_columns(act, self.group, self.exchange)
         d = self.down(act)

@@ -75,3 +75,67 @@ def test_two_ranks_emulated_on_one_stream():
     assert _native.lib().b200i_decode_status(0) == 0
     _native.lib().b200i_comm_destroy(c0)
     _native.lib().b200i_comm_destroy(c1)
+
+
+def _nodes_product(x, w, scale, kind, bias, act):
+    from mojolearn_b200 import torch_ops
+    return torch_ops.product_nodes(x, w, scale, kind, bias=bias, act=act)
+
+
+def _gather_nodes(comm, mode, area, out, ws, nodes, m, n, bias, act):
+    _native.call("b200i_comm_gather_nodes", comm, None, mode, area, ctypes.c_void_p(out.data_ptr()), out.stride(0),
+                 ctypes.c_void_p(ws.data_ptr()), nodes, m, n, ctypes.c_void_p(bias.data_ptr()) if bias is not None else None, act)
+
+
+@pytest.mark.parametrize("kind", ["f32", "int8"])
+def test_gather_that_folds_the_leaf_groups(kind):
+    """b200i_gemm_w_nodes + b200i_comm_gather_nodes give the words of the finished product followed by the plain
+    gather: plain, bias + gelu and gated stores, two ranks emulated on one stream and a world of one."""
+    from mojolearn_b200 import torch_ops
+    from mojolearn_b200.linalg import OP_NT, W_F32, W_INT8_EXP
+    g = torch.Generator(device="cuda").manual_seed(7)
+    c0, c1, solo = _create(0, 2, 8 << 20), _create(1, 2, 8 << 20), _create(0, 1, 8 << 20)
+    _native.call("b200i_comm_attach_local", c0, 1, c1)
+    _native.call("b200i_comm_attach_local", c1, 0, c0)
+    split = 0
+    cases = ((32, 256, 2048, 0, False), (32, 512, 8192, 0, False), (8, 256, 4096, 1, True), (32, 2048, 2048, 4, False), (5, 64, 6000 - 6000 % 16, 6, True),
+             (1, 128, 2048, 0, False))
+    for epoch, (m, n, k, act, with_bias) in enumerate(cases):
+        for c in (c0, c1, solo):
+            _native.call("b200i_comm_advance", c, None)
+        if act >= 4 and not _native.lib().b200i_pair_epilogue_fits(m, n, k, OP_NT):
+            continue
+        x = torch.randn((m, k), generator=g, device="cuda")
+        shards = []
+        for r in range(2):
+            if kind == "int8":
+                w = torch.randint(-127, 128, (n, k), generator=g, device="cuda", dtype=torch.int8)
+                scale = torch.randint(-12, -4, (n,), generator=g, device="cuda", dtype=torch.int32)
+                wk = W_INT8_EXP
+            else:
+                w, scale, wk = torch.randn((n, k), generator=g, device="cuda"), None, W_F32
+            bias = torch.randn((n,), generator=g, device="cuda") if with_bias else None
+            shards.append((w, scale, wk, bias))
+        want = [torch_ops.product(x, w, s, wk, OP_NT, bias=b, act=act) for (w, s, wk, b) in shards]
+        wout = want[0].shape[1]
+        parts = [_nodes_product(x, w, s, wk, b, act) for (w, s, wk, b) in shards]
+        assert parts[0][2] == parts[1][2]
+        if parts[0][2] == 1:  # the plan did not split: the finished product came back
+            assert torch.equal(parts[0][0], want[0]) and torch.equal(parts[1][0], want[1]), (m, n, k, act)
+            continue
+        split += 1
+        o0 = torch.full((m, 2 * wout), -1.0, device="cuda")
+        o1 = torch.full((m, 2 * wout), -1.0, device="cuda")
+        os_ = torch.full((m, wout), -1.0, device="cuda")
+        _gather_nodes(c0, SEND, 0, o0, parts[0][1], parts[0][2], m, n, shards[0][3], act)
+        _gather_nodes(c1, SEND_RECV, 0, o1, parts[1][1], parts[1][2], m, n, shards[1][3], act)
+        _gather(c0, RECV, 0, o0, None)
+        _gather_nodes(solo, SEND_RECV, 0, os_, parts[0][1], parts[0][2], m, n, shards[0][3], act)
+        torch.cuda.synchronize()
+        both = torch.cat(want, dim=1)
+        assert torch.equal(o0, both) and torch.equal(o1, both), (m, n, k, act)
+        assert torch.equal(os_, want[0]), (m, n, k, act)
+    assert split >= 3, split
+    assert _native.lib().b200i_decode_status(0) == 0
+    for c in (c0, c1, solo):
+        _native.lib().b200i_comm_destroy(c)
