@@ -461,7 +461,7 @@ int64_t launch_product(int dev, cudaStream_t st, float *c, const float *a, const
         if (!skinny_plan_fits(m, n, k, op) || !aligned(b, 16) || !aligned(a, 16))
             return fail(err, err_cap, "identical gemm: the skinny plan needs op NT, m <= 32, k a multiple of 16 and 16-byte aligned operands");
         // low-bit weights stay in registers; float32 windows are too wide for that and go through shared memory
-        if (g.wkind != W_F32) launch_skinny_reg(g, plan.groups, st);
+        if (g.wkind != W_F32) launch_skinny_reg(g, plan.groups, sm_count(dev), st);
         else launch_skinny(g, plan.groups, st);
         g_launches++;
     } else {

@@ -146,7 +146,8 @@ def test_skinny_plan_every_storage_kind():
     rng = np.random.default_rng(11)
     shapes = [(5, 300, 512, 0), (8, 1030, 4096, 8), (9, 520, 2048, 4), (16, 1000, 1024, 0), (17, 700, 4096, 16),
               (32, 513, 2048, 2), (32, 256, 64, 0), (12, 99, 4096 + 128, 8), (3, 2050, 768, 2), (1, 40, 16, 0),
-              (8, 260, 8192, 1), (5, 99, 128 * 43, 1)]  # 64 and 43 leaf groups: the group fold's full and ragged stacks
+              (8, 260, 8192, 1), (5, 99, 128 * 43, 1),  # 64 and 43 leaf groups: the group fold's full and ragged stacks
+              (32, 768, 2048, 1), (27, 600, 2048, 1)]  # 48 CTAs of 32 rows: the low-bit kernel splits the rows once (16 + 16, 16 + 11)
     for (m, n, k, gl) in shapes:
         x = rng.standard_normal((m, k)).astype(np.float32)
         codes = rng.integers(-127, 128, (n, k)).astype(np.int8)
