@@ -229,7 +229,6 @@ void timing_end(int slot, cudaStream_t st) {
 }
 
 size_t round256(size_t v) { return (v + 255) / 256 * 256; }
-size_t round256_sz(size_t v) { return round256(v); }
 
 // rows below which packing the operands costs more than the bulk-copy pipeline returns
 constexpr long long PACKED_MIN_EXTENT = 256;

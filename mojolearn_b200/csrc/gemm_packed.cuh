@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(PK_THREADS, 2) gemm_packed_kernel(const Packed
     unsigned long long *full = reinterpret_cast<unsigned long long *>(pk_smem + PK_STAGES * PK_STAGE_FLOATS);
     unsigned long long *empty = full + PK_STAGES;
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
     const int tile_m = blockIdx.x / g.tiles_n, tile_n = blockIdx.x % g.tiles_n;
     const int t_first = blockIdx.y * g.group_leaves;
     const int t_end = min(t_first + g.group_leaves, g.leaves);
